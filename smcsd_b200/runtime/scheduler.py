@@ -1,0 +1,396 @@
+"""Group scheduler: admission, prefill, fan-out to particles, the decode loop (sequential
+or overlapped with host post-processing), finalize and streaming of results.
+
+Role of the reference's scheduler (smcsd/core/scheduler.py:202-1002): waiting / prefill /
+running group queues, admission against slot capacity with reservations (:236-243,
+:609-650), prefill before decode (:615-630), materialize with rollback (:734-828),
+the overlapped loop whose post-processing runs one step late (:415-488), drain and
+finalize (:960-1002), idle-time leak checks (:518-561).  This scheduler owns the model
+objects and pools directly (the reference reaches them through SGLang's model runner).
+"""
+from __future__ import annotations
+
+import logging
+import os
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional
+
+import torch
+
+from ..config import EngineArgs
+from ..io_types import (AbortReq, GenerateRequest, ParticleOutput, ProfileReq, RequestOutput, RpcReq, RpcResp,
+                        validate_request)
+from ..memory.pools import BlockTable, KVPool, KVSpec, PageAllocator, StatePool, cobudget_pages
+from ..models import build_model
+from ..utils import debug as smc_debug
+from .slot_state import CycleInputs, HostSnapshot, SlotState
+from .worker import PrefillItem, SMCWorker
+
+log = logging.getLogger("smcsd_b200.scheduler")
+
+
+@dataclass
+class SequenceGroup:
+    """One user request and its N particles."""
+    req: GenerateRequest
+    n_particles: int
+    parent_row: Optional[int] = None
+    x0: Optional[int] = None
+    reserved_pages: int = 0
+    t_arrive: float = 0.0
+    t_first_token: float = 0.0
+    cycles: int = 0
+
+    @property
+    def rid(self) -> str:
+        return self.req.rid
+
+
+def _resolve_device(args: EngineArgs, local_rank: int = 0) -> torch.device:
+    if args.device == "cpu":
+        return torch.device("cpu")
+    if args.device in ("auto", "cuda") and torch.cuda.is_available():
+        dev = torch.device("cuda", args.base_gpu_id + local_rank)
+        torch.cuda.set_device(dev)
+        return dev
+    if args.device == "cuda":
+        raise RuntimeError("device='cuda' requested but no GPU is visible")
+    return torch.device("cpu")
+
+
+class SMCScheduler:
+    def __init__(self, args: EngineArgs, *, tp_rank: int = 0, tp_size: int = 1, dp_rank: int = 0,
+                 local_rank: int = 0, target=None, draft=None, comm=None):
+        self.args = args.finalize() if args.defer_bonus is None else args
+        a = self.args
+        self.tp_rank, self.tp_size, self.dp_rank = tp_rank, tp_size, dp_rank
+        self.device = _resolve_device(a, local_rank)
+        on_cuda = self.device.type == "cuda"
+        self.dtype = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}[a.dtype]
+        backend = a.backend
+        if backend == "auto":
+            backend = "native" if on_cuda and self.dtype == torch.bfloat16 else "torch"
+        self.backend = backend
+        if os.environ.get("SMC_SYNC_DEBUG") == "1" and on_cuda:
+            torch.cuda.set_sync_debug_mode("warn")
+        # ---- models -----------------------------------------------------------
+        seed = a.random_seed
+        self.target = target if target is not None else build_model(
+            a.model_path, self.dtype, self.device, tp_rank, tp_size, seed=seed)
+        d_tp = (0, 1) if a.replicate_draft else (tp_rank, tp_size)
+        self.draft = draft if draft is not None else build_model(
+            a.draft_model_path, self.dtype, self.device, d_tp[0], d_tp[1], seed=seed + 1)
+        if self.target.cfg.vocab_size != self.draft.cfg.vocab_size:
+            raise ValueError("target and draft must share a vocabulary")
+        self.context_len = int(a.context_length or min(self.target.cfg.max_position, 16384))
+        # ---- memory -----------------------------------------------------------
+        N, G = a.n_particles, a.gamma + 1
+        self.max_groups = a.max_running_requests
+        n_slots = self.max_groups * N
+        n_parent_rows = max(self.max_groups, 4)
+        kv_t = KVSpec(len(self.target.cfg.attn_layers), self.target.n_kv_heads, self.target.cfg.head_dim, self.dtype)
+        kv_d = KVSpec(len(self.draft.cfg.attn_layers), self.draft.n_kv_heads, self.draft.cfg.head_dim, self.dtype)
+        n_rows = n_slots + n_parent_rows
+        spec_t, spec_d = self.target.state_spec(), self.draft.state_spec()
+        state_bytes = sum(s.row_bytes * n_rows * (1 + (G if i == 0 else 2)) for i, s in enumerate((spec_t, spec_d)) if s)
+        if a.max_total_tokens:
+            n_pages = int(a.max_total_tokens)
+        elif on_cuda:
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = int(total * a.mem_fraction_static) - (total - free)
+            n_pages = cobudget_pages(budget, kv_t.cell_bytes, kv_d.cell_bytes, 0, state_bytes)
+            n_pages = min(n_pages, self.max_groups * (self.context_len + N * self.context_len))
+        else:
+            n_pages = min(self.max_groups * N * 512 + 4096, 1 << 16)
+        if n_pages < N * G * 2:
+            raise RuntimeError(f"not enough memory for the KV pools (pages={n_pages})")
+        self.alloc = PageAllocator(n_pages, self.device)
+        self.bt = BlockTable(n_slots, n_parent_rows, self.context_len, self.device)
+        self.kv_t = KVPool(kv_t, n_pages, self.device)
+        self.kv_d = KVPool(kv_d, n_pages, self.device)
+        self.state_t = StatePool(spec_t, n_rows, self.device, depth=G) if spec_t else None
+        self.state_d = StatePool(spec_d, n_rows, self.device, depth=2) if spec_d else None
+        # ---- native backend -----------------------------------------------------
+        self.native_state = None
+        self.native_runner = None
+        if backend == "native":
+            from ..ops import native_backend
+            self.native_state, self.native_runner = native_backend.create(self, comm)
+        pools = [p for p in (self.state_t, self.state_d) if p is not None]
+        self.state = SlotState(max_groups=self.max_groups, n_particles=N, gamma=a.gamma,
+                               max_output_len=self.context_len, block_table=self.bt, allocator=self.alloc,
+                               device=self.device, seed=seed, resample_threshold=a.resample_threshold,
+                               resample_method=a.resample_method, state_pools=pools, native=self.native_state)
+        if a.resample_method != "systematic" and backend == "native":
+            raise ValueError("the fused resampling kernels implement 'systematic' only")
+        self.worker = SMCWorker(a, self.target, self.draft, self.kv_t, self.kv_d, self.bt, self.alloc,
+                                self.state_t, self.state_d, native_runner=self.native_runner)
+        # ---- queues -------------------------------------------------------------
+        self.waiting: Deque[SequenceGroup] = deque()
+        self.running: Dict[str, SequenceGroup] = {}
+        self.reserved_pages = 0
+        self.pending: Deque = deque()       # snapshots awaiting host post-processing
+        self.outbox: List = []
+        self.final_gen = torch.Generator().manual_seed(seed * 31 + 5)
+        self.stats = dict(cycles=0, prefills=0, finished=0, aborted=0, resampled_groups=0, decode_tokens=0)
+        self.profiler = None
+        self._profile_steps_left = None
+        self._cycle_events: List = []
+        self.emit_particles = a.emit_particle_output
+
+    # ------------------------------------------------------------------ intake
+    def add_request(self, req: GenerateRequest) -> None:
+        err = validate_request(req, self.context_len, self.args.gamma)
+        if err is None and self.args.max_queued_requests is not None and \
+                len(self.waiting) >= self.args.max_queued_requests:
+            err = "the request queue is full"
+        if err is not None:
+            self.stats["aborted"] += 1
+            self.outbox.append(RequestOutput(req.rid, [], True, {"type": "abort", "message": err},
+                                             len(req.input_ids), 0, aborted=True, error=err))
+            return
+        self.waiting.append(SequenceGroup(req, self.args.n_particles, t_arrive=time.time()))
+
+    def abort(self, rid: str) -> None:
+        for g in list(self.waiting):
+            if g.rid == rid:
+                self.waiting.remove(g)
+                self.outbox.append(RequestOutput(rid, [], True, {"type": "abort"}, aborted=True))
+                return
+        g = self.running.get(rid)
+        if g is not None:
+            self._flush_pending()
+            self._release_group(g)
+            self.outbox.append(RequestOutput(rid, [], True, {"type": "abort"}, aborted=True))
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running or self.pending)
+
+    # ------------------------------------------------------------------ admission
+    def _pages_needed(self, g: SequenceGroup) -> int:
+        L = len(g.req.input_ids)
+        return L + self.args.n_particles * (g.req.sampling_params.max_new_tokens + 2 * (self.args.gamma + 1))
+
+    def _admit(self) -> List[SequenceGroup]:
+        """Admit waiting groups while slots, parent rows and worst-case pages are available.
+        Pages are reserved up front, so a running group can never run the pool dry."""
+        admitted: List[SequenceGroup] = []
+        free_groups = len(self.state.free_rows) - 0
+        while self.waiting and free_groups - len(admitted) > 0:
+            g = self.waiting[0]
+            need = self._pages_needed(g)
+            if need > self.alloc.size:
+                self.waiting.popleft()
+                msg = f"request needs {need} KV pages; the pool holds {self.alloc.size}"
+                self.outbox.append(RequestOutput(g.rid, [], True, {"type": "abort", "message": msg},
+                                                 len(g.req.input_ids), 0, aborted=True, error=msg))
+                self.stats["aborted"] += 1
+                continue
+            if self.reserved_pages + need > self.alloc.size:
+                break
+            row = self.bt.alloc_parent_row()
+            if row is None:
+                break
+            self.waiting.popleft()
+            g.parent_row = row
+            g.reserved_pages = need
+            self.reserved_pages += need
+            admitted.append(g)
+        return admitted
+
+    # ------------------------------------------------------------------ prefill + fan-out
+    def _run_prefill(self, groups: List[SequenceGroup]) -> None:
+        self._flush_pending()               # prefill mutates allocator state from the host
+        items = []
+        for g in groups:
+            L = len(g.req.input_ids)
+            pages = self.alloc.alloc(L)
+            if pages is None:
+                raise RuntimeError("page reservation violated")
+            self.bt.table[g.parent_row, :L] = pages
+            items.append(PrefillItem(g.parent_row, g.req.input_ids))
+        x0 = self.worker.prefill(items).tolist()          # one blocking read per prefill batch
+        self.stats["prefills"] += len(groups)
+        for g, tok in zip(groups, x0):
+            g.x0 = int(tok)
+            g.t_first_token = time.time()
+            self._materialize(g)
+
+    def _materialize(self, g: SequenceGroup) -> None:
+        req, sp = g.req, g.req.sampling_params
+        L = len(req.input_ids)
+        eos = list(req.eos_token_ids or []) + list(sp.stop_token_ids or [])
+        done_eos = (not sp.ignore_eos) and g.x0 in eos
+        if done_eos or sp.max_new_tokens <= 1:
+            # finished at prefill: never fans out
+            reason = {"type": "stop", "matched": g.x0} if done_eos else {"type": "length", "length": 1}
+            self.alloc.dec_ref_and_free(self.bt.table[g.parent_row, :L])
+            self._finish_parent_rows(g)
+            self.outbox.append(RequestOutput(g.rid, [g.x0], True, reason, L, 1))
+            self.stats["finished"] += 1
+            return
+        try:
+            self.state.allocate_group(g.rid, prompt_len=L, x0=g.x0, last_prompt_token=req.input_ids[-1],
+                                      max_new_tokens=sp.max_new_tokens, ignore_eos=sp.ignore_eos, eos_ids=eos,
+                                      parent_row=g.parent_row)
+        except Exception as e:  # roll back and abort this one group
+            log.exception("materialize failed for %s", g.rid)
+            self.alloc.dec_ref_and_free(self.bt.table[g.parent_row, :L])
+            self._finish_parent_rows(g)
+            self.outbox.append(RequestOutput(g.rid, [], True, {"type": "abort", "message": str(e)}, L, 0,
+                                             aborted=True, error=str(e)))
+            self.stats["aborted"] += 1
+            return
+        if self.state_t is not None:
+            pass  # recurrent state fan-out happens inside allocate_group
+        self.bt.free_parent_row(g.parent_row)
+        g.parent_row = None
+        self.running[g.rid] = g
+
+    def _finish_parent_rows(self, g: SequenceGroup) -> None:
+        if g.parent_row is not None:
+            for pool in (self.state_t, self.state_d):
+                if pool is not None:
+                    pool.clear_rows(torch.tensor([g.parent_row], device=self.device))
+            self.bt.free_parent_row(g.parent_row)
+            g.parent_row = None
+        self.reserved_pages -= g.reserved_pages
+        g.reserved_pages = 0
+
+    # ------------------------------------------------------------------ decode
+    def _run_decode(self) -> None:
+        st = self.state
+        if self.native_runner is not None and self.native_runner.can_run_cycle(st):
+            self.native_runner.run_cycle(st, self.worker)          # one captured graph: prologue..resample
+        else:
+            cin = st.prepare_cycle()
+            out = self.worker.decode_cycle(cin)
+            st.write_back(cin, out)
+            n = st.resample()
+            if n > 0:
+                self.stats["resampled_groups"] += n
+        self.stats["cycles"] += 1
+        self.stats["decode_tokens"] += st.bs * (self.args.gamma + 1)
+        snap = st.snapshot_to_host()
+        self.pending.append((snap, list(self.running.keys())))
+
+    def _process_snapshot(self, snap: HostSnapshot, rids: List[str]) -> None:
+        snap.wait()
+        if snap.alloc_error:
+            raise RuntimeError("device page allocator ran dry inside a decode cycle")
+        for rid in rids:
+            g = self.running.get(rid)
+            if g is None:
+                continue
+            g.cycles += 1
+            if not self.state.group_has_active(rid, snap.finished):
+                self._finalize(g)
+
+    def _flush_pending(self) -> None:
+        while self.pending:
+            self._process_snapshot(*self.pending.popleft())
+
+    def _finalize(self, g: SequenceGroup) -> None:
+        res = self.state.finalize_group(g.rid, self.final_gen)
+        L = len(g.req.input_ids)
+        out = RequestOutput(g.rid, res["output_ids"], True, res["finish_reason"], L, len(res["output_ids"]))
+        if self.emit_particles:
+            self.outbox.append(ParticleOutput(g.rid, res["particle_output_ids"], res["log_Z_hat"],
+                                              res["log_w_tilde"], res["picked"]))
+        self.outbox.append(out)
+        smc_debug.append_diag_record({"event": "finalize", "rid": g.rid, "log_Z_hat": res["log_Z_hat"],
+                                      "cycles": g.cycles, "completion_tokens": len(res["output_ids"])})
+        self._release_group(g)
+        self.stats["finished"] += 1
+
+    def _release_group(self, g: SequenceGroup) -> None:
+        self.state.free_group(g.rid)
+        self.running.pop(g.rid, None)
+        self.reserved_pages -= g.reserved_pages
+        g.reserved_pages = 0
+
+    # ------------------------------------------------------------------ one iteration
+    def step(self) -> List:
+        """One scheduler iteration: admitted prefills run before decode; with overlap on, the host
+        post-processes cycle t-1 after enqueuing cycle t (finish detection is one cycle late,
+        which is harmless because finished particles are absorbing)."""
+        if self.profiler is not None:
+            self._profile_tick()
+        admitted = self._admit()
+        if admitted:
+            self._run_prefill(admitted)
+        elif self.running:
+            self._run_decode()
+            keep = 1 if (self.args.enable_overlap and self.device.type == "cuda") else 0
+            while len(self.pending) > keep:
+                self._process_snapshot(*self.pending.popleft())
+        else:
+            self._flush_pending()
+            if not self.waiting:
+                self.check_idle_invariants()
+        out, self.outbox = self.outbox, []
+        return out
+
+    def run_until_idle(self) -> List:
+        outs: List = []
+        while self.has_work():
+            outs.extend(self.step())
+        outs.extend(self.step())
+        return outs
+
+    # ------------------------------------------------------------------ invariants / info
+    def check_idle_invariants(self) -> None:
+        """With nothing running, every page is free and no slot is held."""
+        if self.running or self.pending:
+            return
+        if os.environ.get("SMC_STRICT_MEM_CHECK", "1") != "1":
+            return
+        free = self.alloc.available()
+        if free != self.alloc.size:
+            raise RuntimeError(f"KV page leak: {self.alloc.size - free} pages still held while idle")
+        if len(self.state.free_slots) != self.state.max_slots:
+            raise RuntimeError("slot leak while idle")
+        if self.reserved_pages != 0:
+            raise RuntimeError(f"page reservation leak: {self.reserved_pages}")
+
+    def server_info(self) -> dict:
+        return dict(args=self.args.to_dict(), backend=self.backend, device=str(self.device),
+                    kv_pages=self.alloc.size, context_len=self.context_len, stats=dict(self.stats),
+                    n_running=len(self.running), n_waiting=len(self.waiting),
+                    target=self.target.cfg.name, draft=self.draft.cfg.name)
+
+    def flush_cache(self) -> bool:
+        return not self.has_work()
+
+    # ------------------------------------------------------------------ profiling
+    def handle_profile(self, req: ProfileReq) -> dict:
+        from ..utils.profiling import SchedulerProfiler
+        if req.action == "start":
+            self.profiler = SchedulerProfiler(req, rank=self.tp_rank)
+            self.profiler.start()
+            self._profile_steps_left = req.num_steps
+            return {"ok": True}
+        if self.profiler is not None:
+            path = self.profiler.stop()
+            self.profiler = None
+            return {"ok": True, "trace": path}
+        return {"ok": False, "message": "profiler not running"}
+
+    def _profile_tick(self) -> None:
+        if self._profile_steps_left is None:
+            return
+        if self._profile_steps_left <= 0:
+            self.profiler.stop()
+            self.profiler = None
+            self._profile_steps_left = None
+        else:
+            self._profile_steps_left -= 1
+
+    def handle_rpc(self, req: RpcReq) -> RpcResp:
+        try:
+            fn = getattr(self, req.method)
+            return RpcResp(req.req_id, self.tp_rank, True, fn(**req.kwargs))
+        except Exception as e:
+            return RpcResp(req.req_id, self.tp_rank, False, repr(e))

@@ -1,0 +1,64 @@
+"""End-to-end CPU plumbing run on the tiny Llama pair (fp32, random init, no GPU)."""
+import torch
+
+from smcsd_b200 import SMCEngine
+
+
+def _prompts(n=8, length=32, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, 4096, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def _engine(**kw):
+    base = dict(n_particles=4, gamma=4, draft_temperature=0.7, target_temperature=0.7, dtype="float32",
+                device="cpu", max_running_requests=8, resample_threshold=0.5)
+    base.update(kw)
+    return SMCEngine("preset:tiny-target", "preset:tiny-draft", **base)
+
+
+def test_plumbing_run_tiny_llama():
+    eng = _engine()
+    outs = eng.generate(input_ids=_prompts(), sampling_params={"max_new_tokens": 64, "ignore_eos": True})
+    assert len(outs) == 8
+    for o in outs:
+        assert o["completion_tokens"] == 64 and len(o["output_ids"]) == 64
+        assert o["finish_reason"]["type"] == "length"
+        assert len(o["smc_particle_output_ids"]) == 4
+        assert len(o["smc_log_w_tilde"]) == 4
+        assert all(0 <= t < 4096 for t in o["output_ids"])
+    sched = eng._sched
+    sched.check_idle_invariants()
+    sched.alloc.check_conservation()
+    assert sched.stats["finished"] == 8
+
+
+def test_seed_determinism_and_single_input():
+    a = _engine(random_seed=3).generate(input_ids=_prompts(1)[0], sampling_params={"max_new_tokens": 20, "ignore_eos": True})
+    b = _engine(random_seed=3).generate(input_ids=_prompts(1)[0], sampling_params={"max_new_tokens": 20, "ignore_eos": True})
+    assert isinstance(a, dict)
+    assert a["output_ids"] == b["output_ids"]
+    assert a["smc_log_Z_hat"] == b["smc_log_Z_hat"]
+
+
+def test_legacy_schedule_and_more_requests_than_slots():
+    eng = _engine(defer_bonus=False, max_running_requests=2)
+    outs = eng.generate(input_ids=_prompts(5, 16), sampling_params={"max_new_tokens": 12, "ignore_eos": True})
+    assert [o["completion_tokens"] for o in outs] == [12] * 5
+    eng._sched.check_idle_invariants()
+
+
+def test_eos_stops_and_prefill_finish():
+    eng = _engine()
+    p = _prompts(1)[0]
+    # every token is a stop token: the request ends at x0, before any fan-out
+    o = eng.generate(input_ids=p, sampling_params={"max_new_tokens": 30, "stop_token_ids": list(range(4096))[:8]})
+    assert o["completion_tokens"] >= 1
+    o2 = eng.generate(input_ids=p, sampling_params={"max_new_tokens": 1, "ignore_eos": True})
+    assert o2["completion_tokens"] == 1 and o2["finish_reason"]["type"] == "length"
+    eng._sched.check_idle_invariants()
+
+
+def test_rejected_features_abort():
+    eng = _engine()
+    o = eng.generate(input_ids=_prompts(1)[0], sampling_params={"max_new_tokens": 8, "stop": ["abc"]})
+    assert o.get("aborted") and "stop strings" in o["error"]
