@@ -1,0 +1,180 @@
+#!/usr/bin/env python
+"""Headline benchmark: output tokens/s of SMC speculative decoding, Llama-3.1-8B target +
+Llama-3.2-1B draft, N=8 particles, gamma=8, T=0.7, one request per GPU (data-parallel replicas),
+bf16 random-init weights, synthetic prompts (uniform token ids, log-normal lengths, median 200).
+
+A "step" is one decode cycle: every particle advances gamma+1 = 9 tokens, so each request emits
+9 output tokens per step.  The device-timed value brackets exactly K replays of the cycle with
+CUDA events (max over ranks); the end-to-end value times whole ``SMCEngine.generate`` calls
+(prompt upload from pinned memory, prefill, all cycles, token download).
+
+    python bench.py --gpus 1 --steps 40 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 40 --warmup 5
+    python bench.py --impl reference        # prints why the reference cannot run here
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+PUBLISHED_TOKS = 677.0     # reference docs/smc/performance.md:14-16 (1x B200, 256-token prompts)
+
+
+def reference_arm(args) -> int:
+    """The reference is a thin layer over a patched SGLang fork that is absent from its tree
+    (empty submodule) and from this image, so its stock code path cannot start."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref"))
+    why = None
+    try:
+        import smcsd  # noqa: F401
+        why = "reference imported but no runner is wired"
+    except Exception as e:  # ModuleNotFoundError: sglang
+        why = f"{type(e).__name__}: {e} (smcsd installs, but its SGLang fork submodule is empty and sglang is not on this image)"
+    print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "torch", "reference"])
+    ap.add_argument("--target", default="llama-3.1-8b")
+    ap.add_argument("--draft", default="llama-3.2-1b")
+    ap.add_argument("-N", "--n-particles", type=int, default=8)
+    ap.add_argument("-g", "--gamma", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=0, help="fixed prompt length (0 = log-normal, median 200)")
+    ap.add_argument("--e2e-requests", type=int, default=2)
+    ap.add_argument("--e2e-new-tokens", type=int, default=512)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    from smcsd_b200 import SMCEngine
+    from smcsd_b200.io_types import GenerateRequest, SamplingParams
+    from smcsd_b200.ops import native as K
+    from smcsd_b200.utils.profiling import ClockSampler
+    from smcsd_b200.utils.prompts import lognormal_lengths, random_prompts
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    G = args.gamma + 1
+    steps, warm = args.steps, max(args.warmup, 3)
+    need_tokens = (steps + warm + 4) * G + 1
+    new_tokens = max(512, need_tokens)
+    eng = SMCEngine(f"preset:{args.target}", f"preset:{args.draft}", n_particles=args.n_particles, gamma=args.gamma,
+                    draft_temperature=0.7, target_temperature=0.7, resample_threshold=0.5, max_running_requests=1,
+                    base_gpu_id=local, context_length=4096 + new_tokens, random_seed=rank,
+                    backend="native" if args.impl == "native" else "torch", in_process=True,
+                    cycle_graph=not args.no_graph, mem_fraction_static=0.6)
+    sched = eng._sched
+    vocab = sched.target.cfg.vocab_size
+    lens = [args.prompt_len] if args.prompt_len else lognormal_lengths(1, seed=1000 + rank)
+    prompt = random_prompts(lens, vocab, seed=rank)[0]
+
+    # ---- device-timed region: K decode cycles of one live request ------------------------------
+    sched.add_request(GenerateRequest("bench", prompt, SamplingParams(max_new_tokens=new_tokens, ignore_eos=True)))
+    sched.step()                      # prefill + fan-out
+    for _ in range(warm):
+        sched.step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local).start() if rank == 0 else None
+    l0 = K.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        sched.step()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    per_cycle_launches = getattr(sched.native_runner, "launches_per_cycle", 0) if sched.native_runner else 0
+    launches = per_cycle_launches * steps if per_cycle_launches else K.launch_count - l0
+    status = sched.native_runner.check_status() if sched.native_runner else 0
+    sched.abort("bench")
+    sched.step()
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    toks = steps * G * world
+    value = toks / (ms_max / 1e3)
+
+    # ---- end to end through SMCEngine.generate ---------------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        n_req = args.e2e_requests
+        lens2 = lognormal_lengths(n_req, seed=2000 + rank)
+        prompts = random_prompts(lens2, vocab, seed=77 + rank)
+        sp = {"max_new_tokens": args.e2e_new_tokens, "ignore_eos": True}
+        eng.generate(input_ids=prompts[0][:16], sampling_params={"max_new_tokens": 2 * G, "ignore_eos": True})
+        b0 = dict(sched.io_bytes)
+        c0 = sched.stats["cycles"]
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        n_out = 0
+        for p in prompts:
+            o = eng.generate(input_ids=p, sampling_params=sp)
+            n_out += o["completion_tokens"]
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        tt = torch.tensor([dt], device="cuda", dtype=torch.float64)
+        nn = torch.tensor([float(n_out)], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dist.all_reduce(nn, op=dist.ReduceOp.SUM)
+        cyc = max(sched.stats["cycles"] - c0, 1)
+        e2e = {"value": float(nn.item()) / float(tt.item()), "unit": "output tokens/s",
+               "h2d_bytes_per_step": (sched.io_bytes["h2d"] - b0["h2d"]) / cyc,
+               "d2h_bytes_per_step": (sched.io_bytes["d2h"] - b0["d2h"]) / cyc,
+               "requests_per_gpu": n_req, "new_tokens": args.e2e_new_tokens, "prompt_lens": lens2,
+               "timing": "wall clock around generate() calls, cuda-synchronized, max over ranks"}
+
+    if rank == 0:
+        line = {
+            "metric": "output tokens/s (Llama-3.1-8B target + Llama-3.2-1B draft, SMC N=8 gamma=8)",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warm,
+            "ms_per_step": ms_max / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": value / (PUBLISHED_TOKS * world), "dtype": "bf16", "data": "synthetic",
+            "impl": args.impl,
+            "config": {"model": f"{args.target}+{args.draft}", "global_batch": world, "seq_len": lens[0],
+                       "parallelism": f"dp{world}", "n_particles": args.n_particles, "gamma": args.gamma,
+                       "tokens_per_step_per_request": G, "cycle_graph": not args.no_graph,
+                       "l2": "inputs larger than L2: every step streams 16 GB of target and 8 x 2.5 GB of draft weights",
+                       "weights": "random-init bf16 from a seed", "vs_baseline_note":
+                       "published 677 tok/s is per GPU, single request; scaled by n_gpus for the aggregate"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "device_status": int(status),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,220 @@
+// Small fused kernels around the GEMMs: each one also performs the split-K reduction of the
+// GEMM that feeds it, so partial sums never make an extra trip through memory.
+//   embed_rmsnorm      token ids -> residual stream (fp32) + normalised bf16 activations
+//   add_rmsnorm        residual += sum_s partials ; normalised bf16 activations
+//   rope_kv_write      sum_s qkv partials -> rotated q (bf16) ; rotated k and v into the paged cache
+//   swiglu_partials    sum_s gate/up partials -> silu(gate) * up (bf16)
+#include "common.cuh"
+
+namespace smc {
+
+template <int VEC_ITERS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int nw = blockDim.x >> 5;
+  float t = lane < nw ? red[lane] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+// One block per token row.  d <= 256 * 4 * MAXV.
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAXV = 8;   // float4 per thread -> d up to 8192
+
+__global__ void __launch_bounds__(NORM_THREADS)
+add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, int splits, long long split_stride,
+                   const int* __restrict__ ids, const __nv_bfloat16* __restrict__ embed,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ xn, int ldx, int d, float eps,
+                   int plus_one, int pdl) {
+  __shared__ float red[32];
+  if (pdl) pdl_wait_prior_grid();
+  const int m = blockIdx.x;
+  const int nvec = d >> 2;
+  float4 v[NORM_MAXV];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+    if (c < nvec) {
+      float4 a;
+      if (ids != nullptr) {
+        const __nv_bfloat16* e = embed + (size_t)ids[m] * d + c * 4;
+        const uint2 raw = *reinterpret_cast<const uint2*>(e);
+        const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        a = make_float4(__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1));
+      } else {
+        a = reinterpret_cast<const float4*>(h + (size_t)m * d)[c];
+      }
+      for (int s = 0; s < splits; ++s) {
+        const float4 b = reinterpret_cast<const float4*>(partials + (size_t)s * split_stride + (size_t)m * d)[c];
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+      }
+      v[i] = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+  }
+  const float tot = block_sum<0>(ss, red);
+  const float inv = rsqrtf(tot / (float)d + eps);
+  if (pdl) pdl_launch_dependents();
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+    if (c < nvec) {
+      reinterpret_cast<float4*>(h + (size_t)m * d)[c] = v[i];
+      if (xn != nullptr) {
+        const uint2 wr = *reinterpret_cast<const uint2*>(w + c * 4);
+        const __nv_bfloat162 w0 = *reinterpret_cast<const __nv_bfloat162*>(&wr.x);
+        const __nv_bfloat162 w1 = *reinterpret_cast<const __nv_bfloat162*>(&wr.y);
+        const float add = plus_one ? 1.f : 0.f;
+        __nv_bfloat162 o0 = __floats2bfloat162_rn(v[i].x * inv * (__low2float(w0) + add),
+                                                  v[i].y * inv * (__high2float(w0) + add));
+        __nv_bfloat162 o1 = __floats2bfloat162_rn(v[i].z * inv * (__low2float(w1) + add),
+                                                  v[i].w * inv * (__high2float(w1) + add));
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&o0);
+        o.y = *reinterpret_cast<uint32_t*>(&o1);
+        *reinterpret_cast<uint2*>(xn + (size_t)m * ldx + c * 4) = o;
+      }
+    }
+  }
+}
+
+// One block per token.  qkv partials [splits, M, (Hq + 2 Hkv) * D]; rope table [max_pos, rd] = cos | sin.
+__global__ void __launch_bounds__(256)
+rope_kv_write_kernel(const float* __restrict__ partials, int splits, long long split_stride,
+                     const int* __restrict__ positions, const int* __restrict__ cache_locs,
+                     const float* __restrict__ rope, int rd, int max_pos, __nv_bfloat16* __restrict__ q_out,
+                     __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int n_pages, int Hq,
+                     int Hkv, int D, int* status, int pdl) {
+  if (pdl) pdl_wait_prior_grid();
+  const int m = blockIdx.x;
+  const int nq = Hq * D, nk = Hkv * D, ntot = nq + 2 * nk;
+  int pos = positions[m];
+  int loc = cache_locs[m];
+  if (pos < 0 || pos >= max_pos || loc < 0 || loc > n_pages) {
+    if (threadIdx.x == 0) atomicOr(status, SMC_ERR_BOUNDS);
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    loc = 0;
+  }
+  const float* row = partials + (size_t)m * ntot;
+  const float* cs = rope + (size_t)pos * rd;
+  const int half = rd >> 1;
+  // rotated pairs of q and k heads
+  const int pairs_per_head = D >> 1;
+  const int n_rot_heads = Hq + Hkv;
+  for (int idx = threadIdx.x; idx < n_rot_heads * pairs_per_head; idx += blockDim.x) {
+    const int head = idx / pairs_per_head, i = idx % pairs_per_head;
+    // element i pairs with i + half inside the rotary span; dims beyond rd pass through
+    const int base = head * D;
+    float x1 = 0.f, x2 = 0.f;
+    int i1, i2;
+    bool rot;
+    if (i < half) { i1 = i; i2 = i + half; rot = true; }
+    else { const int j = i - half; i1 = rd + 2 * j; i2 = rd + 2 * j + 1; rot = false; }
+    for (int s = 0; s < splits; ++s) {
+      const float* r = row + (size_t)s * split_stride;
+      x1 += r[base + i1];
+      x2 += r[base + i2];
+    }
+    float o1 = x1, o2 = x2;
+    if (rot) {
+      const float c = cs[i], sn = cs[half + i];
+      o1 = x1 * c - x2 * sn;
+      o2 = x2 * c + x1 * sn;
+    }
+    if (head < Hq) {
+      q_out[(size_t)m * nq + base + i1] = __float2bfloat16(o1);
+      q_out[(size_t)m * nq + base + i2] = __float2bfloat16(o2);
+    } else {
+      const int kb = (head - Hq) * D;
+      k_pool[(size_t)loc * nk + kb + i1] = __float2bfloat16(o1);
+      k_pool[(size_t)loc * nk + kb + i2] = __float2bfloat16(o2);
+    }
+  }
+  for (int idx = threadIdx.x; idx < nk; idx += blockDim.x) {
+    float x = 0.f;
+    for (int s = 0; s < splits; ++s) x += row[(size_t)s * split_stride + nq + nk + idx];
+    v_pool[(size_t)loc * nk + idx] = __float2bfloat16(x);
+  }
+  if (pdl) pdl_launch_dependents();
+}
+
+// act[m, c] = silu(gate) * up with gate/up interleaved in blocks of `blk` channels.
+__global__ void __launch_bounds__(256)
+swiglu_partials_kernel(const float* __restrict__ partials, int splits, long long split_stride,
+                       __nv_bfloat16* __restrict__ act, int M, int ffn, int blk, int ldo, int pdl) {
+  if (pdl) pdl_wait_prior_grid();
+  const long long total = (long long)M * ffn;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int m = (int)(idx / ffn), c = (int)(idx % ffn);
+    const int gi = (c / blk) * 2 * blk + (c % blk);
+    float g = 0.f, u = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* r = partials + (size_t)s * split_stride + (size_t)m * 2 * ffn;
+      g += r[gi];
+      u += r[gi + blk];
+    }
+    act[(size_t)m * ldo + c] = __float2bfloat16(g / (1.f + __expf(-g)) * u);
+  }
+  if (pdl) pdl_launch_dependents();
+}
+
+template <typename K, typename... Args>
+static int launch_pdl(K kern, dim3 grid, dim3 block, cudaStream_t st, int pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, kern, args...));
+  return 0;
+}
+
+}  // namespace smc
+
+// h [M, d] fp32 in/out.  With ids != null the row is first loaded from the embedding table
+// (h's previous content is ignored); partials may be null (splits = 0).
+SMC_API int smc_add_rmsnorm(float* h, const float* partials, int splits, long long split_stride, const int* ids,
+                            const void* embed, const void* w, void* xn, int ldx, int M, int d, float eps,
+                            int plus_one, int pdl, cudaStream_t st) {
+  using namespace smc;
+  if (M <= 0) return 0;
+  if ((d & 3) || d > NORM_THREADS * 4 * NORM_MAXV) return -30;
+  return launch_pdl(add_rmsnorm_kernel, dim3(M), dim3(NORM_THREADS), st, pdl, h, partials, splits, split_stride, ids,
+                    (const __nv_bfloat16*)embed, (const __nv_bfloat16*)w, (__nv_bfloat16*)xn, ldx, d, eps, plus_one,
+                    pdl);
+}
+
+SMC_API int smc_rope_kv_write(const float* partials, int splits, long long split_stride, const int* positions,
+                              const int* cache_locs, const float* rope, int rd, int max_pos, void* q_out, void* k_pool,
+                              void* v_pool, int n_pages, int M, int Hq, int Hkv, int D, int* status, int pdl,
+                              cudaStream_t st) {
+  using namespace smc;
+  if (M <= 0) return 0;
+  if (rd > D || (rd & 1) || (D & 1)) return -31;
+  return launch_pdl(rope_kv_write_kernel, dim3(M), dim3(256), st, pdl, partials, splits, split_stride, positions,
+                    cache_locs, rope, rd, max_pos, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+                    (__nv_bfloat16*)v_pool, n_pages, Hq, Hkv, D, status, pdl);
+}
+
+SMC_API int smc_swiglu_partials(const float* partials, int splits, long long split_stride, void* act, int M, int ffn,
+                                int blk, int ldo, int pdl, cudaStream_t st) {
+  using namespace smc;
+  if (M <= 0) return 0;
+  long long total = (long long)M * ffn;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  return launch_pdl(swiglu_partials_kernel, dim3(blocks), dim3(256), st, pdl, partials, splits, split_stride,
+                    (__nv_bfloat16*)act, M, ffn, blk, ldo, pdl);
+}

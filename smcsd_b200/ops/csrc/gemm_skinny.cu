@@ -1,0 +1,354 @@
+// Weight-streaming GEMM for few-token batches on sm_100a:  Y[m, n] = sum_k X[m, k] * W[n, k].
+//
+// Decode-time SMC batches have 8..72 token rows, so the product is bound by reading W once.
+// The operands are swapped for the 5th-generation tensor cores: a 128-row slab of W is the
+// M operand of tcgen05.mma, the token rows are the N operand (16..256 wide), and the fp32
+// accumulator tile [128 weight rows x tokens] lives in tensor memory.  One CTA streams one
+// slab over one K range through a multi-stage TMA -> shared-memory ring (SWIZZLE_128B tiles,
+// consumed directly by UMMA descriptors); split-K ranges fill all 148 SMs when a matrix has
+// few slabs.  Warp 0 is the TMA producer, warp 1 issues the MMAs, all four warps run the
+// epilogue straight out of tensor memory.
+//
+// Epilogues: fp32 split-K partials (summed by the consumer kernel), bf16 output, and a fused
+// SwiGLU for gate/up matrices whose rows are interleaved in blocks of 64 channels.
+//
+// Every mbarrier wait is bounded; on a timeout the CTA raises a status bit, drains its
+// outstanding copies, frees its tensor memory and returns.
+#include "common.cuh"
+
+namespace smc {
+
+enum { EPI_PARTIAL_F32 = 0, EPI_BF16 = 1, EPI_SWIGLU_BF16 = 2 };
+
+struct GemmParams {
+  int N, K, M;          // weight rows, reduction length, token rows
+  int kblocks;          // ceil(K / 64)
+  int splits;
+  void* out;            // fp32 [splits, M, N] | bf16 [M, ldo]
+  int ldo;
+  int* status;
+  int pdl;              // 1: wait for the previous grid only before touching activations
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int BM = 128, BK = 64;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN <= 32 ? 5 : 4;
+  static constexpr int TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                         const __grid_constant__ CUtensorMap tmX,
+                                                         const GemmParams p) {
+  using C = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* accum = empty + C::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile int* sh_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* sh_issued = sh_abort + 1;
+  volatile int* sh_consumed = sh_abort + 2;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x, split = blockIdx.y, m_tile = blockIdx.z;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    *sh_abort = 0;
+    *sh_issued = 0;
+    *sh_consumed = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // balanced K partition
+  const int kb_begin = (int)(((long long)p.kblocks * split) / p.splits);
+  const int kb_end = (int)(((long long)p.kblocks * (split + 1)) / p.splits);
+  const int nkb = kb_end - kb_begin;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      // Weights do not depend on the previous kernel: start streaming them before the
+      // programmatic-dependency wait, then fetch the activations.
+      const int pre = nkb < C::STAGES ? nkb : C::STAGES;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full[i], C::STAGE_BYTES);
+        tma_load_2d(smem + i * C::STAGE_BYTES, &tmW, &full[i], (kb_begin + i) * C::BK, n_tile * C::BM, pol_w);
+      }
+      if (p.pdl) pdl_wait_prior_grid();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem + i * C::STAGE_BYTES + C::A_BYTES, &tmX, &full[i], (kb_begin + i) * C::BK, m_tile * BN,
+                    pol_x);
+      *sh_issued = pre;
+      for (int i = pre; i < nkb; ++i) {
+        const int s = i % C::STAGES;
+        const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
+        if (*sh_abort || !mbar_wait(&empty[s], ph ^ 1u)) {
+          *sh_abort = 1;
+          break;
+        }
+        mbar_expect_tx(&full[s], C::STAGE_BYTES);
+        tma_load_2d(smem + s * C::STAGE_BYTES, &tmW, &full[s], (kb_begin + i) * C::BK, n_tile * C::BM, pol_w);
+        tma_load_2d(smem + s * C::STAGE_BYTES + C::A_BYTES, &tmX, &full[s], (kb_begin + i) * C::BK, m_tile * BN,
+                    pol_x);
+        *sh_issued = i + 1;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(C::BM, BN);
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % C::STAGES;
+        const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
+        if (*sh_abort || !mbar_wait(&full[s], ph)) {
+          *sh_abort = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+        const uint64_t adesc = umma_desc_k_sw128(a_addr);
+        const uint64_t bdesc = umma_desc_k_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < C::BK / 16; ++k)   // advance 32 bytes (16 bf16) inside the swizzle atom
+          umma_bf16_ss(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) ? 1u : 0u);
+        umma_commit(&empty[s]);
+        *sh_consumed = i + 1;
+      }
+      if (!*sh_abort) umma_commit(accum);
+    }
+    __syncwarp();
+  }
+
+  // ---- wait for the accumulator (all threads), bounded ------------------------------------
+  bool ok = nkb > 0;
+  if (ok && !mbar_try_wait(accum, 0)) {
+    const long long t0 = clock64();
+    for (;;) {
+      if (mbar_try_wait(accum, 0)) break;
+      if (*sh_abort || clock64() - t0 > SMC_SPIN_CYCLES) {
+        ok = false;
+        break;
+      }
+    }
+  }
+  const int failed = __syncthreads_or(ok ? 0 : 1);
+  tc_fence_after();
+  if (p.pdl) pdl_launch_dependents();
+
+  if (!failed) {
+    const int row_in_tile = warp * 32 + lane;
+    const int n = n_tile * C::BM + row_in_tile;
+    const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const int m_base = m_tile * BN;
+    if constexpr (EPI == EPI_SWIGLU_BF16) {
+      // rows 0..63 of the slab are gate channels, rows 64..127 the matching up channels
+      float* sbuf = reinterpret_cast<float*>(smem);      // the ring is idle: every MMA has completed
+      constexpr int LD = BN + 1;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(taddr + c0, r);
+        tmem_ld_wait();
+        if (warp >= 2) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sbuf[(row_in_tile - 64) * LD + c0 + j] = __uint_as_float(r[j]);
+        }
+        __syncthreads();
+        if (warp < 2) {
+          const int ch = n_tile * 64 + row_in_tile;
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m_base + c0 + j;
+            if (m < p.M && ch * 2 < p.N) {
+              const float g = __uint_as_float(r[j]);
+              const float u = sbuf[row_in_tile * LD + c0 + j];
+              out[(size_t)m * p.ldo + ch] = __float2bfloat16(g / (1.0f + __expf(-g)) * u);
+            }
+          }
+        }
+        __syncthreads();
+      }
+    } else {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(taddr + c0, r);
+        tmem_ld_wait();
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m_base + c0 + j;
+            if (m < p.M) {
+              if constexpr (EPI == EPI_PARTIAL_F32) {
+                reinterpret_cast<float*>(p.out)[((size_t)split * p.M + m) * p.N + n] = __uint_as_float(r[j]);
+              } else {
+                reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] =
+                    __float2bfloat16(__uint_as_float(r[j]));
+              }
+            }
+          }
+        }
+      }
+    }
+  } else if (threadIdx.x == 0) {
+    if (nkb > 0) atomicOr(p.status, SMC_ERR_BARRIER_TIMEOUT);
+    // drain copies that were issued but never consumed, so none lands after the CTA is gone
+    const int issued = *sh_issued, consumed = *sh_consumed;
+    for (int i = consumed; i < issued; ++i)
+      (void)mbar_wait(&full[i % C::STAGES], (uint32_t)(i / C::STAGES) & 1u);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &ptr, 12000, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// bf16 matrix [rows, cols] row-major with leading dimension ld (elements); box = [box_rows, 64 cols]
+static int make_tmap(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2 - (int)r;
+}
+
+template <int BN, int EPI>
+static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, dim3 grid, cudaStream_t st) {
+  using C = GemmCfg<BN>;
+  static bool configured = false;
+  auto kern = gemm_skinny_kernel<BN, EPI>;
+  if (!configured) {
+    CUDA_CHECK_RET(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl ? 1 : 0;
+  CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p));
+  return 0;
+}
+
+template <int EPI>
+static int dispatch_bn(int bn, const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3 g, cudaStream_t st) {
+  switch (bn) {
+    case 16: return launch<16, EPI>(a, b, p, g, st);
+    case 32: return launch<32, EPI>(a, b, p, g, st);
+    case 64: return launch<64, EPI>(a, b, p, g, st);
+    case 80: return launch<80, EPI>(a, b, p, g, st);
+    case 128: return launch<128, EPI>(a, b, p, g, st);
+    case 256: return launch<256, EPI>(a, b, p, g, st);
+  }
+  return -10;
+}
+
+}  // namespace smc
+
+// Token-tile width used for a batch of M rows.
+SMC_API int smc_gemm_bn_for(int M) {
+  if (M <= 16) return 16;
+  if (M <= 32) return 32;
+  if (M <= 64) return 64;
+  if (M <= 80) return 80;
+  if (M <= 128) return 128;
+  return 256;
+}
+
+// Split-K factor that gives every SM about two resident CTAs while keeping >= 4 k-blocks per CTA.
+SMC_API int smc_gemm_default_splits(int N, int K, int M) {
+  const int n_tiles = (N + 127) / 128;
+  const int bn = smc_gemm_bn_for(M);
+  const int m_tiles = (M + bn - 1) / bn;
+  const int kblocks = (K + 63) / 64;
+  int s = (296 + n_tiles * m_tiles - 1) / (n_tiles * m_tiles);
+  int cap = kblocks / 4;
+  if (cap < 1) cap = 1;
+  if (s > cap) s = cap;
+  if (s > 32) s = 32;
+  if (s < 1) s = 1;
+  return s;
+}
+
+// W [N, K] bf16 row-major, X [M, ldx] bf16 row-major (ldx >= K).
+// epi 0: out = fp32 [splits, M, N] partials; epi 1: out = bf16 [M, ldo] (splits must be 1);
+// epi 2: out = bf16 [M, ldo] holding SwiGLU(gate, up) for N/2 channels (splits must be 1, N % 128 == 0).
+SMC_API int smc_gemm_skinny(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo,
+                            int splits, int epi, int* status, int pdl, cudaStream_t stream) {
+  using namespace smc;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 8) != 0 || (ldx % 8) != 0) return -20;       // row pitch must be a multiple of 16 bytes
+  if (epi != EPI_PARTIAL_F32 && splits != 1) return -21;
+  if (epi == EPI_SWIGLU_BF16 && (N % 128) != 0) return -22;
+  const int bn = smc_gemm_bn_for(M);
+  GemmParams p;
+  p.N = N; p.K = K; p.M = M;
+  p.kblocks = (K + 63) / 64;
+  p.splits = splits < 1 ? 1 : (splits > p.kblocks ? p.kblocks : splits);
+  p.out = out; p.ldo = ldo; p.status = status; p.pdl = pdl;
+  CUtensorMap tmW, tmX;
+  int rc = make_tmap(&tmW, W, N, K, K, 128);
+  if (rc) return rc;
+  rc = make_tmap(&tmX, X, M, K, ldx, bn);
+  if (rc) return rc;
+  dim3 grid((N + 127) / 128, p.splits, (M + bn - 1) / bn);
+  switch (epi) {
+    case EPI_PARTIAL_F32: return dispatch_bn<EPI_PARTIAL_F32>(bn, tmW, tmX, p, grid, stream);
+    case EPI_BF16: return dispatch_bn<EPI_BF16>(bn, tmW, tmX, p, grid, stream);
+    case EPI_SWIGLU_BF16: return dispatch_bn<EPI_SWIGLU_BF16>(bn, tmW, tmX, p, grid, stream);
+  }
+  return -11;
+}

@@ -1,0 +1,225 @@
+"""ctypes bindings of the sm_100a kernel library.
+
+Every wrapper launches on PyTorch's current CUDA stream, takes torch tensors, allocates
+nothing on its own (scratch buffers are passed in) and is therefore safe to capture in a CUDA
+graph.  The library must be present on a GPU machine: ``lib()`` raises instead of falling
+back to PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libsmcsd_b200.so")
+_lib = None
+
+EPI_PARTIAL_F32, EPI_BF16, EPI_SWIGLU_BF16 = 0, 1, 2
+ERR_BARRIER_TIMEOUT, ERR_PEER_TIMEOUT, ERR_ALLOC_EXHAUSTED, ERR_BOUNDS = 1, 2, 4, 8
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def available() -> bool:
+    return os.path.exists(_LIB_PATH)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            from . import build as _build
+            _build.build()
+        _lib = C.CDLL(_LIB_PATH)
+        _declare(_lib)
+    return _lib
+
+
+def _declare(L) -> None:
+    vp, i, ll, f, d, ull = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_double, C.c_ulonglong
+    L.smc_gemm_skinny.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, vp, i, vp]
+    L.smc_gemm_bn_for.argtypes = [i]
+    L.smc_gemm_default_splits.argtypes = [i, i, i]
+    L.smc_add_rmsnorm.argtypes = [vp, vp, i, ll, vp, vp, vp, vp, i, i, i, f, i, i, vp]
+    L.smc_rope_kv_write.argtypes = [vp, i, ll, vp, vp, vp, i, i, vp, vp, vp, i, i, i, i, i, vp, i, vp]
+    L.smc_swiglu_partials.argtypes = [vp, i, ll, vp, i, i, i, i, i, vp]
+    L.smc_attention_extend.argtypes = [vp, vp, vp, vp, i, i, vp, vp, vp, vp, vp, i, i, i, i, i, i, f, vp, i, vp]
+    L.smc_sample_scratch_bytes.argtypes = [i, i]
+    L.smc_sample_or_score.argtypes = [vp, i, ll, ll, i, i, f, f, f, vp, ull, vp, i, vp, i, vp, vp, vp, i, vp]
+    L.smc_slot_arrays_size.argtypes = []
+    L.smc_prepare_cycle.argtypes = [vp, vp, i, i, vp, vp, vp]
+    L.smc_assemble_verify.argtypes = [vp, vp, i, i, vp]
+    L.smc_cycle_io_size.argtypes = []
+    L.smc_write_back.argtypes = [vp, vp, i, i, vp, vp, vp, vp, vp, f, i, vp, vp, vp]
+    L.smc_collect_resample.argtypes = [vp, vp, i, vp, i, d, ull, vp, vp, vp, vp, vp]
+    L.smc_state_copy.argtypes = [vp, ll, ll, i, i, vp, vp, vp, i, vp]
+    for name in ("smc_gemm_skinny", "smc_add_rmsnorm", "smc_rope_kv_write", "smc_swiglu_partials",
+                 "smc_attention_extend", "smc_sample_or_score", "smc_prepare_cycle", "smc_write_back",
+                 "smc_collect_resample", "smc_state_copy", "smc_gemm_bn_for", "smc_gemm_default_splits",
+                 "smc_sample_scratch_bytes", "smc_slot_arrays_size", "smc_assemble_verify", "smc_cycle_io_size"):
+        getattr(L, name).restype = C.c_int
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+# kernels launched through this module (a captured graph replays the launches counted at capture)
+launch_count = 0
+_KERNELS_PER_CALL = {"smc_attention_extend": 2, "smc_sample_or_score": 2, "smc_collect_resample": 2}
+
+
+def _check(rc: int, what: str) -> None:
+    global launch_count
+    if rc != 0:
+        raise NativeError(f"{what} failed with code {rc}")
+    launch_count += _KERNELS_PER_CALL.get(what, 1)
+
+
+# ----------------------------------------------------------------------------- GEMM
+def gemm_default_splits(N: int, K: int, M: int) -> int:
+    return lib().smc_gemm_default_splits(N, K, M)
+
+
+def gemm_skinny(W: torch.Tensor, X: torch.Tensor, out: torch.Tensor, *, M: int, splits: int = 1,
+                epi: int = EPI_PARTIAL_F32, ldx: Optional[int] = None, ldo: Optional[int] = None,
+                status: torch.Tensor, pdl: bool = False) -> None:
+    """out = X[:M] @ W.T on the tcgen05 tensor cores.  W [N, K] bf16; X rows of pitch ``ldx``."""
+    N, K = W.shape
+    ldx = ldx if ldx is not None else X.stride(0)
+    ldo = ldo if ldo is not None else (out.stride(0) if out.dim() == 2 else N)
+    _check(lib().smc_gemm_skinny(_p(W), _p(X), _p(out), N, K, M, ldx, ldo, splits, epi, _p(status), int(pdl),
+                                 _stream()), "smc_gemm_skinny")
+
+
+# ----------------------------------------------------------------------------- fused elementwise
+def add_rmsnorm(h: torch.Tensor, w: Optional[torch.Tensor], xn: Optional[torch.Tensor], *, M: int, d: int, eps: float,
+                partials: Optional[torch.Tensor] = None, splits: int = 0, split_stride: int = 0,
+                ids: Optional[torch.Tensor] = None, embed: Optional[torch.Tensor] = None, ldx: Optional[int] = None,
+                plus_one: bool = False, pdl: bool = False) -> None:
+    ldx = ldx if ldx is not None else (xn.stride(0) if xn is not None else d)
+    _check(lib().smc_add_rmsnorm(_p(h), _p(partials), splits, split_stride, _p(ids), _p(embed), _p(w), _p(xn), ldx, M,
+                                 d, eps, int(plus_one), int(pdl), _stream()), "smc_add_rmsnorm")
+
+
+def rope_kv_write(partials: torch.Tensor, splits: int, split_stride: int, positions: torch.Tensor,
+                  cache_locs: torch.Tensor, rope: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Tensor,
+                  v_pool: torch.Tensor, *, M: int, Hq: int, Hkv: int, D: int, status: torch.Tensor,
+                  pdl: bool = False) -> None:
+    _check(lib().smc_rope_kv_write(_p(partials), splits, split_stride, _p(positions), _p(cache_locs), _p(rope),
+                                   rope.shape[1], rope.shape[0], _p(q_out), _p(k_pool), _p(v_pool),
+                                   k_pool.shape[0] - 1, M, Hq, Hkv, D, _p(status), int(pdl), _stream()),
+           "smc_rope_kv_write")
+
+
+def swiglu_partials(partials: torch.Tensor, splits: int, split_stride: int, act: torch.Tensor, *, M: int, ffn: int,
+                    blk: int, pdl: bool = False) -> None:
+    _check(lib().smc_swiglu_partials(_p(partials), splits, split_stride, _p(act), M, ffn, blk, act.stride(0), int(pdl),
+                                     _stream()), "smc_swiglu_partials")
+
+
+def attention_extend(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                     rows: torch.Tensor, prefix_lens: torch.Tensor, part_acc: torch.Tensor, part_ml: torch.Tensor,
+                     out: torch.Tensor, *, bs: int, E: int, Hq: int, Hkv: int, D: int, splits: int, scale: float,
+                     status: torch.Tensor, pdl: bool = False) -> None:
+    _check(lib().smc_attention_extend(_p(q), _p(k_pool), _p(v_pool), _p(block_table), block_table.stride(0),
+                                      k_pool.shape[0] - 1, _p(rows), _p(prefix_lens), _p(part_acc), _p(part_ml),
+                                      _p(out), bs, E, Hq, Hkv, D, splits, scale, _p(status), int(pdl), _stream()),
+           "smc_attention_extend")
+
+
+def sample_scratch_bytes(rows: int, nchunks: int) -> int:
+    return lib().smc_sample_scratch_bytes(rows, nchunks)
+
+
+def sample_or_score(logits: torch.Tensor, *, rows: int, V: int, splits: int, split_stride: int, row_stride: int,
+                    temperature: float, alpha: float, softcap: float, tokens_in: Optional[torch.Tensor], seed: int,
+                    cycle_counter: torch.Tensor, call_id: int, scratch: torch.Tensor, nchunks: int,
+                    tok_out: torch.Tensor, logp_out: torch.Tensor, logz_out: Optional[torch.Tensor],
+                    pdl: bool = False) -> None:
+    _check(lib().smc_sample_or_score(_p(logits), splits, split_stride, row_stride, rows, V, temperature, alpha,
+                                     softcap, _p(tokens_in), seed & 0xFFFFFFFFFFFFFFFF, _p(cycle_counter), call_id,
+                                     _p(scratch), nchunks, _p(tok_out), _p(logp_out), _p(logz_out), int(pdl),
+                                     _stream()), "smc_sample_or_score")
+
+
+# ----------------------------------------------------------------------------- SMC state
+class SlotArrays(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("seq_lens", "verified_ids", "prev_ids", "token_counts", "finished",
+                                         "finished_len", "finish_code", "matched_eos", "ignore_eos",
+                                         "max_new_tokens", "eos_ids", "log_weights", "interval_weights",
+                                         "all_token_ids")] + \
+               [("max_out", C.c_int), ("block_table", C.c_void_p), ("bt_stride", C.c_int), ("refcount", C.c_void_p),
+                ("free_stack", C.c_void_p), ("free_count", C.c_void_p), ("alloc_error", C.c_void_p),
+                ("n_pages", C.c_int)]
+
+
+def make_slot_arrays(state) -> SlotArrays:
+    a = SlotArrays()
+    for n in ("seq_lens", "verified_ids", "prev_ids", "token_counts", "finished", "finished_len", "finish_code",
+              "matched_eos", "ignore_eos", "max_new_tokens", "eos_ids", "log_weights", "interval_weights",
+              "all_token_ids"):
+        setattr(a, n, getattr(state, n).data_ptr())
+    a.max_out = state.max_output_len
+    a.block_table = state.bt.table.data_ptr()
+    a.bt_stride = state.bt.table.stride(0)
+    a.refcount = state.alloc.refcount.data_ptr()
+    a.free_stack = state.alloc.free_stack.data_ptr()
+    a.free_count = state.alloc.free_count.data_ptr()
+    a.alloc_error = state.alloc.error_flag.data_ptr()
+    a.n_pages = state.alloc.size
+    assert C.sizeof(a) == lib().smc_slot_arrays_size(), "SlotArrays layout mismatch"
+    return a
+
+
+class CycleIO(C.Structure):
+    NAMES = ("orig_seq", "x0", "prev", "cache_locs", "positions_verify", "step_pos", "step_locs", "head_ids",
+             "head_pos", "head_locs", "head_prefix", "verify_ids", "verify_given")
+    _fields_ = [(n, C.c_void_p) for n in NAMES]
+
+
+def make_cycle_io(bufs: dict) -> CycleIO:
+    io = CycleIO()
+    for n in CycleIO.NAMES:
+        setattr(io, n, bufs[n].data_ptr())
+    assert C.sizeof(io) == lib().smc_cycle_io_size()
+    return io
+
+
+def prepare_cycle(arrays: SlotArrays, active, bs, G, counters, io: CycleIO):
+    _check(lib().smc_prepare_cycle(C.byref(arrays), _p(active), bs, G, _p(counters), C.byref(io), _stream()),
+           "smc_prepare_cycle")
+
+
+def assemble_verify(io: CycleIO, drafts, bs, gamma):
+    _check(lib().smc_assemble_verify(C.byref(io), _p(drafts), bs, gamma, _stream()), "smc_assemble_verify")
+
+
+def write_back(arrays: SlotArrays, active, bs, gamma, drafts, logq, verify_tok, verify_logp, verify_logz, alpha,
+               use_logz, tokens_out, diff_out):
+    _check(lib().smc_write_back(C.byref(arrays), _p(active), bs, gamma, _p(drafts), _p(logq), _p(verify_tok),
+                                _p(verify_logp), _p(verify_logz), alpha, int(use_logz), _p(tokens_out), _p(diff_out),
+                                _stream()), "smc_write_back")
+
+
+def collect_resample(arrays: SlotArrays, active_rows, n_groups, group_to_slots, N, threshold, seed, counters,
+                     group_log_z, job_dst, job_src):
+    _check(lib().smc_collect_resample(C.byref(arrays), _p(active_rows), n_groups, _p(group_to_slots), N, threshold,
+                                      seed & 0xFFFFFFFFFFFFFFFF, _p(counters), _p(group_log_z), _p(job_dst),
+                                      _p(job_src), _stream()), "smc_collect_resample")
+
+
+def state_copy(state_tensor: torch.Tensor, n_layers: int, n_rows: int, counters, job_dst, job_src, max_jobs: int):
+    row_bytes = state_tensor[0, 0].numel() * state_tensor.element_size()
+    _check(lib().smc_state_copy(_p(state_tensor), state_tensor.stride(0) * state_tensor.element_size(), row_bytes,
+                                n_layers, n_rows, _p(counters), _p(job_dst), _p(job_src), max_jobs, _stream()),
+           "smc_state_copy")

@@ -1,0 +1,370 @@
+"""The sm_100a execution path: model forwards as chains of the hand-written kernels, the SMC
+state transitions as device kernels, and the whole decode cycle captured in one CUDA graph.
+
+One cycle = prologue (page assignment) -> draft head + gamma-1 single draft steps, each followed
+by the fused Gumbel sampler -> target verify -> fused scoring / bonus draw -> write-back -> ESS
+test, systematic resampling and ancestor copy.  Nothing in it touches the host, so a replay is a
+single launch and the host loop only reads a pinned snapshot one cycle later.  (The reference
+captures draft + verify + scoring and leaves write-back / resampling as eager launches:
+smcsd/model_executor/smc_draft_phase_graph_runner.py:824-1197, smcsd/core/scheduler.py:879-914.)
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..models.layers import ExtendBatch
+from ..runtime.slot_state import CycleInputs, CycleOutputs
+from . import native as K
+
+
+def _env_flag(name: str, default: bool) -> bool:
+    v = os.environ.get(name)
+    return default if v is None else v.strip().lower() in ("1", "true", "yes", "on")
+
+
+class NativeLlama:
+    """Kernel-chain forward of a dense Llama-style model over a paged KV cache."""
+
+    def __init__(self, model, kv, block_table: torch.Tensor, max_tokens: int, max_logit_rows: int,
+                 attn_splits: int, status: torch.Tensor, pdl: bool):
+        self.m, self.kv, self.bt = model, kv, block_table
+        c = model.cfg
+        self.c = c
+        dev = model.device
+        self.T = max_tokens
+        self.status = status
+        self.pdl = pdl
+        self.attn_splits = attn_splits
+        self.nq, self.nkv, self.D = model.n_heads, model.n_kv_heads, c.head_dim
+        self.d, self.ffn = c.hidden_size, model.ffn
+        self.nqkv = (self.nq + 2 * self.nkv) * self.D
+        self.V = model.lm_head.shape[0]
+        f32, bf16 = torch.float32, torch.bfloat16
+        self.h = torch.empty(max_tokens, self.d, dtype=f32, device=dev)
+        self.xn = torch.empty(max_tokens, self.d, dtype=bf16, device=dev)
+        self.q = torch.empty(max_tokens, self.nq * self.D, dtype=bf16, device=dev)
+        self.attn = torch.empty(max_tokens, self.nq * self.D, dtype=bf16, device=dev)
+        self.act = torch.empty(max_tokens, self.ffn, dtype=bf16, device=dev)
+        self.max_splits = 32
+        widest = max(self.nqkv, self.d, 2 * self.ffn)
+        self.partials = torch.empty(self.max_splits * max_tokens * widest // 2 + max_tokens * widest, dtype=f32,
+                                    device=dev)
+        self.part_acc = torch.empty(max_tokens * self.nq * attn_splits * self.D, dtype=f32, device=dev)
+        self.part_ml = torch.empty(max_tokens * self.nq * attn_splits * 2, dtype=f32, device=dev)
+        self.logits = torch.empty(max_logit_rows, self.V, dtype=f32, device=dev)
+        self.fuse_swiglu = model.gu_block == 64 and (2 * self.ffn) % 128 == 0 and _env_flag("SMC_FUSE_SWIGLU", True)
+        self._splits_cache: Dict = {}
+
+    def _splits(self, N: int, Kdim: int, M: int) -> int:
+        key = (N, Kdim, M)
+        s = self._splits_cache.get(key)
+        if s is None:
+            s = K.gemm_default_splits(N, Kdim, M)
+            while s > 1 and s * M * N > self.partials.numel():
+                s -= 1
+            self._splits_cache[key] = s
+        return s
+
+    def _gemm_partials(self, W: torch.Tensor, X: torch.Tensor, M: int, ldx: Optional[int] = None):
+        N, Kdim = W.shape
+        s = self._splits(N, Kdim, M)
+        K.gemm_skinny(W, X, self.partials, M=M, splits=s, epi=K.EPI_PARTIAL_F32, ldx=ldx, status=self.status,
+                      pdl=self.pdl)
+        return s, M * N
+
+    def forward(self, ids: torch.Tensor, positions: torch.Tensor, cache_locs: torch.Tensor, rows: torch.Tensor,
+                prefix_lens: torch.Tensor, bs: int, E: int) -> torch.Tensor:
+        """Runs every layer for bs*E tokens; returns the final-norm activations ``xn`` [T, d] (bf16)."""
+        m, c, pdl = self.m, self.c, self.pdl
+        T = bs * E
+        assert T <= self.T
+        L0 = m.layers[0]
+        K.add_rmsnorm(self.h, L0.ln1, self.xn, M=T, d=self.d, eps=c.rms_eps, ids=ids, embed=m.embed, pdl=pdl)
+        n_layers = len(m.layers)
+        scale = self.D ** -0.5
+        for li, L in enumerate(m.layers):
+            s, stride = self._gemm_partials(L.wqkv, self.xn, T)
+            K.rope_kv_write(self.partials, s, stride, positions, cache_locs, m.rope, self.q, self.kv.k[li],
+                            self.kv.v[li], M=T, Hq=self.nq, Hkv=self.nkv, D=self.D, status=self.status, pdl=pdl)
+            K.attention_extend(self.q, self.kv.k[li], self.kv.v[li], self.bt, rows, prefix_lens, self.part_acc,
+                               self.part_ml, self.attn, bs=bs, E=E, Hq=self.nq, Hkv=self.nkv, D=self.D,
+                               splits=self.attn_splits, scale=scale, status=self.status, pdl=pdl)
+            s, stride = self._gemm_partials(L.wo, self.attn, T)
+            K.add_rmsnorm(self.h, L.ln2, self.xn, M=T, d=self.d, eps=c.rms_eps, partials=self.partials, splits=s,
+                          split_stride=stride, pdl=pdl)
+            if self.fuse_swiglu:
+                K.gemm_skinny(L.wgu, self.xn, self.act, M=T, splits=1, epi=K.EPI_SWIGLU_BF16, ldo=self.act.stride(0),
+                              status=self.status, pdl=pdl)
+            else:
+                s, stride = self._gemm_partials(L.wgu, self.xn, T)
+                K.swiglu_partials(self.partials, s, stride, self.act, M=T, ffn=self.ffn, blk=m.gu_block, pdl=pdl)
+            s, stride = self._gemm_partials(L.wdown, self.act, T)
+            w_next = m.layers[li + 1].ln1 if li + 1 < n_layers else m.final_norm
+            K.add_rmsnorm(self.h, w_next, self.xn, M=T, d=self.d, eps=c.rms_eps, partials=self.partials, splits=s,
+                          split_stride=stride, pdl=pdl)
+        return self.xn
+
+    def lm_head(self, rows: int, row_offset: int = 0, row_step: int = 1) -> torch.Tensor:
+        """fp32 logits [rows, V] of xn rows ``row_offset + i * row_step``."""
+        X = self.xn[row_offset:]
+        K.gemm_skinny(self.m.lm_head, X, self.logits, M=rows, splits=1, epi=K.EPI_PARTIAL_F32,
+                      ldx=self.d * row_step, status=self.status, pdl=self.pdl)
+        return self.logits
+
+
+class NativeState:
+    """Device-kernel versions of the SlotState transitions (bound to one SlotState)."""
+
+    def __init__(self, max_bs: int, gamma: int, device):
+        self.G = gamma + 1
+        self.gamma = gamma
+        self.device = device
+        i32 = dict(dtype=torch.int32, device=device)
+        G, g = self.G, gamma
+        self.bufs = dict(
+            orig_seq=torch.zeros(max_bs, **i32), x0=torch.zeros(max_bs, **i32), prev=torch.zeros(max_bs, **i32),
+            cache_locs=torch.zeros(max_bs * G, **i32), positions_verify=torch.zeros(max_bs * G, **i32),
+            step_pos=torch.zeros(G * max_bs, **i32), step_locs=torch.zeros(G * max_bs, **i32),
+            head_ids=torch.zeros(max_bs * 2, **i32), head_pos=torch.zeros(max_bs * 2, **i32),
+            head_locs=torch.zeros(max_bs * 2, **i32), head_prefix=torch.zeros(max_bs, **i32),
+            verify_ids=torch.zeros(max_bs * G, **i32), verify_given=torch.zeros(max_bs * G, **i32))
+        self.io = K.make_cycle_io(self.bufs)
+        self.active = torch.zeros(max_bs, **i32)
+        self.active_rows = torch.zeros(max_bs, **i32)
+        self.drafts = torch.zeros(g * max_bs, **i32)                 # [gamma, bs] step-major
+        self.logq = torch.zeros(g * max_bs, dtype=torch.float32, device=device)
+        self.verify_tok = torch.zeros(max_bs * G, **i32)
+        self.verify_logp = torch.zeros(max_bs * G, dtype=torch.float32, device=device)
+        self.verify_logz = torch.zeros(max_bs * G, dtype=torch.float32, device=device)
+        self.tokens_out = torch.zeros(max_bs * G, **i32)
+        self.diff_out = torch.zeros(max_bs * g, dtype=torch.float32, device=device)
+        self.job_dst = torch.zeros(max_bs, **i32)
+        self.job_src = torch.zeros(max_bs, **i32)
+        self._arrays = None
+        self._version = -1
+        self.bs = 0
+        self.n_groups = 0
+
+    def bind(self, st) -> None:
+        self._arrays = K.make_slot_arrays(st)
+
+    def sync_membership(self, st) -> None:
+        """Refresh the persistent active-slot buffers after a group joined or left."""
+        if st.version == self._version:
+            return
+        self._version = st.version
+        self.bs = int(st.active_slots.numel())
+        self.n_groups = len(st.active_rows_host)
+        if self.bs:
+            self.active[: self.bs].copy_(st.active_slots, non_blocking=True)
+            self.active_rows[: self.n_groups].copy_(st.active_rows, non_blocking=True)
+
+    # ---- SlotState hooks --------------------------------------------------------
+    def prepare_cycle(self, st, slots) -> CycleInputs:
+        if self._arrays is None:
+            self.bind(st)
+        self.sync_membership(st)
+        bs, G = self.bs, self.G
+        K.prepare_cycle(self._arrays, self.active, bs, G, st.counters, self.io)
+        b = self.bufs
+        return CycleInputs(slots=self.active[:bs], orig_seq_lens=b["orig_seq"][:bs], x0=b["x0"][:bs],
+                           prev=b["prev"][:bs], cache_locs=b["cache_locs"][: bs * G].view(bs, G))
+
+    def write_back(self, st, cin: CycleInputs, out: CycleOutputs) -> None:
+        """Eager-path entry: the outputs come from a torch-computed cycle, so restage them."""
+        bs, g, G = self.bs, self.gamma, self.G
+        self.drafts[: g * bs].view(g, bs).copy_(out.tokens[:, :g].t())
+        self.verify_tok[: bs * G].view(bs, G)[:, g] = out.tokens[:, g]
+        # store diff as alpha * logp - logq with logq = 0
+        self.logq[: g * bs].zero_()
+        self.verify_logp[: bs * G].view(bs, G)[:, :g] = out.logprob_diff.float()
+        use_logz = out.bonus_logz is not None
+        if use_logz:
+            self.verify_logz[: bs * G].view(bs, G)[:, g] = out.bonus_logz.float()
+        K.write_back(self._arrays, self.active, bs, g, self.drafts, self.logq, self.verify_tok, self.verify_logp,
+                     self.verify_logz, 1.0, use_logz, self.tokens_out, self.diff_out)
+
+    def write_back_native(self, st, alpha: float) -> None:
+        K.write_back(self._arrays, self.active, self.bs, self.gamma, self.drafts, self.logq, self.verify_tok,
+                     self.verify_logp, self.verify_logz, alpha, alpha != 1.0, self.tokens_out, self.diff_out)
+
+    def collect_and_resample(self, st) -> None:
+        K.collect_resample(self._arrays, self.active_rows, self.n_groups, st.group_to_slots, st.N, float(st.threshold),
+                           st.seed, st.counters, st.group_log_Z, self.job_dst, self.job_src)
+        max_jobs = self.n_groups * (st.N - 1)
+        for pool in st.state_pools:
+            K.state_copy(pool.conv, pool.conv.shape[0], pool.n_rows, st.counters, self.job_dst, self.job_src, max_jobs)
+            K.state_copy(pool.temporal, pool.temporal.shape[0], pool.n_rows, st.counters, self.job_dst, self.job_src,
+                         max_jobs)
+
+
+class NativeRunner:
+    """Drives the kernel-chain forwards for one scheduler; owns the captured cycle graphs."""
+
+    def __init__(self, sched, nstate: NativeState):
+        a = sched.args
+        self.args = a
+        self.ns = nstate
+        self.device = sched.device
+        self.gamma, self.G = a.gamma, a.gamma + 1
+        self.max_bs = sched.max_groups * a.n_particles
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        pdl = _env_flag("SMC_PDL", True)
+        self.pdl = pdl
+        splits = int(a.attention_num_kv_splits)
+        self.target = self._wrap(sched.target, sched.kv_t, sched.bt.table, self.max_bs * self.G, self.max_bs * self.G,
+                                 splits, pdl)
+        self.draft = self._wrap(sched.draft, sched.kv_d, sched.bt.table, self.max_bs * 2, self.max_bs, splits, pdl)
+        self.nchunks = 32
+        rows = self.max_bs * self.G
+        self.sample_scratch = torch.empty(K.sample_scratch_bytes(rows, self.nchunks), dtype=torch.uint8,
+                                          device=self.device)
+        self.seed = int(a.random_seed) * 1000003 + 12345
+        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.use_graph = bool(a.cycle_graph)
+        self.T_draft, self.T_target, self.alpha = float(a.draft_temperature), float(a.target_temperature), float(a.power_alpha)
+        self.defer = bool(a.defer_bonus)
+        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.launches_per_cycle = 0
+
+    def _wrap(self, model, kv, bt, max_tokens, max_logit_rows, splits, pdl):
+        if model.cfg.arch != "llama":
+            from .native_hybrid import NativeHybrid
+            return NativeHybrid(model, kv, bt, max_tokens, max_logit_rows, splits, self.status, pdl, runner=self)
+        return NativeLlama(model, kv, bt, max_tokens, max_logit_rows, splits, self.status, pdl)
+
+    # ---- prefill: plain PyTorch forward on the GPU (one pass per request) ----------
+    def prefill(self, worker, items) -> torch.Tensor:
+        native, worker.native = worker.native, None
+        try:
+            return worker.prefill(items)
+        finally:
+            worker.native = native
+
+    # ---- the cycle, as a sequence of kernel launches ---------------------------------
+    def _sample(self, nm, rows: int, call_id: int, temperature: float, alpha: float, tokens_in, tok_out, logp_out,
+                logz_out) -> None:
+        K.sample_or_score(nm.logits, rows=rows, V=nm.c.vocab_size if nm.m.tp_size == 1 else nm.V, splits=1,
+                          split_stride=0, row_stride=nm.logits.stride(0), temperature=temperature, alpha=alpha,
+                          softcap=float(nm.c.logit_softcap), tokens_in=tokens_in, seed=self.seed,
+                          cycle_counter=self._counters, call_id=call_id, scratch=self.sample_scratch,
+                          nchunks=self.nchunks, tok_out=tok_out, logp_out=logp_out, logz_out=logz_out, pdl=self.pdl)
+
+    def _cycle_body(self, st) -> None:
+        ns, b = self.ns, self.ns.bufs
+        bs, g, G = ns.bs, self.gamma, self.G
+        self._counters = st.counters
+        rows = ns.active[:bs]
+        dr, lq = ns.drafts, ns.logq
+        if self.defer:
+            self.draft.forward(b["head_ids"], b["head_pos"], b["head_locs"], rows, b["head_prefix"], bs, 2)
+            self.draft.lm_head(bs, row_offset=1, row_step=2)
+            self._sample(self.draft, bs, 0, self.T_draft, 1.0, None, dr[:bs], lq[:bs], None)
+            for s in range(1, g):
+                self.draft.forward(dr[(s - 1) * bs: s * bs], b["step_pos"][s * bs:(s + 1) * bs],
+                                   b["step_locs"][s * bs:(s + 1) * bs], rows, b["step_pos"][s * bs:(s + 1) * bs], bs, 1)
+                self.draft.lm_head(bs)
+                self._sample(self.draft, bs, s, self.T_draft, 1.0, None, dr[s * bs:(s + 1) * bs],
+                             lq[s * bs:(s + 1) * bs], None)
+        else:
+            for s in range(g + 1):
+                ids = b["x0"] if s == 0 else dr[(s - 1) * bs: s * bs]
+                self.draft.forward(ids, b["step_pos"][s * bs:(s + 1) * bs], b["step_locs"][s * bs:(s + 1) * bs], rows,
+                                   b["step_pos"][s * bs:(s + 1) * bs], bs, 1)
+                if s == g:
+                    break
+                self.draft.lm_head(bs)
+                self._sample(self.draft, bs, s, self.T_draft, 1.0, None, dr[s * bs:(s + 1) * bs],
+                             lq[s * bs:(s + 1) * bs], None)
+        K.assemble_verify(ns.io, dr, bs, g)
+        self.target.forward(b["verify_ids"], b["positions_verify"], b["cache_locs"], rows, b["orig_seq"], bs, G)
+        self.target.lm_head(bs * G)
+        self._sample(self.target, bs * G, g + 1, self.T_target, self.alpha, b["verify_given"], ns.verify_tok,
+                     ns.verify_logp, ns.verify_logz)
+
+    def decode_cycle(self, worker, cin: CycleInputs) -> CycleOutputs:
+        """Eager kernel chain for one cycle (the graph path replays the same launches)."""
+        st = self.st
+        self._cycle_body(st)
+        ns = self.ns
+        bs, g, G = ns.bs, self.gamma, self.G
+        drafts = ns.drafts[: g * bs].view(g, bs).t()
+        tokens = torch.cat([drafts, ns.verify_tok[: bs * G].view(bs, G)[:, g:]], dim=1)
+        diff = self.alpha * ns.verify_logp[: bs * G].view(bs, G)[:, :g] - ns.logq[: g * bs].view(g, bs).t()
+        logz = ns.verify_logz[: bs * G].view(bs, G)[:, g] if self.alpha != 1.0 else None
+        return CycleOutputs(tokens=tokens, logprob_diff=diff, bonus_logz=logz)
+
+    # ---- whole-cycle graph ----------------------------------------------------------
+    def can_run_cycle(self, st) -> bool:
+        return True
+
+    def _full_cycle(self, st) -> None:
+        ns = self.ns
+        K.prepare_cycle(ns._arrays, ns.active, ns.bs, self.G, st.counters, ns.io)
+        self._cycle_body(st)
+        ns.write_back_native(st, self.alpha)
+        ns.collect_and_resample(st)
+
+    def run_cycle(self, st, worker) -> None:
+        ns = self.ns
+        if ns._arrays is None:
+            ns.bind(st)
+        ns.sync_membership(st)
+        st.step += 1
+        bs = ns.bs
+        if not self.use_graph:
+            self._full_cycle(st)
+            return
+        gr = self.graphs.get(bs)
+        if gr is None:
+            # warm up once eagerly on a side stream (also JIT-free: everything is precompiled), then capture
+            gr = torch.cuda.CUDAGraph()
+            saved = self._save_state(st)
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._full_cycle(st)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            self._restore_state(st, saved)
+            n0 = K.launch_count
+            with torch.cuda.graph(gr):
+                self._full_cycle(st)
+            self.launches_per_cycle = K.launch_count - n0
+            self._restore_state(st, saved)
+            self.graphs[bs] = gr
+        gr.replay()
+
+    # capture runs the cycle for real; put the mutable state back afterwards
+    def _mutable(self, st) -> List[torch.Tensor]:
+        al = st.alloc
+        ts = [st.seq_lens, st.verified_ids, st.prev_ids, st.token_counts, st.finished, st.finished_len, st.finish_code,
+              st.matched_eos, st.log_weights, st.interval_weights, st.group_log_Z, st.counters, al.refcount,
+              al.free_stack, al.free_count, al.error_flag, st.bt.table]
+        for pool in st.state_pools:
+            ts += [pool.conv, pool.temporal]
+        return ts
+
+    def _save_state(self, st):
+        return [t.clone() for t in self._mutable(st)]
+
+    def _restore_state(self, st, saved) -> None:
+        for t, s in zip(self._mutable(st), saved):
+            t.copy_(s)
+
+    def check_status(self) -> int:
+        self._status_host.copy_(self.status)
+        return int(self._status_host[0])
+
+
+def create(sched, comm=None):
+    """Build the device-state and runner objects for a scheduler."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("the native backend needs a CUDA device")
+    K.lib()     # fail loudly if the kernel library is missing
+    ns = NativeState(sched.max_groups * sched.args.n_particles, sched.args.gamma, sched.device)
+    runner = NativeRunner(sched, ns)
+    return ns, runner

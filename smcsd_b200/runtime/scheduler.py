@@ -125,6 +125,8 @@ class SMCScheduler:
                                resample_method=a.resample_method, state_pools=pools, native=self.native_state)
         if a.resample_method != "systematic" and backend == "native":
             raise ValueError("the fused resampling kernels implement 'systematic' only")
+        if self.native_runner is not None:
+            self.native_runner.st = self.state
         self.worker = SMCWorker(a, self.target, self.draft, self.kv_t, self.kv_d, self.bt, self.alloc,
                                 self.state_t, self.state_d, native_runner=self.native_runner)
         # ---- queues -------------------------------------------------------------
@@ -139,6 +141,9 @@ class SMCScheduler:
         self._profile_steps_left = None
         self._cycle_events: List = []
         self.emit_particles = a.emit_particle_output
+        # bytes moved across PCIe by this scheduler (prompt uploads; snapshots and final tokens back)
+        self.io_bytes = {"h2d": 0, "d2h": 0}
+        self.worker.io_bytes = self.io_bytes
 
     # ------------------------------------------------------------------ intake
     def add_request(self, req: GenerateRequest) -> None:
@@ -274,6 +279,7 @@ class SMCScheduler:
         self.stats["cycles"] += 1
         self.stats["decode_tokens"] += st.bs * (self.args.gamma + 1)
         snap = st.snapshot_to_host()
+        self.io_bytes["d2h"] += snap.finished.numel() + 8
         self.pending.append((snap, list(self.running.keys())))
 
     def _process_snapshot(self, snap: HostSnapshot, rids: List[str]) -> None:
@@ -294,6 +300,7 @@ class SMCScheduler:
 
     def _finalize(self, g: SequenceGroup) -> None:
         res = self.state.finalize_group(g.rid, self.final_gen)
+        self.io_bytes["d2h"] += self.args.n_particles * (self.state.max_output_len * 4 + 40)
         L = len(g.req.input_ids)
         out = RequestOutput(g.rid, res["output_ids"], True, res["finish_reason"], L, len(res["output_ids"]))
         if self.emit_particles:

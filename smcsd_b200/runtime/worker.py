@@ -49,6 +49,7 @@ class SMCWorker:
         self.gen = torch.Generator(device=self.device)
         self.gen.manual_seed(int(args.random_seed) * 7919 + 17)
         self.cycles = 0
+        self.io_bytes = {"h2d": 0, "d2h": 0}
 
     # ------------------------------------------------------------------ prefill
     def prefill(self, items: Sequence[PrefillItem]) -> torch.Tensor:
@@ -57,7 +58,10 @@ class SMCWorker:
         if self.native is not None:
             return self.native.prefill(self, items)
         lens = [len(it.input_ids) for it in items]
-        ids = torch.tensor([t for it in items for t in it.input_ids], dtype=torch.int64, device=self.device)
+        ids = torch.tensor([t for it in items for t in it.input_ids], dtype=torch.int64)
+        if self.device.type == "cuda":          # prompts cross PCIe from pinned memory
+            ids = ids.pin_memory().to(self.device, non_blocking=True)
+            self.io_bytes["h2d"] += ids.numel() * 8
         pos = torch.cat([torch.arange(L, device=self.device) for L in lens])
         locs = torch.cat([self.bt.table[it.row, :L] for it, L in zip(items, lens)])
         rows = torch.tensor([it.row for it in items], dtype=torch.int32, device=self.device)
@@ -80,6 +84,7 @@ class SMCWorker:
             dbatch = batch
         if sum(dbatch.lens()) > 0:
             self.draft.forward_torch(dbatch, self.kv_d, self.bt.table, self.state_d)
+        self.io_bytes["d2h"] += 4 * len(items)
         return x0.to(torch.int32)
 
     # ------------------------------------------------------------------ decode

@@ -1,0 +1,310 @@
+"""sm_100a kernels against plain-PyTorch fp32 references (needs a B200)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _K():
+    from smcsd_b200.ops import native as K
+    K.lib()
+    return K
+
+
+def _status():
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+# ------------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("N,Kd,M,splits", [
+    (3072, 2048, 8, 0), (6144, 4096, 72, 0), (2048, 8192, 8, 0), (4096, 14336, 72, 0), (512, 256, 16, 1),
+    (1024, 688, 5, 2), (2048, 2048, 200, 1), (2048, 1024, 300, 3), (128256, 2048, 8, 1), (4096, 4096, 33, 0),
+    (300, 512, 100, 1),
+])
+def test_gemm_partials(N, Kd, M, splits):
+    K = _K()
+    torch.manual_seed(0)
+    W = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    X = torch.randn(M, Kd, device="cuda").bfloat16()
+    s = splits or K.gemm_default_splits(N, Kd, M)
+    out = torch.full((s, M, N), float("nan"), device="cuda")
+    st = _status()
+    K.gemm_skinny(W, X, out, M=M, splits=s, epi=K.EPI_PARTIAL_F32, status=st)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    ref = X.float() @ W.float().t()
+    got = out.sum(0)
+    err = (got - ref).abs().max().item()
+    assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
+
+
+def test_gemm_bf16_and_strided_rows():
+    K = _K()
+    torch.manual_seed(1)
+    N, Kd, M = 1024, 512, 8
+    W = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    X2 = torch.randn(2 * M, Kd, device="cuda").bfloat16()
+    out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    st = _status()
+    # every second row starting at row 1 (the draft head reads only its x0 rows this way)
+    K.gemm_skinny(W, X2[1:], out, M=M, splits=1, epi=K.EPI_BF16, ldx=2 * Kd, status=st)
+    torch.cuda.synchronize()
+    ref = X2[1::2].float() @ W.float().t()
+    assert int(st) == 0
+    assert (out.float() - ref).abs().max().item() < 3e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("ffn,d,M", [(8192, 2048, 8), (14336, 4096, 72), (1024, 256, 40)])
+def test_gemm_swiglu_epilogue(ffn, d, M):
+    K = _K()
+    from smcsd_b200.models.llama import interleave_gate_up
+    torch.manual_seed(2)
+    Wg = (torch.randn(ffn, d, device="cuda") * 0.05).bfloat16()
+    Wu = (torch.randn(ffn, d, device="cuda") * 0.05).bfloat16()
+    Wgu = interleave_gate_up(Wg, Wu, 64)
+    X = torch.randn(M, d, device="cuda").bfloat16()
+    act = torch.zeros(M, ffn, device="cuda", dtype=torch.bfloat16)
+    st = _status()
+    K.gemm_skinny(Wgu, X, act, M=M, splits=1, epi=K.EPI_SWIGLU_BF16, ldo=ffn, status=st)
+    torch.cuda.synchronize()
+    g, u = X.float() @ Wg.float().t(), X.float() @ Wu.float().t()
+    ref = torch.nn.functional.silu(g) * u
+    assert int(st) == 0
+    assert (act.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
+    # the unfused path (partials + separate activation kernel) agrees
+    s = 2
+    part = torch.zeros(s, M, 2 * ffn, device="cuda")
+    K.gemm_skinny(Wgu, X, part, M=M, splits=s, epi=K.EPI_PARTIAL_F32, status=st)
+    act2 = torch.zeros_like(act)
+    K.swiglu_partials(part, s, M * 2 * ffn, act2, M=M, ffn=ffn, blk=64)
+    torch.cuda.synchronize()
+    assert (act2.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
+
+
+# ------------------------------------------------------------------------------- norm / rope
+def test_add_rmsnorm_and_embed():
+    K = _K()
+    from smcsd_b200.models.layers import rmsnorm
+    torch.manual_seed(3)
+    M, d, S = 9, 2048, 3
+    h = torch.randn(M, d, device="cuda")
+    part = torch.randn(S, M, d, device="cuda")
+    w = torch.randn(d, device="cuda").bfloat16()
+    xn = torch.zeros(M, d, device="cuda", dtype=torch.bfloat16)
+    h_ref = h + part.sum(0)
+    K.add_rmsnorm(h, w, xn, M=M, d=d, eps=1e-5, partials=part, splits=S, split_stride=M * d)
+    torch.cuda.synchronize()
+    assert torch.allclose(h, h_ref, atol=1e-5)
+    ref = rmsnorm(h_ref, w.float(), 1e-5)
+    assert (xn.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
+    emb = torch.randn(100, d, device="cuda").bfloat16()
+    ids = torch.randint(0, 100, (M,), device="cuda", dtype=torch.int32)
+    K.add_rmsnorm(h, w, xn, M=M, d=d, eps=1e-5, ids=ids, embed=emb, plus_one=True)
+    torch.cuda.synchronize()
+    assert torch.equal(h, emb[ids.long()].float())
+    ref = rmsnorm(h, w.float(), 1e-5, plus_one=True)
+    assert (xn.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,rd", [(32, 8, 64, 64), (32, 8, 128, 128), (4, 2, 256, 64)])
+def test_rope_kv_write(Hq, Hkv, D, rd):
+    K = _K()
+    from smcsd_b200.models.layers import apply_rope, rope_table
+    torch.manual_seed(4)
+    M, S, pages = 7, 2, 50
+    n = (Hq + 2 * Hkv) * D
+    part = torch.randn(S, M, n, device="cuda")
+    pos = torch.randint(0, 500, (M,), device="cuda", dtype=torch.int32)
+    locs = torch.randperm(pages, device="cuda")[:M].to(torch.int32) + 1
+    table = rope_table(rd, 10000.0, None, 512, "cuda")
+    q = torch.zeros(M, Hq * D, device="cuda", dtype=torch.bfloat16)
+    kp = torch.zeros(pages + 1, Hkv * D, device="cuda", dtype=torch.bfloat16)
+    vp = torch.zeros_like(kp)
+    st = _status()
+    K.rope_kv_write(part, S, M * n, pos, locs, table, q, kp, vp, M=M, Hq=Hq, Hkv=Hkv, D=D, status=st)
+    torch.cuda.synchronize()
+    full = part.sum(0)
+    qr = apply_rope(full[:, :Hq * D].view(M, Hq, D), pos, table).reshape(M, -1)
+    kr = apply_rope(full[:, Hq * D:(Hq + Hkv) * D].view(M, Hkv, D), pos, table).reshape(M, -1)
+    vr = full[:, (Hq + Hkv) * D:]
+    assert int(st) == 0
+    assert (q.float() - qr).abs().max().item() < 3e-2
+    assert (kp[locs.long()].float() - kr).abs().max().item() < 3e-2
+    assert (vp[locs.long()].float() - vr).abs().max().item() < 3e-2
+
+
+# ------------------------------------------------------------------------------- attention
+@pytest.mark.parametrize("bs,E,Hq,Hkv,D,ctx", [
+    (8, 9, 32, 8, 128, 1500), (8, 9, 32, 8, 128, 3), (5, 2, 32, 8, 64, 300), (8, 1, 32, 8, 64, 700),
+    (3, 9, 4, 4, 64, 200), (4, 9, 16, 2, 256, 260), (2, 5, 4, 2, 64, 0),
+])
+def test_attention_extend(bs, E, Hq, Hkv, D, ctx):
+    K = _K()
+    from smcsd_b200.models.layers import ExtendBatch, paged_attention_reference
+    torch.manual_seed(5)
+    pages = bs * (ctx + E) + 64
+    kp = torch.randn(pages + 1, Hkv * D, device="cuda").bfloat16()
+    vp = torch.randn(pages + 1, Hkv * D, device="cuda").bfloat16()
+    max_ctx = ctx + E + 8
+    bt = torch.zeros(bs + 2, max_ctx, device="cuda", dtype=torch.int32)
+    perm = (torch.randperm(pages, device="cuda") + 1).to(torch.int32)
+    prefix = torch.tensor([max(0, ctx - 17 * i) for i in range(bs)], device="cuda", dtype=torch.int32)
+    rows = torch.arange(bs, device="cuda", dtype=torch.int32) + 1
+    off = 0
+    for b in range(bs):
+        L = int(prefix[b]) + E
+        bt[b + 1, :L] = perm[off:off + L]
+        off += L
+    q = torch.randn(bs * E, Hq, D, device="cuda").bfloat16()
+    splits = 8
+    pa = torch.zeros(bs * E * Hq * splits * D, device="cuda")
+    pm = torch.zeros(bs * E * Hq * splits * 2, device="cuda")
+    out = torch.zeros(bs * E, Hq * D, device="cuda", dtype=torch.bfloat16)
+    st = _status()
+    K.attention_extend(q, kp, vp, bt, rows, prefix, pa, pm, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D, splits=splits,
+                       scale=D ** -0.5, status=st)
+    torch.cuda.synchronize()
+    batch = ExtendBatch(None, None, None, rows, prefix, extend_len=E)
+    ref = paged_attention_reference(q, kp, vp, bt, batch, Hkv).reshape(bs * E, -1).float()
+    assert int(st) == 0
+    err = (out.float() - ref).abs().max().item()
+    assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
+
+
+# ------------------------------------------------------------------------------- sampling
+def _sample(K, logits, T, alpha, tokens_in, seed=7, counter=0, call_id=0, softcap=0.0):
+    rows, V = logits.shape
+    nch = 32
+    scratch = torch.empty(K.sample_scratch_bytes(rows, nch), dtype=torch.uint8, device="cuda")
+    tok = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    lp = torch.zeros(rows, device="cuda")
+    lz = torch.zeros(rows, device="cuda")
+    ctr = torch.tensor([counter], dtype=torch.int64, device="cuda")
+    K.sample_or_score(logits, rows=rows, V=V, splits=1, split_stride=0, row_stride=logits.stride(0), temperature=T,
+                      alpha=alpha, softcap=softcap, tokens_in=tokens_in, seed=seed, cycle_counter=ctr, call_id=call_id,
+                      scratch=scratch, nchunks=nch, tok_out=tok, logp_out=lp, logz_out=lz)
+    torch.cuda.synchronize()
+    return tok, lp, lz
+
+
+def test_score_mode_matches_torch():
+    K = _K()
+    from smcsd_b200.smc.math import chosen_logprob
+    torch.manual_seed(6)
+    logits = torch.randn(72, 128256, device="cuda") * 3
+    toks = torch.randint(0, 128256, (72,), device="cuda", dtype=torch.int32)
+    _, lp, _ = _sample(K, logits, 0.7, 1.0, toks)
+    ref = chosen_logprob(logits, toks.long(), 0.7)
+    assert (lp - ref).abs().max().item() < 2e-3
+
+
+def test_sample_mode_logp_logz_and_determinism():
+    K = _K()
+    torch.manual_seed(7)
+    logits = torch.randn(8, 128256, device="cuda") * 2
+    alpha, T = 1.7, 0.7
+    tok, lp, lz = _sample(K, logits, T, alpha, None)
+    scaled = alpha * logits / T
+    ref_lp = scaled.gather(1, tok.long().unsqueeze(1)).squeeze(1) - torch.logsumexp(scaled, -1)
+    ref_lz = torch.logsumexp(scaled, -1) - alpha * torch.logsumexp(logits / T, -1)
+    assert (lp - ref_lp).abs().max().item() < 2e-3
+    assert (lz - ref_lz).abs().max().item() < 2e-3
+    _, _, lz1 = _sample(K, logits, T, 1.0, None)
+    assert lz1.abs().max().item() == 0.0
+    tok2, _, _ = _sample(K, logits, T, alpha, None)
+    assert torch.equal(tok, tok2)
+    tok3, _, _ = _sample(K, logits, T, alpha, None, counter=1)
+    assert not torch.equal(tok, tok3)
+    # mixed rows: given tokens are scored, the rest sampled
+    given = torch.full((8,), -1, dtype=torch.int32, device="cuda")
+    given[:4] = 5
+    tok4, lp4, _ = _sample(K, logits, T, 1.0, given)
+    assert (tok4[:4] == 5).all()
+    ref = (logits / T)[:4, 5] - torch.logsumexp(logits[:4] / T, -1)
+    assert (lp4[:4] - ref).abs().max().item() < 2e-3
+
+
+def test_sample_distribution_tv():
+    K = _K()
+    torch.manual_seed(8)
+    V, rows = 512, 2000
+    base = torch.randn(V, device="cuda") * 1.5
+    logits = base.unsqueeze(0).repeat(rows, 1).contiguous()
+    counts = torch.zeros(V, device="cuda")
+    for it in range(10):
+        tok, _, _ = _sample(K, logits, 0.7, 1.0, None, counter=it)
+        counts += torch.bincount(tok.long(), minlength=V).float()
+    emp = counts / counts.sum()
+    p = torch.softmax(base / 0.7, -1)
+    assert 0.5 * (emp - p).abs().sum().item() < 0.08
+
+
+# ------------------------------------------------------------------------------- SMC state kernels
+def _make_states(N=4, groups=3, gamma=4, seed=0):
+    from smcsd_b200.memory.pools import BlockTable, PageAllocator
+    from smcsd_b200.ops.native_backend import NativeState
+    from smcsd_b200.runtime.slot_state import SlotState
+    out = []
+    for native in (False, True):
+        alloc = PageAllocator(4096, "cuda")
+        bt = BlockTable(groups * N, 4, 256, "cuda")
+        ns = NativeState(groups * N, gamma, torch.device("cuda")) if native else None
+        st = SlotState(max_groups=groups, n_particles=N, gamma=gamma, max_output_len=256, block_table=bt,
+                       allocator=alloc, device="cuda", seed=seed, resample_threshold=0.5, native=ns)
+        for gi in range(groups):
+            L = 10 + gi
+            row = bt.alloc_parent_row()
+            pages = alloc.alloc(L)
+            bt.table[row, :L] = pages
+            st.allocate_group(f"g{gi}", prompt_len=L, x0=100 + gi, last_prompt_token=7, max_new_tokens=20 - 6 * gi,
+                              ignore_eos=(gi == 1), eos_ids=[3, 5], parent_row=row)
+            bt.free_parent_row(row)
+        out.append(st)
+    return out
+
+
+def test_state_kernels_match_torch_reference():
+    _K()
+    from smcsd_b200.runtime.slot_state import CycleOutputs
+    ref, nat = _make_states()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for cyc in range(5):
+        cr, cn = ref.prepare_cycle(), nat.prepare_cycle()
+        assert torch.equal(cr.orig_seq_lens, cn.orig_seq_lens) and torch.equal(cr.x0, cn.x0)
+        assert torch.equal(cr.prev, cn.prev)
+        bs = cr.slots.numel()
+        tokens = torch.randint(0, 12, (bs, 5), generator=g, device="cuda", dtype=torch.int32)
+        diff = torch.randn(bs, 4, generator=g, device="cuda") * 2.0
+        logz = torch.randn(bs, generator=g, device="cuda") * 0.1
+        out = CycleOutputs(tokens, diff, logz)
+        ref.write_back(cr, out)
+        nat.write_back(cn, out)
+        torch.cuda.synchronize()
+        for f in ("token_counts", "finished", "finished_len", "finish_code", "matched_eos", "verified_ids", "prev_ids"):
+            assert torch.equal(getattr(ref, f), getattr(nat, f)), (cyc, f)
+        assert torch.allclose(ref.log_weights, nat.log_weights, atol=1e-5)
+        assert torch.equal(ref.all_token_ids, nat.all_token_ids)
+        ref.resample()
+        nat.resample()
+        torch.cuda.synchronize()
+        assert torch.equal(ref.seq_lens, nat.seq_lens)
+        assert torch.allclose(ref.interval_weights, nat.interval_weights, atol=1e-5), cyc
+        assert torch.allclose(ref.group_log_Z, nat.group_log_Z, atol=1e-5), cyc
+        assert torch.equal(ref.all_token_ids, nat.all_token_ids)
+        assert torch.equal(ref.token_counts, nat.token_counts)
+        # same sharing structure: each row's pages have the same refcounts in both worlds
+        for s in range(ref.max_slots):
+            L = int(ref.seq_lens[s])
+            rr = ref.alloc.refcount[ref.bt.table[s, :L].long()]
+            rn = nat.alloc.refcount[nat.bt.table[s, :L].long()]
+            assert torch.equal(rr, rn), (cyc, s)
+        assert ref.alloc.available() == nat.alloc.available()
+        nat.alloc.check_conservation()
+    assert int(nat.counters[2]) > 0, "no group resampled: the test did not exercise the copy path"
+    for gi in range(3):
+        nat.free_group(f"g{gi}")
+        ref.free_group(f"g{gi}")
+    nat.alloc.check_conservation()
+    assert nat.alloc.available() == nat.alloc.size
