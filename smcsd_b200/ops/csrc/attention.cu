@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(32 * 8) attn_extend_kernel(const AttnParams p)
   const int b = blockIdx.x / p.Hkv, kvh = blockIdx.x % p.Hkv;
   const int split = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (p.pdl) pdl_wait_prior_grid();
+  if (p.pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
 
   // stage this CTA's query rows: row r = e * G + g  ->  token b * E + e, head kvh * G + g
   for (int idx = threadIdx.x; idx < R * (D / 8); idx += blockDim.x) {
@@ -148,7 +148,6 @@ __global__ void __launch_bounds__(32 * 8) attn_extend_kernel(const AttnParams p)
       }
     }
   }
-  if (p.pdl) pdl_launch_dependents();
   // ---- write this split's partial state
 #pragma unroll
   for (int r = 0; r < RW; ++r) {
@@ -170,7 +169,7 @@ __global__ void __launch_bounds__(32 * 8) attn_extend_kernel(const AttnParams p)
 // out[qrow, :] = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M)
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                   __nv_bfloat16* __restrict__ out, int splits, int D, int pdl) {
-  if (pdl) pdl_wait_prior_grid();
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const size_t qrow = blockIdx.x;
   float M = -INFINITY;
   for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(qrow * splits + s) * 2]);
@@ -188,7 +187,6 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const floa
     }
     out[qrow * D + d] = __float2bfloat16(a * inv);
   }
-  if (pdl) pdl_launch_dependents();
 }
 
 template <int D, int RW>

@@ -1,0 +1,500 @@
+// Fused attention step for uniform extend length E (1 = draft decode, 2 = draft head,
+// gamma+1 = target verify) over the token-granular paged KV cache.  One launch per layer does
+//   q/k/v of the new tokens from the fp32 QKV GEMM output: optional per-head RMSNorm, rotary
+//   embedding, bf16 rounding; new K/V rows written to their pages
+//   attention of the E*G query rows of one KV head (GQA packed) over [cached prefix | new tokens]
+//   merge of the CTA's key-ways, optional sigmoid output gate, bf16 output rows
+// so the separate rope / KV-write / split-merge kernels disappear from the hot loop.
+//
+// CTA = (sequence, kv head[, key split]); warps = m-tiles (16 query rows each) x key-ways.  Each
+// key-way streams 32-key tiles: page ids are read once per range, K/V rows are gathered into
+// padded shared-memory tiles with cp.async (all rows of a tile in flight together, double
+// buffered), scores and P*V run on tensor cores (mma.sync m16n8k16, bf16 in / fp32 out) with
+// flash-style running max / sum in registers.  The new tokens form a last, causally masked tile
+// served from shared memory.
+#include "common.cuh"
+
+namespace smc {
+
+struct FusedAttnParams {
+  const float* qkv;          // [T, ld_qkv] fp32
+  int ld_qkv, q_off, gate_off, k_off, v_off;
+  const int* positions;      // [T]
+  const int* cache_locs;     // [T]
+  const float* rope;         // [max_pos, rd] cos | sin
+  int rd, max_pos;
+  const __nv_bfloat16* qn_w; // [D] or null: per-head RMSNorm weights for q and k
+  const __nv_bfloat16* kn_w;
+  float norm_eps;
+  int norm_plus_one;
+  __nv_bfloat16* k_pool;     // [pages + 1, Hkv * D]
+  __nv_bfloat16* v_pool;
+  int n_pages;
+  const int* block_table;
+  int bt_stride;
+  const int* rows;           // [bs]
+  const int* prefix_lens;    // [bs]
+  __nv_bfloat16* out;        // [T, Hq * D]
+  float* part_acc;           // [T * Hq, KS, D]   (KS > 1 only)
+  float* part_ml;            // [T * Hq, KS, 2]
+  int E, Hq, Hkv, KS, n_mt, n_kw;
+  float scale;
+  int* status;
+  int pdl;
+};
+
+constexpr int TK = 32;          // keys per streamed tile
+constexpr int RANGE = 2048;     // page ids staged per pass
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void group_barrier(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(smem_row)));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Running flash state of one warp: rows g and g+8 of its m-tile.
+template <int D>
+struct WarpState {
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[D / 8][4];
+};
+
+// One tile of NT*8 keys.  Kt / Vt: [keys][D + 8] bf16.  valid(col, row) says whether key `col` of the
+// tile is visible to local query row `row` (0..15).
+template <int D, int NT, bool Q_REGS, class Valid>
+__device__ __forceinline__ void process_tile(const __nv_bfloat16* Kt, const __nv_bfloat16* Vt,
+                                             const uint32_t (&qa)[Q_REGS ? D / 16 : 1][4],
+                                             const __nv_bfloat16* Qs_mt, float scale, WarpState<D>& st, Valid valid) {
+  constexpr int LD = D + 8;
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  float s[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    uint32_t a[4];
+    if constexpr (Q_REGS) {
+      a[0] = qa[kk][0]; a[1] = qa[kk][1]; a[2] = qa[kk][2]; a[3] = qa[kk][3];
+    } else {
+      a[0] = *reinterpret_cast<const uint32_t*>(Qs_mt + g * LD + kk * 16 + 2 * t);
+      a[1] = *reinterpret_cast<const uint32_t*>(Qs_mt + (g + 8) * LD + kk * 16 + 2 * t);
+      a[2] = *reinterpret_cast<const uint32_t*>(Qs_mt + g * LD + kk * 16 + 2 * t + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(Qs_mt + (g + 8) * LD + kk * 16 + 2 * t + 8);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const __nv_bfloat16* kr = Kt + (nt * 8 + g) * LD + kk * 16 + 2 * t;
+      mma16816(s[nt], a, *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+    }
+  }
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col = nt * 8 + 2 * t + (c & 1), row = g + 8 * (c >> 1);
+      const float v = valid(col, row) ? s[nt][c] * scale : -INFINITY;
+      s[nt][c] = v;
+      if (c < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+    }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
+  const float c0 = mn0 == -INFINITY ? 1.f : __expf(st.m0 - mn0);
+  const float c1 = mn1 == -INFINITY ? 1.f : __expf(st.m1 - mn1);
+  st.m0 = mn0; st.m1 = mn1;
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    s[nt][0] = mn0 == -INFINITY ? 0.f : __expf(s[nt][0] - mn0);
+    s[nt][1] = mn0 == -INFINITY ? 0.f : __expf(s[nt][1] - mn0);
+    s[nt][2] = mn1 == -INFINITY ? 0.f : __expf(s[nt][2] - mn1);
+    s[nt][3] = mn1 == -INFINITY ? 0.f : __expf(s[nt][3] - mn1);
+    sum0 += s[nt][0] + s[nt][1];
+    sum1 += s[nt][2] + s[nt][3];
+  }
+  st.l0 = st.l0 * c0 + sum0;
+  st.l1 = st.l1 * c1 + sum1;
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) {
+    st.o[nt][0] *= c0; st.o[nt][1] *= c0; st.o[nt][2] *= c1; st.o[nt][3] *= c1;
+  }
+  // P (bf16) x V
+  const int mat = lane >> 3, rr = lane & 7;
+#pragma unroll
+  for (int k2 = 0; k2 < NT / 2; ++k2) {
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * k2][0], s[2 * k2][1]);
+    a[1] = pack_bf16(s[2 * k2][2], s[2 * k2][3]);
+    a[2] = pack_bf16(s[2 * k2 + 1][0], s[2 * k2 + 1][1]);
+    a[3] = pack_bf16(s[2 * k2 + 1][2], s[2 * k2 + 1][3]);
+#pragma unroll
+    for (int nt = 0; nt < D / 8; nt += 2) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, Vt + (k2 * 16 + (mat & 1) * 8 + rr) * LD + (nt + (mat >> 1)) * 8);
+      mma16816(st.o[nt], a, b[0], b[1]);
+      mma16816(st.o[nt + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p) {
+  constexpr int LD = D + 8;
+  constexpr bool Q_REGS = D <= 128;
+  extern __shared__ __align__(16) uint8_t smem_fa[];
+  const int n_mt = p.n_mt, n_kw = p.n_kw;
+  const int G = p.Hq / p.Hkv, R = p.E * G, Rpad = n_mt * 16;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_fa);             // [Rpad][LD]
+  __nv_bfloat16* Kn = Qs + (size_t)Rpad * LD;                                 // [16][LD]
+  __nv_bfloat16* Vn = Kn + 16 * LD;                                           // [16][LD]
+  int* pg = reinterpret_cast<int*>(Vn + 16 * LD);                             // [RANGE]
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(pg + RANGE);        // [n_kw][2 stages][K|V][TK][LD]
+  constexpr int TILE = TK * LD;
+
+  const int b = blockIdx.x / p.Hkv, kvh = blockIdx.x % p.Hkv, ks = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mt = warp % n_mt, kw = warp / n_mt;
+  const int nwarps = blockDim.x >> 5;
+  if (p.pdl) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+  }
+  const int prefix = p.prefix_lens[b];
+  const size_t kv_row = (size_t)p.Hkv * D;
+
+  // ---- phase 0: q / k / v of the new tokens (norm, rope, bf16), one warp per head row ----------
+  const int half = p.rd >> 1;
+  for (int item = warp; item < Rpad + 32; item += nwarps) {
+    // items: [0, Rpad) q rows, [Rpad, Rpad+16) k rows, [Rpad+16, Rpad+32) v rows
+    __nv_bfloat16* dst;
+    const float* src = nullptr;
+    const __nv_bfloat16* nw = nullptr;
+    int pos = 0;
+    bool rope = false;
+    if (item < Rpad) {
+      dst = Qs + (size_t)item * LD;
+      if (item < R) {
+        const int e = item / G, gq = item % G, tkn = b * p.E + e;
+        src = p.qkv + (size_t)tkn * p.ld_qkv + p.q_off + (size_t)(kvh * G + gq) * D;
+        pos = p.positions[tkn]; rope = true; nw = p.qn_w;
+      }
+    } else {
+      const int e = (item - Rpad) & 15;
+      const bool is_k = item < Rpad + 16;
+      dst = (is_k ? Kn : Vn) + (size_t)e * LD;
+      if (e < p.E) {
+        const int tkn = b * p.E + e;
+        src = p.qkv + (size_t)tkn * p.ld_qkv + (is_k ? p.k_off : p.v_off) + (size_t)kvh * D;
+        pos = p.positions[tkn]; rope = is_k; nw = is_k ? p.kn_w : nullptr;
+      }
+    }
+    if (src == nullptr) {
+      for (int i = lane; i < D / 2; i += 32) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
+      continue;
+    }
+    if (pos < 0 || pos >= p.max_pos) {
+      if (lane == 0) atomicOr(p.status, SMC_ERR_BOUNDS);
+      pos = pos < 0 ? 0 : p.max_pos - 1;
+    }
+    float rstd = 1.f;
+    if (nw != nullptr) {
+      float ss = 0.f;
+      for (int i = lane; i < D; i += 32) ss += src[i] * src[i];
+      rstd = rsqrtf(warp_sum(ss) / (float)D + p.norm_eps);
+    }
+    const float* cs = p.rope + (size_t)pos * p.rd;
+    for (int i = lane; i < D / 2; i += 32) {
+      int i1, i2;
+      bool rot;
+      if (i < half) { i1 = i; i2 = i + half; rot = rope; }
+      else { const int j = i - half; i1 = p.rd + 2 * j; i2 = i1 + 1; rot = false; }
+      float x1 = src[i1], x2 = src[i2];
+      if (nw != nullptr) {
+        const float add = p.norm_plus_one ? 1.f : 0.f;
+        x1 *= rstd * (__bfloat162float(nw[i1]) + add);
+        x2 *= rstd * (__bfloat162float(nw[i2]) + add);
+      }
+      if (rot) {
+        const float c = cs[i], sn = cs[half + i];
+        const float y1 = x1 * c - x2 * sn, y2 = x2 * c + x1 * sn;
+        x1 = y1; x2 = y2;
+      }
+      dst[i1] = __float2bfloat16(x1);
+      dst[i2] = __float2bfloat16(x2);
+    }
+  }
+  __syncthreads();
+  // new K/V rows go to their pages (one CTA per (sequence, kv head) writes them)
+  if (ks == p.KS - 1) {
+    constexpr int CPR = D / 8;
+    for (int c = threadIdx.x; c < p.E * CPR * 2; c += blockDim.x) {
+      const bool is_v = c >= p.E * CPR;
+      const int cc = is_v ? c - p.E * CPR : c;
+      const int e = cc / CPR, col = cc % CPR;
+      int loc = p.cache_locs[b * p.E + e];
+      if (loc < 0 || loc > p.n_pages) { atomicOr(p.status, SMC_ERR_BOUNDS); loc = 0; }
+      const uint4 v = *reinterpret_cast<const uint4*>((is_v ? Vn : Kn) + (size_t)e * LD + col * 8);
+      *reinterpret_cast<uint4*>((is_v ? p.v_pool : p.k_pool) + (size_t)loc * kv_row + (size_t)kvh * D + col * 8) = v;
+    }
+  }
+
+  // ---- phase 1: query fragments -----------------------------------------------------------------
+  const int g = lane >> 2, t = lane & 3;
+  const __nv_bfloat16* Qs_mt = Qs + (size_t)mt * 16 * LD;
+  uint32_t qa[Q_REGS ? D / 16 : 1][4];
+  if constexpr (Q_REGS) {
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      qa[kk][0] = *reinterpret_cast<const uint32_t*>(Qs_mt + g * LD + kk * 16 + 2 * t);
+      qa[kk][1] = *reinterpret_cast<const uint32_t*>(Qs_mt + (g + 8) * LD + kk * 16 + 2 * t);
+      qa[kk][2] = *reinterpret_cast<const uint32_t*>(Qs_mt + g * LD + kk * 16 + 2 * t + 8);
+      qa[kk][3] = *reinterpret_cast<const uint32_t*>(Qs_mt + (g + 8) * LD + kk * 16 + 2 * t + 8);
+    }
+  }
+  WarpState<D> st;
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) st.o[nt][0] = st.o[nt][1] = st.o[nt][2] = st.o[nt][3] = 0.f;
+
+  // ---- phase 2: cached prefix, streamed in 32-key tiles -------------------------------------------
+  int per = (prefix + p.KS - 1) / p.KS;
+  per = (per + TK - 1) / TK * TK;
+  const int kb = ks * per, ke = min(prefix, kb + per);
+  const int* bt = p.block_table + (size_t)p.rows[b] * p.bt_stride;
+  const int gsize = 32 * n_mt, gt = mt * 32 + lane;   // thread index inside this key-way's group
+  __nv_bfloat16* my_tiles = tiles + (size_t)kw * 4 * TILE;
+  constexpr int CPR = D / 8;
+  for (int r0 = kb; r0 < ke; r0 += RANGE) {
+    const int r1 = min(ke, r0 + RANGE);
+    __syncthreads();
+    for (int i = threadIdx.x; i < r1 - r0; i += blockDim.x) {
+      int page = bt[r0 + i];
+      if (page < 0 || page > p.n_pages) { atomicOr(p.status, SMC_ERR_BOUNDS); page = 0; }
+      pg[i] = page;
+    }
+    __syncthreads();
+    const int ntiles = (r1 - r0 + TK - 1) / TK;
+    auto issue = [&](int tile, int stage) {
+      __nv_bfloat16* Kt = my_tiles + (size_t)stage * 2 * TILE;
+      __nv_bfloat16* Vt = Kt + TILE;
+      const int k0 = tile * TK;
+      for (int c = gt; c < TK * CPR; c += gsize) {
+        const int key = c / CPR, col = c % CPR;
+        const int page = (r0 + k0 + key < r1) ? pg[k0 + key] : 0;
+        const size_t off = (size_t)page * kv_row + (size_t)kvh * D + col * 8;
+        cp_async16(Kt + key * LD + col * 8, p.k_pool + off);
+        cp_async16(Vt + key * LD + col * 8, p.v_pool + off);
+      }
+      cp_async_commit();
+    };
+    int it = 0;
+    if (kw < ntiles) issue(kw, 0);
+    for (int tile = kw; tile < ntiles; tile += n_kw, ++it) {
+      const int stage = it & 1;
+      if (tile + n_kw < ntiles) { issue(tile + n_kw, stage ^ 1); cp_async_wait<1>(); }
+      else cp_async_wait<0>();
+      group_barrier(1 + kw, gsize);
+      const int nvalid = min(TK, r1 - r0 - tile * TK);
+      const __nv_bfloat16* Kt = my_tiles + (size_t)stage * 2 * TILE;
+      process_tile<D, TK / 8, Q_REGS>(Kt, Kt + TILE, qa, Qs_mt, p.scale, st,
+                                      [nvalid](int col, int) { return col < nvalid; });
+      group_barrier(1 + kw, gsize);
+    }
+  }
+  // ---- phase 3: the new tokens, causally masked (key-way 0 of the last split) ----------------------
+  if (ks == p.KS - 1 && kw == 0) {
+    const int E = p.E, base_row = mt * 16;
+    process_tile<D, 2, Q_REGS>(Kn, Vn, qa, Qs_mt, p.scale, st, [E, G, base_row](int col, int row) {
+      return col < E && col <= (base_row + row) / G;
+    });
+  }
+  st.l0 += __shfl_xor_sync(0xffffffffu, st.l0, 1);
+  st.l0 += __shfl_xor_sync(0xffffffffu, st.l0, 2);
+  st.l1 += __shfl_xor_sync(0xffffffffu, st.l1, 1);
+  st.l1 += __shfl_xor_sync(0xffffffffu, st.l1, 2);
+
+  // ---- phase 4: merge the key-ways in a fixed order, then write ------------------------------------
+  __syncthreads();
+  float* marea = reinterpret_cast<float*>(tiles);
+  const int slot_floats = 16 * D + 64;
+  if (kw > 0) {
+    float* slot = marea + (size_t)((kw - 1) * n_mt + mt) * slot_floats;
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt) {
+      *reinterpret_cast<float2*>(slot + g * D + nt * 8 + 2 * t) = make_float2(st.o[nt][0], st.o[nt][1]);
+      *reinterpret_cast<float2*>(slot + (g + 8) * D + nt * 8 + 2 * t) = make_float2(st.o[nt][2], st.o[nt][3]);
+    }
+    if (t == 0) {
+      slot[16 * D + g] = st.m0; slot[16 * D + 8 + g] = st.m1;
+      slot[16 * D + 16 + g] = st.l0; slot[16 * D + 24 + g] = st.l1;
+    }
+  }
+  __syncthreads();
+  if (kw == 0) {
+    for (int k2 = 1; k2 < n_kw; ++k2) {
+      const float* slot = marea + (size_t)((k2 - 1) * n_mt + mt) * slot_floats;
+      const float m0b = slot[16 * D + g], m1b = slot[16 * D + 8 + g];
+      const float l0b = slot[16 * D + 16 + g], l1b = slot[16 * D + 24 + g];
+      const float M0 = fmaxf(st.m0, m0b), M1 = fmaxf(st.m1, m1b);
+      const float a0 = M0 == -INFINITY ? 1.f : __expf(st.m0 - M0), b0 = M0 == -INFINITY ? 0.f : __expf(m0b - M0);
+      const float a1 = M1 == -INFINITY ? 1.f : __expf(st.m1 - M1), b1 = M1 == -INFINITY ? 0.f : __expf(m1b - M1);
+      st.l0 = st.l0 * a0 + l0b * b0; st.l1 = st.l1 * a1 + l1b * b1;
+      st.m0 = M0; st.m1 = M1;
+#pragma unroll
+      for (int nt = 0; nt < D / 8; ++nt) {
+        const float2 x0 = *reinterpret_cast<const float2*>(slot + g * D + nt * 8 + 2 * t);
+        const float2 x1 = *reinterpret_cast<const float2*>(slot + (g + 8) * D + nt * 8 + 2 * t);
+        st.o[nt][0] = st.o[nt][0] * a0 + x0.x * b0; st.o[nt][1] = st.o[nt][1] * a0 + x0.y * b0;
+        st.o[nt][2] = st.o[nt][2] * a1 + x1.x * b1; st.o[nt][3] = st.o[nt][3] * a1 + x1.y * b1;
+      }
+    }
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+      const int r = mt * 16 + g + 8 * hrow;
+      if (r >= R) continue;
+      const int e = r / G, gq = r % G, tkn = b * p.E + e, head = kvh * G + gq;
+      const float l = hrow ? st.l1 : st.l0, m = hrow ? st.m1 : st.m0;
+      if (p.KS == 1) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* orow = p.out + ((size_t)tkn * p.Hq + head) * D;
+        const float* grow = p.gate_off >= 0 ? p.qkv + (size_t)tkn * p.ld_qkv + p.gate_off + (size_t)head * D : nullptr;
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt) {
+          float v0 = st.o[nt][2 * hrow] * inv, v1 = st.o[nt][2 * hrow + 1] * inv;
+          if (grow != nullptr) {
+            const float2 gg = *reinterpret_cast<const float2*>(grow + nt * 8 + 2 * t);
+            v0 *= 1.f / (1.f + __expf(-gg.x));
+            v1 *= 1.f / (1.f + __expf(-gg.y));
+          }
+          *reinterpret_cast<uint32_t*>(orow + nt * 8 + 2 * t) = pack_bf16(v0, v1);
+        }
+      } else {
+        const size_t qrow = (size_t)tkn * p.Hq + head;
+        float* pa = p.part_acc + (qrow * p.KS + ks) * D;
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt)
+          *reinterpret_cast<float2*>(pa + nt * 8 + 2 * t) = make_float2(st.o[nt][2 * hrow], st.o[nt][2 * hrow + 1]);
+        if (t == 0) {
+          p.part_ml[(qrow * p.KS + ks) * 2] = m;
+          p.part_ml[(qrow * p.KS + ks) * 2 + 1] = l;
+        }
+      }
+    }
+  }
+}
+
+// merge of key splits (KS > 1) with the optional output gate
+__global__ void attn_fused_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                        __nv_bfloat16* __restrict__ out, const float* __restrict__ qkv, int ld_qkv,
+                                        int gate_off, int Hq, int KS, int D, int pdl) {
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
+  const size_t qrow = blockIdx.x;
+  const int tkn = (int)(qrow / Hq), head = (int)(qrow % Hq);
+  float M = -INFINITY;
+  for (int s = 0; s < KS; ++s) M = fmaxf(M, part_ml[(qrow * KS + s) * 2]);
+  float denom = 0.f;
+  for (int s = 0; s < KS; ++s) {
+    const float m = part_ml[(qrow * KS + s) * 2];
+    if (m != -INFINITY) denom += part_ml[(qrow * KS + s) * 2 + 1] * __expf(m - M);
+  }
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < KS; ++s) {
+      const float m = part_ml[(qrow * KS + s) * 2];
+      if (m != -INFINITY) a += part_acc[(qrow * KS + s) * D + d] * __expf(m - M);
+    }
+    a *= inv;
+    if (gate_off >= 0) {
+      const float gv = qkv[(size_t)tkn * ld_qkv + gate_off + (size_t)head * D + d];
+      a *= 1.f / (1.f + __expf(-gv));
+    }
+    out[qrow * D + d] = __float2bfloat16(a);
+  }
+}
+
+static size_t fused_smem_bytes(int D, int n_mt, int n_kw) {
+  const size_t LD = D + 8;
+  size_t b = ((size_t)n_mt * 16 + 32) * LD * 2 + RANGE * 4;
+  size_t tiles = (size_t)n_kw * 4 * TK * LD * 2;
+  size_t merge = (size_t)(n_kw > 1 ? (n_kw - 1) * n_mt : 0) * (16 * D + 64) * 4;
+  return b + (tiles > merge ? tiles : merge);
+}
+
+}  // namespace smc
+
+// qkv: fp32 [T, ld_qkv] with query heads at q_off, optional gate heads at gate_off (< 0: none), key heads
+// at k_off, value heads at v_off.  out: bf16 [T, Hq*D].  part_acc / part_ml: scratch, used when KS > 1.
+SMC_API int smc_attention_fused(const float* qkv, int ld_qkv, int q_off, int gate_off, int k_off, int v_off,
+                                const int* positions, const int* cache_locs, const float* rope, int rd, int max_pos,
+                                const void* qn_w, const void* kn_w, float norm_eps, int norm_plus_one, void* k_pool,
+                                void* v_pool, int n_pages, const int* block_table, int bt_stride, const int* rows,
+                                const int* prefix_lens, void* out, float* part_acc, float* part_ml, int bs, int E,
+                                int Hq, int Hkv, int D, int KS, float scale, int* status, int pdl, cudaStream_t st) {
+  using namespace smc;
+  if (bs <= 0) return 0;
+  if (Hq % Hkv || E < 1 || E > 16 || (rd & 1) || rd > D) return -70;
+  const int G = Hq / Hkv, R = E * G;
+  const int n_mt = (R + 15) / 16;
+  if (n_mt > 8) return -71;
+  int n_kw = 8 / n_mt;
+  if (n_kw > 4) n_kw = 4;
+  if (n_kw < 1) n_kw = 1;
+  FusedAttnParams p;
+  p.qkv = qkv; p.ld_qkv = ld_qkv; p.q_off = q_off; p.gate_off = gate_off; p.k_off = k_off; p.v_off = v_off;
+  p.positions = positions; p.cache_locs = cache_locs; p.rope = rope; p.rd = rd; p.max_pos = max_pos;
+  p.qn_w = (const __nv_bfloat16*)qn_w; p.kn_w = (const __nv_bfloat16*)kn_w; p.norm_eps = norm_eps;
+  p.norm_plus_one = norm_plus_one;
+  p.k_pool = (__nv_bfloat16*)k_pool; p.v_pool = (__nv_bfloat16*)v_pool; p.n_pages = n_pages;
+  p.block_table = block_table; p.bt_stride = bt_stride; p.rows = rows; p.prefix_lens = prefix_lens;
+  p.out = (__nv_bfloat16*)out; p.part_acc = part_acc; p.part_ml = part_ml;
+  p.E = E; p.Hq = Hq; p.Hkv = Hkv; p.KS = KS; p.n_mt = n_mt; p.n_kw = n_kw; p.scale = scale; p.status = status;
+  p.pdl = pdl;
+  const size_t smem = fused_smem_bytes(D, n_mt, n_kw);
+  void (*kern)(const FusedAttnParams) = nullptr;
+  if (D == 64) kern = attn_fused_kernel<64>;
+  else if (D == 128) kern = attn_fused_kernel<128>;
+  else if (D == 256) kern = attn_fused_kernel<256>;
+  else return -72;
+  CUDA_CHECK_RET(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(bs * Hkv, KS);
+  cfg.blockDim = dim3(32 * n_mt * n_kw);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, kern, p));
+  if (KS > 1) {
+    cfg.gridDim = dim3(bs * E * Hq);
+    cfg.blockDim = dim3(D < 128 ? 64 : 128);
+    cfg.dynamicSmemBytes = 0;
+    CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, attn_fused_merge_kernel, (const float*)part_acc, (const float*)part_ml,
+                                      (__nv_bfloat16*)out, qkv, ld_qkv, gate_off, Hq, KS, D, pdl));
+  }
+  return 0;
+}

@@ -31,7 +31,7 @@ add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, in
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ xn, int ldx, int d, float eps,
                    int plus_one, int pdl) {
   __shared__ float red[32];
-  if (pdl) pdl_wait_prior_grid();
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const int m = blockIdx.x;
   const int nvec = d >> 2;
   float4 v[NORM_MAXV];
@@ -60,7 +60,6 @@ add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, in
   }
   const float tot = block_sum<0>(ss, red);
   const float inv = rsqrtf(tot / (float)d + eps);
-  if (pdl) pdl_launch_dependents();
 #pragma unroll
   for (int i = 0; i < NORM_MAXV; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
@@ -91,7 +90,7 @@ rope_kv_write_kernel(const float* __restrict__ partials, int splits, long long s
                      const float* __restrict__ rope, int rd, int max_pos, __nv_bfloat16* __restrict__ q_out,
                      __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int n_pages, int Hq,
                      int Hkv, int D, int* status, int pdl) {
-  if (pdl) pdl_wait_prior_grid();
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const int m = blockIdx.x;
   const int nq = Hq * D, nk = Hkv * D, ntot = nq + 2 * nk;
   int pos = positions[m];
@@ -141,14 +140,13 @@ rope_kv_write_kernel(const float* __restrict__ partials, int splits, long long s
     for (int s = 0; s < splits; ++s) x += row[(size_t)s * split_stride + nq + nk + idx];
     v_pool[(size_t)loc * nk + idx] = __float2bfloat16(x);
   }
-  if (pdl) pdl_launch_dependents();
 }
 
 // act[m, c] = silu(gate) * up with gate/up interleaved in blocks of `blk` channels.
 __global__ void __launch_bounds__(256)
 swiglu_partials_kernel(const float* __restrict__ partials, int splits, long long split_stride,
                        __nv_bfloat16* __restrict__ act, int M, int ffn, int blk, int ldo, int pdl) {
-  if (pdl) pdl_wait_prior_grid();
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const long long total = (long long)M * ffn;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
@@ -162,7 +160,6 @@ swiglu_partials_kernel(const float* __restrict__ partials, int splits, long long
     }
     act[(size_t)m * ldo + c] = __float2bfloat16(g / (1.f + __expf(-g)) * u);
   }
-  if (pdl) pdl_launch_dependents();
 }
 
 template <typename K, typename... Args>

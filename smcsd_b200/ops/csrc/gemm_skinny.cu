@@ -9,8 +9,13 @@
 // few slabs.  Warp 0 is the TMA producer, warp 1 issues the MMAs, all four warps run the
 // epilogue straight out of tensor memory.
 //
-// Epilogues: fp32 split-K partials (summed by the consumer kernel), bf16 output, and a fused
-// SwiGLU for gate/up matrices whose rows are interleaved in blocks of 64 channels.
+// Split-K reduction happens on chip: the CTAs of one slab form a thread-block cluster along K,
+// park their fp32 tiles in shared memory and sum them in a fixed order through distributed
+// shared memory, so the result is deterministic and no partial sums visit HBM.
+//
+// Epilogues: fp32 store, fp32 accumulate into the residual stream (h += X W^T), fp32 split-K
+// partials in global memory (oracle / fallback), bf16 store, and a fused SwiGLU for gate/up
+// matrices whose rows are interleaved in blocks of 64 channels.
 //
 // Every mbarrier wait is bounded; on a timeout the CTA raises a status bit, drains its
 // outstanding copies, frees its tensor memory and returns.
@@ -18,7 +23,7 @@
 
 namespace smc {
 
-enum { EPI_PARTIAL_F32 = 0, EPI_BF16 = 1, EPI_SWIGLU_BF16 = 2 };
+enum { EPI_PARTIAL_F32 = 0, EPI_BF16 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_F32 = 3, EPI_RESID_F32 = 4 };
 
 struct GemmParams {
   int N, K, M;          // weight rows, reduction length, token rows
@@ -59,6 +64,9 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x, split = blockIdx.y, m_tile = blockIdx.z;
+  // Let the next kernel of the stream start its prologue (and its weight prefetch) right away;
+  // it still waits for this grid to finish before it touches anything this grid writes.
+  if (p.pdl) pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -157,7 +165,6 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
   }
   const int failed = __syncthreads_or(ok ? 0 : 1);
   tc_fence_after();
-  if (p.pdl) pdl_launch_dependents();
 
   if (!failed) {
     const int row_in_tile = warp * 32 + lane;
@@ -193,6 +200,17 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
         }
         __syncthreads();
       }
+    } else if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32) {
+      // park this CTA's tile as sbuf[token][128 weight rows]; the cluster reduces it below
+      float* sbuf = reinterpret_cast<float*>(smem);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(taddr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) sbuf[(c0 + j) * C::BM + row_in_tile] = __uint_as_float(r[j]);
+      }
     } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -221,6 +239,34 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
     const int issued = *sh_issued, consumed = *sh_consumed;
     for (int i = consumed; i < issued; ++i)
       (void)mbar_wait(&full[i % C::STAGES], (uint32_t)(i / C::STAGES) & 1u);
+  }
+
+  if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32) {
+    // ---- on-chip split-K reduction across the cluster (CTA rank == split index) --------------
+    // Both cluster barriers are unconditional so that a CTA that gave up still releases its peers.
+    __shared__ int sh_failed;
+    if (threadIdx.x == 0) sh_failed = failed;
+    cluster_sync();
+    const uint32_t S = (uint32_t)p.splits;
+    bool any_failed = false;
+    for (uint32_t s = 0; s < S; ++s) any_failed |= ld_dsmem_u32(smem_u32(&sh_failed), s) != 0;
+    if (!any_failed) {
+      const float* sbuf = reinterpret_cast<const float*>(smem);
+      const int n = n_tile * C::BM + (int)threadIdx.x;
+      const int m_base = m_tile * BN;
+      float* out = reinterpret_cast<float*>(p.out);
+      // tokens are dealt round-robin to the CTAs of the cluster; ranks are summed in a fixed order
+      for (int c = split; c < BN && m_base + c < p.M; c += (int)S) {
+        const uint32_t a = smem_u32(sbuf + c * C::BM + threadIdx.x);
+        float acc = 0.f;
+        for (uint32_t s = 0; s < S; ++s) acc += ld_dsmem_f32(a, s);
+        if (n < p.N) {
+          float* dst = out + (size_t)(m_base + c) * p.ldo + n;
+          if constexpr (EPI == EPI_RESID_F32) *dst += acc; else *dst = acc;
+        }
+      }
+    }
+    cluster_sync();
   }
 
   tc_fence_before();
@@ -274,11 +320,22 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmPara
   cfg.blockDim = dim3(128);
   cfg.dynamicSmemBytes = C::SMEM_BYTES;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (p.pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = (unsigned)p.splits;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = p.pdl ? 1 : 0;
+  cfg.numAttrs = na;
   CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p));
   return 0;
 }
@@ -323,7 +380,20 @@ SMC_API int smc_gemm_default_splits(int N, int K, int M) {
   return s;
 }
 
+// Cluster size (1, 2, 4 or 8) for the on-chip split-K epilogues.
+SMC_API int smc_gemm_cluster_splits(int N, int K, int M) {
+  const int n_tiles = (N + 127) / 128;
+  const int bn = smc_gemm_bn_for(M);
+  const int m_tiles = (M + bn - 1) / bn;
+  const int kblocks = (K + 63) / 64;
+  int s = 1;
+  while (s < 8 && n_tiles * m_tiles * s * 2 <= 256 && kblocks / (s * 2) >= 2) s *= 2;
+  return s;
+}
+
 // W [N, K] bf16 row-major, X [M, ldx] bf16 row-major (ldx >= K).
+// epi 3: out = fp32 [M, ldo] = X W^T;  epi 4: out (fp32 [M, ldo]) += X W^T.  Both reduce split-K inside a
+// thread-block cluster, so splits must be 1, 2, 4 or 8.
 // epi 0: out = fp32 [splits, M, N] partials; epi 1: out = bf16 [M, ldo] (splits must be 1);
 // epi 2: out = bf16 [M, ldo] holding SwiGLU(gate, up) for N/2 channels (splits must be 1, N % 128 == 0).
 SMC_API int smc_gemm_skinny(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo,
@@ -331,7 +401,9 @@ SMC_API int smc_gemm_skinny(const void* W, const void* X, void* out, int N, int 
   using namespace smc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) != 0 || (ldx % 8) != 0) return -20;       // row pitch must be a multiple of 16 bytes
-  if (epi != EPI_PARTIAL_F32 && splits != 1) return -21;
+  const bool clustered = epi == EPI_STORE_F32 || epi == EPI_RESID_F32;
+  if (!clustered && epi != EPI_PARTIAL_F32 && splits != 1) return -21;
+  if (clustered && !(splits == 1 || splits == 2 || splits == 4 || splits == 8)) return -23;
   if (epi == EPI_SWIGLU_BF16 && (N % 128) != 0) return -22;
   const int bn = smc_gemm_bn_for(M);
   GemmParams p;
@@ -349,6 +421,8 @@ SMC_API int smc_gemm_skinny(const void* W, const void* X, void* out, int N, int 
     case EPI_PARTIAL_F32: return dispatch_bn<EPI_PARTIAL_F32>(bn, tmW, tmX, p, grid, stream);
     case EPI_BF16: return dispatch_bn<EPI_BF16>(bn, tmW, tmX, p, grid, stream);
     case EPI_SWIGLU_BF16: return dispatch_bn<EPI_SWIGLU_BF16>(bn, tmW, tmX, p, grid, stream);
+    case EPI_STORE_F32: return dispatch_bn<EPI_STORE_F32>(bn, tmW, tmX, p, grid, stream);
+    case EPI_RESID_F32: return dispatch_bn<EPI_RESID_F32>(bn, tmW, tmX, p, grid, stream);
   }
   return -11;
 }

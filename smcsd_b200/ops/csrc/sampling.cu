@@ -32,7 +32,7 @@ sample_stage1_kernel(const float* __restrict__ logits, int splits, long long spl
                      float inv_temp, float alpha, const int* __restrict__ tokens_in, uint64_t seed,
                      const long long* __restrict__ cycle_counter, int call_id, float softcap,
                      RowPartial* __restrict__ parts, int pdl) {
-  if (pdl) pdl_wait_prior_grid();
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const int row = blockIdx.x, chunk = blockIdx.y, nchunks = gridDim.y;
   const int per = (((V + nchunks - 1) / nchunks) + 3) & ~3;
   const int c_begin = chunk * per, c_end = min(V, c_begin + per);
@@ -109,7 +109,6 @@ sample_stage1_kernel(const float* __restrict__ logits, int splits, long long spl
     }
     parts[(size_t)row * nchunks + chunk] = a;
   }
-  if (pdl) pdl_launch_dependents();
 }
 
 __global__ void sample_stage2_kernel(const RowPartial* __restrict__ parts, int nchunks, const float* __restrict__ logits,
@@ -117,7 +116,7 @@ __global__ void sample_stage2_kernel(const RowPartial* __restrict__ parts, int n
                                      float alpha, float softcap, const int* __restrict__ tokens_in,
                                      int* __restrict__ tok_out, float* __restrict__ logp_out,
                                      float* __restrict__ logz_out, int rows, int pdl) {
-  if (pdl) pdl_wait_prior_grid();
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row < rows) {
     RowPartial a = parts[(size_t)row * nchunks];
@@ -146,7 +145,6 @@ __global__ void sample_stage2_kernel(const RowPartial* __restrict__ parts, int n
       if (logz_out) logz_out[row] = (alpha != 1.f) ? lse_s - alpha * (a.max_b + __logf(a.sum_b)) : 0.f;
     }
   }
-  if (pdl) pdl_launch_dependents();
 }
 
 }  // namespace smc

@@ -17,7 +17,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libsmcsd_b200.so")
 _lib = None
 
-EPI_PARTIAL_F32, EPI_BF16, EPI_SWIGLU_BF16 = 0, 1, 2
+EPI_PARTIAL_F32, EPI_BF16, EPI_SWIGLU_BF16, EPI_STORE_F32, EPI_RESID_F32 = 0, 1, 2, 3, 4
 ERR_BARRIER_TIMEOUT, ERR_PEER_TIMEOUT, ERR_ALLOC_EXHAUSTED, ERR_BOUNDS = 1, 2, 4, 8
 
 
@@ -45,10 +45,15 @@ def _declare(L) -> None:
     L.smc_gemm_skinny.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, vp, i, vp]
     L.smc_gemm_bn_for.argtypes = [i]
     L.smc_gemm_default_splits.argtypes = [i, i, i]
+    L.smc_gemm_cluster_splits.argtypes = [i, i, i]
+    L.smc_gemm_cluster_splits.restype = C.c_int
     L.smc_add_rmsnorm.argtypes = [vp, vp, i, ll, vp, vp, vp, vp, i, i, i, f, i, i, vp]
     L.smc_rope_kv_write.argtypes = [vp, i, ll, vp, vp, vp, i, i, vp, vp, vp, i, i, i, i, i, vp, i, vp]
     L.smc_swiglu_partials.argtypes = [vp, i, ll, vp, i, i, i, i, i, vp]
     L.smc_attention_extend.argtypes = [vp, vp, vp, vp, i, i, vp, vp, vp, vp, vp, i, i, i, i, i, i, f, vp, i, vp]
+    L.smc_attention_fused.argtypes = [vp, i, i, i, i, i, vp, vp, vp, i, i, vp, vp, f, i, vp, vp, i, vp, i, vp, vp, vp,
+                                      vp, vp, i, i, i, i, i, i, f, vp, i, vp]
+    L.smc_attention_fused.restype = C.c_int
     L.smc_sample_scratch_bytes.argtypes = [i, i]
     L.smc_sample_or_score.argtypes = [vp, i, ll, ll, i, i, f, f, f, vp, ull, vp, i, vp, i, vp, vp, vp, i, vp]
     L.smc_slot_arrays_size.argtypes = []
@@ -88,6 +93,10 @@ def _check(rc: int, what: str) -> None:
 # ----------------------------------------------------------------------------- GEMM
 def gemm_default_splits(N: int, K: int, M: int) -> int:
     return lib().smc_gemm_default_splits(N, K, M)
+
+
+def gemm_cluster_splits(N: int, K: int, M: int) -> int:
+    return lib().smc_gemm_cluster_splits(N, K, M)
 
 
 def gemm_skinny(W: torch.Tensor, X: torch.Tensor, out: torch.Tensor, *, M: int, splits: int = 1,
@@ -135,6 +144,24 @@ def attention_extend(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
                                       k_pool.shape[0] - 1, _p(rows), _p(prefix_lens), _p(part_acc), _p(part_ml),
                                       _p(out), bs, E, Hq, Hkv, D, splits, scale, _p(status), int(pdl), _stream()),
            "smc_attention_extend")
+
+
+def attention_fused(qkv: torch.Tensor, positions: torch.Tensor, cache_locs: torch.Tensor, rope: torch.Tensor,
+                    k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, rows: torch.Tensor,
+                    prefix_lens: torch.Tensor, out: torch.Tensor, part_acc: torch.Tensor, part_ml: torch.Tensor, *,
+                    bs: int, E: int, Hq: int, Hkv: int, D: int, KS: int, scale: float, status: torch.Tensor,
+                    q_off: int = 0, gate_off: int = -1, k_off: Optional[int] = None, v_off: Optional[int] = None,
+                    qn_w: Optional[torch.Tensor] = None, kn_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6,
+                    norm_plus_one: bool = False, pdl: bool = False) -> None:
+    """Norm/rope/KV-write of the new tokens + paged causal attention + split merge, one launch per layer."""
+    k_off = Hq * D if k_off is None else k_off
+    v_off = k_off + Hkv * D if v_off is None else v_off
+    _check(lib().smc_attention_fused(_p(qkv), qkv.stride(0), q_off, gate_off, k_off, v_off, _p(positions),
+                                     _p(cache_locs), _p(rope), rope.shape[1], rope.shape[0], _p(qn_w), _p(kn_w),
+                                     norm_eps, int(norm_plus_one), _p(k_pool), _p(v_pool), k_pool.shape[0] - 1,
+                                     _p(block_table), block_table.stride(0), _p(rows), _p(prefix_lens), _p(out),
+                                     _p(part_acc), _p(part_ml), bs, E, Hq, Hkv, D, KS, scale, _p(status), int(pdl),
+                                     _stream()), "smc_attention_fused" if KS == 1 else "smc_attention_extend")
 
 
 def sample_scratch_bytes(rows: int, nchunks: int) -> int:

@@ -48,36 +48,34 @@ class NativeLlama:
         self.q = torch.empty(max_tokens, self.nq * self.D, dtype=bf16, device=dev)
         self.attn = torch.empty(max_tokens, self.nq * self.D, dtype=bf16, device=dev)
         self.act = torch.empty(max_tokens, self.ffn, dtype=bf16, device=dev)
-        self.max_splits = 32
-        widest = max(self.nqkv, self.d, 2 * self.ffn)
-        self.partials = torch.empty(self.max_splits * max_tokens * widest // 2 + max_tokens * widest, dtype=f32,
-                                    device=dev)
-        self.part_acc = torch.empty(max_tokens * self.nq * attn_splits * self.D, dtype=f32, device=dev)
-        self.part_ml = torch.empty(max_tokens * self.nq * attn_splits * 2, dtype=f32, device=dev)
+        self.qkv = torch.empty(max_tokens, self.nqkv, dtype=f32, device=dev)
+        self.KS = 1 if block_table.shape[1] <= 6144 else (2 if block_table.shape[1] <= 16384 else 4)
+        self.part_acc = torch.empty(max_tokens * self.nq * self.KS * self.D if self.KS > 1 else 1, dtype=f32, device=dev)
+        self.part_ml = torch.empty(max_tokens * self.nq * self.KS * 2 if self.KS > 1 else 1, dtype=f32, device=dev)
         self.logits = torch.empty(max_logit_rows, self.V, dtype=f32, device=dev)
-        self.fuse_swiglu = model.gu_block == 64 and (2 * self.ffn) % 128 == 0 and _env_flag("SMC_FUSE_SWIGLU", True)
+        self.fuse_swiglu = model.gu_block == 64 and (2 * self.ffn) % 128 == 0
+        if not self.fuse_swiglu:
+            self.gu = torch.empty(max_tokens, 2 * self.ffn, dtype=f32, device=dev)
         self._splits_cache: Dict = {}
 
     def _splits(self, N: int, Kdim: int, M: int) -> int:
         key = (N, Kdim, M)
         s = self._splits_cache.get(key)
         if s is None:
-            s = K.gemm_default_splits(N, Kdim, M)
-            while s > 1 and s * M * N > self.partials.numel():
-                s -= 1
-            self._splits_cache[key] = s
+            s = self._splits_cache[key] = K.gemm_cluster_splits(N, Kdim, M)
         return s
 
-    def _gemm_partials(self, W: torch.Tensor, X: torch.Tensor, M: int, ldx: Optional[int] = None):
+    def _gemm(self, W: torch.Tensor, X: torch.Tensor, out: torch.Tensor, M: int, epi: int, ldx: Optional[int] = None):
+        """fp32 store / residual-accumulate GEMM; split-K is reduced on chip inside a CTA cluster."""
         N, Kdim = W.shape
-        s = self._splits(N, Kdim, M)
-        K.gemm_skinny(W, X, self.partials, M=M, splits=s, epi=K.EPI_PARTIAL_F32, ldx=ldx, status=self.status,
-                      pdl=self.pdl)
-        return s, M * N
+        K.gemm_skinny(W, X, out, M=M, splits=self._splits(N, Kdim, M), epi=epi, ldx=ldx, ldo=out.stride(0),
+                      status=self.status, pdl=self.pdl)
 
     def forward(self, ids: torch.Tensor, positions: torch.Tensor, cache_locs: torch.Tensor, rows: torch.Tensor,
                 prefix_lens: torch.Tensor, bs: int, E: int) -> torch.Tensor:
-        """Runs every layer for bs*E tokens; returns the final-norm activations ``xn`` [T, d] (bf16)."""
+        """Runs every layer for bs*E tokens; returns the final-norm activations ``xn`` [T, d] (bf16).
+        Seven launches per layer: QKV GEMM, fused attention step, o-proj GEMM (h +=), RMSNorm,
+        gate/up GEMM with SwiGLU epilogue, down GEMM (h +=), RMSNorm."""
         m, c, pdl = self.m, self.c, self.pdl
         T = bs * E
         assert T <= self.T
@@ -86,32 +84,28 @@ class NativeLlama:
         n_layers = len(m.layers)
         scale = self.D ** -0.5
         for li, L in enumerate(m.layers):
-            s, stride = self._gemm_partials(L.wqkv, self.xn, T)
-            K.rope_kv_write(self.partials, s, stride, positions, cache_locs, m.rope, self.q, self.kv.k[li],
-                            self.kv.v[li], M=T, Hq=self.nq, Hkv=self.nkv, D=self.D, status=self.status, pdl=pdl)
-            K.attention_extend(self.q, self.kv.k[li], self.kv.v[li], self.bt, rows, prefix_lens, self.part_acc,
-                               self.part_ml, self.attn, bs=bs, E=E, Hq=self.nq, Hkv=self.nkv, D=self.D,
-                               splits=self.attn_splits, scale=scale, status=self.status, pdl=pdl)
-            s, stride = self._gemm_partials(L.wo, self.attn, T)
-            K.add_rmsnorm(self.h, L.ln2, self.xn, M=T, d=self.d, eps=c.rms_eps, partials=self.partials, splits=s,
-                          split_stride=stride, pdl=pdl)
+            self._gemm(L.wqkv, self.xn, self.qkv, T, K.EPI_STORE_F32)
+            K.attention_fused(self.qkv, positions, cache_locs, m.rope, self.kv.k[li], self.kv.v[li], self.bt, rows,
+                              prefix_lens, self.attn, self.part_acc, self.part_ml, bs=bs, E=E, Hq=self.nq,
+                              Hkv=self.nkv, D=self.D, KS=self.KS, scale=scale, status=self.status, pdl=pdl)
+            self._gemm(L.wo, self.attn, self.h, T, K.EPI_RESID_F32)
+            K.add_rmsnorm(self.h, L.ln2, self.xn, M=T, d=self.d, eps=c.rms_eps, pdl=pdl)
             if self.fuse_swiglu:
                 K.gemm_skinny(L.wgu, self.xn, self.act, M=T, splits=1, epi=K.EPI_SWIGLU_BF16, ldo=self.act.stride(0),
                               status=self.status, pdl=pdl)
             else:
-                s, stride = self._gemm_partials(L.wgu, self.xn, T)
-                K.swiglu_partials(self.partials, s, stride, self.act, M=T, ffn=self.ffn, blk=m.gu_block, pdl=pdl)
-            s, stride = self._gemm_partials(L.wdown, self.act, T)
+                self._gemm(L.wgu, self.xn, self.gu, T, K.EPI_STORE_F32)
+                K.swiglu_partials(self.gu, 1, 0, self.act, M=T, ffn=self.ffn, blk=m.gu_block, pdl=pdl)
+            self._gemm(L.wdown, self.act, self.h, T, K.EPI_RESID_F32)
             w_next = m.layers[li + 1].ln1 if li + 1 < n_layers else m.final_norm
-            K.add_rmsnorm(self.h, w_next, self.xn, M=T, d=self.d, eps=c.rms_eps, partials=self.partials, splits=s,
-                          split_stride=stride, pdl=pdl)
+            K.add_rmsnorm(self.h, w_next, self.xn, M=T, d=self.d, eps=c.rms_eps, pdl=pdl)
         return self.xn
 
     def lm_head(self, rows: int, row_offset: int = 0, row_step: int = 1) -> torch.Tensor:
         """fp32 logits [rows, V] of xn rows ``row_offset + i * row_step``."""
         X = self.xn[row_offset:]
-        K.gemm_skinny(self.m.lm_head, X, self.logits, M=rows, splits=1, epi=K.EPI_PARTIAL_F32,
-                      ldx=self.d * row_step, status=self.status, pdl=self.pdl)
+        K.gemm_skinny(self.m.lm_head, X, self.logits, M=rows, splits=1, epi=K.EPI_STORE_F32,
+                      ldx=self.d * row_step, ldo=self.logits.stride(0), status=self.status, pdl=self.pdl)
         return self.logits
 
 

@@ -40,6 +40,34 @@ def test_gemm_partials(N, Kd, M, splits):
     assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
 
 
+@pytest.mark.parametrize("N,Kd,M,splits", [
+    (3072, 2048, 8, 8), (2048, 8192, 8, 8), (6144, 4096, 72, 4), (4096, 14336, 72, 4), (2048, 2048, 8, 1),
+    (1024, 512, 40, 2), (128256, 2048, 8, 1), (300, 1024, 9, 4), (2048, 2048, 200, 2), (4096, 4096, 72, 0),
+])
+def test_gemm_cluster_splitk(N, Kd, M, splits):
+    """Split-K reduced on chip through distributed shared memory: plain store and residual accumulate."""
+    K = _K()
+    torch.manual_seed(11)
+    W = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    X = torch.randn(M, Kd, device="cuda").bfloat16()
+    s = splits or K.gemm_cluster_splits(N, Kd, M)
+    ref = X.float() @ W.float().t()
+    st = _status()
+    out = torch.full((M, N), float("nan"), device="cuda")
+    K.gemm_skinny(W, X, out, M=M, splits=s, epi=K.EPI_STORE_F32, ldo=N, status=st)
+    h0 = torch.randn(M, N, device="cuda")
+    h = h0.clone()
+    K.gemm_skinny(W, X, h, M=M, splits=s, epi=K.EPI_RESID_F32, ldo=N, status=st)
+    out2 = torch.full((M, N), float("nan"), device="cuda")
+    K.gemm_skinny(W, X, out2, M=M, splits=s, epi=K.EPI_STORE_F32, ldo=N, status=st, pdl=True)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    tol = 2e-2 * max(1.0, ref.abs().max().item())
+    assert (out - ref).abs().max().item() < tol
+    assert (h - h0 - ref).abs().max().item() < tol
+    assert torch.equal(out, out2), "the cluster reduction must be bit-deterministic"
+
+
 def test_gemm_bf16_and_strided_rows():
     K = _K()
     torch.manual_seed(1)
@@ -308,3 +336,77 @@ def test_state_kernels_match_torch_reference():
         ref.free_group(f"g{gi}")
     nat.alloc.check_conservation()
     assert nat.alloc.available() == nat.alloc.size
+
+
+# ------------------------------------------------------------------------------- fused attention step
+@pytest.mark.parametrize("bs,E,Hq,Hkv,D,ctx,KS,rd,extras", [
+    (8, 9, 32, 8, 128, 1500, 1, 128, False), (8, 1, 32, 8, 64, 700, 1, 64, False), (5, 2, 32, 8, 64, 300, 1, 64, False),
+    (8, 9, 32, 8, 128, 3, 1, 128, False), (3, 9, 4, 4, 64, 200, 1, 64, False), (4, 9, 16, 2, 256, 260, 1, 64, True),
+    (2, 5, 4, 2, 64, 0, 1, 64, False), (4, 9, 32, 8, 128, 2500, 1, 128, False), (4, 9, 32, 8, 128, 2500, 2, 128, False),
+    (3, 1, 8, 2, 128, 900, 4, 128, True), (8, 9, 64, 8, 128, 100, 1, 128, False),
+])
+def test_attention_fused(bs, E, Hq, Hkv, D, ctx, KS, rd, extras):
+    K = _K()
+    from smcsd_b200.models.layers import ExtendBatch, apply_rope, paged_attention_reference, rmsnorm, rope_table
+    torch.manual_seed(9)
+    dev = "cuda"
+    T = bs * E
+    pages = bs * (ctx + E) + 64
+    kp = torch.randn(pages + 1, Hkv * D, device=dev).bfloat16()
+    vp = torch.randn(pages + 1, Hkv * D, device=dev).bfloat16()
+    max_ctx = ctx + E + 8
+    bt = torch.zeros(bs + 2, max_ctx, device=dev, dtype=torch.int32)
+    perm = (torch.randperm(pages, device=dev) + 1).to(torch.int32)
+    prefix = torch.tensor([max(0, ctx - 17 * i) for i in range(bs)], device=dev, dtype=torch.int32)
+    rows = torch.arange(bs, device=dev, dtype=torch.int32) + 1
+    locs = torch.zeros(T, device=dev, dtype=torch.int32)
+    pos = torch.zeros(T, device=dev, dtype=torch.int32)
+    off = 0
+    for b in range(bs):
+        P = int(prefix[b])
+        L = P + E
+        bt[b + 1, :L] = perm[off:off + L]
+        locs[b * E:(b + 1) * E] = perm[off + P:off + L]
+        pos[b * E:(b + 1) * E] = torch.arange(P, L, device=dev)
+        off += L
+    gate = extras
+    nq, nk = Hq * D, Hkv * D
+    ld = nq * (2 if gate else 1) + 2 * nk
+    qkv = torch.randn(T, ld, device=dev)
+    q_off, gate_off = 0, (nq if gate else -1)
+    k_off = nq * (2 if gate else 1)
+    v_off = k_off + nk
+    table = rope_table(rd, 10000.0, None, max_ctx + 8, dev)
+    qn = (torch.randn(D, device=dev) * 0.1).bfloat16() if extras else None
+    kn = (torch.randn(D, device=dev) * 0.1).bfloat16() if extras else None
+    # reference
+    q = qkv[:, :nq].view(T, Hq, D)
+    k = qkv[:, k_off:k_off + nk].view(T, Hkv, D)
+    v = qkv[:, v_off:v_off + nk].view(T, Hkv, D)
+    if extras:
+        q = rmsnorm(q, qn.float(), 1e-6, plus_one=True)
+        k = rmsnorm(k, kn.float(), 1e-6, plus_one=True)
+    qr = apply_rope(q, pos, table).bfloat16()
+    kr = apply_rope(k, pos, table).bfloat16()
+    kp_ref, vp_ref = kp.clone(), vp.clone()
+    kp_ref[locs.long()] = kr.reshape(T, -1)
+    vp_ref[locs.long()] = v.bfloat16().reshape(T, -1)
+    batch = ExtendBatch(None, None, None, rows, prefix, extend_len=E)
+    ref = paged_attention_reference(qr, kp_ref, vp_ref, bt, batch, Hkv).float()
+    if gate:
+        ref = ref * torch.sigmoid(qkv[:, nq:2 * nq].view(T, Hq, D))
+    ref = ref.reshape(T, -1)
+    out = torch.zeros(T, nq, device=dev, dtype=torch.bfloat16)
+    pa = torch.zeros(T * Hq * KS * D, device=dev)
+    pm = torch.zeros(T * Hq * KS * 2, device=dev)
+    st = _status()
+    K.attention_fused(qkv, pos, locs, table, kp, vp, bt, rows, prefix, out, pa, pm, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D,
+                      KS=KS, scale=D ** -0.5, status=st, q_off=q_off, gate_off=gate_off, k_off=k_off, v_off=v_off,
+                      qn_w=qn, kn_w=kn, norm_eps=1e-6, norm_plus_one=True)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    assert torch.equal(kp[locs.long()], kp_ref[locs.long()]) or \
+        (kp[locs.long()].float() - kp_ref[locs.long()].float()).abs().max().item() < 4e-2
+    assert (vp[locs.long()].float() - vp_ref[locs.long()].float()).abs().max().item() < 1e-6
+    err = (out.float() - ref).abs().max().item()
+    assert err < 3e-2 * max(1.0, ref.abs().max().item()), err
