@@ -184,65 +184,87 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   const int prefix = p.prefix_lens[b];
   const size_t kv_row = (size_t)p.Hkv * D;
 
-  // ---- phase 0: q / k / v of the new tokens (norm, rope, bf16), one warp per head row ----------
+  // ---- phase 0: q / k / v of the new tokens (norm, rope, bf16) ------------------------------------
   const int half = p.rd >> 1;
-  for (int item = warp; item < Rpad + 32; item += nwarps) {
-    // items: [0, Rpad) q rows, [Rpad, Rpad+16) k rows, [Rpad+16, Rpad+32) v rows
-    __nv_bfloat16* dst;
-    const float* src = nullptr;
-    const __nv_bfloat16* nw = nullptr;
+  __shared__ int s_pos[16];
+  if (threadIdx.x < 16) {
     int pos = 0;
-    bool rope = false;
+    if ((int)threadIdx.x < p.E) {
+      pos = p.positions[b * p.E + threadIdx.x];
+      if (pos < 0 || pos >= p.max_pos) {
+        atomicOr(p.status, SMC_ERR_BOUNDS);
+        pos = pos < 0 ? 0 : p.max_pos - 1;
+      }
+    }
+    s_pos[threadIdx.x] = pos;
+  }
+  __syncthreads();
+  // rows: [0, Rpad) queries, [Rpad, Rpad+16) keys, [Rpad+16, Rpad+32) values; rows past R / E are zero
+  auto row_info = [&](int item, __nv_bfloat16*& dst, const float*& src, const __nv_bfloat16*& nw, int& pos,
+                      bool& rope) {
+    src = nullptr; nw = nullptr; pos = 0; rope = false;
     if (item < Rpad) {
       dst = Qs + (size_t)item * LD;
       if (item < R) {
-        const int e = item / G, gq = item % G, tkn = b * p.E + e;
-        src = p.qkv + (size_t)tkn * p.ld_qkv + p.q_off + (size_t)(kvh * G + gq) * D;
-        pos = p.positions[tkn]; rope = true; nw = p.qn_w;
+        const int e = item / G, gq = item % G;
+        src = p.qkv + (size_t)(b * p.E + e) * p.ld_qkv + p.q_off + (size_t)(kvh * G + gq) * D;
+        pos = s_pos[e]; rope = true; nw = p.qn_w;
       }
     } else {
       const int e = (item - Rpad) & 15;
       const bool is_k = item < Rpad + 16;
       dst = (is_k ? Kn : Vn) + (size_t)e * LD;
       if (e < p.E) {
-        const int tkn = b * p.E + e;
-        src = p.qkv + (size_t)tkn * p.ld_qkv + (is_k ? p.k_off : p.v_off) + (size_t)kvh * D;
-        pos = p.positions[tkn]; rope = is_k; nw = is_k ? p.kn_w : nullptr;
+        src = p.qkv + (size_t)(b * p.E + e) * p.ld_qkv + (is_k ? p.k_off : p.v_off) + (size_t)kvh * D;
+        pos = s_pos[e]; rope = is_k; nw = is_k ? p.kn_w : nullptr;
       }
     }
-    if (src == nullptr) {
-      for (int i = lane; i < D / 2; i += 32) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
-      continue;
-    }
-    if (pos < 0 || pos >= p.max_pos) {
-      if (lane == 0) atomicOr(p.status, SMC_ERR_BOUNDS);
-      pos = pos < 0 ? 0 : p.max_pos - 1;
-    }
-    float rstd = 1.f;
+  };
+  auto emit_pair = [&](__nv_bfloat16* dst, const float* src, const __nv_bfloat16* nw, float rstd, int pos, bool rope,
+                       int i) {
+    int i1, i2;
+    bool rot;
+    if (i < half) { i1 = i; i2 = i + half; rot = rope; }
+    else { const int j = i - half; i1 = p.rd + 2 * j; i2 = i1 + 1; rot = false; }
+    float x1 = src[i1], x2 = src[i2];
     if (nw != nullptr) {
-      float ss = 0.f;
-      for (int i = lane; i < D; i += 32) ss += src[i] * src[i];
-      rstd = rsqrtf(warp_sum(ss) / (float)D + p.norm_eps);
+      const float add = p.norm_plus_one ? 1.f : 0.f;
+      x1 *= rstd * (__bfloat162float(nw[i1]) + add);
+      x2 *= rstd * (__bfloat162float(nw[i2]) + add);
     }
-    const float* cs = p.rope + (size_t)pos * p.rd;
-    for (int i = lane; i < D / 2; i += 32) {
-      int i1, i2;
-      bool rot;
-      if (i < half) { i1 = i; i2 = i + half; rot = rope; }
-      else { const int j = i - half; i1 = p.rd + 2 * j; i2 = i1 + 1; rot = false; }
-      float x1 = src[i1], x2 = src[i2];
+    if (rot) {
+      const float* cs = p.rope + (size_t)pos * p.rd;
+      const float c = cs[i], sn = cs[half + i];
+      const float y1 = x1 * c - x2 * sn, y2 = x2 * c + x1 * sn;
+      x1 = y1; x2 = y2;
+    }
+    dst[i1] = __float2bfloat16(x1);
+    dst[i2] = __float2bfloat16(x2);
+  };
+  if (p.qn_w == nullptr && p.kn_w == nullptr) {
+    // no per-head norm: every (row, pair) is independent, so spread them over all threads
+    for (int idx = threadIdx.x; idx < (Rpad + 32) * (D / 2); idx += blockDim.x) {
+      const int item = idx / (D / 2), i = idx % (D / 2);
+      __nv_bfloat16* dst; const float* src; const __nv_bfloat16* nw; int pos; bool rope;
+      row_info(item, dst, src, nw, pos, rope);
+      if (src == nullptr) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
+      else emit_pair(dst, src, nullptr, 1.f, pos, rope, i);
+    }
+  } else {
+    for (int item = warp; item < Rpad + 32; item += nwarps) {
+      __nv_bfloat16* dst; const float* src; const __nv_bfloat16* nw; int pos; bool rope;
+      row_info(item, dst, src, nw, pos, rope);
+      if (src == nullptr) {
+        for (int i = lane; i < D / 2; i += 32) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
+        continue;
+      }
+      float rstd = 1.f;
       if (nw != nullptr) {
-        const float add = p.norm_plus_one ? 1.f : 0.f;
-        x1 *= rstd * (__bfloat162float(nw[i1]) + add);
-        x2 *= rstd * (__bfloat162float(nw[i2]) + add);
+        float ss = 0.f;
+        for (int i = lane; i < D; i += 32) ss += src[i] * src[i];
+        rstd = rsqrtf(warp_sum(ss) / (float)D + p.norm_eps);
       }
-      if (rot) {
-        const float c = cs[i], sn = cs[half + i];
-        const float y1 = x1 * c - x2 * sn, y2 = x2 * c + x1 * sn;
-        x1 = y1; x2 = y2;
-      }
-      dst[i1] = __float2bfloat16(x1);
-      dst[i2] = __float2bfloat16(x2);
+      for (int i = lane; i < D / 2; i += 32) emit_pair(dst, src, nw, rstd, pos, rope, i);
     }
   }
   __syncthreads();
