@@ -180,3 +180,70 @@ SMC_API int smc_sample_or_score(const float* logits, int splits, long long split
                                     logz_out, rows, pdl));
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in smc_no_alloc.h).
+// ---------------------------------------------------------------------------------------------------
+#include <stdio.h>
+
+#include "smc_no_alloc.h"
+
+namespace smc {
+constexpr int STATIC_NCHUNKS = 32;
+// Scratch for the per-(row, chunk) partial results.  In host code this name is only a handle for the
+// symbol: the address kernels can use is obtained with cudaGetSymbolAddress below.
+static __device__ __align__(256) RowPartial g_static_sample_scratch[SMC_STATIC_SAMPLE_MAX_ROWS * STATIC_NCHUNKS];
+static RowPartial* g_static_scratch_addr[64] = {nullptr};
+static thread_local char g_no_alloc_error[256] = "";
+}  // namespace smc
+
+SMC_API const char* smc_no_alloc_last_error(void) { return smc::g_no_alloc_error; }
+
+SMC_API int smc_sample_or_score_static(const float* logits, int splits, long long split_stride, long long row_stride,
+                                       int rows, int V, float temperature, float alpha, float softcap,
+                                       const int* tokens_in, unsigned long long seed, const long long* cycle_counter,
+                                       int call_id, int* tok_out, float* logp_out, float* logz_out,
+                                       cudaStream_t stream) {
+  using namespace smc;
+  g_no_alloc_error[0] = '\0';
+  if (rows <= 0) return 0;
+  if (rows > SMC_STATIC_SAMPLE_MAX_ROWS) {
+    snprintf(g_no_alloc_error, sizeof(g_no_alloc_error),
+             "smc_sample_or_score_static: %d rows requested, the built-in scratch holds at most %d", rows,
+             SMC_STATIC_SAMPLE_MAX_ROWS);
+    return SMC_STATIC_ERR_TOO_LARGE;
+  }
+  if ((row_stride & 3) || (split_stride & 3) || temperature <= 0.f || V <= 0 || splits < 1) {
+    snprintf(g_no_alloc_error, sizeof(g_no_alloc_error),
+             "smc_sample_or_score_static: bad argument (strides must be multiples of 4, temperature > 0)");
+    return SMC_STATIC_ERR_ARG;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    snprintf(g_no_alloc_error, sizeof(g_no_alloc_error), "smc_sample_or_score_static: cannot identify the device");
+    return SMC_STATIC_ERR_SETUP;
+  }
+  if (g_static_scratch_addr[dev] == nullptr) {
+    // once per device, with that device current: resolve the device address of the scratch array
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_sample_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      snprintf(g_no_alloc_error, sizeof(g_no_alloc_error),
+               "smc_sample_or_score_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return SMC_STATIC_ERR_SETUP;
+    }
+    g_static_scratch_addr[dev] = static_cast<RowPartial*>(ptr);
+  }
+  RowPartial* scratch = g_static_scratch_addr[dev];
+  const float inv_temp = 1.0f / temperature;
+  sample_stage1_kernel<<<dim3(rows, STATIC_NCHUNKS), S1_THREADS, 0, stream>>>(
+      logits, splits, split_stride, row_stride, V, inv_temp, alpha, tokens_in, (uint64_t)seed, cycle_counter, call_id,
+      softcap, scratch, 0);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  sample_stage2_kernel<<<(rows + 63) / 64, 64, 0, stream>>>(scratch, STATIC_NCHUNKS, logits, splits, split_stride,
+                                                            row_stride, inv_temp, alpha, softcap, tokens_in, tok_out,
+                                                            logp_out, logz_out, rows, 0);
+  return (int)cudaGetLastError();
+}
