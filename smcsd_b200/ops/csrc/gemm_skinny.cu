@@ -255,14 +255,37 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
       const int n = n_tile * C::BM + (int)threadIdx.x;
       const int m_base = m_tile * BN;
       float* out = reinterpret_cast<float*>(p.out);
-      // tokens are dealt round-robin to the CTAs of the cluster; ranks are summed in a fixed order
-      for (int c = split; c < BN && m_base + c < p.M; c += (int)S) {
-        const uint32_t a = smem_u32(sbuf + c * C::BM + threadIdx.x);
-        float acc = 0.f;
-        for (uint32_t s = 0; s < S; ++s) acc += ld_dsmem_f32(a, s);
-        if (n < p.N) {
-          float* dst = out + (size_t)(m_base + c) * p.ldo + n;
-          if constexpr (EPI == EPI_RESID_F32) *dst += acc; else *dst = acc;
+      // tokens are dealt round-robin to the CTAs of the cluster; ranks are summed in a fixed order.
+      // All remote loads of a batch of tokens are issued before the first add, so their
+      // latencies overlap instead of queueing up behind one another.
+      uint32_t rbase[8];
+#pragma unroll
+      for (uint32_t s = 0; s < 8; ++s) rbase[s] = s < S ? dsmem_map(smem_u32(sbuf) + threadIdx.x * 4u, s) : 0u;
+      constexpr int UN = 4;
+      for (int c0 = split; c0 < BN && m_base + c0 < p.M; c0 += (int)S * UN) {
+        float v[UN][8];
+        float prev[UN];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int c = c0 + u * (int)S;
+          const bool live = c < BN && m_base + c < p.M;
+#pragma unroll
+          for (uint32_t s = 0; s < 8; ++s)
+            v[u][s] = (live && s < S) ? ld_dsmem_f32_at(rbase[s] + (uint32_t)c * (C::BM * 4u)) : 0.f;
+          prev[u] = 0.f;
+          if constexpr (EPI == EPI_RESID_F32) {
+            if (live && n < p.N) prev[u] = out[(size_t)(m_base + c) * p.ldo + n];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int c = c0 + u * (int)S;
+          if (c < BN && m_base + c < p.M && n < p.N) {
+            float acc = 0.f;
+#pragma unroll
+            for (uint32_t s = 0; s < 8; ++s) acc += v[u][s];
+            out[(size_t)(m_base + c) * p.ldo + n] = prev[u] + acc;
+          }
         }
       }
     }
