@@ -1,0 +1,270 @@
+"""HTTP serving: ``python -m smcsd_b200.http_server --model ... --draft-model ... -N 8 -g 8``.
+
+Routes: ``/generate`` (native), ``/v1/completions`` and ``/v1/models`` (OpenAI style), ``/health``,
+``/health_generate``, ``/server_info`` (alias ``/get_server_info``), ``/get_model_info``,
+``/flush_cache``.  Concurrent HTTP requests are multiplexed onto the SMC scheduler by a pump thread
+that owns the engine: it feeds new requests into the scheduler between decode cycles and resolves
+each request's future when its group finalizes, so many clients share the batched decode loop.
+Same CLI flags and routes as the reference server (smcsd/http_server.py:140-212; the routes it
+inherits from SGLang are the ones its scripts use, scripts/accuracy_test_gsm8k_http.py:121-223).
+The particle side channel is not sent over HTTP (the reference drops it in this mode too,
+smcsd/core/scheduler.py:987-1001); ``smc_log_Z_hat`` is included in ``meta_info``.
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import logging
+import queue
+import threading
+import time
+import uuid
+from typing import Any, Dict, List, Optional
+
+from .config import EngineArgs
+from .io_types import GenerateRequest, ParticleOutput, RequestOutput, SamplingParams
+
+log = logging.getLogger("smcsd_b200.http")
+
+
+class EngineBridge:
+    """Thread that owns the engine and multiplexes asynchronous requests onto it."""
+
+    def __init__(self, engine):
+        self.engine = engine
+        self.inbox: "queue.Queue" = queue.Queue()
+        self.futures: Dict[str, Any] = {}
+        self.logz: Dict[str, float] = {}
+        self.partial: Dict[str, List[int]] = {}
+        self.loop: Optional[asyncio.AbstractEventLoop] = None
+        self._stop = threading.Event()
+        self.thread = threading.Thread(target=self._pump, name="smc-engine-pump", daemon=True)
+        self.n_served = 0
+        self.last_step_time = time.time()
+
+    def start(self, loop: asyncio.AbstractEventLoop) -> None:
+        self.loop = loop
+        self.thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+        self.thread.join(timeout=10)
+
+    async def submit(self, input_ids: List[int], sp: SamplingParams) -> dict:
+        rid = uuid.uuid4().hex
+        fut = self.loop.create_future()
+        self.futures[rid] = fut
+        req = GenerateRequest(rid, list(input_ids), sp, eos_token_ids=self.engine._eos_ids(), arrival_time=time.time())
+        self.inbox.put(req)
+        return await fut
+
+    def _resolve(self, rid: str, result: dict) -> None:
+        fut = self.futures.pop(rid, None)
+        if fut is not None and not fut.done():
+            fut.set_result(result)
+
+    def _handle(self, o) -> None:
+        if isinstance(o, ParticleOutput):
+            self.logz[o.rid] = o.log_Z_hat
+            return
+        if not isinstance(o, RequestOutput):
+            return
+        acc = self.partial.setdefault(o.rid, [])
+        acc.extend(o.output_ids)
+        if o.finished:
+            ids = self.partial.pop(o.rid)
+            res = dict(output_ids=ids, completion_tokens=len(ids), prompt_tokens=o.prompt_tokens,
+                       finish_reason=o.finish_reason, aborted=o.aborted, error=o.error,
+                       smc_log_Z_hat=self.logz.pop(o.rid, None))
+            self.n_served += 1
+            self.loop.call_soon_threadsafe(self._resolve, o.rid, res)
+
+    def _pump(self) -> None:
+        eng = self.engine
+        sched = eng._sched
+        while not self._stop.is_set():
+            try:
+                if sched is not None:           # scheduler in this process
+                    block = not sched.has_work()
+                    try:
+                        while True:
+                            req = self.inbox.get(timeout=0.02) if block else self.inbox.get_nowait()
+                            sched.add_request(req)
+                            block = False
+                    except queue.Empty:
+                        pass
+                    if sched.has_work() or sched.outbox:
+                        for o in sched.step():
+                            self._handle(o)
+                        self.last_step_time = time.time()
+                else:                           # scheduler processes behind ZMQ
+                    try:
+                        while True:
+                            req = self.inbox.get_nowait()
+                            eng._tx[eng._rr].send_pyobj(req)
+                            eng._rr = (eng._rr + 1) % len(eng._tx)
+                    except queue.Empty:
+                        pass
+                    if eng._rx.poll(20):
+                        self._handle(eng._rx.recv_pyobj())
+                        self.last_step_time = time.time()
+                    else:
+                        eng._check_children()
+            except Exception as e:  # surface the failure to every waiting client
+                log.exception("engine pump failed")
+                for rid in list(self.futures):
+                    self.loop.call_soon_threadsafe(
+                        self._resolve, rid, dict(output_ids=[], completion_tokens=0, prompt_tokens=0,
+                                                 finish_reason={"type": "abort", "message": repr(e)}, aborted=True,
+                                                 error=repr(e), smc_log_Z_hat=None))
+                time.sleep(0.1)
+
+
+def build_app(engine, model_name: str = "smc"):
+    from fastapi import FastAPI, HTTPException
+    from fastapi.responses import JSONResponse
+
+    app = FastAPI(title="smcsd_b200")
+    bridge = EngineBridge(engine)
+    app.state.bridge = bridge
+
+    @app.on_event("startup")
+    async def _startup():
+        bridge.start(asyncio.get_running_loop())
+
+    @app.on_event("shutdown")
+    async def _shutdown():
+        bridge.stop()
+
+    def _encode(text_or_ids) -> List[int]:
+        if isinstance(text_or_ids, str):
+            if engine.tokenizer is None:
+                raise HTTPException(400, "this server has no tokenizer; send input_ids")
+            return engine.tokenizer.encode(text_or_ids)
+        return list(text_or_ids)
+
+    def _decode(ids: List[int]) -> str:
+        return engine.tokenizer.decode(ids, skip_special_tokens=True) if engine.tokenizer is not None else ""
+
+    async def _one(ids: List[int], params: Optional[dict]) -> dict:
+        try:
+            sp = SamplingParams.from_dict(params).normalize()
+        except (TypeError, ValueError) as e:
+            raise HTTPException(400, str(e))
+        r = await bridge.submit(ids, sp)
+        if r["aborted"]:
+            raise HTTPException(400, r["error"] or "request aborted")
+        return {"text": _decode(r["output_ids"]), "output_ids": r["output_ids"],
+                "meta_info": {"id": uuid.uuid4().hex, "prompt_tokens": len(ids),
+                              "completion_tokens": r["completion_tokens"], "finish_reason": r["finish_reason"],
+                              "smc_log_Z_hat": r["smc_log_Z_hat"]}}
+
+    @app.post("/generate")
+    async def generate(body: Dict[str, Any]):
+        text, ids = body.get("text"), body.get("input_ids")
+        if (text is None) == (ids is None):
+            raise HTTPException(400, "send exactly one of text / input_ids")
+        params = body.get("sampling_params") or {}
+        src = text if text is not None else ids
+        many = isinstance(src, list) and len(src) > 0 and isinstance(src[0], (list, str))
+        items = src if many else [src]
+        plist = params if isinstance(params, list) else [params] * len(items)
+        outs = await asyncio.gather(*[_one(_encode(x), p) for x, p in zip(items, plist)])
+        return outs if many else outs[0]
+
+    @app.post("/v1/completions")
+    async def completions(body: Dict[str, Any]):
+        prompt = body.get("prompt")
+        if prompt is None:
+            raise HTTPException(400, "prompt is required")
+        prompts = prompt if isinstance(prompt, list) and prompt and isinstance(prompt[0], (str, list)) else [prompt]
+        params = {"max_new_tokens": int(body.get("max_tokens", 16)), "temperature": body.get("temperature", 1.0),
+                  "ignore_eos": bool(body.get("ignore_eos", False))}
+        if body.get("stop"):
+            params["stop"] = body["stop"]
+        if body.get("stop_token_ids"):
+            params["stop_token_ids"] = body["stop_token_ids"]
+        outs = await asyncio.gather(*[_one(_encode(p), params) for p in prompts])
+        choices = [{"index": i, "text": o["text"], "token_ids": o["output_ids"],
+                    "finish_reason": "length" if o["meta_info"]["finish_reason"]["type"] == "length" else "stop"}
+                   for i, o in enumerate(outs)]
+        pt = sum(o["meta_info"]["prompt_tokens"] for o in outs)
+        ct = sum(o["meta_info"]["completion_tokens"] for o in outs)
+        return {"id": "cmpl-" + uuid.uuid4().hex, "object": "text_completion", "created": int(time.time()),
+                "model": body.get("model", model_name), "choices": choices,
+                "usage": {"prompt_tokens": pt, "completion_tokens": ct, "total_tokens": pt + ct}}
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "smcsd_b200"}]}
+
+    @app.get("/health")
+    async def health():
+        return JSONResponse({"status": "ok"})
+
+    @app.get("/health_generate")
+    async def health_generate():
+        vocab_ok = [1, 2, 3, 4]
+        await _one(vocab_ok, {"max_new_tokens": 2, "ignore_eos": True})
+        return JSONResponse({"status": "ok"})
+
+    def _info() -> dict:
+        info = dict(engine.scheduler_info[0]) if engine.scheduler_info else {}
+        if engine._sched is not None:
+            info = engine._sched.server_info()
+        info["n_served"] = bridge.n_served
+        info["smc"] = {"n_particles": engine.args.n_particles, "gamma": engine.args.gamma,
+                       "draft_temperature": engine.args.draft_temperature,
+                       "target_temperature": engine.args.target_temperature,
+                       "resample_threshold": engine.args.resample_threshold}
+        return info
+
+    @app.get("/server_info")
+    async def server_info():
+        return _info()
+
+    @app.get("/get_server_info")
+    async def get_server_info():
+        return _info()
+
+    @app.get("/get_model_info")
+    async def model_info():
+        return {"model_path": str(engine.args.model_path), "draft_model_path": str(engine.args.draft_model_path),
+                "is_generation": True}
+
+    @app.post("/flush_cache")
+    async def flush_cache():
+        ok = engine._sched.flush_cache() if engine._sched is not None else True
+        return JSONResponse({"flushed": bool(ok)}, status_code=200 if ok else 400)
+
+    return app
+
+
+def build_engine_from_args(ns: argparse.Namespace):
+    from .engine import SMCEngine
+    a = EngineArgs.from_cli_args(ns)
+    kw = a.to_dict()
+    model, draft = a.model_path, a.draft_model_path
+    for k in ("model_path", "draft_model_path", "extra"):
+        kw.pop(k, None)
+    return SMCEngine(model, draft, **kw)
+
+
+def launch_server(ns: argparse.Namespace) -> None:
+    import uvicorn
+    engine = build_engine_from_args(ns)
+    app = build_app(engine, model_name=str(ns.model_path))
+    uvicorn.run(app, host=ns.host, port=ns.port, log_level=ns.log_level if ns.log_level != "error" else "warning")
+
+
+def main(argv=None) -> None:
+    p = argparse.ArgumentParser("smcsd_b200.http_server")
+    EngineArgs.add_cli_args(p)
+    p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--port", type=int, default=30000)
+    ns = p.parse_args(argv)
+    launch_server(ns)
+
+
+if __name__ == "__main__":
+    main()

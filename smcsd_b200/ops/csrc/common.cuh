@@ -143,6 +143,25 @@ __device__ __forceinline__ uint32_t ld_dsmem_u32(uint32_t local_addr, uint32_t r
   return v;
 }
 
+// ---------------------------------------------------------------- cross-GPU counters (system scope)
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait until a counter written by other GPUs reaches `want`.  Returns false on timeout.
+__device__ __forceinline__ bool wait_counter_sys(const unsigned long long* p, unsigned long long want) {
+  if (ld_acquire_sys_u64(p) >= want) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (ld_acquire_sys_u64(p) >= want) return true;
+    if (clock64() - t0 > SMC_SPIN_CYCLES) return false;
+  }
+}
+// order generic-proxy visibility before subsequent async-proxy (TMA) reads
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // ---------------------------------------------------------------- programmatic dependent launch
 __device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

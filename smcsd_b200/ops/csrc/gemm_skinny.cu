@@ -19,11 +19,29 @@
 //
 // Every mbarrier wait is bounded; on a timeout the CTA raises a status bit, drains its
 // outstanding copies, frees its tensor memory and returns.
+#include <string.h>
+
 #include "common.cuh"
 
 namespace smc {
 
-enum { EPI_PARTIAL_F32 = 0, EPI_BF16 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_F32 = 3, EPI_RESID_F32 = 4 };
+enum { EPI_PARTIAL_F32 = 0, EPI_BF16 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_F32 = 3, EPI_RESID_F32 = 4, EPI_RS_F32 = 5 };
+
+// Tensor-parallel links of one GEMM.  Consumer side (all-gather -> GEMM): peers store their
+// activation rows into this GPU's buffer and bump a counter here; the TMA producer waits for the
+// counter before it fetches activations from local memory.  Producer side (GEMM -> reduce-scatter):
+// the epilogue stores each reduced token row straight into the owning rank's receive buffer over
+// NVLink (plain peer stores) and bumps that rank's counter.  Counters only grow; the value to wait
+// for is derived from a device-resident epoch so captured graphs work unchanged on every replay.
+struct TpLink {
+  const unsigned long long* ag_flag;   // null: no all-gather wait
+  const long long* epoch;              // device epoch, first use has epoch 1
+  long long ag_uses, ag_idx, ag_inc;   // wait for ((epoch-1)*uses + idx + 1) * inc
+  unsigned long long peer_base[8];     // symmetric-heap base address on every rank
+  long long rs_off, rs_flag_off;       // byte offsets of the receive buffer / its counter in the heap
+  int tp, rank, rows_per_rank, pad;
+  int* arrive;                         // local arrival counter of this call site (self-resetting)
+};
 
 struct GemmParams {
   int N, K, M;          // weight rows, reduction length, token rows
@@ -33,6 +51,7 @@ struct GemmParams {
   int ldo;
   int* status;
   int pdl;              // 1: wait for the previous grid only before touching activations
+  TpLink tp;
 };
 
 template <int BN>
@@ -107,6 +126,16 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
         tma_load_2d(smem + i * C::STAGE_BYTES, &tmW, &full[i], (kb_begin + i) * C::BK, n_tile * C::BM, pol_w);
       }
       if (p.pdl) pdl_wait_prior_grid();
+      if (p.tp.ag_flag != nullptr) {
+        // activations are being pushed by the peers: wait (bounded) for all of their rows
+        const unsigned long long want =
+            (unsigned long long)(((*p.tp.epoch - 1) * p.tp.ag_uses + p.tp.ag_idx + 1) * p.tp.ag_inc);
+        if (!wait_counter_sys(p.tp.ag_flag, want)) {
+          atomicOr(p.status, SMC_ERR_PEER_TIMEOUT);
+          *sh_abort = 1;
+        }
+        fence_proxy_async_all();
+      }
       for (int i = 0; i < pre; ++i)
         tma_load_2d(smem + i * C::STAGE_BYTES + C::A_BYTES, &tmX, &full[i], (kb_begin + i) * C::BK, m_tile * BN,
                     pol_x);
@@ -200,7 +229,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
         }
         __syncthreads();
       }
-    } else if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32) {
+    } else if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32 || EPI == EPI_RS_F32) {
       // park this CTA's tile as sbuf[token][128 weight rows]; the cluster reduces it below
       float* sbuf = reinterpret_cast<float*>(smem);
 #pragma unroll 1
@@ -241,7 +270,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
       (void)mbar_wait(&full[i % C::STAGES], (uint32_t)(i / C::STAGES) & 1u);
   }
 
-  if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32) {
+  if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32 || EPI == EPI_RS_F32) {
     // ---- on-chip split-K reduction across the cluster (CTA rank == split index) --------------
     // Both cluster barriers are unconditional so that a CTA that gave up still releases its peers.
     __shared__ int sh_failed;
@@ -284,8 +313,32 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
             float acc = 0.f;
 #pragma unroll
             for (uint32_t s = 0; s < 8; ++s) acc += v[u][s];
-            out[(size_t)(m_base + c) * p.ldo + n] = prev[u] + acc;
+            if constexpr (EPI == EPI_RS_F32) {
+              // reduce-scatter: the token row belongs to rank `owner`; store into its receive buffer
+              const int m = m_base + c, owner = m / p.tp.rows_per_rank, ml = m - owner * p.tp.rows_per_rank;
+              float* dst = reinterpret_cast<float*>(p.tp.peer_base[owner] + p.tp.rs_off) +
+                           ((size_t)p.tp.rank * p.tp.rows_per_rank + ml) * p.ldo + n;
+              *dst = acc;
+            } else {
+              out[(size_t)(m_base + c) * p.ldo + n] = prev[u] + acc;
+            }
           }
+        }
+      }
+    }
+    if constexpr (EPI == EPI_RS_F32) {
+      // publish: every CTA makes its peer stores visible system-wide and checks in; the last CTA of
+      // the grid bumps every rank's counter once, so the counters advance by `tp` per GEMM whatever
+      // the batch size is
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        const int total = (int)(gridDim.x * gridDim.y * gridDim.z);
+        if (atomicAdd(p.tp.arrive, 1) == total - 1) {
+          *p.tp.arrive = 0;
+          __threadfence_system();
+          for (int o = 0; o < p.tp.tp; ++o)
+            atomicAdd_system(reinterpret_cast<unsigned long long*>(p.tp.peer_base[o] + p.tp.rs_flag_off), 1ull);
         }
       }
     }
@@ -350,7 +403,7 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmPara
     attr[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
   }
-  if (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32) {
+  if (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32 || EPI == EPI_RS_F32) {
     attr[na].id = cudaLaunchAttributeClusterDimension;
     attr[na].val.clusterDim.x = 1;
     attr[na].val.clusterDim.y = (unsigned)p.splits;
@@ -419,21 +472,23 @@ SMC_API int smc_gemm_cluster_splits(int N, int K, int M) {
 // thread-block cluster, so splits must be 1, 2, 4 or 8.
 // epi 0: out = fp32 [splits, M, N] partials; epi 1: out = bf16 [M, ldo] (splits must be 1);
 // epi 2: out = bf16 [M, ldo] holding SwiGLU(gate, up) for N/2 channels (splits must be 1, N % 128 == 0).
-SMC_API int smc_gemm_skinny(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo,
-                            int splits, int epi, int* status, int pdl, cudaStream_t stream) {
+static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo, int splits,
+                      int epi, int* status, int pdl, const smc::TpLink* tp, cudaStream_t stream) {
   using namespace smc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) != 0 || (ldx % 8) != 0) return -20;       // row pitch must be a multiple of 16 bytes
-  const bool clustered = epi == EPI_STORE_F32 || epi == EPI_RESID_F32;
+  const bool clustered = epi == EPI_STORE_F32 || epi == EPI_RESID_F32 || epi == EPI_RS_F32;
   if (!clustered && epi != EPI_PARTIAL_F32 && splits != 1) return -21;
   if (clustered && !(splits == 1 || splits == 2 || splits == 4 || splits == 8)) return -23;
   if (epi == EPI_SWIGLU_BF16 && (N % 128) != 0) return -22;
+  if (epi == EPI_RS_F32 && (tp == nullptr || tp->tp < 1 || tp->tp > 8 || tp->rows_per_rank < 1)) return -24;
   const int bn = smc_gemm_bn_for(M);
   GemmParams p;
   p.N = N; p.K = K; p.M = M;
   p.kblocks = (K + 63) / 64;
   p.splits = splits < 1 ? 1 : (splits > p.kblocks ? p.kblocks : splits);
   p.out = out; p.ldo = ldo; p.status = status; p.pdl = pdl;
+  if (tp != nullptr) p.tp = *tp; else memset(&p.tp, 0, sizeof(p.tp));
   CUtensorMap tmW, tmX;
   int rc = make_tmap(&tmW, W, N, K, K, 128);
   if (rc) return rc;
@@ -446,6 +501,23 @@ SMC_API int smc_gemm_skinny(const void* W, const void* X, void* out, int N, int 
     case EPI_SWIGLU_BF16: return dispatch_bn<EPI_SWIGLU_BF16>(bn, tmW, tmX, p, grid, stream);
     case EPI_STORE_F32: return dispatch_bn<EPI_STORE_F32>(bn, tmW, tmX, p, grid, stream);
     case EPI_RESID_F32: return dispatch_bn<EPI_RESID_F32>(bn, tmW, tmX, p, grid, stream);
+    case EPI_RS_F32: return dispatch_bn<EPI_RS_F32>(bn, tmW, tmX, p, grid, stream);
   }
   return -11;
 }
+
+SMC_API int smc_gemm_skinny(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo,
+                            int splits, int epi, int* status, int pdl, cudaStream_t stream) {
+  return gemm_entry(W, X, out, N, K, M, ldx, ldo, splits, epi, status, pdl, nullptr, stream);
+}
+
+// Tensor-parallel variant: `tp` describes the all-gather wait of the activation operand and / or the
+// reduce-scatter target of the output (epi 5: reduced token rows are stored into the owning rank's
+// receive buffer [src_rank, rows_per_rank, ldo] fp32 and that rank's counter is bumped).
+SMC_API int smc_gemm_skinny_tp(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo,
+                               int splits, int epi, int* status, int pdl, const smc::TpLink* tp,
+                               cudaStream_t stream) {
+  return gemm_entry(W, X, out, N, K, M, ldx, ldo, splits, epi, status, pdl, tp, stream);
+}
+
+SMC_API int smc_tp_link_size() { return (int)sizeof(smc::TpLink); }

@@ -250,3 +250,81 @@ def state_copy(state_tensor: torch.Tensor, n_layers: int, n_rows: int, counters,
     _check(lib().smc_state_copy(_p(state_tensor), state_tensor.stride(0) * state_tensor.element_size(), row_bytes,
                                 n_layers, n_rows, _p(counters), _p(job_dst), _p(job_src), max_jobs, _stream()),
            "smc_state_copy")
+
+
+# ----------------------------------------------------------------------------- tensor-parallel links
+EPI_RS_F32 = 5
+
+
+class TpLink(C.Structure):
+    _fields_ = [("ag_flag", C.c_void_p), ("epoch", C.c_void_p), ("ag_uses", C.c_longlong), ("ag_idx", C.c_longlong),
+                ("ag_inc", C.c_longlong), ("peer_base", C.c_ulonglong * 8), ("rs_off", C.c_longlong),
+                ("rs_flag_off", C.c_longlong), ("tp", C.c_int), ("rank", C.c_int), ("rows_per_rank", C.c_int),
+                ("pad", C.c_int), ("arrive", C.c_void_p)]
+
+
+class TpPeers(C.Structure):
+    _fields_ = [("base", C.c_ulonglong * 8), ("tp", C.c_int), ("rank", C.c_int)]
+
+
+def _declare_tp(L) -> None:
+    if getattr(L, "_tp_declared", False):
+        return
+    vp, i, ll, f, ull = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_ulonglong
+    L.smc_gemm_skinny_tp.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, vp, i, vp, vp]
+    L.smc_tp_norm_allgather.argtypes = [vp, vp, vp, vp, ll, ll, ll, vp, vp, vp, vp, ll, ll, i, i, i, f, i, vp, vp, i, vp]
+    L.smc_tp_sample_or_score.argtypes = [vp, vp, ll, i, i, i, i, f, f, f, vp, ull, vp, i, ll, vp, ll, vp, ll, ll, vp, i,
+                                         vp, vp, vp, vp, vp, i, i, vp]
+    L.smc_tp_bump_counter.argtypes = [vp, ull, vp]
+    L.smc_tp_wait_counter.argtypes = [vp, ull, vp, vp, vp]
+    for n in ("smc_gemm_skinny_tp", "smc_tp_norm_allgather", "smc_tp_sample_or_score", "smc_tp_bump_counter",
+              "smc_tp_wait_counter", "smc_tp_link_size", "smc_tp_peers_size", "smc_tp_partial_bytes"):
+        getattr(L, n).restype = C.c_int
+    assert C.sizeof(TpLink) == L.smc_tp_link_size(), "TpLink layout mismatch"
+    assert C.sizeof(TpPeers) == L.smc_tp_peers_size(), "TpPeers layout mismatch"
+    L._tp_declared = True
+
+
+def tp_lib():
+    L = lib()
+    _declare_tp(L)
+    return L
+
+
+def gemm_skinny_tp(W: torch.Tensor, X: torch.Tensor, out: Optional[torch.Tensor], *, M: int, splits: int, epi: int,
+                   link: TpLink, ldx: Optional[int] = None, ldo: int, status: torch.Tensor, pdl: bool = False) -> None:
+    N, K = W.shape
+    ldx = ldx if ldx is not None else X.stride(0)
+    _check(tp_lib().smc_gemm_skinny_tp(_p(W), _p(X), _p(out), N, K, M, ldx, ldo, splits, epi, _p(status), int(pdl),
+                                       C.byref(link), _stream()), "smc_gemm_skinny_tp")
+
+
+def tp_norm_allgather(peers: TpPeers, h_local, rs_buf, rs_flag_ptr: int, rs_uses: int, rs_idx: int, rs_inc: int,
+                      epoch, ids, embed, w, xn_off: int, ag_flag_off: int, rows_per_rank: int, my_rows: int, d: int,
+                      eps: float, plus_one: bool, arrive, status, pdl: bool = False) -> None:
+    _check(tp_lib().smc_tp_norm_allgather(C.byref(peers), _p(h_local), _p(rs_buf), C.c_void_p(rs_flag_ptr), rs_uses,
+                                          rs_idx, rs_inc, _p(epoch), _p(ids), _p(embed), _p(w), xn_off, ag_flag_off,
+                                          rows_per_rank, my_rows, d, eps, int(plus_one), _p(arrive), _p(status), int(pdl),
+                                          _stream()), "smc_tp_norm_allgather")
+
+
+def tp_sample_or_score(peers: TpPeers, logits, *, rows: int, Vshard: int, v0: int, Vtotal: int, temperature: float,
+                       alpha: float, softcap: float, tokens_in, seed: int, cycle_counter, call_id: int,
+                       gather_off: int, gather_local_ptr: int, flag_off: int, flag_local_ptr: int, uses: int, idx: int,
+                       epoch, nchunks: int, tok_out, logp_out, logz_out, arrive, status, pdl: bool = False,
+                       phase: int = 0) -> None:
+    _check(tp_lib().smc_tp_sample_or_score(C.byref(peers), _p(logits), logits.stride(0), rows, Vshard, v0, Vtotal,
+                                           temperature, alpha, softcap, _p(tokens_in), seed & 0xFFFFFFFFFFFFFFFF,
+                                           _p(cycle_counter), call_id, gather_off, C.c_void_p(gather_local_ptr),
+                                           flag_off, C.c_void_p(flag_local_ptr), uses, idx, _p(epoch), nchunks,
+                                           _p(tok_out), _p(logp_out), _p(logz_out), _p(arrive), _p(status), int(pdl), phase,
+                                           _stream()), "smc_sample_or_score" if phase == 0 else "smc_tp_sample_phase")
+
+
+def tp_bump_counter(flag_ptr: int, by: int) -> None:
+    _check(tp_lib().smc_tp_bump_counter(C.c_void_p(flag_ptr), by, _stream()), "smc_tp_bump_counter")
+
+
+def tp_wait_counter(flag_ptr: int, want: int, outcome: torch.Tensor, status: torch.Tensor) -> None:
+    _check(tp_lib().smc_tp_wait_counter(C.c_void_p(flag_ptr), want, _p(outcome), _p(status), _stream()),
+           "smc_tp_wait_counter")

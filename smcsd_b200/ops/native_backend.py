@@ -198,10 +198,12 @@ class NativeState:
 class NativeRunner:
     """Drives the kernel-chain forwards for one scheduler; owns the captured cycle graphs."""
 
-    def __init__(self, sched, nstate: NativeState):
+    def __init__(self, sched, nstate: NativeState, comm=None):
         a = sched.args
         self.args = a
         self.ns = nstate
+        self.comm = comm
+        self.heap = None
         self.device = sched.device
         self.gamma, self.G = a.gamma, a.gamma + 1
         self.max_bs = sched.max_groups * a.n_particles
@@ -228,6 +230,18 @@ class NativeRunner:
         if model.cfg.arch != "llama":
             from .native_hybrid import NativeHybrid
             return NativeHybrid(model, kv, bt, max_tokens, max_logit_rows, splits, self.status, pdl, runner=self)
+        if model.tp_size > 1:
+            # tensor-parallel target: peers are reached through the symmetric heap, never through NCCL
+            from ..parallel.symm import SymmHeap
+            from .native_tp import NativeLlamaTP
+            if self.comm is None:
+                raise RuntimeError("a tensor-parallel model needs a process group (launch one rank per GPU)")
+            if self.heap is None:
+                need = 4 * max_tokens * model.cfg.hidden_size * 8 + max_tokens * 32 * 32 * model.tp_size + (8 << 20)
+                self.heap = SymmHeap(need, self.device, self.comm.device_group, self.comm.group_rank,
+                                     self.comm.group_size)
+            model.tp_group = self.comm.device_group      # the PyTorch prefill path all-reduces through NCCL
+            return NativeLlamaTP(model, kv, bt, max_tokens, max_logit_rows, splits, self.status, pdl, self.heap)
         return NativeLlama(model, kv, bt, max_tokens, max_logit_rows, splits, self.status, pdl)
 
     # ---- prefill: plain PyTorch forward on the GPU (one pass per request) ----------
@@ -241,6 +255,11 @@ class NativeRunner:
     # ---- the cycle, as a sequence of kernel launches ---------------------------------
     def _sample(self, nm, rows: int, call_id: int, temperature: float, alpha: float, tokens_in, tok_out, logp_out,
                 logz_out) -> None:
+        if hasattr(nm, "tp_sample"):
+            nm.tp_sample(rows=rows, temperature=temperature, alpha=alpha, tokens_in=tokens_in, seed=self.seed,
+                         cycle_counter=self._counters, call_id=call_id, tok_out=tok_out, logp_out=logp_out,
+                         logz_out=logz_out)
+            return
         K.sample_or_score(nm.logits, rows=rows, V=nm.c.vocab_size if nm.m.tp_size == 1 else nm.V, splits=1,
                           split_stride=0, row_stride=nm.logits.stride(0), temperature=temperature, alpha=alpha,
                           softcap=float(nm.c.logit_softcap), tokens_in=tokens_in, seed=self.seed,
@@ -360,5 +379,5 @@ def create(sched, comm=None):
         raise RuntimeError("the native backend needs a CUDA device")
     K.lib()     # fail loudly if the kernel library is missing
     ns = NativeState(sched.max_groups * sched.args.n_particles, sched.args.gamma, sched.device)
-    runner = NativeRunner(sched, ns)
+    runner = NativeRunner(sched, ns, comm)
     return ns, runner

@@ -1,0 +1,80 @@
+"""HTTP server on the CPU path: real uvicorn server in a thread, queried with ``requests``."""
+import socket
+import threading
+import time
+
+import pytest
+import requests
+import torch
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.fixture(scope="module")
+def server():
+    import uvicorn
+
+    from smcsd_b200 import SMCEngine
+    from smcsd_b200.http_server import build_app
+    eng = SMCEngine("preset:tiny-target", "preset:tiny-draft", n_particles=4, gamma=4, dtype="float32", device="cpu",
+                    max_running_requests=4, draft_temperature=0.7, target_temperature=0.7)
+    app = build_app(eng, "tiny")
+    port = _free_port()
+    cfg = uvicorn.Config(app, host="127.0.0.1", port=port, log_level="warning")
+    srv = uvicorn.Server(cfg)
+    t = threading.Thread(target=srv.run, daemon=True)
+    t.start()
+    base = f"http://127.0.0.1:{port}"
+    for _ in range(100):
+        try:
+            if requests.get(base + "/health", timeout=1).status_code == 200:
+                break
+        except Exception:
+            time.sleep(0.1)
+    yield base
+    srv.should_exit = True
+    t.join(timeout=10)
+
+
+def test_generate_and_info(server):
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 4096, (20,), generator=g).tolist()
+    r = requests.post(server + "/generate", json={"input_ids": ids, "sampling_params": {"max_new_tokens": 12, "ignore_eos": True}}, timeout=120)
+    assert r.status_code == 200
+    j = r.json()
+    assert j["meta_info"]["completion_tokens"] == 12 and len(j["output_ids"]) == 12
+    assert j["meta_info"]["finish_reason"]["type"] == "length"
+    info = requests.get(server + "/server_info", timeout=10).json()
+    assert info["smc"]["n_particles"] == 4 and info["n_served"] >= 1
+    assert requests.get(server + "/get_model_info", timeout=10).status_code == 200
+    assert requests.post(server + "/flush_cache", timeout=10).status_code == 200
+
+
+def test_concurrent_requests_and_batch(server):
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 4096, (10 + i,), generator=g).tolist() for i in range(6)]
+    results = [None] * 6
+
+    def call(i):
+        results[i] = requests.post(server + "/generate", json={"input_ids": prompts[i], "sampling_params": {"max_new_tokens": 9 + i, "ignore_eos": True}}, timeout=300).json()
+    ts = [threading.Thread(target=call, args=(i,)) for i in range(6)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    for i, r in enumerate(results):
+        assert r["meta_info"]["completion_tokens"] == 9 + i
+    r = requests.post(server + "/generate", json={"input_ids": prompts[:2], "sampling_params": {"max_new_tokens": 5, "ignore_eos": True}}, timeout=120).json()
+    assert isinstance(r, list) and len(r) == 2
+
+
+def test_openai_completions_and_errors(server):
+    r = requests.post(server + "/v1/completions", json={"prompt": [5, 6, 7, 8], "max_tokens": 7, "ignore_eos": True}, timeout=120)
+    j = r.json()
+    assert j["object"] == "text_completion" and j["usage"]["completion_tokens"] == 7
+    assert requests.get(server + "/v1/models", timeout=10).json()["data"][0]["id"] == "tiny"
+    bad = requests.post(server + "/generate", json={"input_ids": [1, 2], "sampling_params": {"max_new_tokens": 4, "stop": ["x"]}}, timeout=60)
+    assert bad.status_code == 400
+    assert requests.post(server + "/generate", json={}, timeout=10).status_code == 400
