@@ -82,6 +82,12 @@ class SMCScheduler:
         d_tp = (0, 1) if a.replicate_draft else (tp_rank, tp_size)
         self.draft = draft if draft is not None else build_model(
             a.draft_model_path, self.dtype, self.device, d_tp[0], d_tp[1], seed=seed + 1)
+        self.comm = comm
+        if comm is not None and tp_size > 1:
+            # the PyTorch path (prefill, CPU ranks, cuBLAS baseline) reduces through torch.distributed
+            self.target.tp_group = comm.device_group
+            if not a.replicate_draft:
+                self.draft.tp_group = comm.device_group
         if self.target.cfg.vocab_size != self.draft.cfg.vocab_size:
             raise ValueError("target and draft must share a vocabulary")
         self.context_len = int(a.context_length or min(self.target.cfg.max_position, 16384))
