@@ -148,7 +148,7 @@ class LlamaModel:
         dev, dt = self.device, self.dtype
 
         def get(name):
-            return ck.get(name).to(device=dev, dtype=dt)
+            return ck.get(name).to(device=dev, dtype=dt, copy=True)   # never alias the mmap
 
         self.embed = get(f"{pre}embed_tokens.weight")
         self.final_norm = get(f"{pre}norm.weight")

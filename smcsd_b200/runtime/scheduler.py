@@ -100,7 +100,7 @@ class SMCScheduler:
         kv_d = KVSpec(len(self.draft.cfg.attn_layers), self.draft.n_kv_heads, self.draft.cfg.head_dim, self.dtype)
         n_rows = n_slots + n_parent_rows
         spec_t, spec_d = self.target.state_spec(), self.draft.state_spec()
-        state_bytes = sum(s.row_bytes * n_rows * (1 + (G if i == 0 else 2)) for i, s in enumerate((spec_t, spec_d)) if s)
+        state_bytes = sum(s.row_bytes * n_rows for s in (spec_t, spec_d) if s)
         if a.max_total_tokens:
             n_pages = int(a.max_total_tokens)
         elif on_cuda:
@@ -116,8 +116,8 @@ class SMCScheduler:
         self.bt = BlockTable(n_slots, n_parent_rows, self.context_len, self.device)
         self.kv_t = KVPool(kv_t, n_pages, self.device)
         self.kv_d = KVPool(kv_d, n_pages, self.device)
-        self.state_t = StatePool(spec_t, n_rows, self.device, depth=G) if spec_t else None
-        self.state_d = StatePool(spec_d, n_rows, self.device, depth=2) if spec_d else None
+        self.state_t = StatePool(spec_t, n_rows, self.device) if spec_t else None
+        self.state_d = StatePool(spec_d, n_rows, self.device) if spec_d else None
         # ---- native backend -----------------------------------------------------
         self.native_state = None
         self.native_runner = None
@@ -221,6 +221,9 @@ class SMCScheduler:
             if pages is None:
                 raise RuntimeError("page reservation violated")
             self.bt.table[g.parent_row, :L] = pages
+            for pool in (self.state_t, self.state_d):       # recurrent state of a reused parent row starts at zero
+                if pool is not None:
+                    pool.clear_rows(torch.tensor([g.parent_row], device=self.device))
             items.append(PrefillItem(g.parent_row, g.req.input_ids))
         x0 = self.worker.prefill(items).tolist()          # one blocking read per prefill batch
         self.stats["prefills"] += len(groups)

@@ -113,10 +113,9 @@ class SMCWorker:
         ids = torch.stack([cin.prev.long(), cin.x0.long()], dim=1).reshape(-1)
         pos = torch.stack([S - 1, S], dim=1).reshape(-1)
         locs = torch.stack([loc_prev.long(), cin.cache_locs[:, 0].long()], dim=1).reshape(-1)
-        head = ExtendBatch(ids, pos, locs, cin.slots, (S - 1).to(torch.int32), extend_len=2, save_steps=True)
+        # SMC accepts every token, so stateful models simply end the pass on the last token's state
+        head = ExtendBatch(ids, pos, locs, cin.slots, (S - 1).to(torch.int32), extend_len=2)
         hid = self.draft.forward_torch(head, self.kv_d, self.bt.table, self.state_d)
-        if self.state_d is not None and getattr(self.draft, "has_state", False):
-            self.state_d.commit(sl, 1)
         logits = self.draft.logits_torch(hid.view(bs, 2, -1)[:, 1])
         d, lq = self._sample_draft(logits)
         drafts, logqs = [d], [lq]
@@ -153,10 +152,8 @@ class SMCWorker:
         ids = torch.cat([cin.x0.view(bs, 1).long(), drafts.long()], dim=1)            # [bs, G]
         pos = S.unsqueeze(1) + torch.arange(G, device=self.device).unsqueeze(0)
         vb = ExtendBatch(ids.reshape(-1), pos.reshape(-1), cin.cache_locs.reshape(-1).long(), cin.slots,
-                         cin.orig_seq_lens.to(torch.int32), extend_len=G, save_steps=True)
+                         cin.orig_seq_lens.to(torch.int32), extend_len=G)
         hid = self.target.forward_torch(vb, self.kv_t, self.bt.table, self.state_t)
-        if self.state_t is not None and getattr(self.target, "has_state", False):
-            self.state_t.commit(cin.slots.long(), gamma)
         logits = self.target.logits_torch(hid).view(bs, G, -1)
         score = smc_math.chosen_logprob(logits[:, :gamma], drafts.long(), self.T_target)
         diff = self.alpha * score - logq
