@@ -1,0 +1,149 @@
+// Gated DeltaNet (linear attention) step kernels for E new tokens per sequence row (E = 1 draft
+// decode, 2 draft head, gamma+1 target verify).  SMC accepts every token, so the recurrent state is
+// advanced in place through all E tokens.
+//   gdn_conv      depthwise causal conv (width W) + SiLU over the mixed q|k|v channels, one thread per
+//                 (row, channel); also rolls the conv window kept in the state pool
+//   gdn_recurrent one CTA per (row, value head); thread j owns column j of the state S [dk, dv] in
+//                 registers, so the delta-rule update and the read-out are thread-local:
+//                     S *= exp(g);  kv = S^T k;  delta = (v - kv) * beta;  S += k (x) delta;  o = S^T q
+//                 followed by the gated RMSNorm of the head output (norm, weight, * silu(z)) -> bf16
+#include "common.cuh"
+
+namespace smc {
+
+// proj: fp32 [T, ldp] = mixed (conv_dim) | z (value_dim) | b (Hv) | a (Hv).
+__global__ void gdn_conv_kernel(const float* __restrict__ proj, int ldp, float* __restrict__ conv_state,
+                                const int* __restrict__ state_rows, const __nv_bfloat16* __restrict__ conv_w,
+                                float* __restrict__ conv_out, int bs, int E, int conv_dim, int W, int pdl) {
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= bs * conv_dim) return;
+  const int b = idx / conv_dim, ch = idx % conv_dim;
+  float* win = conv_state + ((size_t)state_rows[b] * conv_dim + ch) * (W - 1);
+  float hist[8];
+  float w[8];
+  for (int i = 0; i < W - 1; ++i) hist[i] = win[i];
+  for (int i = 0; i < W; ++i) w[i] = __bfloat162float(conv_w[ch * W + i]);
+  for (int e = 0; e < E; ++e) {
+    const float x = proj[(size_t)(b * E + e) * ldp + ch];
+    float acc = w[W - 1] * x;
+    for (int i = 0; i < W - 1; ++i) acc += w[i] * hist[i];
+    for (int i = 0; i + 1 < W - 1; ++i) hist[i] = hist[i + 1];
+    hist[W - 2] = x;
+    conv_out[(size_t)(b * E + e) * conv_dim + ch] = acc / (1.f + __expf(-acc));
+  }
+  for (int i = 0; i < W - 1; ++i) win[i] = hist[i];
+}
+
+template <int DK>
+__global__ void gdn_recurrent_kernel(const float* __restrict__ conv_out, const float* __restrict__ proj, int ldp,
+                                     float* __restrict__ temporal, const int* __restrict__ state_rows,
+                                     const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                                     const __nv_bfloat16* __restrict__ gnorm_w, __nv_bfloat16* __restrict__ out,
+                                     int E, int Hk, int Hv, int dv, int conv_dim, float eps, int pdl) {
+  __shared__ float q_s[DK], k_s[DK], red[8];
+  __shared__ float scal[4];
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
+  const int b = blockIdx.x, vh = blockIdx.y, kh = vh / (Hv / Hk);
+  const int j = threadIdx.x;              // value-dim column owned by this thread (j < dv does real work)
+  const int key_dim = Hk * DK, value_dim = Hv * dv;
+  const bool live = j < dv;
+  float* Sg = temporal + (((size_t)state_rows[b] * Hv + vh) * DK) * dv;
+  float S[DK];
+#pragma unroll
+  for (int i = 0; i < DK; ++i) S[i] = live ? Sg[(size_t)i * dv + j] : 0.f;
+  const float wj = live ? __bfloat162float(gnorm_w[j]) : 0.f;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  for (int e = 0; e < E; ++e) {
+    const size_t t = (size_t)b * E + e;
+    const float* co = conv_out + t * conv_dim;
+    // l2-normalised q (scaled by dk^-1/2) and k of this key head
+    float qv = 0.f, kv_ = 0.f;
+    if (j < DK) { qv = co[kh * DK + j]; kv_ = co[key_dim + kh * DK + j]; }
+    float sq = warp_sum(qv * qv), sk = warp_sum(kv_ * kv_);
+    if ((j & 31) == 0) { red[j >> 5] = sq; red[4 + (j >> 5)] = sk; }
+    __syncthreads();
+    if (j == 0) {
+      float a = 0.f, c = 0.f;
+      for (int w = 0; w < nwarps; ++w) { a += red[w]; c += red[4 + w]; }
+      scal[0] = rsqrtf(a + 1e-6f) * rsqrtf((float)DK);
+      scal[1] = rsqrtf(c + 1e-6f);
+      const float av = proj[t * ldp + conv_dim + value_dim + Hv + vh];
+      const float bv = proj[t * ldp + conv_dim + value_dim + vh];
+      const float x = av + dt_bias[vh];
+      const float sp = x > 20.f ? x : log1pf(__expf(x));
+      scal[2] = __expf(-__expf(A_log[vh]) * sp);          // exp(g)
+      scal[3] = 1.f / (1.f + __expf(-bv));                // beta
+    }
+    __syncthreads();
+    if (j < DK) { q_s[j] = qv * scal[0]; k_s[j] = kv_ * scal[1]; }
+    __syncthreads();
+    const float decay = scal[2], beta = scal[3];
+    const float v = live ? co[2 * key_dim + vh * dv + j] : 0.f;
+    float kvm = 0.f;
+#pragma unroll
+    for (int i = 0; i < DK; ++i) { S[i] *= decay; kvm = fmaf(S[i], k_s[i], kvm); }
+    const float delta = (v - kvm) * beta;
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < DK; ++i) { S[i] = fmaf(k_s[i], delta, S[i]); o = fmaf(S[i], q_s[i], o); }
+    // gated RMSNorm over the head's dv outputs
+    float so = warp_sum(live ? o * o : 0.f);
+    __syncthreads();
+    if ((j & 31) == 0) red[j >> 5] = so;
+    __syncthreads();
+    float tot = 0.f;
+    for (int w = 0; w < nwarps; ++w) tot += red[w];
+    if (live) {
+      const float y = __bfloat162float(__float2bfloat16(o * rsqrtf(tot / (float)dv + eps)));
+      const float z = proj[t * ldp + conv_dim + vh * dv + j];
+      out[t * value_dim + vh * dv + j] = __float2bfloat16(y * wj * (z / (1.f + __expf(-z))));
+    }
+    __syncthreads();
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < DK; ++i) Sg[(size_t)i * dv + j] = S[i];
+  }
+}
+
+}  // namespace smc
+
+SMC_API int smc_gdn_step(const float* proj, int ldp, float* conv_state, float* temporal, const int* state_rows,
+                         const void* conv_w, const float* dt_bias, const float* A_log, const void* gnorm_w,
+                         float* conv_out, void* out, int bs, int E, int Hk, int Hv, int dk, int dv, int W, float eps,
+                         int pdl, cudaStream_t st) {
+  using namespace smc;
+  if (bs <= 0) return 0;
+  if (W < 2 || W > 8 || Hv % Hk || dv > 256 || dk > 256) return -100;
+  const int conv_dim = 2 * Hk * dk + Hv * dv;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.gridDim = dim3((bs * conv_dim + 255) / 256);
+  cfg.blockDim = dim3(256);
+  CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_conv_kernel, proj, ldp, conv_state, state_rows,
+                                    (const __nv_bfloat16*)conv_w, conv_out, bs, E, conv_dim, W, pdl));
+  int threads = dv > dk ? dv : dk;
+  threads = (threads + 31) / 32 * 32;
+  if (threads > 128) return -101;
+  cfg.gridDim = dim3(bs, Hv);
+  cfg.blockDim = dim3(threads);
+#define GDN_LAUNCH(DKV)                                                                                           \
+  CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_recurrent_kernel<DKV>, (const float*)conv_out, proj, ldp, temporal, \
+                                    state_rows, dt_bias, A_log, (const __nv_bfloat16*)gnorm_w,                    \
+                                    (__nv_bfloat16*)out, E, Hk, Hv, dv, conv_dim, eps, pdl))
+  switch (dk) {
+    case 128: GDN_LAUNCH(128); break;
+    case 64: GDN_LAUNCH(64); break;
+    case 32: GDN_LAUNCH(32); break;
+    case 16: GDN_LAUNCH(16); break;
+    default: return -102;
+  }
+#undef GDN_LAUNCH
+  return 0;
+}

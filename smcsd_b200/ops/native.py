@@ -328,3 +328,24 @@ def tp_bump_counter(flag_ptr: int, by: int) -> None:
 def tp_wait_counter(flag_ptr: int, want: int, outcome: torch.Tensor, status: torch.Tensor) -> None:
     _check(tp_lib().smc_tp_wait_counter(C.c_void_p(flag_ptr), want, _p(outcome), _p(status), _stream()),
            "smc_tp_wait_counter")
+
+
+# ----------------------------------------------------------------------------- gated delta net
+def gdn_step(proj: torch.Tensor, conv_state: torch.Tensor, temporal: torch.Tensor, state_rows: torch.Tensor,
+             conv_w: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, gnorm_w: torch.Tensor,
+             conv_out: torch.Tensor, out: torch.Tensor, *, bs: int, E: int, Hk: int, Hv: int, dk: int, dv: int, W: int,
+             eps: float, pdl: bool = False) -> None:
+    """Conv + gated delta rule + gated RMSNorm for E new tokens per row; advances the state of one layer in place.
+    conv_state [rows, conv_dim, W-1] fp32 and temporal [rows, Hv, dk, dv] fp32 are that layer's slices."""
+    L = lib()
+    if not getattr(L, "_gdn_declared", False):
+        vp, i, f = C.c_void_p, C.c_int, C.c_float
+        L.smc_gdn_step.argtypes = [vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, i, vp]
+        L.smc_gdn_step.restype = C.c_int
+        L._gdn_declared = True
+    _check(L.smc_gdn_step(_p(proj), proj.stride(0), _p(conv_state), _p(temporal), _p(state_rows), _p(conv_w),
+                          _p(dt_bias), _p(A_log), _p(gnorm_w), _p(conv_out), _p(out), bs, E, Hk, Hv, dk, dv, W, eps,
+                          int(pdl), _stream()), "smc_gdn_step")
+
+
+_KERNELS_PER_CALL["smc_gdn_step"] = 2

@@ -212,8 +212,9 @@ class NativeRunner:
         self.pdl = pdl
         splits = int(a.attention_num_kv_splits)
         self.target = self._wrap(sched.target, sched.kv_t, sched.bt.table, self.max_bs * self.G, self.max_bs * self.G,
-                                 splits, pdl)
-        self.draft = self._wrap(sched.draft, sched.kv_d, sched.bt.table, self.max_bs * 2, self.max_bs, splits, pdl)
+                                 splits, pdl, sched.state_t)
+        self.draft = self._wrap(sched.draft, sched.kv_d, sched.bt.table, self.max_bs * 2, self.max_bs, splits, pdl,
+                                sched.state_d)
         self.nchunks = 32
         rows = self.max_bs * self.G
         self.sample_scratch = torch.empty(K.sample_scratch_bytes(rows, self.nchunks), dtype=torch.uint8,
@@ -226,10 +227,11 @@ class NativeRunner:
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.launches_per_cycle = 0
 
-    def _wrap(self, model, kv, bt, max_tokens, max_logit_rows, splits, pdl):
+    def _wrap(self, model, kv, bt, max_tokens, max_logit_rows, splits, pdl, state=None):
         if model.cfg.arch != "llama":
             from .native_hybrid import NativeHybrid
-            return NativeHybrid(model, kv, bt, max_tokens, max_logit_rows, splits, self.status, pdl, runner=self)
+            return NativeHybrid(model, kv, bt, max_tokens, max_logit_rows, splits, self.status, pdl, runner=self,
+                                state=state)
         if model.tp_size > 1:
             # tensor-parallel target: peers are reached through the symmetric heap, never through NCCL
             from ..parallel.symm import SymmHeap

@@ -1,0 +1,102 @@
+"""Hybrid Gated-DeltaNet model on the sm_100a kernel chain (needs a B200)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _hybrid_cfg():
+    from smcsd_b200.models.config import ModelConfig
+    lt = ["linear_attention", "linear_attention", "linear_attention", "full_attention"] * 2
+    return ModelConfig(arch="hybrid_gdn", vocab_size=8192, hidden_size=512, n_layers=8, n_heads=4, n_kv_heads=2,
+                       head_dim=128, ffn_size=1024, rope_theta=10000.0, max_position=2048, layer_types=lt,
+                       gdn_n_k_heads=2, gdn_n_v_heads=4, gdn_head_k_dim=64, gdn_head_v_dim=64, gdn_conv_width=4,
+                       partial_rotary=0.25, attn_output_gate=True, qk_norm=True, norm_plus_one=True, rms_eps=1e-6,
+                       name="hybrid-test")
+
+
+def _dense_draft():
+    from smcsd_b200.models.config import ModelConfig
+    return ModelConfig(arch="llama", vocab_size=8192, hidden_size=256, n_layers=2, n_heads=4, n_kv_heads=2,
+                       head_dim=64, ffn_size=768, max_position=2048, tie_embeddings=True, name="dense-draft")
+
+
+def test_native_hybrid_forward_matches_torch():
+    from smcsd_b200 import SMCEngine
+    from smcsd_b200.models.layers import ExtendBatch
+    eng = SMCEngine(_hybrid_cfg(), _dense_draft(), n_particles=4, gamma=4, max_running_requests=2, context_length=512,
+                    device="cuda", max_total_tokens=8192, backend="native", cycle_graph=False)
+    s = eng._sched
+    m, nm = s.target, s.native_runner.target
+    dev = "cuda"
+    bs, P = 4, 19
+    g = torch.Generator(device=dev).manual_seed(0)
+    rows = torch.arange(bs, dtype=torch.int32, device=dev)
+    for b in range(bs):
+        s.bt.table[b, :P + 8] = s.alloc.alloc(P + 8)
+    ids = torch.randint(0, 8192, (bs * P,), generator=g, device=dev)
+    pre = ExtendBatch(ids, torch.arange(P, device=dev).repeat(bs), s.bt.table[:bs, :P].reshape(-1), rows,
+                      torch.zeros(bs, dtype=torch.int32, device=dev), extend_len=0, extend_lens=[P] * bs,
+                      prefix_lens_host=[0] * bs)
+    m.forward_torch(pre, s.kv_t, s.bt.table, s.state_t)
+    conv0, temp0 = s.state_t.conv.clone(), s.state_t.temporal.clone()
+    kk, vv = s.kv_t.k.clone(), s.kv_t.v.clone()
+    for E in (5, 1, 2):
+        ids2 = torch.randint(0, 8192, (bs * E,), generator=g, device=dev, dtype=torch.int32)
+        pos2 = (torch.arange(E, device=dev) + P).repeat(bs).to(torch.int32)
+        locs2 = s.bt.table[:bs, P:P + E].reshape(-1).contiguous()
+        pref = torch.full((bs,), P, dtype=torch.int32, device=dev)
+        ext = ExtendBatch(ids2.long(), pos2.long(), locs2, rows, pref, extend_len=E, prefix_lens_host=[P] * bs)
+        ref = m.logits_torch(m.forward_torch(ext, s.kv_t, s.bt.table, s.state_t))
+        conv_ref, temp_ref = s.state_t.conv.clone(), s.state_t.temporal.clone()
+        # rewind the recurrent state and the cache, then run the kernel chain on the same inputs
+        s.state_t.conv.copy_(conv0); s.state_t.temporal.copy_(temp0); s.kv_t.k.copy_(kk); s.kv_t.v.copy_(vv)
+        nm.forward(ids2, pos2, locs2, rows, pref, bs, E)
+        got = nm.lm_head(bs * E)[: bs * E].clone()
+        torch.cuda.synchronize()
+        assert s.native_runner.check_status() == 0
+        scale = ref.abs().max().item()
+        assert (got - ref).abs().max().item() < 0.08 * scale, E
+        assert (s.state_t.temporal[:, :bs] - temp_ref[:, :bs]).abs().max().item() < 0.05 * max(1.0, temp_ref.abs().max().item())
+        assert (s.state_t.conv[:, :bs] - conv_ref[:, :bs]).abs().max().item() < 0.05 * max(1.0, conv_ref.abs().max().item())
+        s.state_t.conv.copy_(conv0); s.state_t.temporal.copy_(temp0); s.kv_t.k.copy_(kk); s.kv_t.v.copy_(vv)
+
+
+def test_engine_hybrid_target_dense_draft_native():
+    from smcsd_b200 import SMCEngine
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 8192, (30,), generator=g).tolist() for _ in range(3)]
+    outs = {}
+    for graph in (False, True):
+        eng = SMCEngine(_hybrid_cfg(), _dense_draft(), n_particles=4, gamma=4, max_running_requests=2,
+                        context_length=512, device="cuda", max_total_tokens=8192, backend="native", cycle_graph=graph,
+                        draft_temperature=0.7, target_temperature=0.7, random_seed=2)
+        o = eng.generate(input_ids=prompts, sampling_params={"max_new_tokens": 31, "ignore_eos": True})
+        assert [x["completion_tokens"] for x in o] == [31] * 3
+        assert eng._sched.native_runner.check_status() == 0
+        eng._sched.check_idle_invariants()
+        outs[graph] = o
+    for a, b in zip(outs[False], outs[True]):
+        assert a["output_ids"] == b["output_ids"]
+
+
+def test_hybrid_state_follows_resampling_native():
+    from smcsd_b200.config import EngineArgs
+    from smcsd_b200.io_types import GenerateRequest, ParticleOutput, SamplingParams
+    from smcsd_b200.models import build_model
+    from smcsd_b200.runtime.scheduler import SMCScheduler
+    cfg = _hybrid_cfg()
+    model = build_model(cfg, torch.bfloat16, "cuda", seed=0)
+    args = EngineArgs(model_path=cfg, draft_model_path=cfg, n_particles=4, gamma=3, max_running_requests=1,
+                      context_length=512, device="cuda", max_total_tokens=8192, backend="native",
+                      draft_temperature=0.8, target_temperature=0.8, resample_threshold=2.0).finalize()
+    sched = SMCScheduler(args, target=model, draft=model)
+    g = torch.Generator().manual_seed(3)
+    sched.add_request(GenerateRequest("r", torch.randint(0, 8192, (17,), generator=g).tolist(),
+                                      SamplingParams(max_new_tokens=25, ignore_eos=True)))
+    outs = sched.run_until_idle()
+    po = [o for o in outs if isinstance(o, ParticleOutput)][0]
+    assert int(sched.state.counters[2]) > 0
+    # the draft advances its state token by token, the target in gamma+1-token passes; bf16 noise only
+    assert max(abs(w) for w in po.log_w_tilde) < 0.6, po.log_w_tilde
+    assert sched.native_runner.check_status() == 0
