@@ -354,6 +354,14 @@ SMC_API int smc_collect_resample(const SlotArrays* a, const int* active_rows, in
   return (int)cudaGetLastError();
 }
 
+// Applies a job list produced elsewhere (the particle-parallel collect kernel) to local ancestors.
+SMC_API int smc_resample_apply(const SlotArrays* a, const long long* counters, const int* job_dst, const int* job_src,
+                               int max_jobs, cudaStream_t st) {
+  if (max_jobs <= 0) return 0;
+  smc::resample_apply_kernel<<<max_jobs, 128, 0, st>>>(*a, counters, job_dst, job_src);
+  return (int)cudaGetLastError();
+}
+
 SMC_API int smc_state_copy(void* state, long long layer_stride_bytes, long long row_bytes, int n_layers, int n_rows,
                            const long long* counters, const int* job_dst, const int* job_src, int max_jobs,
                            cudaStream_t st) {

@@ -1,0 +1,232 @@
+"""Particle-parallel groups: the N particles of every request are sharded over R ranks.
+
+Every rank holds full target and draft replicas and its own paged KV and recurrent-state pools,
+prefills the prompt itself (so the prompt prefix is replicated per rank) and advances its
+``N_local = N / R`` particles of every group.  Resampling is global: interval weights are
+exchanged by peer stores, every rank derives the same systematic-resampling plan from the same
+Philox offset, and a destination whose ancestor lives on another GPU pops fresh local pages,
+rewrites its block-table suffix and gathers the ancestor's post-prompt KV rows and recurrent state
+over NVLink from inside the kernel (``smcsd_b200/ops/csrc/particle_parallel.cu``).  The reference
+keeps all particles of a group on one GPU and resamples by pointer copies only
+(smcsd/core/kernels/fused_resample_kv.py:98-105); this capability is new here.
+
+``plan_global`` / ``apply_reference`` restate the same algorithm in plain PyTorch for CPU ranks
+(gloo) and as the oracle of the kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..smc import math as smc_math
+
+SLOT_FIELDS = ("seq_lens", "verified_ids", "prev_ids", "token_counts", "finished", "finished_len", "finish_code",
+               "matched_eos", "all_token_ids")
+
+
+# ----------------------------------------------------------------------------------- oracle / CPU path
+def plan_global(weights_by_rank: Sequence[torch.Tensor], threshold: float, seed: int, step: int, row: int):
+    """Resampling decision for one group from every rank's interval log-weights.
+    Returns (resample?, [(dst_rank, dst_idx, src_rank, src_idx)], logZ increment)."""
+    n_local = int(weights_by_rank[0].numel())
+    iw = torch.cat([w.double().cpu() for w in weights_by_rank])
+    N = iw.numel()
+    w = smc_math.normalize_log_weights(iw)
+    ess = float(1.0 / (w * w).sum())
+    if N < 2 or threshold <= 0 or not ess < threshold * N:
+        return False, [], 0.0
+    u = smc_math.philox_uniform(seed, step, row)
+    dst, src = smc_math.resample_plan(w, u)
+    jobs = [(d // n_local, d % n_local, s // n_local, s % n_local) for d, s in zip(dst, src)]
+    return True, jobs, float(smc_math.logz_increment(iw))
+
+
+def apply_reference(states, kv_pools_by_rank, jobs, row: int) -> None:
+    """Plain-PyTorch execution of a global plan over per-rank SlotStates living in one process.
+    ``kv_pools_by_rank[r]`` is the list of KV pools (target, draft) of rank r."""
+    for dr, di, sr, si in jobs:
+        dst_st, src_st = states[dr], states[sr]
+        dslot = dst_st.row_slots[row][di]
+        sslot = src_st.row_slots[row][si]
+        if dr == sr:
+            dst_st._copy_particle(dslot, sslot)
+            continue
+        P = int(dst_st.prompt_lens[dslot])
+        Ld, Ls = int(dst_st.seq_lens[dslot]), int(src_st.seq_lens[sslot])
+        if Ld > P:
+            dst_st.alloc.dec_ref_and_free(dst_st.bt.table[dslot, P:Ld].clone())
+        new_pages = dst_st.alloc.alloc(Ls - P)
+        dst_st.bt.table[dslot, P:Ls] = new_pages
+        src_pages = src_st.bt.table[sslot, P:Ls].long()
+        for pd, ps in zip(kv_pools_by_rank[dr], kv_pools_by_rank[sr]):
+            pd.k[:, new_pages.long()] = ps.k[:, src_pages].to(pd.k.device)
+            pd.v[:, new_pages.long()] = ps.v[:, src_pages].to(pd.v.device)
+        for f in ("seq_lens", "verified_ids", "prev_ids", "token_counts", "finished", "finished_len", "finish_code",
+                  "matched_eos"):
+            getattr(dst_st, f)[dslot] = getattr(src_st, f)[sslot].to(dst_st.device)
+        n = int(src_st.token_counts[sslot])
+        dst_st.all_token_ids[dslot, :n] = src_st.all_token_ids[sslot, :n].to(dst_st.device)
+        for pd, ps in zip(dst_st.state_pools, src_st.state_pools):
+            pd.conv[:, dslot] = ps.conv[:, sslot].to(pd.conv.device)
+            pd.temporal[:, dslot] = ps.temporal[:, sslot].to(pd.temporal.device)
+
+
+# ----------------------------------------------------------------------------------- kernel path
+class PpTensor(C.Structure):
+    _fields_ = [("base", C.c_ulonglong), ("layer_stride", C.c_longlong), ("row_bytes", C.c_longlong),
+                ("n_layers", C.c_int), ("by_slot", C.c_int)]
+
+
+class PpRank(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in SLOT_FIELDS + ("block_table", "group_to_slots")] + [("t", PpTensor * 8)]
+
+
+class PpWorld(C.Structure):
+    _fields_ = [("r", PpRank * 8), ("heap_base", C.c_ulonglong * 8), ("n_ranks", C.c_int), ("rank", C.c_int),
+                ("n_tensors", C.c_int), ("n_local", C.c_int), ("max_out", C.c_int), ("bt_stride", C.c_int),
+                ("max_groups", C.c_int), ("pad", C.c_int)]
+
+
+class PpLocal(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("seq_lens", "verified_ids", "prev_ids", "token_counts", "finished",
+                                         "finished_len", "finish_code", "matched_eos", "all_token_ids", "block_table",
+                                         "prompt_lens", "log_weights", "interval_weights", "refcount", "free_stack",
+                                         "free_count", "alloc_error")] + [("n_pages", C.c_int)]
+
+
+def _tensor_desc(t: torch.Tensor, by_slot: bool, addr: int) -> Tuple[int, int, int, int, int]:
+    es = t.element_size()
+    return addr, t.stride(0) * es, t[0, 0].numel() * es, t.shape[0], int(by_slot)
+
+
+class ParticleParallel:
+    """Drives the particle-parallel resampling kernels for one rank.
+
+    ``addr(rank, tensor_on_this_rank) -> int`` returns the address at which ``rank`` holds its copy of
+    the given local tensor (same offset in the symmetric heap on real ranks; an explicit table in a
+    single-GPU emulation).  ``comm_base[r]`` / offsets locate the gather buffer and the two counters."""
+
+    def __init__(self, st, ns, kv_pools, rank: int, world: int, addr: Callable[[int, torch.Tensor], int],
+                 comm_base: List[int], comm_local: torch.Tensor, status: torch.Tensor):
+        from ..ops import native as K
+        self.K = K
+        L = K.lib()
+        vp, i, ll, d, ull = C.c_void_p, C.c_int, C.c_longlong, C.c_double, C.c_ulonglong
+        L.smc_pp_share_weights.argtypes = [vp, vp, vp, i, vp, ll, ll, vp]
+        L.smc_pp_collect.argtypes = [vp, vp, vp, vp, vp, i, vp, d, ull, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+        L.smc_pp_fetch.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, i, i, i, vp]
+        L.smc_pp_barrier.argtypes = [vp, ll, vp, vp, vp, i, vp]
+        L.smc_resample_apply.argtypes = [vp, vp, vp, vp, i, vp]
+        for n in ("smc_pp_share_weights", "smc_pp_collect", "smc_pp_fetch", "smc_pp_barrier", "smc_resample_apply",
+                  "smc_pp_world_size", "smc_pp_local_size"):
+            getattr(L, n).restype = C.c_int
+        assert C.sizeof(PpWorld) == L.smc_pp_world_size() and C.sizeof(PpLocal) == L.smc_pp_local_size()
+        self.L = L
+        self.st, self.ns, self.rank, self.world = st, ns, rank, world
+        self.status = status
+        dev = st.device
+        tensors = []
+        for pool in kv_pools:
+            tensors += [(pool.k, False), (pool.v, False)]
+        for pool in st.state_pools:
+            tensors += [(pool.conv, True), (pool.temporal, True)]
+        assert len(tensors) <= 8
+        self.total_layers = sum(t.shape[0] for t, _ in tensors)
+        w = PpWorld()
+        for r in range(world):
+            for f in SLOT_FIELDS:
+                setattr(w.r[r], f, addr(r, getattr(st, f)))
+            w.r[r].block_table = addr(r, st.bt.table)
+            w.r[r].group_to_slots = addr(r, st.group_to_slots)
+            for ti, (t, by_slot) in enumerate(tensors):
+                a, ls, rb, nl, bs_ = _tensor_desc(t, by_slot, addr(r, t))
+                w.r[r].t[ti].base, w.r[r].t[ti].layer_stride, w.r[r].t[ti].row_bytes = a, ls, rb
+                w.r[r].t[ti].n_layers, w.r[r].t[ti].by_slot = nl, bs_
+                assert rb % 16 == 0
+            w.heap_base[r] = comm_base[r]
+        w.n_ranks, w.rank, w.n_tensors, w.n_local = world, rank, len(tensors), st.N
+        w.max_out, w.bt_stride, w.max_groups = st.max_output_len, st.bt.table.stride(0), st.max_groups
+        self.world_host = w
+        raw = bytes(w)
+        self.world_dev = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
+        loc = PpLocal()
+        for f in ("seq_lens", "verified_ids", "prev_ids", "token_counts", "finished", "finished_len", "finish_code",
+                  "matched_eos", "all_token_ids", "prompt_lens", "log_weights", "interval_weights"):
+            setattr(loc, f, getattr(st, f).data_ptr())
+        loc.block_table = st.bt.table.data_ptr()
+        loc.refcount, loc.free_stack = st.alloc.refcount.data_ptr(), st.alloc.free_stack.data_ptr()
+        loc.free_count, loc.alloc_error = st.alloc.free_count.data_ptr(), st.alloc.error_flag.data_ptr()
+        loc.n_pages = st.alloc.size
+        self.loc = loc
+        # communication area (same layout on every rank): gather doubles, then two 64-bit counters
+        self.gather_off = 0
+        n_gather = world * st.max_groups * st.N
+        self.flag_w_off = (n_gather * 8 + 255) // 256 * 256
+        self.flag_b_off = self.flag_w_off + 256
+        self.comm_bytes = self.flag_b_off + 256
+        assert comm_local.numel() >= self.comm_bytes
+        self.comm_local = comm_local
+        max_jobs = st.max_slots
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.rjob_dst, self.rjob_rank = torch.zeros(max_jobs, **i32), torch.zeros(max_jobs, **i32)
+        self.rjob_idx, self.rjob_src = torch.zeros(max_jobs, **i32), torch.zeros(max_jobs, **i32)
+
+    @staticmethod
+    def comm_bytes_needed(world: int, max_groups: int, n_local: int) -> int:
+        return (world * max_groups * n_local * 8 + 255) // 256 * 256 + 512
+
+    def _s(self):
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _chk(self, rc, what):
+        if rc != 0:
+            raise RuntimeError(f"{what} failed with code {rc}")
+
+    def share(self) -> None:
+        st, ns = self.st, self.ns
+        ns.sync_membership(st)
+        self._chk(self.L.smc_pp_share_weights(self.world_dev.data_ptr(), st.interval_weights.data_ptr(),
+                                              ns.active_rows.data_ptr(), ns.n_groups, st.group_to_slots.data_ptr(),
+                                              self.gather_off, self.flag_w_off, self._s()), "pp_share_weights")
+
+    def collect_and_apply(self, release_only: bool = False, phase: int = 0) -> None:
+        """phase 0: everything; 1: collect + local jobs + release of remote destinations; 2: adopt + copy."""
+        st, ns, L = self.st, self.ns, self.L
+        base = self.comm_local.data_ptr()
+        if phase in (0, 1):
+            st.counters[1].zero_()
+            st.counters[3].zero_()
+            self._chk(L.smc_pp_collect(self.world_dev.data_ptr(), C.byref(self.loc), base + self.gather_off,
+                                       base + self.flag_w_off, ns.active_rows.data_ptr(), ns.n_groups,
+                                       st.group_to_slots.data_ptr(), float(st.threshold), st.seed & (2**64 - 1),
+                                       st.counters.data_ptr(), st.group_log_Z.data_ptr(), ns.job_dst.data_ptr(),
+                                       ns.job_src.data_ptr(), self.rjob_dst.data_ptr(), self.rjob_rank.data_ptr(),
+                                       self.rjob_idx.data_ptr(), self.status.data_ptr(), self._s()), "pp_collect")
+            max_jobs = ns.n_groups * st.N
+            self._chk(L.smc_resample_apply(C.byref(ns._arrays), st.counters.data_ptr(), ns.job_dst.data_ptr(),
+                                           ns.job_src.data_ptr(), max_jobs, self._s()), "resample_apply")
+            for pool in st.state_pools:
+                self.K.state_copy(pool.conv, pool.conv.shape[0], pool.n_rows, st.counters, ns.job_dst, ns.job_src,
+                                  max_jobs)
+                self.K.state_copy(pool.temporal, pool.temporal.shape[0], pool.n_rows, st.counters, ns.job_dst,
+                                  ns.job_src, max_jobs)
+        max_jobs = ns.n_groups * st.N
+        fetch_phase = {0: 0, 1: 1, 2: 2}[phase]
+        self._chk(L.smc_pp_fetch(self.world_dev.data_ptr(), C.byref(self.loc), st.bt.table.stride(0),
+                                 st.counters.data_ptr(), self.rjob_dst.data_ptr(), self.rjob_rank.data_ptr(),
+                                 self.rjob_idx.data_ptr(), self.rjob_src.data_ptr(), max_jobs, self.total_layers,
+                                 fetch_phase, self._s()), "pp_fetch")
+
+    def barrier(self, phase: int = 0) -> None:
+        base = self.comm_local.data_ptr()
+        self._chk(self.L.smc_pp_barrier(self.world_dev.data_ptr(), self.flag_b_off, base + self.flag_b_off,
+                                        self.st.counters.data_ptr(), self.status.data_ptr(), phase, self._s()),
+                  "pp_barrier")
+
+    def resample(self) -> None:
+        """One rank's whole resampling step (real multi-GPU ranks call this once per cycle)."""
+        self.share()
+        self.collect_and_apply()
+        self.barrier()

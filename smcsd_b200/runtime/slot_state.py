@@ -99,6 +99,7 @@ class SlotState:
         self.matched_eos = torch.zeros(S, **i32)
         self.ignore_eos = torch.zeros(S, dtype=torch.bool, device=dev)
         self.max_new_tokens = torch.zeros(S, **i32)
+        self.prompt_lens = torch.zeros(S, **i32)          # length of the shared (replicated) prompt prefix
         self.eos_ids = torch.full((S, MAX_EOS), -1, **i32)
         self.log_weights = torch.zeros(S, dtype=torch.float64, device=dev)
         self.interval_weights = torch.zeros(S, dtype=torch.float64, device=dev)
@@ -156,6 +157,7 @@ class SlotState:
             for pool in self.state_pools:
                 pool.copy_rows(idx, src)
         self.seq_lens.index_fill_(0, idx, int(prompt_len))
+        self.prompt_lens.index_fill_(0, idx, int(prompt_len))
         self.verified_ids.index_fill_(0, idx, int(x0))
         # seeded with the last committed token so the first deferred head rewrites S-1 idempotently
         self.prev_ids.index_fill_(0, idx, int(last_prompt_token))
