@@ -145,3 +145,22 @@ def test_cross_rank_resample_matches_reference(with_state):
             sn.alloc.check_conservation()
             assert sn.alloc.available() == sr.alloc.available()
     assert n_cross > 0, "no cross-rank ancestor was drawn: the test did not exercise the NVLink path"
+
+
+@pytest.mark.multigpu
+def test_cross_rank_resample_real_ranks(tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "res.json"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=root)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29544", os.path.join(root, "tests", "mp_pp_check.py"), str(out)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = json.loads(out.read_text())
+    assert res["ok"] and res["status"] == 0 and res["n_cross"] > 0
