@@ -10,6 +10,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from typing import Dict, Iterable, Iterator, List, Optional, Tuple
 
 import torch
@@ -50,7 +51,9 @@ class SafetensorsFile:
             n *= s
         if n == 0:
             return torch.empty(shape, dtype=dt)
-        t = torch.frombuffer(self._mm, dtype=dt, count=n, offset=self._base + b)
+        with warnings.catch_warnings():         # the mapping is read-only by design; callers copy out of it
+            warnings.simplefilter("ignore", UserWarning)
+            t = torch.frombuffer(self._mm, dtype=dt, count=n, offset=self._base + b)
         return t.view(shape)
 
     def close(self) -> None:

@@ -1,0 +1,121 @@
+"""Micro-benchmarks of the sm_100a kernels with a roofline read-out.
+
+    python -m smcsd_b200.ops.bench_kernels                       # the standard table (graph-timed)
+    python -m smcsd_b200.ops.bench_kernels --only gemm --N 16384 --K 2048 --M 8 --epi swiglu --iters 3 --plain
+
+Kernels are timed with CUDA events around CUDA-graph replays of many launches that rotate through
+enough distinct weight copies to exceed L2, so reads come from HBM.  ``--plain`` launches a few
+iterations eagerly instead (small footprint; the form to put under ``ncu``).  Fractions are of the
+measured peaks in ``MEASURED_PEAKS.json`` when present.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import native as K
+
+EPIS = {"store": K.EPI_STORE_F32, "resid": K.EPI_RESID_F32, "swiglu": K.EPI_SWIGLU_BF16, "bf16": K.EPI_BF16}
+
+
+def peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(here, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            j = json.load(f)
+        return j.get("hbm_gbs", 6650.0), j.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def time_graph(fn, inner: int, reps: int = 20) -> float:
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(inner):
+            fn()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1000.0 / reps / inner
+
+
+def gemm_case(N, Kd, M, epi, splits, pdl=True, plain=False, iters=3, copies=None):
+    dev = "cuda"
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    mb = N * Kd * 2 / 1e6
+    copies = copies or max(2, int(400 / mb) + 1)
+    if plain:
+        copies = 2
+    Ws = [(torch.randn(N, Kd, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+    X = torch.randn(M, Kd, device=dev).bfloat16()
+    if epi == K.EPI_SWIGLU_BF16:
+        out, ldo = torch.zeros(M, N // 2, device=dev, dtype=torch.bfloat16), N // 2
+    elif epi == K.EPI_BF16:
+        out, ldo = torch.zeros(M, N, device=dev, dtype=torch.bfloat16), N
+    else:
+        out, ldo = torch.zeros(M, N, device=dev), N
+    s = splits or (K.gemm_cluster_splits(N, Kd, M) if epi in (K.EPI_STORE_F32, K.EPI_RESID_F32) else 1)
+    idx = [0]
+
+    def fn():
+        K.gemm_skinny(Ws[idx[0] % copies], X, out, M=M, splits=s, epi=epi, ldo=ldo, status=st, pdl=pdl)
+        idx[0] += 1
+    if plain:
+        for _ in range(iters):
+            fn()
+        torch.cuda.synchronize()
+        return None
+    us = time_graph(fn, copies * 4)
+    assert int(st) == 0
+    return us, mb, s
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None, choices=[None, "gemm"])
+    ap.add_argument("--N", type=int, default=16384)
+    ap.add_argument("--K", type=int, default=2048)
+    ap.add_argument("--M", type=int, default=8)
+    ap.add_argument("--epi", default="swiglu", choices=list(EPIS))
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--plain", action="store_true")
+    args = ap.parse_args()
+    K.lib()
+    hbm, tf, src = peaks()
+    if args.only == "gemm":
+        r = gemm_case(args.N, args.K, args.M, EPIS[args.epi], args.splits, plain=args.plain, iters=args.iters)
+        if r:
+            us, mb, s = r
+            print(json.dumps({"kernel": "gemm_skinny", "N": args.N, "K": args.K, "M": args.M, "epi": args.epi,
+                              "splits": s, "us": us, "GBps": mb / us * 1e3, f"frac_of_{src}_hbm": mb / us * 1e3 / hbm}))
+        return
+    table = [("1B qkv", 3072, 2048, 8, "store"), ("1B o_proj", 2048, 2048, 8, "resid"),
+             ("1B gate_up+swiglu", 16384, 2048, 8, "swiglu"), ("1B down", 2048, 8192, 8, "resid"),
+             ("1B lm_head", 128256, 2048, 8, "store"), ("8B qkv", 6144, 4096, 72, "store"),
+             ("8B o_proj", 4096, 4096, 72, "resid"), ("8B gate_up+swiglu", 28672, 4096, 72, "swiglu"),
+             ("8B down", 4096, 14336, 72, "resid"), ("8B lm_head", 128256, 4096, 72, "store")]
+    print(f"peaks ({src}): HBM {hbm:.0f} GB/s, bf16 {tf:.0f} TFLOP/s")
+    print(f"{'case':22s} {'MB':>7s} {'splits':>6s} {'us':>8s} {'GB/s':>8s} {'of HBM':>7s} {'TFLOP/s':>8s}")
+    for name, N, Kd, M, epi in table:
+        us, mb, s = gemm_case(N, Kd, M, EPIS[epi], 0)
+        flops = 2.0 * N * Kd * M
+        print(f"{name:22s} {mb:7.1f} {s:6d} {us:8.2f} {mb / us * 1e3:8.0f} {mb / us * 1e3 / hbm:7.2f} "
+              f"{flops / us / 1e6:8.1f}")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,140 @@
+"""Scheduler and slot-state logic on CPU: admission under page reservations, lifecycle, finalize, refcount
+conservation, overlap-vs-sequential equivalence, flags and request validation."""
+import os
+
+import pytest
+import torch
+
+from smcsd_b200.config import EngineArgs, env_flag
+from smcsd_b200.io_types import GenerateRequest, ParticleOutput, RequestOutput, SamplingParams, validate_request
+from smcsd_b200.runtime.scheduler import SMCScheduler
+
+
+def _sched(**kw):
+    base = dict(model_path="preset:tiny-target", draft_model_path="preset:tiny-draft", n_particles=4, gamma=3,
+                dtype="float32", device="cpu", max_running_requests=2, draft_temperature=0.7, target_temperature=0.7)
+    base.update(kw)
+    return SMCScheduler(EngineArgs(**base).finalize())
+
+
+def _req(rid, n=10, **sp):
+    g = torch.Generator().manual_seed(hash(rid) % 1000)
+    return GenerateRequest(rid, torch.randint(0, 4096, (n,), generator=g).tolist(), SamplingParams(**sp))
+
+
+def test_admission_is_gated_by_slots_and_pages():
+    s = _sched(max_running_requests=2, max_total_tokens=400)
+    for i in range(4):
+        s.add_request(_req(f"r{i}", max_new_tokens=20, ignore_eos=True))
+    s.step()
+    assert len(s.running) <= 2 and len(s.waiting) >= 2
+    assert s.reserved_pages <= s.alloc.size
+    outs = s.run_until_idle()
+    done = [o for o in outs if isinstance(o, RequestOutput)]
+    assert len(done) == 4 and all(o.completion_tokens == 20 for o in done)
+    s.check_idle_invariants()
+    s.alloc.check_conservation()
+
+
+def test_request_larger_than_pool_is_aborted_not_hung():
+    s = _sched(max_total_tokens=120)
+    s.add_request(_req("big", n=30, max_new_tokens=500, ignore_eos=True))
+    outs = s.run_until_idle()
+    o = [x for x in outs if isinstance(x, RequestOutput)][0]
+    assert o.aborted and "KV pages" in o.error
+
+
+def test_queue_limit_and_abort():
+    s = _sched(max_queued_requests=1)
+    s.add_request(_req("a", max_new_tokens=30, ignore_eos=True))
+    s.add_request(_req("b", max_new_tokens=30, ignore_eos=True))
+    assert any(isinstance(o, RequestOutput) and o.aborted and "queue" in o.error for o in s.outbox)
+    s.step()
+    s.step()
+    s.abort("a")
+    outs = s.run_until_idle()
+    assert any(isinstance(o, RequestOutput) and o.rid == "a" and o.aborted for o in outs)
+    s.check_idle_invariants()
+
+
+def test_prev_token_is_seeded_with_last_prompt_token():
+    s = _sched()
+    r = _req("x", n=7, max_new_tokens=9, ignore_eos=True)
+    s.add_request(r)
+    s.step()
+    slots = s.state.row_slots[s.state.group_rows["x"]]
+    assert all(int(s.state.prev_ids[i]) == r.input_ids[-1] for i in slots)
+    assert all(int(s.state.seq_lens[i]) == 7 for i in slots)
+    assert all(int(s.state.token_counts[i]) == 1 for i in slots)
+    # fan-out shares the prompt pages: every prompt page is referenced once per particle
+    pages = s.bt.table[slots[0], :7].long()
+    assert (s.alloc.refcount[pages] == 4).all()
+    s.run_until_idle()
+    s.check_idle_invariants()
+
+
+def test_finalize_reports_posterior_pick_and_particles():
+    s = _sched()
+    s.add_request(_req("p", max_new_tokens=11, ignore_eos=True))
+    outs = s.run_until_idle()
+    po = [o for o in outs if isinstance(o, ParticleOutput)][0]
+    ro = [o for o in outs if isinstance(o, RequestOutput)][0]
+    assert len(po.particle_output_ids) == 4 and 0 <= po.picked < 4
+    assert ro.output_ids == po.particle_output_ids[po.picked]
+    assert ro.finish_reason == {"type": "length", "length": 11}
+    assert len(po.log_w_tilde) == 4 and isinstance(po.log_Z_hat, float)
+
+
+def test_single_particle_never_resamples():
+    s = _sched(n_particles=1)
+    s.add_request(_req("one", max_new_tokens=15, ignore_eos=True))
+    outs = s.run_until_idle()
+    assert s.stats["resampled_groups"] == 0
+    assert [o for o in outs if isinstance(o, RequestOutput)][0].completion_tokens == 15
+
+
+def test_multinomial_resampling_runs_on_the_torch_path():
+    s = _sched(resample_method="multinomial", resample_threshold=2.0)
+    s.add_request(_req("m", max_new_tokens=13, ignore_eos=True))
+    s.run_until_idle()
+    assert s.stats["resampled_groups"] > 0
+    s.check_idle_invariants()
+
+
+def test_env_switch_beats_keyword_beats_default(monkeypatch):
+    assert env_flag("SMC_X_UNSET", None, True) is True
+    assert env_flag("SMC_X_UNSET", False, True) is False
+    monkeypatch.setenv("SMC_DEFER_BONUS", "0")
+    a = EngineArgs(model_path="a", draft_model_path="b", defer_bonus=True).finalize()
+    assert a.defer_bonus is False
+    monkeypatch.setenv("SMC_DEFER_BONUS", "1")
+    assert EngineArgs(model_path="a", draft_model_path="b", defer_bonus=False).finalize().defer_bonus is True
+    g = EngineArgs(model_path="a", draft_model_path="b", draft_temperature=0.0).finalize()
+    assert g.cycle_graph is False           # greedy proposals take the eager path
+    with pytest.raises(ValueError):
+        EngineArgs(model_path="a", draft_model_path="b", power_alpha=0.0).finalize()
+
+
+def test_request_validation_messages():
+    ok = GenerateRequest("r", [1, 2, 3], SamplingParams(max_new_tokens=4))
+    assert validate_request(ok, 128, 4) is None
+    for field, val, word in [("image_data", object(), "multimodal"), ("input_embeds", [1.0], "input_embeds"),
+                             ("grammar", "g", "grammar"), ("return_logprob", True, "return_logprob"),
+                             ("return_hidden_states", True, "hidden"), ("return_routed_experts", True, "experts")]:
+        r = GenerateRequest("r", [1, 2, 3], SamplingParams(max_new_tokens=4))
+        setattr(r, field, val)
+        assert word in validate_request(r, 128, 4)
+    assert "stop regex" in validate_request(GenerateRequest("r", [1], SamplingParams(stop_regex="a+")), 128, 4)
+    assert "context" in validate_request(GenerateRequest("r", [1] * 100, SamplingParams(max_new_tokens=100)), 128, 4)
+    assert "empty" in validate_request(GenerateRequest("r", [], SamplingParams()), 128, 4)
+
+
+def test_debug_records_are_appended(tmp_path, monkeypatch):
+    import json
+    path = tmp_path / "diag.jsonl"
+    monkeypatch.setenv("SMC_DIAG_PATH", str(path))
+    s = _sched()
+    s.add_request(_req("d", max_new_tokens=6, ignore_eos=True))
+    s.run_until_idle()
+    rec = [json.loads(x) for x in path.read_text().splitlines()]
+    assert rec and rec[0]["event"] == "finalize" and "pid" in rec[0] and "timestamp_ns" in rec[0]
