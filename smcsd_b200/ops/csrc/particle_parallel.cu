@@ -57,20 +57,29 @@ struct PpLocal {              // this rank's mutable arrays
 };
 
 // ---- 1. share weights --------------------------------------------------------------------------
-// gather buffer on every rank: double [n_ranks, max_groups, n_local]
+// gather buffer on every rank: double [n_ranks, max_groups, n_local + 1]; the extra entry of a row carries
+// the number of this rank's particles of the group that are still unfinished
 __global__ void pp_share_weights_kernel(const PpWorld* __restrict__ w, const double* __restrict__ interval,
-                                        const int* __restrict__ active_rows, int n_groups,
-                                        const int* __restrict__ group_to_slots, long long gather_off,
+                                        const uint8_t* __restrict__ finished, const int* __restrict__ active_rows,
+                                        int n_groups, const int* __restrict__ group_to_slots, long long gather_off,
                                         long long flag_off) {
   const PpWorld& W = *w;
-  const int total = n_groups * W.n_local;
+  const int stride = W.n_local + 1;
+  const int total = n_groups * stride;
   for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
-    const int gi = idx / W.n_local, i = idx % W.n_local;
+    const int gi = idx / stride, i = idx % stride;
     const int row = active_rows[gi];
-    const double v = interval[group_to_slots[row * W.n_local + i]];
+    double v;
+    if (i < W.n_local) {
+      v = interval[group_to_slots[row * W.n_local + i]];
+    } else {
+      int alive = 0;
+      for (int k = 0; k < W.n_local; ++k) alive += finished[group_to_slots[row * W.n_local + k]] ? 0 : 1;
+      v = (double)alive;
+    }
     for (int pr = 0; pr < W.n_ranks; ++pr) {
       double* dst = reinterpret_cast<double*>(W.heap_base[pr] + gather_off) +
-                    ((size_t)W.rank * W.max_groups + row) * W.n_local + i;
+                    ((size_t)W.rank * W.max_groups + row) * stride + i;
       *dst = v;
     }
   }
@@ -88,7 +97,7 @@ __global__ void pp_collect_kernel(const PpWorld* __restrict__ w, PpLocal loc, co
                                   unsigned long long seed, long long* __restrict__ counters,
                                   double* __restrict__ group_log_z, int* __restrict__ job_dst,
                                   int* __restrict__ job_src, int* __restrict__ rjob_dst, int* __restrict__ rjob_rank,
-                                  int* __restrict__ rjob_idx, int* status) {
+                                  int* __restrict__ rjob_idx, int* __restrict__ group_active, int* status) {
   const PpWorld& W = *w;
   const int gi = blockIdx.x, lane = threadIdx.x;
   if (gi >= n_groups) return;
@@ -102,7 +111,13 @@ __global__ void pp_collect_kernel(const PpWorld* __restrict__ w, PpLocal loc, co
   const int row = active_rows[gi];
   const int pr = lane / W.n_local, pi = lane % W.n_local;       // global particle `lane` lives on rank pr
   const bool have = lane < N;
-  const double iw = have ? gather[((size_t)pr * W.max_groups + row) * W.n_local + pi] : -INFINITY;
+  const int stride = W.n_local + 1;
+  const double iw = have ? gather[((size_t)pr * W.max_groups + row) * stride + pi] : -INFINITY;
+  {  // particles of this group that are still running, over all ranks (same value on every rank)
+    double alive = lane < W.n_ranks ? gather[((size_t)lane * W.max_groups + row) * stride + W.n_local] : 0.0;
+    for (int o = 16; o > 0; o >>= 1) alive += __shfl_xor_sync(0xffffffffu, alive, o);
+    if (lane == 0) group_active[row] = (int)(alive + 0.5);
+  }
   double mx = iw;
   for (int o = 16; o > 0; o >>= 1) mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   const double ex = have ? exp(iw - mx) : 0.0;
@@ -298,10 +313,10 @@ SMC_API int smc_pp_world_size() { return (int)sizeof(PpWorld); }
 SMC_API int smc_pp_local_size() { return (int)sizeof(PpLocal); }
 
 // phases let a single-GPU emulation interleave the ranks: 1 = share, 2 = collect + local/remote apply, 3 = barrier
-SMC_API int smc_pp_share_weights(const PpWorld* w_dev, const double* interval, const int* active_rows, int n_groups,
-                                 const int* group_to_slots, long long gather_off, long long flag_off, cudaStream_t st) {
+SMC_API int smc_pp_share_weights(const PpWorld* w_dev, const double* interval, const uint8_t* finished,
+                                 const int* active_rows, int n_groups, const int* group_to_slots, long long gather_off, long long flag_off, cudaStream_t st) {
   if (n_groups <= 0) return 0;
-  pp_share_weights_kernel<<<1, 256, 0, st>>>(w_dev, interval, active_rows, n_groups, group_to_slots, gather_off,
+  pp_share_weights_kernel<<<1, 256, 0, st>>>(w_dev, interval, finished, active_rows, n_groups, group_to_slots, gather_off,
                                              flag_off);
   return (int)cudaGetLastError();
 }
@@ -310,11 +325,11 @@ SMC_API int smc_pp_collect(const PpWorld* w_dev, const PpLocal* loc, const doubl
                            const unsigned long long* flag, const int* active_rows, int n_groups,
                            const int* group_to_slots, double threshold, unsigned long long seed, long long* counters,
                            double* group_log_z, int* job_dst, int* job_src, int* rjob_dst, int* rjob_rank,
-                           int* rjob_idx, int* status, cudaStream_t st) {
+                           int* rjob_idx, int* group_active, int* status, cudaStream_t st) {
   if (n_groups <= 0) return 0;
   pp_collect_kernel<<<n_groups, 32, 0, st>>>(w_dev, *loc, gather, flag, active_rows, n_groups, group_to_slots,
                                              threshold, seed, counters, group_log_z, job_dst, job_src, rjob_dst,
-                                             rjob_rank, rjob_idx, status);
+                                             rjob_rank, rjob_idx, group_active, status);
   return (int)cudaGetLastError();
 }
 

@@ -186,6 +186,9 @@ class NativeState:
                      self.verify_logp, self.verify_logz, alpha, alpha != 1.0, self.tokens_out, self.diff_out)
 
     def collect_and_resample(self, st) -> None:
+        if st.pp is not None:                     # particles of a group are spread over several GPUs
+            st.pp.resample_native(st)
+            return
         K.collect_resample(self._arrays, self.active_rows, self.n_groups, st.group_to_slots, st.N, float(st.threshold),
                            st.seed, st.counters, st.group_log_Z, self.job_dst, self.job_src)
         max_jobs = self.n_groups * (st.N - 1)
@@ -219,7 +222,7 @@ class NativeRunner:
         rows = self.max_bs * self.G
         self.sample_scratch = torch.empty(K.sample_scratch_bytes(rows, self.nchunks), dtype=torch.uint8,
                                           device=self.device)
-        self.seed = int(a.random_seed) * 1000003 + 12345
+        self.seed = int(a.random_seed) * 1000003 + 12345 + 7919 * getattr(sched, "pp_rank", 0)
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.use_graph = bool(a.cycle_graph)
         self.T_draft, self.T_target, self.alpha = float(a.draft_temperature), float(a.target_temperature), float(a.power_alpha)
@@ -367,8 +370,12 @@ class NativeRunner:
         return [t.clone() for t in self._mutable(st)]
 
     def _restore_state(self, st, saved) -> None:
+        step = st.counters[0:1].clone()
         for t, s in zip(self._mutable(st), saved):
             t.copy_(s)
+        if st.pp is not None:
+            # cross-rank counters advanced during the warm-up cycle; keep the cycle number in step with them
+            st.counters[0:1].copy_(step)
 
     def check_status(self) -> int:
         self._status_host.copy_(self.status)

@@ -114,8 +114,8 @@ class ParticleParallel:
         self.K = K
         L = K.lib()
         vp, i, ll, d, ull = C.c_void_p, C.c_int, C.c_longlong, C.c_double, C.c_ulonglong
-        L.smc_pp_share_weights.argtypes = [vp, vp, vp, i, vp, ll, ll, vp]
-        L.smc_pp_collect.argtypes = [vp, vp, vp, vp, vp, i, vp, d, ull, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+        L.smc_pp_share_weights.argtypes = [vp, vp, vp, vp, i, vp, ll, ll, vp]
+        L.smc_pp_collect.argtypes = [vp, vp, vp, vp, vp, i, vp, d, ull, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
         L.smc_pp_fetch.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, i, i, i, vp]
         L.smc_pp_barrier.argtypes = [vp, ll, vp, vp, vp, i, vp]
         L.smc_resample_apply.argtypes = [vp, vp, vp, vp, i, vp]
@@ -162,7 +162,7 @@ class ParticleParallel:
         self.loc = loc
         # communication area (same layout on every rank): gather doubles, then two 64-bit counters
         self.gather_off = 0
-        n_gather = world * st.max_groups * st.N
+        n_gather = world * st.max_groups * (st.N + 1)
         self.flag_w_off = (n_gather * 8 + 255) // 256 * 256
         self.flag_b_off = self.flag_w_off + 256
         self.comm_bytes = self.flag_b_off + 256
@@ -175,7 +175,7 @@ class ParticleParallel:
 
     @staticmethod
     def comm_bytes_needed(world: int, max_groups: int, n_local: int) -> int:
-        return (world * max_groups * n_local * 8 + 255) // 256 * 256 + 512
+        return (world * max_groups * (n_local + 1) * 8 + 255) // 256 * 256 + 512
 
     def _s(self):
         return C.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -188,7 +188,7 @@ class ParticleParallel:
         st, ns = self.st, self.ns
         ns.sync_membership(st)
         self._chk(self.L.smc_pp_share_weights(self.world_dev.data_ptr(), st.interval_weights.data_ptr(),
-                                              ns.active_rows.data_ptr(), ns.n_groups, st.group_to_slots.data_ptr(),
+                                              st.finished.data_ptr(), ns.active_rows.data_ptr(), ns.n_groups, st.group_to_slots.data_ptr(),
                                               self.gather_off, self.flag_w_off, self._s()), "pp_share_weights")
 
     def collect_and_apply(self, release_only: bool = False, phase: int = 0) -> None:
@@ -203,7 +203,8 @@ class ParticleParallel:
                                        st.group_to_slots.data_ptr(), float(st.threshold), st.seed & (2**64 - 1),
                                        st.counters.data_ptr(), st.group_log_Z.data_ptr(), ns.job_dst.data_ptr(),
                                        ns.job_src.data_ptr(), self.rjob_dst.data_ptr(), self.rjob_rank.data_ptr(),
-                                       self.rjob_idx.data_ptr(), self.status.data_ptr(), self._s()), "pp_collect")
+                                       self.rjob_idx.data_ptr(), st.group_active.data_ptr(), self.status.data_ptr(),
+                                       self._s()), "pp_collect")
             max_jobs = ns.n_groups * st.N
             self._chk(L.smc_resample_apply(C.byref(ns._arrays), st.counters.data_ptr(), ns.job_dst.data_ptr(),
                                            ns.job_src.data_ptr(), max_jobs, self._s()), "resample_apply")
@@ -230,3 +231,108 @@ class ParticleParallel:
         self.share()
         self.collect_and_apply()
         self.barrier()
+
+
+# ----------------------------------------------------------------------------------- engine-facing drivers
+class PpHost:
+    """Host-side helpers shared by both execution paths (object gathers at finalize)."""
+
+    def __init__(self, group, rank: int, world: int):
+        self.group, self.rank, self.world = group, rank, world
+
+    def all_gather_objects(self, obj):
+        import torch.distributed as dist
+        out = [None] * self.world
+        dist.all_gather_object(out, obj, group=self.group)
+        return out
+
+
+class PpTorch(PpHost):
+    """Particle-parallel resampling over ``torch.distributed`` (gloo on CPU ranks): the plumbing path and the
+    oracle of the kernel path.  Payloads of cross-rank ancestors travel as broadcast objects."""
+
+    def __init__(self, group, rank: int, world: int, kv_pools):
+        super().__init__(group, rank, world)
+        self.kv_pools = kv_pools
+
+    def _export(self, st, slot: int) -> dict:
+        P, L = int(st.prompt_lens[slot]), int(st.seq_lens[slot])
+        pages = st.bt.table[slot, P:L].long()
+        n = int(st.token_counts[slot])
+        return dict(
+            L=L, n=n, tokens=st.all_token_ids[slot, :n].cpu(),
+            scal={f: getattr(st, f)[slot].cpu() for f in ("verified_ids", "prev_ids", "token_counts", "finished",
+                                                          "finished_len", "finish_code", "matched_eos")},
+            kv=[(p.k[:, pages].cpu(), p.v[:, pages].cpu()) for p in self.kv_pools],
+            state=[(p.conv[:, slot].cpu(), p.temporal[:, slot].cpu()) for p in st.state_pools])
+
+    def _import(self, st, slot: int, pay: dict) -> None:
+        P, Ld = int(st.prompt_lens[slot]), int(st.seq_lens[slot])
+        if Ld > P:
+            st.alloc.dec_ref_and_free(st.bt.table[slot, P:Ld].clone())
+        L = pay["L"]
+        new_pages = st.alloc.alloc(L - P)
+        if new_pages is None:
+            raise RuntimeError("KV page pool exhausted while adopting a remote ancestor")
+        st.bt.table[slot, P:L] = new_pages
+        for p, (k, v) in zip(self.kv_pools, pay["kv"]):
+            p.k[:, new_pages.long()] = k.to(p.k.device)
+            p.v[:, new_pages.long()] = v.to(p.v.device)
+        st.seq_lens[slot] = L
+        for f, val in pay["scal"].items():
+            getattr(st, f)[slot] = val.to(st.device)
+        st.all_token_ids[slot, :pay["n"]] = pay["tokens"].to(st.device)
+        for p, (c, t) in zip(st.state_pools, pay["state"]):
+            p.conv[:, slot] = c.to(p.conv.device)
+            p.temporal[:, slot] = t.to(p.temporal.device)
+
+    def resample_torch(self, st) -> int:
+        import torch.distributed as dist
+        rows = st.active_rows_host
+        if not rows:
+            return 0
+        n_local = st.N
+        # running particles per group over all ranks (drives the identical drain decision on every rank)
+        alive = torch.zeros(st.max_groups, dtype=torch.int32)
+        w_local = torch.zeros(len(rows), n_local, dtype=torch.float64)
+        for i, row in enumerate(rows):
+            idx = torch.tensor(st.row_slots[row], dtype=torch.long, device=st.device)
+            alive[row] = int((~st.finished[idx]).sum())
+            w_local[i] = st.interval_weights[idx].cpu()
+        dist.all_reduce(alive, group=self.group)
+        st.group_active.copy_(alive.to(st.device))
+        gathered = [torch.zeros_like(w_local) for _ in range(self.world)]
+        dist.all_gather(gathered, w_local, group=self.group)
+        n_res = 0
+        for i, row in enumerate(rows):
+            go, jobs, inc = plan_global([g[i] for g in gathered], st.threshold, st.seed, st.step, row)
+            if not go:
+                continue
+            n_res += 1
+            slots = st.row_slots[row]
+            for dr, di, sr, si in jobs:
+                if dr == sr:
+                    if dr == self.rank:
+                        st._copy_particle(slots[di], slots[si])
+                    continue
+                box = [self._export(st, slots[si]) if self.rank == sr else None]
+                dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, sr), group=self.group)
+                if self.rank == dr:
+                    self._import(st, slots[di], box[0])
+            idx = torch.tensor(slots, dtype=torch.long, device=st.device)
+            st.interval_weights[idx] = 0.0
+            st.log_weights[idx] = 0.0
+            st.group_log_Z[row] += inc
+        st.n_resamples += n_res
+        return n_res
+
+
+class PpNative(PpHost):
+    """Kernel path: weight exchange, plan and cross-GPU gather all happen in kernels over the symmetric heap."""
+
+    def __init__(self, group, rank: int, world: int, driver: ParticleParallel):
+        super().__init__(group, rank, world)
+        self.driver = driver
+
+    def resample_native(self, st) -> None:
+        self.driver.resample()

@@ -83,7 +83,9 @@ def run_scheduler_process(args: EngineArgs, rank: int, world: int, ports: PortAr
         if world > 1:
             comm = Comm.init(rank, world, args, ports.dist_port, group_size=group)
         tp_rank = in_group % args.tp_size
-        sched = SMCScheduler(args, tp_rank=tp_rank, tp_size=args.tp_size, dp_rank=replica, local_rank=rank, comm=comm)
+        pp_rank = in_group // args.tp_size
+        sched = SMCScheduler(args, tp_rank=tp_rank, tp_size=args.tp_size, dp_rank=replica, local_rank=rank, comm=comm,
+                             pp_rank=pp_rank, pp_size=args.pp_size)
         ctx = zmq.Context(1)
         leader = in_group == 0
         if leader:

@@ -62,10 +62,16 @@ def _resolve_device(args: EngineArgs, local_rank: int = 0) -> torch.device:
 
 class SMCScheduler:
     def __init__(self, args: EngineArgs, *, tp_rank: int = 0, tp_size: int = 1, dp_rank: int = 0,
-                 local_rank: int = 0, target=None, draft=None, comm=None):
+                 local_rank: int = 0, target=None, draft=None, comm=None, pp_rank: int = 0, pp_size: int = 1):
         self.args = args.finalize() if args.defer_bonus is None else args
         a = self.args
         self.tp_rank, self.tp_size, self.dp_rank = tp_rank, tp_size, dp_rank
+        self.pp_rank, self.pp_size = pp_rank, pp_size
+        if a.n_particles % pp_size:
+            raise ValueError("n_particles must be a multiple of the particle-parallel size")
+        if pp_size > 1 and tp_size > 1:
+            raise NotImplementedError("particle-parallel groups run with replicated (tp_size=1) models")
+        self.n_local = a.n_particles // pp_size          # particles of each group held by this rank
         self.device = _resolve_device(a, local_rank)
         on_cuda = self.device.type == "cuda"
         self.dtype = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}[a.dtype]
@@ -92,7 +98,7 @@ class SMCScheduler:
             raise ValueError("target and draft must share a vocabulary")
         self.context_len = int(a.context_length or min(self.target.cfg.max_position, 16384))
         # ---- memory -----------------------------------------------------------
-        N, G = a.n_particles, a.gamma + 1
+        N, G = self.n_local, a.gamma + 1
         self.max_groups = a.max_running_requests
         n_slots = self.max_groups * N
         n_parent_rows = max(self.max_groups, 4)
@@ -134,7 +140,9 @@ class SMCScheduler:
         if self.native_runner is not None:
             self.native_runner.st = self.state
         self.worker = SMCWorker(a, self.target, self.draft, self.kv_t, self.kv_d, self.bt, self.alloc,
-                                self.state_t, self.state_d, native_runner=self.native_runner)
+                                self.state_t, self.state_d, native_runner=self.native_runner, noise_rank=pp_rank)
+        if pp_size > 1:
+            self._init_particle_parallel(comm)
         # ---- queues -------------------------------------------------------------
         self.waiting: Deque[SequenceGroup] = deque()
         self.running: Dict[str, SequenceGroup] = {}
@@ -150,6 +158,54 @@ class SMCScheduler:
         # bytes moved across PCIe by this scheduler (prompt uploads; snapshots and final tokens back)
         self.io_bytes = {"h2d": 0, "d2h": 0}
         self.worker.io_bytes = self.io_bytes
+
+    def _init_particle_parallel(self, comm) -> None:
+        """Particles of every group are sharded over the ranks of this model-parallel group."""
+        from ..parallel import particle_parallel as ppm
+        if comm is None:
+            raise RuntimeError("particle-parallel groups need one process per rank")
+        kvs = [self.kv_t, self.kv_d]
+        if self.native_runner is None:
+            self.state.pp = ppm.PpTorch(comm.host_group, self.pp_rank, self.pp_size, kvs)
+            return
+        from ..parallel.symm import SymmHeap
+        st = self.state
+        small = ("seq_lens", "verified_ids", "prev_ids", "token_counts", "finished", "finished_len", "finish_code",
+                 "matched_eos", "all_token_ids", "group_to_slots")
+        big = [(self.bt, "table")] + [(kv, n) for kv in kvs for n in ("k", "v")] + \
+              [(p, n) for p in st.state_pools for n in ("conv", "temporal")]
+        need = sum(getattr(st, f).numel() * getattr(st, f).element_size() + 256 for f in small)
+        need += sum(getattr(o, n).numel() * getattr(o, n).element_size() + 256 for o, n in big)
+        need += ppm.ParticleParallel.comm_bytes_needed(self.pp_size, st.max_groups, st.N) + (1 << 20)
+        heap = SymmHeap(need, self.device, comm.device_group, self.pp_rank, self.pp_size)
+        offsets = {}
+
+        def migrate(obj, name):
+            t = getattr(obj, name)
+            off = heap.alloc(name, t.numel() * t.element_size())
+            v = heap.view(off, t.shape, t.dtype)
+            v.copy_(t)
+            setattr(obj, name, v)
+            offsets[v.data_ptr()] = off
+            del t
+        for f in small:
+            migrate(st, f)
+        for o, n in big:
+            migrate(o, n)
+        torch.cuda.empty_cache()
+        nbytes = ppm.ParticleParallel.comm_bytes_needed(self.pp_size, st.max_groups, st.N)
+        comm_off = heap.alloc("pp_comm", nbytes)
+        comm_local = heap.view(comm_off, (nbytes,), torch.uint8)
+        ns = self.native_state
+        ns.bind(st)
+        for nm in (self.native_runner.target, self.native_runner.draft):
+            nm.bt = self.bt.table                      # the block table now lives in the symmetric heap
+        drv = ppm.ParticleParallel(st, ns, kvs, self.pp_rank, self.pp_size,
+                                   lambda q, t: heap.ptrs[q] + offsets[t.data_ptr()],
+                                   [p + comm_off for p in heap.ptrs], comm_local, self.native_runner.status)
+        self._pp_heap = heap
+        st.pp = ppm.PpNative(comm.host_group, self.pp_rank, self.pp_size, drv)
+        heap.barrier()
 
     # ------------------------------------------------------------------ intake
     def add_request(self, req: GenerateRequest) -> None:
@@ -182,7 +238,7 @@ class SMCScheduler:
     # ------------------------------------------------------------------ admission
     def _pages_needed(self, g: SequenceGroup) -> int:
         L = len(g.req.input_ids)
-        return L + self.args.n_particles * (g.req.sampling_params.max_new_tokens + 2 * (self.args.gamma + 1))
+        return L + self.n_local * (g.req.sampling_params.max_new_tokens + 2 * (self.args.gamma + 1))
 
     def _admit(self) -> List[SequenceGroup]:
         """Admit waiting groups while slots, parent rows and worst-case pages are available.
@@ -300,7 +356,7 @@ class SMCScheduler:
             if g is None:
                 continue
             g.cycles += 1
-            if not self.state.group_has_active(rid, snap.finished):
+            if not self.state.group_has_active(rid, snap):
                 self._finalize(g)
 
     def _flush_pending(self) -> None:

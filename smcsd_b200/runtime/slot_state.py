@@ -53,6 +53,7 @@ class HostSnapshot:
         pin = device.type == "cuda"
         self.finished = torch.zeros(n_slots, dtype=torch.bool, pin_memory=pin)
         self.scalars = torch.zeros(4, dtype=torch.int32, pin_memory=pin)   # free_count, alloc_error, n_resampled, step
+        self.group_active = None            # [max_groups] running particles per group over all ranks (particle-parallel)
         self.event = torch.cuda.Event() if pin else None
 
     def wait(self) -> None:
@@ -107,6 +108,8 @@ class SlotState:
         self.group_to_slots = torch.full((max_groups, n_particles), EMPTY_SLOT, **i32)
         self.row_in_use = torch.zeros(max_groups, dtype=torch.bool, device=dev)
         self.group_log_Z = torch.zeros(max_groups, dtype=torch.float64, device=dev)
+        self.group_active = torch.zeros(max_groups, **i32)    # particle-parallel: running particles per group, all ranks
+        self.pp = None                                        # particle-parallel driver (None: all particles are local)
         # device-side counters: [0] cycle step (Philox counter), [1] resample jobs this cycle,
         # [2] groups resampled in total
         self.counters = torch.zeros(4, dtype=torch.int64, device=dev)
@@ -272,6 +275,8 @@ class SlotState:
         if self.native is not None:
             self.native.collect_and_resample(self)
             return -1
+        if self.pp is not None:
+            return self.pp.resample_torch(self)
         n_res = 0
         N = self.N
         if N < 2 or self.threshold <= 0.0:
@@ -324,13 +329,19 @@ class SlotState:
         snap.finished.copy_(self.finished, non_blocking=True)
         snap.scalars[0:1].copy_(self.alloc.free_count, non_blocking=True)
         snap.scalars[1:2].copy_(self.alloc.error_flag, non_blocking=True)
+        if self.pp is not None:
+            if snap.group_active is None:
+                snap.group_active = torch.zeros(self.max_groups, dtype=torch.int32, pin_memory=self._pin)
+            snap.group_active.copy_(self.group_active, non_blocking=True)
         if snap.event is not None:
             snap.event.record()
         return snap
 
-    def group_has_active(self, group_id: str, finished_host: torch.Tensor) -> bool:
-        slots = self.row_slots[self.group_rows[group_id]]
-        return not all(bool(finished_host[s]) for s in slots)
+    def group_has_active(self, group_id: str, snap) -> bool:
+        row = self.group_rows[group_id]
+        if self.pp is not None:              # the count covers every rank's particles, so all ranks agree
+            return int(snap.group_active[row]) > 0
+        return not all(bool(snap.finished[s]) for s in self.row_slots[row])
 
     # ------------------------------------------------------------------ finalize
     def finalize_group(self, group_id: str, generator: Optional[torch.Generator] = None) -> dict:
@@ -352,6 +363,18 @@ class SlotState:
         for j in range(self.N):
             n = flen[j] if codes[j] != FINISH_NONE else counts[j]
             outs.append(hist[j, : min(n, self.max_output_len)].tolist())
+        if self.pp is not None:
+            # every rank contributes its particles; all ranks end up with the same global view and pick
+            parts = self.pp.all_gather_objects(dict(outs=outs, lw=lw.tolist(), iw=iw.tolist(), codes=codes,
+                                                    matched=matched))
+            outs = [o for p_ in parts for o in p_["outs"]]
+            codes = [c for p_ in parts for c in p_["codes"]]
+            matched = [m for p_ in parts for m in p_["matched"]]
+            lw = torch.tensor([x for p_ in parts for x in p_["lw"]], dtype=torch.float64)
+            iw = torch.tensor([x for p_ in parts for x in p_["iw"]], dtype=torch.float64)
+            log_z = float(self.group_log_Z[row].cpu() + torch.logsumexp(iw, 0) - math.log(iw.numel()))
+            probs = torch.softmax(lw, dim=0).float()
+            pick = int(torch.multinomial(probs, 1, generator=generator))
         reason = {"type": "length", "length": len(outs[pick])} if codes[pick] == FINISH_LENGTH else (
             {"type": "stop", "matched": matched[pick]} if codes[pick] == FINISH_EOS else {"type": "abort"})
         return dict(output_ids=outs[pick], finish_reason=reason, picked=pick, particle_output_ids=outs,

@@ -32,7 +32,7 @@ class SMCWorker:
     def __init__(self, args: EngineArgs, target, draft, kv_target: KVPool, kv_draft: KVPool,
                  block_table: BlockTable, allocator: PageAllocator,
                  state_target: Optional[StatePool] = None, state_draft: Optional[StatePool] = None,
-                 native_runner=None):
+                 native_runner=None, noise_rank: int = 0):
         self.args = args
         self.target, self.draft = target, draft
         self.kv_t, self.kv_d = kv_target, kv_draft
@@ -46,8 +46,12 @@ class SMCWorker:
         self.alpha = float(args.power_alpha)
         self.defer_bonus = bool(args.defer_bonus)
         self.native = native_runner
+        # x0 is shared by every particle of a group (and by every rank holding some of them): its noise comes
+        # from a rank-independent stream; the decode noise differs per rank so particles stay distinct
+        self.gen_prefill = torch.Generator(device=self.device)
+        self.gen_prefill.manual_seed(int(args.random_seed) * 7919 + 17)
         self.gen = torch.Generator(device=self.device)
-        self.gen.manual_seed(int(args.random_seed) * 7919 + 17)
+        self.gen.manual_seed(int(args.random_seed) * 7919 + 17 + 104729 * (noise_rank + 1) * (1 if noise_rank else 0))
         self.cycles = 0
         self.io_bytes = {"h2d": 0, "d2h": 0}
 
@@ -71,7 +75,7 @@ class SMCWorker:
         hid = self.target.forward_torch(batch, self.kv_t, self.bt.table, self.state_t)
         last = torch.tensor(lens, device=self.device).cumsum(0) - 1
         logits = self.target.logits_torch(hid[last])
-        x0, _, _ = smc_math.gumbel_sample(logits, self.T_target, self.alpha, generator=self.gen)
+        x0, _, _ = smc_math.gumbel_sample(logits, self.T_target, self.alpha, generator=self.gen_prefill)
         # draft: full prompt for dense drafts; stateful drafts under the deferred schedule stop one
         # token short so the first head forward advances the recurrent state through S-1 exactly once
         if getattr(self.draft, "has_state", False) and self.defer_bonus:
