@@ -154,6 +154,7 @@ class SMCScheduler:
         self.profiler = None
         self._profile_steps_left = None
         self._cycle_events: List = []
+        self._time_cycles = os.environ.get("SMC_TIME_CYCLES", "0") == "1"    # device-timed ms per decode cycle
         self.emit_particles = a.emit_particle_output
         # bytes moved across PCIe by this scheduler (prompt uploads; snapshots and final tokens back)
         self.io_bytes = {"h2d": 0, "d2h": 0}
@@ -332,6 +333,10 @@ class SMCScheduler:
     # ------------------------------------------------------------------ decode
     def _run_decode(self) -> None:
         st = self.state
+        timed = self._time_cycles and self.device.type == "cuda"
+        if timed:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
         if self.native_runner is not None and self.native_runner.can_run_cycle(st):
             self.native_runner.run_cycle(st, self.worker)          # one captured graph: prologue..resample
         else:
@@ -341,6 +346,11 @@ class SMCScheduler:
             n = st.resample()
             if n > 0:
                 self.stats["resampled_groups"] += n
+        if timed:
+            e1.record()
+            self._cycle_events.append((e0, e1, st.bs))
+            if len(self._cycle_events) > 4096:
+                del self._cycle_events[:2048]
         self.stats["cycles"] += 1
         self.stats["decode_tokens"] += st.bs * (self.args.gamma + 1)
         snap = st.snapshot_to_host()
@@ -426,6 +436,20 @@ class SMCScheduler:
             raise RuntimeError("slot leak while idle")
         if self.reserved_pages != 0:
             raise RuntimeError(f"page reservation leak: {self.reserved_pages}")
+
+    def cycle_timing(self, last: int = 0, reset: bool = False) -> dict:
+        """Device time of the recorded decode cycles (CUDA events; needs SMC_TIME_CYCLES=1)."""
+        if not self._cycle_events:
+            return {"cycles": 0}
+        torch.cuda.synchronize(self.device)
+        ev = self._cycle_events[-last:] if last else self._cycle_events
+        ms = [a.elapsed_time(b) for a, b, _ in ev]
+        rows = [n for _, _, n in ev]
+        out = {"cycles": len(ms), "ms_mean": sum(ms) / len(ms), "ms_min": min(ms), "ms_max": max(ms),
+               "ms_total": sum(ms), "rows_mean": sum(rows) / len(rows)}
+        if reset:
+            self._cycle_events.clear()
+        return out
 
     def server_info(self) -> dict:
         return dict(args=self.args.to_dict(), backend=self.backend, device=str(self.device),
