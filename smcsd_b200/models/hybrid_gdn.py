@@ -62,6 +62,46 @@ def gdn_recurrent_step(S, q, k, v, g, beta):
     return S, out
 
 
+def gdn_chunked(S, q, k, v, g, beta, chunk: int = 64):
+    """Chunk-parallel gated delta rule for long passes (prefill): same recurrence as ``gdn_recurrent_step`` applied
+    token by token, evaluated with the WY / forward-substitution form inside chunks of ``chunk`` tokens.
+    S [H, dk, dv]; q, k [T, H, dk]; v [T, H, dv]; g, beta [T, H].  Returns (S_final, out [T, H, dv])."""
+    T, H, dk = q.shape
+    dv = v.shape[-1]
+    pad = (-T) % chunk
+    if pad:
+        z = lambda x: torch.cat([x, x.new_zeros(pad, *x.shape[1:])], dim=0)
+        q, k, v, g, beta = z(q), z(k), z(v), z(g), z(beta)
+    n = (T + pad) // chunk
+    # [H, n, C, *]
+    q, k, v = (x.view(n, chunk, H, -1).permute(2, 0, 1, 3) for x in (q, k, v))
+    g = g.view(n, chunk, H).permute(2, 0, 1)
+    beta = beta.view(n, chunk, H).permute(2, 0, 1)
+    gc = g.cumsum(-1)
+    k_beta, v_beta = k * beta.unsqueeze(-1), v * beta.unsqueeze(-1)
+    tril = torch.tril(torch.ones(chunk, chunk, dtype=torch.bool, device=q.device))
+    decay = torch.where(tril, (gc.unsqueeze(-1) - gc.unsqueeze(-2)).exp(), torch.zeros((), device=q.device))
+    strict = torch.tril(torch.ones(chunk, chunk, dtype=torch.bool, device=q.device), -1)
+    A = -(k_beta @ k.transpose(-1, -2)) * decay
+    A = torch.where(strict, A, torch.zeros((), device=q.device))
+    for i in range(1, chunk):
+        row = A[..., i, :i].clone()
+        A[..., i, :i] = row + (row.unsqueeze(-1) * A[..., :i, :i]).sum(-2)
+    A = A + torch.eye(chunk, device=q.device)
+    v_w = A @ v_beta
+    k_cum = A @ (k_beta * gc.exp().unsqueeze(-1))
+    out = torch.empty(H, n, chunk, dv, device=q.device, dtype=q.dtype)
+    for c in range(n):
+        qc, kc, vc = q[:, c], k[:, c], v_w[:, c]
+        local = torch.where(tril, (qc @ kc.transpose(-1, -2)) * decay[:, c], torch.zeros((), device=q.device))
+        v_new = vc - k_cum[:, c] @ S
+        out[:, c] = (qc * gc[:, c].exp().unsqueeze(-1)) @ S + local @ v_new
+        last = gc[:, c, -1]
+        S = S * last.exp().view(H, 1, 1) + (kc * (last.unsqueeze(-1) - gc[:, c]).exp().unsqueeze(-1)).transpose(-1, -2) @ v_new
+    out = out.permute(1, 2, 0, 3).reshape(n * chunk, H, dv)[:T]
+    return S, out
+
+
 class HybridGDNModel:
     has_state = True
 
@@ -230,9 +270,13 @@ class HybridGDNModel:
             if rep > 1:
                 q = q.repeat_interleave(rep, dim=1)
                 k = k.repeat_interleave(rep, dim=1)
-            for t in range(e_len):
-                S, o = gdn_recurrent_step(S, q[t], k[t], v[t], g[t0 + t], beta[t0 + t])
-                out[t0 + t] = o
+            if e_len >= 32:          # prefill: chunk-parallel form
+                S, o = gdn_chunked(S, q, k, v, g[t0:t0 + e_len], beta[t0:t0 + e_len])
+                out[t0:t0 + e_len] = o
+            else:
+                for t in range(e_len):
+                    S, o = gdn_recurrent_step(S, q[t], k[t], v[t], g[t0 + t], beta[t0 + t])
+                    out[t0 + t] = o
             state.temporal[si, r] = S.to(state.temporal.dtype)
             t0 += e_len
         # gated RMSNorm over each head's dv (plain weight), then the output projection

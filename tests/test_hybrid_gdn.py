@@ -117,3 +117,24 @@ def test_hybrid_state_follows_particles_through_resampling():
     po = [o for o in outs if isinstance(o, ParticleOutput)][0]
     assert sched.stats["resampled_groups"] > 0
     assert max(abs(w) for w in po.log_w_tilde) < 1e-3
+
+
+def test_chunked_delta_rule_equals_token_recurrence():
+    from smcsd_b200.models.hybrid_gdn import gdn_chunked, gdn_recurrent_step
+    g_ = torch.Generator().manual_seed(0)
+    T, H, dk, dv = 150, 3, 16, 24
+    q = torch.randn(T, H, dk, generator=g_)
+    k = torch.randn(T, H, dk, generator=g_)
+    q = q / q.norm(dim=-1, keepdim=True) * dk ** -0.5
+    k = k / k.norm(dim=-1, keepdim=True)
+    v = torch.randn(T, H, dv, generator=g_)
+    g = -torch.rand(T, H, generator=g_) * 0.3
+    beta = torch.rand(T, H, generator=g_)
+    S0 = torch.randn(H, dk, dv, generator=g_) * 0.1
+    S, outs = S0.clone(), []
+    for t in range(T):
+        S, o = gdn_recurrent_step(S, q[t], k[t], v[t], g[t], beta[t])
+        outs.append(o)
+    ref = torch.stack(outs)
+    S2, out2 = gdn_chunked(S0.clone(), q, k, v, g, beta, chunk=64)
+    assert (out2 - ref).abs().max() < 1e-4 and (S2 - S).abs().max() < 1e-4
