@@ -18,6 +18,8 @@ namespace smc {
 
 struct FusedAttnParams {
   const float* qkv;          // [T, ld_qkv] fp32
+  const __nv_bfloat16* q_in; // optional: rotated bf16 queries [T, Hq*D]; then K/V of the new tokens are already in
+                             // their pages and every key is read through the block table (prefill passes)
   int ld_qkv, q_off, gate_off, k_off, v_off;
   const int* positions;      // [T]
   const int* cache_locs;     // [T]
@@ -78,12 +80,13 @@ struct WarpState {
   float o[D / 8][4];
 };
 
-// One tile of NT*8 keys.  Kt / Vt: [keys][D + 8] bf16.  valid(col, row) says whether key `col` of the
-// tile is visible to local query row `row` (0..15).
-template <int D, int NT, bool Q_REGS, class Valid>
+// One tile of NT*8 keys.  Kt / Vt: [keys][D + 8] bf16.  Key `col` of the tile is visible to this thread's
+// query rows g / g+8 iff col < nvalid and col <= lim0 / lim1 (the causal limits, precomputed by the caller).
+template <int D, int NT, bool Q_REGS>
 __device__ __forceinline__ void process_tile(const __nv_bfloat16* Kt, const __nv_bfloat16* Vt,
                                              const uint32_t (&qa)[Q_REGS ? D / 16 : 1][4],
-                                             const __nv_bfloat16* Qs_mt, float scale, WarpState<D>& st, Valid valid) {
+                                             const __nv_bfloat16* Qs_mt, float scale, WarpState<D>& st, int nvalid,
+                                             int lim0, int lim1) {
   constexpr int LD = D + 8;
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   float s[NT][4];
@@ -111,8 +114,9 @@ __device__ __forceinline__ void process_tile(const __nv_bfloat16* Kt, const __nv
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      const int col = nt * 8 + 2 * t + (c & 1), row = g + 8 * (c >> 1);
-      const float v = valid(col, row) ? s[nt][c] * scale : -INFINITY;
+      const int col = nt * 8 + 2 * t + (c & 1);
+      const bool vis = col < nvalid && col <= (c < 2 ? lim0 : lim1);
+      const float v = vis ? s[nt][c] * scale : -INFINITY;
       s[nt][c] = v;
       if (c < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
     }
@@ -184,92 +188,107 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   const int prefix = p.prefix_lens[b];
   const size_t kv_row = (size_t)p.Hkv * D;
 
-  // ---- phase 0: q / k / v of the new tokens (norm, rope, bf16) ------------------------------------
-  const int half = p.rd >> 1;
-  __shared__ int s_pos[16];
-  if (threadIdx.x < 16) {
-    int pos = 0;
-    if ((int)threadIdx.x < p.E) {
-      pos = p.positions[b * p.E + threadIdx.x];
-      if (pos < 0 || pos >= p.max_pos) {
-        atomicOr(p.status, SMC_ERR_BOUNDS);
-        pos = pos < 0 ? 0 : p.max_pos - 1;
+  const bool pool_only = p.q_in != nullptr;
+  if (pool_only) {
+    // queries were rotated by an earlier kernel; stage them (zero padded) and skip the new-token K/V work
+    for (int idx = threadIdx.x; idx < Rpad * (D / 8); idx += blockDim.x) {
+      const int r = idx / (D / 8), c = idx % (D / 8);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < R) {
+        const int e = r / G, gq = r % G;
+        v = *reinterpret_cast<const uint4*>(p.q_in + ((size_t)(b * p.E + e) * p.Hq + kvh * G + gq) * D + c * 8);
       }
+      *reinterpret_cast<uint4*>(Qs + (size_t)r * LD + c * 8) = v;
     }
-    s_pos[threadIdx.x] = pos;
-  }
-  __syncthreads();
-  // rows: [0, Rpad) queries, [Rpad, Rpad+16) keys, [Rpad+16, Rpad+32) values; rows past R / E are zero
-  auto row_info = [&](int item, __nv_bfloat16*& dst, const float*& src, const __nv_bfloat16*& nw, int& pos,
-                      bool& rope) {
-    src = nullptr; nw = nullptr; pos = 0; rope = false;
-    if (item < Rpad) {
-      dst = Qs + (size_t)item * LD;
-      if (item < R) {
-        const int e = item / G, gq = item % G;
-        src = p.qkv + (size_t)(b * p.E + e) * p.ld_qkv + p.q_off + (size_t)(kvh * G + gq) * D;
-        pos = s_pos[e]; rope = true; nw = p.qn_w;
+    __syncthreads();
+  } else {
+  // ---- phase 0: q / k / v of the new tokens (norm, rope, bf16) ------------------------------------
+    const int half = p.rd >> 1;
+    __shared__ int s_pos[16];
+    if (threadIdx.x < 16) {
+      int pos = 0;
+      if ((int)threadIdx.x < p.E) {
+        pos = p.positions[b * p.E + threadIdx.x];
+        if (pos < 0 || pos >= p.max_pos) {
+          atomicOr(p.status, SMC_ERR_BOUNDS);
+          pos = pos < 0 ? 0 : p.max_pos - 1;
+        }
+      }
+      s_pos[threadIdx.x] = pos;
+    }
+    __syncthreads();
+    // rows: [0, Rpad) queries, [Rpad, Rpad+16) keys, [Rpad+16, Rpad+32) values; rows past R / E are zero
+    auto row_info = [&](int item, __nv_bfloat16*& dst, const float*& src, const __nv_bfloat16*& nw, int& pos,
+                        bool& rope) {
+      src = nullptr; nw = nullptr; pos = 0; rope = false;
+      if (item < Rpad) {
+        dst = Qs + (size_t)item * LD;
+        if (item < R) {
+          const int e = item / G, gq = item % G;
+          src = p.qkv + (size_t)(b * p.E + e) * p.ld_qkv + p.q_off + (size_t)(kvh * G + gq) * D;
+          pos = s_pos[e]; rope = true; nw = p.qn_w;
+        }
+      } else {
+        const int e = (item - Rpad) & 15;
+        const bool is_k = item < Rpad + 16;
+        dst = (is_k ? Kn : Vn) + (size_t)e * LD;
+        if (e < p.E) {
+          src = p.qkv + (size_t)(b * p.E + e) * p.ld_qkv + (is_k ? p.k_off : p.v_off) + (size_t)kvh * D;
+          pos = s_pos[e]; rope = is_k; nw = is_k ? p.kn_w : nullptr;
+        }
+      }
+    };
+    auto emit_pair = [&](__nv_bfloat16* dst, const float* src, const __nv_bfloat16* nw, float rstd, int pos, bool rope,
+                         int i) {
+      int i1, i2;
+      bool rot;
+      if (i < half) { i1 = i; i2 = i + half; rot = rope; }
+      else { const int j = i - half; i1 = p.rd + 2 * j; i2 = i1 + 1; rot = false; }
+      float x1 = src[i1], x2 = src[i2];
+      if (nw != nullptr) {
+        const float add = p.norm_plus_one ? 1.f : 0.f;
+        x1 *= rstd * (__bfloat162float(nw[i1]) + add);
+        x2 *= rstd * (__bfloat162float(nw[i2]) + add);
+      }
+      if (rot) {
+        const float* cs = p.rope + (size_t)pos * p.rd;
+        const float c = cs[i], sn = cs[half + i];
+        const float y1 = x1 * c - x2 * sn, y2 = x2 * c + x1 * sn;
+        x1 = y1; x2 = y2;
+      }
+      dst[i1] = __float2bfloat16(x1);
+      dst[i2] = __float2bfloat16(x2);
+    };
+    if (p.qn_w == nullptr && p.kn_w == nullptr) {
+      // no per-head norm: every (row, pair) is independent, so spread them over all threads
+      for (int idx = threadIdx.x; idx < (Rpad + 32) * (D / 2); idx += blockDim.x) {
+        const int item = idx / (D / 2), i = idx % (D / 2);
+        __nv_bfloat16* dst; const float* src; const __nv_bfloat16* nw; int pos; bool rope;
+        row_info(item, dst, src, nw, pos, rope);
+        if (src == nullptr) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
+        else emit_pair(dst, src, nullptr, 1.f, pos, rope, i);
       }
     } else {
-      const int e = (item - Rpad) & 15;
-      const bool is_k = item < Rpad + 16;
-      dst = (is_k ? Kn : Vn) + (size_t)e * LD;
-      if (e < p.E) {
-        src = p.qkv + (size_t)(b * p.E + e) * p.ld_qkv + (is_k ? p.k_off : p.v_off) + (size_t)kvh * D;
-        pos = s_pos[e]; rope = is_k; nw = is_k ? p.kn_w : nullptr;
+      for (int item = warp; item < Rpad + 32; item += nwarps) {
+        __nv_bfloat16* dst; const float* src; const __nv_bfloat16* nw; int pos; bool rope;
+        row_info(item, dst, src, nw, pos, rope);
+        if (src == nullptr) {
+          for (int i = lane; i < D / 2; i += 32) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
+          continue;
+        }
+        float rstd = 1.f;
+        if (nw != nullptr) {
+          float ss = 0.f;
+          for (int i = lane; i < D; i += 32) ss += src[i] * src[i];
+          rstd = rsqrtf(warp_sum(ss) / (float)D + p.norm_eps);
+        }
+        for (int i = lane; i < D / 2; i += 32) emit_pair(dst, src, nw, rstd, pos, rope, i);
       }
     }
-  };
-  auto emit_pair = [&](__nv_bfloat16* dst, const float* src, const __nv_bfloat16* nw, float rstd, int pos, bool rope,
-                       int i) {
-    int i1, i2;
-    bool rot;
-    if (i < half) { i1 = i; i2 = i + half; rot = rope; }
-    else { const int j = i - half; i1 = p.rd + 2 * j; i2 = i1 + 1; rot = false; }
-    float x1 = src[i1], x2 = src[i2];
-    if (nw != nullptr) {
-      const float add = p.norm_plus_one ? 1.f : 0.f;
-      x1 *= rstd * (__bfloat162float(nw[i1]) + add);
-      x2 *= rstd * (__bfloat162float(nw[i2]) + add);
-    }
-    if (rot) {
-      const float* cs = p.rope + (size_t)pos * p.rd;
-      const float c = cs[i], sn = cs[half + i];
-      const float y1 = x1 * c - x2 * sn, y2 = x2 * c + x1 * sn;
-      x1 = y1; x2 = y2;
-    }
-    dst[i1] = __float2bfloat16(x1);
-    dst[i2] = __float2bfloat16(x2);
-  };
-  if (p.qn_w == nullptr && p.kn_w == nullptr) {
-    // no per-head norm: every (row, pair) is independent, so spread them over all threads
-    for (int idx = threadIdx.x; idx < (Rpad + 32) * (D / 2); idx += blockDim.x) {
-      const int item = idx / (D / 2), i = idx % (D / 2);
-      __nv_bfloat16* dst; const float* src; const __nv_bfloat16* nw; int pos; bool rope;
-      row_info(item, dst, src, nw, pos, rope);
-      if (src == nullptr) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
-      else emit_pair(dst, src, nullptr, 1.f, pos, rope, i);
-    }
-  } else {
-    for (int item = warp; item < Rpad + 32; item += nwarps) {
-      __nv_bfloat16* dst; const float* src; const __nv_bfloat16* nw; int pos; bool rope;
-      row_info(item, dst, src, nw, pos, rope);
-      if (src == nullptr) {
-        for (int i = lane; i < D / 2; i += 32) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
-        continue;
-      }
-      float rstd = 1.f;
-      if (nw != nullptr) {
-        float ss = 0.f;
-        for (int i = lane; i < D; i += 32) ss += src[i] * src[i];
-        rstd = rsqrtf(warp_sum(ss) / (float)D + p.norm_eps);
-      }
-      for (int i = lane; i < D / 2; i += 32) emit_pair(dst, src, nw, rstd, pos, rope, i);
-    }
+    __syncthreads();
   }
-  __syncthreads();
   // new K/V rows go to their pages (one CTA per (sequence, kv head) writes them)
-  if (ks == p.KS - 1) {
+  if (ks == p.KS - 1 && !pool_only) {
     constexpr int CPR = D / 8;
     for (int c = threadIdx.x; c < p.E * CPR * 2; c += blockDim.x) {
       const bool is_v = c >= p.E * CPR;
@@ -295,14 +314,17 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       qa[kk][3] = *reinterpret_cast<const uint32_t*>(Qs_mt + (g + 8) * LD + kk * 16 + 2 * t + 8);
     }
   }
+  // new-token index of this thread's two query rows (rows past R are padding and masked out at the end)
+  const int e_row0 = (mt * 16 + g) / G, e_row1 = (mt * 16 + g + 8) / G;
   WarpState<D> st;
 #pragma unroll
   for (int nt = 0; nt < D / 8; ++nt) st.o[nt][0] = st.o[nt][1] = st.o[nt][2] = st.o[nt][3] = 0.f;
 
   // ---- phase 2: cached prefix, streamed in 32-key tiles -------------------------------------------
-  int per = (prefix + p.KS - 1) / p.KS;
+  const int n_keys = pool_only ? prefix + p.E : prefix;     // keys served from the paged cache
+  int per = (n_keys + p.KS - 1) / p.KS;
   per = (per + TK - 1) / TK * TK;
-  const int kb = ks * per, ke = min(prefix, kb + per);
+  const int kb = ks * per, ke = min(n_keys, kb + per);
   const int* bt = p.block_table + (size_t)p.rows[b] * p.bt_stride;
   const int gsize = 32 * n_mt, gt = mt * 32 + lane;   // thread index inside this key-way's group
   __nv_bfloat16* my_tiles = tiles + (size_t)kw * 4 * TILE;
@@ -339,17 +361,15 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       group_barrier(1 + kw, gsize);
       const int nvalid = min(TK, r1 - r0 - tile * TK);
       const __nv_bfloat16* Kt = my_tiles + (size_t)stage * 2 * TILE;
-      process_tile<D, TK / 8, Q_REGS>(Kt, Kt + TILE, qa, Qs_mt, p.scale, st,
-                                      [nvalid](int col, int) { return col < nvalid; });
+      const int key0 = r0 + tile * TK;
+      process_tile<D, TK / 8, Q_REGS>(Kt, Kt + TILE, qa, Qs_mt, p.scale, st, nvalid, prefix + e_row0 - key0,
+                                      prefix + e_row1 - key0);
       group_barrier(1 + kw, gsize);
     }
   }
   // ---- phase 3: the new tokens, causally masked (key-way 0 of the last split) ----------------------
-  if (ks == p.KS - 1 && kw == 0) {
-    const int E = p.E, base_row = mt * 16;
-    process_tile<D, 2, Q_REGS>(Kn, Vn, qa, Qs_mt, p.scale, st, [E, G, base_row](int col, int row) {
-      return col < E && col <= (base_row + row) / G;
-    });
+  if (ks == p.KS - 1 && kw == 0 && !pool_only) {
+    process_tile<D, 2, Q_REGS>(Kn, Vn, qa, Qs_mt, p.scale, st, p.E, e_row0, e_row1);
   }
   st.l0 += __shfl_xor_sync(0xffffffffu, st.l0, 1);
   st.l0 += __shfl_xor_sync(0xffffffffu, st.l0, 2);
@@ -468,7 +488,7 @@ static size_t fused_smem_bytes(int D, int n_mt, int n_kw) {
 
 // qkv: fp32 [T, ld_qkv] with query heads at q_off, optional gate heads at gate_off (< 0: none), key heads
 // at k_off, value heads at v_off.  out: bf16 [T, Hq*D].  part_acc / part_ml: scratch, used when KS > 1.
-SMC_API int smc_attention_fused(const float* qkv, int ld_qkv, int q_off, int gate_off, int k_off, int v_off,
+SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, int q_off, int gate_off, int k_off, int v_off,
                                 const int* positions, const int* cache_locs, const float* rope, int rd, int max_pos,
                                 const void* qn_w, const void* kn_w, float norm_eps, int norm_plus_one, void* k_pool,
                                 void* v_pool, int n_pages, const int* block_table, int bt_stride, const int* rows,
@@ -484,7 +504,7 @@ SMC_API int smc_attention_fused(const float* qkv, int ld_qkv, int q_off, int gat
   if (n_kw > 4) n_kw = 4;
   if (n_kw < 1) n_kw = 1;
   FusedAttnParams p;
-  p.qkv = qkv; p.ld_qkv = ld_qkv; p.q_off = q_off; p.gate_off = gate_off; p.k_off = k_off; p.v_off = v_off;
+  p.qkv = qkv; p.q_in = (const __nv_bfloat16*)q_in; p.ld_qkv = ld_qkv; p.q_off = q_off; p.gate_off = gate_off; p.k_off = k_off; p.v_off = v_off;
   p.positions = positions; p.cache_locs = cache_locs; p.rope = rope; p.rd = rd; p.max_pos = max_pos;
   p.qn_w = (const __nv_bfloat16*)qn_w; p.kn_w = (const __nv_bfloat16*)kn_w; p.norm_eps = norm_eps;
   p.norm_plus_one = norm_plus_one;

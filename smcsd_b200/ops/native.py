@@ -51,7 +51,7 @@ def _declare(L) -> None:
     L.smc_rope_kv_write.argtypes = [vp, i, ll, vp, vp, vp, i, i, vp, vp, vp, i, i, i, i, i, vp, i, vp]
     L.smc_swiglu_partials.argtypes = [vp, i, ll, vp, i, i, i, i, i, vp]
     L.smc_attention_extend.argtypes = [vp, vp, vp, vp, i, i, vp, vp, vp, vp, vp, i, i, i, i, i, i, f, vp, i, vp]
-    L.smc_attention_fused.argtypes = [vp, i, i, i, i, i, vp, vp, vp, i, i, vp, vp, f, i, vp, vp, i, vp, i, vp, vp, vp,
+    L.smc_attention_fused.argtypes = [vp, vp, i, i, i, i, i, vp, vp, vp, i, i, vp, vp, f, i, vp, vp, i, vp, i, vp, vp, vp,
                                       vp, vp, i, i, i, i, i, i, f, vp, i, vp]
     L.smc_attention_fused.restype = C.c_int
     L.smc_sample_scratch_bytes.argtypes = [i, i]
@@ -152,11 +152,11 @@ def attention_fused(qkv: torch.Tensor, positions: torch.Tensor, cache_locs: torc
                     bs: int, E: int, Hq: int, Hkv: int, D: int, KS: int, scale: float, status: torch.Tensor,
                     q_off: int = 0, gate_off: int = -1, k_off: Optional[int] = None, v_off: Optional[int] = None,
                     qn_w: Optional[torch.Tensor] = None, kn_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6,
-                    norm_plus_one: bool = False, pdl: bool = False) -> None:
+                    norm_plus_one: bool = False, pdl: bool = False, q_in: Optional[torch.Tensor] = None) -> None:
     """Norm/rope/KV-write of the new tokens + paged causal attention + split merge, one launch per layer."""
     k_off = Hq * D if k_off is None else k_off
     v_off = k_off + Hkv * D if v_off is None else v_off
-    _check(lib().smc_attention_fused(_p(qkv), qkv.stride(0), q_off, gate_off, k_off, v_off, _p(positions),
+    _check(lib().smc_attention_fused(_p(qkv), _p(q_in), qkv.stride(0), q_off, gate_off, k_off, v_off, _p(positions),
                                      _p(cache_locs), _p(rope), rope.shape[1], rope.shape[0], _p(qn_w), _p(kn_w),
                                      norm_eps, int(norm_plus_one), _p(k_pool), _p(v_pool), k_pool.shape[0] - 1,
                                      _p(block_table), block_table.stride(0), _p(rows), _p(prefix_lens), _p(out),

