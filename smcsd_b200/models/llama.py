@@ -210,6 +210,24 @@ class LlamaModel:
             lg = torch.tanh(lg / cap) * cap
         return lg
 
+    def fold_norms(self) -> "LlamaModel":
+        """Multiply every RMSNorm weight into the matrix that consumes the normalised activations (W <- W diag(w),
+        w <- 1).  The function computed is unchanged; afterwards a GEMM can take the raw residual stream as its
+        operand and apply only the per-token 1/rms factor in its epilogue."""
+        if getattr(self, "_folded", False):
+            return self
+        for L in self.layers:
+            L.wqkv = (L.wqkv.float() * L.ln1.float().unsqueeze(0)).to(self.dtype)
+            L.wgu = (L.wgu.float() * L.ln2.float().unsqueeze(0)).to(self.dtype)
+            L.ln1 = torch.ones_like(L.ln1)
+            L.ln2 = torch.ones_like(L.ln2)
+        if self.lm_head.data_ptr() == self.embed.data_ptr():
+            self.lm_head = self.lm_head.clone()            # tied embeddings: the folded head needs its own copy
+        self.lm_head = (self.lm_head.float() * self.final_norm.float().unsqueeze(0)).to(self.dtype)
+        self.final_norm = torch.ones_like(self.final_norm)
+        self._folded = True
+        return self
+
     # recurrent-state hooks (no-ops for dense models)
     has_state = False
 

@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, int splits, long long split_stride,
                    const int* __restrict__ ids, const __nv_bfloat16* __restrict__ embed,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ xn, int ldx, int d, float eps,
-                   int plus_one, int pdl) {
+                   int plus_one, __nv_bfloat16* __restrict__ hb, float* __restrict__ ssq, int pdl) {
   __shared__ float red[32];
   if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const int m = blockIdx.x;
@@ -60,11 +60,19 @@ add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, in
   }
   const float tot = block_sum<0>(ss, red);
   const float inv = rsqrtf(tot / (float)d + eps);
+  if (ssq != nullptr && threadIdx.x == 0) ssq[m] = tot;     // for GEMMs that apply the norm in their epilogue
 #pragma unroll
   for (int i = 0; i < NORM_MAXV; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
     if (c < nvec) {
       reinterpret_cast<float4*>(h + (size_t)m * d)[c] = v[i];
+      if (hb != nullptr) {
+        __nv_bfloat162 r0 = __floats2bfloat162_rn(v[i].x, v[i].y), r1 = __floats2bfloat162_rn(v[i].z, v[i].w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&r0);
+        o.y = *reinterpret_cast<uint32_t*>(&r1);
+        *reinterpret_cast<uint2*>(hb + (size_t)m * d + c * 4) = o;
+      }
       if (xn != nullptr) {
         const uint2 wr = *reinterpret_cast<const uint2*>(w + c * 4);
         const __nv_bfloat162 w0 = *reinterpret_cast<const __nv_bfloat162*>(&wr.x);
@@ -184,13 +192,13 @@ static int launch_pdl(K kern, dim3 grid, dim3 block, cudaStream_t st, int pdl, A
 // (h's previous content is ignored); partials may be null (splits = 0).
 SMC_API int smc_add_rmsnorm(float* h, const float* partials, int splits, long long split_stride, const int* ids,
                             const void* embed, const void* w, void* xn, int ldx, int M, int d, float eps,
-                            int plus_one, int pdl, cudaStream_t st) {
+                            int plus_one, void* hb, float* ssq, int pdl, cudaStream_t st) {
   using namespace smc;
   if (M <= 0) return 0;
   if ((d & 3) || d > NORM_THREADS * 4 * NORM_MAXV) return -30;
   return launch_pdl(add_rmsnorm_kernel, dim3(M), dim3(NORM_THREADS), st, pdl, h, partials, splits, split_stride, ids,
                     (const __nv_bfloat16*)embed, (const __nv_bfloat16*)w, (__nv_bfloat16*)xn, ldx, d, eps, plus_one,
-                    pdl);
+                    (__nv_bfloat16*)hb, ssq, pdl);
 }
 
 SMC_API int smc_rope_kv_write(const float* partials, int splits, long long split_stride, const int* positions,

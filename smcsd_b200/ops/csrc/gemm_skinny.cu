@@ -52,6 +52,17 @@ struct GemmParams {
   int* status;
   int pdl;              // 1: wait for the previous grid only before touching activations
   TpLink tp;
+  // RMSNorm folded into the GEMMs (norm weights are pre-multiplied into W):
+  //   consumer side: the activation operand is the raw bf16 residual stream; every output column (token) is scaled
+  //     by rstd = rsqrt(sum_p ssq_in[p, m] / norm_d + eps) in the epilogue;
+  //   producer side (residual epilogue): besides h += X W^T it writes the bf16 copy of the new rows and the
+  //     sum of squares of its 128 columns per token into ssq_out[n_tile, m], summed later in a fixed order.
+  const float* ssq_in;
+  int ssq_parts, ssq_ld, ssq_mstride;     // token of output row m is ssq column m * ssq_mstride
+  float norm_inv_d, norm_eps;
+  float* ssq_out;
+  __nv_bfloat16* hb_out;
+  int hb_ld;
 };
 
 template <int BN>
@@ -195,6 +206,20 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
   const int failed = __syncthreads_or(ok ? 0 : 1);
   tc_fence_after();
 
+  __shared__ float s_rstd[BN];
+  if (p.ssq_in != nullptr) {
+    for (int c = threadIdx.x; c < BN; c += blockDim.x) {
+      const int m = m_tile * BN + c;
+      float ss = 0.f;
+      if (m < p.M)
+        for (int q = 0; q < p.ssq_parts; ++q) ss += p.ssq_in[(size_t)q * p.ssq_ld + (size_t)m * p.ssq_mstride];
+      s_rstd[c] = rsqrtf(ss * p.norm_inv_d + p.norm_eps);
+    }
+  } else {
+    for (int c = threadIdx.x; c < BN; c += blockDim.x) s_rstd[c] = 1.f;
+  }
+  __syncthreads();
+
   if (!failed) {
     const int row_in_tile = warp * 32 + lane;
     const int n = n_tile * C::BM + row_in_tile;
@@ -221,8 +246,8 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
           for (int j = 0; j < 16; ++j) {
             const int m = m_base + c0 + j;
             if (m < p.M && ch * 2 < p.N) {
-              const float g = __uint_as_float(r[j]);
-              const float u = sbuf[row_in_tile * LD + c0 + j];
+              const float g = __uint_as_float(r[j]) * s_rstd[c0 + j];
+              const float u = sbuf[row_in_tile * LD + c0 + j] * s_rstd[c0 + j];
               out[(size_t)m * p.ldo + ch] = __float2bfloat16(g / (1.0f + __expf(-g)) * u);
             }
           }
@@ -252,10 +277,11 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
             const int m = m_base + c0 + j;
             if (m < p.M) {
               if constexpr (EPI == EPI_PARTIAL_F32) {
-                reinterpret_cast<float*>(p.out)[((size_t)split * p.M + m) * p.N + n] = __uint_as_float(r[j]);
+                reinterpret_cast<float*>(p.out)[((size_t)split * p.M + m) * p.N + n] =
+                    __uint_as_float(r[j]) * s_rstd[c0 + j];
               } else {
                 reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] =
-                    __float2bfloat16(__uint_as_float(r[j]));
+                    __float2bfloat16(__uint_as_float(r[j]) * s_rstd[c0 + j]);
               }
             }
           }
@@ -274,6 +300,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
     // ---- on-chip split-K reduction across the cluster (CTA rank == split index) --------------
     // Both cluster barriers are unconditional so that a CTA that gave up still releases its peers.
     __shared__ int sh_failed;
+    __shared__ float s_red[4][4];
     if (threadIdx.x == 0) sh_failed = failed;
     cluster_sync();
     const uint32_t S = (uint32_t)p.splits;
@@ -294,6 +321,9 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
       for (int c0 = split; c0 < BN && m_base + c0 < p.M; c0 += (int)S * UN) {
         float v[UN][8];
         float prev[UN];
+        float sq[UN];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) sq[u] = 0.f;
 #pragma unroll
         for (int u = 0; u < UN; ++u) {
           const int c = c0 + u * (int)S;
@@ -313,6 +343,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
             float acc = 0.f;
 #pragma unroll
             for (uint32_t s = 0; s < 8; ++s) acc += v[u][s];
+            acc *= s_rstd[c];
             if constexpr (EPI == EPI_RS_F32) {
               // reduce-scatter: the token row belongs to rank `owner`; store into its receive buffer
               const int m = m_base + c, owner = m / p.tp.rows_per_rank, ml = m - owner * p.tp.rows_per_rank;
@@ -320,8 +351,31 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
                            ((size_t)p.tp.rank * p.tp.rows_per_rank + ml) * p.ldo + n;
               *dst = acc;
             } else {
-              out[(size_t)(m_base + c) * p.ldo + n] = prev[u] + acc;
+              const float hv = prev[u] + acc;
+              out[(size_t)(m_base + c) * p.ldo + n] = hv;
+              if constexpr (EPI == EPI_RESID_F32) {
+                if (p.hb_out != nullptr) p.hb_out[(size_t)(m_base + c) * p.hb_ld + n] = __float2bfloat16(hv);
+                sq[u] = hv * hv;
+              }
             }
+          }
+        }
+        if constexpr (EPI == EPI_RESID_F32) {
+          if (p.ssq_out != nullptr) {
+            // sum of squares of this slab's 128 columns for each token this CTA owns (block reduction, fixed order)
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+              float v = warp_sum(sq[u]);
+              if (lane == 0) s_red[u][warp] = v;
+            }
+            __syncthreads();
+            if (threadIdx.x < UN) {
+              const int c = c0 + (int)threadIdx.x * (int)S;
+              if (c < BN && m_base + c < p.M)
+                p.ssq_out[(size_t)n_tile * p.ssq_ld + m_base + c] =
+                    s_red[threadIdx.x][0] + s_red[threadIdx.x][1] + s_red[threadIdx.x][2] + s_red[threadIdx.x][3];
+            }
+            __syncthreads();
           }
         }
       }
@@ -472,8 +526,13 @@ SMC_API int smc_gemm_cluster_splits(int N, int K, int M) {
 // thread-block cluster, so splits must be 1, 2, 4 or 8.
 // epi 0: out = fp32 [splits, M, N] partials; epi 1: out = bf16 [M, ldo] (splits must be 1);
 // epi 2: out = bf16 [M, ldo] holding SwiGLU(gate, up) for N/2 channels (splits must be 1, N % 128 == 0).
+struct NormLink {            // host-side description of the folded RMSNorm (all fields optional)
+  const float* ssq_in; int ssq_parts; int ssq_ld; int norm_d; float norm_eps; float* ssq_out; void* hb_out; int hb_ld;
+  int ssq_mstride;
+};
+
 static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo, int splits,
-                      int epi, int* status, int pdl, const smc::TpLink* tp, cudaStream_t stream) {
+                      int epi, int* status, int pdl, const smc::TpLink* tp, const NormLink* nl, cudaStream_t stream) {
   using namespace smc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) != 0 || (ldx % 8) != 0) return -20;       // row pitch must be a multiple of 16 bytes
@@ -489,6 +548,16 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
   p.splits = splits < 1 ? 1 : (splits > p.kblocks ? p.kblocks : splits);
   p.out = out; p.ldo = ldo; p.status = status; p.pdl = pdl;
   if (tp != nullptr) p.tp = *tp; else memset(&p.tp, 0, sizeof(p.tp));
+  p.ssq_mstride = 1;
+  p.ssq_in = nullptr; p.ssq_parts = 0; p.ssq_ld = 0; p.norm_inv_d = 0.f; p.norm_eps = 0.f; p.ssq_out = nullptr;
+  p.hb_out = nullptr; p.hb_ld = 0;
+  if (nl != nullptr) {
+    p.ssq_in = nl->ssq_in; p.ssq_parts = nl->ssq_parts; p.ssq_ld = nl->ssq_ld;
+    p.norm_inv_d = nl->norm_d > 0 ? 1.0f / (float)nl->norm_d : 0.f; p.norm_eps = nl->norm_eps;
+    p.ssq_out = nl->ssq_out; p.hb_out = (__nv_bfloat16*)nl->hb_out; p.hb_ld = nl->hb_ld;
+    p.ssq_mstride = nl->ssq_mstride > 0 ? nl->ssq_mstride : 1;
+    if (p.ssq_out != nullptr && epi != EPI_RESID_F32) return -25;
+  }
   CUtensorMap tmW, tmX;
   int rc = make_tmap(&tmW, W, N, K, K, 128);
   if (rc) return rc;
@@ -508,7 +577,7 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
 
 SMC_API int smc_gemm_skinny(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo,
                             int splits, int epi, int* status, int pdl, cudaStream_t stream) {
-  return gemm_entry(W, X, out, N, K, M, ldx, ldo, splits, epi, status, pdl, nullptr, stream);
+  return gemm_entry(W, X, out, N, K, M, ldx, ldo, splits, epi, status, pdl, nullptr, nullptr, stream);
 }
 
 // Tensor-parallel variant: `tp` describes the all-gather wait of the activation operand and / or the
@@ -517,7 +586,19 @@ SMC_API int smc_gemm_skinny(const void* W, const void* X, void* out, int N, int 
 SMC_API int smc_gemm_skinny_tp(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo,
                                int splits, int epi, int* status, int pdl, const smc::TpLink* tp,
                                cudaStream_t stream) {
-  return gemm_entry(W, X, out, N, K, M, ldx, ldo, splits, epi, status, pdl, tp, stream);
+  return gemm_entry(W, X, out, N, K, M, ldx, ldo, splits, epi, status, pdl, tp, nullptr, stream);
+}
+
+// GEMM with the RMSNorm folded in.  ssq_in [ssq_parts, ssq_ld] fp32: per-token partial sums of squares of the
+// activation rows (null: no scaling); outputs are scaled per token by rsqrt(sum / norm_d + eps).  With epi 4 and
+// ssq_out / hb_out given, the residual epilogue also emits the bf16 copy of the updated rows and their per-slab
+// sums of squares ssq_out[n_tile, m] for the next consumer.
+SMC_API int smc_gemm_skinny_norm(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo,
+                                 int splits, int epi, int* status, int pdl, const float* ssq_in, int ssq_parts,
+                                 int ssq_ld, int norm_d, float norm_eps, float* ssq_out, void* hb_out, int hb_ld,
+                                 int ssq_mstride, cudaStream_t stream) {
+  NormLink nl = {ssq_in, ssq_parts, ssq_ld, norm_d, norm_eps, ssq_out, hb_out, hb_ld, ssq_mstride};
+  return gemm_entry(W, X, out, N, K, M, ldx, ldo, splits, epi, status, pdl, nullptr, &nl, stream);
 }
 
 SMC_API int smc_tp_link_size() { return (int)sizeof(smc::TpLink); }

@@ -47,7 +47,9 @@ def _declare(L) -> None:
     L.smc_gemm_default_splits.argtypes = [i, i, i]
     L.smc_gemm_cluster_splits.argtypes = [i, i, i]
     L.smc_gemm_cluster_splits.restype = C.c_int
-    L.smc_add_rmsnorm.argtypes = [vp, vp, i, ll, vp, vp, vp, vp, i, i, i, f, i, i, vp]
+    L.smc_add_rmsnorm.argtypes = [vp, vp, i, ll, vp, vp, vp, vp, i, i, i, f, i, vp, vp, i, vp]
+    L.smc_gemm_skinny_norm.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, vp, i, vp, i, i, i, f, vp, vp, i, i, vp]
+    L.smc_gemm_skinny_norm.restype = C.c_int
     L.smc_rope_kv_write.argtypes = [vp, i, ll, vp, vp, vp, i, i, vp, vp, vp, i, i, i, i, i, vp, i, vp]
     L.smc_swiglu_partials.argtypes = [vp, i, ll, vp, i, i, i, i, i, vp]
     L.smc_attention_extend.argtypes = [vp, vp, vp, vp, i, i, vp, vp, vp, vp, vp, i, i, i, i, i, i, f, vp, i, vp]
@@ -110,14 +112,35 @@ def gemm_skinny(W: torch.Tensor, X: torch.Tensor, out: torch.Tensor, *, M: int, 
                                  _stream()), "smc_gemm_skinny")
 
 
+def gemm_skinny_norm(W: torch.Tensor, X: torch.Tensor, out: torch.Tensor, *, M: int, splits: int, epi: int, ldo: int,
+                     status: torch.Tensor, ssq_in: Optional[torch.Tensor] = None, ssq_parts: int = 0, norm_d: int = 0,
+                     norm_eps: float = 0.0, ssq_out: Optional[torch.Tensor] = None, hb_out: Optional[torch.Tensor] = None,
+                     ldx: Optional[int] = None, pdl: bool = False, ssq_ld: int = 0, ssq_mstride: int = 1) -> None:
+    """GEMM with the RMSNorm folded in: outputs scaled per token by rsqrt(sum_p ssq_in[p, m] / norm_d + eps); the
+    residual epilogue can emit the bf16 copy of the new rows (``hb_out``) and their sums of squares (``ssq_out``
+    [n_tiles, ld]) for the next consumer."""
+    N, K = W.shape
+    ldx = ldx if ldx is not None else X.stride(0)
+    if not ssq_ld:
+        ref = ssq_in if ssq_in is not None else ssq_out
+        ssq_ld = ref.stride(0) if ref is not None and ref.dim() == 2 else 0
+    _check(lib().smc_gemm_skinny_norm(_p(W), _p(X), _p(out), N, K, M, ldx, ldo, splits, epi, _p(status), int(pdl),
+                                      _p(ssq_in), ssq_parts, ssq_ld, norm_d, norm_eps, _p(ssq_out), _p(hb_out),
+                                      hb_out.stride(0) if hb_out is not None else 0, ssq_mstride, _stream()),
+           "smc_gemm_skinny")
+
+
 # ----------------------------------------------------------------------------- fused elementwise
 def add_rmsnorm(h: torch.Tensor, w: Optional[torch.Tensor], xn: Optional[torch.Tensor], *, M: int, d: int, eps: float,
                 partials: Optional[torch.Tensor] = None, splits: int = 0, split_stride: int = 0,
                 ids: Optional[torch.Tensor] = None, embed: Optional[torch.Tensor] = None, ldx: Optional[int] = None,
-                plus_one: bool = False, pdl: bool = False) -> None:
+                plus_one: bool = False, pdl: bool = False, hb: Optional[torch.Tensor] = None,
+                ssq: Optional[torch.Tensor] = None) -> None:
+    """h (+= partials | = embedding rows); optional outputs: normalised bf16 ``xn``, raw bf16 copy ``hb`` and the
+    per-row sum of squares ``ssq`` (for GEMMs that apply the norm in their epilogue)."""
     ldx = ldx if ldx is not None else (xn.stride(0) if xn is not None else d)
     _check(lib().smc_add_rmsnorm(_p(h), _p(partials), splits, split_stride, _p(ids), _p(embed), _p(w), _p(xn), ldx, M,
-                                 d, eps, int(plus_one), int(pdl), _stream()), "smc_add_rmsnorm")
+                                 d, eps, int(plus_one), _p(hb), _p(ssq), int(pdl), _stream()), "smc_add_rmsnorm")
 
 
 def rope_kv_write(partials: torch.Tensor, splits: int, split_stride: int, positions: torch.Tensor,

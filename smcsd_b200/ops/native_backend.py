@@ -57,6 +57,53 @@ class NativeLlama:
         if not self.fuse_swiglu:
             self.gu = torch.empty(max_tokens, 2 * self.ffn, dtype=f32, device=dev)
         self._splits_cache: Dict = {}
+        # RMSNorm folded into the GEMMs: consumers read the raw bf16 residual stream ``hb`` and scale by 1/rms in
+        # their epilogue; residual GEMMs emit ``hb`` and per-slab sums of squares.  Five launches per layer.
+        self.fold = self.fuse_swiglu and model.tp_size == 1 and _env_flag("SMC_FOLD_NORM", True)
+        if self.fold:
+            model.fold_norms()
+            self.hb = torch.empty(max_tokens, self.d, dtype=bf16, device=dev)
+            self.n_parts = (self.d + 127) // 128
+            self.ssq = torch.zeros(self.n_parts, max_tokens, dtype=f32, device=dev)
+
+    def _forward_folded(self, ids, positions, cache_locs, rows, prefix_lens, bs: int, E: int, two_pass: bool):
+        m, c, pdl = self.m, self.c, self.pdl
+        T = bs * E
+        K.add_rmsnorm(self.h, None, None, M=T, d=self.d, eps=c.rms_eps, ids=ids, embed=m.embed, hb=self.hb,
+                      ssq=self.ssq, pdl=pdl)
+        parts = 1
+        scale = self.D ** -0.5
+        ld = self.ssq.stride(0)
+        for li, L in enumerate(m.layers):
+            K.gemm_skinny_norm(L.wqkv, self.hb, self.qkv, M=T, splits=self._splits(self.nqkv, self.d, T),
+                               epi=K.EPI_STORE_F32, ldo=self.qkv.stride(0), status=self.status, ssq_in=self.ssq,
+                               ssq_parts=parts, norm_d=self.d, norm_eps=c.rms_eps, ssq_ld=ld, pdl=pdl)
+            q_in = None
+            if two_pass:
+                K.rope_kv_write(self.qkv, 1, 0, positions, cache_locs, m.rope, self.q, self.kv.k[li], self.kv.v[li],
+                                M=T, Hq=self.nq, Hkv=self.nkv, D=self.D, status=self.status, pdl=pdl)
+                q_in = self.q
+            K.attention_fused(self.qkv, positions, cache_locs, m.rope, self.kv.k[li], self.kv.v[li], self.bt, rows,
+                              prefix_lens, self.attn, self.part_acc, self.part_ml, bs=bs, E=E, Hq=self.nq,
+                              Hkv=self.nkv, D=self.D, KS=self.KS, scale=scale, status=self.status, pdl=pdl, q_in=q_in)
+            K.gemm_skinny_norm(L.wo, self.attn, self.h, M=T, splits=self._splits(self.d, self.nq * self.D, T),
+                               epi=K.EPI_RESID_F32, ldo=self.d, status=self.status, ssq_out=self.ssq, hb_out=self.hb,
+                               ssq_ld=ld, pdl=pdl)
+            parts = self.n_parts
+            K.gemm_skinny_norm(L.wgu, self.hb, self.act, M=T, splits=1, epi=K.EPI_SWIGLU_BF16,
+                               ldo=self.act.stride(0), status=self.status, ssq_in=self.ssq, ssq_parts=parts,
+                               norm_d=self.d, norm_eps=c.rms_eps, ssq_ld=ld, pdl=pdl)
+            K.gemm_skinny_norm(L.wdown, self.act, self.h, M=T, splits=self._splits(self.d, self.ffn, T),
+                               epi=K.EPI_RESID_F32, ldo=self.d, status=self.status, ssq_out=self.ssq, hb_out=self.hb,
+                               ssq_ld=ld, pdl=pdl)
+        return self.hb
+
+    def final_hidden(self, rows_idx: torch.Tensor) -> torch.Tensor:
+        """Post-final-norm hidden rows (bf16) for callers that project with PyTorch (x0 at prefill)."""
+        from ..models.layers import rmsnorm
+        if self.fold:
+            return rmsnorm(self.h[rows_idx], self.m.final_norm, self.c.rms_eps).to(torch.bfloat16)
+        return self.xn[rows_idx]
 
     def _splits(self, N: int, Kdim: int, M: int) -> int:
         key = (N, Kdim, M)
@@ -81,6 +128,8 @@ class NativeLlama:
         m, c, pdl = self.m, self.c, self.pdl
         T = bs * E
         assert T <= self.T
+        if self.fold:
+            return self._forward_folded(ids, positions, cache_locs, rows, prefix_lens, bs, E, two_pass)
         L0 = m.layers[0]
         K.add_rmsnorm(self.h, L0.ln1, self.xn, M=T, d=self.d, eps=c.rms_eps, ids=ids, embed=m.embed, pdl=pdl)
         n_layers = len(m.layers)
@@ -109,7 +158,14 @@ class NativeLlama:
         return self.xn
 
     def lm_head(self, rows: int, row_offset: int = 0, row_step: int = 1) -> torch.Tensor:
-        """fp32 logits [rows, V] of xn rows ``row_offset + i * row_step``."""
+        """fp32 logits [rows, V] of the final hidden rows ``row_offset + i * row_step``."""
+        if self.fold:
+            K.gemm_skinny_norm(self.m.lm_head, self.hb[row_offset:], self.logits, M=rows, splits=1,
+                               epi=K.EPI_STORE_F32, ldx=self.d * row_step, ldo=self.logits.stride(0),
+                               status=self.status, ssq_in=self.ssq[:, row_offset:], ssq_parts=self.n_parts,
+                               norm_d=self.d, norm_eps=self.c.rms_eps, ssq_ld=self.ssq.stride(0),
+                               ssq_mstride=row_step, pdl=self.pdl)
+            return self.logits
         X = self.xn[row_offset:]
         K.gemm_skinny(self.m.lm_head, X, self.logits, M=rows, splits=1, epi=K.EPI_STORE_F32,
                       ldx=self.d * row_step, ldo=self.logits.stride(0), status=self.status, pdl=self.pdl)
@@ -318,8 +374,7 @@ class NativeRunner:
         bs = sum(n_blocks)
         tgt.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True)
         last = torch.tensor(last_rows, dtype=torch.long, device=dev)
-        hid = tgt.xn[last]
-        logits = self.target.m.logits_torch(hid)
+        logits = self.target.m.logits_torch(tgt.final_hidden(last))
         from ..smc import math as smc_math
         x0, _, _ = smc_math.gumbel_sample(logits, self.T_target, self.alpha, generator=worker.gen_prefill)
         drf.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True)

@@ -131,7 +131,6 @@ def test_native_prefill_matches_torch_prefill():
     torch.cuda.synchronize()
     assert r.check_status() == 0
     kt, vt, kd = s.kv_t.k.clone(), s.kv_t.v.clone(), s.kv_d.k.clone()
-    hid_native = r._pf_target.xn.clone()
     s.kv_t.k.zero_(); s.kv_t.v.zero_(); s.kv_d.k.zero_()
     native, s.worker.native = s.worker.native, None
     s.worker.gen_prefill.manual_seed(int(s.args.random_seed) * 7919 + 17)

@@ -410,3 +410,52 @@ def test_attention_fused(bs, E, Hq, Hkv, D, ctx, KS, rd, extras):
     assert (vp[locs.long()].float() - vp_ref[locs.long()].float()).abs().max().item() < 1e-6
     err = (out.float() - ref).abs().max().item()
     assert err < 3e-2 * max(1.0, ref.abs().max().item()), err
+
+
+# ------------------------------------------------------------------------------- RMSNorm folded into the GEMMs
+@pytest.mark.parametrize("d,ffn,M", [(2048, 8192, 8), (4096, 14336, 72), (512, 1536, 20)])
+def test_gemm_with_folded_rmsnorm(d, ffn, M):
+    """Producer: h += X W^T also emits bf16(h) and per-slab sums of squares.  Consumer: GEMM on the raw bf16 rows,
+    scaled per token by 1/rms in the epilogue == GEMM on the normalised rows."""
+    K = _K()
+    from smcsd_b200.models.llama import interleave_gate_up
+    torch.manual_seed(21)
+    dev = "cuda"
+    st = _status()
+    Wd = (torch.randn(d, ffn, device=dev) * 0.03).bfloat16()
+    act = torch.randn(M, ffn, device=dev).bfloat16()
+    h0 = torch.randn(M, d, device=dev)
+    h = h0.clone()
+    parts = (d + 127) // 128
+    ssq = torch.zeros(parts, 128, device=dev)          # leading dimension 128 > M on purpose
+    hb = torch.zeros(M, d, device=dev, dtype=torch.bfloat16)
+    s = K.gemm_cluster_splits(d, ffn, M)
+    K.gemm_skinny_norm(Wd, act, h, M=M, splits=s, epi=K.EPI_RESID_F32, ldo=d, status=st, ssq_out=ssq, hb_out=hb)
+    torch.cuda.synchronize()
+    h_ref = h0 + act.float() @ Wd.float().t()
+    assert (h - h_ref).abs().max().item() < 2e-2 * max(1.0, h_ref.abs().max().item())
+    assert torch.equal(hb, h.bfloat16())
+    ssq_ref = (h.float() ** 2).view(M, parts, -1).sum(-1).t()
+    assert torch.allclose(ssq[:, :M], ssq_ref, rtol=1e-4, atol=1e-3)
+    # consumer with SwiGLU epilogue
+    Wg = (torch.randn(ffn, d, device=dev) * 0.03).bfloat16()
+    Wu = (torch.randn(ffn, d, device=dev) * 0.03).bfloat16()
+    Wgu = interleave_gate_up(Wg, Wu, 64)
+    out = torch.zeros(M, ffn, device=dev, dtype=torch.bfloat16)
+    K.gemm_skinny_norm(Wgu, hb, out, M=M, splits=1, epi=K.EPI_SWIGLU_BF16, ldo=ffn, status=st, ssq_in=ssq,
+                       ssq_parts=parts, norm_d=d, norm_eps=1e-5)
+    xn = hb.float() * torch.rsqrt((h.float() ** 2).mean(-1, keepdim=True) + 1e-5)
+    ref = torch.nn.functional.silu(xn @ Wg.float().t()) * (xn @ Wu.float().t())
+    torch.cuda.synchronize()
+    assert (out.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
+    # consumer with the clustered fp32 store and a strided row selection (every second row from row 1)
+    Wq = (torch.randn(1024, d, device=dev) * 0.03).bfloat16()
+    rows = (M - 1 + 1) // 2
+    q = torch.zeros(rows, 1024, device=dev)
+    K.gemm_skinny_norm(Wq, hb[1:], q, M=rows, splits=K.gemm_cluster_splits(1024, d, rows), epi=K.EPI_STORE_F32,
+                       ldo=1024, status=st, ssq_in=ssq[:, 1:], ssq_parts=parts, norm_d=d, norm_eps=1e-5,
+                       ldx=2 * d, ssq_ld=ssq.stride(0), ssq_mstride=2)
+    torch.cuda.synchronize()
+    ref = xn[1::2][:rows] @ Wq.float().t()
+    assert int(st) == 0
+    assert (q - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
