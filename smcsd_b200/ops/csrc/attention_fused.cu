@@ -187,8 +187,54 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   }
   const int prefix = p.prefix_lens[b];
   const size_t kv_row = (size_t)p.Hkv * D;
-
   const bool pool_only = p.q_in != nullptr;
+  const int g = lane >> 2, t = lane & 3;
+
+  // ---- key range of this CTA and the first K/V fetch (runs under the new-token work below) -----------
+  const int n_keys = pool_only ? prefix + p.E : prefix;     // keys served from the paged cache
+  int per = (n_keys + p.KS - 1) / p.KS;
+  per = (per + TK - 1) / TK * TK;
+  const int kb = ks * per, ke = min(n_keys, kb + per);
+  const int* bt = p.block_table + (size_t)p.rows[b] * p.bt_stride;
+  const int gsize = 32 * n_mt, gt = mt * 32 + lane;   // thread index inside this key-way's group
+  __nv_bfloat16* my_tiles = tiles + (size_t)kw * 4 * TILE;
+  constexpr int CPR = D / 8;
+  __shared__ int s_pos[16];
+  auto load_pages = [&](int r0, int r1) {
+    for (int i = threadIdx.x; i < r1 - r0; i += blockDim.x) {
+      int page = bt[r0 + i];
+      if (page < 0 || page > p.n_pages) { atomicOr(p.status, SMC_ERR_BOUNDS); page = 0; }
+      pg[i] = page;
+    }
+  };
+  auto issue = [&](int r0, int r1, int tile, int stage) {
+    __nv_bfloat16* Kt = my_tiles + (size_t)stage * 2 * TILE;
+    __nv_bfloat16* Vt = Kt + TILE;
+    const int k0 = tile * TK;
+    for (int c = gt; c < TK * CPR; c += gsize) {
+      const int key = c / CPR, col = c % CPR;
+      const int page = (r0 + k0 + key < r1) ? pg[k0 + key] : 0;
+      const size_t off = (size_t)page * kv_row + (size_t)kvh * D + col * 8;
+      cp_async16(Kt + key * LD + col * 8, p.k_pool + off);
+      cp_async16(Vt + key * LD + col * 8, p.v_pool + off);
+    }
+    cp_async_commit();
+  };
+  if (threadIdx.x < 16) {
+    int pos = 0;
+    if ((int)threadIdx.x < p.E) {
+      pos = p.positions[b * p.E + threadIdx.x];
+      if (pos < 0 || pos >= p.max_pos) {
+        atomicOr(p.status, SMC_ERR_BOUNDS);
+        pos = pos < 0 ? 0 : p.max_pos - 1;
+      }
+    }
+    s_pos[threadIdx.x] = pos;
+  }
+  if (kb < ke) load_pages(kb, min(ke, kb + RANGE));
+  __syncthreads();
+  if (kb < ke && kw < (min(ke, kb + RANGE) - kb + TK - 1) / TK) issue(kb, min(ke, kb + RANGE), kw, 0);
+
   if (pool_only) {
     // queries were rotated by an earlier kernel; stage them (zero padded) and skip the new-token K/V work
     for (int idx = threadIdx.x; idx < Rpad * (D / 8); idx += blockDim.x) {
@@ -204,85 +250,98 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   } else {
   // ---- phase 0: q / k / v of the new tokens (norm, rope, bf16) ------------------------------------
     const int half = p.rd >> 1;
-    __shared__ int s_pos[16];
-    if (threadIdx.x < 16) {
-      int pos = 0;
-      if ((int)threadIdx.x < p.E) {
-        pos = p.positions[b * p.E + threadIdx.x];
-        if (pos < 0 || pos >= p.max_pos) {
-          atomicOr(p.status, SMC_ERR_BOUNDS);
-          pos = pos < 0 ? 0 : p.max_pos - 1;
-        }
-      }
-      s_pos[threadIdx.x] = pos;
-    }
-    __syncthreads();
-    // rows: [0, Rpad) queries, [Rpad, Rpad+16) keys, [Rpad+16, Rpad+32) values; rows past R / E are zero
-    auto row_info = [&](int item, __nv_bfloat16*& dst, const float*& src, const __nv_bfloat16*& nw, int& pos,
-                        bool& rope) {
-      src = nullptr; nw = nullptr; pos = 0; rope = false;
-      if (item < Rpad) {
-        dst = Qs + (size_t)item * LD;
-        if (item < R) {
-          const int e = item / G, gq = item % G;
-          src = p.qkv + (size_t)(b * p.E + e) * p.ld_qkv + p.q_off + (size_t)(kvh * G + gq) * D;
-          pos = s_pos[e]; rope = true; nw = p.qn_w;
-        }
+    // real rows: [0, R) queries, [R, R+E) keys, [R+E, R+2E) values
+    auto real_row = [&](int j, __nv_bfloat16*& dst, const float*& src, int& pos) {
+      if (j < R) {
+        const int e = j / G, gq = j % G;
+        dst = Qs + (size_t)j * LD;
+        src = p.qkv + (size_t)(b * p.E + e) * p.ld_qkv + p.q_off + (size_t)(kvh * G + gq) * D;
+        pos = s_pos[e];
       } else {
-        const int e = (item - Rpad) & 15;
-        const bool is_k = item < Rpad + 16;
+        const bool is_k = j < R + p.E;
+        const int e = is_k ? j - R : j - R - p.E;
         dst = (is_k ? Kn : Vn) + (size_t)e * LD;
-        if (e < p.E) {
-          src = p.qkv + (size_t)(b * p.E + e) * p.ld_qkv + (is_k ? p.k_off : p.v_off) + (size_t)kvh * D;
-          pos = s_pos[e]; rope = is_k; nw = is_k ? p.kn_w : nullptr;
-        }
+        src = p.qkv + (size_t)(b * p.E + e) * p.ld_qkv + (is_k ? p.k_off : p.v_off) + (size_t)kvh * D;
+        pos = s_pos[e];
       }
     };
-    auto emit_pair = [&](__nv_bfloat16* dst, const float* src, const __nv_bfloat16* nw, float rstd, int pos, bool rope,
-                         int i) {
-      int i1, i2;
-      bool rot;
-      if (i < half) { i1 = i; i2 = i + half; rot = rope; }
-      else { const int j = i - half; i1 = p.rd + 2 * j; i2 = i1 + 1; rot = false; }
-      float x1 = src[i1], x2 = src[i2];
-      if (nw != nullptr) {
-        const float add = p.norm_plus_one ? 1.f : 0.f;
-        x1 *= rstd * (__bfloat162float(nw[i1]) + add);
-        x2 *= rstd * (__bfloat162float(nw[i2]) + add);
-      }
-      if (rot) {
+    auto store4 = [](__nv_bfloat16* dst, float4 v) {
+      uint2 o;
+      o.x = pack_bf16(v.x, v.y);
+      o.y = pack_bf16(v.z, v.w);
+      *reinterpret_cast<uint2*>(dst) = o;
+    };
+    // zero the padding rows
+    for (int idx = threadIdx.x; idx < (Rpad - R) * (D / 8); idx += blockDim.x)
+      *reinterpret_cast<uint4*>(Qs + (size_t)(R + idx / (D / 8)) * LD + (idx % (D / 8)) * 8) = make_uint4(0u, 0u, 0u, 0u);
+    for (int idx = threadIdx.x; idx < 2 * (16 - p.E) * (D / 8); idx += blockDim.x) {
+      const int rr = idx / (D / 8), c = idx % (D / 8);
+      __nv_bfloat16* base = rr < 16 - p.E ? Kn + (size_t)(p.E + rr) * LD : Vn + (size_t)(p.E + rr - (16 - p.E)) * LD;
+      *reinterpret_cast<uint4*>(base + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (p.qn_w == nullptr && p.kn_w == nullptr && (half & 3) == 0) {
+      // no per-head norm: float4-wide, fully independent work items (few loop trips, all loads in flight)
+      const int hq = half >> 2;
+      for (int idx = threadIdx.x; idx < (R + p.E) * hq; idx += blockDim.x) {       // rotated part of q and k rows
+        const int j = idx / hq, i4 = (idx % hq) * 4;
+        __nv_bfloat16* dst; const float* src; int pos;
+        real_row(j, dst, src, pos);
         const float* cs = p.rope + (size_t)pos * p.rd;
-        const float c = cs[i], sn = cs[half + i];
-        const float y1 = x1 * c - x2 * sn, y2 = x2 * c + x1 * sn;
-        x1 = y1; x2 = y2;
+        const float4 a = *reinterpret_cast<const float4*>(src + i4);
+        const float4 bb = *reinterpret_cast<const float4*>(src + half + i4);
+        const float4 c = *reinterpret_cast<const float4*>(cs + i4);
+        const float4 sn = *reinterpret_cast<const float4*>(cs + half + i4);
+        store4(dst + i4, make_float4(a.x * c.x - bb.x * sn.x, a.y * c.y - bb.y * sn.y, a.z * c.z - bb.z * sn.z,
+                                     a.w * c.w - bb.w * sn.w));
+        store4(dst + half + i4, make_float4(bb.x * c.x + a.x * sn.x, bb.y * c.y + a.y * sn.y, bb.z * c.z + a.z * sn.z,
+                                            bb.w * c.w + a.w * sn.w));
       }
-      dst[i1] = __float2bfloat16(x1);
-      dst[i2] = __float2bfloat16(x2);
-    };
-    if (p.qn_w == nullptr && p.kn_w == nullptr) {
-      // no per-head norm: every (row, pair) is independent, so spread them over all threads
-      for (int idx = threadIdx.x; idx < (Rpad + 32) * (D / 2); idx += blockDim.x) {
-        const int item = idx / (D / 2), i = idx % (D / 2);
-        __nv_bfloat16* dst; const float* src; const __nv_bfloat16* nw; int pos; bool rope;
-        row_info(item, dst, src, nw, pos, rope);
-        if (src == nullptr) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
-        else emit_pair(dst, src, nullptr, 1.f, pos, rope, i);
+      const int pq = (D - p.rd) >> 2;                                               // pass-through dims of q and k rows
+      for (int idx = threadIdx.x; idx < (R + p.E) * pq; idx += blockDim.x) {
+        const int j = idx / pq, i4 = p.rd + (idx % pq) * 4;
+        __nv_bfloat16* dst; const float* src; int pos;
+        real_row(j, dst, src, pos);
+        store4(dst + i4, *reinterpret_cast<const float4*>(src + i4));
+      }
+      for (int idx = threadIdx.x; idx < p.E * (D / 4); idx += blockDim.x) {         // value rows
+        const int j = R + p.E + idx / (D / 4), i4 = (idx % (D / 4)) * 4;
+        __nv_bfloat16* dst; const float* src; int pos;
+        real_row(j, dst, src, pos);
+        store4(dst + i4, *reinterpret_cast<const float4*>(src + i4));
       }
     } else {
-      for (int item = warp; item < Rpad + 32; item += nwarps) {
-        __nv_bfloat16* dst; const float* src; const __nv_bfloat16* nw; int pos; bool rope;
-        row_info(item, dst, src, nw, pos, rope);
-        if (src == nullptr) {
-          for (int i = lane; i < D / 2; i += 32) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
-          continue;
-        }
+      // per-head RMSNorm (hybrid attention layers): one warp per row
+      for (int j = warp; j < R + 2 * p.E; j += nwarps) {
+        __nv_bfloat16* dst; const float* src; int pos;
+        real_row(j, dst, src, pos);
+        const bool is_v = j >= R + p.E;
+        const __nv_bfloat16* nw = is_v ? nullptr : (j < R ? p.qn_w : p.kn_w);
         float rstd = 1.f;
         if (nw != nullptr) {
           float ss = 0.f;
           for (int i = lane; i < D; i += 32) ss += src[i] * src[i];
           rstd = rsqrtf(warp_sum(ss) / (float)D + p.norm_eps);
         }
-        for (int i = lane; i < D / 2; i += 32) emit_pair(dst, src, nw, rstd, pos, rope, i);
+        const float* cs = p.rope + (size_t)pos * p.rd;
+        const float add = p.norm_plus_one ? 1.f : 0.f;
+        for (int i = lane; i < D / 2; i += 32) {
+          int i1, i2;
+          bool rot;
+          if (i < half) { i1 = i; i2 = i + half; rot = !is_v; }
+          else { const int jj = i - half; i1 = p.rd + 2 * jj; i2 = i1 + 1; rot = false; }
+          float x1 = src[i1], x2 = src[i2];
+          if (nw != nullptr) {
+            x1 *= rstd * (__bfloat162float(nw[i1]) + add);
+            x2 *= rstd * (__bfloat162float(nw[i2]) + add);
+          }
+          if (rot) {
+            const float c = cs[i], sn = cs[half + i];
+            const float y1 = x1 * c - x2 * sn, y2 = x2 * c + x1 * sn;
+            x1 = y1; x2 = y2;
+          }
+          dst[i1] = __float2bfloat16(x1);
+          dst[i2] = __float2bfloat16(x2);
+        }
       }
     }
     __syncthreads();
@@ -302,7 +361,6 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   }
 
   // ---- phase 1: query fragments -----------------------------------------------------------------
-  const int g = lane >> 2, t = lane & 3;
   const __nv_bfloat16* Qs_mt = Qs + (size_t)mt * 16 * LD;
   uint32_t qa[Q_REGS ? D / 16 : 1][4];
   if constexpr (Q_REGS) {
@@ -321,42 +379,19 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   for (int nt = 0; nt < D / 8; ++nt) st.o[nt][0] = st.o[nt][1] = st.o[nt][2] = st.o[nt][3] = 0.f;
 
   // ---- phase 2: cached prefix, streamed in 32-key tiles -------------------------------------------
-  const int n_keys = pool_only ? prefix + p.E : prefix;     // keys served from the paged cache
-  int per = (n_keys + p.KS - 1) / p.KS;
-  per = (per + TK - 1) / TK * TK;
-  const int kb = ks * per, ke = min(n_keys, kb + per);
-  const int* bt = p.block_table + (size_t)p.rows[b] * p.bt_stride;
-  const int gsize = 32 * n_mt, gt = mt * 32 + lane;   // thread index inside this key-way's group
-  __nv_bfloat16* my_tiles = tiles + (size_t)kw * 4 * TILE;
-  constexpr int CPR = D / 8;
   for (int r0 = kb; r0 < ke; r0 += RANGE) {
     const int r1 = min(ke, r0 + RANGE);
-    __syncthreads();
-    for (int i = threadIdx.x; i < r1 - r0; i += blockDim.x) {
-      int page = bt[r0 + i];
-      if (page < 0 || page > p.n_pages) { atomicOr(p.status, SMC_ERR_BOUNDS); page = 0; }
-      pg[i] = page;
-    }
-    __syncthreads();
     const int ntiles = (r1 - r0 + TK - 1) / TK;
-    auto issue = [&](int tile, int stage) {
-      __nv_bfloat16* Kt = my_tiles + (size_t)stage * 2 * TILE;
-      __nv_bfloat16* Vt = Kt + TILE;
-      const int k0 = tile * TK;
-      for (int c = gt; c < TK * CPR; c += gsize) {
-        const int key = c / CPR, col = c % CPR;
-        const int page = (r0 + k0 + key < r1) ? pg[k0 + key] : 0;
-        const size_t off = (size_t)page * kv_row + (size_t)kvh * D + col * 8;
-        cp_async16(Kt + key * LD + col * 8, p.k_pool + off);
-        cp_async16(Vt + key * LD + col * 8, p.v_pool + off);
-      }
-      cp_async_commit();
-    };
+    if (r0 != kb) {                       // the first range was staged (and its first tiles requested) above
+      __syncthreads();
+      load_pages(r0, r1);
+      __syncthreads();
+      if (kw < ntiles) issue(r0, r1, kw, 0);
+    }
     int it = 0;
-    if (kw < ntiles) issue(kw, 0);
     for (int tile = kw; tile < ntiles; tile += n_kw, ++it) {
       const int stage = it & 1;
-      if (tile + n_kw < ntiles) { issue(tile + n_kw, stage ^ 1); cp_async_wait<1>(); }
+      if (tile + n_kw < ntiles) { issue(r0, r1, tile + n_kw, stage ^ 1); cp_async_wait<1>(); }
       else cp_async_wait<0>();
       group_barrier(1 + kw, gsize);
       const int nvalid = min(TK, r1 - r0 - tile * TK);
@@ -500,9 +535,9 @@ SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, 
   const int G = Hq / Hkv, R = E * G;
   const int n_mt = (R + 15) / 16;
   if (n_mt > 8) return -71;
-  int n_kw = 8 / n_mt;
-  if (n_kw > 4) n_kw = 4;
+  int n_kw = 8 / n_mt;                   // key-ways: as many as fit in 8 warps and ~200 KB of shared memory
   if (n_kw < 1) n_kw = 1;
+  while (n_kw > 1 && fused_smem_bytes(D, n_mt, n_kw) > 200 * 1024) --n_kw;
   FusedAttnParams p;
   p.qkv = qkv; p.q_in = (const __nv_bfloat16*)q_in; p.ld_qkv = ld_qkv; p.q_off = q_off; p.gate_off = gate_off; p.k_off = k_off; p.v_off = v_off;
   p.positions = positions; p.cache_locs = cache_locs; p.rope = rope; p.rd = rd; p.max_pos = max_pos;
