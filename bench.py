@@ -48,9 +48,10 @@ def main() -> int:
     ap.add_argument("--draft", default="llama-3.2-1b")
     ap.add_argument("-N", "--n-particles", type=int, default=8)
     ap.add_argument("-g", "--gamma", type=int, default=8)
-    ap.add_argument("--prompt-len", type=int, default=0, help="fixed prompt length (0 = log-normal, median 200)")
+    ap.add_argument("--prompt-len", type=int, default=256,
+                    help="prompt length in tokens (the published headline uses 256; 0 = log-normal, median 200)")
     ap.add_argument("--e2e-requests", type=int, default=2)
-    ap.add_argument("--e2e-new-tokens", type=int, default=512)
+    ap.add_argument("--e2e-new-tokens", type=int, default=1024, help="the published headline generates 1024")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     args = ap.parse_args()
@@ -81,7 +82,8 @@ def main() -> int:
     new_tokens = max(512, need_tokens)
     eng = SMCEngine(f"preset:{args.target}", f"preset:{args.draft}", n_particles=args.n_particles, gamma=args.gamma,
                     draft_temperature=0.7, target_temperature=0.7, resample_threshold=0.5, max_running_requests=1,
-                    base_gpu_id=local, context_length=4096 + new_tokens, random_seed=rank,
+                    base_gpu_id=local, context_length=max(4096, args.prompt_len) + max(new_tokens, args.e2e_new_tokens) + 4 * G,
+                    random_seed=rank,
                     backend="native" if args.impl == "native" else "torch", in_process=True,
                     cycle_graph=not args.no_graph, mem_fraction_static=0.6)
     sched = eng._sched
@@ -92,6 +94,8 @@ def main() -> int:
     # ---- device-timed region: K decode cycles of one live request ------------------------------
     sched.add_request(GenerateRequest("bench", prompt, SamplingParams(max_new_tokens=new_tokens, ignore_eos=True)))
     sched.step()                      # prefill + fan-out
+    if not sched.running:
+        raise SystemExit(f"the benchmark request was not admitted: {[getattr(o, 'error', None) for o in sched.outbox]}")
     for _ in range(warm):
         sched.step()
     torch.cuda.synchronize()
@@ -127,7 +131,7 @@ def main() -> int:
     e2e = None
     if not args.no_e2e:
         n_req = args.e2e_requests
-        lens2 = lognormal_lengths(n_req, seed=2000 + rank)
+        lens2 = [args.prompt_len] * n_req if args.prompt_len else lognormal_lengths(n_req, seed=2000 + rank)
         prompts = random_prompts(lens2, vocab, seed=77 + rank)
         sp = {"max_new_tokens": args.e2e_new_tokens, "ignore_eos": True}
         eng.generate(input_ids=prompts[0][:16], sampling_params={"max_new_tokens": 2 * G, "ignore_eos": True})

@@ -37,9 +37,7 @@ struct FusedAttnParams {
   const int* rows;           // [bs]
   const int* prefix_lens;    // [bs]
   __nv_bfloat16* out;        // [T, Hq * D]
-  float* part_acc;           // [T * Hq, KS, D]   (KS > 1 only)
-  float* part_ml;            // [T * Hq, KS, 2]
-  int E, Hq, Hkv, KS, n_mt, n_kw;
+  int E, Hq, Hkv, KS, n_mt, n_kw, stg;    // stg: stages of each key-way's K/V tile ring (2..6)
   float scale;
   int* status;
   int pdl;
@@ -54,6 +52,16 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// wait until at most `pending` of this thread's copy groups are still in flight (pending in 0..4)
+__device__ __forceinline__ void cp_async_wait_dyn(int pending) {
+  switch (pending) {
+    case 0: cp_async_wait<0>(); break;
+    case 1: cp_async_wait<1>(); break;
+    case 2: cp_async_wait<2>(); break;
+    case 3: cp_async_wait<3>(); break;
+    default: cp_async_wait<4>(); break;
+  }
+}
 __device__ __forceinline__ void group_barrier(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
@@ -174,7 +182,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   __nv_bfloat16* Kn = Qs + (size_t)Rpad * LD;                                 // [16][LD]
   __nv_bfloat16* Vn = Kn + 16 * LD;                                           // [16][LD]
   int* pg = reinterpret_cast<int*>(Vn + 16 * LD);                             // [RANGE]
-  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(pg + RANGE);        // [n_kw][2 stages][K|V][TK][LD]
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(pg + RANGE);        // [n_kw][stg stages][K|V][TK][LD]
   constexpr int TILE = TK * LD;
 
   const int b = blockIdx.x / p.Hkv, kvh = blockIdx.x % p.Hkv, ks = blockIdx.y;
@@ -197,7 +205,8 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   const int kb = ks * per, ke = min(n_keys, kb + per);
   const int* bt = p.block_table + (size_t)p.rows[b] * p.bt_stride;
   const int gsize = 32 * n_mt, gt = mt * 32 + lane;   // thread index inside this key-way's group
-  __nv_bfloat16* my_tiles = tiles + (size_t)kw * 4 * TILE;
+  const int stg = p.stg;
+  __nv_bfloat16* my_tiles = tiles + (size_t)kw * stg * 2 * TILE;
   constexpr int CPR = D / 8;
   __shared__ int s_pos[16];
   auto load_pages = [&](int r0, int r1) {
@@ -218,7 +227,16 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       cp_async16(Kt + key * LD + col * 8, p.k_pool + off);
       cp_async16(Vt + key * LD + col * 8, p.v_pool + off);
     }
-    cp_async_commit();
+  };
+  // Ring of `stg` tiles per key-way: the prologue requests the first stg-1 tiles of a range, then every
+  // iteration waits for its tile, refills the stage consumed one iteration earlier and computes.  One copy group
+  // is committed per slot whether or not it holds a tile, so the group arithmetic stays uniform.
+  auto prologue = [&](int r0, int r1) {
+    const int nt_r = (r1 - r0 + TK - 1) / TK;
+    for (int j = 0; j < stg - 1; ++j) {
+      if (kw + j * n_kw < nt_r) issue(r0, r1, kw + j * n_kw, j);
+      cp_async_commit();
+    }
   };
   if (threadIdx.x < 16) {
     int pos = 0;
@@ -233,7 +251,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   }
   if (kb < ke) load_pages(kb, min(ke, kb + RANGE));
   __syncthreads();
-  if (kb < ke && kw < (min(ke, kb + RANGE) - kb + TK - 1) / TK) issue(kb, min(ke, kb + RANGE), kw, 0);
+  if (kb < ke) prologue(kb, min(ke, kb + RANGE));
 
   if (pool_only) {
     // queries were rotated by an earlier kernel; stage them (zero padded) and skip the new-token K/V work
@@ -383,25 +401,27 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
     const int r1 = min(ke, r0 + RANGE);
     const int ntiles = (r1 - r0 + TK - 1) / TK;
     if (r0 != kb) {                       // the first range was staged (and its first tiles requested) above
+      cp_async_wait<0>();
       __syncthreads();
       load_pages(r0, r1);
       __syncthreads();
-      if (kw < ntiles) issue(r0, r1, kw, 0);
+      prologue(r0, r1);
     }
-    int it = 0;
-    for (int tile = kw; tile < ntiles; tile += n_kw, ++it) {
-      const int stage = it & 1;
-      if (tile + n_kw < ntiles) { issue(r0, r1, tile + n_kw, stage ^ 1); cp_async_wait<1>(); }
-      else cp_async_wait<0>();
-      group_barrier(1 + kw, gsize);
+    int j = 0;
+    for (int tile = kw; tile < ntiles; tile += n_kw, ++j) {
+      cp_async_wait_dyn(stg - 2);         // tile j of this key-way has landed
+      group_barrier(1 + kw, gsize);       // ... for every thread of the group, and tile j-1 is fully consumed
+      const int jn = j + stg - 1;
+      if (kw + jn * n_kw < ntiles) issue(r0, r1, kw + jn * n_kw, jn % stg);
+      cp_async_commit();
       const int nvalid = min(TK, r1 - r0 - tile * TK);
-      const __nv_bfloat16* Kt = my_tiles + (size_t)stage * 2 * TILE;
+      const __nv_bfloat16* Kt = my_tiles + (size_t)(j % stg) * 2 * TILE;
       const int key0 = r0 + tile * TK;
       process_tile<D, TK / 8, Q_REGS>(Kt, Kt + TILE, qa, Qs_mt, p.scale, st, nvalid, prefix + e_row0 - key0,
                                       prefix + e_row1 - key0);
-      group_barrier(1 + kw, gsize);
     }
   }
+  cp_async_wait<0>();
   // ---- phase 3: the new tokens, causally masked (key-way 0 of the last split) ----------------------
   if (ks == p.KS - 1 && kw == 0 && !pool_only) {
     process_tile<D, 2, Q_REGS>(Kn, Vn, qa, Qs_mt, p.scale, st, p.E, e_row0, e_row1);
@@ -446,83 +466,116 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
         st.o[nt][2] = st.o[nt][2] * a1 + x1.x * b1; st.o[nt][3] = st.o[nt][3] * a1 + x1.y * b1;
       }
     }
+  }
+  // ---- phase 5: merge the key splits across the cluster (CTA rank == split index), rank 0 writes ------
+  if (p.KS > 1) {
+    __syncthreads();                       // the key-way slots above have been consumed
+    if (kw == 0 && ks > 0) {
+      float* slot = marea + (size_t)mt * slot_floats;
+#pragma unroll
+      for (int nt = 0; nt < D / 8; ++nt) {
+        *reinterpret_cast<float2*>(slot + g * D + nt * 8 + 2 * t) = make_float2(st.o[nt][0], st.o[nt][1]);
+        *reinterpret_cast<float2*>(slot + (g + 8) * D + nt * 8 + 2 * t) = make_float2(st.o[nt][2], st.o[nt][3]);
+      }
+      if (t == 0) {
+        slot[16 * D + g] = st.m0; slot[16 * D + 8 + g] = st.m1;
+        slot[16 * D + 16 + g] = st.l0; slot[16 * D + 24 + g] = st.l1;
+      }
+    }
+    cluster_sync();
+    if (kw == 0 && ks == 0) {
+      const uint32_t local = smem_u32(marea + (size_t)mt * slot_floats);
+      for (int r2 = 1; r2 < p.KS; ++r2) {
+        const uint32_t rem = dsmem_map(local, (uint32_t)r2);
+        const float m0b = ld_dsmem_f32_at(rem + (16 * D + g) * 4), m1b = ld_dsmem_f32_at(rem + (16 * D + 8 + g) * 4);
+        const float l0b = ld_dsmem_f32_at(rem + (16 * D + 16 + g) * 4), l1b = ld_dsmem_f32_at(rem + (16 * D + 24 + g) * 4);
+        const float M0 = fmaxf(st.m0, m0b), M1 = fmaxf(st.m1, m1b);
+        const float a0 = M0 == -INFINITY ? 1.f : __expf(st.m0 - M0), b0 = M0 == -INFINITY ? 0.f : __expf(m0b - M0);
+        const float a1 = M1 == -INFINITY ? 1.f : __expf(st.m1 - M1), b1 = M1 == -INFINITY ? 0.f : __expf(m1b - M1);
+        st.l0 = st.l0 * a0 + l0b * b0; st.l1 = st.l1 * a1 + l1b * b1;
+        st.m0 = M0; st.m1 = M1;
+#pragma unroll
+        for (int n0 = 0; n0 < D / 8; n0 += 8) {      // batches of remote loads first, then the arithmetic
+          float2 x0[8], x1[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            x0[i] = ld_dsmem_f32x2_at(rem + (g * D + (n0 + i) * 8 + 2 * t) * 4);
+            x1[i] = ld_dsmem_f32x2_at(rem + ((g + 8) * D + (n0 + i) * 8 + 2 * t) * 4);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int nt = n0 + i;
+            st.o[nt][0] = st.o[nt][0] * a0 + x0[i].x * b0; st.o[nt][1] = st.o[nt][1] * a0 + x0[i].y * b0;
+            st.o[nt][2] = st.o[nt][2] * a1 + x1[i].x * b1; st.o[nt][3] = st.o[nt][3] * a1 + x1[i].y * b1;
+          }
+        }
+      }
+    }
+  }
+  if (kw == 0 && ks == 0) {
 #pragma unroll
     for (int hrow = 0; hrow < 2; ++hrow) {
       const int r = mt * 16 + g + 8 * hrow;
       if (r >= R) continue;
       const int e = r / G, gq = r % G, tkn = b * p.E + e, head = kvh * G + gq;
-      const float l = hrow ? st.l1 : st.l0, m = hrow ? st.m1 : st.m0;
-      if (p.KS == 1) {
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* orow = p.out + ((size_t)tkn * p.Hq + head) * D;
-        const float* grow = p.gate_off >= 0 ? p.qkv + (size_t)tkn * p.ld_qkv + p.gate_off + (size_t)head * D : nullptr;
+      const float l = hrow ? st.l1 : st.l0;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = p.out + ((size_t)tkn * p.Hq + head) * D;
+      const float* grow = p.gate_off >= 0 ? p.qkv + (size_t)tkn * p.ld_qkv + p.gate_off + (size_t)head * D : nullptr;
 #pragma unroll
-        for (int nt = 0; nt < D / 8; ++nt) {
-          float v0 = st.o[nt][2 * hrow] * inv, v1 = st.o[nt][2 * hrow + 1] * inv;
-          if (grow != nullptr) {
-            const float2 gg = *reinterpret_cast<const float2*>(grow + nt * 8 + 2 * t);
-            v0 *= 1.f / (1.f + __expf(-gg.x));
-            v1 *= 1.f / (1.f + __expf(-gg.y));
-          }
-          *reinterpret_cast<uint32_t*>(orow + nt * 8 + 2 * t) = pack_bf16(v0, v1);
+      for (int nt = 0; nt < D / 8; ++nt) {
+        float v0 = st.o[nt][2 * hrow] * inv, v1 = st.o[nt][2 * hrow + 1] * inv;
+        if (grow != nullptr) {
+          const float2 gg = *reinterpret_cast<const float2*>(grow + nt * 8 + 2 * t);
+          v0 *= 1.f / (1.f + __expf(-gg.x));
+          v1 *= 1.f / (1.f + __expf(-gg.y));
         }
-      } else {
-        const size_t qrow = (size_t)tkn * p.Hq + head;
-        float* pa = p.part_acc + (qrow * p.KS + ks) * D;
-#pragma unroll
-        for (int nt = 0; nt < D / 8; ++nt)
-          *reinterpret_cast<float2*>(pa + nt * 8 + 2 * t) = make_float2(st.o[nt][2 * hrow], st.o[nt][2 * hrow + 1]);
-        if (t == 0) {
-          p.part_ml[(qrow * p.KS + ks) * 2] = m;
-          p.part_ml[(qrow * p.KS + ks) * 2 + 1] = l;
-        }
+        *reinterpret_cast<uint32_t*>(orow + nt * 8 + 2 * t) = pack_bf16(v0, v1);
       }
     }
   }
+  // the other splits keep their shared memory alive until rank 0 has read it
+  if (p.KS > 1) cluster_sync();
 }
 
-// merge of key splits (KS > 1) with the optional output gate
-__global__ void attn_fused_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                        __nv_bfloat16* __restrict__ out, const float* __restrict__ qkv, int ld_qkv,
-                                        int gate_off, int Hq, int KS, int D, int pdl) {
-  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
-  const size_t qrow = blockIdx.x;
-  const int tkn = (int)(qrow / Hq), head = (int)(qrow % Hq);
-  float M = -INFINITY;
-  for (int s = 0; s < KS; ++s) M = fmaxf(M, part_ml[(qrow * KS + s) * 2]);
-  float denom = 0.f;
-  for (int s = 0; s < KS; ++s) {
-    const float m = part_ml[(qrow * KS + s) * 2];
-    if (m != -INFINITY) denom += part_ml[(qrow * KS + s) * 2 + 1] * __expf(m - M);
-  }
-  const float inv = denom > 0.f ? 1.f / denom : 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float a = 0.f;
-    for (int s = 0; s < KS; ++s) {
-      const float m = part_ml[(qrow * KS + s) * 2];
-      if (m != -INFINITY) a += part_acc[(qrow * KS + s) * D + d] * __expf(m - M);
-    }
-    a *= inv;
-    if (gate_off >= 0) {
-      const float gv = qkv[(size_t)tkn * ld_qkv + gate_off + (size_t)head * D + d];
-      a *= 1.f / (1.f + __expf(-gv));
-    }
-    out[qrow * D + d] = __float2bfloat16(a);
-  }
-}
-
-static size_t fused_smem_bytes(int D, int n_mt, int n_kw) {
+static size_t fused_smem_bytes(int D, int n_mt, int n_kw, int stg) {
   const size_t LD = D + 8;
   size_t b = ((size_t)n_mt * 16 + 32) * LD * 2 + RANGE * 4;
-  size_t tiles = (size_t)n_kw * 4 * TK * LD * 2;
-  size_t merge = (size_t)(n_kw > 1 ? (n_kw - 1) * n_mt : 0) * (16 * D + 64) * 4;
+  size_t tiles = (size_t)n_kw * stg * 2 * TK * LD * 2;
+  // key-way slots of the in-CTA merge; one slot per m-tile is also what the cross-split merge parks
+  size_t merge = (size_t)(n_kw > 1 ? (n_kw - 1) * n_mt : n_mt) * (16 * D + 64) * 4;
   return b + (tiles > merge ? tiles : merge);
 }
 
 }  // namespace smc
 
+// Key-range splits (1, 2, 4 or 8) for `bs` sequences of about `ctx` cached tokens.  A split is taken while the grid
+// still fits one wave of one CTA per SM and every key-way keeps at least two 32-key tiles; kernels small enough
+// for two CTAs per SM may go to two waves' worth of CTAs once every key-way would still stream eight tiles.
+SMC_API int smc_attention_kv_splits(int bs, int E, int Hq, int Hkv, int D, int ctx) {
+  using namespace smc;
+  if (bs <= 0 || Hkv <= 0 || Hq % Hkv || E < 1) return 1;
+  const int R = E * (Hq / Hkv), n_mt = (R + 15) / 16;
+  int n_kw = 8 / n_mt;
+  if (n_kw < 1) n_kw = 1;
+  while (n_kw > 1 && fused_smem_bytes(D, n_mt, n_kw, 2) > 200 * 1024) --n_kw;
+  const bool two_per_sm = fused_smem_bytes(D, n_mt, n_kw, 2) <= 110 * 1024;
+  const long long base = (long long)bs * Hkv;
+  int ks = 1;
+  while (ks < 8) {
+    const int nk = ks * 2;
+    const int tiles_per_way = ctx / (nk * TK * n_kw);
+    if (base * nk <= 148 && tiles_per_way >= 2) ks = nk;
+    else if (two_per_sm && base * nk <= 296 && tiles_per_way >= 8) ks = nk;
+    else break;
+  }
+  return ks;
+}
+
 // qkv: fp32 [T, ld_qkv] with query heads at q_off, optional gate heads at gate_off (< 0: none), key heads
-// at k_off, value heads at v_off.  out: bf16 [T, Hq*D].  part_acc / part_ml: scratch, used when KS > 1.
+// at k_off, value heads at v_off.  out: bf16 [T, Hq*D].  KS in {1, 2, 4, 8} key-range splits per
+// (sequence, kv head) run as one thread-block cluster and are merged through distributed shared memory;
+// part_acc / part_ml are ignored (kept so existing callers need not change).
 SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, int q_off, int gate_off, int k_off, int v_off,
                                 const int* positions, const int* cache_locs, const float* rope, int rd, int max_pos,
                                 const void* qn_w, const void* kn_w, float norm_eps, int norm_plus_one, void* k_pool,
@@ -532,12 +585,18 @@ SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, 
   using namespace smc;
   if (bs <= 0) return 0;
   if (Hq % Hkv || E < 1 || E > 16 || (rd & 1) || rd > D) return -70;
+  if (!(KS == 1 || KS == 2 || KS == 4 || KS == 8)) return -73;
   const int G = Hq / Hkv, R = E * G;
   const int n_mt = (R + 15) / 16;
   if (n_mt > 8) return -71;
   int n_kw = 8 / n_mt;                   // key-ways: as many as fit in 8 warps and ~200 KB of shared memory
   if (n_kw < 1) n_kw = 1;
-  while (n_kw > 1 && fused_smem_bytes(D, n_mt, n_kw) > 200 * 1024) --n_kw;
+  while (n_kw > 1 && fused_smem_bytes(D, n_mt, n_kw, 2) > 200 * 1024) --n_kw;
+  // Ring depth: a grid that fits the GPU in one wave with one CTA per SM spends the whole shared memory on tiles
+  // in flight; larger grids stay under half of it so two CTAs share an SM.
+  const size_t budget = (size_t)bs * Hkv * KS <= 148 ? 200 * 1024 : 100 * 1024;
+  int stg = 2;
+  while (stg < 6 && fused_smem_bytes(D, n_mt, n_kw, stg + 1) <= budget) ++stg;
   FusedAttnParams p;
   p.qkv = qkv; p.q_in = (const __nv_bfloat16*)q_in; p.ld_qkv = ld_qkv; p.q_off = q_off; p.gate_off = gate_off; p.k_off = k_off; p.v_off = v_off;
   p.positions = positions; p.cache_locs = cache_locs; p.rope = rope; p.rd = rd; p.max_pos = max_pos;
@@ -545,33 +604,37 @@ SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, 
   p.norm_plus_one = norm_plus_one;
   p.k_pool = (__nv_bfloat16*)k_pool; p.v_pool = (__nv_bfloat16*)v_pool; p.n_pages = n_pages;
   p.block_table = block_table; p.bt_stride = bt_stride; p.rows = rows; p.prefix_lens = prefix_lens;
-  p.out = (__nv_bfloat16*)out; p.part_acc = part_acc; p.part_ml = part_ml;
-  p.E = E; p.Hq = Hq; p.Hkv = Hkv; p.KS = KS; p.n_mt = n_mt; p.n_kw = n_kw; p.scale = scale; p.status = status;
+  p.out = (__nv_bfloat16*)out;
+  p.E = E; p.Hq = Hq; p.Hkv = Hkv; p.KS = KS; p.n_mt = n_mt; p.n_kw = n_kw; p.stg = stg; p.scale = scale; p.status = status;
   p.pdl = pdl;
-  const size_t smem = fused_smem_bytes(D, n_mt, n_kw);
+  const size_t smem = fused_smem_bytes(D, n_mt, n_kw, stg);
   void (*kern)(const FusedAttnParams) = nullptr;
   if (D == 64) kern = attn_fused_kernel<64>;
   else if (D == 128) kern = attn_fused_kernel<128>;
   else if (D == 256) kern = attn_fused_kernel<256>;
   else return -72;
   CUDA_CHECK_RET(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (KS > 1) {                            // the splits of one (sequence, kv head) form a cluster along y
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = (unsigned)KS;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(bs * Hkv, KS);
   cfg.blockDim = dim3(32 * n_mt * n_kw);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = na;
   CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, kern, p));
-  if (KS > 1) {
-    cfg.gridDim = dim3(bs * E * Hq);
-    cfg.blockDim = dim3(D < 128 ? 64 : 128);
-    cfg.dynamicSmemBytes = 0;
-    CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, attn_fused_merge_kernel, (const float*)part_acc, (const float*)part_ml,
-                                      (__nv_bfloat16*)out, qkv, ld_qkv, gate_off, Hq, KS, D, pdl));
-  }
   return 0;
 }

@@ -136,6 +136,11 @@ __device__ __forceinline__ float ld_dsmem_f32_at(uint32_t remote_addr) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote_addr));
   return v;
 }
+__device__ __forceinline__ float2 ld_dsmem_f32x2_at(uint32_t remote_addr) {
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(remote_addr));
+  return v;
+}
 __device__ __forceinline__ uint32_t ld_dsmem_u32(uint32_t local_addr, uint32_t rank) {
   uint32_t remote, v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));

@@ -150,6 +150,66 @@ rope_kv_write_kernel(const float* __restrict__ partials, int splits, long long s
   }
 }
 
+// General form of the new-token stage for prompt passes: one block per token, one warp per head row.
+// qkv fp32 [M, ld] holds q heads at q_off, k heads at k_off, v heads at v_off (other columns, e.g. an output
+// gate, are ignored).  Optional per-head RMSNorm of q and k (weights [D], optionally stored as w - 1), rotary
+// over the first rd dims (pairs i, i + rd/2), bf16 rounding; q -> q_out [M, Hq*D], k/v -> their cache pages.
+__global__ void __launch_bounds__(256)
+rope_kv_write_heads_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, int v_off,
+                           const int* __restrict__ positions, const int* __restrict__ cache_locs,
+                           const float* __restrict__ rope, int rd, int max_pos,
+                           const __nv_bfloat16* __restrict__ qn_w, const __nv_bfloat16* __restrict__ kn_w, float eps,
+                           int plus_one, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool,
+                           __nv_bfloat16* __restrict__ v_pool, int n_pages, int Hq, int Hkv, int D, int* status,
+                           int pdl) {
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
+  const int m = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  int pos = positions[m];
+  int loc = cache_locs[m];
+  if (pos < 0 || pos >= max_pos || loc < 0 || loc > n_pages) {
+    if (threadIdx.x == 0) atomicOr(status, SMC_ERR_BOUNDS);
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    loc = 0;
+  }
+  const float* cs = rope + (size_t)pos * rd;
+  const int half = rd >> 1;
+  const float add = plus_one ? 1.f : 0.f;
+  const size_t kv_row = (size_t)Hkv * D;
+  for (int j = warp; j < Hq + 2 * Hkv; j += nwarps) {
+    const bool is_q = j < Hq, is_v = j >= Hq + Hkv;
+    const int hd = is_q ? j : (is_v ? j - Hq - Hkv : j - Hq);
+    const float* src = qkv + (size_t)m * ld + (is_q ? q_off : (is_v ? v_off : k_off)) + (size_t)hd * D;
+    __nv_bfloat16* dst = is_q ? q_out + ((size_t)m * Hq + hd) * D
+                              : (is_v ? v_pool : k_pool) + (size_t)loc * kv_row + (size_t)hd * D;
+    const __nv_bfloat16* nw = is_v ? nullptr : (is_q ? qn_w : kn_w);
+    float rstd = 1.f;
+    if (nw != nullptr) {
+      float ss = 0.f;
+      for (int i = lane; i < D; i += 32) ss += src[i] * src[i];
+      rstd = rsqrtf(warp_sum(ss) / (float)D + eps);
+    }
+    for (int i = lane; i < D / 2; i += 32) {
+      int i1, i2;
+      bool rot;
+      if (i < half) { i1 = i; i2 = i + half; rot = !is_v; }
+      else { const int jj = i - half; i1 = rd + 2 * jj; i2 = i1 + 1; rot = false; }
+      float x1 = src[i1], x2 = src[i2];
+      if (nw != nullptr) {
+        x1 *= rstd * (__bfloat162float(nw[i1]) + add);
+        x2 *= rstd * (__bfloat162float(nw[i2]) + add);
+      }
+      if (rot) {
+        const float c = cs[i], sn = cs[half + i];
+        const float y1 = x1 * c - x2 * sn, y2 = x2 * c + x1 * sn;
+        x1 = y1; x2 = y2;
+      }
+      dst[i1] = __float2bfloat16(x1);
+      dst[i2] = __float2bfloat16(x2);
+    }
+  }
+}
+
 // act[m, c] = silu(gate) * up with gate/up interleaved in blocks of `blk` channels.
 __global__ void __launch_bounds__(256)
 swiglu_partials_kernel(const float* __restrict__ partials, int splits, long long split_stride,
@@ -211,6 +271,20 @@ SMC_API int smc_rope_kv_write(const float* partials, int splits, long long split
   return launch_pdl(rope_kv_write_kernel, dim3(M), dim3(256), st, pdl, partials, splits, split_stride, positions,
                     cache_locs, rope, rd, max_pos, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
                     (__nv_bfloat16*)v_pool, n_pages, Hq, Hkv, D, status, pdl);
+}
+
+SMC_API int smc_rope_kv_write_heads(const float* qkv, int ld, int q_off, int k_off, int v_off, const int* positions,
+                                    const int* cache_locs, const float* rope, int rd, int max_pos, const void* qn_w,
+                                    const void* kn_w, float eps, int plus_one, void* q_out, void* k_pool,
+                                    void* v_pool, int n_pages, int M, int Hq, int Hkv, int D, int* status, int pdl,
+                                    cudaStream_t st) {
+  using namespace smc;
+  if (M <= 0) return 0;
+  if (rd > D || (rd & 1) || (D & 1)) return -32;
+  return launch_pdl(rope_kv_write_heads_kernel, dim3(M), dim3(256), st, pdl, qkv, ld, q_off, k_off, v_off, positions,
+                    cache_locs, rope, rd, max_pos, (const __nv_bfloat16*)qn_w, (const __nv_bfloat16*)kn_w, eps,
+                    plus_one, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_pages, Hq, Hkv,
+                    D, status, pdl);
 }
 
 SMC_API int smc_swiglu_partials(const float* partials, int splits, long long split_stride, void* act, int M, int ffn,

@@ -14,23 +14,26 @@ namespace smc {
 // proj: fp32 [T, ldp] = mixed (conv_dim) | z (value_dim) | b (Hv) | a (Hv).
 __global__ void gdn_conv_kernel(const float* __restrict__ proj, int ldp, float* __restrict__ conv_state,
                                 const int* __restrict__ state_rows, const __nv_bfloat16* __restrict__ conv_w,
-                                float* __restrict__ conv_out, int bs, int E, int conv_dim, int W, int pdl) {
+                                float* __restrict__ conv_out, int bs, int E, int conv_dim, int W,
+                                const int* __restrict__ tok_off, const int* __restrict__ tok_len, int pdl) {
   if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= bs * conv_dim) return;
   const int b = idx / conv_dim, ch = idx % conv_dim;
+  const size_t t0 = tok_off ? (size_t)tok_off[b] : (size_t)b * E;
+  if (tok_len) E = tok_len[b];
   float* win = conv_state + ((size_t)state_rows[b] * conv_dim + ch) * (W - 1);
   float hist[8];
   float w[8];
   for (int i = 0; i < W - 1; ++i) hist[i] = win[i];
   for (int i = 0; i < W; ++i) w[i] = __bfloat162float(conv_w[ch * W + i]);
   for (int e = 0; e < E; ++e) {
-    const float x = proj[(size_t)(b * E + e) * ldp + ch];
+    const float x = proj[(t0 + e) * ldp + ch];
     float acc = w[W - 1] * x;
     for (int i = 0; i < W - 1; ++i) acc += w[i] * hist[i];
     for (int i = 0; i + 1 < W - 1; ++i) hist[i] = hist[i + 1];
     hist[W - 2] = x;
-    conv_out[(size_t)(b * E + e) * conv_dim + ch] = acc / (1.f + __expf(-acc));
+    conv_out[(t0 + e) * conv_dim + ch] = acc / (1.f + __expf(-acc));
   }
   for (int i = 0; i < W - 1; ++i) win[i] = hist[i];
 }
@@ -40,11 +43,14 @@ __global__ void gdn_recurrent_kernel(const float* __restrict__ conv_out, const f
                                      float* __restrict__ temporal, const int* __restrict__ state_rows,
                                      const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                                      const __nv_bfloat16* __restrict__ gnorm_w, __nv_bfloat16* __restrict__ out,
-                                     int E, int Hk, int Hv, int dv, int conv_dim, float eps, int pdl) {
+                                     int E, int Hk, int Hv, int dv, int conv_dim, float eps,
+                                     const int* __restrict__ tok_off, const int* __restrict__ tok_len, int pdl) {
   __shared__ float q_s[DK], k_s[DK], red[8];
   __shared__ float scal[4];
   if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const int b = blockIdx.x, vh = blockIdx.y, kh = vh / (Hv / Hk);
+  const size_t t0 = tok_off ? (size_t)tok_off[b] : (size_t)b * E;
+  if (tok_len) E = tok_len[b];
   const int j = threadIdx.x;              // value-dim column owned by this thread (j < dv does real work)
   const int key_dim = Hk * DK, value_dim = Hv * dv;
   const bool live = j < dv;
@@ -55,7 +61,7 @@ __global__ void gdn_recurrent_kernel(const float* __restrict__ conv_out, const f
   const float wj = live ? __bfloat162float(gnorm_w[j]) : 0.f;
   const int nwarps = (blockDim.x + 31) >> 5;
   for (int e = 0; e < E; ++e) {
-    const size_t t = (size_t)b * E + e;
+    const size_t t = t0 + e;
     const float* co = conv_out + t * conv_dim;
     // l2-normalised q (scaled by dk^-1/2) and k of this key head
     float qv = 0.f, kv_ = 0.f;
@@ -109,11 +115,14 @@ __global__ void gdn_recurrent_kernel(const float* __restrict__ conv_out, const f
 
 }  // namespace smc
 
-SMC_API int smc_gdn_step(const float* proj, int ldp, float* conv_state, float* temporal, const int* state_rows,
-                         const void* conv_w, const float* dt_bias, const float* A_log, const void* gnorm_w,
-                         float* conv_out, void* out, int bs, int E, int Hk, int Hv, int dk, int dv, int W, float eps,
-                         int pdl, cudaStream_t st) {
+// Rows of variable length (prompt passes): row b covers tokens [tok_off[b], tok_off[b] + tok_len[b]) of the
+// token-major buffers.  With tok_off == tok_len == null every row has E tokens laid out back to back.
+SMC_API int smc_gdn_varlen(const float* proj, int ldp, float* conv_state, float* temporal, const int* state_rows,
+                           const void* conv_w, const float* dt_bias, const float* A_log, const void* gnorm_w,
+                           float* conv_out, void* out, int bs, int E, const int* tok_off, const int* tok_len, int Hk,
+                           int Hv, int dk, int dv, int W, float eps, int pdl, cudaStream_t st) {
   using namespace smc;
+  if ((tok_off == nullptr) != (tok_len == nullptr)) return -103;
   if (bs <= 0) return 0;
   if (W < 2 || W > 8 || Hv % Hk || dv > 256 || dk > 256) return -100;
   const int conv_dim = 2 * Hk * dk + Hv * dv;
@@ -127,7 +136,7 @@ SMC_API int smc_gdn_step(const float* proj, int ldp, float* conv_state, float* t
   cfg.gridDim = dim3((bs * conv_dim + 255) / 256);
   cfg.blockDim = dim3(256);
   CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_conv_kernel, proj, ldp, conv_state, state_rows,
-                                    (const __nv_bfloat16*)conv_w, conv_out, bs, E, conv_dim, W, pdl));
+                                    (const __nv_bfloat16*)conv_w, conv_out, bs, E, conv_dim, W, tok_off, tok_len, pdl));
   int threads = dv > dk ? dv : dk;
   threads = (threads + 31) / 32 * 32;
   if (threads > 128) return -101;
@@ -136,7 +145,7 @@ SMC_API int smc_gdn_step(const float* proj, int ldp, float* conv_state, float* t
 #define GDN_LAUNCH(DKV)                                                                                           \
   CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_recurrent_kernel<DKV>, (const float*)conv_out, proj, ldp, temporal, \
                                     state_rows, dt_bias, A_log, (const __nv_bfloat16*)gnorm_w,                    \
-                                    (__nv_bfloat16*)out, E, Hk, Hv, dv, conv_dim, eps, pdl))
+                                    (__nv_bfloat16*)out, E, Hk, Hv, dv, conv_dim, eps, tok_off, tok_len, pdl))
   switch (dk) {
     case 128: GDN_LAUNCH(128); break;
     case 64: GDN_LAUNCH(64); break;
@@ -146,4 +155,12 @@ SMC_API int smc_gdn_step(const float* proj, int ldp, float* conv_state, float* t
   }
 #undef GDN_LAUNCH
   return 0;
+}
+
+SMC_API int smc_gdn_step(const float* proj, int ldp, float* conv_state, float* temporal, const int* state_rows,
+                         const void* conv_w, const float* dt_bias, const float* A_log, const void* gnorm_w,
+                         float* conv_out, void* out, int bs, int E, int Hk, int Hv, int dk, int dv, int W, float eps,
+                         int pdl, cudaStream_t st) {
+  return smc_gdn_varlen(proj, ldp, conv_state, temporal, state_rows, conv_w, dt_bias, A_log, gnorm_w, conv_out, out, bs,
+                        E, nullptr, nullptr, Hk, Hv, dk, dv, W, eps, pdl, st);
 }

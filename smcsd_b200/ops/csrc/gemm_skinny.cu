@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
   const int kb_end = (int)(((long long)p.kblocks * (split + 1)) / p.splits);
   const int nkb = kb_end - kb_begin;
 
+  __shared__ float s_rstd[BN];
   if (warp == 0) {
     if (elect_one()) {
       const uint64_t pol_w = l2_policy_evict_first();
@@ -189,6 +190,22 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
       if (!*sh_abort) umma_commit(accum);
     }
     __syncwarp();
+  } else {
+    // warps 2 and 3 are idle until the epilogue: they turn the per-slab sums of squares of the activation rows
+    // into the per-token 1/rms factors while the weight stream runs
+    const int tid2 = threadIdx.x - 64;
+    if (p.ssq_in != nullptr) {
+      if (p.pdl) pdl_wait_prior_grid();
+      for (int c = tid2; c < BN; c += 64) {
+        const int m = m_tile * BN + c;
+        float ss = 0.f;
+        if (m < p.M)
+          for (int q = 0; q < p.ssq_parts; ++q) ss += p.ssq_in[(size_t)q * p.ssq_ld + (size_t)m * p.ssq_mstride];
+        s_rstd[c] = rsqrtf(ss * p.norm_inv_d + p.norm_eps);
+      }
+    } else {
+      for (int c = tid2; c < BN; c += 64) s_rstd[c] = 1.f;
+    }
   }
 
   // ---- wait for the accumulator (all threads), bounded ------------------------------------
@@ -205,20 +222,6 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
   }
   const int failed = __syncthreads_or(ok ? 0 : 1);
   tc_fence_after();
-
-  __shared__ float s_rstd[BN];
-  if (p.ssq_in != nullptr) {
-    for (int c = threadIdx.x; c < BN; c += blockDim.x) {
-      const int m = m_tile * BN + c;
-      float ss = 0.f;
-      if (m < p.M)
-        for (int q = 0; q < p.ssq_parts; ++q) ss += p.ssq_in[(size_t)q * p.ssq_ld + (size_t)m * p.ssq_mstride];
-      s_rstd[c] = rsqrtf(ss * p.norm_inv_d + p.norm_eps);
-    }
-  } else {
-    for (int c = threadIdx.x; c < BN; c += blockDim.x) s_rstd[c] = 1.f;
-  }
-  __syncthreads();
 
   if (!failed) {
     const int row_in_tile = warp * 32 + lane;

@@ -153,6 +153,29 @@ def rope_kv_write(partials: torch.Tensor, splits: int, split_stride: int, positi
            "smc_rope_kv_write")
 
 
+def rope_kv_write_heads(qkv: torch.Tensor, positions: torch.Tensor, cache_locs: torch.Tensor, rope: torch.Tensor,
+                        q_out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *, M: int, Hq: int, Hkv: int,
+                        D: int, status: torch.Tensor, q_off: int = 0, k_off: Optional[int] = None,
+                        v_off: Optional[int] = None, qn_w: Optional[torch.Tensor] = None,
+                        kn_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6, norm_plus_one: bool = False,
+                        pdl: bool = False) -> None:
+    """New-token stage on its own (prompt passes): per-head RMSNorm, rotary, bf16; q rows to ``q_out``, k/v rows to
+    their cache pages.  Column offsets select q / k / v inside the fp32 projection rows."""
+    L = lib()
+    if not getattr(L, "_rkh_declared", False):
+        vp, i, f = C.c_void_p, C.c_int, C.c_float
+        L.smc_rope_kv_write_heads.argtypes = [vp, i, i, i, i, vp, vp, vp, i, i, vp, vp, f, i, vp, vp, vp, i, i, i, i, i,
+                                              vp, i, vp]
+        L.smc_rope_kv_write_heads.restype = C.c_int
+        L._rkh_declared = True
+    k_off = Hq * D if k_off is None else k_off
+    v_off = k_off + Hkv * D if v_off is None else v_off
+    _check(L.smc_rope_kv_write_heads(_p(qkv), qkv.stride(0), q_off, k_off, v_off, _p(positions), _p(cache_locs),
+                                     _p(rope), rope.shape[1], rope.shape[0], _p(qn_w), _p(kn_w), norm_eps,
+                                     int(norm_plus_one), _p(q_out), _p(k_pool), _p(v_pool), k_pool.shape[0] - 1, M, Hq,
+                                     Hkv, D, _p(status), int(pdl), _stream()), "smc_rope_kv_write_heads")
+
+
 def swiglu_partials(partials: torch.Tensor, splits: int, split_stride: int, act: torch.Tensor, *, M: int, ffn: int,
                     blk: int, pdl: bool = False) -> None:
     _check(lib().smc_swiglu_partials(_p(partials), splits, split_stride, _p(act), M, ffn, blk, act.stride(0), int(pdl),
@@ -184,7 +207,19 @@ def attention_fused(qkv: torch.Tensor, positions: torch.Tensor, cache_locs: torc
                                      norm_eps, int(norm_plus_one), _p(k_pool), _p(v_pool), k_pool.shape[0] - 1,
                                      _p(block_table), block_table.stride(0), _p(rows), _p(prefix_lens), _p(out),
                                      _p(part_acc), _p(part_ml), bs, E, Hq, Hkv, D, KS, scale, _p(status), int(pdl),
-                                     _stream()), "smc_attention_fused" if KS == 1 else "smc_attention_extend")
+                                     _stream()), "smc_attention_fused")
+
+
+def attn_kv_splits(ctx: int, bs: int, Hkv: int, E: int = 1, G: int = 4, D: int = 128) -> int:
+    """Key-range splits (1, 2, 4 or 8) the fused attention step should use for ``bs`` sequences of about ``ctx``
+    cached tokens with ``E`` new tokens, ``G`` query heads per kv head and head size ``D``.  The splits of one
+    (sequence, kv head) run as a thread-block cluster and are merged on chip."""
+    L = lib()
+    if not getattr(L, "_aks_declared", False):
+        L.smc_attention_kv_splits.argtypes = [C.c_int] * 6
+        L.smc_attention_kv_splits.restype = C.c_int
+        L._aks_declared = True
+    return L.smc_attention_kv_splits(bs, E, Hkv * G, Hkv, D, int(ctx))
 
 
 def sample_scratch_bytes(rows: int, nchunks: int) -> int:
@@ -357,18 +392,20 @@ def tp_wait_counter(flag_ptr: int, want: int, outcome: torch.Tensor, status: tor
 def gdn_step(proj: torch.Tensor, conv_state: torch.Tensor, temporal: torch.Tensor, state_rows: torch.Tensor,
              conv_w: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, gnorm_w: torch.Tensor,
              conv_out: torch.Tensor, out: torch.Tensor, *, bs: int, E: int, Hk: int, Hv: int, dk: int, dv: int, W: int,
-             eps: float, pdl: bool = False) -> None:
+             eps: float, pdl: bool = False, tok_off: Optional[torch.Tensor] = None,
+             tok_len: Optional[torch.Tensor] = None) -> None:
     """Conv + gated delta rule + gated RMSNorm for E new tokens per row; advances the state of one layer in place.
-    conv_state [rows, conv_dim, W-1] fp32 and temporal [rows, Hv, dk, dv] fp32 are that layer's slices."""
+    conv_state [rows, conv_dim, W-1] fp32 and temporal [rows, Hv, dk, dv] fp32 are that layer's slices.
+    ``tok_off`` / ``tok_len`` (int32 per row) give rows of different lengths at arbitrary token offsets."""
     L = lib()
     if not getattr(L, "_gdn_declared", False):
         vp, i, f = C.c_void_p, C.c_int, C.c_float
-        L.smc_gdn_step.argtypes = [vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, i, vp]
-        L.smc_gdn_step.restype = C.c_int
+        L.smc_gdn_varlen.argtypes = [vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp, i, i, i, i, i, f, i, vp]
+        L.smc_gdn_varlen.restype = C.c_int
         L._gdn_declared = True
-    _check(L.smc_gdn_step(_p(proj), proj.stride(0), _p(conv_state), _p(temporal), _p(state_rows), _p(conv_w),
-                          _p(dt_bias), _p(A_log), _p(gnorm_w), _p(conv_out), _p(out), bs, E, Hk, Hv, dk, dv, W, eps,
-                          int(pdl), _stream()), "smc_gdn_step")
+    _check(L.smc_gdn_varlen(_p(proj), proj.stride(0), _p(conv_state), _p(temporal), _p(state_rows), _p(conv_w),
+                            _p(dt_bias), _p(A_log), _p(gnorm_w), _p(conv_out), _p(out), bs, E, _p(tok_off),
+                            _p(tok_len), Hk, Hv, dk, dv, W, eps, int(pdl), _stream()), "smc_gdn_varlen")
 
 
 _KERNELS_PER_CALL["smc_gdn_step"] = 2

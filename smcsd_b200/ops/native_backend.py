@@ -20,6 +20,11 @@ from ..runtime.slot_state import CycleInputs, CycleOutputs
 from . import native as K
 
 
+def _env_int(name: str, default: int) -> int:
+    v = os.environ.get(name)
+    return default if v is None or v == "" else int(v)
+
+
 def _env_flag(name: str, default: bool) -> bool:
     v = os.environ.get(name)
     return default if v is None else v.strip().lower() in ("1", "true", "yes", "on")
@@ -49,9 +54,8 @@ class NativeLlama:
         self.attn = torch.empty(max_tokens, self.nq * self.D, dtype=bf16, device=dev)
         self.act = torch.empty(max_tokens, self.ffn, dtype=bf16, device=dev)
         self.qkv = torch.empty(max_tokens, self.nqkv, dtype=f32, device=dev)
-        self.KS = 1 if block_table.shape[1] <= 6144 else (2 if block_table.shape[1] <= 16384 else 4)
-        self.part_acc = torch.empty(max_tokens * self.nq * self.KS * self.D if self.KS > 1 else 1, dtype=f32, device=dev)
-        self.part_ml = torch.empty(max_tokens * self.nq * self.KS * 2 if self.KS > 1 else 1, dtype=f32, device=dev)
+        self.ctx = 0                         # context-length hint that sizes the attention key splits, see set_context
+        self.part_acc = self.part_ml = torch.empty(1, dtype=f32, device=dev)     # unused by the fused kernel
         self.logits = torch.empty(max_logit_rows, self.V, dtype=f32, device=dev)
         self.fuse_swiglu = model.gu_block == 64 and (2 * self.ffn) % 128 == 0
         if not self.fuse_swiglu:
@@ -85,7 +89,7 @@ class NativeLlama:
                 q_in = self.q
             K.attention_fused(self.qkv, positions, cache_locs, m.rope, self.kv.k[li], self.kv.v[li], self.bt, rows,
                               prefix_lens, self.attn, self.part_acc, self.part_ml, bs=bs, E=E, Hq=self.nq,
-                              Hkv=self.nkv, D=self.D, KS=self.KS, scale=scale, status=self.status, pdl=pdl, q_in=q_in)
+                              Hkv=self.nkv, D=self.D, KS=self._ks(bs, E), scale=scale, status=self.status, pdl=pdl, q_in=q_in)
             K.gemm_skinny_norm(L.wo, self.attn, self.h, M=T, splits=self._splits(self.d, self.nq * self.D, T),
                                epi=K.EPI_RESID_F32, ldo=self.d, status=self.status, ssq_out=self.ssq, hb_out=self.hb,
                                ssq_ld=ld, pdl=pdl)
@@ -97,6 +101,15 @@ class NativeLlama:
                                epi=K.EPI_RESID_F32, ldo=self.d, status=self.status, ssq_out=self.ssq, hb_out=self.hb,
                                ssq_ld=ld, pdl=pdl)
         return self.hb
+
+    def set_context(self, ctx: int, bs: int, Es=(1, 2)) -> tuple:
+        """Record the context-length hint for the attention key splits; returns the splits chosen for forwards of
+        ``Es`` new tokens per sequence (part of a captured graph's identity: they fix the launch grids)."""
+        self.ctx = int(ctx)
+        return tuple(self._ks(bs, E) for E in Es)
+
+    def _ks(self, bs: int, E: int) -> int:
+        return K.attn_kv_splits(self.ctx, bs, self.nkv, E, self.nq // self.nkv, self.D)
 
     def final_hidden(self, rows_idx: torch.Tensor) -> torch.Tensor:
         """Post-final-norm hidden rows (bf16) for callers that project with PyTorch (x0 at prefill)."""
@@ -143,7 +156,7 @@ class NativeLlama:
                 q_in = self.q
             K.attention_fused(self.qkv, positions, cache_locs, m.rope, self.kv.k[li], self.kv.v[li], self.bt, rows,
                               prefix_lens, self.attn, self.part_acc, self.part_ml, bs=bs, E=E, Hq=self.nq,
-                              Hkv=self.nkv, D=self.D, KS=self.KS, scale=scale, status=self.status, pdl=pdl, q_in=q_in)
+                              Hkv=self.nkv, D=self.D, KS=self._ks(bs, E), scale=scale, status=self.status, pdl=pdl, q_in=q_in)
             self._gemm(L.wo, self.attn, self.h, T, K.EPI_RESID_F32)
             K.add_rmsnorm(self.h, L.ln2, self.xn, M=T, d=self.d, eps=c.rms_eps, pdl=pdl)
             if self.fuse_swiglu:
@@ -286,7 +299,7 @@ class NativeRunner:
         self.sample_scratch = torch.empty(K.sample_scratch_bytes(rows, self.nchunks), dtype=torch.uint8,
                                           device=self.device)
         self.seed = int(a.random_seed) * 1000003 + 12345 + 7919 * getattr(sched, "pp_rank", 0)
-        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
         self.use_graph = bool(a.cycle_graph)
         self.T_draft, self.T_target, self.alpha = float(a.draft_temperature), float(a.target_temperature), float(a.power_alpha)
         self.defer = bool(a.defer_bonus)
@@ -322,10 +335,14 @@ class NativeRunner:
         nm = getattr(self, key, None)
         if nm is None:
             base = self.target if which == "target" else self.draft
-            if not isinstance(base, NativeLlama):
+            if isinstance(base, NativeLlama):
+                nm = NativeLlama(base.m, base.kv, base.bt, self.PREFILL_MAX_TOKENS, 8, base.attn_splits, self.status,
+                                 self.pdl)
+            elif type(base).__name__ == "NativeHybrid":
+                nm = type(base)(base.m, base.kv, base.bt, self.PREFILL_MAX_TOKENS, 8, base.attn_splits, self.status,
+                                self.pdl, runner=self, state=base.state)
+            else:
                 return None
-            nm = NativeLlama(base.m, base.kv, base.bt, self.PREFILL_MAX_TOKENS, 8, base.attn_splits, self.status,
-                             self.pdl)
             setattr(self, key, nm)
         nm.bt = (self.target if which == "target" else self.draft).bt
         return nm
@@ -333,8 +350,9 @@ class NativeRunner:
     def prefill(self, worker, items) -> torch.Tensor:
         """Prompt pass through the kernel chains: every prompt is cut into 16-token blocks that run as rows of one
         batch (block j of a prompt attends to its 16j cached predecessors plus itself), so prefill reuses the
-        decode kernels with token-tile GEMMs.  Hybrid models, tensor-parallel targets and over-long batches take
-        the plain PyTorch forward."""
+        decode kernels with token-tile GEMMs.  Gated-DeltaNet layers of hybrid models walk each prompt once, token
+        by token, with the state held in registers.  Tensor-parallel targets and over-long batches take the plain
+        PyTorch forward."""
         B = self.PREFILL_BLOCK
         lens = [len(it.input_ids) for it in items]
         n_blocks = [(L + B - 1) // B for L in lens]
@@ -372,12 +390,29 @@ class NativeRunner:
             locs[t:t + L] = self.st.bt.table[it.row, :L]
             t += nb * B
         bs = sum(n_blocks)
-        tgt.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True)
+        for nm in (tgt, drf):
+            nm.set_context(max(lens), bs)
+
+        def seqs_for(nm, short: int):
+            # prompts as variable-length rows for the recurrent layers (None for dense models)
+            if not getattr(nm.m, "has_state", False):
+                return {}
+            offs, t = [], 0
+            for nb in n_blocks:
+                offs.append(t)
+                t += nb * B
+            return {"seqs": {"rows": pin(torch.tensor([it.row for it in items], dtype=torch.int32)),
+                             "off": pin(torch.tensor(offs, dtype=torch.int32)),
+                             "len": pin(torch.tensor([max(L - short, 0) for L in lens], dtype=torch.int32)),
+                             "n": len(items)}}
+        tgt.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True, **seqs_for(tgt, 0))
         last = torch.tensor(last_rows, dtype=torch.long, device=dev)
         logits = self.target.m.logits_torch(tgt.final_hidden(last))
         from ..smc import math as smc_math
         x0, _, _ = smc_math.gumbel_sample(logits, self.T_target, self.alpha, generator=worker.gen_prefill)
-        drf.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True)
+        # a stateful draft under the deferred schedule stops one token short: the first head forward of the decode
+        # loop advances its recurrent state through the last prompt token exactly once
+        drf.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True, **seqs_for(drf, 1 if self.defer else 0))
         worker.io_bytes["d2h"] += 4 * len(items)
         return x0.to(torch.int32)
 
@@ -450,17 +485,21 @@ class NativeRunner:
         ns.write_back_native(st, self.alpha)
         ns.collect_and_resample(st)
 
-    def run_cycle(self, st, worker) -> None:
+    def run_cycle(self, st, worker, ctx_hint: int = 0) -> None:
+        """One decode cycle.  ``ctx_hint``: upper bound of the sequence lengths this cycle reaches (known on the host
+        from prompt lengths and cycle counts); it selects how many key ranges the attention steps split into, and
+        with it which captured graph runs."""
         ns = self.ns
         if ns._arrays is None:
             ns.bind(st)
         ns.sync_membership(st)
         st.step += 1
         bs = ns.bs
+        key = (bs, self.target.set_context(ctx_hint, bs, (self.G,)), self.draft.set_context(ctx_hint, bs, (1, 2)))
         if not self.use_graph:
             self._full_cycle(st)
             return
-        gr = self.graphs.get(bs)
+        gr = self.graphs.get(key)
         if gr is None:
             # warm up once eagerly on a side stream (also JIT-free: everything is precompiled), then capture
             gr = torch.cuda.CUDAGraph()
@@ -477,7 +516,7 @@ class NativeRunner:
                 self._full_cycle(st)
             self.launches_per_cycle = K.launch_count - n0
             self._restore_state(st, saved)
-            self.graphs[bs] = gr
+            self.graphs[key] = gr
         gr.replay()
 
     # capture runs the cycle for real; put the mutable state back afterwards

@@ -33,14 +33,14 @@ class NativeHybrid:
         self.win_rows = max((L.win.shape[0] for L in model.layers if L.win is not None), default=8)
         self.h = torch.empty(max_tokens, self.d, dtype=f32, device=dev)
         self.xn = torch.empty(max_tokens, self.d, dtype=bf16, device=dev)
-        self.attn = torch.empty(max_tokens, max(self.nq * self.D, model.value_dim), dtype=bf16, device=dev)
+        self.attn = torch.zeros(max_tokens, max(self.nq * self.D, model.value_dim), dtype=bf16, device=dev)
         self.act = torch.empty(max_tokens, self.ffn, dtype=bf16, device=dev)
         self.qkv = torch.empty(max_tokens, max(self.nqkv, self.win_rows), dtype=f32, device=dev)
         self.conv_out = torch.empty(max_tokens, model.conv_dim, dtype=f32, device=dev)
-        self.KS = 1 if block_table.shape[1] <= 6144 else (2 if block_table.shape[1] <= 16384 else 4)
-        n = max_tokens * self.nq * self.KS
-        self.part_acc = torch.empty(n * self.D if self.KS > 1 else 1, dtype=f32, device=dev)
-        self.part_ml = torch.empty(n * 2 if self.KS > 1 else 1, dtype=f32, device=dev)
+        self.attn_splits = attn_splits
+        self._q = None                      # rotated queries of a prompt pass (allocated on first use)
+        self.ctx = 0                         # context-length hint that sizes the attention key splits, see set_context
+        self.part_acc = self.part_ml = torch.empty(1, dtype=f32, device=dev)     # unused by the fused kernel
         self.logits = torch.empty(max_logit_rows, self.V, dtype=f32, device=dev)
         self.fuse_swiglu = model.gu_block == 64 and (2 * self.ffn) % 128 == 0
         if not self.fuse_swiglu:
@@ -55,10 +55,17 @@ class NativeHybrid:
         K.gemm_skinny(W, X, out, M=M, splits=self._splits_cache[key], epi=epi, ldo=ldo or out.stride(0),
                       status=self.status, pdl=self.pdl)
 
-    def forward(self, ids, positions, cache_locs, rows, prefix_lens, bs: int, E: int):
+    def forward(self, ids, positions, cache_locs, rows, prefix_lens, bs: int, E: int, two_pass: bool = False,
+                seqs=None):
+        """``two_pass`` + ``seqs`` (prompt passes): the batch rows are consecutive E-token blocks of whole prompts.
+        Attention layers first write every new K/V row to the cache, then each block attends through the block
+        table; Gated-DeltaNet layers walk each prompt once from its first to its last real token
+        (``seqs`` = state rows, token offsets and token counts of the prompts, int32 tensors)."""
         m, c, pdl = self.m, self.c, self.pdl
         T = bs * E
         assert T <= self.T and self.state is not None
+        if two_pass and self._q is None:
+            self._q = torch.empty(self.T, self.nq * self.D, dtype=torch.bfloat16, device=m.device)
         po = c.norm_plus_one
         K.add_rmsnorm(self.h, m.layers[0].ln1, self.xn, M=T, d=self.d, eps=c.rms_eps, ids=ids, embed=m.embed,
                       plus_one=po, pdl=pdl)
@@ -72,11 +79,18 @@ class NativeHybrid:
                 self._gemm(L.wqkv, self.xn, self.qkv, T, K.EPI_STORE_F32)
                 gate_off = nq if c.attn_output_gate else -1
                 k_off = 2 * nq if c.attn_output_gate else nq
+                q_in = None
+                if two_pass:
+                    K.rope_kv_write_heads(self.qkv, positions, cache_locs, m.rope, self._q, self.kv.k[ki],
+                                          self.kv.v[ki], M=T, Hq=self.nq, Hkv=self.nkv, D=self.D, status=self.status,
+                                          q_off=0, k_off=k_off, v_off=k_off + self.nkv * self.D, qn_w=L.q_norm,
+                                          kn_w=L.k_norm, norm_eps=c.rms_eps, norm_plus_one=po, pdl=pdl)
+                    q_in = self._q
                 K.attention_fused(self.qkv, positions, cache_locs, m.rope, self.kv.k[ki], self.kv.v[ki], self.bt, rows,
                                   prefix_lens, self.attn, self.part_acc, self.part_ml, bs=bs, E=E, Hq=self.nq,
-                                  Hkv=self.nkv, D=self.D, KS=self.KS, scale=scale, status=self.status, q_off=0,
+                                  Hkv=self.nkv, D=self.D, KS=self._ks(bs, E), scale=scale, status=self.status, q_off=0,
                                   gate_off=gate_off, k_off=k_off, v_off=k_off + self.nkv * self.D, qn_w=L.q_norm,
-                                  kn_w=L.k_norm, norm_eps=c.rms_eps, norm_plus_one=po, pdl=pdl)
+                                  kn_w=L.k_norm, norm_eps=c.rms_eps, norm_plus_one=po, pdl=pdl, q_in=q_in)
                 # the attention output rows are packed [T, Hq*D] at the start of the shared buffer
                 self._gemm(L.wo, self.attn.view(-1)[: T * nq].view(T, nq), self.h, T, K.EPI_RESID_F32)
             else:
@@ -84,9 +98,16 @@ class NativeHybrid:
                 self._gemm(L.win, self.xn, self.qkv, T, K.EPI_STORE_F32)
                 vd = m.value_dim
                 mix = self.attn.view(-1)[: T * vd].view(T, vd)
-                K.gdn_step(self.qkv, self.state.conv[si], self.state.temporal[si], rows, L.conv_w, L.dt_bias, L.A_log,
-                           L.gnorm_w, self.conv_out, mix, bs=bs, E=E, Hk=c.gdn_n_k_heads, Hv=c.gdn_n_v_heads,
-                           dk=c.gdn_head_k_dim, dv=c.gdn_head_v_dim, W=c.gdn_conv_width, eps=c.rms_eps, pdl=pdl)
+                if seqs is not None:
+                    K.gdn_step(self.qkv, self.state.conv[si], self.state.temporal[si], seqs["rows"], L.conv_w,
+                               L.dt_bias, L.A_log, L.gnorm_w, self.conv_out, mix, bs=seqs["n"], E=0,
+                               Hk=c.gdn_n_k_heads, Hv=c.gdn_n_v_heads, dk=c.gdn_head_k_dim, dv=c.gdn_head_v_dim,
+                               W=c.gdn_conv_width, eps=c.rms_eps, pdl=pdl, tok_off=seqs["off"], tok_len=seqs["len"])
+                else:
+                    K.gdn_step(self.qkv, self.state.conv[si], self.state.temporal[si], rows, L.conv_w, L.dt_bias,
+                               L.A_log, L.gnorm_w, self.conv_out, mix, bs=bs, E=E, Hk=c.gdn_n_k_heads,
+                               Hv=c.gdn_n_v_heads, dk=c.gdn_head_k_dim, dv=c.gdn_head_v_dim, W=c.gdn_conv_width,
+                               eps=c.rms_eps, pdl=pdl)
                 self._gemm(L.wout, mix, self.h, T, K.EPI_RESID_F32)
             K.add_rmsnorm(self.h, L.ln2, self.xn, M=T, d=self.d, eps=c.rms_eps, plus_one=po, pdl=pdl)
             if self.fuse_swiglu:
@@ -99,6 +120,19 @@ class NativeHybrid:
             w_next = m.layers[li + 1].ln1 if li + 1 < nL else m.final_norm
             K.add_rmsnorm(self.h, w_next, self.xn, M=T, d=self.d, eps=c.rms_eps, plus_one=po, pdl=pdl)
         return self.xn
+
+    def final_hidden(self, token_rows: torch.Tensor) -> torch.Tensor:
+        """Final-norm activations of selected token rows of the last forward."""
+        return self.xn[token_rows]
+
+    def set_context(self, ctx: int, bs: int, Es=(1, 2)) -> tuple:
+        """Record the context-length hint for the attention key splits; returns the splits chosen for forwards of
+        ``Es`` new tokens per sequence (part of a captured graph's identity: they fix the launch grids)."""
+        self.ctx = int(ctx)
+        return tuple(self._ks(bs, E) for E in Es)
+
+    def _ks(self, bs: int, E: int) -> int:
+        return K.attn_kv_splits(self.ctx, bs, self.nkv, E, self.nq // self.nkv, self.D)
 
     def lm_head(self, rows: int, row_offset: int = 0, row_step: int = 1):
         K.gemm_skinny(self.m.lm_head, self.xn[row_offset:], self.logits, M=rows, splits=1, epi=K.EPI_STORE_F32,

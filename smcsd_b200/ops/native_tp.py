@@ -92,10 +92,8 @@ class NativeLlamaTP:
         self.attn = torch.empty(max_tokens, self.nq * self.D, dtype=bf16, device=dev)
         self.act = torch.empty(max_tokens, self.ffn, dtype=bf16, device=dev)
         self.qkv = torch.empty(max_tokens, self.nqkv, dtype=f32, device=dev)
-        self.KS = 1 if block_table.shape[1] <= 6144 else (2 if block_table.shape[1] <= 16384 else 4)
-        n = max_tokens * self.nq * self.KS
-        self.part_acc = torch.empty(n * self.D if self.KS > 1 else 1, dtype=f32, device=dev)
-        self.part_ml = torch.empty(n * 2 if self.KS > 1 else 1, dtype=f32, device=dev)
+        self.ctx = 0                         # context-length hint that sizes the attention key splits, see set_context
+        self.part_acc = self.part_ml = torch.empty(1, dtype=f32, device=dev)     # unused by the fused kernel
         self.logits = torch.empty(max_logit_rows, self.Vshard, dtype=f32, device=dev)
         assert model.gu_block == 64 and (2 * self.ffn) % 128 == 0, "TP path needs the fused SwiGLU layout"
         self._splits_cache: Dict = {}
@@ -138,7 +136,7 @@ class NativeLlamaTP:
             yield
             K.attention_fused(self.qkv, positions, cache_locs, m.rope, self.kv.k[li], self.kv.v[li], self.bt, rows,
                               prefix_lens, self.attn, self.part_acc, self.part_ml, bs=bs, E=E, Hq=self.nq,
-                              Hkv=self.nkv, D=self.D, KS=self.KS, scale=scale, status=st, pdl=pdl)
+                              Hkv=self.nkv, D=self.D, KS=self._ks(bs, E), scale=scale, status=st, pdl=pdl)
             yield
             lk = ctx.link(rs="rs_o", rows_per_rank=rpr, arrive_slot=1)
             K.gemm_skinny_tp(Lw.wo, self.attn, None, M=T, splits=self._splits(self.d, self.nq * self.D, T),
@@ -163,6 +161,15 @@ class NativeLlamaTP:
             yield
         self._last_L = L
 
+
+    def set_context(self, ctx: int, bs: int, Es=(1, 2)) -> tuple:
+        """Record the context-length hint for the attention key splits; returns the splits chosen for forwards of
+        ``Es`` new tokens per sequence (part of a captured graph's identity: they fix the launch grids)."""
+        self.ctx = int(ctx)
+        return tuple(self._ks(bs, E) for E in Es)
+
+    def _ks(self, bs: int, E: int) -> int:
+        return K.attn_kv_splits(self.ctx, bs, self.nkv, E, self.nq // self.nkv, self.D)
 
     def lm_head(self, rows: int, row_offset: int = 0, row_step: int = 1):
         """This rank's vocabulary shard of the logits [rows, Vshard] (waits for the last all-gather)."""

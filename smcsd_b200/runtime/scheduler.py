@@ -42,6 +42,7 @@ class SequenceGroup:
     t_arrive: float = 0.0
     t_first_token: float = 0.0
     cycles: int = 0
+    launched: int = 0          # decode cycles enqueued for this group (processed or still in flight)
 
     @property
     def rid(self) -> str:
@@ -338,7 +339,9 @@ class SMCScheduler:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
         if self.native_runner is not None and self.native_runner.can_run_cycle(st):
-            self.native_runner.run_cycle(st, self.worker)          # one captured graph: prologue..resample
+            G = self.args.gamma + 1
+            ctx = max((len(g.req.input_ids) + 1 + (g.launched + 1) * G for g in self.running.values()), default=0)
+            self.native_runner.run_cycle(st, self.worker, ctx_hint=ctx)   # one captured graph: prologue..resample
         else:
             cin = st.prepare_cycle()
             out = self.worker.decode_cycle(cin)
@@ -355,6 +358,8 @@ class SMCScheduler:
         self.stats["decode_tokens"] += st.bs * (self.args.gamma + 1)
         snap = st.snapshot_to_host()
         self.io_bytes["d2h"] += snap.finished.numel() + 8
+        for g in self.running.values():
+            g.launched += 1
         self.pending.append((snap, list(self.running.keys())))
 
     def _process_snapshot(self, snap: HostSnapshot, rids: List[str]) -> None:
@@ -368,6 +373,15 @@ class SMCScheduler:
             g.cycles += 1
             if not self.state.group_has_active(rid, snap):
                 self._finalize(g)
+
+    def _all_certain_to_finish(self) -> bool:
+        """True when the cycles already in flight take every running group to its length limit: each cycle
+        appends gamma+1 tokens to the x0 a group starts with, so with overlap on the host knows the last
+        cycle without waiting for its snapshot and does not enqueue a wasted one."""
+        if not self.pending or not self.running:
+            return False
+        G = self.args.gamma + 1
+        return all(1 + g.launched * G >= g.req.sampling_params.max_new_tokens for g in self.running.values())
 
     def _flush_pending(self) -> None:
         while self.pending:
@@ -404,10 +418,13 @@ class SMCScheduler:
         if admitted:
             self._run_prefill(admitted)
         elif self.running:
-            self._run_decode()
-            keep = 1 if (self.args.enable_overlap and self.device.type == "cuda") else 0
-            while len(self.pending) > keep:
-                self._process_snapshot(*self.pending.popleft())
+            if self._all_certain_to_finish():
+                self._flush_pending()
+            else:
+                self._run_decode()
+                keep = 1 if (self.args.enable_overlap and self.device.type == "cuda") else 0
+                while len(self.pending) > keep:
+                    self._process_snapshot(*self.pending.popleft())
         else:
             self._flush_pending()
             if not self.waiting:

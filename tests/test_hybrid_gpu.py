@@ -100,3 +100,57 @@ def test_hybrid_state_follows_resampling_native():
     # the draft advances its state token by token, the target in gamma+1-token passes; bf16 noise only
     assert max(abs(w) for w in po.log_w_tilde) < 0.6, po.log_w_tilde
     assert sched.native_runner.check_status() == 0
+
+
+def test_native_hybrid_prefill_matches_torch_prefill():
+    """Prompt pass of a hybrid target and a hybrid draft through the kernel chains (attention layers over 16-token
+    blocks, Gated-DeltaNet layers walking each prompt once) vs the plain PyTorch forward: same cache contents and
+    the same recurrent state, the draft's one token short under the deferred schedule."""
+    from smcsd_b200.config import EngineArgs
+    from smcsd_b200.models import build_model
+    from smcsd_b200.runtime.scheduler import SMCScheduler
+    from smcsd_b200.runtime.worker import PrefillItem
+    cfg = _hybrid_cfg()
+    model = build_model(cfg, torch.bfloat16, "cuda", seed=0)
+    args = EngineArgs(model_path=cfg, draft_model_path=cfg, n_particles=4, gamma=3, max_running_requests=4,
+                      context_length=512, device="cuda", max_total_tokens=8192, backend="native",
+                      cycle_graph=False).finalize()
+    s = SMCScheduler(args, target=model, draft=model)
+    r = s.native_runner
+    lens = [37, 16, 5, 70]
+    g = torch.Generator().manual_seed(4)
+    items = []
+    for L in lens:
+        row = s.bt.alloc_parent_row()
+        s.bt.table[row, :L] = s.alloc.alloc(L)
+        items.append(PrefillItem(row, torch.randint(0, 8192, (L,), generator=g).tolist()))
+    rows = torch.tensor([it.row for it in items], device="cuda")
+    for pool in (s.state_t, s.state_d):
+        pool.clear_rows(rows)
+    r.prefill(s.worker, items)
+    torch.cuda.synchronize()
+    assert r.check_status() == 0
+    got = [x.clone() for x in (s.kv_t.k, s.kv_t.v, s.kv_d.k, s.state_t.temporal, s.state_t.conv, s.state_d.temporal,
+                               s.state_d.conv)]
+    s.kv_t.k.zero_(); s.kv_t.v.zero_(); s.kv_d.k.zero_()
+    for pool in (s.state_t, s.state_d):
+        pool.clear_rows(rows)
+    native, s.worker.native = s.worker.native, None
+    s.worker.prefill(items)
+    s.worker.native = native
+    ref = [s.kv_t.k, s.kv_t.v, s.kv_d.k, s.state_t.temporal, s.state_t.conv, s.state_d.temporal, s.state_d.conv]
+    names = ["target K", "target V", "draft K", "target temporal", "target conv", "draft temporal", "draft conv"]
+    for it, L in zip(items, lens):
+        for a, b, name in zip(got[:3], ref[:3], names):
+            # the stateful draft stops one token short, so its last prompt page is only written by the kernel path
+            n = L - 1 if name.startswith("draft") else L
+            pages = s.bt.table[it.row, :n].long()
+            x = b[:, pages].float()
+            err = (a[:, pages].float() - x).abs().max().item()
+            assert err < 0.06 * max(1.0, x.abs().max().item()), (name, L, err)
+    for a, b, name in zip(got[3:], ref[3:], names[3:]):
+        x = b[:, rows].float()
+        err = (a[:, rows].float() - x).abs().max().item()
+        assert err < 0.05 * max(1.0, x.abs().max().item()), (name, err)
+    # the two pools must differ: the draft's state stops one token before the target's
+    assert (s.state_t.temporal[:, rows] - s.state_d.temporal[:, rows]).abs().max().item() > 0

@@ -344,6 +344,8 @@ def test_state_kernels_match_torch_reference():
     (8, 9, 32, 8, 128, 3, 1, 128, False), (3, 9, 4, 4, 64, 200, 1, 64, False), (4, 9, 16, 2, 256, 260, 1, 64, True),
     (2, 5, 4, 2, 64, 0, 1, 64, False), (4, 9, 32, 8, 128, 2500, 1, 128, False), (4, 9, 32, 8, 128, 2500, 2, 128, False),
     (3, 1, 8, 2, 128, 900, 4, 128, True), (8, 9, 64, 8, 128, 100, 1, 128, False),
+    (8, 9, 32, 8, 128, 4000, 4, 128, False), (8, 1, 32, 8, 64, 4000, 8, 64, False), (4, 9, 16, 2, 256, 1000, 2, 64, True),
+    (3, 2, 8, 2, 64, 40, 4, 64, False),
 ])
 def test_attention_fused(bs, E, Hq, Hkv, D, ctx, KS, rd, extras):
     K = _K()
