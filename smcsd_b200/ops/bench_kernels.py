@@ -34,6 +34,7 @@ def peaks():
 
 def time_graph(fn, inner: int, reps: int = 20) -> float:
     side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())      # the inputs are still being written on the current stream
     with torch.cuda.stream(side):
         fn()
     torch.cuda.synchronize()
@@ -124,7 +125,7 @@ def attention_case(ctx, bs, E, Hq, Hkv, D, shared_prefix=True, plain=False, iter
         torch.cuda.synchronize()
         return None
     us = time_graph(fn, len(pools) * 4)
-    assert int(st) == 0
+    assert int(st) == 0, f"device status {int(st)}"
     uniq = (ctx if shared_prefix else ctx * bs) * kd * 2 * 2 / 1e6       # distinct K+V bytes
     touched = ctx * bs * kd * 2 * 2 / 1e6                                 # bytes requested by all particles
     return us, uniq, touched, ks
