@@ -29,6 +29,7 @@ def main(argv=None) -> None:
     p.add_argument("--batches", type=int, nargs="*", default=BATCHES)
     p.add_argument("--input-len", type=int, default=256)
     p.add_argument("--output-len", type=int, default=512)
+    p.add_argument("--grid", nargs="*", default=None, help="subset of the (gamma,n) grid, e.g. --grid 8,8 12,8")
     p.add_argument("--merge", nargs="*")
     ns = p.parse_args(argv)
     if ns.merge:
@@ -44,8 +45,9 @@ def main(argv=None) -> None:
     with open(ns.out, "w", newline="") as f:
         w = csv.writer(f)
         w.writerow(["method", "gamma", "n", "tps", "b"])
+        grid = [tuple(int(x) for x in g.split(",")) for g in ns.grid] if ns.grid else GRID
         for b in ns.batches:
-            for gamma, n in GRID:
+            for gamma, n in grid:
                 cmd = [sys.executable, "-O", "-m", "smcsd_b200.bench.offline_throughput", "--model", ns.model,
                        "--draft-model", ns.draft_model, "-N", str(n), "-g", str(gamma), "--smc-draft-temperature", "0.7",
                        "--smc-target-temperature", "0.7", "--num-prompts", str(b), "--max-running-requests", str(b),

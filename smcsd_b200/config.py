@@ -105,6 +105,10 @@ class EngineArgs:
             raise ValueError("power_alpha must be > 0")
         if self.resample_method not in ("systematic", "multinomial"):
             raise ValueError(f"unknown resample_method {self.resample_method!r}")
+        if self.quantization not in (None, "", "none"):
+            raise ValueError(f"quantization={self.quantization!r} is not supported: weights are served in bf16")
+        if self.kv_cache_dtype not in ("auto", "bf16", "bfloat16"):
+            raise ValueError(f"kv_cache_dtype={self.kv_cache_dtype!r} is not supported: the KV cache is bf16")
         self.target_temperature = max(float(self.target_temperature), 1e-5)
         self.defer_bonus = env_flag("SMC_DEFER_BONUS", self.defer_bonus, True)
         self.cycle_graph = env_flag("SMC_CYCLE_GRAPH", self.cycle_graph, True)
@@ -114,6 +118,8 @@ class EngineArgs:
         self.fast_verify = env_flag("SMC_FAST_VERIFY", self.fast_verify, True)
         self.draft_phase_graph = env_flag("SMC_DRAFT_PHASE_GRAPH", self.draft_phase_graph, False)
         self.graph_max_bs = env_int("SMC_DRAFT_GRAPH_MAX_BS", self.graph_max_bs, 64)
+        if self.cuda_graph_max_bs:          # the sweeps size the capture cap as batch x particles
+            self.graph_max_bs = max(self.graph_max_bs, int(self.cuda_graph_max_bs))
         self.graph_max_context = env_int("SMC_DRAFT_GRAPH_MAX_CONTEXT", self.graph_max_context, 8192)
         if self.disable_cuda_graph or self.draft_temperature <= 0.0:
             # greedy proposals take the eager path, like the reference (worker.py:299-300)

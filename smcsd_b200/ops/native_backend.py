@@ -54,7 +54,7 @@ class NativeLlama:
         self.attn = torch.empty(max_tokens, self.nq * self.D, dtype=bf16, device=dev)
         self.act = torch.empty(max_tokens, self.ffn, dtype=bf16, device=dev)
         self.qkv = torch.empty(max_tokens, self.nqkv, dtype=f32, device=dev)
-        self.ctx = 0                         # context-length hint that sizes the attention key splits, see set_context
+        self.ctx_hint = 0                    # context-length bound that sizes the attention key splits, see set_context
         self.part_acc = self.part_ml = torch.empty(1, dtype=f32, device=dev)     # unused by the fused kernel
         self.logits = torch.empty(max_logit_rows, self.V, dtype=f32, device=dev)
         self.fuse_swiglu = model.gu_block == 64 and (2 * self.ffn) % 128 == 0
@@ -105,11 +105,11 @@ class NativeLlama:
     def set_context(self, ctx: int, bs: int, Es=(1, 2)) -> tuple:
         """Record the context-length hint for the attention key splits; returns the splits chosen for forwards of
         ``Es`` new tokens per sequence (part of a captured graph's identity: they fix the launch grids)."""
-        self.ctx = int(ctx)
+        self.ctx_hint = int(ctx)
         return tuple(self._ks(bs, E) for E in Es)
 
     def _ks(self, bs: int, E: int) -> int:
-        return K.attn_kv_splits(self.ctx, bs, self.nkv, E, self.nq // self.nkv, self.D)
+        return K.attn_kv_splits(self.ctx_hint, bs, self.nkv, E, self.nq // self.nkv, self.D)
 
     def final_hidden(self, rows_idx: torch.Tensor) -> torch.Tensor:
         """Post-final-norm hidden rows (bf16) for callers that project with PyTorch (x0 at prefill)."""
@@ -301,6 +301,9 @@ class NativeRunner:
         self.seed = int(a.random_seed) * 1000003 + 12345 + 7919 * getattr(sched, "pp_rank", 0)
         self.graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
         self.use_graph = bool(a.cycle_graph)
+        # capture caps (SMC_DRAFT_GRAPH_MAX_BS / SMC_DRAFT_GRAPH_MAX_CONTEXT): larger batches or contexts launch eagerly
+        self.graph_max_bs = int(a.graph_max_bs)
+        self.graph_max_context = int(a.graph_max_context)
         self.T_draft, self.T_target, self.alpha = float(a.draft_temperature), float(a.target_temperature), float(a.power_alpha)
         self.defer = bool(a.defer_bonus)
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
@@ -496,8 +499,8 @@ class NativeRunner:
         st.step += 1
         bs = ns.bs
         key = (bs, self.target.set_context(ctx_hint, bs, (self.G,)), self.draft.set_context(ctx_hint, bs, (1, 2)))
-        if not self.use_graph:
-            self._full_cycle(st)
+        if not self.use_graph or bs > self.graph_max_bs or ctx_hint > self.graph_max_context:
+            self._full_cycle(st)           # same kernels, launched one by one (beyond the capture caps)
             return
         gr = self.graphs.get(key)
         if gr is None:

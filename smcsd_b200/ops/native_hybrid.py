@@ -39,7 +39,7 @@ class NativeHybrid:
         self.conv_out = torch.empty(max_tokens, model.conv_dim, dtype=f32, device=dev)
         self.attn_splits = attn_splits
         self._q = None                      # rotated queries of a prompt pass (allocated on first use)
-        self.ctx = 0                         # context-length hint that sizes the attention key splits, see set_context
+        self.ctx_hint = 0                    # context-length bound that sizes the attention key splits, see set_context
         self.part_acc = self.part_ml = torch.empty(1, dtype=f32, device=dev)     # unused by the fused kernel
         self.logits = torch.empty(max_logit_rows, self.V, dtype=f32, device=dev)
         self.fuse_swiglu = model.gu_block == 64 and (2 * self.ffn) % 128 == 0
@@ -128,11 +128,11 @@ class NativeHybrid:
     def set_context(self, ctx: int, bs: int, Es=(1, 2)) -> tuple:
         """Record the context-length hint for the attention key splits; returns the splits chosen for forwards of
         ``Es`` new tokens per sequence (part of a captured graph's identity: they fix the launch grids)."""
-        self.ctx = int(ctx)
+        self.ctx_hint = int(ctx)
         return tuple(self._ks(bs, E) for E in Es)
 
     def _ks(self, bs: int, E: int) -> int:
-        return K.attn_kv_splits(self.ctx, bs, self.nkv, E, self.nq // self.nkv, self.D)
+        return K.attn_kv_splits(self.ctx_hint, bs, self.nkv, E, self.nq // self.nkv, self.D)
 
     def lm_head(self, rows: int, row_offset: int = 0, row_step: int = 1):
         K.gemm_skinny(self.m.lm_head, self.xn[row_offset:], self.logits, M=rows, splits=1, epi=K.EPI_STORE_F32,

@@ -92,7 +92,7 @@ class NativeLlamaTP:
         self.attn = torch.empty(max_tokens, self.nq * self.D, dtype=bf16, device=dev)
         self.act = torch.empty(max_tokens, self.ffn, dtype=bf16, device=dev)
         self.qkv = torch.empty(max_tokens, self.nqkv, dtype=f32, device=dev)
-        self.ctx = 0                         # context-length hint that sizes the attention key splits, see set_context
+        self.ctx_hint = 0                    # context-length bound that sizes the attention key splits, see set_context
         self.part_acc = self.part_ml = torch.empty(1, dtype=f32, device=dev)     # unused by the fused kernel
         self.logits = torch.empty(max_logit_rows, self.Vshard, dtype=f32, device=dev)
         assert model.gu_block == 64 and (2 * self.ffn) % 128 == 0, "TP path needs the fused SwiGLU layout"
@@ -165,11 +165,11 @@ class NativeLlamaTP:
     def set_context(self, ctx: int, bs: int, Es=(1, 2)) -> tuple:
         """Record the context-length hint for the attention key splits; returns the splits chosen for forwards of
         ``Es`` new tokens per sequence (part of a captured graph's identity: they fix the launch grids)."""
-        self.ctx = int(ctx)
+        self.ctx_hint = int(ctx)
         return tuple(self._ks(bs, E) for E in Es)
 
     def _ks(self, bs: int, E: int) -> int:
-        return K.attn_kv_splits(self.ctx, bs, self.nkv, E, self.nq // self.nkv, self.D)
+        return K.attn_kv_splits(self.ctx_hint, bs, self.nkv, E, self.nq // self.nkv, self.D)
 
     def lm_head(self, rows: int, row_offset: int = 0, row_step: int = 1):
         """This rank's vocabulary shard of the logits [rows, Vshard] (waits for the last all-gather)."""
