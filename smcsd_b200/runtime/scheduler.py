@@ -25,6 +25,7 @@ from ..io_types import (AbortReq, GenerateRequest, ParticleOutput, ProfileReq, R
 from ..memory.pools import BlockTable, KVPool, KVSpec, PageAllocator, StatePool, cobudget_pages
 from ..models import build_model
 from ..utils import debug as smc_debug
+from ..utils import profiling
 from .slot_state import CycleInputs, HostSnapshot, SlotState
 from .worker import PrefillItem, SMCWorker
 
@@ -148,6 +149,7 @@ class SMCScheduler:
         self.waiting: Deque[SequenceGroup] = deque()
         self.running: Dict[str, SequenceGroup] = {}
         self.reserved_pages = 0
+        self.last_free_pages = self.min_free_pages = self.alloc.size
         self.pending: Deque = deque()       # snapshots awaiting host post-processing
         self.outbox: List = []
         self.final_gen = torch.Generator().manual_seed(seed * 31 + 5)
@@ -283,7 +285,8 @@ class SMCScheduler:
                 if pool is not None:
                     pool.clear_rows(torch.tensor([g.parent_row], device=self.device))
             items.append(PrefillItem(g.parent_row, g.req.input_ids))
-        x0 = self.worker.prefill(items).tolist()          # one blocking read per prefill batch
+        with profiling.span(f"step[PREFILL smc bs={len(items)} toks={sum(len(i.input_ids) for i in items)}]"):
+            x0 = self.worker.prefill(items).tolist()          # one blocking read per prefill batch
         self.stats["prefills"] += len(groups)
         for g, tok in zip(groups, x0):
             g.x0 = int(tok)
@@ -341,7 +344,9 @@ class SMCScheduler:
         if self.native_runner is not None and self.native_runner.can_run_cycle(st):
             G = self.args.gamma + 1
             ctx = max((len(g.req.input_ids) + 1 + (g.launched + 1) * G for g in self.running.values()), default=0)
-            self.native_runner.run_cycle(st, self.worker, ctx_hint=ctx)   # one captured graph: prologue..resample
+            # graph replays bypass module hooks, so the span is labelled here for profiler traces
+            with profiling.span(f"step[DECODE smc-cycle groups={len(self.running)} ctx<={ctx}]"):
+                self.native_runner.run_cycle(st, self.worker, ctx_hint=ctx)   # one captured graph: prologue..resample
         else:
             cin = st.prepare_cycle()
             out = self.worker.decode_cycle(cin)
@@ -355,6 +360,7 @@ class SMCScheduler:
             if len(self._cycle_events) > 4096:
                 del self._cycle_events[:2048]
         self.stats["cycles"] += 1
+        self.stats["group_cycles"] = self.stats.get("group_cycles", 0) + len(self.running)
         self.stats["decode_tokens"] += st.bs * (self.args.gamma + 1)
         snap = st.snapshot_to_host()
         self.io_bytes["d2h"] += snap.finished.numel() + 8
@@ -366,6 +372,10 @@ class SMCScheduler:
         snap.wait()
         if snap.alloc_error:
             raise RuntimeError("device page allocator ran dry inside a decode cycle")
+        self.last_free_pages = snap.free_pages
+        self.min_free_pages = min(self.min_free_pages, snap.free_pages)
+        if self.native_runner is not None:
+            self.stats["resampled_groups"] = int(snap.resampled[0])
         for rid in rids:
             g = self.running.get(rid)
             if g is None:
@@ -468,10 +478,24 @@ class SMCScheduler:
             self._cycle_events.clear()
         return out
 
+    def metrics(self) -> dict:
+        """Serving metrics: KV pool occupancy (from the last cycle snapshot), resample rate per group-cycle,
+        device-timed milliseconds per decode cycle when cycle timing is on."""
+        cyc = max(1, self.stats.get("group_cycles", 0))
+        m = {"kv_pages": self.alloc.size, "kv_pages_free": self.last_free_pages,
+             "kv_occupancy": 1.0 - self.last_free_pages / max(1, self.alloc.size),
+             "kv_occupancy_peak": 1.0 - self.min_free_pages / max(1, self.alloc.size),
+             "kv_pages_reserved": self.reserved_pages,
+             "resample_rate": self.stats.get("resampled_groups", 0) / cyc,
+             "decode_cycles": self.stats.get("cycles", 0), "decode_tokens": self.stats.get("decode_tokens", 0)}
+        if self._time_cycles:
+            m["cycle_ms"] = self.cycle_timing()
+        return m
+
     def server_info(self) -> dict:
         return dict(args=self.args.to_dict(), backend=self.backend, device=str(self.device),
                     kv_pages=self.alloc.size, context_len=self.context_len, stats=dict(self.stats),
-                    n_running=len(self.running), n_waiting=len(self.waiting),
+                    n_running=len(self.running), n_waiting=len(self.waiting), metrics=self.metrics(),
                     target=self.target.cfg.name, draft=self.draft.cfg.name)
 
     def flush_cache(self) -> bool:

@@ -53,6 +53,7 @@ class HostSnapshot:
         pin = device.type == "cuda"
         self.finished = torch.zeros(n_slots, dtype=torch.bool, pin_memory=pin)
         self.scalars = torch.zeros(4, dtype=torch.int32, pin_memory=pin)   # free_count, alloc_error, n_resampled, step
+        self.resampled = torch.zeros(1, dtype=torch.int64, pin_memory=pin)   # cumulative count of resampled groups
         self.group_active = None            # [max_groups] running particles per group over all ranks (particle-parallel)
         self.event = torch.cuda.Event() if pin else None
 
@@ -329,6 +330,7 @@ class SlotState:
         snap.finished.copy_(self.finished, non_blocking=True)
         snap.scalars[0:1].copy_(self.alloc.free_count, non_blocking=True)
         snap.scalars[1:2].copy_(self.alloc.error_flag, non_blocking=True)
+        snap.resampled.copy_(self.counters[2:3], non_blocking=True)     # groups resampled so far (device counter)
         if self.pp is not None:
             if snap.group_active is None:
                 snap.group_active = torch.zeros(self.max_groups, dtype=torch.int32, pin_memory=self._pin)
