@@ -173,7 +173,11 @@ def main():
              ("1B gate_up+swiglu", 16384, 2048, 8, "swiglu"), ("1B down", 2048, 8192, 8, "resid"),
              ("1B lm_head", 128256, 2048, 8, "store"), ("8B qkv", 6144, 4096, 72, "store"),
              ("8B o_proj", 4096, 4096, 72, "resid"), ("8B gate_up+swiglu", 28672, 4096, 72, "swiglu"),
-             ("8B down", 4096, 14336, 72, "resid"), ("8B lm_head", 128256, 4096, 72, "store")]
+             ("8B down", 4096, 14336, 72, "resid"), ("8B lm_head", 128256, 4096, 72, "store"),
+             # batched serving: 8 and 16 requests x 8 particles x 9 verify tokens
+             ("8B gate_up M=576", 28672, 4096, 576, "swiglu"), ("8B down M=576", 4096, 14336, 576, "resid"),
+             ("8B gate_up M=1152", 28672, 4096, 1152, "swiglu"), ("8B down M=1152", 4096, 14336, 1152, "resid"),
+             ("1B gate_up M=128", 16384, 2048, 128, "swiglu"), ("1B down M=128", 2048, 8192, 128, "resid")]
     print(f"peaks ({src}): HBM {hbm:.0f} GB/s, bf16 {tf:.0f} TFLOP/s")
     print(f"{'case':22s} {'MB':>7s} {'splits':>6s} {'us':>8s} {'GB/s':>8s} {'of HBM':>7s} {'TFLOP/s':>8s}")
     for name, N, Kd, M, epi in table:

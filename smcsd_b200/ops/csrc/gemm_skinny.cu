@@ -46,6 +46,7 @@ struct TpLink {
 struct GemmParams {
   int N, K, M;          // weight rows, reduction length, token rows
   int kblocks;          // ceil(K / 64)
+  int m_tiles;          // token tiles (grid x = weight slabs * m_tiles)
   int splits;
   void* out;            // fp32 [splits, M, N] | bf16 [M, ldo]
   int ldo;
@@ -93,7 +94,9 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
   volatile int* sh_consumed = sh_abort + 2;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tile = blockIdx.x, split = blockIdx.y, m_tile = blockIdx.z;
+  // token tiles of one weight slab are neighbours in launch order, so the slab is fetched from HBM once and
+  // the other token tiles find it in L2
+  const int n_tile = blockIdx.x / p.m_tiles, split = blockIdx.y, m_tile = blockIdx.x % p.m_tiles;
   // Let the next kernel of the stream start its prologue (and its weight prefetch) right away;
   // it still waits for this grid to finish before it touches anything this grid writes.
   if (p.pdl) pdl_launch_dependents();
@@ -566,7 +569,8 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
   if (rc) return rc;
   rc = make_tmap(&tmX, X, M, K, ldx, bn);
   if (rc) return rc;
-  dim3 grid((N + 127) / 128, p.splits, (M + bn - 1) / bn);
+  p.m_tiles = (M + bn - 1) / bn;
+  dim3 grid(((N + 127) / 128) * p.m_tiles, p.splits, 1);
   switch (epi) {
     case EPI_PARTIAL_F32: return dispatch_bn<EPI_PARTIAL_F32>(bn, tmW, tmX, p, grid, stream);
     case EPI_BF16: return dispatch_bn<EPI_BF16>(bn, tmW, tmX, p, grid, stream);
