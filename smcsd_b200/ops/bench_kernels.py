@@ -192,6 +192,8 @@ def main():
     for ctx in (256, 1024, 2048, 4096):
         cases.append((f"1B decode E=1 ctx {ctx}", ctx, 8, 1, (32, 8, 64), True))
     cases.append(("8B verify E=9 ctx 4096 private", 4096, 8, 9, (32, 8, 128), False))
+    cases.append(("1B decode E=1 ctx 384 bs=128", 384, 128, 1, (32, 8, 64), False))      # 16 requests x 8 particles
+    cases.append(("8B verify E=9 ctx 384 bs=128", 384, 128, 9, (32, 8, 128), False))
     for name, ctx, bs, E, dims, shared in cases:
         auto = K.attn_kv_splits(ctx, bs, dims[1], E, dims[0] // dims[1], dims[2])
         for ks in sorted({1, 2, 4, auto} if ctx >= 512 else {1, auto}):

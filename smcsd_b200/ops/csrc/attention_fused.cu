@@ -547,6 +547,16 @@ static size_t fused_smem_bytes(int D, int n_mt, int n_kw, int stg) {
   return b + (tiles > merge ? tiles : merge);
 }
 
+// Key-ways per CTA: as many as fit in 8 warps and ~200 KB of shared memory.  Grids of several waves trade
+// key-ways for residency (smaller CTAs, more of them per SM), so one CTA's serial phases overlap another's tiles.
+static int pick_key_ways(int D, int n_mt, long long ctas) {
+  int n_kw = 8 / n_mt;
+  if (n_kw < 1) n_kw = 1;
+  while (n_kw > 1 && fused_smem_bytes(D, n_mt, n_kw, 2) > 200 * 1024) --n_kw;
+  if (ctas > 2 * 148 && n_kw > 4) n_kw = 4;     // measured at 1024 CTAs: 4 key-ways 45 us, 8: 67 us, 2: 57 us
+  return n_kw;
+}
+
 }  // namespace smc
 
 // Key-range splits (1, 2, 4 or 8) for `bs` sequences of about `ctx` cached tokens.  A split is taken while the grid
@@ -556,9 +566,7 @@ SMC_API int smc_attention_kv_splits(int bs, int E, int Hq, int Hkv, int D, int c
   using namespace smc;
   if (bs <= 0 || Hkv <= 0 || Hq % Hkv || E < 1) return 1;
   const int R = E * (Hq / Hkv), n_mt = (R + 15) / 16;
-  int n_kw = 8 / n_mt;
-  if (n_kw < 1) n_kw = 1;
-  while (n_kw > 1 && fused_smem_bytes(D, n_mt, n_kw, 2) > 200 * 1024) --n_kw;
+  const int n_kw = pick_key_ways(D, n_mt, 0);
   const bool two_per_sm = fused_smem_bytes(D, n_mt, n_kw, 2) <= 110 * 1024;
   const long long base = (long long)bs * Hkv;
   int ks = 1;
@@ -589,9 +597,7 @@ SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, 
   const int G = Hq / Hkv, R = E * G;
   const int n_mt = (R + 15) / 16;
   if (n_mt > 8) return -71;
-  int n_kw = 8 / n_mt;                   // key-ways: as many as fit in 8 warps and ~200 KB of shared memory
-  if (n_kw < 1) n_kw = 1;
-  while (n_kw > 1 && fused_smem_bytes(D, n_mt, n_kw, 2) > 200 * 1024) --n_kw;
+  int n_kw = pick_key_ways(D, n_mt, (long long)bs * Hkv * KS);
   // Ring depth: a grid that fits the GPU in one wave with one CTA per SM spends the whole shared memory on tiles
   // in flight; larger grids stay under half of it so two CTAs share an SM.
   const size_t budget = (size_t)bs * Hkv * KS <= 148 ? 200 * 1024 : 100 * 1024;
