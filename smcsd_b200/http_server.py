@@ -2,7 +2,7 @@
 
 Routes: ``/generate`` (native), ``/v1/completions`` and ``/v1/models`` (OpenAI style), ``/health``,
 ``/health_generate``, ``/server_info`` (alias ``/get_server_info``), ``/get_model_info``,
-``/flush_cache``.  Concurrent HTTP requests are multiplexed onto the SMC scheduler by a pump thread
+``/flush_cache``; ``"stream": true`` on the two generation routes answers as server-sent events.  Concurrent HTTP requests are multiplexed onto the SMC scheduler by a pump thread
 that owns the engine: it feeds new requests into the scheduler between decode cycles and resolves
 each request's future when its group finalizes, so many clients share the batched decode loop.
 Same CLI flags and routes as the reference server (smcsd/http_server.py:140-212; the routes it
@@ -121,8 +121,20 @@ class EngineBridge:
 
 
 def build_app(engine, model_name: str = "smc"):
+    import json as _json
+
     from fastapi import FastAPI, HTTPException
-    from fastapi.responses import JSONResponse
+    from fastapi.responses import JSONResponse, StreamingResponse
+
+    def _sse(coro_factory):
+        """Server-sent-event framing for ``stream: true``.  SMC picks the returned particle when the group
+        finishes, so the stream carries one data event with the complete result, then ``[DONE]``."""
+        async def gen():
+            res = await coro_factory()
+            for item in (res if isinstance(res, list) else [res]):
+                yield "data: " + _json.dumps(item) + "\n\n"
+            yield "data: [DONE]\n\n"
+        return StreamingResponse(gen(), media_type="text/event-stream")
 
     app = FastAPI(title="smcsd_b200")
     bridge = EngineBridge(engine)
@@ -169,8 +181,17 @@ def build_app(engine, model_name: str = "smc"):
         many = isinstance(src, list) and len(src) > 0 and isinstance(src[0], (list, str))
         items = src if many else [src]
         plist = params if isinstance(params, list) else [params] * len(items)
-        outs = await asyncio.gather(*[_one(_encode(x), p) for x, p in zip(items, plist)])
-        return outs if many else outs[0]
+        async def run():
+            outs = await asyncio.gather(*[_one(_encode(x), p) for x, p in zip(items, plist)])
+            return outs if many else outs[0]
+        if body.get("stream"):
+            encoded = [_encode(x) for x in items]          # malformed input fails before the stream opens
+
+            async def run_stream():
+                outs = await asyncio.gather(*[_one(e, p) for e, p in zip(encoded, plist)])
+                return outs if many else outs[0]
+            return _sse(run_stream)
+        return await run()
 
     @app.post("/v1/completions")
     async def completions(body: Dict[str, Any]):
@@ -184,15 +205,21 @@ def build_app(engine, model_name: str = "smc"):
             params["stop"] = body["stop"]
         if body.get("stop_token_ids"):
             params["stop_token_ids"] = body["stop_token_ids"]
-        outs = await asyncio.gather(*[_one(_encode(p), params) for p in prompts])
-        choices = [{"index": i, "text": o["text"], "token_ids": o["output_ids"],
-                    "finish_reason": "length" if o["meta_info"]["finish_reason"]["type"] == "length" else "stop"}
-                   for i, o in enumerate(outs)]
-        pt = sum(o["meta_info"]["prompt_tokens"] for o in outs)
-        ct = sum(o["meta_info"]["completion_tokens"] for o in outs)
-        return {"id": "cmpl-" + uuid.uuid4().hex, "object": "text_completion", "created": int(time.time()),
-                "model": body.get("model", model_name), "choices": choices,
-                "usage": {"prompt_tokens": pt, "completion_tokens": ct, "total_tokens": pt + ct}}
+        encoded = [_encode(p) for p in prompts]
+
+        async def run():
+            outs = await asyncio.gather(*[_one(e, params) for e in encoded])
+            choices = [{"index": i, "text": o["text"], "token_ids": o["output_ids"],
+                        "finish_reason": "length" if o["meta_info"]["finish_reason"]["type"] == "length" else "stop"}
+                       for i, o in enumerate(outs)]
+            pt = sum(o["meta_info"]["prompt_tokens"] for o in outs)
+            ct = sum(o["meta_info"]["completion_tokens"] for o in outs)
+            return {"id": "cmpl-" + uuid.uuid4().hex, "object": "text_completion", "created": int(time.time()),
+                    "model": body.get("model", model_name), "choices": choices,
+                    "usage": {"prompt_tokens": pt, "completion_tokens": ct, "total_tokens": pt + ct}}
+        if body.get("stream"):
+            return _sse(run)
+        return await run()
 
     @app.get("/v1/models")
     async def models():

@@ -501,10 +501,28 @@ SMC_API int smc_gemm_bn_for(int M) {
   return 256;
 }
 
+// Token-tile width for a weight matrix of N rows.  Up to 256 tokens one tile covers the batch.  Beyond that every
+// CTA is bound by the bytes it pulls through its SM (a 128-row weight slab plus BN activation rows per k-block),
+// so the width is the one that minimises waves x bytes per CTA: e.g. 1152 tokens on 32 slabs run as 288 tiles of
+// 128 tokens (two full waves) rather than 160 tiles of 256 (one full wave and a nearly empty one).
+static int bn_for(int M, int N) {
+  if (M <= 256 || N <= 0) return smc_gemm_bn_for(M);
+  const long long n_tiles = (N + 127) / 128;
+  long long best_cost = 0;
+  int best = 256;
+  for (int bn = 256; bn >= 128; bn -= 128) {
+    const long long tiles = n_tiles * ((M + bn - 1) / bn);
+    const long long waves = (tiles + 147) / 148;
+    const long long cost = waves * (128 + bn);
+    if (best_cost == 0 || cost < best_cost) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
 // Split-K factor that gives every SM about two resident CTAs while keeping >= 4 k-blocks per CTA.
 SMC_API int smc_gemm_default_splits(int N, int K, int M) {
   const int n_tiles = (N + 127) / 128;
-  const int bn = smc_gemm_bn_for(M);
+  const int bn = bn_for(M, N);
   const int m_tiles = (M + bn - 1) / bn;
   const int kblocks = (K + 63) / 64;
   int s = (296 + n_tiles * m_tiles - 1) / (n_tiles * m_tiles);
@@ -519,7 +537,7 @@ SMC_API int smc_gemm_default_splits(int N, int K, int M) {
 // Cluster size (1, 2, 4 or 8) for the on-chip split-K epilogues.
 SMC_API int smc_gemm_cluster_splits(int N, int K, int M) {
   const int n_tiles = (N + 127) / 128;
-  const int bn = smc_gemm_bn_for(M);
+  const int bn = bn_for(M, N);
   const int m_tiles = (M + bn - 1) / bn;
   const int kblocks = (K + 63) / 64;
   int s = 1;
@@ -547,7 +565,7 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
   if (clustered && !(splits == 1 || splits == 2 || splits == 4 || splits == 8)) return -23;
   if (epi == EPI_SWIGLU_BF16 && (N % 128) != 0) return -22;
   if (epi == EPI_RS_F32 && (tp == nullptr || tp->tp < 1 || tp->tp > 8 || tp->rows_per_rank < 1)) return -24;
-  const int bn = smc_gemm_bn_for(M);
+  const int bn = bn_for(M, N);
   GemmParams p;
   p.N = N; p.K = K; p.M = M;
   p.kblocks = (K + 63) / 64;

@@ -78,3 +78,19 @@ def test_openai_completions_and_errors(server):
     bad = requests.post(server + "/generate", json={"input_ids": [1, 2], "sampling_params": {"max_new_tokens": 4, "stop": ["x"]}}, timeout=60)
     assert bad.status_code == 400
     assert requests.post(server + "/generate", json={}, timeout=10).status_code == 400
+
+
+def test_streaming_routes_answer_as_server_sent_events(server):
+    import json
+    for path, body in (("/generate", {"input_ids": [3, 4, 5, 6, 7], "stream": True,
+                                      "sampling_params": {"max_new_tokens": 6, "ignore_eos": True}}),
+                       ("/v1/completions", {"prompt": [5, 6, 7, 8], "max_tokens": 6, "ignore_eos": True, "stream": True})):
+        r = requests.post(server + path, json=body, timeout=120, stream=True)
+        assert r.status_code == 200 and r.headers["content-type"].startswith("text/event-stream")
+        events = [ln[len("data: "):] for ln in r.iter_lines(decode_unicode=True) if ln and ln.startswith("data: ")]
+        assert events[-1] == "[DONE]" and len(events) == 2
+        payload = json.loads(events[0])
+        n = payload["meta_info"]["completion_tokens"] if path == "/generate" else payload["usage"]["completion_tokens"]
+        assert n == 6
+    m = requests.get(server + "/server_info", timeout=10).json()["metrics"]
+    assert 0.0 <= m["kv_occupancy"] <= 1.0 and m["decode_cycles"] >= 1
