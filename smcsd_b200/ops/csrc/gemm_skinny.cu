@@ -534,7 +534,10 @@ SMC_API int smc_gemm_default_splits(int N, int K, int M) {
   return s;
 }
 
-// Cluster size (1, 2, 4 or 8) for the on-chip split-K epilogues.
+// Cluster size for the on-chip split-K epilogues: the largest power of two that keeps the grid within about two
+// CTAs per SM and leaves every CTA at least two k-blocks.  (Any size from 1 to 8 is accepted by the kernel; sizes
+// chosen to fill exactly one wave with one CTA per SM, e.g. 3 for 48 slabs, measured 8-20 % slower than the next
+// power of two with two CTAs per SM, whose rings keep more bytes in flight.)
 SMC_API int smc_gemm_cluster_splits(int N, int K, int M) {
   const int n_tiles = (N + 127) / 128;
   const int bn = bn_for(M, N);
@@ -547,7 +550,7 @@ SMC_API int smc_gemm_cluster_splits(int N, int K, int M) {
 
 // W [N, K] bf16 row-major, X [M, ldx] bf16 row-major (ldx >= K).
 // epi 3: out = fp32 [M, ldo] = X W^T;  epi 4: out (fp32 [M, ldo]) += X W^T.  Both reduce split-K inside a
-// thread-block cluster, so splits must be 1, 2, 4 or 8.
+// thread-block cluster, so splits must be 1..8.
 // epi 0: out = fp32 [splits, M, N] partials; epi 1: out = bf16 [M, ldo] (splits must be 1);
 // epi 2: out = bf16 [M, ldo] holding SwiGLU(gate, up) for N/2 channels (splits must be 1, N % 128 == 0).
 struct NormLink {            // host-side description of the folded RMSNorm (all fields optional)
@@ -562,7 +565,7 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
   if ((K % 8) != 0 || (ldx % 8) != 0) return -20;       // row pitch must be a multiple of 16 bytes
   const bool clustered = epi == EPI_STORE_F32 || epi == EPI_RESID_F32 || epi == EPI_RS_F32;
   if (!clustered && epi != EPI_PARTIAL_F32 && splits != 1) return -21;
-  if (clustered && !(splits == 1 || splits == 2 || splits == 4 || splits == 8)) return -23;
+  if (clustered && (splits < 1 || splits > 8)) return -23;
   if (epi == EPI_SWIGLU_BF16 && (N % 128) != 0) return -22;
   if (epi == EPI_RS_F32 && (tp == nullptr || tp->tp < 1 || tp->tp > 8 || tp->rows_per_rank < 1)) return -24;
   const int bn = bn_for(M, N);

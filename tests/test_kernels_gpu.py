@@ -43,6 +43,7 @@ def test_gemm_partials(N, Kd, M, splits):
 @pytest.mark.parametrize("N,Kd,M,splits", [
     (3072, 2048, 8, 8), (2048, 8192, 8, 8), (6144, 4096, 72, 4), (4096, 14336, 72, 4), (2048, 2048, 8, 1),
     (1024, 512, 40, 2), (128256, 2048, 8, 1), (300, 1024, 9, 4), (2048, 2048, 200, 2), (4096, 4096, 72, 0),
+    (6144, 4096, 72, 3), (3072, 2048, 8, 6), (3072, 2048, 16, 5), (2048, 4096, 33, 7), (4096, 14336, 600, 0),
 ])
 def test_gemm_cluster_splitk(N, Kd, M, splits):
     """Split-K reduced on chip through distributed shared memory: plain store and residual accumulate."""
