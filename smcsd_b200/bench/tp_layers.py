@@ -30,6 +30,8 @@ def main(argv=None) -> None:
     ap.add_argument("--E", type=int, default=9)
     ap.add_argument("--ctx", type=int, default=256)
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--shard-like", type=int, default=0,
+                    help="shrink heads and FFN by this factor (run on one rank to see one shard's chain without peers)")
     ap.add_argument("--stage-times", action="store_true",
                     help="also time every kernel of the fused chain (eager launches with an event after each)")
     ns = ap.parse_args(argv)
@@ -48,6 +50,9 @@ def main(argv=None) -> None:
     dist.init_process_group("nccl", device_id=dev)
     K.tp_lib()
     cfg = dataclasses.replace(preset(ns.model), n_layers=ns.layers)
+    if ns.shard_like > 1:
+        cfg = dataclasses.replace(cfg, n_heads=cfg.n_heads // ns.shard_like, n_kv_heads=cfg.n_kv_heads // ns.shard_like,
+                                  ffn_size=cfg.ffn_size // ns.shard_like, name=f"{cfg.name}/shard{ns.shard_like}")
     bs, E, P = ns.bs, ns.E, ns.ctx
     T = bs * E
     n_pages = bs * (P + E) + 8

@@ -142,3 +142,53 @@ def test_native_prefill_matches_torch_prefill():
             ref = b[:, pages].float()
             assert (a[:, pages].float() - ref).abs().max().item() < 0.06 * max(1.0, ref.abs().max().item())
     assert x0_native.shape == x0_torch.shape
+
+
+def test_graph_equals_eager_across_attention_split_plans():
+    """A request whose context grows through several attention split plans (each has its own captured graph)
+    produces the same tokens as the eager kernel chain."""
+    from smcsd_b200.ops import native as K
+    outs, keys = {}, None
+    for graph in (False, True):
+        eng = _engine(backend="native", cycle_graph=graph, max_running_requests=1, context_length=2048,
+                      max_total_tokens=32768)
+        o = eng.generate(input_ids=_prompts(1, L=180, seed=5), sampling_params={"max_new_tokens": 700, "ignore_eos": True})
+        assert o[0]["completion_tokens"] == 700
+        assert eng._sched.native_runner.check_status() == 0
+        eng._sched.check_idle_invariants()
+        outs[graph] = o[0]
+        if graph:
+            keys = set(eng._sched.native_runner.graphs.keys())
+    assert outs[False]["output_ids"] == outs[True]["output_ids"]
+    assert len(keys) >= 2, keys                      # the split plan changed at least once along the way
+    assert K.attn_kv_splits(1500, 4, 2, 1, 4, 128) >= K.attn_kv_splits(100, 4, 2, 1, 4, 128)
+
+
+def test_overlapped_loop_equals_sequential_loop():
+    """Post-processing cycle t-1 after enqueuing cycle t only delays finish detection: same outputs."""
+    outs = {}
+    for overlap in (False, True):
+        eng = _engine(backend="native", enable_overlap=overlap)
+        outs[overlap] = eng.generate(input_ids=_prompts(3, L=24, seed=9),
+                                     sampling_params={"max_new_tokens": 33, "stop_token_ids": list(range(16))})
+        eng._sched.check_idle_invariants()
+    for a, b in zip(outs[False], outs[True]):
+        assert a["output_ids"] == b["output_ids"] and a["finish_reason"] == b["finish_reason"]
+
+
+def test_abort_mid_decode_releases_pages_and_slots():
+    from smcsd_b200.io_types import GenerateRequest, RequestOutput, SamplingParams
+    eng = _engine(backend="native", max_running_requests=2)
+    s = eng._sched
+    for i, p in enumerate(_prompts(2, L=30, seed=11)):
+        s.add_request(GenerateRequest(f"r{i}", p, SamplingParams(max_new_tokens=200, ignore_eos=True)))
+    for _ in range(6):
+        s.step()
+    assert len(s.running) == 2
+    s.abort("r0")
+    outs = s.run_until_idle()
+    done = {o.rid: o for o in outs if isinstance(o, RequestOutput)}
+    assert done["r0"].aborted and not done["r1"].aborted and len(done["r1"].output_ids) == 200
+    s.check_idle_invariants()
+    s.alloc.check_conservation()
+    assert s.native_runner.check_status() == 0
