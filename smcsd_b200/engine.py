@@ -224,9 +224,12 @@ class SMCEngine:
 
     def start_profile(self, output_dir: Optional[str] = None, num_steps: Optional[int] = None,
                       activities: Optional[List[str]] = None, with_stack: bool = False,
-                      record_shapes: bool = False, profile_by_stage: bool = False):
+                      record_shapes: bool = False, profile_by_stage: bool = False,
+                      profile_stages: Optional[List[str]] = None):
+        """Start a torch.profiler capture in every scheduler (same arguments as the reference,
+        smcsd/engine.py:376-413); ``profile_stages`` restricts a by-stage capture to "prefill" and / or "decode"."""
         return self._rpc_roundtrip(ProfileReq("start", output_dir, num_steps, activities, with_stack,
-                                              record_shapes, profile_by_stage))
+                                              record_shapes, profile_by_stage, profile_stages))
 
     def stop_profile(self):
         return self._rpc_roundtrip(ProfileReq("stop"))

@@ -93,6 +93,7 @@ class ProfileReq:
     with_stack: bool = False
     record_shapes: bool = False
     profile_by_stage: bool = False
+    profile_stages: Optional[List[str]] = None
 
 
 @dataclass

@@ -425,6 +425,8 @@ class SMCScheduler:
         if self.profiler is not None:
             self._profile_tick()
         admitted = self._admit()
+        if self.profiler is not None and (admitted or self.running):
+            self.profiler.enter_stage("prefill" if admitted else "decode")
         if admitted:
             self._run_prefill(admitted)
         elif self.running:
@@ -511,8 +513,9 @@ class SMCScheduler:
             return {"ok": True}
         if self.profiler is not None:
             path = self.profiler.stop()
+            paths = list(self.profiler.paths)
             self.profiler = None
-            return {"ok": True, "trace": path}
+            return {"ok": True, "trace": path, "traces": paths}
         return {"ok": False, "message": "profiler not running"}
 
     def _profile_tick(self) -> None:

@@ -16,13 +16,22 @@ import torch
 
 
 class SchedulerProfiler:
+    """torch.profiler capture driven by the scheduler.  With ``profile_by_stage`` the capture is cut at every change
+    between prefill and decode iterations and each piece is exported with its stage in the file name
+    (``smc-<time>-rank<r>-<stage>.trace.json.gz``); ``profile_stages`` keeps only the named stages."""
+
     def __init__(self, req, rank: int = 0):
         self.req = req
         self.rank = rank
         self.prof = None
+        self.stage: Optional[str] = None
+        self.paths: List[str] = []
         self.out_dir = req.output_dir or os.environ.get("SMC_PROFILE_DIR", "/tmp/smcsd_b200_profile")
+        self.by_stage = bool(getattr(req, "profile_by_stage", False))
+        st = getattr(req, "profile_stages", None)
+        self.stages = {x.lower() for x in st} if st else None
 
-    def start(self) -> None:
+    def _begin(self) -> None:
         acts = []
         wanted = [a.upper() for a in (self.req.activities or ["CPU", "GPU"])]
         if "CPU" in wanted:
@@ -33,15 +42,34 @@ class SchedulerProfiler:
                                            record_shapes=self.req.record_shapes)
         self.prof.start()
 
-    def stop(self) -> Optional[str]:
+    def _end(self) -> Optional[str]:
         if self.prof is None:
             return None
         self.prof.stop()
         os.makedirs(self.out_dir, exist_ok=True)
-        path = os.path.join(self.out_dir, f"smc-{int(time.time())}-rank{self.rank}.trace.json.gz")
+        tag = f"-{self.stage}" if (self.by_stage and self.stage) else ""
+        path = os.path.join(self.out_dir, f"smc-{time.time_ns() // 1000000}-rank{self.rank}{tag}.trace.json.gz")
         self.prof.export_chrome_trace(path)
         self.prof = None
+        self.paths.append(path)
         return path
+
+    def start(self) -> None:
+        if not self.by_stage:
+            self._begin()
+
+    def enter_stage(self, stage: str) -> None:
+        """Called by the scheduler before a prefill or decode iteration (by-stage captures only)."""
+        if not self.by_stage or stage == self.stage:
+            return
+        self._end()
+        self.stage = stage
+        if self.stages is None or stage in self.stages:
+            self._begin()
+
+    def stop(self) -> Optional[str]:
+        self._end()
+        return self.paths[-1] if self.paths else None
 
 
 @contextmanager

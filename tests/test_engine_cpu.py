@@ -62,3 +62,27 @@ def test_rejected_features_abort():
     eng = _engine()
     o = eng.generate(input_ids=_prompts(1)[0], sampling_params={"max_new_tokens": 8, "stop": ["abc"]})
     assert o.get("aborted") and "stop strings" in o["error"]
+
+
+def test_profiler_traces_whole_run_and_by_stage(tmp_path):
+    """start_profile / stop_profile write Chrome traces; a by-stage capture writes one file per prefill / decode
+    stretch and honours the stage filter."""
+    import glob
+    eng = _engine()
+    ids = [list(range(3, 20))]
+    sp = {"max_new_tokens": 9, "ignore_eos": True}
+    eng.start_profile(output_dir=str(tmp_path / "whole"), activities=["CPU"])
+    eng.generate(input_ids=ids, sampling_params=sp)
+    eng.stop_profile()
+    assert len(glob.glob(str(tmp_path / "whole" / "*.trace.json.gz"))) == 1
+    eng.start_profile(output_dir=str(tmp_path / "staged"), activities=["CPU"], profile_by_stage=True)
+    eng.generate(input_ids=ids, sampling_params=sp)
+    eng.stop_profile()
+    names = sorted(glob.glob(str(tmp_path / "staged" / "*.trace.json.gz")))
+    assert any(n.endswith("-prefill.trace.json.gz") for n in names) and any(n.endswith("-decode.trace.json.gz") for n in names)
+    eng.start_profile(output_dir=str(tmp_path / "decode_only"), activities=["CPU"], profile_by_stage=True,
+                      profile_stages=["decode"])
+    eng.generate(input_ids=ids, sampling_params=sp)
+    eng.stop_profile()
+    names = glob.glob(str(tmp_path / "decode_only" / "*.trace.json.gz"))
+    assert names and all(n.endswith("-decode.trace.json.gz") for n in names)
