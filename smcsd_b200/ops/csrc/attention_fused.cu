@@ -37,6 +37,7 @@ struct FusedAttnParams {
   const int* rows;           // [bs]
   const int* prefix_lens;    // [bs]
   __nv_bfloat16* out;        // [T, Hq * D]
+  int gsub;                  // query heads of one kv head are dealt to gsub CTAs (grid z)
   int E, Hq, Hkv, KS, n_mt, n_kw, stg;    // stg: stages of each key-way's K/V tile ring (2..6)
   float scale;
   int* status;
@@ -177,7 +178,8 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   constexpr bool Q_REGS = D <= 128;
   extern __shared__ __align__(16) uint8_t smem_fa[];
   const int n_mt = p.n_mt, n_kw = p.n_kw;
-  const int G = p.Hq / p.Hkv, R = p.E * G, Rpad = n_mt * 16;
+  // G: query heads per kv head handled by this CTA; hbase: its first query head
+  const int G = p.Hq / p.Hkv / p.gsub, R = p.E * G, Rpad = n_mt * 16;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_fa);             // [Rpad][LD]
   __nv_bfloat16* Kn = Qs + (size_t)Rpad * LD;                                 // [16][LD]
   __nv_bfloat16* Vn = Kn + 16 * LD;                                           // [16][LD]
@@ -186,6 +188,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   constexpr int TILE = TK * LD;
 
   const int b = blockIdx.x / p.Hkv, kvh = blockIdx.x % p.Hkv, ks = blockIdx.y;
+  const int hbase = kvh * (p.Hq / p.Hkv) + (int)blockIdx.z * (p.Hq / p.Hkv / p.gsub);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mt = warp % n_mt, kw = warp / n_mt;
   const int nwarps = blockDim.x >> 5;
@@ -260,7 +263,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (r < R) {
         const int e = r / G, gq = r % G;
-        v = *reinterpret_cast<const uint4*>(p.q_in + ((size_t)(b * p.E + e) * p.Hq + kvh * G + gq) * D + c * 8);
+        v = *reinterpret_cast<const uint4*>(p.q_in + ((size_t)(b * p.E + e) * p.Hq + hbase + gq) * D + c * 8);
       }
       *reinterpret_cast<uint4*>(Qs + (size_t)r * LD + c * 8) = v;
     }
@@ -273,7 +276,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       if (j < R) {
         const int e = j / G, gq = j % G;
         dst = Qs + (size_t)j * LD;
-        src = p.qkv + (size_t)(b * p.E + e) * p.ld_qkv + p.q_off + (size_t)(kvh * G + gq) * D;
+        src = p.qkv + (size_t)(b * p.E + e) * p.ld_qkv + p.q_off + (size_t)(hbase + gq) * D;
         pos = s_pos[e];
       } else {
         const bool is_k = j < R + p.E;
@@ -365,7 +368,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
     __syncthreads();
   }
   // new K/V rows go to their pages (one CTA per (sequence, kv head) writes them)
-  if (ks == p.KS - 1 && !pool_only) {
+  if (ks == p.KS - 1 && !pool_only && blockIdx.z == 0) {
     constexpr int CPR = D / 8;
     for (int c = threadIdx.x; c < p.E * CPR * 2; c += blockDim.x) {
       const bool is_v = c >= p.E * CPR;
@@ -517,7 +520,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
     for (int hrow = 0; hrow < 2; ++hrow) {
       const int r = mt * 16 + g + 8 * hrow;
       if (r >= R) continue;
-      const int e = r / G, gq = r % G, tkn = b * p.E + e, head = kvh * G + gq;
+      const int e = r / G, gq = r % G, tkn = b * p.E + e, head = hbase + gq;
       const float l = hrow ? st.l1 : st.l0;
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* orow = p.out + ((size_t)tkn * p.Hq + head) * D;
@@ -547,6 +550,14 @@ static size_t fused_smem_bytes(int D, int n_mt, int n_kw, int stg) {
   return b + (tiles > merge ? tiles : merge);
 }
 
+// Query heads of one kv head are dealt to 1, 2 or 4 CTAs when a single CTA would hold more than 64 query rows
+// (more than 4 m-tiles leave no warps for key-ways) and the grid still fits one wave.
+static int pick_head_groups(int E, int G, long long ctas) {
+  int gsub = 1;
+  while (gsub < 4 && E * (G / gsub) > 64 && (G / gsub) % 2 == 0 && ctas * gsub * 2 <= 148) gsub *= 2;
+  return gsub;
+}
+
 // Key-ways per CTA: as many as fit in 8 warps and ~200 KB of shared memory.  Grids of several waves trade
 // key-ways for residency (smaller CTAs, more of them per SM), so one CTA's serial phases overlap another's tiles.
 static int pick_key_ways(int D, int n_mt, long long ctas) {
@@ -565,10 +576,11 @@ static int pick_key_ways(int D, int n_mt, long long ctas) {
 SMC_API int smc_attention_kv_splits(int bs, int E, int Hq, int Hkv, int D, int ctx) {
   using namespace smc;
   if (bs <= 0 || Hkv <= 0 || Hq % Hkv || E < 1) return 1;
-  const int R = E * (Hq / Hkv), n_mt = (R + 15) / 16;
+  const int gsub = pick_head_groups(E, Hq / Hkv, (long long)bs * Hkv);
+  const int R = E * (Hq / Hkv / gsub), n_mt = (R + 15) / 16;
   const int n_kw = pick_key_ways(D, n_mt, 0);
   const bool two_per_sm = fused_smem_bytes(D, n_mt, n_kw, 2) <= 110 * 1024;
-  const long long base = (long long)bs * Hkv;
+  const long long base = (long long)bs * Hkv * gsub;
   int ks = 1;
   while (ks < 8) {
     const int nk = ks * 2;
@@ -594,13 +606,14 @@ SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, 
   if (bs <= 0) return 0;
   if (Hq % Hkv || E < 1 || E > 16 || (rd & 1) || rd > D) return -70;
   if (!(KS == 1 || KS == 2 || KS == 4 || KS == 8)) return -73;
-  const int G = Hq / Hkv, R = E * G;
+  const int gsub = pick_head_groups(E, Hq / Hkv, (long long)bs * Hkv);
+  const int G = Hq / Hkv / gsub, R = E * G;
   const int n_mt = (R + 15) / 16;
   if (n_mt > 8) return -71;
-  int n_kw = pick_key_ways(D, n_mt, (long long)bs * Hkv * KS);
+  int n_kw = pick_key_ways(D, n_mt, (long long)bs * Hkv * KS * gsub);
   // Ring depth: a grid that fits the GPU in one wave with one CTA per SM spends the whole shared memory on tiles
   // in flight; larger grids stay under half of it so two CTAs share an SM.
-  const size_t budget = (size_t)bs * Hkv * KS <= 148 ? 200 * 1024 : 100 * 1024;
+  const size_t budget = (size_t)bs * Hkv * KS * gsub <= 148 ? 200 * 1024 : 100 * 1024;
   int stg = 2;
   while (stg < 6 && fused_smem_bytes(D, n_mt, n_kw, stg + 1) <= budget) ++stg;
   FusedAttnParams p;
@@ -611,7 +624,7 @@ SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, 
   p.k_pool = (__nv_bfloat16*)k_pool; p.v_pool = (__nv_bfloat16*)v_pool; p.n_pages = n_pages;
   p.block_table = block_table; p.bt_stride = bt_stride; p.rows = rows; p.prefix_lens = prefix_lens;
   p.out = (__nv_bfloat16*)out;
-  p.E = E; p.Hq = Hq; p.Hkv = Hkv; p.KS = KS; p.n_mt = n_mt; p.n_kw = n_kw; p.stg = stg; p.scale = scale; p.status = status;
+  p.E = E; p.Hq = Hq; p.Hkv = Hkv; p.KS = KS; p.gsub = gsub; p.n_mt = n_mt; p.n_kw = n_kw; p.stg = stg; p.scale = scale; p.status = status;
   p.pdl = pdl;
   const size_t smem = fused_smem_bytes(D, n_mt, n_kw, stg);
   void (*kern)(const FusedAttnParams) = nullptr;
@@ -635,7 +648,7 @@ SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, 
     ++na;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(bs * Hkv, KS);
+  cfg.gridDim = dim3(bs * Hkv, KS, gsub);
   cfg.blockDim = dim3(32 * n_mt * n_kw);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;

@@ -25,7 +25,8 @@
 
 namespace smc {
 
-enum { EPI_PARTIAL_F32 = 0, EPI_BF16 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_F32 = 3, EPI_RESID_F32 = 4, EPI_RS_F32 = 5 };
+enum { EPI_PARTIAL_F32 = 0, EPI_BF16 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_F32 = 3, EPI_RESID_F32 = 4, EPI_RS_F32 = 5,
+       EPI_SWIGLU_SPLIT = 6 };   // 6: SwiGLU after a split-K reduction inside the cluster
 
 // Tensor-parallel links of one GEMM.  Consumer side (all-gather -> GEMM): peers store their
 // activation rows into this GPU's buffer and bump a counter here; the TMA producer waits for the
@@ -260,7 +261,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
         }
         __syncthreads();
       }
-    } else if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32 || EPI == EPI_RS_F32) {
+    } else if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32 || EPI == EPI_RS_F32 || EPI == EPI_SWIGLU_SPLIT) {
       // park this CTA's tile as sbuf[token][128 weight rows]; the cluster reduces it below
       float* sbuf = reinterpret_cast<float*>(smem);
 #pragma unroll 1
@@ -302,11 +303,12 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
       (void)mbar_wait(&full[i % C::STAGES], (uint32_t)(i / C::STAGES) & 1u);
   }
 
-  if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32 || EPI == EPI_RS_F32) {
+  if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32 || EPI == EPI_RS_F32 || EPI == EPI_SWIGLU_SPLIT) {
     // ---- on-chip split-K reduction across the cluster (CTA rank == split index) --------------
     // Both cluster barriers are unconditional so that a CTA that gave up still releases its peers.
     __shared__ int sh_failed;
     __shared__ float s_red[4][4];
+    __shared__ float s_pair[4][64];      // SwiGLU after the reduction: up rows hand their sums to the gate rows
     if (threadIdx.x == 0) sh_failed = failed;
     cluster_sync();
     const uint32_t S = (uint32_t)p.splits;
@@ -350,7 +352,9 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
 #pragma unroll
             for (uint32_t s = 0; s < 8; ++s) acc += v[u][s];
             acc *= s_rstd[c];
-            if constexpr (EPI == EPI_RS_F32) {
+            if constexpr (EPI == EPI_SWIGLU_SPLIT) {
+              prev[u] = acc;               // paired below: rows 0..63 are gate channels, 64..127 the matching up channels
+            } else if constexpr (EPI == EPI_RS_F32) {
               // reduce-scatter: the token row belongs to rank `owner`; store into its receive buffer
               const int m = m_base + c, owner = m / p.tp.rows_per_rank, ml = m - owner * p.tp.rows_per_rank;
               float* dst = reinterpret_cast<float*>(p.tp.peer_base[owner] + p.tp.rs_off) +
@@ -365,6 +369,26 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
               }
             }
           }
+        }
+        if constexpr (EPI == EPI_SWIGLU_SPLIT) {
+          if (warp >= 2) {
+#pragma unroll
+            for (int u = 0; u < UN; ++u) s_pair[u][threadIdx.x - 64] = prev[u];
+          }
+          __syncthreads();
+          if (warp < 2) {
+            const int ch = n_tile * 64 + (int)threadIdx.x;
+            __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+              const int c = c0 + u * (int)S;
+              if (c < BN && m_base + c < p.M && ch * 2 < p.N) {
+                const float g = prev[u], up = s_pair[u][threadIdx.x];
+                ob[(size_t)(m_base + c) * p.ldo + ch] = __float2bfloat16(g / (1.0f + __expf(-g)) * up);
+              }
+            }
+          }
+          __syncthreads();
         }
         if constexpr (EPI == EPI_RESID_F32) {
           if (p.ssq_out != nullptr) {
@@ -390,9 +414,11 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
       // publish: every CTA makes its peer stores visible system-wide and checks in; the last CTA of
       // the grid bumps every rank's counter once, so the counters advance by `tp` per GEMM whatever
       // the batch size is
-      __threadfence_system();
+      // the CTA barrier orders every thread's peer stores before thread 0's fence, and the fence is cumulative, so
+      // one system-scope fence per CTA publishes them all
       __syncthreads();
       if (threadIdx.x == 0) {
+        __threadfence_system();
         const int total = (int)(gridDim.x * gridDim.y * gridDim.z);
         if (atomicAdd(p.tp.arrive, 1) == total - 1) {
           *p.tp.arrive = 0;
@@ -463,7 +489,7 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmPara
     attr[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
   }
-  if (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32 || EPI == EPI_RS_F32) {
+  if (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32 || EPI == EPI_RS_F32 || EPI == EPI_SWIGLU_SPLIT) {
     attr[na].id = cudaLaunchAttributeClusterDimension;
     attr[na].val.clusterDim.x = 1;
     attr[na].val.clusterDim.y = (unsigned)p.splits;
@@ -534,25 +560,25 @@ SMC_API int smc_gemm_default_splits(int N, int K, int M) {
   return s;
 }
 
-// Cluster size for the on-chip split-K epilogues: the largest power of two that keeps the grid within about two
-// CTAs per SM and leaves every CTA at least two k-blocks.  (Any size from 1 to 8 is accepted by the kernel; sizes
-// chosen to fill exactly one wave with one CTA per SM, e.g. 3 for 48 slabs, measured 8-20 % slower than the next
-// power of two with two CTAs per SM, whose rings keep more bytes in flight.)
+// Cluster size for the on-chip split-K epilogues: the largest size up to 8 that keeps the grid within two CTAs per
+// SM (296 CTAs) and leaves every CTA at least two k-blocks.  Two resident CTAs per SM keep more bytes in flight
+// than one: sizes picked to fill exactly one wave with one CTA per SM measured 8-20 % slower.
 SMC_API int smc_gemm_cluster_splits(int N, int K, int M) {
   const int n_tiles = (N + 127) / 128;
   const int bn = bn_for(M, N);
   const int m_tiles = (M + bn - 1) / bn;
   const int kblocks = (K + 63) / 64;
-  int s = 1;
-  while (s < 8 && n_tiles * m_tiles * s * 2 <= 256 && kblocks / (s * 2) >= 2) s *= 2;
-  return s;
+  for (int s = 8; s > 1; --s)
+    if (n_tiles * m_tiles * s <= 296 && kblocks / s >= 2) return s;
+  return 1;
 }
 
 // W [N, K] bf16 row-major, X [M, ldx] bf16 row-major (ldx >= K).
 // epi 3: out = fp32 [M, ldo] = X W^T;  epi 4: out (fp32 [M, ldo]) += X W^T.  Both reduce split-K inside a
 // thread-block cluster, so splits must be 1..8.
 // epi 0: out = fp32 [splits, M, N] partials; epi 1: out = bf16 [M, ldo] (splits must be 1);
-// epi 2: out = bf16 [M, ldo] holding SwiGLU(gate, up) for N/2 channels (splits must be 1, N % 128 == 0).
+// epi 2: out = bf16 [M, ldo] holding SwiGLU(gate, up) for N/2 channels (N % 128 == 0; splits > 1 reduce split-K
+//        inside a cluster first).
 struct NormLink {            // host-side description of the folded RMSNorm (all fields optional)
   const float* ssq_in; int ssq_parts; int ssq_ld; int norm_d; float norm_eps; float* ssq_out; void* hb_out; int hb_ld;
   int ssq_mstride;
@@ -563,10 +589,11 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
   using namespace smc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) != 0 || (ldx % 8) != 0) return -20;       // row pitch must be a multiple of 16 bytes
-  const bool clustered = epi == EPI_STORE_F32 || epi == EPI_RESID_F32 || epi == EPI_RS_F32;
+  if (epi == EPI_SWIGLU_BF16 && splits > 1) epi = EPI_SWIGLU_SPLIT;      // split-K reduced in the cluster, then SwiGLU
+  const bool clustered = epi == EPI_STORE_F32 || epi == EPI_RESID_F32 || epi == EPI_RS_F32 || epi == EPI_SWIGLU_SPLIT;
   if (!clustered && epi != EPI_PARTIAL_F32 && splits != 1) return -21;
   if (clustered && (splits < 1 || splits > 8)) return -23;
-  if (epi == EPI_SWIGLU_BF16 && (N % 128) != 0) return -22;
+  if ((epi == EPI_SWIGLU_BF16 || epi == EPI_SWIGLU_SPLIT) && (N % 128) != 0) return -22;
   if (epi == EPI_RS_F32 && (tp == nullptr || tp->tp < 1 || tp->tp > 8 || tp->rows_per_rank < 1)) return -24;
   const int bn = bn_for(M, N);
   GemmParams p;
@@ -599,6 +626,7 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
     case EPI_STORE_F32: return dispatch_bn<EPI_STORE_F32>(bn, tmW, tmX, p, grid, stream);
     case EPI_RESID_F32: return dispatch_bn<EPI_RESID_F32>(bn, tmW, tmX, p, grid, stream);
     case EPI_RS_F32: return dispatch_bn<EPI_RS_F32>(bn, tmW, tmX, p, grid, stream);
+    case EPI_SWIGLU_SPLIT: return dispatch_bn<EPI_SWIGLU_SPLIT>(bn, tmW, tmX, p, grid, stream);
   }
   return -11;
 }

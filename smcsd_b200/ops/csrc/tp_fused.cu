@@ -112,8 +112,9 @@ tp_norm_allgather_kernel(TpPeers peers, float* __restrict__ h_local, const float
     }
   }
   // the last row of this rank to finish tells every peer that this rank's rows have landed
-  __threadfence_system();
+  // one cumulative system-scope fence per CTA (after the CTA barrier) publishes every thread's peer stores
   __syncthreads();
+  if (threadIdx.x == 0) __threadfence_system();
   if (threadIdx.x == 0 && atomicAdd(arrive, 1) == my_rows - 1) {
     *arrive = 0;
     __threadfence_system();

@@ -101,6 +101,22 @@ def gemm_cluster_splits(N: int, K: int, M: int) -> int:
     return lib().smc_gemm_cluster_splits(N, K, M)
 
 
+def gemm_swiglu_splits(N: int, K: int, M: int) -> int:
+    """Split-K factor of a gate/up GEMM with the SwiGLU epilogue: matrices with few 128-row slabs are cut along K
+    (cluster reduction before the activation) until the grid offers about two CTAs per SM.  ``SMC_GU_SPLITS``
+    overrides the choice."""
+    env = os.environ.get("SMC_GU_SPLITS")
+    if env:
+        return max(1, int(env))
+    bn = lib().smc_gemm_bn_for(M)
+    tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
+    kblocks = (K + 63) // 64
+    s = 1
+    while s < 4 and tiles * s * 2 <= 296 and kblocks // (s * 2) >= 4:
+        s *= 2
+    return s
+
+
 def gemm_skinny(W: torch.Tensor, X: torch.Tensor, out: torch.Tensor, *, M: int, splits: int = 1,
                 epi: int = EPI_PARTIAL_F32, ldx: Optional[int] = None, ldo: Optional[int] = None,
                 status: torch.Tensor, pdl: bool = False) -> None:

@@ -94,7 +94,7 @@ class NativeLlama:
                                epi=K.EPI_RESID_F32, ldo=self.d, status=self.status, ssq_out=self.ssq, hb_out=self.hb,
                                ssq_ld=ld, pdl=pdl)
             parts = self.n_parts
-            K.gemm_skinny_norm(L.wgu, self.hb, self.act, M=T, splits=1, epi=K.EPI_SWIGLU_BF16,
+            K.gemm_skinny_norm(L.wgu, self.hb, self.act, M=T, splits=self._gu_splits(T), epi=K.EPI_SWIGLU_BF16,
                                ldo=self.act.stride(0), status=self.status, ssq_in=self.ssq, ssq_parts=parts,
                                norm_d=self.d, norm_eps=c.rms_eps, ssq_ld=ld, pdl=pdl)
             K.gemm_skinny_norm(L.wdown, self.act, self.h, M=T, splits=self._splits(self.d, self.ffn, T),
@@ -160,7 +160,8 @@ class NativeLlama:
             self._gemm(L.wo, self.attn, self.h, T, K.EPI_RESID_F32)
             K.add_rmsnorm(self.h, L.ln2, self.xn, M=T, d=self.d, eps=c.rms_eps, pdl=pdl)
             if self.fuse_swiglu:
-                K.gemm_skinny(L.wgu, self.xn, self.act, M=T, splits=1, epi=K.EPI_SWIGLU_BF16, ldo=self.act.stride(0),
+                K.gemm_skinny(L.wgu, self.xn, self.act, M=T, splits=self._gu_splits(T), epi=K.EPI_SWIGLU_BF16,
+                              ldo=self.act.stride(0),
                               status=self.status, pdl=pdl)
             else:
                 self._gemm(L.wgu, self.xn, self.gu, T, K.EPI_STORE_F32)
@@ -169,6 +170,13 @@ class NativeLlama:
             w_next = m.layers[li + 1].ln1 if li + 1 < n_layers else m.final_norm
             K.add_rmsnorm(self.h, w_next, self.xn, M=T, d=self.d, eps=c.rms_eps, pdl=pdl)
         return self.xn
+
+    def _gu_splits(self, M: int) -> int:
+        key = ("gu", M)
+        s = self._splits_cache.get(key)
+        if s is None:
+            s = self._splits_cache[key] = K.gemm_swiglu_splits(2 * self.ffn, self.d, M)
+        return s
 
     def lm_head(self, rows: int, row_offset: int = 0, row_step: int = 1) -> torch.Tensor:
         """fp32 logits [rows, V] of the final hidden rows ``row_offset + i * row_step``."""

@@ -111,7 +111,8 @@ class NativeHybrid:
                 self._gemm(L.wout, mix, self.h, T, K.EPI_RESID_F32)
             K.add_rmsnorm(self.h, L.ln2, self.xn, M=T, d=self.d, eps=c.rms_eps, plus_one=po, pdl=pdl)
             if self.fuse_swiglu:
-                K.gemm_skinny(L.wgu, self.xn, self.act, M=T, splits=1, epi=K.EPI_SWIGLU_BF16, ldo=self.act.stride(0),
+                K.gemm_skinny(L.wgu, self.xn, self.act, M=T, splits=self._gu_splits(T), epi=K.EPI_SWIGLU_BF16,
+                              ldo=self.act.stride(0),
                               status=self.status, pdl=pdl)
             else:
                 self._gemm(L.wgu, self.xn, self.gu, T, K.EPI_STORE_F32)
@@ -133,6 +134,13 @@ class NativeHybrid:
 
     def _ks(self, bs: int, E: int) -> int:
         return K.attn_kv_splits(self.ctx_hint, bs, self.nkv, E, self.nq // self.nkv, self.D)
+
+    def _gu_splits(self, M: int) -> int:
+        key = ("gu", M)
+        s = self._splits_cache.get(key)
+        if s is None:
+            s = self._splits_cache[key] = K.gemm_swiglu_splits(2 * self.ffn, self.d, M)
+        return s
 
     def lm_head(self, rows: int, row_offset: int = 0, row_step: int = 1):
         K.gemm_skinny(self.m.lm_head, self.xn[row_offset:], self.logits, M=rows, splits=1, epi=K.EPI_STORE_F32,

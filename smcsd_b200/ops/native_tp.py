@@ -147,7 +147,7 @@ class NativeLlamaTP:
                                 ctx.arrive[2:], st, pdl)
             yield
             lk = ctx.link(ag="ag_b", ag_uses=L, ag_idx=li)
-            K.gemm_skinny_tp(Lw.wgu, self.xn_b, self.act, M=T, splits=1, epi=K.EPI_SWIGLU_BF16, link=lk,
+            K.gemm_skinny_tp(Lw.wgu, self.xn_b, self.act, M=T, splits=self._gu_splits(T), epi=K.EPI_SWIGLU_BF16, link=lk,
                              ldo=self.act.stride(0), status=st, pdl=pdl)
             yield
             lk = ctx.link(rs="rs_down", rows_per_rank=rpr, arrive_slot=3)
@@ -170,6 +170,13 @@ class NativeLlamaTP:
 
     def _ks(self, bs: int, E: int) -> int:
         return K.attn_kv_splits(self.ctx_hint, bs, self.nkv, E, self.nq // self.nkv, self.D)
+
+    def _gu_splits(self, M: int) -> int:
+        key = ("gu", M)
+        s = self._splits_cache.get(key)
+        if s is None:
+            s = self._splits_cache[key] = K.gemm_swiglu_splits(2 * self.ffn, self.d, M)
+        return s
 
     def lm_head(self, rows: int, row_offset: int = 0, row_step: int = 1):
         """This rank's vocabulary shard of the logits [rows, Vshard] (waits for the last all-gather)."""

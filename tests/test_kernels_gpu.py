@@ -110,6 +110,13 @@ def test_gemm_swiglu_epilogue(ffn, d, M):
     K.swiglu_partials(part, s, M * 2 * ffn, act2, M=M, ffn=ffn, blk=64)
     torch.cuda.synchronize()
     assert (act2.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
+    # split-K reduced inside a cluster before the activation
+    for s in (2, 4, 3):
+        act3 = torch.zeros_like(act)
+        K.gemm_skinny(Wgu, X, act3, M=M, splits=s, epi=K.EPI_SWIGLU_BF16, ldo=ffn, status=st, pdl=True)
+        torch.cuda.synchronize()
+        assert int(st) == 0
+        assert (act3.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item()), s
 
 
 # ------------------------------------------------------------------------------- norm / rope
@@ -346,7 +353,7 @@ def test_state_kernels_match_torch_reference():
     (2, 5, 4, 2, 64, 0, 1, 64, False), (4, 9, 32, 8, 128, 2500, 1, 128, False), (4, 9, 32, 8, 128, 2500, 2, 128, False),
     (3, 1, 8, 2, 128, 900, 4, 128, True), (8, 9, 64, 8, 128, 100, 1, 128, False),
     (8, 9, 32, 8, 128, 4000, 4, 128, False), (8, 1, 32, 8, 64, 4000, 8, 64, False), (4, 9, 16, 2, 256, 1000, 2, 64, True),
-    (3, 2, 8, 2, 64, 40, 4, 64, False),
+    (3, 2, 8, 2, 64, 40, 4, 64, False), (8, 9, 16, 2, 128, 300, 2, 128, False), (2, 9, 32, 2, 128, 700, 4, 128, True),
 ])
 def test_attention_fused(bs, E, Hq, Hkv, D, ctx, KS, rd, extras):
     K = _K()
