@@ -69,7 +69,14 @@ def gemm_case(N, Kd, M, epi, splits, pdl=True, plain=False, iters=3, copies=None
         out, ldo = torch.zeros(M, N, device=dev, dtype=torch.bfloat16), N
     else:
         out, ldo = torch.zeros(M, N, device=dev), N
-    s = splits or (K.gemm_cluster_splits(N, Kd, M) if epi in (K.EPI_STORE_F32, K.EPI_RESID_F32) else 1)
+    if splits:
+        s = splits
+    elif epi in (K.EPI_STORE_F32, K.EPI_RESID_F32):
+        s = K.gemm_cluster_splits(N, Kd, M)
+    elif epi == K.EPI_SWIGLU_BF16:
+        s = K.gemm_swiglu_splits(N, Kd, M)
+    else:
+        s = 1
     idx = [0]
 
     def fn():
