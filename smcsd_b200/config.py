@@ -120,7 +120,9 @@ class EngineArgs:
         self.graph_max_bs = env_int("SMC_DRAFT_GRAPH_MAX_BS", self.graph_max_bs, 64)
         if self.cuda_graph_max_bs:          # the sweeps size the capture cap as batch x particles
             self.graph_max_bs = max(self.graph_max_bs, int(self.cuda_graph_max_bs))
-        self.graph_max_context = env_int("SMC_DRAFT_GRAPH_MAX_CONTEXT", self.graph_max_context, 8192)
+        # the reference caps graph replay at 8192 tokens because of its index buffers; the cycle graph here has no
+        # per-context buffers, so the default cap is far out and the knob only exists to force the eager path
+        self.graph_max_context = env_int("SMC_DRAFT_GRAPH_MAX_CONTEXT", self.graph_max_context, 131072)
         if self.disable_cuda_graph or self.draft_temperature <= 0.0:
             # greedy proposals take the eager path, like the reference (worker.py:299-300)
             self.cycle_graph = False

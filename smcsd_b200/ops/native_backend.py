@@ -363,13 +363,16 @@ class NativeRunner:
         batch (block j of a prompt attends to its 16j cached predecessors plus itself), so prefill reuses the
         decode kernels with token-tile GEMMs.  Gated-DeltaNet layers of hybrid models walk each prompt once, token
         by token, with the state held in registers.  Tensor-parallel targets and over-long batches take the plain
-        PyTorch forward."""
+        PyTorch forward.  Dense prompts longer than the chains' token capacity run in several passes over
+        consecutive blocks (earlier passes have already cached their keys)."""
         B = self.PREFILL_BLOCK
         lens = [len(it.input_ids) for it in items]
         n_blocks = [(L + B - 1) // B for L in lens]
         T = sum(n_blocks) * B
         tgt, drf = self._prefill_chain("target"), self._prefill_chain("draft")
-        if tgt is None or drf is None or T > self.PREFILL_MAX_TOKENS or getattr(self.target.m, "tp_size", 1) > 1:
+        stateful = any(getattr(nm.m, "has_state", False) for nm in (tgt, drf) if nm is not None)
+        if tgt is None or drf is None or getattr(self.target.m, "tp_size", 1) > 1 or \
+                (T > self.PREFILL_MAX_TOKENS and stateful):
             native, worker.native = worker.native, None
             try:
                 return worker.prefill(items)
@@ -416,14 +419,30 @@ class NativeRunner:
                              "off": pin(torch.tensor(offs, dtype=torch.int32)),
                              "len": pin(torch.tensor([max(L - short, 0) for L in lens], dtype=torch.int32)),
                              "n": len(items)}}
-        tgt.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True, **seqs_for(tgt, 0))
+        cb = max(1, self.PREFILL_MAX_TOKENS // B)            # blocks per pass
         last = torch.tensor(last_rows, dtype=torch.long, device=dev)
-        logits = self.target.m.logits_torch(tgt.final_hidden(last))
+
+        def run(nm, short: int, want_hidden: bool):
+            if bs <= cb:
+                nm.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True, **seqs_for(nm, short))
+                return nm.final_hidden(last) if want_hidden else None
+            hid = [None] * len(items)
+            for c0 in range(0, bs, cb):
+                nb = min(cb, bs - c0)
+                tok = slice(c0 * B, (c0 + nb) * B)
+                nm.set_context(max(lens), nb)
+                nm.forward(ids[tok], pos[tok], locs[tok], rows[c0:c0 + nb], pref[c0:c0 + nb], nb, B, two_pass=True)
+                if want_hidden:
+                    for i, r in enumerate(last_rows):
+                        if tok.start <= r < tok.stop:
+                            hid[i] = nm.final_hidden(torch.tensor([r - tok.start], dtype=torch.long, device=dev))
+            return torch.cat(hid, 0) if want_hidden else None
+        logits = self.target.m.logits_torch(run(tgt, 0, True))
         from ..smc import math as smc_math
         x0, _, _ = smc_math.gumbel_sample(logits, self.T_target, self.alpha, generator=worker.gen_prefill)
         # a stateful draft under the deferred schedule stops one token short: the first head forward of the decode
         # loop advances its recurrent state through the last prompt token exactly once
-        drf.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True, **seqs_for(drf, 1 if self.defer else 0))
+        run(drf, 1 if self.defer else 0, False)
         worker.io_bytes["d2h"] += 4 * len(items)
         return x0.to(torch.int32)
 

@@ -113,13 +113,16 @@ def test_weights_track_target_over_draft():
     assert sched.native_runner.check_status() == 0
 
 
-def test_native_prefill_matches_torch_prefill():
+@pytest.mark.parametrize("capacity", [None, 64])
+def test_native_prefill_matches_torch_prefill(capacity):
     """Prompt pass through the kernel chains (16-token blocks as batch rows) vs the plain PyTorch forward:
-    same cache contents, same last-token logits."""
+    same cache contents, same last-token logits.  With a small token capacity the prompts run in several passes."""
     from smcsd_b200.runtime.worker import PrefillItem
     eng = _engine(backend="native", cycle_graph=False)
     s = eng._sched
     r = s.native_runner
+    if capacity:
+        r.PREFILL_MAX_TOKENS = capacity
     lens = [37, 16, 5, 70]
     g = torch.Generator().manual_seed(4)
     items = []
