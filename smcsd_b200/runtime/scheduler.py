@@ -150,6 +150,8 @@ class SMCScheduler:
         self.running: Dict[str, SequenceGroup] = {}
         self.reserved_pages = 0
         self.last_free_pages = self.min_free_pages = self.alloc.size
+        self._log_alloc_retries = os.environ.get("SMC_LOG_ALLOC_RETRIES") == "1" and self.device.type == "cuda"
+        self._alloc_retries_seen = 0
         self.pending: Deque = deque()       # snapshots awaiting host post-processing
         self.outbox: List = []
         self.final_gen = torch.Generator().manual_seed(seed * 31 + 5)
@@ -359,6 +361,13 @@ class SMCScheduler:
             self._cycle_events.append((e0, e1, st.bs))
             if len(self._cycle_events) > 4096:
                 del self._cycle_events[:2048]
+        if self._log_alloc_retries:
+            # a caching-allocator retry means a hidden cudaFree + synchronisation inside the decode loop
+            n = torch.cuda.memory_stats(self.device).get("num_alloc_retries", 0)
+            if n != self._alloc_retries_seen:
+                log.warning("caching allocator retried %d time(s) during decode cycle %d", n - self._alloc_retries_seen,
+                            self.stats["cycles"])
+                self._alloc_retries_seen = n
         self.stats["cycles"] += 1
         self.stats["group_cycles"] = self.stats.get("group_cycles", 0) + len(self.running)
         self.stats["decode_tokens"] += st.bs * (self.args.gamma + 1)
@@ -456,7 +465,8 @@ class SMCScheduler:
         """With nothing running, every page is free and no slot is held."""
         if self.running or self.pending:
             return
-        if os.environ.get("SMC_STRICT_MEM_CHECK", "1") != "1":
+        if os.environ.get("SMC_STRICT_MEM_CHECK", os.environ.get("SGLANG_ENABLE_STRICT_MEM_CHECK_DURING_IDLE", "1")) \
+                not in ("1", "true", "True"):
             return
         free = self.alloc.available()
         if free != self.alloc.size:

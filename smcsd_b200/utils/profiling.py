@@ -38,8 +38,11 @@ class SchedulerProfiler:
             acts.append(torch.profiler.ProfilerActivity.CPU)
         if "GPU" in wanted and torch.cuda.is_available():
             acts.append(torch.profiler.ProfilerActivity.CUDA)
-        self.prof = torch.profiler.profile(activities=acts, with_stack=self.req.with_stack,
-                                           record_shapes=self.req.record_shapes)
+        env = os.environ.get                 # the reference's profiler switches are honoured as defaults
+        stack = self.req.with_stack or env("SMC_PROFILE_WITH_STACK", env("SGLANG_PROFILE_WITH_STACK", "0")) == "1"
+        shapes = self.req.record_shapes or \
+            env("SMC_PROFILE_RECORD_SHAPES", env("SGLANG_PROFILE_RECORD_SHAPES", "0")) == "1"
+        self.prof = torch.profiler.profile(activities=acts, with_stack=stack, record_shapes=shapes)
         self.prof.start()
 
     def _end(self) -> Optional[str]:
