@@ -192,6 +192,8 @@ class SMCEngine:
             if o.aborted:
                 d["aborted"] = True
                 d["error"] = o.error
+            if o.time_stats:
+                d["time_stats"] = o.time_stats
             results[o.rid] = d
             pending.discard(o.rid)
 

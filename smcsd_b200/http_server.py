@@ -75,7 +75,7 @@ class EngineBridge:
             ids = self.partial.pop(o.rid)
             res = dict(output_ids=ids, completion_tokens=len(ids), prompt_tokens=o.prompt_tokens,
                        finish_reason=o.finish_reason, aborted=o.aborted, error=o.error,
-                       smc_log_Z_hat=self.logz.pop(o.rid, None))
+                       smc_log_Z_hat=self.logz.pop(o.rid, None), time_stats=o.time_stats)
             self.n_served += 1
             self.loop.call_soon_threadsafe(self._resolve, o.rid, res)
 
@@ -116,7 +116,7 @@ class EngineBridge:
                     self.loop.call_soon_threadsafe(
                         self._resolve, rid, dict(output_ids=[], completion_tokens=0, prompt_tokens=0,
                                                  finish_reason={"type": "abort", "message": repr(e)}, aborted=True,
-                                                 error=repr(e), smc_log_Z_hat=None))
+                                                 error=repr(e), smc_log_Z_hat=None, time_stats=None))
                 time.sleep(0.1)
 
 
@@ -169,7 +169,7 @@ def build_app(engine, model_name: str = "smc"):
         return {"text": _decode(r["output_ids"]), "output_ids": r["output_ids"],
                 "meta_info": {"id": uuid.uuid4().hex, "prompt_tokens": len(ids),
                               "completion_tokens": r["completion_tokens"], "finish_reason": r["finish_reason"],
-                              "smc_log_Z_hat": r["smc_log_Z_hat"]}}
+                              "smc_log_Z_hat": r["smc_log_Z_hat"], "time_stats": r.get("time_stats")}}
 
     @app.post("/generate")
     async def generate(body: Dict[str, Any]):

@@ -67,6 +67,9 @@ class RequestOutput:
     completion_tokens: int = 0
     aborted: bool = False
     error: Optional[str] = None
+    # request time stats in seconds (set on the final slice): time in the queue, arrival to first token
+    # (end of prefill), arrival to completion; and the number of decode cycles the group ran
+    time_stats: Optional[Dict[str, float]] = None
 
 
 @dataclass

@@ -41,6 +41,7 @@ class SequenceGroup:
     x0: Optional[int] = None
     reserved_pages: int = 0
     t_arrive: float = 0.0
+    t_admit: float = 0.0
     t_first_token: float = 0.0
     cycles: int = 0
     launched: int = 0          # decode cycles enqueued for this group (processed or still in flight)
@@ -268,6 +269,7 @@ class SMCScheduler:
                 break
             self.waiting.popleft()
             g.parent_row = row
+            g.t_admit = time.time()
             g.reserved_pages = need
             self.reserved_pages += need
             admitted.append(g)
@@ -411,6 +413,9 @@ class SMCScheduler:
         self.io_bytes["d2h"] += self.args.n_particles * (self.state.max_output_len * 4 + 40)
         L = len(g.req.input_ids)
         out = RequestOutput(g.rid, res["output_ids"], True, res["finish_reason"], L, len(res["output_ids"]))
+        now = time.time()
+        out.time_stats = {"queue_s": max(0.0, g.t_admit - g.t_arrive), "ttft_s": max(0.0, g.t_first_token - g.t_arrive),
+                          "e2e_s": max(0.0, now - g.t_arrive), "decode_cycles": float(g.cycles)}
         if self.emit_particles:
             self.outbox.append(ParticleOutput(g.rid, res["particle_output_ids"], res["log_Z_hat"],
                                               res["log_w_tilde"], res["picked"]))

@@ -22,6 +22,8 @@ def test_plumbing_run_tiny_llama():
     assert len(outs) == 8
     for o in outs:
         assert o["completion_tokens"] == 64 and len(o["output_ids"]) == 64
+        ts = o["time_stats"]
+        assert 0.0 <= ts["queue_s"] <= ts["ttft_s"] <= ts["e2e_s"] and ts["decode_cycles"] >= 1
         assert o["finish_reason"]["type"] == "length"
         assert len(o["smc_particle_output_ids"]) == 4
         assert len(o["smc_log_w_tilde"]) == 4
