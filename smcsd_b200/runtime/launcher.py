@@ -44,7 +44,18 @@ class PortArgs:
 
     @classmethod
     def init_new(cls, n_replicas: int, dist_port: Optional[int] = None) -> "PortArgs":
-        return cls([free_port() for _ in range(n_replicas)], free_port(), free_port(), dist_port or free_port())
+        # all sockets stay bound until every port is chosen, so the ports are distinct
+        socks = []
+        try:
+            for _ in range(n_replicas + 3):
+                s = socket.socket()
+                s.bind(("127.0.0.1", 0))
+                socks.append(s)
+            ports = [s.getsockname()[1] for s in socks]
+        finally:
+            for s in socks:
+                s.close()
+        return cls(ports[:n_replicas], ports[n_replicas], ports[n_replicas + 1], dist_port or ports[n_replicas + 2])
 
 
 def _watch_parent(parent_pid: int) -> None:
