@@ -195,3 +195,39 @@ def test_abort_mid_decode_releases_pages_and_slots():
     s.check_idle_invariants()
     s.alloc.check_conservation()
     assert s.native_runner.check_status() == 0
+
+
+def test_staggered_arrivals_with_changing_batch_sizes():
+    """Requests of different lengths join and leave while others decode: every batch size gets its own captured
+    graph, finished groups free their slots for the queue, and nothing leaks."""
+    from smcsd_b200.io_types import GenerateRequest, RequestOutput, SamplingParams
+    eng = _engine(backend="native", max_running_requests=3)
+    s = eng._sched
+    g = torch.Generator().manual_seed(21)
+    want = {}
+    done = {}
+    arrivals = {0: 2, 3: 1, 5: 2, 11: 1, 12: 3}          # step -> number of new requests
+    k = 0
+    for step in range(400):
+        for _ in range(arrivals.get(step, 0)):
+            L = int(torch.randint(8, 90, (1,), generator=g))
+            n = int(torch.randint(5, 70, (1,), generator=g))
+            rid = f"r{k}"
+            k += 1
+            want[rid] = n
+            s.add_request(GenerateRequest(rid, torch.randint(64, 8192, (L,), generator=g).tolist(),
+                                          SamplingParams(max_new_tokens=n, stop_token_ids=list(range(8)))))
+        for o in s.step():
+            if isinstance(o, RequestOutput) and o.finished:
+                done[o.rid] = o
+        if step > 12 and not s.has_work():
+            break
+    assert set(done) == set(want)
+    for rid, o in done.items():
+        assert not o.aborted and 1 <= len(o.output_ids) <= want[rid]
+        if len(o.output_ids) < want[rid]:
+            assert o.finish_reason["type"] == "stop" and o.output_ids[-1] < 8
+    assert len(s.native_runner.graphs) >= 2
+    s.check_idle_invariants()
+    s.alloc.check_conservation()
+    assert s.native_runner.check_status() == 0
