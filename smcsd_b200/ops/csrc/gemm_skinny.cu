@@ -312,8 +312,10 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
     if (threadIdx.x == 0) sh_failed = failed;
     cluster_sync();
     const uint32_t S = (uint32_t)p.splits;
-    bool any_failed = false;
-    for (uint32_t s = 0; s < S; ++s) any_failed |= ld_dsmem_u32(smem_u32(&sh_failed), s) != 0;
+    // one thread per rank fetches that rank's flag, so the remote reads overlap instead of queueing up
+    int peer_failed = 0;
+    if (threadIdx.x < S) peer_failed = ld_dsmem_u32(smem_u32(&sh_failed), threadIdx.x) != 0;
+    const bool any_failed = __syncthreads_or(peer_failed) != 0;
     if (!any_failed) {
       const float* sbuf = reinterpret_cast<const float*>(smem);
       const int n = n_tile * C::BM + (int)threadIdx.x;
