@@ -45,7 +45,8 @@ __global__ void gdn_recurrent_kernel(const float* __restrict__ conv_out, const f
                                      const __nv_bfloat16* __restrict__ gnorm_w, __nv_bfloat16* __restrict__ out,
                                      int E, int Hk, int Hv, int dv, int conv_dim, float eps,
                                      const int* __restrict__ tok_off, const int* __restrict__ tok_len, int pdl) {
-  __shared__ float q_s[DK], k_s[DK], red[8];
+  __shared__ __align__(16) float q_s[DK], k_s[DK];
+  __shared__ float red[8];
   __shared__ float scal[4];
   if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const int b = blockIdx.x, vh = blockIdx.y, kh = vh / (Hv / Hk);
@@ -86,13 +87,29 @@ __global__ void gdn_recurrent_kernel(const float* __restrict__ conv_out, const f
     __syncthreads();
     const float decay = scal[2], beta = scal[3];
     const float v = live ? co[2 * key_dim + vh * dv + j] : 0.f;
-    float kvm = 0.f;
+    // four independent partial sums per dot product (a single chain of DK dependent FMAs would set the pace),
+    // key / query values fetched four at a time
+    float kv4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < DK; ++i) { S[i] *= decay; kvm = fmaf(S[i], k_s[i], kvm); }
+    for (int i = 0; i < DK; i += 4) {
+      const float4 kk = *reinterpret_cast<const float4*>(&k_s[i]);
+      S[i] *= decay; S[i + 1] *= decay; S[i + 2] *= decay; S[i + 3] *= decay;
+      kv4[0] = fmaf(S[i], kk.x, kv4[0]); kv4[1] = fmaf(S[i + 1], kk.y, kv4[1]);
+      kv4[2] = fmaf(S[i + 2], kk.z, kv4[2]); kv4[3] = fmaf(S[i + 3], kk.w, kv4[3]);
+    }
+    const float kvm = (kv4[0] + kv4[1]) + (kv4[2] + kv4[3]);
     const float delta = (v - kvm) * beta;
-    float o = 0.f;
+    float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < DK; ++i) { S[i] = fmaf(k_s[i], delta, S[i]); o = fmaf(S[i], q_s[i], o); }
+    for (int i = 0; i < DK; i += 4) {
+      const float4 kk = *reinterpret_cast<const float4*>(&k_s[i]);
+      const float4 qq = *reinterpret_cast<const float4*>(&q_s[i]);
+      S[i] = fmaf(kk.x, delta, S[i]); S[i + 1] = fmaf(kk.y, delta, S[i + 1]);
+      S[i + 2] = fmaf(kk.z, delta, S[i + 2]); S[i + 3] = fmaf(kk.w, delta, S[i + 3]);
+      o4[0] = fmaf(S[i], qq.x, o4[0]); o4[1] = fmaf(S[i + 1], qq.y, o4[1]);
+      o4[2] = fmaf(S[i + 2], qq.z, o4[2]); o4[3] = fmaf(S[i + 3], qq.w, o4[3]);
+    }
+    float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
     // gated RMSNorm over the head's dv outputs
     float so = warp_sum(live ? o * o : 0.f);
     __syncthreads();

@@ -67,13 +67,18 @@ struct GemmParams {
   int hb_ld;
 };
 
-template <int BN>
+template <int BN, int EPI>
 struct GemmCfg {
   static constexpr int BM = 128, BK = 64;
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = BN <= 32 ? 5 : 4;
+  // 128-token tiles of the split-K epilogues keep three 32 KB stages so that two CTAs share an SM (a 160- or
+  // 288-CTA grid is then one wave: 8B down at 1152 tokens 193 -> 149 us); the single-wave gate/up grids keep four
+  // (three measured 22 -> 28 us there).
+  static constexpr bool CLUSTERED = EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32 || EPI == EPI_RS_F32 ||
+                                    EPI == EPI_SWIGLU_SPLIT;
+  static constexpr int STAGES = BN <= 32 ? 5 : ((BN == 128 && CLUSTERED) ? 3 : 4);
   static constexpr int TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
@@ -82,7 +87,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW,
                                                          const __grid_constant__ CUtensorMap tmX,
                                                          const GemmParams p) {
-  using C = GemmCfg<BN>;
+  using C = GemmCfg<BN, EPI>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -472,7 +477,7 @@ static int make_tmap(CUtensorMap* tm, const void* base, long long rows, long lon
 
 template <int BN, int EPI>
 static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, dim3 grid, cudaStream_t st) {
-  using C = GemmCfg<BN>;
+  using C = GemmCfg<BN, EPI>;
   static bool configured = false;
   auto kern = gemm_skinny_kernel<BN, EPI>;
   if (!configured) {
@@ -533,14 +538,15 @@ SMC_API int smc_gemm_bn_for(int M) {
 // CTA is bound by the bytes it pulls through its SM (a 128-row weight slab plus BN activation rows per k-block),
 // so the width is the one that minimises waves x bytes per CTA: e.g. 1152 tokens on 32 slabs run as 288 tiles of
 // 128 tokens (two full waves) rather than 160 tiles of 256 (one full wave and a nearly empty one).
-static int bn_for(int M, int N) {
+static int bn_for(int M, int N, bool clustered) {
   if (M <= 256 || N <= 0) return smc_gemm_bn_for(M);
   const long long n_tiles = (N + 127) / 128;
   long long best_cost = 0;
   int best = 256;
   for (int bn = 256; bn >= 128; bn -= 128) {
     const long long tiles = n_tiles * ((M + bn - 1) / bn);
-    const long long waves = (tiles + 147) / 148;
+    const long long slots = (bn == 128 && clustered) ? 296 : 148;      // two 128-token CTAs of that kind fit an SM
+    const long long waves = (tiles + slots - 1) / slots;
     const long long cost = waves * (128 + bn);
     if (best_cost == 0 || cost < best_cost) { best_cost = cost; best = bn; }
   }
@@ -550,7 +556,7 @@ static int bn_for(int M, int N) {
 // Split-K factor that gives every SM about two resident CTAs while keeping >= 4 k-blocks per CTA.
 SMC_API int smc_gemm_default_splits(int N, int K, int M) {
   const int n_tiles = (N + 127) / 128;
-  const int bn = bn_for(M, N);
+  const int bn = bn_for(M, N, false);
   const int m_tiles = (M + bn - 1) / bn;
   const int kblocks = (K + 63) / 64;
   int s = (296 + n_tiles * m_tiles - 1) / (n_tiles * m_tiles);
@@ -567,7 +573,7 @@ SMC_API int smc_gemm_default_splits(int N, int K, int M) {
 // are not powers of two measured clearly slower on B200 (8B QKV, 48 slabs: 3 -> 17.0 us, 4 -> 15.7 us, 6 -> 22.0 us).
 SMC_API int smc_gemm_cluster_splits(int N, int K, int M) {
   const int n_tiles = (N + 127) / 128;
-  const int bn = bn_for(M, N);
+  const int bn = bn_for(M, N, true);
   const int m_tiles = (M + bn - 1) / bn;
   const int kblocks = (K + 63) / 64;
   int s = 1;
@@ -597,7 +603,7 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
   if (clustered && (splits < 1 || splits > 8)) return -23;
   if ((epi == EPI_SWIGLU_BF16 || epi == EPI_SWIGLU_SPLIT) && (N % 128) != 0) return -22;
   if (epi == EPI_RS_F32 && (tp == nullptr || tp->tp < 1 || tp->tp > 8 || tp->rows_per_rank < 1)) return -24;
-  const int bn = bn_for(M, N);
+  const int bn = bn_for(M, N, clustered);
   GemmParams p;
   p.N = N; p.K = K; p.M = M;
   p.kblocks = (K + 63) / 64;
