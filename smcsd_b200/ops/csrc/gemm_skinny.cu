@@ -48,6 +48,7 @@ struct GemmParams {
   int N, K, M;          // weight rows, reduction length, token rows
   int kblocks;          // ceil(K / 64)
   int m_tiles;          // token tiles (grid x = weight slabs * m_tiles)
+  int stages;           // 3 selects the lean build of the 128-token tile (host-side choice only)
   int splits;
   void* out;            // fp32 [splits, M, N] | bf16 [M, ldo]
   int ldo;
@@ -67,33 +68,32 @@ struct GemmParams {
   int hb_ld;
 };
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool LEAN>
 struct GemmCfg {
   static constexpr int BM = 128, BK = 64;
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  // 128-token tiles of the split-K epilogues keep three 32 KB stages so that two CTAs share an SM (a 160- or
-  // 288-CTA grid is then one wave: 8B down at 1152 tokens 193 -> 149 us); the single-wave gate/up grids keep four
-  // (three measured 22 -> 28 us there).
-  static constexpr bool CLUSTERED = EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32 || EPI == EPI_RS_F32 ||
-                                    EPI == EPI_SWIGLU_SPLIT;
-  static constexpr int STAGES = BN <= 32 ? 5 : ((BN == 128 && CLUSTERED) ? 3 : 4);
+  // Ring depth.  128-token tiles come in two builds: LEAN keeps three 32 KB stages so that two CTAs share an SM
+  // (chosen for the split-K epilogues: 8B down at 1152 tokens 193 -> 149 us, and for multi-wave gate/up grids:
+  // 325 -> 262 us at 1152 tokens); single-wave gate/up grids keep four (three measured 22 -> 28 us there).
+  static constexpr int STAGES = BN <= 32 ? 5 : ((BN == 128 && LEAN) ? 3 : 4);
   static constexpr int TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool LEAN>
 __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW,
                                                          const __grid_constant__ CUtensorMap tmX,
                                                          const GemmParams p) {
-  using C = GemmCfg<BN, EPI>;
+  using C = GemmCfg<BN, EPI, LEAN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
-  uint64_t* empty = full + C::STAGES;
-  uint64_t* accum = empty + C::STAGES;
+  constexpr int nst = C::STAGES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + nst * C::STAGE_BYTES);
+  uint64_t* empty = full + nst;
+  uint64_t* accum = empty + nst;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* sh_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* sh_issued = sh_abort + 1;
@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
   if (p.pdl) pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) {
+    for (int s = 0; s < nst; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
       const uint64_t pol_x = l2_policy_evict_last();
       // Weights do not depend on the previous kernel: start streaming them before the
       // programmatic-dependency wait, then fetch the activations.
-      const int pre = nkb < C::STAGES ? nkb : C::STAGES;
+      const int pre = nkb < nst ? nkb : nst;
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&full[i], C::STAGE_BYTES);
         tma_load_2d(smem + i * C::STAGE_BYTES, &tmW, &full[i], (kb_begin + i) * C::BK, n_tile * C::BM, pol_w);
@@ -161,9 +161,11 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
         tma_load_2d(smem + i * C::STAGE_BYTES + C::A_BYTES, &tmX, &full[i], (kb_begin + i) * C::BK, m_tile * BN,
                     pol_x);
       *sh_issued = pre;
-      for (int i = pre; i < nkb; ++i) {
-        const int s = i % C::STAGES;
-        const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
+      // stage index and phase advance by counting (the ring depth is a launch parameter: no division per k-block)
+      int s = pre == nst ? 0 : pre;
+      uint32_t ph = pre == nst ? 1u : 0u;
+      for (int i = pre; i < nkb; ++i, ++s) {
+        if (s == nst) { s = 0; ph ^= 1u; }
         if (*sh_abort || !mbar_wait(&empty[s], ph ^ 1u)) {
           *sh_abort = 1;
           break;
@@ -179,9 +181,10 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
   } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(C::BM, BN);
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % C::STAGES;
-        const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
+      int s = 0;
+      uint32_t ph = 0u;
+      for (int i = 0; i < nkb; ++i, ++s) {
+        if (s == nst) { s = 0; ph ^= 1u; }
         if (*sh_abort || !mbar_wait(&full[s], ph)) {
           *sh_abort = 1;
           break;
@@ -305,7 +308,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
     // drain copies that were issued but never consumed, so none lands after the CTA is gone
     const int issued = *sh_issued, consumed = *sh_consumed;
     for (int i = consumed; i < issued; ++i)
-      (void)mbar_wait(&full[i % C::STAGES], (uint32_t)(i / C::STAGES) & 1u);
+      (void)mbar_wait(&full[i % nst], (uint32_t)(i / nst) & 1u);
   }
 
   if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32 || EPI == EPI_RS_F32 || EPI == EPI_SWIGLU_SPLIT) {
@@ -475,11 +478,11 @@ static int make_tmap(CUtensorMap* tm, const void* base, long long rows, long lon
   return r == CUDA_SUCCESS ? 0 : -2 - (int)r;
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool LEAN = false>
 static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, dim3 grid, cudaStream_t st) {
-  using C = GemmCfg<BN, EPI>;
+  using C = GemmCfg<BN, EPI, LEAN>;
   static bool configured = false;
-  auto kern = gemm_skinny_kernel<BN, EPI>;
+  auto kern = gemm_skinny_kernel<BN, EPI, LEAN>;
   if (!configured) {
     CUDA_CHECK_RET(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured = true;
@@ -516,7 +519,7 @@ static int dispatch_bn(int bn, const CUtensorMap& a, const CUtensorMap& b, const
     case 32: return launch<32, EPI>(a, b, p, g, st);
     case 64: return launch<64, EPI>(a, b, p, g, st);
     case 80: return launch<80, EPI>(a, b, p, g, st);
-    case 128: return launch<128, EPI>(a, b, p, g, st);
+    case 128: return p.stages == 3 ? launch<128, EPI, true>(a, b, p, g, st) : launch<128, EPI, false>(a, b, p, g, st);
     case 256: return launch<256, EPI>(a, b, p, g, st);
   }
   return -10;
@@ -539,13 +542,14 @@ SMC_API int smc_gemm_bn_for(int M) {
 // so the width is the one that minimises waves x bytes per CTA: e.g. 1152 tokens on 32 slabs run as 288 tiles of
 // 128 tokens (two full waves) rather than 160 tiles of 256 (one full wave and a nearly empty one).
 static int bn_for(int M, int N, bool clustered) {
+  (void)clustered;
   if (M <= 256 || N <= 0) return smc_gemm_bn_for(M);
   const long long n_tiles = (N + 127) / 128;
   long long best_cost = 0;
   int best = 256;
   for (int bn = 256; bn >= 128; bn -= 128) {
     const long long tiles = n_tiles * ((M + bn - 1) / bn);
-    const long long slots = (bn == 128 && clustered) ? 296 : 148;      // two 128-token CTAs of that kind fit an SM
+    const long long slots = bn == 128 ? 296 : 148;      // 128-token tiles run two CTAs per SM (three-stage ring)
     const long long waves = (tiles + slots - 1) / slots;
     const long long cost = waves * (128 + bn);
     if (best_cost == 0 || cost < best_cost) { best_cost = cost; best = bn; }
@@ -626,6 +630,12 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
   rc = make_tmap(&tmX, X, M, K, ldx, bn);
   if (rc) return rc;
   p.m_tiles = (M + bn - 1) / bn;
+  {
+    // ring depth: 128-token tiles drop to three stages where two CTAs per SM pay off (see GemmCfg)
+    const long long tiles = (long long)((N + 127) / 128) * p.m_tiles * p.splits;
+    p.stages = bn <= 32 ? 5 : 4;
+    if (bn == 128 && (clustered || tiles > 148)) p.stages = 3;
+  }
   dim3 grid(((N + 127) / 128) * p.m_tiles, p.splits, 1);
   switch (epi) {
     case EPI_PARTIAL_F32: return dispatch_bn<EPI_PARTIAL_F32>(bn, tmW, tmX, p, grid, stream);
