@@ -537,13 +537,13 @@ SMC_API int smc_gemm_bn_for(int M) {
   return 256;
 }
 
-// Token-tile width for a weight matrix of N rows.  Up to 256 tokens one tile covers the batch.  Beyond that every
+// Token-tile width for a weight matrix of N rows.  Up to 128 tokens one tile covers the batch.  Beyond that every
 // CTA is bound by the bytes it pulls through its SM (a 128-row weight slab plus BN activation rows per k-block),
 // so the width is the one that minimises waves x bytes per CTA: e.g. 1152 tokens on 32 slabs run as 288 tiles of
 // 128 tokens (two full waves) rather than 160 tiles of 256 (one full wave and a nearly empty one).
 static int bn_for(int M, int N, bool clustered) {
   (void)clustered;
-  if (M <= 256 || N <= 0) return smc_gemm_bn_for(M);
+  if (M <= 128 || N <= 0) return smc_gemm_bn_for(M);
   const long long n_tiles = (N + 127) / 128;
   long long best_cost = 0;
   int best = 256;
