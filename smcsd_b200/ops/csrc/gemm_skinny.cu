@@ -542,7 +542,10 @@ SMC_API int smc_gemm_bn_for(int M) {
 // so the width is the one that minimises waves x bytes per CTA: e.g. 1152 tokens on 32 slabs run as 288 tiles of
 // 128 tokens (two full waves) rather than 160 tiles of 256 (one full wave and a nearly empty one).
 static int bn_for(int M, int N, bool clustered) {
-  (void)clustered;
+  // 65..128 tokens on a gate/up-sized grid: two 64-token tiles per slab (two CTAs per SM, up to 296 in one wave)
+  // instead of one 128-token tile per SM (1B gate/up at 128 tokens: 22.0 -> 18.1 us)
+  if (!clustered && M > 64 && M <= 128 && N > 0 && ((N + 127) / 128) * 2 <= 296)
+    return 64;
   if (M <= 128 || N <= 0) return smc_gemm_bn_for(M);
   const long long n_tiles = (N + 127) / 128;
   long long best_cost = 0;
