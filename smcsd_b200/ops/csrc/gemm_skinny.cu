@@ -544,8 +544,11 @@ SMC_API int smc_gemm_bn_for(int M) {
 static int bn_for(int M, int N, bool clustered) {
   // 65..128 tokens on a gate/up-sized grid: two 64-token tiles per slab (two CTAs per SM, up to 296 in one wave)
   // instead of one 128-token tile per SM (1B gate/up at 128 tokens: 22.0 -> 18.1 us)
-  if (!clustered && M > 64 && M <= 128 && N > 0 && ((N + 127) / 128) * 2 <= 296)
+  if (!clustered && M > 80 && M <= 128 && N > 0 && ((N + 127) / 128) * 2 <= 296)
     return 64;
+  // 81..128 tokens on the split-K epilogues: two 64-token tiles as well (1B down at 128 tokens: 15.3 -> 13.1 us);
+  // up to 80 tokens the single 80-token tile of the verify pass stays
+  if (clustered && M > 80 && M <= 128 && N > 0) return 64;
   if (M <= 128 || N <= 0) return smc_gemm_bn_for(M);
   const long long n_tiles = (N + 127) / 128;
   long long best_cost = 0;
