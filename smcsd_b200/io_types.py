@@ -140,7 +140,9 @@ def validate_request(req: GenerateRequest, max_context: int, gamma: int) -> Opti
         return "SMC does not support stop regex"
     if len(req.input_ids) == 0:
         return "empty prompt"
-    if len(req.input_ids) + sp.max_new_tokens + gamma + 2 > max_context:
+    # a group that hits its length limit can run one more cycle under the overlapped loop before the host sees the
+    # finished mask, so two cycles of gamma + 1 tokens of slack are kept inside the block-table row
+    if len(req.input_ids) + sp.max_new_tokens + 2 * (gamma + 1) > max_context:
         return (f"prompt ({len(req.input_ids)}) + max_new_tokens ({sp.max_new_tokens}) exceeds "
                 f"the context length ({max_context})")
     return None

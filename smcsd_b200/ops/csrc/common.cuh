@@ -251,8 +251,9 @@ struct Philox {
     out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
   }
 };
-// 24 random bits: strictly inside (0,1) after the fp32 rounding
-__host__ __device__ inline float u32_to_unit(uint32_t x) { return ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f); }
+// 23 random bits mapped to (k + 0.5) / 2^23.  k + 0.5 needs 24 significant bits at most, so every value is exact
+// in fp32 and the result lies in [2^-24, 1 - 2^-24]: never 0 or 1, so -log(-log(u)) stays finite.
+__host__ __device__ inline float u32_to_unit(uint32_t x) { return ((float)(x >> 9) + 0.5f) * (1.0f / 8388608.0f); }
 __host__ __device__ inline double u32_to_unit_d(uint32_t x) { return ((double)x + 0.5) * (1.0 / 4294967296.0); }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -149,6 +149,9 @@ __global__ void sample_stage2_kernel(const RowPartial* __restrict__ parts, int n
 
 }  // namespace smc
 
+// Host-side view of the uniform mapping used for the Gumbel noise (for tests of its open-interval property).
+SMC_API float smc_u32_to_unit(unsigned int x) { return smc::u32_to_unit(x); }
+
 SMC_API int smc_sample_scratch_bytes(int rows, int nchunks) { return rows * nchunks * (int)sizeof(smc::RowPartial); }
 
 // logits fp32 partials [splits, rows(row_stride), V]; tokens_in may be null (all rows sample).

@@ -554,7 +554,9 @@ class NativeRunner:
         al = st.alloc
         ts = [st.seq_lens, st.verified_ids, st.prev_ids, st.token_counts, st.finished, st.finished_len, st.finish_code,
               st.matched_eos, st.log_weights, st.interval_weights, st.group_log_Z, st.counters, al.refcount,
-              al.free_stack, al.free_count, al.error_flag, st.bt.table]
+              al.free_stack, al.free_count, al.error_flag, st.bt.table, st.all_token_ids]
+        if getattr(st, "group_active", None) is not None:
+            ts.append(st.group_active)
         for pool in st.state_pools:
             ts += [pool.conv, pool.temporal]
         return ts

@@ -34,6 +34,8 @@ class Comm:
         group_size = group_size or world
         use_cuda = args.device != "cpu" and torch.cuda.is_available()
         backend = "nccl" if use_cuda else "gloo"
+        # symmetric-memory heaps are used with plain peer loads/stores only: keep them off NVLink multicast objects
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         if not dist.is_initialized():
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             os.environ.setdefault("MASTER_PORT", str(port))

@@ -10,6 +10,7 @@ CUDA graph is captured, so captured kernels can carry the peer addresses as plai
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Tuple
 
 import torch
@@ -17,6 +18,9 @@ import torch
 
 class SymmHeap:
     def __init__(self, nbytes: int, device: torch.device, group, rank: int, world: int):
+        # No kernel here uses multimem / NVLS, and a rank that exits while its buffer is bound to an NVLink multicast
+        # object can fault its peers, so PyTorch's rendezvous is told not to create that binding.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.nbytes = int(nbytes)
         self.device = device

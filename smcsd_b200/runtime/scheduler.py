@@ -236,6 +236,9 @@ class SMCScheduler:
         g = self.running.get(rid)
         if g is not None:
             self._flush_pending()
+            # the pending snapshot may have shown the group finished: then it was finalized and released already
+            if self.running.get(rid) is not g:
+                return
             self._release_group(g)
             self.outbox.append(RequestOutput(rid, [], True, {"type": "abort"}, aborted=True))
 

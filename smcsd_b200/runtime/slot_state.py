@@ -205,7 +205,9 @@ class SlotState:
 
     def free_group(self, group_id: str) -> None:
         """Release a finished group's pages, state rows, slots and row."""
-        row = self.group_rows.pop(group_id)
+        row = self.group_rows.pop(group_id, None)
+        if row is None:                       # already released (e.g. finalized by a snapshot that was still pending)
+            return
         slots = self.row_slots.pop(row)
         idx = self._upload(slots, torch.int64)
         lens = self.seq_lens[idx].tolist()

@@ -138,3 +138,43 @@ def test_debug_records_are_appended(tmp_path, monkeypatch):
     s.run_until_idle()
     rec = [json.loads(x) for x in path.read_text().splitlines()]
     assert rec and rec[0]["event"] == "finalize" and "pid" in rec[0] and "timestamp_ns" in rec[0]
+
+
+def test_abort_of_a_group_whose_final_snapshot_is_pending():
+    """With the overlapped loop a request's last cycle leaves one snapshot pending; an abort that arrives in that
+    window must not release the group twice nor answer twice."""
+    s = _sched(enable_overlap=True)
+    s.add_request(_req("a", max_new_tokens=8, ignore_eos=True))       # gamma + 1 = 4 tokens per cycle: two cycles
+    outs = []
+    for _ in range(50):
+        outs += s.step()
+        if s.pending and "a" in s.running:
+            s.abort("a")
+            outs += list(s.outbox)
+            s.outbox.clear()
+    outs += s.run_until_idle()
+    mine = [o for o in outs if isinstance(o, RequestOutput) and o.rid == "a"]
+    assert len(mine) >= 1
+    assert len([o for o in mine if o.finished]) == 1 or all(o.aborted for o in mine)
+    s.check_idle_invariants()
+    s.alloc.check_conservation()
+
+
+def test_request_at_the_context_limit_survives_the_extra_overlap_cycle():
+    """Two groups with overlap on: the one that ends on length gets one more cycle while the other keeps running;
+    its block-table row must have room for it."""
+    s = _sched(enable_overlap=True, max_running_requests=2)
+    ctx = s.args.context_len if hasattr(s.args, "context_len") else s.bt.table.shape[1]
+    gamma = s.args.gamma
+    n = 12
+    longest = ctx - n - 2 * (gamma + 1)
+    assert validate_request(_req("x", n=n, max_new_tokens=longest + 1), ctx, gamma) is not None
+    assert validate_request(_req("x", n=n, max_new_tokens=longest), ctx, gamma) is None
+    if longest > 400:          # keep the CPU run short: the bound itself is checked above
+        return
+    s.add_request(_req("edge", n=n, max_new_tokens=longest, ignore_eos=True))
+    s.add_request(_req("other", n=n, max_new_tokens=longest, ignore_eos=True))
+    outs = s.run_until_idle()
+    done = [o for o in outs if isinstance(o, RequestOutput)]
+    assert len(done) == 2 and not any(o.aborted for o in done)
+    s.check_idle_invariants()
