@@ -21,7 +21,11 @@
 // outstanding copies, frees its tensor memory and returns.
 #include <string.h>
 
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
+#include "tmap_host.h"
 
 namespace smc {
 
@@ -447,37 +451,6 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &ptr, 12000, cudaEnableDefault, &qres) ==
-            cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// bf16 matrix [rows, cols] row-major with leading dimension ld (elements); box = [box_rows, 64 cols]
-static int make_tmap(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box_rows) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) return -1;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -2 - (int)r;
-}
-
 template <int BN, int EPI, bool LEAN = false>
 static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, dim3 grid, cudaStream_t st) {
   using C = GemmCfg<BN, EPI, LEAN>;
@@ -602,6 +575,37 @@ struct NormLink {            // host-side description of the folded RMSNorm (all
   int ssq_mstride;
 };
 
+// Encoded tensor maps are cached per (base, shape, pitch, box): an encode costs a driver call, and eager chains
+// (prompt passes, batches beyond the graph caps) issue two per GEMM with the same few operands over and over.
+struct TmapKey {
+  const void* base; long long rows, cols, ld; int box;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box == o.box;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = std::hash<const void*>()(k.base);
+    h = h * 1000003u ^ std::hash<long long>()(k.rows * 131 + k.box);
+    h = h * 1000003u ^ std::hash<long long>()(k.cols * 8191 + k.ld);
+    return h;
+  }
+};
+static int cached_tmap(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box) {
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  static std::mutex mu;
+  const TmapKey key{base, rows, cols, ld, box};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *tm = it->second; return 0; }
+  const int rc = smc::make_tmap(tm, base, rows, cols, ld, box);
+  if (rc == 0) {
+    if (cache.size() > 65536) cache.clear();
+    cache.emplace(key, *tm);
+  }
+  return rc;
+}
+
 static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo, int splits,
                       int epi, int* status, int pdl, const smc::TpLink* tp, const NormLink* nl, cudaStream_t stream) {
   using namespace smc;
@@ -631,9 +635,9 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
     if (p.ssq_out != nullptr && epi != EPI_RESID_F32) return -25;
   }
   CUtensorMap tmW, tmX;
-  int rc = make_tmap(&tmW, W, N, K, K, 128);
+  int rc = cached_tmap(&tmW, W, N, K, K, 128);
   if (rc) return rc;
-  rc = make_tmap(&tmX, X, M, K, ldx, bn);
+  rc = cached_tmap(&tmX, X, M, K, ldx, bn);
   if (rc) return rc;
   p.m_tiles = (M + bn - 1) / bn;
   {

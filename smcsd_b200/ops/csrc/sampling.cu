@@ -7,25 +7,11 @@
 // lives in device memory so captured graphs draw fresh noise on every replay.
 // Logits arrive as fp32 split-K partials [splits, rows, V] straight from the lm_head GEMM.
 #include "common.cuh"
+#include "sample_core.cuh"
 
 namespace smc {
 
 constexpr int S1_THREADS = 256;
-
-struct RowPartial {
-  float max_s, sum_s;      // running max / sum of exp for scaled = alpha * x / T
-  float max_b, sum_b;      // same for base = x / T
-  float best, best_scaled; // best perturbed score and its unperturbed scaled value
-  int best_idx;
-  int pad;
-};
-
-__device__ __forceinline__ void lse_merge(float& m, float& s, float m2, float s2) {
-  const float M = fmaxf(m, m2);
-  if (M == -INFINITY) { m = M; s = 0.f; return; }
-  s = s * __expf(m - M) + s2 * __expf(m2 - M);
-  m = M;
-}
 
 __global__ void __launch_bounds__(S1_THREADS)
 sample_stage1_kernel(const float* __restrict__ logits, int splits, long long split_stride, long long row_stride, int V,

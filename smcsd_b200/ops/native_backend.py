@@ -316,6 +316,14 @@ class NativeRunner:
         self.defer = bool(a.defer_bonus)
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.launches_per_cycle = 0
+        # Whole-forward persistent kernels (one launch per model forward) for dense unsharded models; batches beyond
+        # their 128-token tile keep the one-kernel-per-step chains above.  SMC_PERSISTENT=0 switches them off.
+        self.pf_target = self.pf_draft = None
+        if _env_flag("SMC_PERSISTENT", True):
+            from .native_forward import PersistentLlama, supported
+            for name, nm in (("pf_target", self.target), ("pf_draft", self.draft)):
+                if isinstance(nm, NativeLlama) and nm.fold and supported(nm.m, 1):
+                    setattr(self, name, PersistentLlama(nm.m, nm.kv, nm.bt, 128, self.status))
 
     def _wrap(self, model, kv, bt, max_tokens, max_logit_rows, splits, pdl, state=None):
         if model.cfg.arch != "llama":
@@ -460,37 +468,56 @@ class NativeRunner:
                           cycle_counter=self._counters, call_id=call_id, scratch=self.sample_scratch,
                           nchunks=self.nchunks, tok_out=tok_out, logp_out=logp_out, logz_out=logz_out, pdl=self.pdl)
 
+    def _use_pf(self, which: str, tokens: int) -> bool:
+        pf = self.pf_target if which == "target" else self.pf_draft
+        return pf is not None and tokens <= pf.T
+
+    def _model_step(self, which: str, ids, pos, locs, rows, prefix, bs: int, E: int, *, lm_rows: int, lm_off: int = 0,
+                    lm_step: int = 1, call_id: int = 0, temperature: float = 1.0, alpha: float = 1.0, tokens_in=None,
+                    tok_out=None, logp_out=None, logz_out=None) -> None:
+        """One model forward for bs sequences of E new tokens, followed (when lm_rows > 0) by the lm_head over rows
+        lm_off + i * lm_step and the fused sampler / scorer: one persistent launch, or the kernel chain."""
+        if self._use_pf(which, bs * E):
+            pf = self.pf_target if which == "target" else self.pf_draft
+            pf.run(ids, pos, locs, rows, prefix, bs, E, lm_rows=lm_rows, lm_off=lm_off, lm_step=lm_step,
+                   temperature=temperature, alpha=alpha, tokens_in=tokens_in, seed=self.seed,
+                   cycle_counter=self._counters, call_id=call_id, tok_out=tok_out, logp_out=logp_out,
+                   logz_out=logz_out)
+            return
+        nm = self.target if which == "target" else self.draft
+        nm.forward(ids, pos, locs, rows, prefix, bs, E)
+        if lm_rows > 0:
+            nm.lm_head(lm_rows, row_offset=lm_off, row_step=lm_step)
+            self._sample(nm, lm_rows, call_id, temperature, alpha, tokens_in, tok_out, logp_out, logz_out)
+
     def _cycle_body(self, st) -> None:
         ns, b = self.ns, self.ns.bufs
         bs, g, G = ns.bs, self.gamma, self.G
         self._counters = st.counters
         rows = ns.active[:bs]
         dr, lq = ns.drafts, ns.logq
+        Td = self.T_draft
         if self.defer:
-            self.draft.forward(b["head_ids"], b["head_pos"], b["head_locs"], rows, b["head_prefix"], bs, 2)
-            self.draft.lm_head(bs, row_offset=1, row_step=2)
-            self._sample(self.draft, bs, 0, self.T_draft, 1.0, None, dr[:bs], lq[:bs], None)
+            self._model_step("draft", b["head_ids"], b["head_pos"], b["head_locs"], rows, b["head_prefix"], bs, 2,
+                             lm_rows=bs, lm_off=1, lm_step=2, call_id=0, temperature=Td, tok_out=dr[:bs],
+                             logp_out=lq[:bs])
             for s in range(1, g):
-                self.draft.forward(dr[(s - 1) * bs: s * bs], b["step_pos"][s * bs:(s + 1) * bs],
-                                   b["step_locs"][s * bs:(s + 1) * bs], rows, b["step_pos"][s * bs:(s + 1) * bs], bs, 1)
-                self.draft.lm_head(bs)
-                self._sample(self.draft, bs, s, self.T_draft, 1.0, None, dr[s * bs:(s + 1) * bs],
-                             lq[s * bs:(s + 1) * bs], None)
+                sl = slice(s * bs, (s + 1) * bs)
+                self._model_step("draft", dr[(s - 1) * bs: s * bs], b["step_pos"][sl], b["step_locs"][sl], rows,
+                                 b["step_pos"][sl], bs, 1, lm_rows=bs, call_id=s, temperature=Td, tok_out=dr[sl],
+                                 logp_out=lq[sl])
         else:
             for s in range(g + 1):
+                sl = slice(s * bs, (s + 1) * bs)
                 ids = b["x0"] if s == 0 else dr[(s - 1) * bs: s * bs]
-                self.draft.forward(ids, b["step_pos"][s * bs:(s + 1) * bs], b["step_locs"][s * bs:(s + 1) * bs], rows,
-                                   b["step_pos"][s * bs:(s + 1) * bs], bs, 1)
-                if s == g:
-                    break
-                self.draft.lm_head(bs)
-                self._sample(self.draft, bs, s, self.T_draft, 1.0, None, dr[s * bs:(s + 1) * bs],
-                             lq[s * bs:(s + 1) * bs], None)
+                self._model_step("draft", ids, b["step_pos"][sl], b["step_locs"][sl], rows, b["step_pos"][sl], bs, 1,
+                                 lm_rows=bs if s < g else 0, call_id=s, temperature=Td,
+                                 tok_out=dr[sl] if s < g else None, logp_out=lq[sl] if s < g else None)
         K.assemble_verify(ns.io, dr, bs, g)
-        self.target.forward(b["verify_ids"], b["positions_verify"], b["cache_locs"], rows, b["orig_seq"], bs, G)
-        self.target.lm_head(bs * G)
-        self._sample(self.target, bs * G, g + 1, self.T_target, self.alpha, b["verify_given"], ns.verify_tok,
-                     ns.verify_logp, ns.verify_logz)
+        self._model_step("target", b["verify_ids"], b["positions_verify"], b["cache_locs"], rows, b["orig_seq"], bs, G,
+                         lm_rows=bs * G, call_id=g + 1, temperature=self.T_target, alpha=self.alpha,
+                         tokens_in=b["verify_given"], tok_out=ns.verify_tok, logp_out=ns.verify_logp,
+                         logz_out=ns.verify_logz)
 
     def decode_cycle(self, worker, cin: CycleInputs) -> CycleOutputs:
         """Eager kernel chain for one cycle (the graph path replays the same launches)."""
@@ -526,6 +553,10 @@ class NativeRunner:
         st.step += 1
         bs = ns.bs
         key = (bs, self.target.set_context(ctx_hint, bs, (self.G,)), self.draft.set_context(ctx_hint, bs, (1, 2)))
+        if self._use_pf("target", bs * self.G):
+            key += (self.pf_target.set_context(ctx_hint, bs, (self.G,)),)
+        if self._use_pf("draft", bs * 2):
+            key += (self.pf_draft.set_context(ctx_hint, bs, (1, 2)),)
         if not self.use_graph or bs > self.graph_max_bs or ctx_hint > self.graph_max_context:
             self._full_cycle(st)           # same kernels, launched one by one (beyond the capture caps)
             return
