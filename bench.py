@@ -1,12 +1,17 @@
 #!/usr/bin/env python
 """Headline benchmark: output tokens/s of SMC speculative decoding, Llama-3.1-8B target +
 Llama-3.2-1B draft, N=8 particles, gamma=8, T=0.7, one request per GPU (data-parallel replicas),
-bf16 random-init weights, synthetic prompts (uniform token ids, log-normal lengths, median 200).
+bf16 random-init weights, synthetic prompts (uniform token ids).
 
 A "step" is one decode cycle: every particle advances gamma+1 = 9 tokens, so each request emits
-9 output tokens per step.  The device-timed value brackets exactly K replays of the cycle with
-CUDA events (max over ranks); the end-to-end value times whole ``SMCEngine.generate`` calls
-(prompt upload from pinned memory, prefill, all cycles, token download).
+9 output tokens per step.  ``value`` brackets exactly K replays of the cycle with CUDA events (max
+over ranks); ``repeats`` re-times the same K cycles a few more times (median and spread);
+``e2e`` times whole ``SMCEngine.generate`` calls in the published shape (256-token prompts, 1024
+new tokens: prompt upload from pinned memory, prefill, all cycles, token download) and ``config2``
+does the same with log-normal prompt lengths (median 200) and 512 new tokens.  On two or more GPUs
+the same job then measures the fused collective paths: a 70B-shaped tensor-parallel layer chain
+(kernel-issued all-gather / reduce-scatter against cuBLAS + NCCL) and a particle-parallel decode
+cycle with forced cross-GPU resampling, reported under ``fused``.
 
     python bench.py --gpus 1 --steps 40 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
@@ -16,12 +21,14 @@ CUDA events (max over ranks); the end-to-end value times whole ``SMCEngine.gener
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
+import statistics
 import sys
 import time
 
-PUBLISHED_TOKS = 677.0     # reference docs/smc/performance.md:14-16 (1x B200, 256-token prompts)
+PUBLISHED_TOKS = 677.0     # reference docs/smc/performance.md:14-16 (1x B200, 256-token prompts, 1024 outputs)
 
 
 def reference_arm(args) -> int:
@@ -38,6 +45,39 @@ def reference_arm(args) -> int:
     return 0
 
 
+def _e2e(eng, sched, lens, new_tokens, vocab, rank, world, dist, torch, seed):
+    """Wall-clock tokens/s of ``generate`` over the given prompts (one untimed request of the same shape first)."""
+    from smcsd_b200.utils.prompts import random_prompts
+    prompts = random_prompts(lens, vocab, seed=seed + rank)
+    sp = {"max_new_tokens": new_tokens, "ignore_eos": True}
+    # cycle graphs are captured lazily per (batch, attention split plan): warm them up outside the timed region
+    eng.generate(input_ids=random_prompts([max(lens)], vocab, seed=seed + 991 + rank)[0], sampling_params=sp)
+    b0 = dict(sched.io_bytes)
+    c0 = sched.stats["cycles"]
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    n_out = 0
+    for p in prompts:
+        o = eng.generate(input_ids=p, sampling_params=sp)
+        n_out += o["completion_tokens"]
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    tt = torch.tensor([dt], device="cuda", dtype=torch.float64)
+    nn = torch.tensor([float(n_out)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dist.all_reduce(nn, op=dist.ReduceOp.SUM)
+    cyc = max(sched.stats["cycles"] - c0, 1)
+    return {"value": float(nn.item()) / float(tt.item()), "unit": "output tokens/s",
+            "h2d_bytes_per_step": (sched.io_bytes["h2d"] - b0["h2d"]) / cyc,
+            "d2h_bytes_per_step": (sched.io_bytes["d2h"] - b0["d2h"]) / cyc,
+            "requests_per_gpu": len(lens), "new_tokens": new_tokens, "prompt_lens": list(lens),
+            "warmup": "one untimed request of the same shape",
+            "timing": "wall clock around generate() calls, cuda-synchronized, max over ranks"}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -50,9 +90,12 @@ def main() -> int:
     ap.add_argument("-g", "--gamma", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=256,
                     help="prompt length in tokens (the published headline uses 256; 0 = log-normal, median 200)")
+    ap.add_argument("--repeats", type=int, default=4, help="extra timed repeats of the K cycles (median / spread)")
     ap.add_argument("--e2e-requests", type=int, default=2)
     ap.add_argument("--e2e-new-tokens", type=int, default=1024, help="the published headline generates 1024")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-config2", action="store_true")
+    ap.add_argument("--no-fused", action="store_true", help="skip the multi-GPU fused-collective measurements")
     ap.add_argument("--no-graph", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -74,12 +117,16 @@ def main() -> int:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local)
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     G = args.gamma + 1
     steps, warm = args.steps, max(args.warmup, 3)
-    need_tokens = (steps + warm + 4) * G + 1
+    reps = max(0, args.repeats)
+    need_tokens = (steps * (1 + reps) + warm + 4) * G + 1
     new_tokens = max(512, need_tokens)
+    sampler = ClockSampler(local).start() if rank == 0 else None      # clocks over the whole benchmark
     eng = SMCEngine(f"preset:{args.target}", f"preset:{args.draft}", n_particles=args.n_particles, gamma=args.gamma,
                     draft_temperature=0.7, target_temperature=0.7, resample_threshold=0.5, max_running_requests=1,
                     base_gpu_id=local, context_length=max(4096, args.prompt_len) + max(new_tokens, args.e2e_new_tokens) + 4 * G,
@@ -98,83 +145,102 @@ def main() -> int:
         raise SystemExit(f"the benchmark request was not admitted: {[getattr(o, 'error', None) for o in sched.outbox]}")
     for _ in range(warm):
         sched.step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(local).start() if rank == 0 else None
-    l0 = K.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        sched.step()
-    e1.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if sampler else None
-    per_cycle_launches = getattr(sched.native_runner, "launches_per_cycle", 0) if sched.native_runner else 0
-    launches = per_cycle_launches * steps if per_cycle_launches else K.launch_count - l0
-    status = sched.native_runner.check_status() if sched.native_runner else 0
-    sched.abort("bench")
-    sched.step()
-    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
-    toks = steps * G * world
-    value = toks / (ms_max / 1e3)
 
-    # ---- end to end through SMCEngine.generate ---------------------------------------------------
-    e2e = None
-    if not args.no_e2e:
-        n_req = args.e2e_requests
-        lens2 = [args.prompt_len] * n_req if args.prompt_len else lognormal_lengths(n_req, seed=2000 + rank)
-        prompts = random_prompts(lens2, vocab, seed=77 + rank)
-        sp = {"max_new_tokens": args.e2e_new_tokens, "ignore_eos": True}
-        # one untimed request of the same shape: cycle graphs are captured lazily per (batch, attention split plan)
-        eng.generate(input_ids=random_prompts(lens2[:1], vocab, seed=991 + rank)[0], sampling_params=sp)
-        b0 = dict(sched.io_bytes)
-        c0 = sched.stats["cycles"]
+    def timed_cycles() -> float:
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-        t0 = time.perf_counter()
-        n_out = 0
-        for p in prompts:
-            o = eng.generate(input_ids=p, sampling_params=sp)
-            n_out += o["completion_tokens"]
         torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-        tt = torch.tensor([dt], device="cuda", dtype=torch.float64)
-        nn = torch.tensor([float(n_out)], device="cuda", dtype=torch.float64)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            sched.step()
+        e1.record()
+        torch.cuda.synchronize()
         if world > 1:
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            dist.all_reduce(nn, op=dist.ReduceOp.SUM)
-        cyc = max(sched.stats["cycles"] - c0, 1)
-        e2e = {"value": float(nn.item()) / float(tt.item()), "unit": "output tokens/s",
-               "h2d_bytes_per_step": (sched.io_bytes["h2d"] - b0["h2d"]) / cyc,
-               "d2h_bytes_per_step": (sched.io_bytes["d2h"] - b0["d2h"]) / cyc,
-               "requests_per_gpu": n_req, "new_tokens": args.e2e_new_tokens, "prompt_lens": lens2,
-               "warmup": "one untimed request of the same shape",
-               "timing": "wall clock around generate() calls, cuda-synchronized, max over ranks"}
+            dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    l0 = K.launch_count
+    ms_max = timed_cycles()
+    per_cycle_launches = getattr(sched.native_runner, "launches_per_cycle", 0) if sched.native_runner else 0
+    launches = per_cycle_launches * steps if per_cycle_launches else K.launch_count - l0
+    more = [timed_cycles() / steps for _ in range(reps)]
+    status = sched.native_runner.check_status() if sched.native_runner else 0
+    sched.abort("bench")
+    sched.step()
+    toks = steps * G * world
+    value = toks / (ms_max / 1e3)
+    all_ms = [ms_max / steps] + more
+    repeats = {"ms_per_step": all_ms, "median_ms_per_step": statistics.median(all_ms),
+               "min_ms_per_step": min(all_ms), "max_ms_per_step": max(all_ms),
+               "note": "first entry is the headline region; the others re-time the same K cycles later in the request"}
+
+    # ---- end to end through SMCEngine.generate ---------------------------------------------------
+    e2e = config2 = None
+    if not args.no_e2e:
+        n_req = args.e2e_requests
+        lens2 = [args.prompt_len] * n_req if args.prompt_len else lognormal_lengths(n_req, seed=2000 + rank)
+        e2e = _e2e(eng, sched, lens2, args.e2e_new_tokens, vocab, rank, world, dist, torch, seed=77)
+    if not args.no_config2 and not args.no_e2e:
+        lens3 = lognormal_lengths(max(2, args.e2e_requests), seed=3000 + rank)
+        config2 = _e2e(eng, sched, lens3, 512, vocab, rank, world, dist, torch, seed=177)
+        config2["shape"] = "log-normal prompt lengths (median 200, sigma 1, clipped 4..2048), 512 new tokens"
+        config2["vs_published_567_gsm8k_shape"] = None
+    status |= sched.native_runner.check_status() if sched.native_runner else 0
+
+    # ---- fused collective paths (two or more GPUs) ----------------------------------------------------
+    fused = None
+    if world > 1 and not args.no_fused and args.impl == "native":
+        eng.shutdown()
+        del eng, sched
+        gc.collect()
+        torch.cuda.empty_cache()
+        fused = {"status": 0}
+        try:
+            from smcsd_b200.bench import pp_cycle, tp_layers
+            ns = tp_layers._parser().parse_args(["--model", "llama-3.1-70b", "--layers", "8", "--bs", "8", "--E", "9"])
+            r = tp_layers.run(ns, init_pg=False)
+            fused.update({"tp_layer_us": r["fused_us_per_layer"], "tp_layer_nccl_us": r["cublas_nccl_us_per_layer"],
+                          "tp_floor_us": r["floor_us_per_layer"], "tp_tokens": r["tokens"], "tp_size": r["tp"],
+                          "tp_model": "llama-3.1-70b layers (8 full-width layers per rank shard)",
+                          "tp_fraction_of_floor": r["fused_fraction_of_floor"]})
+            fused["status"] |= int(r["device_status"])
+            gc.collect()
+            torch.cuda.empty_cache()
+            r = pp_cycle.run(steps=steps, warmup=warm)
+            fused.update({"pp_cycle_ms": r["pp_cycle_ms"], "pp_nvlink_bytes_per_cycle": r["pp_nvlink_bytes_per_cycle"],
+                          "pp_n_particles": r["n_particles"], "pp_remote_copies_last_cycle": r["remote_copies_last_cycle"],
+                          "pp_tokens_per_s": r["tokens_per_s"]})
+            fused["status"] |= int(r["status"])
+        except Exception as e:       # the headline line must still be printed
+            fused["status"] = -1
+            fused["error"] = f"{type(e).__name__}: {e}"[:300]
+    clocks = sampler.stop() if sampler else None
 
     if rank == 0:
+        e2e_ratio = (e2e["value"] / (PUBLISHED_TOKS * world)) if e2e else None
         line = {
             "metric": "output tokens/s (Llama-3.1-8B target + Llama-3.2-1B draft, SMC N=8 gamma=8)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warm,
             "ms_per_step": ms_max / steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": value / (PUBLISHED_TOKS * world), "dtype": "bf16", "data": "synthetic",
-            "impl": args.impl,
+            "vs_baseline": e2e_ratio if e2e_ratio is not None else value / (PUBLISHED_TOKS * world),
+            "vs_baseline_device_timed": value / (PUBLISHED_TOKS * world),
+            "dtype": "bf16", "data": "synthetic", "impl": args.impl,
             "config": {"model": f"{args.target}+{args.draft}", "global_batch": world, "seq_len": lens[0],
                        "parallelism": f"dp{world}", "n_particles": args.n_particles, "gamma": args.gamma,
                        "tokens_per_step_per_request": G, "cycle_graph": not args.no_graph,
                        "l2": "inputs larger than L2: every step streams 16 GB of target and 8 x 2.5 GB of draft weights",
                        "weights": "random-init bf16 from a seed", "vs_baseline_note":
-                       "published 677 tok/s is per GPU, single request; scaled by n_gpus for the aggregate"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "device_status": int(status),
+                       "vs_baseline = end-to-end tokens/s (e2e.value) over the published 677 tok/s per GPU (wall clock, "
+                       "same 256-in / 1024-out shape); vs_baseline_device_timed divides the device-timed decode rate "
+                       "by the same figure"},
+            "clocks": clocks, "repeats": repeats, "e2e": e2e, "config2": config2, "fused": fused,
+            "gpu_launches": int(launches), "device_status": int(status),
         }
         print(json.dumps(line))
     if world > 1:

@@ -22,7 +22,7 @@ import torch
 import torch.distributed as dist
 
 
-def main(argv=None) -> None:
+def _parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="llama-3.1-70b")
     ap.add_argument("--layers", type=int, default=8)
@@ -34,7 +34,13 @@ def main(argv=None) -> None:
                     help="shrink heads and FFN by this factor (run on one rank to see one shard's chain without peers)")
     ap.add_argument("--stage-times", action="store_true",
                     help="also time every kernel of the fused chain (eager launches with an event after each)")
-    ns = ap.parse_args(argv)
+    return ap
+
+
+def run(ns, init_pg: bool = True) -> dict:
+    """Runs both arms on the ranks of the current torchrun job and returns the result record (the same on every
+    rank).  ``ns``: namespace with the fields of ``_parser()``.  With ``init_pg=False`` the caller's default process
+    group (NCCL) is used and left alive."""
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     from ..memory.pools import KVPool, KVSpec
     from ..models.config import preset
@@ -47,7 +53,8 @@ def main(argv=None) -> None:
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
     torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", device_id=dev)
+    if init_pg:
+        dist.init_process_group("nccl", device_id=dev)
     K.tp_lib()
     cfg = dataclasses.replace(preset(ns.model), n_layers=ns.layers)
     if ns.shard_like > 1:
@@ -163,16 +170,25 @@ def main(argv=None) -> None:
     # bf16 rows arrive twice per layer
     link_bytes = 2 * (world - 1) / world * T * d * 4 + 2 * (world - 1) / world * T * d * 2
     floor_us = max(per_layer_w / (hbm * 1e3), link_bytes / (770.0 * 1e3))
-    if rank == 0:
-        print(json.dumps({
+    res = ({
             "bench": "tp_layers", "model": cfg.name, "layers": ns.layers, "tp": world, "tokens": T, "context": P,
             "fused_us_per_layer": fused_ms * 1e3 / ns.layers, "cublas_nccl_us_per_layer": base_ms * 1e3 / ns.layers,
             "speedup": base_ms / fused_ms, "floor_us_per_layer": floor_us,
             "fused_fraction_of_floor": floor_us / (fused_ms * 1e3 / ns.layers),
             "weight_MB_per_rank_per_layer": per_layer_w / 1e6, "nvlink_MB_per_rank_per_layer": link_bytes / 1e6,
             "peaks": src, "device_status": fused_status, "fused_stage_us_eager": stage_us,
-            "timing": "CUDA events around graph replays, max over ranks"}))
+            "timing": "CUDA events around graph replays, max over ranks"})
     dist.barrier()
+    del nm, heap, m, kv
+    torch.cuda.empty_cache()
+    return res
+
+
+def main(argv=None) -> None:
+    ns = _parser().parse_args(argv)
+    res = run(ns, init_pg=True)
+    if int(os.environ["RANK"]) == 0:
+        print(json.dumps(res))
     dist.destroy_process_group()
 
 

@@ -5,7 +5,9 @@
 // microseconds each) is as long as the time their weights need to stream from HBM.  Here the hand-offs become
 // grid-wide barriers inside one kernel and, more importantly, the weight stream never stops: a producer thread
 // per CTA keeps a shared-memory ring full of weight tiles of the *following* phases (weights do not depend on
-// activations), so HBM stays busy while a phase drains, synchronises and the next one starts.
+// activations), so HBM stays busy while a phase drains, synchronises and the next one starts.  (How much that buys
+// is bounded by the ring: about 13 MB of prefetch on the whole GPU.  Measured, a K-split phase here costs 6-8 us
+// against 4.7-5.4 us for the stand-alone GEMM kernels, so the kernel is an option of the runner, not its default.)
 //
 // Phases (all CTAs walk the same list):
 //   embed                       ids -> fp32 residual h, bf16 copy hb, per-128-column sums of squares
@@ -21,10 +23,12 @@
 //   merge                       per row: token, log-probability, logZ
 //
 // GEMMs are tcgen05 with swapped operands (a 128-row weight slab is the M operand, the tokens are N, fp32
-// accumulator in tensor memory, two accumulators so the epilogue of one unit overlaps the MMAs of the next).  Work is
-// dealt stream-K style: the (slab, k-block) iteration space of a phase is cut into equal contiguous shares, one per
-// CTA; a slab covered by several CTAs is reduced by the last of them to arrive (partials parked in an L2-resident
-// workspace, summed in a fixed order, so results do not depend on arrival order).
+// accumulator in tensor memory, two accumulators so the epilogue of one unit overlaps the MMAs of the next).  The grid
+// is made of thread-block clusters of eight CTAs.  Matrices with few slabs (QKV, o-proj, down) are split along K
+// over the CTAs of a cluster: each parks its fp32 tile in shared memory, signals its seven peers through an
+// mbarrier, and every CTA then sums its share of the token columns over all eight tiles through distributed shared
+// memory in a fixed order (deterministic, nothing visits HBM; a reduction through an L2 workspace measured about
+// 7 us per phase, this one about 1.5).  Matrices with many slabs (gate/up, lm_head) are dealt as whole slabs.
 //
 // Warp roles: 0 = TMA producer, 1 = MMA issuer, 4..7 = epilogue (TMEM lanes 32 * (warp % 4)), 2..7 = attention.
 // Every wait is bounded; a timeout raises a status bit and an abort flag that short-circuits all later waits.
@@ -39,7 +43,7 @@ namespace smc {
 
 constexpr int PF_THREADS = 256;
 constexpr int PF_MAX_STAGES = 12;
-constexpr int PF_RANGE = 1024;            // page ids staged per attention pass
+constexpr int PF_RANGE = 512;             // page ids staged per attention pass
 constexpr int PF_A_BYTES = 128 * 64 * 2;  // one weight tile: 128 rows x 64 k
 constexpr int PF_TMEM_COLS = 256;         // two accumulators of up to 128 columns
 
@@ -77,8 +81,6 @@ struct PfParams {
   __nv_bfloat16* act;            // [M, ffn]
   int ssq_ld, pad1;
   // ---- workspaces
-  float* partials;               // [ctas][2][BN][128] split-K partial tiles
-  int* slab_ctr;                 // [max slabs] arrival counters (zero between uses)
   float* att_part;               // [bs * Hkv * KS][n_mt][16 D + 64] key-split partial states
   int* att_ctr;                  // [bs * Hkv]
   // ---- sampling
@@ -94,14 +96,19 @@ struct PfParams {
   // ---- synchronisation
   unsigned int* sync;            // [0] phase arrivals, [1] exit arrivals, [2] abort flag
   int* status;
+  long long* trace;              // optional [phases][ctas][8] nanosecond stamps: 0 inputs seen ready, 1 phase work done, 2.. detail
 };
 
 struct PfShared {
   uint64_t full[PF_MAX_STAGES], empty[PF_MAX_STAGES], acc_full[2], acc_empty[2];
+  uint64_t red_full, red_done;    // cluster reduction: all eight tiles parked / all eight CTAs done reading this one
   uint32_t tmem_slot;
   volatile int abort, issued, consumed;
   int flag, pad;
+  volatile int open_upto;         // highest phase whose inputs this CTA's leader has seen ready
+  int pad2;
   int pos[16];
+  float xcol[2][4][64];           // up-channel values handed to the gate rows (split gate/up reduction)
   float rstd[128];
   float ssq[2][4][16];
   RowPartial rp[128];
@@ -148,8 +155,10 @@ __device__ __forceinline__ bool pf_wait_counter(const PfCtx& c, const unsigned i
   if (*c.sh_abort) return false;
   const long long t0 = clock64();
   for (;;) {
-    for (int i = 0; i < 32; ++i)
+    for (int i = 0; i < 32; ++i) {
+      __nanosleep(40);                 // hundreds of pollers share one L2 line with the arriving atomics
       if (ld_acquire_gpu_u32(ctr) >= want) return true;
+    }
     if (*c.sh_abort || *c.g_abort) {
       *c.sh_abort = 1;
       return false;
@@ -160,18 +169,62 @@ __device__ __forceinline__ bool pf_wait_counter(const PfCtx& c, const unsigned i
     }
   }
 }
+// The leader's wait for a phase, published to the producer of the same CTA.
+__device__ __forceinline__ void pf_leader_wait(const PfParams& p, const PfCtx& c, volatile int* open_upto, int ph,
+                                               int ncta) {
+  pf_wait_counter(c, p.sync + PF_SYNC_BARRIER, (unsigned int)ph * (unsigned int)ncta);
+  __threadfence();
+  *open_upto = ph;
+}
 __device__ __forceinline__ void bar_epi() { group_barrier(1, 128); }     // warps 4..7
 __device__ __forceinline__ void bar_att() { group_barrier(2, 192); }     // warps 2..7
 
+constexpr int PF_CLUSTER = 8;
+// arrive on the mbarrier at the same shared-memory offset in CTA `rank` of this cluster; earlier writes of the
+// arriving thread (and, through a preceding CTA barrier, of its CTA) are visible to whoever waits with acquire
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(dsmem_map(smem_u32(bar), rank))
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool pf_mbar_wait_cluster(const PfCtx& c, uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  if (*c.sh_abort) return false;
+  const long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (*c.sh_abort || *c.g_abort) {
+      *c.sh_abort = 1;
+      return false;
+    }
+    if (clock64() - t0 > SMC_SPIN_CYCLES) {
+      pf_raise(c, SMC_ERR_BARRIER_TIMEOUT);
+      return false;
+    }
+  }
+}
+
 // ---------------------------------------------------------------- phase list and work shares
 struct GemmDesc {
-  int N, K, n_slabs, kblocks, whole, wmap, xmap, epi;
+  int N, K, n_slabs, kblocks, split, wmap, xmap, epi;
 };
 
 __device__ __forceinline__ int pf_num_phases(const PfParams& p) { return 1 + 5 * p.L + (p.lm_rows > 0 ? 2 : 0); }
 
 __device__ __forceinline__ bool pf_gemm_desc(const PfParams& p, int ph, GemmDesc& g) {
   const int L5 = 5 * p.L;
+  bool lm = false;
   if (ph >= 1 && ph <= L5) {
     const int l = (ph - 1) / 5, j = (ph - 1) % 5;
     const int xbase = 4 * p.L + 1;
@@ -180,45 +233,79 @@ __device__ __forceinline__ bool pf_gemm_desc(const PfParams& p, int ph, GemmDesc
     else if (j == 3) { g.N = 2 * p.ffn; g.K = p.d; g.wmap = 4 * l + 2; g.xmap = xbase; g.epi = PF_EPI_SWIGLU; }
     else if (j == 4) { g.N = p.d; g.K = p.ffn; g.wmap = 4 * l + 3; g.xmap = xbase + 2; g.epi = PF_EPI_RESID; }
     else return false;
-    g.whole = 0;
   } else if (ph == L5 + 1 && p.lm_rows > 0) {
-    g.N = p.V; g.K = p.d; g.wmap = 4 * p.L; g.xmap = 4 * p.L + 4; g.epi = PF_EPI_LMHEAD; g.whole = 1;
+    g.N = p.V; g.K = p.d; g.wmap = 4 * p.L; g.xmap = 4 * p.L + 4; g.epi = PF_EPI_LMHEAD;
+    lm = true;
   } else {
     return false;
   }
   g.n_slabs = (g.N + 127) >> 7;
   g.kblocks = (g.K + 63) >> 6;
+  // few slabs and a reduction long enough to cut in eight: split along K inside the clusters; otherwise whole slabs
+  g.split = (!lm && g.kblocks >= PF_CLUSTER && g.n_slabs * 3 < (int)gridDim.x * 2) ? 1 : 0;
   return true;
 }
 
-// Share of CTA `cta` in the (slab-major, k-block-minor) iteration space of a GEMM phase.
-__device__ __forceinline__ void pf_cta_range(const GemmDesc& g, int cta, int ncta, int& w0, int& w1) {
-  if (g.whole) {
-    const long long s0 = (long long)g.n_slabs * cta / ncta, s1 = (long long)g.n_slabs * (cta + 1) / ncta;
-    w0 = (int)(s0 * g.kblocks);
-    w1 = (int)(s1 * g.kblocks);
+// Work units of a GEMM phase.  Split phases: slab (cluster + i * clusters), k-blocks cut evenly over the eight ranks.
+// Whole phases: consecutive slabs per CTA over the full reduction.
+__device__ __forceinline__ int pf_units(const GemmDesc& g, int cta, int ncta) {
+  if (g.split) {
+    const int cl = cta / PF_CLUSTER, ncl = ncta / PF_CLUSTER;
+    return cl < g.n_slabs ? (g.n_slabs - cl + ncl - 1) / ncl : 0;
+  }
+  const unsigned int ns = (unsigned int)g.n_slabs, un = (unsigned int)ncta;
+  return (int)(ns * (unsigned int)(cta + 1) / un) - (int)(ns * (unsigned int)cta / un);
+}
+__device__ __forceinline__ void pf_unit(const GemmDesc& g, int cta, int ncta, int i, int& slab, int& kb0, int& kb1) {
+  if (g.split) {
+    const int cl = cta / PF_CLUSTER, ncl = ncta / PF_CLUSTER, r = cta % PF_CLUSTER;
+    slab = cl + i * ncl;
+    kb0 = g.kblocks * r / PF_CLUSTER;
+    kb1 = g.kblocks * (r + 1) / PF_CLUSTER;
   } else {
-    const long long W = (long long)g.n_slabs * g.kblocks;
-    w0 = (int)(W * cta / ncta);
-    w1 = (int)(W * (cta + 1) / ncta);
+    slab = (int)((unsigned int)g.n_slabs * (unsigned int)cta / (unsigned int)ncta) + i;
+    kb0 = 0;
+    kb1 = g.kblocks;
   }
 }
 
 struct PfCursor {
-  int ph, w, w_end;
+  int ph, i, n, slab, kb, kb_end;
   GemmDesc g;
-  // position on the first unit of the first GEMM phase >= from_ph in which this CTA has work
+  // position on the first k-block of the first unit of the first GEMM phase >= from_ph in which this CTA has work
   __device__ __forceinline__ bool seek(const PfParams& p, int from_ph, int cta, int ncta, int n_phases) {
     for (ph = from_ph; ph < n_phases; ++ph) {
       if (!pf_gemm_desc(p, ph, g)) continue;
-      pf_cta_range(g, cta, ncta, w, w_end);
-      if (w < w_end) return true;
+      n = pf_units(g, cta, ncta);
+      if (n > 0) {
+        i = 0;
+        pf_unit(g, cta, ncta, 0, slab, kb, kb_end);
+        return true;
+      }
     }
     return false;
   }
+  // next k-block (of this unit, the next unit or the next phase); false at the end of the program
+  __device__ __forceinline__ bool step(const PfParams& p, int cta, int ncta, int n_phases) {
+    if (++kb < kb_end) return true;
+    if (++i < n) {
+      pf_unit(g, cta, ncta, i, slab, kb, kb_end);
+      return true;
+    }
+    return seek(p, ph + 1, cta, ncta, n_phases);
+  }
 };
 
-__device__ __forceinline__ void pf_arrive(const PfParams& p) {
+__device__ __forceinline__ long long pf_now_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void pf_stamp(const PfParams& p, int ph, int which) {
+  if (p.trace != nullptr) p.trace[((size_t)ph * gridDim.x + blockIdx.x) * 8 + which] = pf_now_ns();
+}
+__device__ __forceinline__ void pf_arrive(const PfParams& p, int ph) {
+  pf_stamp(p, ph, 1);
   __threadfence();
   atomicAdd(p.sync + PF_SYNC_BARRIER, 1u);
 }
@@ -239,33 +326,36 @@ __device__ void pf_producer(const PfParams& p, const PfCtx& ctx, PfShared& S, ui
   long long t_idle = clock64();
   while (xv) {
     bool progressed = false;
-    if (wv && (wuse == 0 || mbar_try_wait(&S.empty[wslot], (uint32_t)(wuse - 1) & 1u))) {
-      const int slab = W.w / W.g.kblocks, kb = W.w - slab * W.g.kblocks;
+    // weight tiles first: every free slot of the ring is refilled before the (slow) look at the phase counter
+    while (wv && (wuse == 0 || mbar_test_wait(&S.empty[wslot], (uint32_t)(wuse - 1) & 1u))) {
       mbar_expect_tx(&S.full[wslot], (uint32_t)stage_bytes);
-      tma_load_2d(ring + (size_t)wslot * stage_bytes, p.maps + W.g.wmap, &S.full[wslot], kb * 64, slab * 128, pol_w);
+      tma_load_2d(ring + (size_t)wslot * stage_bytes, p.maps + W.g.wmap, &S.full[wslot], W.kb * 64, W.slab * 128,
+                  pol_w);
       ++wi;
       S.issued = wi;
       if (++wslot == nst) { wslot = 0; ++wuse; }
-      if (++W.w == W.w_end) wv = W.seek(p, W.ph + 1, cta, ncta, n_phases);
+      wv = W.step(p, cta, ncta, n_phases);
       progressed = true;
     }
-    if (xi < wi) {
+    // activation tiles of every stage whose phase is open
+    while (xi < wi) {
       if ((unsigned int)X.ph > open_upto) {
-        const unsigned int done = ld_acquire_gpu_u32(p.sync + PF_SYNC_BARRIER) / (unsigned int)ncta;
+        // the epilogue leader of this CTA watches the phase counter and publishes what it saw: no global
+        // polling here, so refilling the ring is never held up by a round trip to L2
+        const unsigned int done = (unsigned int)S.open_upto;
         if (done > open_upto) {
+          __threadfence();
           open_upto = done;
           fence_proxy_async_all();       // activations were written with ordinary stores by other CTAs
         }
+        if ((unsigned int)X.ph > open_upto) break;
       }
-      if ((unsigned int)X.ph <= open_upto) {
-        const int slab = X.w / X.g.kblocks, kb = X.w - slab * X.g.kblocks;
-        tma_load_2d(ring + (size_t)xslot * stage_bytes + PF_A_BYTES, p.maps + X.g.xmap, &S.full[xslot], kb * 64, 0,
-                    pol_x);
-        ++xi;
-        if (++xslot == nst) xslot = 0;
-        if (++X.w == X.w_end) xv = X.seek(p, X.ph + 1, cta, ncta, n_phases);
-        progressed = true;
-      }
+      tma_load_2d(ring + (size_t)xslot * stage_bytes + PF_A_BYTES, p.maps + X.g.xmap, &S.full[xslot], X.kb * 64, 0,
+                  pol_x);
+      ++xi;
+      if (++xslot == nst) xslot = 0;
+      xv = X.step(p, cta, ncta, n_phases);
+      progressed = true;
     }
     if (progressed) {
       t_idle = clock64();
@@ -288,14 +378,12 @@ __device__ void pf_mma(const PfParams& p, const PfCtx& ctx, PfShared& S, uint8_t
   int slot = 0, unit = 0, consumed = 0;
   uint32_t fph = 0u;
   while (v) {
-    const int slab = C.w / C.g.kblocks;
-    const int seg_end = min(C.w_end, (slab + 1) * C.g.kblocks);
     const int a = unit & 1, use = unit >> 1;
     if (use >= 1 && !pf_mbar_wait(ctx, &S.acc_empty[a], (uint32_t)(use - 1) & 1u)) return;
     tc_fence_after();
     const uint32_t tacc = tmem_base + (uint32_t)a * 128u;
-    bool first = true;
-    for (; C.w < seg_end; ++C.w) {
+    const int nkb = C.kb_end - C.kb;
+    for (int j = 0; j < nkb; ++j) {
       if (!pf_mbar_wait(ctx, &S.full[slot], fph)) return;
       tc_fence_after();
       const uint32_t a_addr = smem_u32(ring + (size_t)slot * stage_bytes);
@@ -303,15 +391,15 @@ __device__ void pf_mma(const PfParams& p, const PfCtx& ctx, PfShared& S, uint8_t
       const uint64_t bdesc = umma_desc_k_sw128(a_addr + PF_A_BYTES);
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        umma_bf16_ss(tacc, adesc + 2 * k, bdesc + 2 * k, idesc, (first && k == 0) ? 0u : 1u);
-      first = false;
+        umma_bf16_ss(tacc, adesc + 2 * k, bdesc + 2 * k, idesc, (j == 0 && k == 0) ? 0u : 1u);
       umma_commit(&S.empty[slot]);
       S.consumed = ++consumed;
       if (++slot == nst) { slot = 0; fph ^= 1u; }
     }
     umma_commit(&S.acc_full[a]);
     ++unit;
-    if (C.w == C.w_end) v = C.seek(p, C.ph + 1, cta, ncta, n_phases);
+    C.kb = C.kb_end - 1;                 // on to the next unit
+    v = C.step(p, cta, ncta, n_phases);
   }
 }
 
@@ -442,14 +530,56 @@ __device__ __forceinline__ void pf_epi_chunk(const PfParams& p, const GemmDesc& 
   }
 }
 
-// Epilogue of one GEMM phase for warps 4..7 (t = 0..127).
+// One token column m of a slab after the cluster reduction; `v` is this thread's row (t = 0..127 of the slab).
+// All 128 epilogue threads call this together (it contains group barriers for two of the epilogues).
+__device__ __forceinline__ void pf_epi_col(const PfParams& p, const GemmDesc& g, PfShared& S, int slab, int m, float v,
+                                           int t, int parity, int u) {
+  const int warp_e = t >> 5, lane = t & 31;
+  const int n = slab * 128 + t;
+  if (g.epi == PF_EPI_QKV) {
+    if (n < g.N) p.qkv[(size_t)m * p.nqkv + n] = v * S.rstd[m];
+  } else if (g.epi == PF_EPI_RESID) {
+    float hv = 0.f;
+    if (n < g.N) {
+      hv = __ldcg(p.h + (size_t)m * p.d + n) + v;
+      p.h[(size_t)m * p.d + n] = hv;
+      p.hb[(size_t)m * p.d + n] = __float2bfloat16(hv);
+    }
+    const float sq = warp_sum(hv * hv);
+    if (lane == 0) S.ssq[parity][warp_e][u] = sq;
+  } else {
+    // gate/up cut along K: rows 64..127 hand their sums to the gate rows 0..63
+    if (t >= 64) S.xcol[parity][u][t - 64] = v;
+  }
+}
+// second half of pf_epi_col for the epilogues that exchange through shared memory (after a group barrier)
+__device__ __forceinline__ void pf_epi_col_finish(const PfParams& p, const GemmDesc& g, PfShared& S, int slab, int m,
+                                                  float v, int t, int parity, int u) {
+  if (g.epi == PF_EPI_RESID) {
+    if (t == u)
+      p.ssq[(size_t)slab * p.ssq_ld + m] =
+          S.ssq[parity][0][u] + S.ssq[parity][1][u] + S.ssq[parity][2][u] + S.ssq[parity][3][u];
+  } else if (g.epi == PF_EPI_SWIGLU) {
+    const int ch = slab * 64 + t;
+    if (t < 64 && ch * 2 < g.N) {
+      const float r = S.rstd[m];
+      const float gt = v * r, up = S.xcol[parity][u][t] * r;
+      p.act[(size_t)m * p.ffn + ch] = __float2bfloat16(gt / (1.0f + __expf(-gt)) * up);
+    }
+  }
+}
+
+// Epilogue of one GEMM phase for warps 4..7 (t = 0..127).  `red_use` counts the cluster reductions this CTA has taken
+// part in (all CTAs of a cluster walk the same units, so the counts agree); `red_pending` is set while peers may
+// still be reading this CTA's parked tile.
 __device__ void pf_gemm_epilogue(const PfParams& p, const PfCtx& ctx, PfShared& S, float* scratch, uint32_t tmem_base,
-                                 const GemmDesc& g, int ph, int cta, int ncta, int t, int& unit) {
+                                 const GemmDesc& g, int ph, int cta, int ncta, int t, int& unit, int& red_use,
+                                 int& red_pending) {
   const int warp_e = t >> 5, lane = t & 31;
   // the inputs of this phase (sums of squares for the folded norm) are ready once every CTA has left the phase before
   if (t == 0) {
-    pf_wait_counter(ctx, p.sync + PF_SYNC_BARRIER, (unsigned int)ph * (unsigned int)ncta);
-    __threadfence();
+    pf_leader_wait(p, ctx, &S.open_upto, ph, ncta);
+    pf_stamp(p, ph, 0);
   }
   bar_epi();
   const int cols = g.epi == PF_EPI_LMHEAD ? p.lm_rows : p.M;
@@ -465,20 +595,19 @@ __device__ void pf_gemm_epilogue(const PfParams& p, const PfCtx& ctx, PfShared& 
     if (g.epi == PF_EPI_LMHEAD) S.rp[t] = RowPartial{-INFINITY, 0.f, -INFINITY, 0.f, -INFINITY, 0.f, 0, __float_as_int(-INFINITY)};
     bar_epi();
   }
-  int w0, w1;
-  pf_cta_range(g, cta, ncta, w0, w1);
+  const int n_units = pf_units(g, cta, ncta);
   const uint32_t lane_off = ((uint32_t)(warp_e * 32)) << 16;
+  const uint32_t rank = (uint32_t)(cta % PF_CLUSTER);
   int parity = 0;
-  for (int w = w0; w < w1;) {
-    const int slab = w / g.kblocks;
-    const int x0 = slab * g.kblocks;
-    const int seg_end = min(w1, x0 + g.kblocks);
-    const bool whole_slab = (w == x0) && (seg_end == x0 + g.kblocks);
+  for (int i = 0; i < n_units; ++i) {
+    int slab, kb0, kb1;
+    pf_unit(g, cta, ncta, i, slab, kb0, kb1);
     const int a = unit & 1, use = unit >> 1;
     pf_mbar_wait(ctx, &S.acc_full[a], (uint32_t)use & 1u);
+    if (t == 0 && i == 0) pf_stamp(p, ph, 2);
     tc_fence_after();
     const uint32_t taddr = tmem_base + (uint32_t)a * 128u + lane_off;
-    if (whole_slab) {
+    if (!g.split) {
       for (int c0 = 0; c0 < cols; c0 += 16) {
         uint32_t r[16];
         float v[16];
@@ -495,70 +624,82 @@ __device__ void pf_gemm_epilogue(const PfParams& p, const PfCtx& ctx, PfShared& 
         parity ^= 1;
       }
     } else {
-      // park the partial tile, then the last contributor of the slab reduces all of them in CTA order
-      const int slot = (w == w0) ? 0 : 1;
-      float* part = p.partials + ((size_t)(cta * 2 + slot) * p.BN) * 128;
+      // ---- cluster reduction: park this CTA's tile, wait for all eight, sum this rank's columns ------------
+      float* park = scratch;             // [cols][128] fp32
+      if (red_pending) {                 // peers may still be reading the tile parked for the previous unit
+        pf_mbar_wait_cluster(ctx, &S.red_done, (uint32_t)(red_use - 1) & 1u);
+        red_pending = 0;
+      }
       for (int c0 = 0; c0 < cols; c0 += 16) {
         uint32_t r[16];
         tmem_ld_32x32b_x16(taddr + c0, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (c0 + j < cols) __stcg(part + (size_t)(c0 + j) * 128 + t, __uint_as_float(r[j]));
+        for (int j = 0; j < 16; ++j) park[(c0 + j) * 128 + t] = __uint_as_float(r[j]);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.acc_empty[a]);
-      // contributors of this slab: the CTAs whose shares intersect its k-blocks
-      const long long W = (long long)g.n_slabs * g.kblocks;
-      const long long x1 = (long long)x0 + g.kblocks;           // one past the slab's last work index
-      const int c_lo = (int)((((long long)x0 + 1) * ncta - 1) / W), c_hi = (int)((x1 * ncta - 1) / W);
       bar_epi();
-      if (t == 0) {
-        int n_contrib = 0;
-        for (int c = c_lo; c <= c_hi; ++c) {
-          const long long s_c = W * c / ncta, e_c = W * (c + 1) / ncta;
-          if ((s_c > x0 ? s_c : x0) < (e_c < x1 ? e_c : x1)) ++n_contrib;
+      if (t < PF_CLUSTER) mbar_arrive_remote(&S.red_full, (uint32_t)t);
+      if (t == 0) pf_stamp(p, ph, 3);
+      pf_mbar_wait_cluster(ctx, &S.red_full, (uint32_t)red_use & 1u);
+      if (t == 0) pf_stamp(p, ph, 4);
+      uint32_t rbase[PF_CLUSTER];
+#pragma unroll
+      for (uint32_t q = 0; q < PF_CLUSTER; ++q) rbase[q] = dsmem_map(smem_u32(park) + (uint32_t)t * 4u, q);
+      constexpr int UN = 4;
+      for (int cb = (int)rank; cb < cols; cb += PF_CLUSTER * UN) {
+        float x[UN][PF_CLUSTER];
+        // all remote loads of a batch of columns are issued before the first add
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int c = cb + u * PF_CLUSTER;
+#pragma unroll
+          for (uint32_t q = 0; q < PF_CLUSTER; ++q)
+            x[u][q] = c < cols ? ld_dsmem_f32_at(rbase[q] + (uint32_t)c * 512u) : 0.f;
         }
-        __threadfence();
-        const int old = atomicAdd(p.slab_ctr + slab, 1);
-        const int last = old == n_contrib - 1;
-        if (last) {
-          p.slab_ctr[slab] = 0;
-          __threadfence();
+        float v[UN];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          float acc = 0.f;
+#pragma unroll
+          for (uint32_t q = 0; q < PF_CLUSTER; ++q) acc += x[u][q];
+          v[u] = acc;
         }
-        S.flag = last;
-      }
-      bar_epi();
-      if (S.flag) {
-        for (int c0 = 0; c0 < cols; c0 += 16) {
-          float v[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0.f;
-          for (int c = c_lo; c <= c_hi; ++c) {
-            const long long s_c = W * c / ncta, e_c = W * (c + 1) / ncta;
-            if ((s_c > x0 ? s_c : x0) >= (e_c < x1 ? e_c : x1)) continue;
-            const float* src = p.partials + ((size_t)(c * 2 + (s_c >= x0 ? 0 : 1)) * p.BN) * 128;
-            float x[16];
+        for (int u = 0; u < UN; ++u) {
+          const int c = cb + u * PF_CLUSTER;
+          if (c < cols) pf_epi_col(p, g, S, slab, c, v[u], t, parity, u);
+        }
+        if (g.epi != PF_EPI_QKV) {
+          bar_epi();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) x[j] = (c0 + j < cols) ? __ldcg(src + (size_t)(c0 + j) * 128 + t) : 0.f;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] += x[j];
+          for (int u = 0; u < UN; ++u) {
+            const int c = cb + u * PF_CLUSTER;
+            if (c < cols) pf_epi_col_finish(p, g, S, slab, c, v[u], t, parity, u);
           }
-          pf_epi_chunk(p, g, S, scratch, slab, c0, v, t, parity);
           parity ^= 1;
         }
       }
+      if (t == 0) pf_stamp(p, ph, 5);
+      bar_epi();                         // every thread of this CTA has finished its remote reads
+      if (t < PF_CLUSTER) mbar_arrive_remote(&S.red_done, (uint32_t)t);
+      ++red_use;
+      red_pending = 1;
     }
-    w = seg_end;
     ++unit;
+  }
+  if (red_pending) {                     // the staging region is reused by the next phase
+    pf_mbar_wait_cluster(ctx, &S.red_done, (uint32_t)(red_use - 1) & 1u);
+    red_pending = 0;
   }
   if (g.epi == PF_EPI_LMHEAD) {
     bar_epi();
     if (t < p.lm_rows) p.sparts[(size_t)t * ncta + cta] = S.rp[t];
   }
   bar_epi();
-  if (t == 0) pf_arrive(p);
+  if (t == 0) pf_arrive(p, ph);
 }
 
 // Last phase: merge the per-CTA partials of every sampled / scored row.
@@ -949,7 +1090,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_forward_kernel(const PfParam
       mbar_init(&S.acc_full[a], 1);
       mbar_init(&S.acc_empty[a], 4);
     }
+    mbar_init(&S.red_full, PF_CLUSTER);
+    mbar_init(&S.red_done, PF_CLUSTER);
     S.abort = 0;
+    S.open_upto = 0;
     S.issued = 0;
     S.consumed = 0;
     S.flag = 0;
@@ -962,6 +1106,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_forward_kernel(const PfParam
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  cluster_sync();                        // every CTA of the cluster has initialised the barriers its peers arrive on
   const uint32_t tmem_base = S.tmem_slot;
   const int n_phases = pf_num_phases(p);
 
@@ -975,32 +1120,34 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_forward_kernel(const PfParam
     const int ta = (int)threadIdx.x - 64;          // attention-group thread (warps 2..7)
     const int t = (int)threadIdx.x - 128;          // epilogue-group thread (warps 4..7); negative for warps 2, 3
     float* scratch = reinterpret_cast<float*>(att_smem);
-    int unit = 0;
+    int unit = 0, red_use = 0, red_pending = 0;
     for (int ph = 0; ph < n_phases; ++ph) {
       GemmDesc g;
       if (ph == 0) {
+        if (t == 0) pf_stamp(p, ph, 0);
         pf_embed_phase(p, cta, ncta, ta);
         bar_att();
-        if (t == 0) pf_arrive(p);
+        if (t == 0) pf_arrive(p, ph);
       } else if (pf_gemm_desc(p, ph, g)) {
-        if (t >= 0) pf_gemm_epilogue(p, ctx, S, scratch, tmem_base, g, ph, cta, ncta, t, unit);
+        if (t >= 0) pf_gemm_epilogue(p, ctx, S, scratch, tmem_base, g, ph, cta, ncta, t, unit, red_use, red_pending);
       } else if (ph <= 5 * p.L) {
         if (t == 0) {
-          pf_wait_counter(ctx, p.sync + PF_SYNC_BARRIER, (unsigned int)ph * (unsigned int)ncta);
-          __threadfence();
+          pf_leader_wait(p, ctx, &S.open_upto, ph, ncta);
+          pf_stamp(p, ph, 0);
         }
         bar_att();
         pf_attention_phase<D>(p, ctx, S, att_smem, (ph - 1) / 5, cta, ncta, ta);
         bar_att();
-        if (t == 0) pf_arrive(p);
+        if (t == 0) pf_arrive(p, ph);
       } else {
         if (t >= 0) {
           if (t == 0) {
-            pf_wait_counter(ctx, p.sync + PF_SYNC_BARRIER, (unsigned int)ph * (unsigned int)ncta);
-            __threadfence();
+            pf_leader_wait(p, ctx, &S.open_upto, ph, ncta);
+            pf_stamp(p, ph, 0);
           }
           bar_epi();
           pf_sample_merge(p, cta, ncta, t);
+          if (t == 0) pf_stamp(p, ph, 1);
         }
       }
     }
@@ -1008,6 +1155,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) pf_forward_kernel(const PfParam
 
   tc_fence_before();
   __syncthreads();
+  cluster_sync();                        // no CTA leaves while a peer could still touch its shared memory
   if (warp == 1) tmem_dealloc(tmem_base, PF_TMEM_COLS);
   if (threadIdx.x == 0) {
     if (S.abort) {
@@ -1040,12 +1188,42 @@ static size_t pf_att_bytes(int D, int n_mt, int n_kw, int stg) {
 
 SMC_API int smc_pf_params_size() { return (int)sizeof(smc::PfParams); }
 
-SMC_API int smc_pf_num_ctas() {
-  int dev = 0, n = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
-  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
-  return n;
+namespace smc {
+static void (*pf_kernel_for(int D))(const PfParams) {
+  if (D == 64) return pf_forward_kernel<64>;
+  if (D == 128) return pf_forward_kernel<128>;
+  return nullptr;
 }
+static const int PF_DYN_SMEM_MAX = 232448 - (int)sizeof(PfShared) - 512;
+
+// Grid of the persistent kernel: as many clusters of eight CTAs (one CTA per SM) as the device can hold at once.
+static int pf_grid(int D) {
+  static int cached[2] = {0, 0};
+  const int ki = D == 64 ? 0 : 1;
+  if (cached[ki] > 0) return cached[ki];
+  auto kern = pf_kernel_for(D);
+  if (!kern) return -101;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_DYN_SMEM_MAX) != cudaSuccess) return -108;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(PF_CLUSTER);
+  cfg.blockDim = dim3(PF_THREADS);
+  cfg.dynamicSmemBytes = (size_t)PF_DYN_SMEM_MAX;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PF_CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) return -109;
+  cached[ki] = n * PF_CLUSTER;
+  return cached[ki];
+}
+}  // namespace smc
+
+// CTAs the persistent kernel is launched with for head size D (a multiple of the cluster size).
+SMC_API int smc_pf_num_ctas(int D) { return smc::pf_grid(D); }
 
 // Writes one 128-byte tensor map for a bf16 matrix [rows, cols] of pitch ld (elements) with a [box_rows, 64] box
 // into host memory at dst (the caller copies the table to the device).
@@ -1073,9 +1251,11 @@ SMC_API int smc_pf_plan(int D, int E, int G, int BN, int* n_mt, int* n_kw, int* 
   int stg = 2;
   while (stg < 4 && pf_att_bytes(D, mt, kw, stg + 1) <= 72 * 1024) ++stg;
   while (kw > 1 && pf_att_bytes(D, mt, kw, stg) > 96 * 1024) --kw;
-  const int att = (int)((pf_att_bytes(D, mt, kw, stg) + 1023) / 1024 * 1024);
+  size_t att_raw = pf_att_bytes(D, mt, kw, stg);
+  if (att_raw < (size_t)BN * 512) att_raw = (size_t)BN * 512;      // the cluster reduction parks a [BN][128] fp32 tile there
+  const int att = (int)((att_raw + 1023) / 1024 * 1024);
   const int stage_bytes = PF_A_BYTES + BN * 128;
-  const int budget = 232448 - (int)sizeof(PfShared) - 512 - 1024 - att;
+  const int budget = PF_DYN_SMEM_MAX - 1024 - att;
   int st = budget / stage_bytes;
   if (st > PF_MAX_STAGES) st = PF_MAX_STAGES;
   if (st < 3) return -105;
@@ -1083,36 +1263,34 @@ SMC_API int smc_pf_plan(int D, int E, int G, int BN, int* n_mt, int* n_kw, int* 
   return 0;
 }
 
-// Launches one forward.  `coop` selects a cooperative launch (all CTAs guaranteed co-resident); without it the grid
-// is one CTA per SM and relies on the stream being otherwise idle.
+// Launches one forward on a grid of clusters of eight CTAs, one CTA per SM.  `coop` adds the cooperative-launch
+// attribute (all CTAs guaranteed co-resident); without it co-residency relies on the stream being otherwise idle,
+// and every wait in the kernel is bounded either way.
 SMC_API int smc_pf_forward(const smc::PfParams* p, int coop, cudaStream_t st) {
   using namespace smc;
-  void (*kern)(const PfParams) = nullptr;
-  if (p->D == 64) kern = pf_forward_kernel<64>;
-  else if (p->D == 128) kern = pf_forward_kernel<128>;
-  else return -101;
+  auto kern = pf_kernel_for(p->D);
+  if (!kern) return -101;
   if (p->M < 1 || p->M > p->BN || p->lm_rows > p->BN || (p->d % 128) != 0 || p->stages < 3 ||
       p->stages > PF_MAX_STAGES || p->Hq % p->Hkv || (p->rd & 7) || p->rd > p->D || ((p->D - p->rd) & 3))
     return -106;
   const int smem = p->ring_bytes + p->att_bytes + 1024;
-  static int configured[2] = {0, 0};
-  const int ki = p->D == 64 ? 0 : 1;
-  if (configured[ki] < smem) {
-    CUDA_CHECK_RET(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured[ki] = smem;
-  }
-  const int ncta = smc_pf_num_ctas();
-  if (ncta <= 0) return -107;
+  if (smem > PF_DYN_SMEM_MAX || p->att_bytes < p->BN * 512) return -110;
+  const int ncta = pf_grid(p->D);
+  if (ncta <= 0) return ncta < 0 ? ncta : -107;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)ncta);
   cfg.blockDim = dim3(PF_THREADS);
   cfg.dynamicSmemBytes = (size_t)smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;
-  attr[0].val.cooperative = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PF_CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeCooperative;
+  attr[1].val.cooperative = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = coop ? 1 : 0;
+  cfg.numAttrs = coop ? 2 : 1;
   CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, kern, *p));
   return 0;
 }

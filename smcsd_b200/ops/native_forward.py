@@ -2,8 +2,10 @@
 
 One launch runs embedding, every decoder layer (QKV GEMM, attention over the paged KV cache, o-proj, gate/up with
 SwiGLU, down) and the lm_head fused with Gumbel sampling / token scoring, for batches of up to 128 token rows.
-The weight stream runs ahead of the activations across phase boundaries, which is what the one-kernel-per-GEMM chain
-cannot do; a decode cycle shrinks from several hundred dependent launches to about a dozen.
+The weight stream runs ahead of the activations across phase boundaries and a decode cycle shrinks from several
+hundred dependent launches to about a dozen.  Measured on B200 the per-phase cost (grid barrier, activation fetch,
+K-split reduction inside clusters of eight) is still higher than that of the stand-alone GEMM kernels, which choose a
+cluster size per matrix, so the runner uses this path only when ``SMC_PERSISTENT=1`` is set.
 
 The reference runs each of these steps as separate library / Triton launches inside a CUDA graph
 (smcsd/model_executor/smc_draft_phase_graph_runner.py:1043-1082 for the draft loop, :666-719 for verify + scoring).
@@ -31,10 +33,10 @@ class PfParams(C.Structure):
         + [(n, C.c_void_p) for n in ("ids", "positions", "cache_locs", "rows", "prefix_lens", "h", "hb", "ssq", "qkv",
                                      "attn", "act")]
         + [("ssq_ld", C.c_int), ("pad1", C.c_int)]
-        + [(n, C.c_void_p) for n in ("partials", "slab_ctr", "att_part", "att_ctr")]
+        + [(n, C.c_void_p) for n in ("att_part", "att_ctr")]
         + [("inv_temp", C.c_float), ("alpha", C.c_float), ("tokens_in", C.c_void_p), ("seed", C.c_ulonglong),
            ("cycle_counter", C.c_void_p), ("call_id", C.c_int), ("pad2", C.c_int)]
-        + [(n, C.c_void_p) for n in ("sparts", "tok_out", "logp_out", "logz_out", "sync", "status")]
+        + [(n, C.c_void_p) for n in ("sparts", "tok_out", "logp_out", "logz_out", "sync", "status", "trace")]
     )
 
 
@@ -47,6 +49,7 @@ def _lib():
     if not _declared:
         vp, i, ll = C.c_void_p, C.c_int, C.c_longlong
         L.smc_pf_params_size.restype = C.c_int
+        L.smc_pf_num_ctas.argtypes = [i]
         L.smc_pf_num_ctas.restype = C.c_int
         L.smc_pf_encode_map.argtypes = [vp, vp, ll, ll, ll, i]
         L.smc_pf_encode_map.restype = C.c_int
@@ -86,9 +89,9 @@ class PersistentLlama:
         self.nqkv = (self.nq + 2 * self.nkv) * self.D
         self.V = model.lm_head.shape[0]
         self.nl = len(model.layers)
-        self.ncta = L.smc_pf_num_ctas()
+        self.ncta = L.smc_pf_num_ctas(self.D)
         if self.ncta <= 0:
-            raise K.NativeError("cannot query the number of SMs")
+            raise K.NativeError(f"cannot size the persistent grid (code {self.ncta})")
         f32, bf16, i32 = torch.float32, torch.bfloat16, torch.int32
         T = self.T
         self.h = torch.zeros(T, self.d, dtype=f32, device=dev)
@@ -98,15 +101,13 @@ class PersistentLlama:
         self.qkv = torch.zeros(T, self.nqkv, dtype=f32, device=dev)
         self.attn = torch.zeros(T, self.nq * self.D, dtype=bf16, device=dev)
         self.act = torch.zeros(T, self.ffn, dtype=bf16, device=dev)
-        self.partials = torch.zeros(self.ncta * 2 * 128 * 128, dtype=f32, device=dev)
-        max_slabs = max((self.V + 127) // 128, (2 * self.ffn + 127) // 128, (self.nqkv + 127) // 128)
-        self.slab_ctr = torch.zeros(max_slabs, dtype=i32, device=dev)
         self.att_ctr = torch.zeros(max(1, T * self.nkv), dtype=i32, device=dev)
         self.att_part = torch.zeros(1, dtype=f32, device=dev)
         self.sparts = torch.zeros(128 * self.ncta * 8, dtype=f32, device=dev)
         self.sync = torch.zeros(4, dtype=torch.int32, device=dev)
         self.coop = os.environ.get("SMC_PF_COOP", "1") not in ("0", "false", "off")
         self.ctx_hint = 0
+        self.trace: Optional[torch.Tensor] = None       # int64 [phases, ctas, 2] when a phase timeline is wanted
         self._tables: Dict[Tuple, torch.Tensor] = {}
         self._plans: Dict[Tuple, Tuple] = {}
 
@@ -200,7 +201,6 @@ class PersistentLlama:
         p.rows, p.prefix_lens = rows.data_ptr(), prefix_lens.data_ptr()
         p.h, p.hb, p.ssq, p.qkv = self.h.data_ptr(), self.hb.data_ptr(), self.ssq.data_ptr(), self.qkv.data_ptr()
         p.attn, p.act, p.ssq_ld = self.attn.data_ptr(), self.act.data_ptr(), self.ssq_ld
-        p.partials, p.slab_ctr = self.partials.data_ptr(), self.slab_ctr.data_ptr()
         p.att_part, p.att_ctr = self.att_part.data_ptr(), self.att_ctr.data_ptr()
         p.inv_temp, p.alpha = 1.0 / float(temperature), float(alpha)
         p.tokens_in = None if tokens_in is None else tokens_in.data_ptr()
@@ -212,12 +212,20 @@ class PersistentLlama:
         p.logp_out = None if logp_out is None else logp_out.data_ptr()
         p.logz_out = None if logz_out is None else logz_out.data_ptr()
         p.sync, p.status = self.sync.data_ptr(), self.status.data_ptr()
+        p.trace = None if self.trace is None else self.trace.data_ptr()
         if lm_rows > 0 and (cycle_counter is None or tok_out is None or logp_out is None):
             raise ValueError("sampling outputs and the cycle counter are required when lm_rows > 0")
         K._check(_lib().smc_pf_forward(C.byref(p), int(self.coop), K._stream()), "smc_pf_forward")
 
+    def n_phases(self, lm_rows: int) -> int:
+        return 1 + 5 * self.nl + (2 if lm_rows > 0 else 0)
+
+    def enable_trace(self) -> torch.Tensor:
+        """Allocate the phase-timeline buffer: per (phase, CTA) eight nanosecond stamps (0: inputs seen ready, 1: work done, 2..: details of the GEMM epilogue)."""
+        self.trace = torch.zeros(self.n_phases(1), self.ncta, 8, dtype=torch.int64, device=self.dev)
+        return self.trace
+
     def reset_sync(self) -> None:
         """Rearm the barrier counters after a launch that reported an error."""
         self.sync.zero_()
-        self.slab_ctr.zero_()
         self.att_ctr.zero_()

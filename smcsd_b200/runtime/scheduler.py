@@ -205,8 +205,10 @@ class SMCScheduler:
         comm_local = heap.view(comm_off, (nbytes,), torch.uint8)
         ns = self.native_state
         ns.bind(st)
-        for nm in (self.native_runner.target, self.native_runner.draft):
-            nm.bt = self.bt.table                      # the block table now lives in the symmetric heap
+        for nm in (self.native_runner.target, self.native_runner.draft, self.native_runner.pf_target,
+                   self.native_runner.pf_draft):
+            if nm is not None:
+                nm.bt = self.bt.table                  # the block table now lives in the symmetric heap
         drv = ppm.ParticleParallel(st, ns, kvs, self.pp_rank, self.pp_size,
                                    lambda q, t: heap.ptrs[q] + offsets[t.data_ptr()],
                                    [p + comm_off for p in heap.ptrs], comm_local, self.native_runner.status)

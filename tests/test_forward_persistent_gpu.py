@@ -144,3 +144,22 @@ def test_persistent_head_rows_and_no_sampling_pass():
     torch.cuda.synchronize()
     assert s.native_runner.check_status() == 0
     assert pf.sync[:3].tolist() == [0, 0, 0]
+
+
+def test_engine_runs_on_the_persistent_path(monkeypatch):
+    """The decode cycle with SMC_PERSISTENT=1: a dozen launches per cycle, clean status, conserved pages."""
+    monkeypatch.setenv("SMC_PERSISTENT", "1")
+    from smcsd_b200 import SMCEngine
+    eng = SMCEngine(_cfg("wide"), _cfg("narrow"), n_particles=4, gamma=4, draft_temperature=0.7, target_temperature=0.7,
+                    max_running_requests=2, context_length=1024, device="cuda", max_total_tokens=16384, random_seed=3,
+                    backend="native", cycle_graph=True)
+    r = eng._sched.native_runner
+    assert r.pf_target is not None and r.pf_draft is not None
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 8192, (40,), generator=g).tolist() for _ in range(2)]
+    outs = eng.generate(input_ids=prompts, sampling_params={"max_new_tokens": 40, "ignore_eos": True})
+    assert [o["completion_tokens"] for o in outs] == [40, 40]
+    assert r.check_status() == 0
+    assert 0 < r.launches_per_cycle <= 40
+    eng._sched.check_idle_invariants()
+    eng._sched.alloc.check_conservation()
