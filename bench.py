@@ -190,7 +190,6 @@ def main() -> int:
         lens3 = lognormal_lengths(max(2, args.e2e_requests), seed=3000 + rank)
         config2 = _e2e(eng, sched, lens3, 512, vocab, rank, world, dist, torch, seed=177)
         config2["shape"] = "log-normal prompt lengths (median 200, sigma 1, clipped 4..2048), 512 new tokens"
-        config2["vs_published_567_gsm8k_shape"] = None
     status |= sched.native_runner.check_status() if sched.native_runner else 0
 
     # ---- fused collective paths (two or more GPUs) ----------------------------------------------------

@@ -4,7 +4,7 @@
         --data /path/to/gsm8k_test.jsonl --num-questions 200 -N 8 -g 8
 
 Reports accuracy, invalid-answer rate and output tok/s (the reference's scripts/accuracy_test_gsm8k.py:101-174,
-242-294).  The dataset is a local JSONL with ``question`` / ``answer`` fields; nothing is downloaded.
+242-294); ``--mode baseline`` runs plain sampling from the target model instead of SMC.  The dataset is a local JSONL with ``question`` / ``answer`` fields; nothing is downloaded.
 """
 from __future__ import annotations
 
@@ -77,9 +77,12 @@ def main(argv=None) -> None:
     p.add_argument("--num-questions", type=int, default=200)
     p.add_argument("--max-new-tokens", type=int, default=512)
     p.add_argument("--min-accuracy", type=float, default=None)
+    p.add_argument("--mode", default="smc_engine", choices=["smc_engine", "baseline"],
+                   help="baseline: plain sampling from the target model at --temperature (vanilla arm)")
+    p.add_argument("--temperature", type=float, default=0.7, help="sampling temperature of the baseline arm")
     ns = p.parse_args(argv)
-    from ..http_server import build_engine_from_args
-    eng = build_engine_from_args(ns)
+    from ..http_server import build_baseline_engine_from_args, build_engine_from_args
+    eng = build_engine_from_args(ns) if ns.mode == "smc_engine" else build_baseline_engine_from_args(ns, ns.temperature)
     qs = load_questions(ns.data, ns.num_questions)
     prompts = [build_prompt(eng.tokenizer, q["question"]) for q in qs]
     golds = [gold_answer(q["answer"]) for q in qs]
@@ -88,7 +91,7 @@ def main(argv=None) -> None:
     dt = time.perf_counter() - t0
     acc, inv = score([o["text"] for o in outs], golds)
     toks = sum(o["completion_tokens"] for o in outs)
-    print(json.dumps({"accuracy": acc, "invalid": inv, "num_questions": len(qs), "output_tok_per_s": toks / dt,
+    print(json.dumps({"mode": ns.mode, "accuracy": acc, "invalid": inv, "num_questions": len(qs), "output_tok_per_s": toks / dt,
                       "latency_s": dt}))
     eng.shutdown()
     if ns.min_accuracy is not None and acc < ns.min_accuracy:

@@ -11,7 +11,8 @@ request / input / output / total throughput with the ``Output token throughput (
 scripts parse, and appends a JSON line to ``--result-file``.  Timing is wall clock around the whole
 ``generate`` call (tokenization and prefill included), like the reference harness
 (scripts/tps_benchmark_scripts/bench_offline_throughput.py:332-337,390-440); the device-timed number is
-``bench.py`` at the repository root.
+``bench.py`` at the repository root.  ``--backend-name engine`` runs the vanilla arm (plain target sampling at
+``--temperature`` through the same kernels) for side-by-side numbers.
 """
 from __future__ import annotations
 
@@ -58,7 +59,9 @@ def build_prompts(ns, vocab: int) -> List[List[int]]:
 def main(argv=None) -> None:
     p = argparse.ArgumentParser("offline_throughput")
     EngineArgs.add_cli_args(p)
-    p.add_argument("--backend-name", default="smc_engine", choices=["smc_engine"])
+    p.add_argument("--backend-name", "--bench-backend", dest="backend_name", default="smc_engine",
+                   choices=["smc_engine", "engine"],
+                   help="smc_engine: SMC speculative decoding; engine: plain sampling from the target (vanilla arm)")
     p.add_argument("--dataset-name", default="random",
                    choices=["random", "lognormal", "generated-shared-prefix", "file"])
     p.add_argument("--dataset-path", default=None)
@@ -74,8 +77,9 @@ def main(argv=None) -> None:
     p.add_argument("--result-file", default=None)
     p.add_argument("--temperature", type=float, default=0.7, help="accepted for parity; SMC uses the engine temperatures")
     ns = p.parse_args(argv)
-    from ..http_server import build_engine_from_args
-    eng = build_engine_from_args(ns)
+    from ..http_server import build_baseline_engine_from_args, build_engine_from_args
+    eng = build_engine_from_args(ns) if ns.backend_name == "smc_engine" else \
+        build_baseline_engine_from_args(ns, ns.temperature)
     vocab = eng._sched.target.cfg.vocab_size if eng._sched is not None else 32000
     prompts = build_prompts(ns, vocab)
     sp = {"max_new_tokens": ns.random_output_len, "ignore_eos": True, "temperature": ns.temperature}

@@ -75,7 +75,7 @@ def run(steps: int = 20, warmup: int = 5, particles_per_rank: int = 2, gamma: in
     dist.barrier()
     res = {"bench": "pp_cycle", "ranks": world, "n_particles": particles_per_rank * world, "gamma": gamma,
            "model": f"{tgt.name}+{drf.name}", "target_layers": tgt.n_layers, "pp_cycle_ms": float(tmax[0].item()),
-           "tokens_per_s": particles_per_rank * world * 0 + G / (float(tmax[0].item()) / 1e3),
+           "tokens_per_s": G / (float(tmax[0].item()) / 1e3),
            "remote_copies_last_cycle": int(tsum[1].item()),
            "pp_nvlink_bytes_per_cycle": int(tsum[1].item()) * suffix * row_bytes,
            "status": int(tmax[2].item()), "timing": "CUDA events around the decode cycles, max over ranks"}

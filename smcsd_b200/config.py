@@ -81,8 +81,7 @@ class EngineArgs:
     quantization: Optional[str] = None
     disable_cuda_graph: bool = False
     cuda_graph_max_bs: Optional[int] = None
-    attention_num_kv_splits: int = 16
-    stream_interval: int = 50
+    attention_num_kv_splits: int = 16   # upper bound of the key-range splits the attention planner may choose
     log_level: str = "error"
     # ---- parallelism --------------------------------------------------------
     tp_size: int = 1                    # tensor-parallel ranks for the target

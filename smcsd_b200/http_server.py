@@ -277,6 +277,25 @@ def build_engine_from_args(ns: argparse.Namespace):
     return SMCEngine(model, draft, **kw)
 
 
+def build_baseline_engine_from_args(ns: argparse.Namespace, temperature: float = 1.0):
+    """Vanilla arm of the harnesses: plain sampling from the target model through the same kernels and scheduler.
+    It is the engine with one particle, gamma = 1 and the target as its own proposal at the same temperature: every
+    proposed token is then an exact draw from the target distribution, the importance weights stay constant and
+    nothing is ever resampled, so the output law is that of ordinary autoregressive sampling at about one weight
+    pass per generated token (the reference's ``--backend engine`` / ``--mode baseline`` arms:
+    scripts/tps_benchmark_scripts/bench_offline_throughput.py:144-171, scripts/accuracy_test_gsm8k.py:177)."""
+    from .engine import SMCEngine
+    a = EngineArgs.from_cli_args(ns)
+    kw = a.to_dict()
+    model = a.model_path
+    for k in ("model_path", "draft_model_path", "extra"):
+        kw.pop(k, None)
+    t = max(float(temperature), 1e-5)
+    kw.update(n_particles=1, gamma=1, draft_temperature=t, target_temperature=t, power_alpha=1.0,
+              resample_threshold=0.0)
+    return SMCEngine(model, model, **kw)
+
+
 def launch_server(ns: argparse.Namespace) -> None:
     import uvicorn
     engine = build_engine_from_args(ns)

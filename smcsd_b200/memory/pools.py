@@ -170,22 +170,16 @@ class StateSpec:
 
 
 class StatePool:
-    """Conv window and temporal state per (layer, row).  ``depth`` extra copies per row hold
-    the intermediate states of a multi-token pass until one of them is committed."""
+    """Conv window and temporal state per (layer, row).  Multi-token passes advance the state in place (SMC accepts
+    every token), so no per-position copies are kept."""
 
-    def __init__(self, spec: StateSpec, n_rows: int, device, depth: int = 0):
+    def __init__(self, spec: StateSpec, n_rows: int, device):
         self.spec = spec
         self.n_rows = n_rows
         self.conv = torch.zeros(spec.n_layers, n_rows, spec.conv_dim, spec.conv_width - 1,
                                 dtype=spec.conv_dtype, device=device)
         self.temporal = torch.zeros(spec.n_layers, n_rows, spec.n_heads, spec.head_k_dim, spec.head_v_dim,
                                     dtype=spec.state_dtype, device=device)
-        self.depth = depth
-        if depth:
-            self.conv_steps = torch.zeros(spec.n_layers, n_rows, depth, spec.conv_dim, spec.conv_width - 1,
-                                          dtype=spec.conv_dtype, device=device)
-            self.temporal_steps = torch.zeros(spec.n_layers, n_rows, depth, spec.n_heads, spec.head_k_dim,
-                                              spec.head_v_dim, dtype=spec.state_dtype, device=device)
 
     def copy_rows(self, dst: torch.Tensor, src: torch.Tensor) -> None:
         """dst[i] <- src[i] for every layer (fan-out at materialize, resample copies)."""
@@ -201,12 +195,6 @@ class StatePool:
         r = rows.long()
         self.conv[:, r] = 0
         self.temporal[:, r] = 0
-
-    def commit(self, rows: torch.Tensor, step: int) -> None:
-        """Promote intermediate state ``step`` of each row to the live state."""
-        r = rows.long()
-        self.conv[:, r] = self.conv_steps[:, r, step]
-        self.temporal[:, r] = self.temporal_steps[:, r, step]
 
 
 def cobudget_pages(available_bytes: int, target_cell: int, draft_cell: int,

@@ -52,7 +52,6 @@ def _declare(L) -> None:
     L.smc_gemm_skinny_norm.restype = C.c_int
     L.smc_rope_kv_write.argtypes = [vp, i, ll, vp, vp, vp, i, i, vp, vp, vp, i, i, i, i, i, vp, i, vp]
     L.smc_swiglu_partials.argtypes = [vp, i, ll, vp, i, i, i, i, i, vp]
-    L.smc_attention_extend.argtypes = [vp, vp, vp, vp, i, i, vp, vp, vp, vp, vp, i, i, i, i, i, i, f, vp, i, vp]
     L.smc_attention_fused.argtypes = [vp, vp, i, i, i, i, i, vp, vp, vp, i, i, vp, vp, f, i, vp, vp, i, vp, i, vp, vp, vp,
                                       vp, vp, i, i, i, i, i, i, f, vp, i, vp]
     L.smc_attention_fused.restype = C.c_int
@@ -66,7 +65,7 @@ def _declare(L) -> None:
     L.smc_collect_resample.argtypes = [vp, vp, i, vp, i, d, ull, vp, vp, vp, vp, vp]
     L.smc_state_copy.argtypes = [vp, ll, ll, i, i, vp, vp, vp, i, vp]
     for name in ("smc_gemm_skinny", "smc_add_rmsnorm", "smc_rope_kv_write", "smc_swiglu_partials",
-                 "smc_attention_extend", "smc_sample_or_score", "smc_prepare_cycle", "smc_write_back",
+                 "smc_sample_or_score", "smc_prepare_cycle", "smc_write_back",
                  "smc_collect_resample", "smc_state_copy", "smc_gemm_bn_for", "smc_gemm_default_splits",
                  "smc_sample_scratch_bytes", "smc_slot_arrays_size", "smc_assemble_verify", "smc_cycle_io_size"):
         getattr(L, name).restype = C.c_int
@@ -82,7 +81,7 @@ def _stream():
 
 # kernels launched through this module (a captured graph replays the launches counted at capture)
 launch_count = 0
-_KERNELS_PER_CALL = {"smc_attention_extend": 2, "smc_sample_or_score": 2, "smc_collect_resample": 2}
+_KERNELS_PER_CALL = {"smc_sample_or_score": 2, "smc_collect_resample": 2}
 
 
 def _check(rc: int, what: str) -> None:
@@ -196,16 +195,6 @@ def swiglu_partials(partials: torch.Tensor, splits: int, split_stride: int, act:
                     blk: int, pdl: bool = False) -> None:
     _check(lib().smc_swiglu_partials(_p(partials), splits, split_stride, _p(act), M, ffn, blk, act.stride(0), int(pdl),
                                      _stream()), "smc_swiglu_partials")
-
-
-def attention_extend(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
-                     rows: torch.Tensor, prefix_lens: torch.Tensor, part_acc: torch.Tensor, part_ml: torch.Tensor,
-                     out: torch.Tensor, *, bs: int, E: int, Hq: int, Hkv: int, D: int, splits: int, scale: float,
-                     status: torch.Tensor, pdl: bool = False) -> None:
-    _check(lib().smc_attention_extend(_p(q), _p(k_pool), _p(v_pool), _p(block_table), block_table.stride(0),
-                                      k_pool.shape[0] - 1, _p(rows), _p(prefix_lens), _p(part_acc), _p(part_ml),
-                                      _p(out), bs, E, Hq, Hkv, D, splits, scale, _p(status), int(pdl), _stream()),
-           "smc_attention_extend")
 
 
 def attention_fused(qkv: torch.Tensor, positions: torch.Tensor, cache_locs: torch.Tensor, rope: torch.Tensor,

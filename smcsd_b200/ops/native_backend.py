@@ -109,7 +109,11 @@ class NativeLlama:
         return tuple(self._ks(bs, E) for E in Es)
 
     def _ks(self, bs: int, E: int) -> int:
-        return K.attn_kv_splits(self.ctx_hint, bs, self.nkv, E, self.nq // self.nkv, self.D)
+        ks = K.attn_kv_splits(self.ctx_hint, bs, self.nkv, E, self.nq // self.nkv, self.D)
+        cap = max(1, int(self.attn_splits))          # attention_num_kv_splits bounds the planner's choice (1 = never split)
+        while ks > cap:
+            ks //= 2
+        return ks
 
     def final_hidden(self, rows_idx: torch.Tensor) -> torch.Tensor:
         """Post-final-norm hidden rows (bf16) for callers that project with PyTorch (x0 at prefill)."""
@@ -225,6 +229,7 @@ class NativeState:
         self._version = -1
         self.bs = 0
         self.n_groups = 0
+        self.fused_write_back = True
 
     def bind(self, st) -> None:
         self._arrays = K.make_slot_arrays(st)
@@ -253,6 +258,14 @@ class NativeState:
 
     def write_back(self, st, cin: CycleInputs, out: CycleOutputs) -> None:
         """Eager-path entry: the outputs come from a torch-computed cycle, so restage them."""
+        if not self.fused_write_back:
+            # SMC_FUSED_WRITE_BACK=0: the PyTorch reference of the same state transition
+            native, st.native = st.native, None
+            try:
+                st.write_back(cin, out)
+            finally:
+                st.native = native
+            return
         bs, g, G = self.bs, self.gamma, self.G
         self.drafts[: g * bs].view(g, bs).copy_(out.tokens[:, :g].t())
         self.verify_tok[: bs * G].view(bs, G)[:, g] = out.tokens[:, g]
@@ -314,6 +327,25 @@ class NativeRunner:
         self.graph_max_context = int(a.graph_max_context)
         self.T_draft, self.T_target, self.alpha = float(a.draft_temperature), float(a.target_temperature), float(a.power_alpha)
         self.defer = bool(a.defer_bonus)
+        # A/B switches (environment > argument > default on).  Switching a fused step off routes it to the PyTorch
+        # implementation of the same step; such cycles launch eagerly, like the reference's downgrade of its graph
+        # runners (smcsd/core/worker.py:296-327, smcsd/core/req_state.py:129-133).
+        self.fused_sampling = bool(a.fused_sampling)
+        self.fused_write_back = bool(a.fused_write_back)
+        self.fast_verify = bool(a.fast_verify)
+        self.draft_phase_graph = bool(a.draft_phase_graph)
+        self.switched_off = not (self.fused_sampling and self.fused_write_back and self.fast_verify)
+        if self.switched_off or _env_flag("SMC_DEFER_BONUS_EAGER", False):
+            if self.use_graph:
+                import logging
+                logging.getLogger(__name__).warning(
+                    "cycle graph disabled: a fused step is switched off (fused_sampling=%s fused_write_back=%s "
+                    "fast_verify=%s) or SMC_DEFER_BONUS_EAGER is set", self.fused_sampling, self.fused_write_back,
+                    self.fast_verify)
+            self.use_graph = False
+            self.draft_phase_graph = self.draft_phase_graph and not self.switched_off
+        self._torch_gen = None
+        self.draft_graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.launches_per_cycle = 0
         # Whole-forward persistent kernels (one launch per model forward, lm_head fused with sampling) for dense
@@ -457,8 +489,43 @@ class NativeRunner:
         return x0.to(torch.int32)
 
     # ---- the cycle, as a sequence of kernel launches ---------------------------------
+    def _sample_torch(self, nm, rows: int, temperature: float, alpha: float, tokens_in, tok_out, logp_out,
+                      logz_out) -> None:
+        """PyTorch Gumbel-max / scoring chain over the logits in memory (the path SMC_FUSED_SAMPLING=0 selects;
+        same math as smcsd/core/worker.py:721-778)."""
+        V = nm.c.vocab_size
+        x = nm.logits[:rows, :V].float()
+        cap = float(nm.c.logit_softcap)
+        if cap > 0:
+            x = torch.tanh(x / cap) * cap
+        base = x / temperature
+        scaled = base * alpha
+        lse_s = torch.logsumexp(scaled, dim=-1)
+        lse_b = torch.logsumexp(base, dim=-1) if alpha != 1.0 else lse_s
+        if self._torch_gen is None:
+            self._torch_gen = torch.Generator(device=self.device)
+            self._torch_gen.manual_seed(self.seed & 0x7FFFFFFF)
+        u = torch.rand(scaled.shape, generator=self._torch_gen, device=self.device).clamp_(1e-10, 1.0 - 1e-7)
+        tok = torch.argmax(scaled - torch.log(-torch.log(u)), dim=-1)
+        logp = scaled.gather(1, tok[:, None])[:, 0] - lse_s
+        logz = lse_s - alpha * lse_b if alpha != 1.0 else torch.zeros_like(lse_s)
+        if tokens_in is not None:
+            given = tokens_in[:rows].long()
+            score = given >= 0
+            g = given.clamp(min=0)
+            tok = torch.where(score, g, tok)
+            logp = torch.where(score, base.gather(1, g[:, None])[:, 0] - lse_b, logp)
+            logz = torch.where(score, torch.zeros_like(logz), logz)
+        tok_out[:rows].copy_(tok.to(torch.int32))
+        logp_out[:rows].copy_(logp)
+        if logz_out is not None:
+            logz_out[:rows].copy_(logz)
+
     def _sample(self, nm, rows: int, call_id: int, temperature: float, alpha: float, tokens_in, tok_out, logp_out,
                 logz_out) -> None:
+        if not self.fused_sampling and not hasattr(nm, "tp_sample"):
+            self._sample_torch(nm, rows, temperature, alpha, tokens_in, tok_out, logp_out, logz_out)
+            return
         if hasattr(nm, "tp_sample"):
             nm.tp_sample(rows=rows, temperature=temperature, alpha=alpha, tokens_in=tokens_in, seed=self.seed,
                          cycle_counter=self._counters, call_id=call_id, tok_out=tok_out, logp_out=logp_out,
@@ -472,7 +539,17 @@ class NativeRunner:
 
     def _use_pf(self, which: str, tokens: int) -> bool:
         pf = self.pf_target if which == "target" else self.pf_draft
-        return pf is not None and tokens <= pf.T
+        return pf is not None and tokens <= pf.T and not self.switched_off
+
+    def _verify_torch(self, nm, ids, pos, locs, rows, prefix, bs: int, E: int) -> None:
+        """Target verify through the plain PyTorch forward (cuBLAS GEMMs, reference attention loop): what
+        SMC_FAST_VERIFY=0 selects.  Fills the chain's logits buffer."""
+        T = bs * E
+        pl = prefix[:bs].tolist()
+        ext = ExtendBatch(ids[:T].long(), pos[:T].long(), locs[:T], rows[:bs], prefix[:bs], extend_len=E,
+                          prefix_lens_host=pl)
+        hid = nm.m.forward_torch(ext, nm.kv, nm.bt)
+        nm.logits[:T, :nm.c.vocab_size].copy_(nm.m.logits_torch(hid))
 
     def _model_step(self, which: str, ids, pos, locs, rows, prefix, bs: int, E: int, *, lm_rows: int, lm_off: int = 0,
                     lm_step: int = 1, call_id: int = 0, temperature: float = 1.0, alpha: float = 1.0, tokens_in=None,
@@ -487,12 +564,20 @@ class NativeRunner:
                    logz_out=logz_out)
             return
         nm = self.target if which == "target" else self.draft
-        nm.forward(ids, pos, locs, rows, prefix, bs, E)
+        if which == "target" and not self.fast_verify and isinstance(nm, NativeLlama):
+            self._verify_torch(nm, ids, pos, locs, rows, prefix, bs, E)
+        else:
+            nm.forward(ids, pos, locs, rows, prefix, bs, E)
+            if lm_rows > 0:
+                nm.lm_head(lm_rows, row_offset=lm_off, row_step=lm_step)
         if lm_rows > 0:
-            nm.lm_head(lm_rows, row_offset=lm_off, row_step=lm_step)
             self._sample(nm, lm_rows, call_id, temperature, alpha, tokens_in, tok_out, logp_out, logz_out)
 
     def _cycle_body(self, st) -> None:
+        self._draft_body(st)
+        self._verify_body(st)
+
+    def _draft_body(self, st) -> None:
         ns, b = self.ns, self.ns.bufs
         bs, g, G = ns.bs, self.gamma, self.G
         self._counters = st.counters
@@ -515,6 +600,13 @@ class NativeRunner:
                 self._model_step("draft", ids, b["step_pos"][sl], b["step_locs"][sl], rows, b["step_pos"][sl], bs, 1,
                                  lm_rows=bs if s < g else 0, call_id=s, temperature=Td,
                                  tok_out=dr[sl] if s < g else None, logp_out=lq[sl] if s < g else None)
+
+    def _verify_body(self, st) -> None:
+        ns, b = self.ns, self.ns.bufs
+        bs, g, G = ns.bs, self.gamma, self.G
+        self._counters = st.counters
+        rows = ns.active[:bs]
+        dr = ns.drafts
         K.assemble_verify(ns.io, dr, bs, g)
         self._model_step("target", b["verify_ids"], b["positions_verify"], b["cache_locs"], rows, b["orig_seq"], bs, G,
                          lm_rows=bs * G, call_id=g + 1, temperature=self.T_target, alpha=self.alpha,
@@ -524,8 +616,32 @@ class NativeRunner:
     def decode_cycle(self, worker, cin: CycleInputs) -> CycleOutputs:
         """Eager kernel chain for one cycle (the graph path replays the same launches)."""
         st = self.st
-        self._cycle_body(st)
         ns = self.ns
+        # this entry is driven step by step from the host, so one small read for the attention split plan is fine
+        ctx = int(cin.orig_seq_lens.max().item()) + self.G if cin.orig_seq_lens.numel() else 0
+        self.target.set_context(ctx, ns.bs, (self.G,))
+        self.draft.set_context(ctx, ns.bs, (1, 2))
+        if self.draft_phase_graph and not self.switched_off and ns.bs <= self.graph_max_bs:
+            # draft-only graph (SMC_DRAFT_PHASE_GRAPH): the gamma draft forwards and their sampling replay as one
+            # launch, verify and scoring stay eager.  The draft part only reads the buffers the prologue kernel filled
+            # and its noise is keyed by the cycle counter, so running it once eagerly before the capture is harmless.
+            key = (ns.bs, self.draft.set_context(self.target.ctx_hint, ns.bs, (1, 2)))
+            gr = self.draft_graphs.get(key)
+            if gr is None:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    self._draft_body(st)
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    self._draft_body(st)
+                self.draft_graphs[key] = gr
+            gr.replay()
+            self._verify_body(st)
+        else:
+            self._cycle_body(st)
         bs, g, G = ns.bs, self.gamma, self.G
         drafts = ns.drafts[: g * bs].view(g, bs).t()
         tokens = torch.cat([drafts, ns.verify_tok[: bs * G].view(bs, G)[:, g:]], dim=1)
@@ -535,7 +651,10 @@ class NativeRunner:
 
     # ---- whole-cycle graph ----------------------------------------------------------
     def can_run_cycle(self, st) -> bool:
-        return True
+        """The whole cycle as one kernel sequence (graph, or the same launches eagerly beyond the capture caps).
+        With a fused step switched off, or the draft-only graph asked for, the scheduler drives the cycle step by
+        step instead: prologue kernel, ``decode_cycle``, write-back, resampling."""
+        return not self.switched_off and not (self.draft_phase_graph and not self.use_graph)
 
     def _full_cycle(self, st) -> None:
         ns = self.ns
@@ -616,5 +735,6 @@ def create(sched, comm=None):
         raise RuntimeError("the native backend needs a CUDA device")
     K.lib()     # fail loudly if the kernel library is missing
     ns = NativeState(sched.max_groups * sched.args.n_particles, sched.args.gamma, sched.device)
+    ns.fused_write_back = bool(sched.args.fused_write_back)
     runner = NativeRunner(sched, ns, comm)
     return ns, runner

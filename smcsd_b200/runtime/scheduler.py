@@ -88,7 +88,12 @@ class SMCScheduler:
         seed = a.random_seed
         self.target = target if target is not None else build_model(
             a.model_path, self.dtype, self.device, tp_rank, tp_size, seed=seed)
+        if tp_size > 1 and not a.replicate_draft and backend == "native":
+            raise ValueError("replicate_draft=False (a tensor-parallel draft) is only available with backend='torch': "
+                             "the kernel path keeps a full draft replica on every rank")
         d_tp = (0, 1) if a.replicate_draft else (tp_rank, tp_size)
+        if draft is None and tp_size == 1 and a.draft_model_path == a.model_path:
+            draft = self.target           # the target as its own proposal (vanilla arm): one set of weights, two KV pools
         self.draft = draft if draft is not None else build_model(
             a.draft_model_path, self.dtype, self.device, d_tp[0], d_tp[1], seed=seed + 1)
         self.comm = comm

@@ -1,8 +1,8 @@
 """The SMC decode cycle: prefill + x0, draft autoregression (deferred-bonus or legacy
 schedule), one batched target verify, per-position log-weight differences and the bonus
 token.  Two executions of the same cycle exist: this eager path over the model objects'
-plain-PyTorch forwards (CPU, oracle, cuBLAS baseline) and the captured sm_100a kernel
-chain in ``cycle_graph.py`` that the worker switches to on a B200.
+plain-PyTorch forwards (CPU, oracle, cuBLAS baseline) and the sm_100a kernel chain of
+``ops/native_backend.py`` (captured as one CUDA graph per cycle) that the worker hands over to on a B200.
 
 Algorithm per the reference worker (smcsd/core/worker.py:642-717 prefill and x0,
 :780-891 deferred draft schedule, :1046-1092 legacy schedule, :1095-1166 verify,

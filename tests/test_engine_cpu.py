@@ -88,3 +88,24 @@ def test_profiler_traces_whole_run_and_by_stage(tmp_path):
     eng.stop_profile()
     names = glob.glob(str(tmp_path / "decode_only" / "*.trace.json.gz"))
     assert names and all(n.endswith("-decode.trace.json.gz") for n in names)
+
+
+def test_vanilla_arm_is_plain_target_sampling():
+    """The baseline arm of the harnesses: one particle, gamma 1, the target as its own proposal.  Weights stay at
+    zero (proposal == target), nothing resamples and the requested number of tokens comes out."""
+    import argparse
+
+    from smcsd_b200.config import EngineArgs
+    from smcsd_b200.http_server import build_baseline_engine_from_args
+    p = argparse.ArgumentParser()
+    EngineArgs.add_cli_args(p)
+    ns = p.parse_args(["--model", "preset:tiny-target", "--draft-model", "preset:tiny-draft", "--dtype", "float32",
+                       "--device", "cpu", "--max-running-requests", "2"])
+    eng = build_baseline_engine_from_args(ns, temperature=0.8)
+    assert eng.args.n_particles == 1 and eng.args.gamma == 1
+    outs = eng.generate(input_ids=[[5, 6, 7, 8], [9, 10, 11]], sampling_params={"max_new_tokens": 12, "ignore_eos": True})
+    assert [o["completion_tokens"] for o in outs] == [12, 12]
+    for o in outs:
+        assert abs(o["smc_log_Z_hat"]) < 1e-4 and all(abs(w) < 1e-4 for w in o["smc_log_w_tilde"])
+    assert eng._sched.stats["resampled_groups"] == 0
+    eng.shutdown()

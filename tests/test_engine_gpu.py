@@ -231,3 +231,52 @@ def test_staggered_arrivals_with_changing_batch_sizes():
     s.check_idle_invariants()
     s.alloc.check_conservation()
     assert s.native_runner.check_status() == 0
+
+
+def _gen(eng, n=2, new=45):
+    o = eng.generate(input_ids=_prompts(n, L=30, seed=21), sampling_params={"max_new_tokens": new, "ignore_eos": True})
+    assert eng._sched.native_runner.check_status() == 0
+    eng._sched.check_idle_invariants()
+    eng._sched.alloc.check_conservation()
+    return o
+
+
+def test_write_back_switch_and_draft_phase_graph_equal_the_eager_chain():
+    """SMC_FUSED_WRITE_BACK=0 routes the state transition to the PyTorch reference, and the draft-only graph replays
+    the same draft launches: both must reproduce the eager kernel chain token for token."""
+    base = _gen(_engine(backend="native", cycle_graph=False))
+    wb = _engine(backend="native", cycle_graph=False, fused_write_back=False)
+    assert wb._sched.native_runner.switched_off and not wb._sched.native_runner.can_run_cycle(wb._sched.state)
+    out_wb = _gen(wb)
+    dpg = _engine(backend="native", cycle_graph=False, draft_phase_graph=True)
+    out_dpg = _gen(dpg)
+    assert len(dpg._sched.native_runner.draft_graphs) >= 1
+    for a, b, c in zip(base, out_wb, out_dpg):
+        assert a["output_ids"] == b["output_ids"] == c["output_ids"]
+        assert abs(a["smc_log_Z_hat"] - b["smc_log_Z_hat"]) < 1e-5
+        assert abs(a["smc_log_Z_hat"] - c["smc_log_Z_hat"]) < 1e-6
+
+
+def test_sampling_and_verify_switches_run_the_pytorch_steps():
+    """SMC_FUSED_SAMPLING=0 / SMC_FAST_VERIFY=0: the cycle graph is dropped with a warning and the PyTorch sampler /
+    PyTorch verify forward take over; outputs stay well-formed and the importance weights stay finite."""
+    import math
+    for kw in (dict(fused_sampling=False), dict(fast_verify=False)):
+        eng = _engine(backend="native", **kw)
+        r = eng._sched.native_runner
+        assert r.switched_off and not r.use_graph
+        o = _gen(eng)
+        assert [x["completion_tokens"] for x in o] == [45, 45]
+        assert all(math.isfinite(x["smc_log_Z_hat"]) for x in o)
+
+
+def test_attention_split_cap_is_honoured():
+    eng = _engine(backend="native", attention_num_kv_splits=1, max_running_requests=1, context_length=2048,
+                  max_total_tokens=32768)
+    nm = eng._sched.native_runner.target
+    nm.set_context(1800, 4, (5,))
+    assert nm._ks(4, 5) == 1
+    eng2 = _engine(backend="native", max_running_requests=1, context_length=2048, max_total_tokens=32768)
+    nm2 = eng2._sched.native_runner.target
+    nm2.set_context(1800, 4, (5,))
+    assert nm2._ks(4, 5) >= 2

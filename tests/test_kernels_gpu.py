@@ -37,7 +37,8 @@ def test_gemm_partials(N, Kd, M, splits):
     ref = X.float() @ W.float().t()
     got = out.sum(0)
     err = (got - ref).abs().max().item()
-    assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
+    # bf16 products are exact in fp32, so only the accumulation order differs from the fp32 reference
+    assert err < 1e-3 * max(1.0, ref.abs().max().item()), err
 
 
 @pytest.mark.parametrize("N,Kd,M,splits", [
@@ -63,7 +64,7 @@ def test_gemm_cluster_splitk(N, Kd, M, splits):
     K.gemm_skinny(W, X, out2, M=M, splits=s, epi=K.EPI_STORE_F32, ldo=N, status=st, pdl=True)
     torch.cuda.synchronize()
     assert int(st) == 0
-    tol = 2e-2 * max(1.0, ref.abs().max().item())
+    tol = 1e-3 * max(1.0, ref.abs().max().item())
     assert (out - ref).abs().max().item() < tol
     assert (h - h0 - ref).abs().max().item() < tol
     assert torch.equal(out, out2), "the cluster reduction must be bit-deterministic"
@@ -82,7 +83,7 @@ def test_gemm_bf16_and_strided_rows():
     torch.cuda.synchronize()
     ref = X2[1::2].float() @ W.float().t()
     assert int(st) == 0
-    assert (out.float() - ref).abs().max().item() < 3e-2 * ref.abs().max().item()
+    assert (out.float() - ref).abs().max().item() < 6e-3 * ref.abs().max().item()      # one bf16 rounding of the output
 
 
 @pytest.mark.parametrize("ffn,d,M", [(8192, 2048, 8), (14336, 4096, 72), (1024, 256, 40)])
@@ -101,7 +102,7 @@ def test_gemm_swiglu_epilogue(ffn, d, M):
     g, u = X.float() @ Wg.float().t(), X.float() @ Wu.float().t()
     ref = torch.nn.functional.silu(g) * u
     assert int(st) == 0
-    assert (act.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
+    assert (act.float() - ref).abs().max().item() < 6e-3 * max(1.0, ref.abs().max().item())
     # the unfused path (partials + separate activation kernel) agrees
     s = 2
     part = torch.zeros(s, M, 2 * ffn, device="cuda")
@@ -109,14 +110,14 @@ def test_gemm_swiglu_epilogue(ffn, d, M):
     act2 = torch.zeros_like(act)
     K.swiglu_partials(part, s, M * 2 * ffn, act2, M=M, ffn=ffn, blk=64)
     torch.cuda.synchronize()
-    assert (act2.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
+    assert (act2.float() - ref).abs().max().item() < 6e-3 * max(1.0, ref.abs().max().item())
     # split-K reduced inside a cluster before the activation
     for s in (2, 4, 3):
         act3 = torch.zeros_like(act)
         K.gemm_skinny(Wgu, X, act3, M=M, splits=s, epi=K.EPI_SWIGLU_BF16, ldo=ffn, status=st, pdl=True)
         torch.cuda.synchronize()
         assert int(st) == 0
-        assert (act3.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item()), s
+        assert (act3.float() - ref).abs().max().item() < 6e-3 * max(1.0, ref.abs().max().item()), s
 
 
 # ------------------------------------------------------------------------------- norm / rope
@@ -169,44 +170,6 @@ def test_rope_kv_write(Hq, Hkv, D, rd):
     assert (q.float() - qr).abs().max().item() < 3e-2
     assert (kp[locs.long()].float() - kr).abs().max().item() < 3e-2
     assert (vp[locs.long()].float() - vr).abs().max().item() < 3e-2
-
-
-# ------------------------------------------------------------------------------- attention
-@pytest.mark.parametrize("bs,E,Hq,Hkv,D,ctx", [
-    (8, 9, 32, 8, 128, 1500), (8, 9, 32, 8, 128, 3), (5, 2, 32, 8, 64, 300), (8, 1, 32, 8, 64, 700),
-    (3, 9, 4, 4, 64, 200), (4, 9, 16, 2, 256, 260), (2, 5, 4, 2, 64, 0),
-])
-def test_attention_extend(bs, E, Hq, Hkv, D, ctx):
-    K = _K()
-    from smcsd_b200.models.layers import ExtendBatch, paged_attention_reference
-    torch.manual_seed(5)
-    pages = bs * (ctx + E) + 64
-    kp = torch.randn(pages + 1, Hkv * D, device="cuda").bfloat16()
-    vp = torch.randn(pages + 1, Hkv * D, device="cuda").bfloat16()
-    max_ctx = ctx + E + 8
-    bt = torch.zeros(bs + 2, max_ctx, device="cuda", dtype=torch.int32)
-    perm = (torch.randperm(pages, device="cuda") + 1).to(torch.int32)
-    prefix = torch.tensor([max(0, ctx - 17 * i) for i in range(bs)], device="cuda", dtype=torch.int32)
-    rows = torch.arange(bs, device="cuda", dtype=torch.int32) + 1
-    off = 0
-    for b in range(bs):
-        L = int(prefix[b]) + E
-        bt[b + 1, :L] = perm[off:off + L]
-        off += L
-    q = torch.randn(bs * E, Hq, D, device="cuda").bfloat16()
-    splits = 8
-    pa = torch.zeros(bs * E * Hq * splits * D, device="cuda")
-    pm = torch.zeros(bs * E * Hq * splits * 2, device="cuda")
-    out = torch.zeros(bs * E, Hq * D, device="cuda", dtype=torch.bfloat16)
-    st = _status()
-    K.attention_extend(q, kp, vp, bt, rows, prefix, pa, pm, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D, splits=splits,
-                       scale=D ** -0.5, status=st)
-    torch.cuda.synchronize()
-    batch = ExtendBatch(None, None, None, rows, prefix, extend_len=E)
-    ref = paged_attention_reference(q, kp, vp, bt, batch, Hkv).reshape(bs * E, -1).float()
-    assert int(st) == 0
-    err = (out.float() - ref).abs().max().item()
-    assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
 
 
 # ------------------------------------------------------------------------------- sampling
