@@ -466,67 +466,12 @@ __device__ __forceinline__ void pf_epi_chunk(const PfParams& p, const GemmDesc& 
     // lm_head: transpose the chunk through shared memory, then 8 threads share one token column (16 rows each)
     float* tr = scratch + parity * (16 * 129);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) tr[j * 129 + t] = v[j];
+    for (int j = 0; j < 16; ++j) tr[j * 129 + t] = v[j] * S.rstd[min(c0 + j, 127)];
     bar_epi();
-    const int col = t >> 3, sub = t & 7, m = c0 + col;
-    const unsigned int gmask = 0xFFu << (lane & 24);        // the 8 lanes that share this column
-    if (m < p.lm_rows) {
-      const int given = p.tokens_in != nullptr ? p.tokens_in[m] : -1;
-      const bool sampling = given < 0;
-      const float r = S.rstd[m];
-      const Philox rng(p.seed);
-      const long long cyc = *p.cycle_counter;
-      const uint32_t ctr_lo = (uint32_t)cyc, ctr_hi = (uint32_t)(cyc >> 32);
-      float max_s = -INFINITY, sum_s = 0.f, max_b = -INFINITY, sum_b = 0.f, best = -INFINITY, best_scaled = 0.f;
-      float given_logit = -INFINITY;
-      const int nb = slab * 128 + sub * 16;
-      int best_idx = nb < p.V ? nb : 0;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint32_t rnd[4] = {0u, 0u, 0u, 0u};
-        const int c4 = nb + q * 4;
-        if (sampling && c4 < p.V)
-          rng.run((uint32_t)(c4 >> 2), (uint32_t)m, (uint32_t)p.call_id ^ (ctr_hi << 8), ctr_lo, rnd);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int c = c4 + i;
-          if (c >= p.V) continue;
-          float x = tr[col * 129 + sub * 16 + q * 4 + i] * r;
-          if (p.softcap > 0.f) x = tanhf(x / p.softcap) * p.softcap;
-          const float b = x * p.inv_temp, sc = b * p.alpha;
-          if (sc > max_s) { sum_s = sum_s * __expf(max_s - sc) + 1.f; max_s = sc; } else { sum_s += __expf(sc - max_s); }
-          if (p.alpha != 1.f) {
-            if (b > max_b) { sum_b = sum_b * __expf(max_b - b) + 1.f; max_b = b; } else { sum_b += __expf(b - max_b); }
-          }
-          if (sampling) {
-            const float u = u32_to_unit(rnd[i]);
-            const float pert = sc + (-__logf(-__logf(u)));
-            if (pert > best) { best = pert; best_scaled = sc; best_idx = c; }
-          } else if (c == given) {
-            given_logit = x;
-          }
-        }
-      }
-#pragma unroll
-      for (int o = 1; o < 8; o <<= 1) {
-        lse_merge(max_s, sum_s, __shfl_xor_sync(gmask, max_s, o), __shfl_xor_sync(gmask, sum_s, o));
-        lse_merge(max_b, sum_b, __shfl_xor_sync(gmask, max_b, o), __shfl_xor_sync(gmask, sum_b, o));
-        const float b2 = __shfl_xor_sync(gmask, best, o), bs2 = __shfl_xor_sync(gmask, best_scaled, o);
-        const int i2 = __shfl_xor_sync(gmask, best_idx, o);
-        if (b2 > best || (b2 == best && i2 < best_idx)) { best = b2; best_scaled = bs2; best_idx = i2; }
-        given_logit = fmaxf(given_logit, __shfl_xor_sync(gmask, given_logit, o));
-      }
-      if (sub == 0) {
-        RowPartial a = S.rp[m];
-        lse_merge(a.max_s, a.sum_s, max_s, sum_s);
-        lse_merge(a.max_b, a.sum_b, max_b, sum_b);
-        if (best > a.best || (best == a.best && best_idx < a.best_idx)) {
-          a.best = best; a.best_scaled = best_scaled; a.best_idx = best_idx;
-        }
-        if (given_logit != -INFINITY) a.pad = __float_as_int(given_logit);
-        S.rp[m] = a;
-      }
-    }
+    SampleArgs sa;
+    sa.inv_temp = p.inv_temp; sa.alpha = p.alpha; sa.softcap = p.softcap; sa.V = p.V; sa.rows = p.lm_rows;
+    sa.call_id = p.call_id; sa.tokens_in = p.tokens_in; sa.seed = p.seed; sa.cycle_counter = p.cycle_counter;
+    lm_reduce_chunk(sa, tr, slab * 128, c0, 0, t, S.rp);
   }
 }
 
@@ -592,7 +537,7 @@ __device__ void pf_gemm_epilogue(const PfParams& p, const PfCtx& ctx, PfShared& 
       for (int q = 0; q < parts; ++q) ss += __ldcg(p.ssq + (size_t)q * p.ssq_ld + col);
       S.rstd[t] = rsqrtf(ss / (float)p.d + p.rms_eps);
     }
-    if (g.epi == PF_EPI_LMHEAD) S.rp[t] = RowPartial{-INFINITY, 0.f, -INFINITY, 0.f, -INFINITY, 0.f, 0, __float_as_int(-INFINITY)};
+    if (g.epi == PF_EPI_LMHEAD) S.rp[t] = row_partial_neutral();
     bar_epi();
   }
   const int n_units = pf_units(g, cta, ncta);
@@ -705,49 +650,11 @@ __device__ void pf_gemm_epilogue(const PfParams& p, const PfCtx& ctx, PfShared& 
 // Last phase: merge the per-CTA partials of every sampled / scored row.
 __device__ void pf_sample_merge(const PfParams& p, int cta, int ncta, int t) {
   if (t >= 32) return;
-  const int lane = t;
-  for (int row = cta; row < p.lm_rows; row += ncta) {
-    RowPartial a{-INFINITY, 0.f, -INFINITY, 0.f, -INFINITY, 0.f, 0, __float_as_int(-INFINITY)};
-    float given_logit = -INFINITY;
-    for (int c = lane; c < ncta; c += 32) {
-      const RowPartial* src = p.sparts + (size_t)row * ncta + c;
-      RowPartial b;
-      b.max_s = __ldcg(&src->max_s); b.sum_s = __ldcg(&src->sum_s);
-      b.max_b = __ldcg(&src->max_b); b.sum_b = __ldcg(&src->sum_b);
-      b.best = __ldcg(&src->best); b.best_scaled = __ldcg(&src->best_scaled);
-      b.best_idx = __ldcg(&src->best_idx); b.pad = __ldcg(&src->pad);
-      lse_merge(a.max_s, a.sum_s, b.max_s, b.sum_s);
-      lse_merge(a.max_b, a.sum_b, b.max_b, b.sum_b);
-      if (b.best > a.best || (b.best == a.best && b.best_idx < a.best_idx)) {
-        a.best = b.best; a.best_scaled = b.best_scaled; a.best_idx = b.best_idx;
-      }
-      given_logit = fmaxf(given_logit, __int_as_float(b.pad));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      lse_merge(a.max_s, a.sum_s, __shfl_xor_sync(0xffffffffu, a.max_s, o), __shfl_xor_sync(0xffffffffu, a.sum_s, o));
-      lse_merge(a.max_b, a.sum_b, __shfl_xor_sync(0xffffffffu, a.max_b, o), __shfl_xor_sync(0xffffffffu, a.sum_b, o));
-      const float b2 = __shfl_xor_sync(0xffffffffu, a.best, o), bs2 = __shfl_xor_sync(0xffffffffu, a.best_scaled, o);
-      const int i2 = __shfl_xor_sync(0xffffffffu, a.best_idx, o);
-      if (b2 > a.best || (b2 == a.best && i2 < a.best_idx)) { a.best = b2; a.best_scaled = bs2; a.best_idx = i2; }
-      given_logit = fmaxf(given_logit, __shfl_xor_sync(0xffffffffu, given_logit, o));
-    }
-    if (lane == 0) {
-      const float lse_s = a.max_s + __logf(a.sum_s);
-      const int given = p.tokens_in != nullptr ? p.tokens_in[row] : -1;
-      if (given >= 0) {
-        // score mode reports log softmax(x / T)[token] (alpha is applied by the caller)
-        const float lse_b = (p.alpha != 1.f) ? a.max_b + __logf(a.sum_b) : lse_s;
-        p.tok_out[row] = given;
-        p.logp_out[row] = given_logit * p.inv_temp - lse_b;
-        if (p.logz_out) p.logz_out[row] = 0.f;
-      } else {
-        p.tok_out[row] = a.best_idx;
-        p.logp_out[row] = a.best_scaled - lse_s;
-        if (p.logz_out) p.logz_out[row] = (p.alpha != 1.f) ? lse_s - p.alpha * (a.max_b + __logf(a.sum_b)) : 0.f;
-      }
-    }
-  }
+  SampleArgs sa;
+  sa.inv_temp = p.inv_temp; sa.alpha = p.alpha; sa.softcap = p.softcap; sa.V = p.V; sa.rows = p.lm_rows;
+  sa.call_id = p.call_id; sa.tokens_in = p.tokens_in; sa.seed = p.seed; sa.cycle_counter = p.cycle_counter;
+  for (int row = cta; row < p.lm_rows; row += ncta)
+    sample_merge_row(sa, p.sparts + (size_t)row * ncta, ncta, 1, row, t, p.tok_out, p.logp_out, p.logz_out);
 }
 
 // ---------------------------------------------------------------- embedding phase (warps 2..7)

@@ -25,12 +25,14 @@
 #include <unordered_map>
 
 #include "common.cuh"
+#include "sample_core.cuh"
 #include "tmap_host.h"
 
 namespace smc {
 
 enum { EPI_PARTIAL_F32 = 0, EPI_BF16 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_F32 = 3, EPI_RESID_F32 = 4, EPI_RS_F32 = 5,
-       EPI_SWIGLU_SPLIT = 6 };   // 6: SwiGLU after a split-K reduction inside the cluster
+       EPI_SWIGLU_SPLIT = 6,     // 6: SwiGLU after a split-K reduction inside the cluster
+       EPI_LMHEAD = 7 };         // 7: lm_head: every slab is reduced to per-row sampling partials, logits are not stored
 
 // Tensor-parallel links of one GEMM.  Consumer side (all-gather -> GEMM): peers store their
 // activation rows into this GPU's buffer and bump a counter here; the TMA producer waits for the
@@ -70,6 +72,8 @@ struct GemmParams {
   float* ssq_out;
   __nv_bfloat16* hb_out;
   int hb_ld;
+  // lm_head with fused sampling / scoring (EPI_LMHEAD): out = RowPartial [M, slabs]
+  SampleArgs samp;
 };
 
 template <int BN, int EPI, bool LEAN>
@@ -284,6 +288,31 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 16; ++j) sbuf[(c0 + j) * C::BM + row_in_tile] = __uint_as_float(r[j]);
       }
+    } else if constexpr (EPI == EPI_LMHEAD) {
+      // Sampling / scoring straight out of tensor memory: the slab's 128 vocabulary rows are reduced per token to
+      // (max, sum-exp, best Gumbel candidate, chosen logit); a small merge kernel combines the slabs.
+      float* tr = reinterpret_cast<float*>(smem);        // [2][16][129]; the ring is idle: every MMA has completed
+      __shared__ RowPartial s_rp[BN];
+      for (int c = threadIdx.x; c < BN; c += 128) s_rp[c] = row_partial_neutral();
+      __syncthreads();
+      int parity = 0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN && m_base + c0 < p.M; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(taddr + c0, r);
+        tmem_ld_wait();
+        float* trp = tr + parity * (16 * 129);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) trp[j * 129 + row_in_tile] = __uint_as_float(r[j]) * s_rstd[c0 + j];
+        __syncthreads();
+        lm_reduce_chunk(p.samp, trp, n_tile * C::BM, c0, m_base, (int)threadIdx.x, s_rp);
+        parity ^= 1;
+      }
+      __syncthreads();
+      RowPartial* parts = reinterpret_cast<RowPartial*>(p.out);
+      const int n_slabs = (p.N + C::BM - 1) / C::BM;
+      for (int c = threadIdx.x; c < BN; c += 128)
+        if (m_base + c < p.M) parts[(size_t)(m_base + c) * n_slabs + n_tile] = s_rp[c];
     } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -607,7 +636,8 @@ static int cached_tmap(CUtensorMap* tm, const void* base, long long rows, long l
 }
 
 static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo, int splits,
-                      int epi, int* status, int pdl, const smc::TpLink* tp, const NormLink* nl, cudaStream_t stream) {
+                      int epi, int* status, int pdl, const smc::TpLink* tp, const NormLink* nl, cudaStream_t stream,
+                      const smc::SampleArgs* samp = nullptr) {
   using namespace smc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) != 0 || (ldx % 8) != 0) return -20;       // row pitch must be a multiple of 16 bytes
@@ -617,6 +647,7 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
   if (clustered && (splits < 1 || splits > 8)) return -23;
   if ((epi == EPI_SWIGLU_BF16 || epi == EPI_SWIGLU_SPLIT) && (N % 128) != 0) return -22;
   if (epi == EPI_RS_F32 && (tp == nullptr || tp->tp < 1 || tp->tp > 8 || tp->rows_per_rank < 1)) return -24;
+  if (epi == EPI_LMHEAD && (samp == nullptr || splits != 1 || M > 256)) return -26;
   const int bn = bn_for(M, N, clustered);
   GemmParams p;
   p.N = N; p.K = K; p.M = M;
@@ -627,6 +658,8 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
   p.ssq_mstride = 1;
   p.ssq_in = nullptr; p.ssq_parts = 0; p.ssq_ld = 0; p.norm_inv_d = 0.f; p.norm_eps = 0.f; p.ssq_out = nullptr;
   p.hb_out = nullptr; p.hb_ld = 0;
+  memset(&p.samp, 0, sizeof(p.samp));
+  if (samp != nullptr) p.samp = *samp;
   if (nl != nullptr) {
     p.ssq_in = nl->ssq_in; p.ssq_parts = nl->ssq_parts; p.ssq_ld = nl->ssq_ld;
     p.norm_inv_d = nl->norm_d > 0 ? 1.0f / (float)nl->norm_d : 0.f; p.norm_eps = nl->norm_eps;
@@ -655,6 +688,7 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
     case EPI_RESID_F32: return dispatch_bn<EPI_RESID_F32>(bn, tmW, tmX, p, grid, stream);
     case EPI_RS_F32: return dispatch_bn<EPI_RS_F32>(bn, tmW, tmX, p, grid, stream);
     case EPI_SWIGLU_SPLIT: return dispatch_bn<EPI_SWIGLU_SPLIT>(bn, tmW, tmX, p, grid, stream);
+    case EPI_LMHEAD: return dispatch_bn<EPI_LMHEAD>(bn, tmW, tmX, p, grid, stream);
   }
   return -11;
 }
@@ -683,6 +717,50 @@ SMC_API int smc_gemm_skinny_norm(const void* W, const void* X, void* out, int N,
                                  int ssq_mstride, cudaStream_t stream) {
   NormLink nl = {ssq_in, ssq_parts, ssq_ld, norm_d, norm_eps, ssq_out, hb_out, hb_ld, ssq_mstride};
   return gemm_entry(W, X, out, N, K, M, ldx, ldo, splits, epi, status, pdl, nullptr, &nl, stream);
+}
+
+namespace smc {
+__global__ void __launch_bounds__(32) lm_sample_merge_kernel(SampleArgs a, const RowPartial* __restrict__ parts,
+                                                            int n_slabs, int* tok_out, float* logp_out,
+                                                            float* logz_out, int pdl) {
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
+  const int row = blockIdx.x;
+  sample_merge_row(a, parts + (size_t)row * n_slabs, n_slabs, 1, row, (int)threadIdx.x, tok_out, logp_out, logz_out);
+}
+}  // namespace smc
+
+SMC_API int smc_lm_parts_bytes(int rows, int V) { return rows * ((V + 127) / 128) * (int)sizeof(smc::RowPartial); }
+
+// lm_head fused with sampling / scoring: logits = (X W^T) * rstd are reduced per 128-row vocabulary slab inside the
+// GEMM epilogue (they never reach memory), then one warp per row merges the slabs.  Rows choose their mode through
+// tokens_in (>= 0: score that token, < 0 or null: sample from softmax(alpha * x / T)); same outputs and the same
+// noise stream as smc_sample_or_score on stored logits.  parts: scratch of smc_lm_parts_bytes(M, V) bytes.
+SMC_API int smc_lm_head_sample(const void* W, const void* X, int V, int K, int M, int ldx, int* status, int pdl,
+                               const float* ssq_in, int ssq_parts, int ssq_ld, int norm_d, float norm_eps,
+                               int ssq_mstride, float temperature, float alpha, float softcap, const int* tokens_in,
+                               unsigned long long seed, const long long* cycle_counter, int call_id, void* parts,
+                               int* tok_out, float* logp_out, float* logz_out, cudaStream_t stream) {
+  using namespace smc;
+  if (M <= 0) return 0;
+  if (temperature <= 0.f || parts == nullptr || cycle_counter == nullptr) return -27;
+  SampleArgs a;
+  a.inv_temp = 1.0f / temperature; a.alpha = alpha; a.softcap = softcap; a.V = V; a.rows = M; a.call_id = call_id;
+  a.tokens_in = tokens_in; a.seed = seed; a.cycle_counter = cycle_counter;
+  NormLink nl = {ssq_in, ssq_parts, ssq_ld, norm_d, norm_eps, nullptr, nullptr, 0, ssq_mstride};
+  int rc = gemm_entry(W, X, parts, V, K, M, ldx, 0, 1, EPI_LMHEAD, status, pdl, nullptr, &nl, stream, &a);
+  if (rc) return rc;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)M);
+  cfg.blockDim = dim3(32);
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, lm_sample_merge_kernel, a, (const RowPartial*)parts, (V + 127) / 128, tok_out,
+                                    logp_out, logz_out, pdl));
+  return 0;
 }
 
 SMC_API int smc_tp_link_size() { return (int)sizeof(smc::TpLink); }

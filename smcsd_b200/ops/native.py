@@ -242,6 +242,38 @@ def sample_or_score(logits: torch.Tensor, *, rows: int, V: int, splits: int, spl
                                      _stream()), "smc_sample_or_score")
 
 
+def lm_parts_bytes(rows: int, V: int) -> int:
+    L = lib()
+    L.smc_lm_parts_bytes.argtypes = [C.c_int, C.c_int]
+    L.smc_lm_parts_bytes.restype = C.c_int
+    return L.smc_lm_parts_bytes(rows, V)
+
+
+def lm_head_sample(W: torch.Tensor, X: torch.Tensor, *, M: int, V: int, ldx: int, status: torch.Tensor,
+                   temperature: float, alpha: float, softcap: float, tokens_in: Optional[torch.Tensor], seed: int,
+                   cycle_counter: torch.Tensor, call_id: int, parts: torch.Tensor, tok_out: torch.Tensor,
+                   logp_out: torch.Tensor, logz_out: Optional[torch.Tensor], ssq_in: Optional[torch.Tensor] = None,
+                   ssq_parts: int = 0, ssq_ld: int = 0, norm_d: int = 0, norm_eps: float = 0.0, ssq_mstride: int = 1,
+                   pdl: bool = False) -> None:
+    """lm_head GEMM whose epilogue samples / scores every row straight out of tensor memory (the logits are never
+    stored) followed by the per-row merge of the vocabulary slabs.  W [rows >= V, K] bf16; X rows of pitch ``ldx``."""
+    L = lib()
+    if not getattr(L, "_lmhs_declared", False):
+        vp, i, f, ull = C.c_void_p, C.c_int, C.c_float, C.c_ulonglong
+        L.smc_lm_head_sample.argtypes = [vp, vp, i, i, i, i, vp, i, vp, i, i, i, f, i, f, f, f, vp, ull, vp, i, vp, vp,
+                                         vp, vp, vp]
+        L.smc_lm_head_sample.restype = C.c_int
+        L._lmhs_declared = True
+    assert parts.numel() * parts.element_size() >= lm_parts_bytes(M, V)
+    _check(L.smc_lm_head_sample(_p(W), _p(X), V, W.shape[1], M, ldx, _p(status), int(pdl), _p(ssq_in), ssq_parts,
+                                ssq_ld, norm_d, norm_eps, ssq_mstride, temperature, alpha, softcap, _p(tokens_in),
+                                seed & 0xFFFFFFFFFFFFFFFF, _p(cycle_counter), call_id, _p(parts), _p(tok_out),
+                                _p(logp_out), _p(logz_out), _stream()), "smc_lm_head_sample")
+
+
+_KERNELS_PER_CALL["smc_lm_head_sample"] = 2
+
+
 # ----------------------------------------------------------------------------- SMC state
 class SlotArrays(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("seq_lens", "verified_ids", "prev_ids", "token_counts", "finished",

@@ -61,6 +61,7 @@ class NativeLlama:
         if not self.fuse_swiglu:
             self.gu = torch.empty(max_tokens, 2 * self.ffn, dtype=f32, device=dev)
         self._splits_cache: Dict = {}
+        self._lm_parts = None                # per-(row, vocabulary slab) partials of the fused lm_head sampler
         # RMSNorm folded into the GEMMs: consumers read the raw bf16 residual stream ``hb`` and scale by 1/rms in
         # their epilogue; residual GEMMs emit ``hb`` and per-slab sums of squares.  Five launches per layer.
         self.fold = self.fuse_swiglu and model.tp_size == 1 and _env_flag("SMC_FOLD_NORM", True)
@@ -181,6 +182,27 @@ class NativeLlama:
         if s is None:
             s = self._splits_cache[key] = K.gemm_swiglu_splits(2 * self.ffn, self.d, M)
         return s
+
+    def lm_head_sample(self, rows: int, row_offset: int, row_step: int, *, temperature: float, alpha: float,
+                       tokens_in, seed: int, cycle_counter, call_id: int, tok_out, logp_out, logz_out) -> None:
+        """lm_head over the final hidden rows ``row_offset + i * row_step`` with sampling / scoring done in the GEMM
+        epilogue: the [rows, V] logits never reach memory (what the reference does with an all-gathered logits
+        tensor plus two sampling kernels: smcsd/core/worker.py:684-707, smcsd/core/kernels/fused_sampling.py:42-214)."""
+        V = self.c.vocab_size
+        if self._lm_parts is None or self._lm_parts.numel() < K.lm_parts_bytes(rows, V):
+            self._lm_parts = torch.empty(K.lm_parts_bytes(max(rows, self.logits.shape[0]), V), dtype=torch.uint8,
+                                         device=self.h.device)
+        kw = {}
+        if self.fold:
+            X = self.hb[row_offset:]
+            kw = dict(ssq_in=self.ssq[:, row_offset:], ssq_parts=self.n_parts, ssq_ld=self.ssq.stride(0), norm_d=self.d,
+                      norm_eps=self.c.rms_eps, ssq_mstride=row_step)
+        else:
+            X = self.xn[row_offset:]
+        K.lm_head_sample(self.m.lm_head, X, M=rows, V=V, ldx=self.d * row_step, status=self.status,
+                         temperature=temperature, alpha=alpha, softcap=float(self.c.logit_softcap), tokens_in=tokens_in,
+                         seed=seed, cycle_counter=cycle_counter, call_id=call_id, parts=self._lm_parts, tok_out=tok_out,
+                         logp_out=logp_out, logz_out=logz_out, pdl=self.pdl, **kw)
 
     def lm_head(self, rows: int, row_offset: int = 0, row_step: int = 1) -> torch.Tensor:
         """fp32 logits [rows, V] of the final hidden rows ``row_offset + i * row_step``."""
@@ -334,6 +356,7 @@ class NativeRunner:
         self.fused_write_back = bool(a.fused_write_back)
         self.fast_verify = bool(a.fast_verify)
         self.draft_phase_graph = bool(a.draft_phase_graph)
+        self.fused_lm_head = _env_flag("SMC_FUSED_LM_HEAD", True)     # sampling inside the lm_head epilogue (A/B knob)
         self.switched_off = not (self.fused_sampling and self.fused_write_back and self.fast_verify)
         if self.switched_off or _env_flag("SMC_DEFER_BONUS_EAGER", False):
             if self.use_graph:
@@ -568,6 +591,12 @@ class NativeRunner:
             self._verify_torch(nm, ids, pos, locs, rows, prefix, bs, E)
         else:
             nm.forward(ids, pos, locs, rows, prefix, bs, E)
+            if lm_rows > 0 and self.fused_sampling and self.fused_lm_head and type(nm) is NativeLlama and lm_rows <= 256:
+                # sampling / scoring inside the lm_head epilogue: no logits in memory, one merge launch
+                nm.lm_head_sample(lm_rows, lm_off, lm_step, temperature=temperature, alpha=alpha, tokens_in=tokens_in,
+                                  seed=self.seed, cycle_counter=self._counters, call_id=call_id, tok_out=tok_out,
+                                  logp_out=logp_out, logz_out=logz_out)
+                return
             if lm_rows > 0:
                 nm.lm_head(lm_rows, row_offset=lm_off, row_step=lm_step)
         if lm_rows > 0:

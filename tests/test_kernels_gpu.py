@@ -432,3 +432,38 @@ def test_gemm_with_folded_rmsnorm(d, ffn, M):
     ref = xn[1::2][:rows] @ Wq.float().t()
     assert int(st) == 0
     assert (q - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
+
+
+# ------------------------------------------------------------------------------- lm_head fused with sampling
+@pytest.mark.parametrize("V,d,M,step", [(128256, 2048, 8, 1), (128256, 4096, 72, 1), (1000, 256, 8, 2), (8192, 512, 130, 1)])
+def test_lm_head_sampling_epilogue_matches_sampler_on_stored_logits(V, d, M, step):
+    """Sampling / scoring inside the lm_head epilogue against the stand-alone sampler run on the stored logits of the
+    same GEMM (same noise stream): same tokens, same log-probabilities; and against fp32 PyTorch for the scored rows."""
+    K = _K()
+    torch.manual_seed(4)
+    W = (torch.randn(V, d, device="cuda") * 0.05).bfloat16()
+    X = torch.randn(M * step, d, device="cuda").bfloat16()
+    st = _status()
+    logits = torch.zeros(M, V, device="cuda")
+    K.gemm_skinny(W, X[step - 1:], logits, M=M, splits=1, epi=K.EPI_STORE_F32, ldx=d * step, ldo=V, status=st)
+    tokens_in = torch.full((M,), -1, dtype=torch.int32, device="cuda")
+    tokens_in[::2] = torch.randint(0, V, (tokens_in[::2].numel(),), device="cuda", dtype=torch.int32)
+    counters = torch.tensor([3, 0, 0, 0], dtype=torch.int64, device="cuda")
+    T, alpha = 0.7, 1.4
+    tok_a, lp_a, lz_a = _sample(K, logits, T, alpha, tokens_in, seed=99, counter=3, call_id=2)
+    parts = torch.empty(K.lm_parts_bytes(M, V), dtype=torch.uint8, device="cuda")
+    tok_b = torch.zeros(M, dtype=torch.int32, device="cuda")
+    lp_b = torch.zeros(M, device="cuda")
+    lz_b = torch.zeros(M, device="cuda")
+    K.lm_head_sample(W, X[step - 1:], M=M, V=V, ldx=d * step, status=st, temperature=T, alpha=alpha, softcap=0.0,
+                     tokens_in=tokens_in, seed=99, cycle_counter=counters, call_id=2, parts=parts, tok_out=tok_b,
+                     logp_out=lp_b, logz_out=lz_b)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    assert torch.equal(tok_a, tok_b)
+    assert (lp_a - lp_b).abs().max().item() < 2e-3
+    assert (lz_a - lz_b).abs().max().item() < 2e-3
+    ref = torch.log_softmax(X[step - 1::step].float() @ W.float().t() / T, dim=-1)
+    sc = tokens_in >= 0
+    got_ref = ref[torch.arange(M, device="cuda")[sc], tokens_in[sc].long()]
+    assert (lp_b[sc] - got_ref).abs().max().item() < 5e-3
