@@ -43,6 +43,14 @@ struct FusedAttnParams {
   float scale;
   int* status;
   int pdl;
+  // Shared-prefix ("cascade") passes.  A group pass serves the query rows of several sequences that share a prompt
+  // from one stream of its keys (rotated queries in q_in, keys [0, prefix), no causal limit) and parks the
+  // unnormalised state per (token, head) in part_out; the per-sequence pass then starts at key_begin[b] and folds
+  // that state in (part_in) before it normalises.  State row: D values, running max, running sum.
+  const int* key_begin;      // [bs] or null: first key of this sequence served by this launch
+  float* part_out;           // [T, Hq, D + 2] or null
+  const float* part_in;      // [T, Hq, D + 2] or null
+  int causal;                // 0: every key of the range is visible to every query row
 };
 
 constexpr int RANGE = 2048;     // page ids staged per pass
@@ -77,10 +85,11 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   const int g = lane >> 2, t = lane & 3;
 
   // ---- key range of this CTA and the first K/V fetch (runs under the new-token work below) -----------
-  const int n_keys = pool_only ? prefix + p.E : prefix;     // keys served from the paged cache
-  int per = (n_keys + p.KS - 1) / p.KS;
+  const int n_keys = (pool_only && p.causal) ? prefix + p.E : prefix;     // keys served from the paged cache
+  const int kbeg = p.key_begin != nullptr ? max(0, min(p.key_begin[b], n_keys)) : 0;
+  int per = (n_keys - kbeg + p.KS - 1) / p.KS;
   per = (per + TK - 1) / TK * TK;
-  const int kb = ks * per, ke = min(n_keys, kb + per);
+  const int kb = kbeg + ks * per, ke = min(n_keys, kb + per);
   const int* bt = p.block_table + (size_t)p.rows[b] * p.bt_stride;
   const int gsize = 32 * n_mt, gt = mt * 32 + lane;   // thread index inside this key-way's group
   const int stg = p.stg;
@@ -295,8 +304,9 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       const int nvalid = min(TK, r1 - r0 - tile * TK);
       const __nv_bfloat16* Kt = my_tiles + (size_t)(j % stg) * 2 * TILE;
       const int key0 = r0 + tile * TK;
-      process_tile<D, TK / 8, Q_REGS>(Kt, Kt + TILE, qa, Qs_mt, p.scale, st, nvalid, prefix + e_row0 - key0,
-                                      prefix + e_row1 - key0);
+      process_tile<D, TK / 8, Q_REGS>(Kt, Kt + TILE, qa, Qs_mt, p.scale, st, nvalid,
+                                      p.causal ? prefix + e_row0 - key0 : 0x3fffffff,
+                                      p.causal ? prefix + e_row1 - key0 : 0x3fffffff);
     }
   }
   cp_async_wait<0>();
@@ -396,13 +406,40 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       const int r = mt * 16 + g + 8 * hrow;
       if (r >= R) continue;
       const int e = r / G, gq = r % G, tkn = b * p.E + e, head = hbase + gq;
-      const float l = hrow ? st.l1 : st.l0;
+      float m = hrow ? st.m1 : st.m0, l = hrow ? st.l1 : st.l0;
+      float a_self = 1.f, a_in = 0.f;
+      const float* sin_row = nullptr;
+      if (p.part_in != nullptr) {
+        // fold in the state a group pass left for this (token, head): flash-decoding merge of two partial softmaxes
+        sin_row = p.part_in + ((size_t)tkn * p.Hq + head) * (D + 2);
+        const float m_in = sin_row[D], l_in = sin_row[D + 1];
+        const float M = fmaxf(m, m_in);
+        a_self = M == -INFINITY ? 1.f : __expf(m - M);
+        a_in = M == -INFINITY ? 0.f : __expf(m_in - M);
+        l = l * a_self + l_in * a_in;
+        m = M;
+      }
+      if (p.part_out != nullptr) {
+        float* so = p.part_out + ((size_t)tkn * p.Hq + head) * (D + 2);
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt)
+          *reinterpret_cast<float2*>(so + nt * 8 + 2 * t) = make_float2(st.o[nt][2 * hrow], st.o[nt][2 * hrow + 1]);
+        if (t == 0) { so[D] = m; so[D + 1] = l; }
+        continue;
+      }
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* orow = p.out + ((size_t)tkn * p.Hq + head) * D;
       const float* grow = p.gate_off >= 0 ? p.qkv + (size_t)tkn * p.ld_qkv + p.gate_off + (size_t)head * D : nullptr;
 #pragma unroll
       for (int nt = 0; nt < D / 8; ++nt) {
-        float v0 = st.o[nt][2 * hrow] * inv, v1 = st.o[nt][2 * hrow + 1] * inv;
+        float v0 = st.o[nt][2 * hrow] * a_self, v1 = st.o[nt][2 * hrow + 1] * a_self;
+        if (sin_row != nullptr) {
+          const float2 x = *reinterpret_cast<const float2*>(sin_row + nt * 8 + 2 * t);
+          v0 += x.x * a_in;
+          v1 += x.y * a_in;
+        }
+        v0 *= inv;
+        v1 *= inv;
         if (grow != nullptr) {
           const float2 gg = *reinterpret_cast<const float2*>(grow + nt * 8 + 2 * t);
           v0 *= 1.f / (1.f + __expf(-gg.x));
@@ -471,17 +508,46 @@ SMC_API int smc_attention_kv_splits(int bs, int E, int Hq, int Hkv, int D, int c
 // at k_off, value heads at v_off.  out: bf16 [T, Hq*D].  KS in {1, 2, 4, 8} key-range splits per
 // (sequence, kv head) run as one thread-block cluster and are merged through distributed shared memory;
 // part_acc / part_ml are ignored (kept so existing callers need not change).
+SMC_API int smc_attention_fused_ex(const float* qkv, const void* q_in, int ld_qkv, int q_off, int gate_off, int k_off,
+                                   int v_off, const int* positions, const int* cache_locs, const float* rope, int rd,
+                                   int max_pos, const void* qn_w, const void* kn_w, float norm_eps, int norm_plus_one,
+                                   void* k_pool, void* v_pool, int n_pages, const int* block_table, int bt_stride,
+                                   const int* rows, const int* prefix_lens, void* out, int bs, int E, int Hq, int Hkv,
+                                   int D, int KS, float scale, int* status, int pdl, const int* key_begin,
+                                   float* part_out, const float* part_in, int causal, cudaStream_t st);
+
 SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, int q_off, int gate_off, int k_off, int v_off,
                                 const int* positions, const int* cache_locs, const float* rope, int rd, int max_pos,
                                 const void* qn_w, const void* kn_w, float norm_eps, int norm_plus_one, void* k_pool,
                                 void* v_pool, int n_pages, const int* block_table, int bt_stride, const int* rows,
                                 const int* prefix_lens, void* out, float* part_acc, float* part_ml, int bs, int E,
                                 int Hq, int Hkv, int D, int KS, float scale, int* status, int pdl, cudaStream_t st) {
+  (void)part_acc;
+  (void)part_ml;
+  return smc_attention_fused_ex(qkv, q_in, ld_qkv, q_off, gate_off, k_off, v_off, positions, cache_locs, rope, rd, max_pos,
+                                qn_w, kn_w, norm_eps, norm_plus_one, k_pool, v_pool, n_pages, block_table, bt_stride, rows,
+                                prefix_lens, out, bs, E, Hq, Hkv, D, KS, scale, status, pdl, nullptr, nullptr, nullptr, 1,
+                                st);
+}
+
+// Same, with the shared-prefix options: key_begin [bs] (first key served), part_out / part_in [T, Hq, D + 2] fp32
+// (unnormalised attention state parked by a group pass / folded in by the per-sequence pass), causal (0: no limit).
+// A group pass takes rotated queries (q_in), may span more than 16 tokens per "sequence" (E * Hq / Hkv <= 128 query
+// rows) and keeps all query heads of a kv head in one CTA so that its keys are streamed once.
+SMC_API int smc_attention_fused_ex(const float* qkv, const void* q_in, int ld_qkv, int q_off, int gate_off, int k_off,
+                                   int v_off, const int* positions, const int* cache_locs, const float* rope, int rd,
+                                   int max_pos, const void* qn_w, const void* kn_w, float norm_eps, int norm_plus_one,
+                                   void* k_pool, void* v_pool, int n_pages, const int* block_table, int bt_stride,
+                                   const int* rows, const int* prefix_lens, void* out, int bs, int E, int Hq, int Hkv,
+                                   int D, int KS, float scale, int* status, int pdl, const int* key_begin,
+                                   float* part_out, const float* part_in, int causal, cudaStream_t st) {
   using namespace smc;
   if (bs <= 0) return 0;
-  if (Hq % Hkv || E < 1 || E > 16 || (rd & 1) || rd > D) return -70;
+  if (Hq % Hkv || E < 1 || (rd & 1) || rd > D) return -70;
+  if (E > 16 && (q_in == nullptr || E * (Hq / Hkv) > 128)) return -70;
+  if (!causal && q_in == nullptr) return -74;
   if (!(KS == 1 || KS == 2 || KS == 4 || KS == 8)) return -73;
-  const int gsub = pick_head_groups(E, Hq / Hkv, (long long)bs * Hkv);
+  const int gsub = part_out != nullptr ? 1 : pick_head_groups(E, Hq / Hkv, (long long)bs * Hkv);
   const int G = Hq / Hkv / gsub, R = E * G;
   const int n_mt = (R + 15) / 16;
   if (n_mt > 8) return -71;
@@ -501,6 +567,7 @@ SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, 
   p.out = (__nv_bfloat16*)out;
   p.E = E; p.Hq = Hq; p.Hkv = Hkv; p.KS = KS; p.gsub = gsub; p.n_mt = n_mt; p.n_kw = n_kw; p.stg = stg; p.scale = scale; p.status = status;
   p.pdl = pdl;
+  p.key_begin = key_begin; p.part_out = part_out; p.part_in = part_in; p.causal = causal ? 1 : 0;
   const size_t smem = fused_smem_bytes(D, n_mt, n_kw, stg);
   void (*kern)(const FusedAttnParams) = nullptr;
   if (D == 64) kern = attn_fused_kernel<64>;

@@ -52,9 +52,9 @@ def _declare(L) -> None:
     L.smc_gemm_skinny_norm.restype = C.c_int
     L.smc_rope_kv_write.argtypes = [vp, i, ll, vp, vp, vp, i, i, vp, vp, vp, i, i, i, i, i, vp, i, vp]
     L.smc_swiglu_partials.argtypes = [vp, i, ll, vp, i, i, i, i, i, vp]
-    L.smc_attention_fused.argtypes = [vp, vp, i, i, i, i, i, vp, vp, vp, i, i, vp, vp, f, i, vp, vp, i, vp, i, vp, vp, vp,
-                                      vp, vp, i, i, i, i, i, i, f, vp, i, vp]
-    L.smc_attention_fused.restype = C.c_int
+    L.smc_attention_fused_ex.argtypes = [vp, vp, i, i, i, i, i, vp, vp, vp, i, i, vp, vp, f, i, vp, vp, i, vp, i, vp, vp,
+                                         vp, i, i, i, i, i, i, f, vp, i, vp, vp, vp, i, vp]
+    L.smc_attention_fused_ex.restype = C.c_int
     L.smc_sample_scratch_bytes.argtypes = [i, i]
     L.smc_sample_or_score.argtypes = [vp, i, ll, ll, i, i, f, f, f, vp, ull, vp, i, vp, i, vp, vp, vp, i, vp]
     L.smc_slot_arrays_size.argtypes = []
@@ -199,20 +199,26 @@ def swiglu_partials(partials: torch.Tensor, splits: int, split_stride: int, act:
 
 def attention_fused(qkv: torch.Tensor, positions: torch.Tensor, cache_locs: torch.Tensor, rope: torch.Tensor,
                     k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, rows: torch.Tensor,
-                    prefix_lens: torch.Tensor, out: torch.Tensor, part_acc: torch.Tensor, part_ml: torch.Tensor, *,
+                    prefix_lens: torch.Tensor, out: Optional[torch.Tensor], part_acc: Optional[torch.Tensor] = None,
+                    part_ml: Optional[torch.Tensor] = None, *,
                     bs: int, E: int, Hq: int, Hkv: int, D: int, KS: int, scale: float, status: torch.Tensor,
                     q_off: int = 0, gate_off: int = -1, k_off: Optional[int] = None, v_off: Optional[int] = None,
                     qn_w: Optional[torch.Tensor] = None, kn_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6,
-                    norm_plus_one: bool = False, pdl: bool = False, q_in: Optional[torch.Tensor] = None) -> None:
-    """Norm/rope/KV-write of the new tokens + paged causal attention + split merge, one launch per layer."""
+                    norm_plus_one: bool = False, pdl: bool = False, q_in: Optional[torch.Tensor] = None,
+                    key_begin: Optional[torch.Tensor] = None, part_out: Optional[torch.Tensor] = None,
+                    part_in: Optional[torch.Tensor] = None, causal: bool = True) -> None:
+    """Norm/rope/KV-write of the new tokens + paged causal attention + split merge, one launch per layer.
+    Shared-prefix passes: ``causal=False`` with ``q_in`` and ``part_out`` serves the rows of several sequences from
+    one stream of their common keys and parks the unnormalised state; ``key_begin`` / ``part_in`` make the
+    per-sequence launch start after those keys and fold the state in.  (``part_acc`` / ``part_ml`` are ignored.)"""
     k_off = Hq * D if k_off is None else k_off
     v_off = k_off + Hkv * D if v_off is None else v_off
-    _check(lib().smc_attention_fused(_p(qkv), _p(q_in), qkv.stride(0), q_off, gate_off, k_off, v_off, _p(positions),
-                                     _p(cache_locs), _p(rope), rope.shape[1], rope.shape[0], _p(qn_w), _p(kn_w),
-                                     norm_eps, int(norm_plus_one), _p(k_pool), _p(v_pool), k_pool.shape[0] - 1,
-                                     _p(block_table), block_table.stride(0), _p(rows), _p(prefix_lens), _p(out),
-                                     _p(part_acc), _p(part_ml), bs, E, Hq, Hkv, D, KS, scale, _p(status), int(pdl),
-                                     _stream()), "smc_attention_fused")
+    _check(lib().smc_attention_fused_ex(_p(qkv), _p(q_in), qkv.stride(0), q_off, gate_off, k_off, v_off, _p(positions),
+                                        _p(cache_locs), _p(rope), rope.shape[1], rope.shape[0], _p(qn_w), _p(kn_w),
+                                        norm_eps, int(norm_plus_one), _p(k_pool), _p(v_pool), k_pool.shape[0] - 1,
+                                        _p(block_table), block_table.stride(0), _p(rows), _p(prefix_lens), _p(out),
+                                        bs, E, Hq, Hkv, D, KS, scale, _p(status), int(pdl), _p(key_begin),
+                                        _p(part_out), _p(part_in), int(causal), _stream()), "smc_attention_fused")
 
 
 def attn_kv_splits(ctx: int, bs: int, Hkv: int, E: int = 1, G: int = 4, D: int = 128) -> int:

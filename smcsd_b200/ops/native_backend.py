@@ -62,6 +62,11 @@ class NativeLlama:
             self.gu = torch.empty(max_tokens, 2 * self.ffn, dtype=f32, device=dev)
         self._splits_cache: Dict = {}
         self._lm_parts = None                # per-(row, vocabulary slab) partials of the fused lm_head sampler
+        # shared-prefix attention: parked state per (token, head) and, filled by the runner when the batch changes,
+        # the per-sequence shared lengths and the block-table rows / shared lengths of every NP-th sequence
+        self.att_state = torch.zeros(max_tokens, self.nq, self.D + 2, dtype=f32, device=dev)
+        self.cascade_bufs = None
+        self._cascade: Dict = {}
         # RMSNorm folded into the GEMMs: consumers read the raw bf16 residual stream ``hb`` and scale by 1/rms in
         # their epilogue; residual GEMMs emit ``hb`` and per-slab sums of squares.  Five launches per layer.
         self.fold = self.fuse_swiglu and model.tp_size == 1 and _env_flag("SMC_FOLD_NORM", True)
@@ -83,14 +88,7 @@ class NativeLlama:
             K.gemm_skinny_norm(L.wqkv, self.hb, self.qkv, M=T, splits=self._splits(self.nqkv, self.d, T),
                                epi=K.EPI_STORE_F32, ldo=self.qkv.stride(0), status=self.status, ssq_in=self.ssq,
                                ssq_parts=parts, norm_d=self.d, norm_eps=c.rms_eps, ssq_ld=ld, pdl=pdl)
-            q_in = None
-            if two_pass:
-                K.rope_kv_write(self.qkv, 1, 0, positions, cache_locs, m.rope, self.q, self.kv.k[li], self.kv.v[li],
-                                M=T, Hq=self.nq, Hkv=self.nkv, D=self.D, status=self.status, pdl=pdl)
-                q_in = self.q
-            K.attention_fused(self.qkv, positions, cache_locs, m.rope, self.kv.k[li], self.kv.v[li], self.bt, rows,
-                              prefix_lens, self.attn, self.part_acc, self.part_ml, bs=bs, E=E, Hq=self.nq,
-                              Hkv=self.nkv, D=self.D, KS=self._ks(bs, E), scale=scale, status=self.status, pdl=pdl, q_in=q_in)
+            self._attention(li, positions, cache_locs, rows, prefix_lens, bs, E, two_pass, scale)
             K.gemm_skinny_norm(L.wo, self.attn, self.h, M=T, splits=self._splits(self.d, self.nq * self.D, T),
                                epi=K.EPI_RESID_F32, ldo=self.d, status=self.status, ssq_out=self.ssq, hb_out=self.hb,
                                ssq_ld=ld, pdl=pdl)
@@ -103,11 +101,79 @@ class NativeLlama:
                                ssq_ld=ld, pdl=pdl)
         return self.hb
 
+    def _attention(self, li: int, positions, cache_locs, rows, prefix_lens, bs: int, E: int, two_pass: bool,
+                   scale: float) -> None:
+        """Attention step of layer ``li``.  One fused launch (rope, KV write, attention) by default.  With a
+        shared-prefix plan (see ``set_prefix``) three launches: rope + KV write, one pass over the prompt keys for
+        several particles of a group at a time, then the per-particle pass over the remaining keys that folds the
+        parked state in (the reference describes this "cascade" for decode: docs/smc/performance.md:116-128)."""
+        m, pdl, T = self.m, self.pdl, bs * E
+        k, v = self.kv.k[li], self.kv.v[li]
+        plan = None if two_pass else self._cascade.get(E)
+        if plan is None or bs % plan["NP"] != 0:
+            q_in = None
+            if two_pass:
+                K.rope_kv_write(self.qkv, 1, 0, positions, cache_locs, m.rope, self.q, k, v, M=T, Hq=self.nq,
+                                Hkv=self.nkv, D=self.D, status=self.status, pdl=pdl)
+                q_in = self.q
+            K.attention_fused(self.qkv, positions, cache_locs, m.rope, k, v, self.bt, rows, prefix_lens, self.attn,
+                              bs=bs, E=E, Hq=self.nq, Hkv=self.nkv, D=self.D, KS=self._ks(bs, E), scale=scale,
+                              status=self.status, pdl=pdl, q_in=q_in)
+            return
+        NP, cb = plan["NP"], self.cascade_bufs
+        K.rope_kv_write(self.qkv, 1, 0, positions, cache_locs, m.rope, self.q, k, v, M=T, Hq=self.nq, Hkv=self.nkv,
+                        D=self.D, status=self.status, pdl=pdl)
+        K.attention_fused(self.qkv, positions, cache_locs, m.rope, k, v, self.bt, cb["rows_g"][NP], cb["shared_g"][NP],
+                          None, bs=bs // NP, E=NP * E, Hq=self.nq, Hkv=self.nkv, D=self.D, KS=plan["KSg"], scale=scale,
+                          status=self.status, pdl=pdl, q_in=self.q, part_out=self.att_state, causal=False)
+        K.attention_fused(self.qkv, positions, cache_locs, m.rope, k, v, self.bt, rows, prefix_lens, self.attn, bs=bs,
+                          E=E, Hq=self.nq, Hkv=self.nkv, D=self.D, KS=plan["KSs"], scale=scale, status=self.status,
+                          pdl=pdl, q_in=self.q, key_begin=cb["shared"], part_in=self.att_state)
+
     def set_context(self, ctx: int, bs: int, Es=(1, 2)) -> tuple:
         """Record the context-length hint for the attention key splits; returns the splits chosen for forwards of
         ``Es`` new tokens per sequence (part of a captured graph's identity: they fix the launch grids)."""
         self.ctx_hint = int(ctx)
         return tuple(self._ks(bs, E) for E in Es)
+
+    # Shortest shared prompt for which the extra two launches per layer pay off.  Measured on B200 (8 particles,
+    # 256 own tokens each): single-token steps 0.87x at 4k, 1.16x at 8k, 1.5x at 16k, 2.0x at 32k prompt tokens.  The
+    # verify shape (9 tokens x 4 heads per particle) is bound by the mma.sync issue rate, not by key traffic, and
+    # loses at every length (0.6-0.7x), so it keeps the single launch unless SMC_CASCADE_VERIFY=1.
+    CASCADE_MIN_PROMPT = 8192
+
+    def set_prefix(self, min_prompt: int, max_prompt: int, bs: int, n_particles: int, Es=(1, 2)) -> tuple:
+        """Plan the shared-prefix passes for forwards of ``Es`` new tokens per sequence: ``min_prompt`` / ``max_prompt``
+        bound the prompt lengths of the running groups (all particles of a group share the prompt's pages).  Returns
+        the plan's identity for the graph key (empty when the passes are off)."""
+        self._cascade = {}
+        thr = _env_int("SMC_CASCADE_MIN_PROMPT", self.CASCADE_MIN_PROMPT)
+        if self.cascade_bufs is None or min_prompt < thr or thr <= 0:
+            return ()
+        G = self.nq // self.nkv
+        key = []
+        verify_too = _env_flag("SMC_CASCADE_VERIFY", False)
+        for E in Es:
+            if E > 2 and not verify_too:
+                continue
+            NP = 0
+            for cand in (8, 4, 2):
+                if n_particles % cand == 0 and cand * E * G <= 128 and cand in self.cascade_bufs["rows_g"]:
+                    NP = cand
+                    break
+            if NP == 0:
+                continue
+            n_mt = (NP * E * G + 15) // 16
+            n_kw = max(1, 8 // n_mt)
+            base = (bs // NP) * self.nkv
+            ksg = 1
+            while ksg < 8 and base * ksg * 2 <= 148 and max_prompt // (ksg * 2 * 32 * n_kw) >= 2:
+                ksg *= 2
+            suffix = max(self.ctx_hint - min_prompt, 1)
+            kss = K.attn_kv_splits(suffix, bs, self.nkv, E, G, self.D)
+            self._cascade[E] = {"NP": NP, "KSg": ksg, "KSs": kss}
+            key.append((E, NP, ksg, kss))
+        return tuple(key)
 
     def _ks(self, bs: int, E: int) -> int:
         ks = K.attn_kv_splits(self.ctx_hint, bs, self.nkv, E, self.nq // self.nkv, self.D)
@@ -154,14 +220,7 @@ class NativeLlama:
         scale = self.D ** -0.5
         for li, L in enumerate(m.layers):
             self._gemm(L.wqkv, self.xn, self.qkv, T, K.EPI_STORE_F32)
-            q_in = None
-            if two_pass:
-                K.rope_kv_write(self.qkv, 1, 0, positions, cache_locs, m.rope, self.q, self.kv.k[li], self.kv.v[li],
-                                M=T, Hq=self.nq, Hkv=self.nkv, D=self.D, status=self.status, pdl=pdl)
-                q_in = self.q
-            K.attention_fused(self.qkv, positions, cache_locs, m.rope, self.kv.k[li], self.kv.v[li], self.bt, rows,
-                              prefix_lens, self.attn, self.part_acc, self.part_ml, bs=bs, E=E, Hq=self.nq,
-                              Hkv=self.nkv, D=self.D, KS=self._ks(bs, E), scale=scale, status=self.status, pdl=pdl, q_in=q_in)
+            self._attention(li, positions, cache_locs, rows, prefix_lens, bs, E, two_pass, scale)
             self._gemm(L.wo, self.attn, self.h, T, K.EPI_RESID_F32)
             K.add_rmsnorm(self.h, L.ln2, self.xn, M=T, d=self.d, eps=c.rms_eps, pdl=pdl)
             if self.fuse_swiglu:
@@ -252,6 +311,12 @@ class NativeState:
         self.bs = 0
         self.n_groups = 0
         self.fused_write_back = True
+        # shared-prefix attention inputs, rewritten when the batch changes: keys every particle of a group shares
+        # (its prompt minus one, so that the draft head's shorter prefix is covered as well), and for NP = 2, 4, 8 the
+        # block-table row and shared length of every NP-th sequence
+        self.shared = torch.zeros(max_bs, **i32)
+        self.rows_g = {n: torch.zeros(max(1, max_bs // n), **i32) for n in (2, 4, 8)}
+        self.shared_g = {n: torch.zeros(max(1, max_bs // n), **i32) for n in (2, 4, 8)}
 
     def bind(self, st) -> None:
         self._arrays = K.make_slot_arrays(st)
@@ -266,6 +331,12 @@ class NativeState:
         if self.bs:
             self.active[: self.bs].copy_(st.active_slots, non_blocking=True)
             self.active_rows[: self.n_groups].copy_(st.active_rows, non_blocking=True)
+            bs = self.bs
+            self.shared[:bs] = (st.prompt_lens[st.active_slots.long()] - 1).clamp_(min=0)
+            for n in (2, 4, 8):
+                if bs % n == 0:
+                    self.rows_g[n][: bs // n] = self.active[:bs:n]
+                    self.shared_g[n][: bs // n] = self.shared[:bs:n]
 
     # ---- SlotState hooks --------------------------------------------------------
     def prepare_cycle(self, st, slots) -> CycleInputs:
@@ -337,6 +408,9 @@ class NativeRunner:
                                  splits, pdl, sched.state_t)
         self.draft = self._wrap(sched.draft, sched.kv_d, sched.bt.table, self.max_bs * 2, self.max_bs, splits, pdl,
                                 sched.state_d)
+        for nm in (self.target, self.draft):
+            if type(nm) is NativeLlama:
+                nm.cascade_bufs = {"shared": nstate.shared, "rows_g": nstate.rows_g, "shared_g": nstate.shared_g}
         self.nchunks = 32
         rows = self.max_bs * self.G
         self.sample_scratch = torch.empty(K.sample_scratch_bytes(rows, self.nchunks), dtype=torch.uint8,
@@ -462,12 +536,16 @@ class NativeRunner:
         worker.io_bytes["h2d"] += ids_h.numel() * 9
         rows = pin(torch.tensor(rows_h, dtype=torch.int32))
         pref = pin(torch.tensor(pref_h, dtype=torch.int32))
-        # page of every (padded) token: the prompt's pages, scratch page 0 for the padding
-        locs = torch.zeros(T, dtype=torch.int32, device=dev)
+        # page of every (padded) token: the prompt's pages, scratch page 0 for the padding -- one gather for the batch
+        row_of = torch.zeros(T, dtype=torch.long)
+        col_of = torch.zeros(T, dtype=torch.long)
         t = 0
         for it, L, nb in zip(items, lens, n_blocks):
-            locs[t:t + L] = self.st.bt.table[it.row, :L]
+            row_of[t:t + L] = it.row
+            col_of[t:t + L] = torch.arange(L)
             t += nb * B
+        locs = torch.where(valid, self.st.bt.table[pin(row_of), pin(col_of)], torch.zeros((), dtype=torch.int32, device=dev))
+        worker.io_bytes["h2d"] += T * 16
         bs = sum(n_blocks)
         for nm in (tgt, drf):
             nm.set_context(max(lens), bs)
@@ -487,29 +565,75 @@ class NativeRunner:
         cb = max(1, self.PREFILL_MAX_TOKENS // B)            # blocks per pass
         last = torch.tensor(last_rows, dtype=torch.long, device=dev)
 
+        def grab(nm, idx):
+            """Final-layer rows ``idx`` of the chain's buffers: raw bf16 residual rows + their sums of squares when the
+            norm is folded into the lm_head, the normalised rows otherwise."""
+            if getattr(nm, "fold", False):
+                return {"x": nm.hb[idx], "ssq": nm.ssq[:, idx], "normed": nm.final_hidden(idx)}
+            return {"x": nm.final_hidden(idx), "ssq": None, "normed": nm.final_hidden(idx)}
+
         def run(nm, short: int, want_hidden: bool):
             if bs <= cb:
                 nm.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True, **seqs_for(nm, short))
-                return nm.final_hidden(last) if want_hidden else None
-            hid = [None] * len(items)
-            for c0 in range(0, bs, cb):
-                nb = min(cb, bs - c0)
-                tok = slice(c0 * B, (c0 + nb) * B)
-                nm.set_context(max(lens), nb)
-                nm.forward(ids[tok], pos[tok], locs[tok], rows[c0:c0 + nb], pref[c0:c0 + nb], nb, B, two_pass=True)
-                if want_hidden:
-                    for i, r in enumerate(last_rows):
-                        if tok.start <= r < tok.stop:
-                            hid[i] = nm.final_hidden(torch.tensor([r - tok.start], dtype=torch.long, device=dev))
-            return torch.cat(hid, 0) if want_hidden else None
-        logits = self.target.m.logits_torch(run(tgt, 0, True))
-        from ..smc import math as smc_math
-        x0, _, _ = smc_math.gumbel_sample(logits, self.T_target, self.alpha, generator=worker.gen_prefill)
+                parts = [grab(nm, last)] if want_hidden else []
+            else:
+                parts, order = [], []
+                for c0 in range(0, bs, cb):
+                    nb = min(cb, bs - c0)
+                    tok = slice(c0 * B, (c0 + nb) * B)
+                    nm.set_context(max(lens), nb)
+                    nm.forward(ids[tok], pos[tok], locs[tok], rows[c0:c0 + nb], pref[c0:c0 + nb], nb, B, two_pass=True)
+                    if want_hidden:
+                        here = [(i, r - tok.start) for i, r in enumerate(last_rows) if tok.start <= r < tok.stop]
+                        if here:
+                            order += [i for i, _ in here]
+                            parts.append(grab(nm, pin(torch.tensor([r for _, r in here], dtype=torch.long))))
+                if want_hidden and order != sorted(order):
+                    raise RuntimeError("prompt blocks are laid out in request order")
+            if not want_hidden:
+                return None
+            fold = parts[0]["ssq"] is not None
+            return {"n": len(items), "x": torch.cat([q["x"] for q in parts], 0),
+                    "ssq": torch.cat([q["ssq"] for q in parts], 1) if fold else None,
+                    "normed": lambda: torch.cat([q["normed"] for q in parts], 0)}
+        x0 = self._sample_x0(tgt, run(tgt, 0, True), worker)
         # a stateful draft under the deferred schedule stops one token short: the first head forward of the decode
         # loop advances its recurrent state through the last prompt token exactly once
         run(drf, 1 if self.defer else 0, False)
         worker.io_bytes["d2h"] += 4 * len(items)
         return x0.to(torch.int32)
+
+    def _sample_x0(self, nm, hidden, worker) -> torch.Tensor:
+        """x0 of every prompt: a draw from softmax(alpha * logits / T_target) of the last prompt token.  Dense chains
+        project and sample with the fused lm_head kernel (no logits in memory, noise keyed by the running count of
+        prefilled prompts); other targets project with PyTorch (reference: smcsd/core/worker.py:668-707)."""
+        n = hidden["n"]
+        if type(nm) is NativeLlama and self.fused_sampling and self.fused_lm_head and n <= 256:
+            dev = self.device
+            if getattr(self, "_x0_counter", None) is None:
+                self._x0_counter = torch.zeros(1, dtype=torch.int64, device=dev)
+                self._x0_done = 0
+            self._x0_counter.fill_(self._x0_done)
+            self._x0_done += n
+            tok = torch.zeros(n, dtype=torch.int32, device=dev)
+            lp = torch.zeros(n, dtype=torch.float32, device=dev)
+            V = nm.c.vocab_size
+            if nm._lm_parts is None or nm._lm_parts.numel() < K.lm_parts_bytes(n, V):
+                nm._lm_parts = torch.empty(K.lm_parts_bytes(max(n, 8), V), dtype=torch.uint8, device=dev)
+            kw = {}
+            if hidden["ssq"] is not None:
+                ssq = hidden["ssq"].contiguous()
+                kw = dict(ssq_in=ssq, ssq_parts=ssq.shape[0], ssq_ld=ssq.stride(0), norm_d=nm.d, norm_eps=nm.c.rms_eps)
+            X = hidden["x"].contiguous()
+            K.lm_head_sample(nm.m.lm_head, X, M=n, V=V, ldx=X.stride(0), status=self.status, temperature=self.T_target,
+                             alpha=self.alpha, softcap=float(nm.c.logit_softcap), tokens_in=None,
+                             seed=self.seed ^ 0x5EED, cycle_counter=self._x0_counter, call_id=4096, parts=nm._lm_parts,
+                             tok_out=tok, logp_out=lp, logz_out=None, **kw)
+            return tok
+        from ..smc import math as smc_math
+        logits = self.target.m.logits_torch(hidden["normed"]())
+        x0, _, _ = smc_math.gumbel_sample(logits, self.T_target, self.alpha, generator=worker.gen_prefill)
+        return x0
 
     # ---- the cycle, as a sequence of kernel launches ---------------------------------
     def _sample_torch(self, nm, rows: int, temperature: float, alpha: float, tokens_in, tok_out, logp_out,
@@ -650,6 +774,7 @@ class NativeRunner:
         ctx = int(cin.orig_seq_lens.max().item()) + self.G if cin.orig_seq_lens.numel() else 0
         self.target.set_context(ctx, ns.bs, (self.G,))
         self.draft.set_context(ctx, ns.bs, (1, 2))
+        self._plan_prefix(st, ns.bs, None)          # the step-by-step path keeps the single-launch attention
         if self.draft_phase_graph and not self.switched_off and ns.bs <= self.graph_max_bs:
             # draft-only graph (SMC_DRAFT_PHASE_GRAPH): the gamma draft forwards and their sampling replay as one
             # launch, verify and scoring stay eager.  The draft part only reads the buffers the prologue kernel filled
@@ -692,10 +817,20 @@ class NativeRunner:
         ns.write_back_native(st, self.alpha)
         ns.collect_and_resample(st)
 
-    def run_cycle(self, st, worker, ctx_hint: int = 0) -> None:
+    def _plan_prefix(self, st, bs: int, prompt_hint) -> tuple:
+        """Shared-prefix attention plans of both models for this cycle (part of the graph key)."""
+        lo, hi = prompt_hint if prompt_hint else (0, 0)
+        key = ()
+        for nm, Es in ((self.target, (self.G,)), (self.draft, (1, 2))):
+            if type(nm) is NativeLlama:
+                key += (nm.set_prefix(int(lo), int(hi), bs, st.N, Es),)
+        return key
+
+    def run_cycle(self, st, worker, ctx_hint: int = 0, prompt_hint=None) -> None:
         """One decode cycle.  ``ctx_hint``: upper bound of the sequence lengths this cycle reaches (known on the host
         from prompt lengths and cycle counts); it selects how many key ranges the attention steps split into, and
-        with it which captured graph runs."""
+        with it which captured graph runs.  ``prompt_hint``: (shortest, longest) prompt among the running groups; long
+        shared prompts switch the attention steps to their shared-prefix passes."""
         ns = self.ns
         if ns._arrays is None:
             ns.bind(st)
@@ -707,6 +842,7 @@ class NativeRunner:
             key += (self.pf_target.set_context(ctx_hint, bs, (self.G,)),)
         if self._use_pf("draft", bs * 2):
             key += (self.pf_draft.set_context(ctx_hint, bs, (1, 2)),)
+        key += self._plan_prefix(st, bs, prompt_hint)
         if not self.use_graph or bs > self.graph_max_bs or ctx_hint > self.graph_max_context:
             self._full_cycle(st)           # same kernels, launched one by one (beyond the capture caps)
             return

@@ -358,9 +358,11 @@ class SMCScheduler:
         if self.native_runner is not None and self.native_runner.can_run_cycle(st):
             G = self.args.gamma + 1
             ctx = max((len(g.req.input_ids) + 1 + (g.launched + 1) * G for g in self.running.values()), default=0)
+            plens = [len(g.req.input_ids) for g in self.running.values()]
             # graph replays bypass module hooks, so the span is labelled here for profiler traces
             with profiling.span(f"step[DECODE smc-cycle groups={len(self.running)} ctx<={ctx}]"):
-                self.native_runner.run_cycle(st, self.worker, ctx_hint=ctx)   # one captured graph: prologue..resample
+                self.native_runner.run_cycle(st, self.worker, ctx_hint=ctx,   # one captured graph: prologue..resample
+                                             prompt_hint=(min(plens), max(plens)) if plens else None)
         else:
             cin = st.prepare_cycle()
             out = self.worker.decode_cycle(cin)
@@ -552,6 +554,51 @@ class SMCScheduler:
             self._profile_steps_left = None
         else:
             self._profile_steps_left -= 1
+
+    def score_tokens(self, input_ids: List[int], continuation: List[int], temperature: float = 1.0) -> List[float]:
+        """Diagnostic RPC: log softmax(logits / T)[continuation[i + 1]] at position i of ``continuation`` appended to
+        the prompt, computed by the engine's own target path (prompt pass, then one verify-shaped pass of up to 16
+        tokens: the kernel chain, tensor-parallel or not, with the fused scorer).  Gives tests a logit-level quantity
+        that must agree between parallel layouts.  Only for an idle scheduler."""
+        if self.running or self.waiting or self.pending:
+            raise RuntimeError("score_tokens needs an idle scheduler")
+        from .worker import PrefillItem
+        E, L = len(continuation), len(input_ids)
+        if not (2 <= E <= 16):
+            raise ValueError("continuation must hold 2..16 tokens")
+        dev = self.device
+        row = self.bt.alloc_parent_row()
+        pages = self.alloc.alloc(L + E)
+        self.bt.table[row, :L + E] = pages
+        try:
+            self.worker.prefill([PrefillItem(row, list(input_ids))])
+            ids = torch.tensor(continuation, dtype=torch.int32, device=dev)
+            pos = torch.arange(L, L + E, dtype=torch.int32, device=dev)
+            locs = pages[L:L + E].to(torch.int32).contiguous()
+            rows = torch.tensor([row], dtype=torch.int32, device=dev)
+            pref = torch.tensor([L], dtype=torch.int32, device=dev)
+            given = torch.tensor(list(continuation[1:]) + [0], dtype=torch.int32, device=dev)
+            if self.native_runner is not None:
+                r = self.native_runner
+                tok = torch.zeros(E, dtype=torch.int32, device=dev)
+                lp = torch.zeros(E, dtype=torch.float32, device=dev)
+                r._counters = self.state.counters
+                r.target.set_context(L + E, 1, (E,))
+                r._model_step("target", ids, pos, locs, rows, pref, 1, E, lm_rows=E, call_id=0,
+                              temperature=float(temperature), alpha=1.0, tokens_in=given, tok_out=tok, logp_out=lp)
+                out = lp[:E - 1].tolist()
+                if r.check_status() != 0:
+                    raise RuntimeError(f"device status {r.check_status()}")
+            else:
+                from ..models.layers import ExtendBatch
+                ext = ExtendBatch(ids.long(), pos.long(), locs, rows, pref, extend_len=E, prefix_lens_host=[L])
+                logits = self.target.logits_torch(self.target.forward_torch(ext, self.kv_t, self.bt.table))
+                lsm = torch.log_softmax(logits.float() / float(temperature), dim=-1)
+                out = lsm[torch.arange(E - 1, device=dev), given[:E - 1].long()].tolist()
+        finally:
+            self.alloc.free(pages)
+            self.bt.free_parent_row(row)
+        return out
 
     def handle_rpc(self, req: RpcReq) -> RpcResp:
         try:

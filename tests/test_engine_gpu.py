@@ -280,3 +280,40 @@ def test_attention_split_cap_is_honoured():
     nm2 = eng2._sched.native_runner.target
     nm2.set_context(1800, 4, (5,))
     assert nm2._ks(4, 5) >= 2
+
+
+def test_score_tokens_rpc_native_matches_pytorch():
+    """The diagnostic scoring RPC (prompt pass + one verify-shaped pass + fused scorer) against the PyTorch model."""
+    prompt, cont = _prompts(1, L=50, seed=12)[0], _prompts(1, L=10, seed=13)[0]
+    a = _engine(backend="native")._sched.score_tokens(prompt, cont, 0.7)
+    b = _engine(backend="torch")._sched.score_tokens(prompt, cont, 0.7)
+    assert len(a) == len(b) == 9
+    assert max(abs(x - y) for x, y in zip(a, b)) < 0.05, (a, b)
+
+
+def test_shared_prefix_attention_in_the_decode_cycle(monkeypatch):
+    """The shared-prefix passes forced on for short prompts (draft steps: 4 particles per group pass, verify: 2).
+    With draft == target every log-weight increment must stay ~0, which it only does if the single-token, two-token
+    and verify attention paths all compute the same softmax; and the graph replays match the eager launches."""
+    from smcsd_b200.config import EngineArgs
+    from smcsd_b200.io_types import GenerateRequest, ParticleOutput, SamplingParams
+    from smcsd_b200.models import build_model
+    from smcsd_b200.runtime.scheduler import SMCScheduler
+    monkeypatch.setenv("SMC_CASCADE_MIN_PROMPT", "32")
+    monkeypatch.setenv("SMC_CASCADE_VERIFY", "1")
+    tgt, _ = _cfgs()
+    model = build_model(tgt, torch.bfloat16, "cuda", seed=0)
+    outs = {}
+    for graph in (False, True):
+        args = EngineArgs(model_path=tgt, draft_model_path=tgt, n_particles=4, gamma=4, draft_temperature=0.7,
+                          target_temperature=0.7, max_running_requests=2, context_length=512, device="cuda",
+                          max_total_tokens=8192, backend="native", resample_threshold=0.0, cycle_graph=graph).finalize()
+        sched = SMCScheduler(args, target=model, draft=model)
+        sched.add_request(GenerateRequest("r", _prompts(1, L=70)[0], SamplingParams(max_new_tokens=30, ignore_eos=True)))
+        o = sched.run_until_idle()
+        assert sched.native_runner.target._cascade and sched.native_runner.draft._cascade     # the plans were on
+        po = [x for x in o if isinstance(x, ParticleOutput)][0]
+        assert max(abs(w) for w in po.log_w_tilde) < 0.35, po.log_w_tilde
+        assert sched.native_runner.check_status() == 0
+        outs[graph] = po.particle_output_ids
+    assert outs[False] == outs[True]

@@ -49,7 +49,21 @@ def test_tensor_parallel_engine_two_gpus_matches_single_gpu():
     for r, o in zip(ref, outs):
         assert o["completion_tokens"] == 21
         agree = sum(int(a == b) for a, b in zip(r["output_ids"], o["output_ids"])) / 21
-        assert agree >= 0.5      # bf16 summation order differs between the sharded and unsharded chains
+        assert agree >= 0.5      # sampled sequences part ways after the first flipped draw; the bound below is the tight one
+
+
+def test_tensor_parallel_scores_match_single_gpu_at_logit_level():
+    """Log-probabilities of a fixed continuation, computed by each engine's own target path (prompt pass + one
+    verify-shaped pass through the fused all-gather / reduce-scatter chain and the vocab-parallel scorer), agree with
+    the single-GPU kernel chain to bf16 accumulation noise."""
+    prompt, cont = _prompts(1, L=40, seed=3)[0], _prompts(1, L=9, seed=4)[0]
+    ref_eng = _engine(in_process=True)
+    ref = ref_eng._sched.score_tokens(prompt, cont, 0.7)
+    with _engine(tp_size=2) as eng:
+        res = eng.collective_rpc("score_tokens", input_ids=prompt, continuation=cont, temperature=0.7)
+    assert all(r.ok for r in res), [r.value for r in res]
+    for r in res:                                   # every rank holds the same merged scores
+        assert max(abs(a - b) for a, b in zip(r.value, ref)) < 0.05, (r.value, ref)
 
 
 def test_data_parallel_engine_two_gpus():

@@ -385,6 +385,64 @@ def test_attention_fused(bs, E, Hq, Hkv, D, ctx, KS, rd, extras):
     assert err < 3e-2 * max(1.0, ref.abs().max().item()), err
 
 
+@pytest.mark.parametrize("groups,N,NP,E,Hq,Hkv,D,P,suffix,KSg,KSs", [
+    (1, 8, 8, 1, 32, 8, 64, 1500, 300, 4, 2), (1, 8, 2, 9, 32, 8, 128, 2100, 200, 4, 1), (2, 4, 4, 2, 8, 2, 64, 700, 40, 2, 1),
+    (1, 8, 8, 1, 32, 8, 64, 100, 1200, 1, 4), (1, 4, 2, 5, 8, 2, 128, 333, 0, 1, 1),
+])
+def test_attention_shared_prefix_passes(groups, N, NP, E, Hq, Hkv, D, P, suffix, KSg, KSs):
+    """Shared-prefix attention: one pass over the prompt keys for NP particles at a time (state parked per token and
+    head), then the per-particle pass over the remaining keys folds it in.  Must equal plain causal attention."""
+    K = _K()
+    from smcsd_b200.models.layers import ExtendBatch, paged_attention_reference
+    torch.manual_seed(13)
+    dev = "cuda"
+    bs = groups * N
+    T = bs * E
+    pages = groups * P + bs * (suffix + E) + 64
+    kp = torch.randn(pages + 1, Hkv * D, device=dev).bfloat16()
+    vp = torch.randn(pages + 1, Hkv * D, device=dev).bfloat16()
+    perm = (torch.randperm(pages, device=dev) + 1).to(torch.int32)
+    bt = torch.zeros(bs + 2, P + suffix + E + 8, device=dev, dtype=torch.int32)
+    off = 0
+    shared = []
+    for gi in range(groups):
+        shared.append(perm[off:off + P])
+        off += P
+    prefix = torch.zeros(bs, device=dev, dtype=torch.int32)
+    for b in range(bs):
+        gi = b // N
+        own = suffix - (b % 3)                      # particles of a group may differ in length in this test
+        own = max(own, 0)
+        bt[b + 1, :P] = shared[gi]
+        bt[b + 1, P:P + own + E] = perm[off:off + own + E]
+        off += own + E
+        prefix[b] = P + own
+    rows = torch.arange(bs, device=dev, dtype=torch.int32) + 1
+    q = torch.randn(T, Hq, D, device=dev).bfloat16()                 # rotated queries; new K/V already in their pages
+    batch = ExtendBatch(None, None, None, rows, prefix, extend_len=E)
+    ref = paged_attention_reference(q, kp, vp, bt, batch, Hkv).float().reshape(T, -1)
+    st = _status()
+    dummy = torch.zeros(8, device=dev)
+    qkv = torch.zeros(T, (Hq + 2 * Hkv) * D, device=dev)
+    pos = torch.zeros(T, device=dev, dtype=torch.int32)
+    locs = torch.zeros(T, device=dev, dtype=torch.int32)
+    table = torch.zeros(16, D, device=dev)
+    state = torch.zeros(T, Hq, D + 2, device=dev)
+    n_super = bs // NP
+    rows_g = rows[::NP].contiguous()
+    shared_len = torch.full((bs,), P, device=dev, dtype=torch.int32)
+    K.attention_fused(qkv, pos, locs, table, kp, vp, bt, rows_g, shared_len[::NP].contiguous(), None, bs=n_super, E=NP * E,
+                      Hq=Hq, Hkv=Hkv, D=D, KS=KSg, scale=D ** -0.5, status=st, q_in=q.reshape(T, -1), part_out=state,
+                      causal=False)
+    out = torch.zeros(T, Hq * D, device=dev, dtype=torch.bfloat16)
+    K.attention_fused(qkv, pos, locs, table, kp, vp, bt, rows, prefix, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D, KS=KSs,
+                      scale=D ** -0.5, status=st, q_in=q.reshape(T, -1), key_begin=shared_len, part_in=state)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    err = (out.float() - ref).abs().max().item()
+    assert err < 3e-2 * max(1.0, ref.abs().max().item()), err
+
+
 # ------------------------------------------------------------------------------- RMSNorm folded into the GEMMs
 @pytest.mark.parametrize("d,ffn,M", [(2048, 8192, 8), (4096, 14336, 72), (512, 1536, 20)])
 def test_gemm_with_folded_rmsnorm(d, ffn, M):
