@@ -24,6 +24,8 @@ def main(argv=None) -> None:
     ap.add_argument("--particles", type=int, default=8)
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--contiguous", action="store_true",
+                    help="the prompt sits in consecutive pages (a fresh pool) instead of randomly scattered ones")
     ns = ap.parse_args(argv)
     from ..ops import native as K
     dev = torch.device("cuda", 0)
@@ -45,6 +47,8 @@ def main(argv=None) -> None:
                  for _ in range(ns.layers)]
         bt = torch.zeros(bs + 1, P + S + E + 8, dtype=torch.int32, device=dev)
         perm = (torch.randperm(n_pages, device=dev) + 1).to(torch.int32)
+        if ns.contiguous:
+            perm = (torch.arange(n_pages, device=dev) + 1).to(torch.int32)
         for b in range(bs):
             bt[b, :P] = perm[:P]
             bt[b, P:P + S + E] = perm[P + b * (S + E): P + (b + 1) * (S + E)]
@@ -82,6 +86,31 @@ def main(argv=None) -> None:
                 K.attention_fused(qkv, pos, locs, rope, k, v, bt, rows, prefix, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D,
                                   KS=kss, scale=D ** -0.5, status=status, pdl=True, q_in=q, key_begin=shared, part_in=state)
 
+        # the tcgen05 pass takes all particles of the group at once (its query rows are tiled by 128)
+        rows_t, shared_t = rows[::N].contiguous(), shared[::N].contiguous()
+        kst = K.attention_tc_splits(bs // N, Hkv, P, N * E * G)
+        state_tc = torch.zeros(kst, T, Hq, D + 2, device=dev)
+
+        def cascade_tc():
+            for k, v in pools:
+                K.rope_kv_write(qkv, 1, 0, pos, locs, rope, q, k, v, M=T, Hq=Hq, Hkv=Hkv, D=D, status=status, pdl=True)
+                K.attention_prefix_tc(q, k, v, bt, rows_t, shared_t, state_tc, n_seq=bs // N, E=N * E, T=T, Hq=Hq,
+                                      Hkv=Hkv, D=D, KS=kst, scale=D ** -0.5, status=status)
+                K.attention_fused(qkv, pos, locs, rope, k, v, bt, rows, prefix, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D,
+                                  KS=kss, scale=D ** -0.5, status=status, pdl=False, q_in=q, key_begin=shared,
+                                  part_in=state_tc, part_in_n=kst, part_in_stride=state_tc.stride(0))
+
+        def group_mma():
+            for k, v in pools:
+                K.attention_fused(qkv, pos, locs, rope, k, v, bt, rows_g, shared_g, None, bs=bs // NP, E=NP * E, Hq=Hq,
+                                  Hkv=Hkv, D=D, KS=ksg, scale=D ** -0.5, status=status, pdl=False, q_in=q, part_out=state,
+                                  causal=False)
+
+        def group_tc():
+            for k, v in pools:
+                K.attention_prefix_tc(q, k, v, bt, rows_t, shared_t, state_tc, n_seq=bs // N, E=N * E, T=T, Hq=Hq,
+                                      Hkv=Hkv, D=D, KS=kst, scale=D ** -0.5, status=status)
+
         def timed(fn):
             fn()
             torch.cuda.synchronize()
@@ -103,9 +132,26 @@ def main(argv=None) -> None:
         o1 = out.float().clone()
         t2 = timed(cascade)
         err = float((out.float() - o1).abs().max())
+        t3 = timed(cascade_tc)
+        err_tc = float((out.float() - o1).abs().max())
+        t4, t5 = timed(group_mma), timed(group_tc)
+        trace = torch.zeros(4096, 12, dtype=torch.int64, device=dev)
+        k0, v0 = pools[0]
+        K.attention_prefix_tc(q, k0, v0, bt, rows_t, shared_t, state_tc, n_seq=bs // N, E=N * E, T=T, Hq=Hq, Hkv=Hkv, D=D,
+                              KS=kst, scale=D ** -0.5, status=status, trace=trace)
+        torch.cuda.synchronize()
+        used = trace[trace[:, 4] > 0].double()
+        wait_share = (used[:, [0, 1, 2, 3, 5, 6, 7]] / used[:, 4:5]).mean(0).tolist() if used.numel() else []
+        wait_share += (used[:, 8:11] / used[:, 11:12].clamp(min=1)).mean(0).tolist() if used.numel() else []
+        wait_share += [float(used[:, 4].mean())] if used.numel() else []
         kv_bytes = (P + N * S) * Hkv * D * 2 * 2
-        rows_out.append({"shape": ns.shape, "prompt": P, "suffix": S, "particles": N, "E": E, "single_us": t1,
-                         "shared_prefix_us": t2, "speedup": t1 / t2, "splits_single": ks1, "splits_group": ksg,
+        rows_out.append({"shape": ns.shape, "pages": "consecutive" if ns.contiguous else "scattered", "prompt": P, "suffix": S, "particles": N, "E": E, "single_us": t1,
+                         "shared_prefix_us": t2, "speedup": t1 / t2, "shared_prefix_tcgen05_us": t3, "speedup_tcgen05": t1 / t3,
+                         "splits_group_tcgen05": kst, "group_pass_us": t4,
+                         "group_pass_tcgen05_us": t5,
+                         "tcgen05_wait_shares": dict(zip(["scores_ready", "score_load", "p_buffer", "exp_store", "mma_kv",
+                                                          "mma_score_buffer", "mma_p", "load_stage_free", "load_issue", "load_landing",
+                                                          "softmax_total_cycles"], [round(x, 3) for x in wait_share])), "max_abs_diff_tcgen05": err_tc, "splits_single": ks1, "splits_group": ksg,
                          "splits_suffix": kss, "particles_per_group_pass": NP, "max_abs_diff": err,
                          "unique_kv_MB_per_layer": kv_bytes / 1e6, "status": int(status.item())})
         print(json.dumps(rows_out[-1]))

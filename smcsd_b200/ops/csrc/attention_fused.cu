@@ -49,7 +49,9 @@ struct FusedAttnParams {
   // that state in (part_in) before it normalises.  State row: D values, running max, running sum.
   const int* key_begin;      // [bs] or null: first key of this sequence served by this launch
   float* part_out;           // [T, Hq, D + 2] or null
-  const float* part_in;      // [T, Hq, D + 2] or null
+  const float* part_in;      // [part_in_n, T, Hq, D + 2] or null: states of the key splits of the group pass
+  int part_in_n;             // number of states to fold in (>= 1 when part_in is given)
+  long long part_in_stride;  // floats between consecutive states
   int causal;                // 0: every key of the range is visible to every query row
 };
 
@@ -407,16 +409,27 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       if (r >= R) continue;
       const int e = r / G, gq = r % G, tkn = b * p.E + e, head = hbase + gq;
       float m = hrow ? st.m1 : st.m0, l = hrow ? st.l1 : st.l0;
-      float a_self = 1.f, a_in = 0.f;
+      float a_self = 1.f;
+      float a_in[8];
       const float* sin_row = nullptr;
       if (p.part_in != nullptr) {
-        // fold in the state a group pass left for this (token, head): flash-decoding merge of two partial softmaxes
+        // fold in the states a group pass left for this (token, head): flash-decoding merge of partial softmaxes
         sin_row = p.part_in + ((size_t)tkn * p.Hq + head) * (D + 2);
-        const float m_in = sin_row[D], l_in = sin_row[D + 1];
-        const float M = fmaxf(m, m_in);
+        float M = m;
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (q < p.part_in_n) M = fmaxf(M, sin_row[(size_t)q * p.part_in_stride + D]);
         a_self = M == -INFINITY ? 1.f : __expf(m - M);
-        a_in = M == -INFINITY ? 0.f : __expf(m_in - M);
-        l = l * a_self + l_in * a_in;
+        l *= a_self;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          a_in[q] = 0.f;
+          if (q < p.part_in_n) {
+            const float m_in = sin_row[(size_t)q * p.part_in_stride + D], l_in = sin_row[(size_t)q * p.part_in_stride + D + 1];
+            a_in[q] = (M == -INFINITY || m_in == -INFINITY) ? 0.f : __expf(m_in - M);
+            l += l_in * a_in[q];
+          }
+        }
         m = M;
       }
       if (p.part_out != nullptr) {
@@ -434,9 +447,13 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       for (int nt = 0; nt < D / 8; ++nt) {
         float v0 = st.o[nt][2 * hrow] * a_self, v1 = st.o[nt][2 * hrow + 1] * a_self;
         if (sin_row != nullptr) {
-          const float2 x = *reinterpret_cast<const float2*>(sin_row + nt * 8 + 2 * t);
-          v0 += x.x * a_in;
-          v1 += x.y * a_in;
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            if (q < p.part_in_n) {
+              const float2 x = *reinterpret_cast<const float2*>(sin_row + (size_t)q * p.part_in_stride + nt * 8 + 2 * t);
+              v0 += x.x * a_in[q];
+              v1 += x.y * a_in[q];
+            }
         }
         v0 *= inv;
         v1 *= inv;
@@ -514,7 +531,8 @@ SMC_API int smc_attention_fused_ex(const float* qkv, const void* q_in, int ld_qk
                                    void* k_pool, void* v_pool, int n_pages, const int* block_table, int bt_stride,
                                    const int* rows, const int* prefix_lens, void* out, int bs, int E, int Hq, int Hkv,
                                    int D, int KS, float scale, int* status, int pdl, const int* key_begin,
-                                   float* part_out, const float* part_in, int causal, cudaStream_t st);
+                                   float* part_out, const float* part_in, int part_in_n, long long part_in_stride,
+                                   int causal, cudaStream_t st);
 
 SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, int q_off, int gate_off, int k_off, int v_off,
                                 const int* positions, const int* cache_locs, const float* rope, int rd, int max_pos,
@@ -526,12 +544,13 @@ SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, 
   (void)part_ml;
   return smc_attention_fused_ex(qkv, q_in, ld_qkv, q_off, gate_off, k_off, v_off, positions, cache_locs, rope, rd, max_pos,
                                 qn_w, kn_w, norm_eps, norm_plus_one, k_pool, v_pool, n_pages, block_table, bt_stride, rows,
-                                prefix_lens, out, bs, E, Hq, Hkv, D, KS, scale, status, pdl, nullptr, nullptr, nullptr, 1,
-                                st);
+                                prefix_lens, out, bs, E, Hq, Hkv, D, KS, scale, status, pdl, nullptr, nullptr, nullptr, 0, 0,
+                                1, st);
 }
 
 // Same, with the shared-prefix options: key_begin [bs] (first key served), part_out / part_in [T, Hq, D + 2] fp32
-// (unnormalised attention state parked by a group pass / folded in by the per-sequence pass), causal (0: no limit).
+// (unnormalised attention state parked by a group pass / folded in by the per-sequence pass; part_in may hold up to
+// eight states, part_in_stride floats apart, one per key split of the group pass), causal (0: no limit).
 // A group pass takes rotated queries (q_in), may span more than 16 tokens per "sequence" (E * Hq / Hkv <= 128 query
 // rows) and keeps all query heads of a kv head in one CTA so that its keys are streamed once.
 SMC_API int smc_attention_fused_ex(const float* qkv, const void* q_in, int ld_qkv, int q_off, int gate_off, int k_off,
@@ -540,8 +559,10 @@ SMC_API int smc_attention_fused_ex(const float* qkv, const void* q_in, int ld_qk
                                    void* k_pool, void* v_pool, int n_pages, const int* block_table, int bt_stride,
                                    const int* rows, const int* prefix_lens, void* out, int bs, int E, int Hq, int Hkv,
                                    int D, int KS, float scale, int* status, int pdl, const int* key_begin,
-                                   float* part_out, const float* part_in, int causal, cudaStream_t st) {
+                                   float* part_out, const float* part_in, int part_in_n, long long part_in_stride,
+                                   int causal, cudaStream_t st) {
   using namespace smc;
+  if (part_in != nullptr && (part_in_n < 1 || part_in_n > 8)) return -75;
   if (bs <= 0) return 0;
   if (Hq % Hkv || E < 1 || (rd & 1) || rd > D) return -70;
   if (E > 16 && (q_in == nullptr || E * (Hq / Hkv) > 128)) return -70;
@@ -568,6 +589,7 @@ SMC_API int smc_attention_fused_ex(const float* qkv, const void* q_in, int ld_qk
   p.E = E; p.Hq = Hq; p.Hkv = Hkv; p.KS = KS; p.gsub = gsub; p.n_mt = n_mt; p.n_kw = n_kw; p.stg = stg; p.scale = scale; p.status = status;
   p.pdl = pdl;
   p.key_begin = key_begin; p.part_out = part_out; p.part_in = part_in; p.causal = causal ? 1 : 0;
+  p.part_in_n = part_in_n; p.part_in_stride = part_in_stride;
   const size_t smem = fused_smem_bytes(D, n_mt, n_kw, stg);
   void (*kern)(const FusedAttnParams) = nullptr;
   if (D == 64) kern = attn_fused_kernel<64>;

@@ -53,7 +53,7 @@ def _declare(L) -> None:
     L.smc_rope_kv_write.argtypes = [vp, i, ll, vp, vp, vp, i, i, vp, vp, vp, i, i, i, i, i, vp, i, vp]
     L.smc_swiglu_partials.argtypes = [vp, i, ll, vp, i, i, i, i, i, vp]
     L.smc_attention_fused_ex.argtypes = [vp, vp, i, i, i, i, i, vp, vp, vp, i, i, vp, vp, f, i, vp, vp, i, vp, i, vp, vp,
-                                         vp, i, i, i, i, i, i, f, vp, i, vp, vp, vp, i, vp]
+                                         vp, i, i, i, i, i, i, f, vp, i, vp, vp, vp, i, ll, i, vp]
     L.smc_attention_fused_ex.restype = C.c_int
     L.smc_sample_scratch_bytes.argtypes = [i, i]
     L.smc_sample_or_score.argtypes = [vp, i, ll, ll, i, i, f, f, f, vp, ull, vp, i, vp, i, vp, vp, vp, i, vp]
@@ -206,7 +206,8 @@ def attention_fused(qkv: torch.Tensor, positions: torch.Tensor, cache_locs: torc
                     qn_w: Optional[torch.Tensor] = None, kn_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6,
                     norm_plus_one: bool = False, pdl: bool = False, q_in: Optional[torch.Tensor] = None,
                     key_begin: Optional[torch.Tensor] = None, part_out: Optional[torch.Tensor] = None,
-                    part_in: Optional[torch.Tensor] = None, causal: bool = True) -> None:
+                    part_in: Optional[torch.Tensor] = None, causal: bool = True, part_in_n: int = 1,
+                    part_in_stride: int = 0) -> None:
     """Norm/rope/KV-write of the new tokens + paged causal attention + split merge, one launch per layer.
     Shared-prefix passes: ``causal=False`` with ``q_in`` and ``part_out`` serves the rows of several sequences from
     one stream of their common keys and parks the unnormalised state; ``key_begin`` / ``part_in`` make the
@@ -218,7 +219,36 @@ def attention_fused(qkv: torch.Tensor, positions: torch.Tensor, cache_locs: torc
                                         norm_eps, int(norm_plus_one), _p(k_pool), _p(v_pool), k_pool.shape[0] - 1,
                                         _p(block_table), block_table.stride(0), _p(rows), _p(prefix_lens), _p(out),
                                         bs, E, Hq, Hkv, D, KS, scale, _p(status), int(pdl), _p(key_begin),
-                                        _p(part_out), _p(part_in), int(causal), _stream()), "smc_attention_fused")
+                                        _p(part_out), _p(part_in), part_in_n if part_in is not None else 0,
+                                        part_in_stride, int(causal), _stream()), "smc_attention_fused")
+
+
+def attention_tc_splits(n_seq: int, Hkv: int, keys: int, rows: int = 128) -> int:
+    L = lib()
+    L.smc_attention_tc_splits.argtypes = [C.c_int] * 4
+    L.smc_attention_tc_splits.restype = C.c_int
+    return L.smc_attention_tc_splits(n_seq, Hkv, keys, rows)
+
+
+def attention_prefix_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                        rows: torch.Tensor, key_count: torch.Tensor, part_out: torch.Tensor, *, n_seq: int, E: int,
+                        T: int, Hq: int, Hkv: int, D: int, KS: int, scale: float, status: torch.Tensor,
+                        trace: Optional[torch.Tensor] = None, use_tma: bool = True) -> None:
+    """Shared-prefix attention pass on tcgen05: the E tokens (all query heads) of every (super-)sequence against keys
+    [0, key_count) of its block-table row, no causal limit; parks the unnormalised state of every key split in
+    ``part_out`` [KS, T, Hq, D + 2].  ``trace`` (int64 [CTAs, 12], optional) receives the cycles every CTA spent in
+    its waits: softmax {scores ready, score load, P buffer free, exp + store, total}, MMA {K/V, score buffer, P}, first
+    loader warp {stage free, copy issue, landing, total}.  Tiles of 64 consecutive pages are fetched by TMA unless
+    ``use_tma`` is off; scattered tiles are gathered row by row."""
+    L = lib()
+    if not getattr(L, "_atc_declared", False):
+        vp, i, f = C.c_void_p, C.c_int, C.c_float
+        L.smc_attention_prefix_tc.argtypes = [vp, vp, vp, i, vp, i, vp, vp, vp, i, i, i, i, i, i, i, f, vp, vp, i, vp]
+        L.smc_attention_prefix_tc.restype = C.c_int
+        L._atc_declared = True
+    _check(L.smc_attention_prefix_tc(_p(q), _p(k_pool), _p(v_pool), k_pool.shape[0] - 1, _p(block_table),
+                                     block_table.stride(0), _p(rows), _p(key_count), _p(part_out), n_seq, E, T, Hq, Hkv,
+                                     D, KS, scale, _p(status), _p(trace), int(use_tma), _stream()), "smc_attention_prefix_tc")
 
 
 def attn_kv_splits(ctx: int, bs: int, Hkv: int, E: int = 1, G: int = 4, D: int = 128) -> int:

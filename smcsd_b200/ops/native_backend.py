@@ -20,6 +20,11 @@ from ..runtime.slot_state import CycleInputs, CycleOutputs
 from . import native as K
 
 
+# Shared-prefix group pass on the tcgen05 kernel instead of the mma.sync one (SMC_ATTN_TC): 0 never, 1 for forwards of
+# more than two tokens per sequence (the verify shape, where its 128-row tiles are well filled), 2 always.
+ATTN_TC_DEFAULT = 1
+
+
 def _env_int(name: str, default: int) -> int:
     v = os.environ.get(name)
     return default if v is None or v == "" else int(v)
@@ -65,8 +70,10 @@ class NativeLlama:
         # shared-prefix attention: parked state per (token, head) and, filled by the runner when the batch changes,
         # the per-sequence shared lengths and the block-table rows / shared lengths of every NP-th sequence
         self.att_state = torch.zeros(max_tokens, self.nq, self.D + 2, dtype=f32, device=dev)
+        self.att_state_tc = None             # [key split, token, head, D + 2] states of the tcgen05 group pass
         self.cascade_bufs = None
         self._cascade: Dict = {}
+        self.attn_tc = _env_int("SMC_ATTN_TC", ATTN_TC_DEFAULT)
         # RMSNorm folded into the GEMMs: consumers read the raw bf16 residual stream ``hb`` and scale by 1/rms in
         # their epilogue; residual GEMMs emit ``hb`` and per-slab sums of squares.  Five launches per layer.
         self.fold = self.fuse_swiglu and model.tp_size == 1 and _env_flag("SMC_FOLD_NORM", True)
@@ -123,6 +130,19 @@ class NativeLlama:
         NP, cb = plan["NP"], self.cascade_bufs
         K.rope_kv_write(self.qkv, 1, 0, positions, cache_locs, m.rope, self.q, k, v, M=T, Hq=self.nq, Hkv=self.nkv,
                         D=self.D, status=self.status, pdl=pdl)
+        if plan["tc"]:
+            # group pass on the tcgen05 kernel: one parked state per key split, folded in by the per-particle pass
+            if self.att_state_tc is None:
+                self.att_state_tc = torch.zeros(8, self.T, self.nq, self.D + 2, dtype=torch.float32, device=self.h.device)
+            K.attention_prefix_tc(self.q, k, v, self.bt, cb["rows_g"][NP], cb["shared_g"][NP], self.att_state_tc,
+                                  n_seq=bs // NP, E=NP * E, T=self.T, Hq=self.nq, Hkv=self.nkv, D=self.D,
+                                  KS=plan["KSg"], scale=scale, status=self.status)
+            K.attention_fused(self.qkv, positions, cache_locs, m.rope, k, v, self.bt, rows, prefix_lens, self.attn,
+                              bs=bs, E=E, Hq=self.nq, Hkv=self.nkv, D=self.D, KS=plan["KSs"], scale=scale,
+                              status=self.status, pdl=False, q_in=self.q, key_begin=cb["shared"],
+                              part_in=self.att_state_tc, part_in_n=plan["KSg"],
+                              part_in_stride=self.att_state_tc.stride(0))
+            return
         K.attention_fused(self.qkv, positions, cache_locs, m.rope, k, v, self.bt, cb["rows_g"][NP], cb["shared_g"][NP],
                           None, bs=bs // NP, E=NP * E, Hq=self.nq, Hkv=self.nkv, D=self.D, KS=plan["KSg"], scale=scale,
                           status=self.status, pdl=pdl, q_in=self.q, part_out=self.att_state, causal=False)
@@ -137,10 +157,13 @@ class NativeLlama:
         return tuple(self._ks(bs, E) for E in Es)
 
     # Shortest shared prompt for which the extra two launches per layer pay off.  Measured on B200 (8 particles,
-    # 256 own tokens each): single-token steps 0.87x at 4k, 1.16x at 8k, 1.5x at 16k, 2.0x at 32k prompt tokens.  The
-    # verify shape (9 tokens x 4 heads per particle) is bound by the mma.sync issue rate, not by key traffic, and
-    # loses at every length (0.6-0.7x), so it keeps the single launch unless SMC_CASCADE_VERIFY=1.
+    # 256 own tokens each): single-token steps with the mma.sync group pass 0.87x at 4k, 1.1x at 8k, 1.5x at 16k, 2.0x
+    # at 32k prompt tokens.  The verify shape (9 tokens x 4 heads per particle) loses at every length with the mma.sync
+    # group pass (bound by its issue rate) and wins with the tcgen05 one: pages scattered 1.0x at 8k, 1.14x at 12k,
+    # 1.2x at 16k, 1.4x at 32k; prompt in consecutive pages 1.2x at 8k, 1.5x at 12k, 1.9x at 32k.
+    # SMC_CASCADE_VERIFY=1 / 0 forces the verify-shape passes on / off.
     CASCADE_MIN_PROMPT = 8192
+    CASCADE_MIN_PROMPT_VERIFY = 12288
 
     def set_prefix(self, min_prompt: int, max_prompt: int, bs: int, n_particles: int, Es=(1, 2)) -> tuple:
         """Plan the shared-prefix passes for forwards of ``Es`` new tokens per sequence: ``min_prompt`` / ``max_prompt``
@@ -152,27 +175,35 @@ class NativeLlama:
             return ()
         G = self.nq // self.nkv
         key = []
-        verify_too = _env_flag("SMC_CASCADE_VERIFY", False)
+        verify_env = os.environ.get("SMC_CASCADE_VERIFY", "")
         for E in Es:
-            if E > 2 and not verify_too:
-                continue
+            tc = self.D in (64, 128) and n_particles in self.cascade_bufs["rows_g"] and \
+                (self.attn_tc >= 2 or (self.attn_tc == 1 and E > 2))
+            if E > 2:
+                on = tc and min_prompt >= max(thr, self.CASCADE_MIN_PROMPT_VERIFY) if verify_env == "" else verify_env == "1"
+                if not on:
+                    continue
             NP = 0
-            for cand in (8, 4, 2):
-                if n_particles % cand == 0 and cand * E * G <= 128 and cand in self.cascade_bufs["rows_g"]:
-                    NP = cand
-                    break
-            if NP == 0:
-                continue
-            n_mt = (NP * E * G + 15) // 16
-            n_kw = max(1, 8 // n_mt)
-            base = (bs // NP) * self.nkv
-            ksg = 1
-            while ksg < 8 and base * ksg * 2 <= 148 and max_prompt // (ksg * 2 * 32 * n_kw) >= 2:
-                ksg *= 2
+            if tc:                                   # the tcgen05 pass tiles its query rows: whole groups at once
+                NP = n_particles
+                ksg = K.attention_tc_splits(bs // NP, self.nkv, max_prompt, NP * E * G)
+            else:
+                for cand in (8, 4, 2):
+                    if n_particles % cand == 0 and cand * E * G <= 128 and cand in self.cascade_bufs["rows_g"]:
+                        NP = cand
+                        break
+                if NP == 0:
+                    continue
+                n_mt = (NP * E * G + 15) // 16
+                n_kw = max(1, 8 // n_mt)
+                base = (bs // NP) * self.nkv
+                ksg = 1
+                while ksg < 8 and base * ksg * 2 <= 148 and max_prompt // (ksg * 2 * 32 * n_kw) >= 2:
+                    ksg *= 2
             suffix = max(self.ctx_hint - min_prompt, 1)
             kss = K.attn_kv_splits(suffix, bs, self.nkv, E, G, self.D)
-            self._cascade[E] = {"NP": NP, "KSg": ksg, "KSs": kss}
-            key.append((E, NP, ksg, kss))
+            self._cascade[E] = {"NP": NP, "KSg": ksg, "KSs": kss, "tc": tc}
+            key.append((E, NP, ksg, kss, tc))
         return tuple(key)
 
     def _ks(self, bs: int, E: int) -> int:
@@ -281,7 +312,7 @@ class NativeLlama:
 class NativeState:
     """Device-kernel versions of the SlotState transitions (bound to one SlotState)."""
 
-    def __init__(self, max_bs: int, gamma: int, device):
+    def __init__(self, max_bs: int, gamma: int, device, n_particles: int = 0):
         self.G = gamma + 1
         self.gamma = gamma
         self.device = device
@@ -313,10 +344,11 @@ class NativeState:
         self.fused_write_back = True
         # shared-prefix attention inputs, rewritten when the batch changes: keys every particle of a group shares
         # (its prompt minus one, so that the draft head's shorter prefix is covered as well), and for NP = 2, 4, 8 the
-        # block-table row and shared length of every NP-th sequence
+        # (and the group size) the block-table row and shared length of every NP-th sequence
         self.shared = torch.zeros(max_bs, **i32)
-        self.rows_g = {n: torch.zeros(max(1, max_bs // n), **i32) for n in (2, 4, 8)}
-        self.shared_g = {n: torch.zeros(max(1, max_bs // n), **i32) for n in (2, 4, 8)}
+        sizes = {2, 4, 8} | ({int(n_particles)} if n_particles > 1 else set())
+        self.rows_g = {n: torch.zeros(max(1, max_bs // n), **i32) for n in sizes}
+        self.shared_g = {n: torch.zeros(max(1, max_bs // n), **i32) for n in sizes}
 
     def bind(self, st) -> None:
         self._arrays = K.make_slot_arrays(st)
@@ -333,7 +365,7 @@ class NativeState:
             self.active_rows[: self.n_groups].copy_(st.active_rows, non_blocking=True)
             bs = self.bs
             self.shared[:bs] = (st.prompt_lens[st.active_slots.long()] - 1).clamp_(min=0)
-            for n in (2, 4, 8):
+            for n in self.rows_g:
                 if bs % n == 0:
                     self.rows_g[n][: bs // n] = self.active[:bs:n]
                     self.shared_g[n][: bs // n] = self.shared[:bs:n]
@@ -468,7 +500,9 @@ class NativeRunner:
             if self.comm is None:
                 raise RuntimeError("a tensor-parallel model needs a process group (launch one rank per GPU)")
             if self.heap is None:
-                need = 4 * max_tokens * model.cfg.hidden_size * 8 + max_tokens * 32 * 32 * model.tp_size + (8 << 20)
+                pf = self.PREFILL_MAX_TOKENS_TP            # a second, prompt-sized chain shares the heap
+                need = 4 * (max_tokens + pf) * model.cfg.hidden_size * 8 + \
+                    (max_tokens + pf) * 32 * 32 * model.tp_size + (8 << 20)
                 self.heap = SymmHeap(need, self.device, self.comm.device_group, self.comm.group_rank,
                                      self.comm.group_size)
             model.tp_group = self.comm.device_group      # the PyTorch prefill path all-reduces through NCCL
@@ -478,6 +512,7 @@ class NativeRunner:
     # ---- prefill ---------------------------------------------------------------------------------------
     PREFILL_BLOCK = 16
     PREFILL_MAX_TOKENS = 4096
+    PREFILL_MAX_TOKENS_TP = 1024         # token capacity of the tensor-parallel prompt chain (symmetric-heap buffers)
 
     def _prefill_chain(self, which: str):
         """Kernel chains sized for prompt passes (built on first use; weights are shared with the decode chains)."""
@@ -491,6 +526,10 @@ class NativeRunner:
             elif type(base).__name__ == "NativeHybrid":
                 nm = type(base)(base.m, base.kv, base.bt, self.PREFILL_MAX_TOKENS, 8, base.attn_splits, self.status,
                                 self.pdl, runner=self, state=base.state)
+            elif type(base).__name__ == "NativeLlamaTP" and self.heap is not None:
+                # tensor-parallel prompts run through the same fused all-gather / reduce-scatter chain as decode
+                nm = type(base)(base.m, base.kv, base.bt, self.PREFILL_MAX_TOKENS_TP, 256, 8, self.status, self.pdl,
+                                self.heap)
             else:
                 return None
             setattr(self, key, nm)
@@ -510,8 +549,7 @@ class NativeRunner:
         T = sum(n_blocks) * B
         tgt, drf = self._prefill_chain("target"), self._prefill_chain("draft")
         stateful = any(getattr(nm.m, "has_state", False) for nm in (tgt, drf) if nm is not None)
-        if tgt is None or drf is None or getattr(self.target.m, "tp_size", 1) > 1 or \
-                (T > self.PREFILL_MAX_TOKENS and stateful):
+        if tgt is None or drf is None or (T > self.PREFILL_MAX_TOKENS and stateful) or len(items) > 256:
             native, worker.native = worker.native, None
             try:
                 return worker.prefill(items)
@@ -562,12 +600,16 @@ class NativeRunner:
                              "off": pin(torch.tensor(offs, dtype=torch.int32)),
                              "len": pin(torch.tensor([max(L - short, 0) for L in lens], dtype=torch.int32)),
                              "n": len(items)}}
-        cb = max(1, self.PREFILL_MAX_TOKENS // B)            # blocks per pass
+        cb = max(1, min(nm.T for nm in (tgt, drf)) // B)     # blocks per pass
         last = torch.tensor(last_rows, dtype=torch.long, device=dev)
 
         def grab(nm, idx):
             """Final-layer rows ``idx`` of the chain's buffers: raw bf16 residual rows + their sums of squares when the
             norm is folded into the lm_head, the normalised rows otherwise."""
+            if hasattr(nm, "wait_final_rows"):          # tensor-parallel chain: peers' rows must have landed first
+                nm.wait_final_rows()
+                rows_n = nm.xn_a[idx]
+                return {"x": rows_n, "ssq": None, "normed": rows_n}
             if getattr(nm, "fold", False):
                 return {"x": nm.hb[idx], "ssq": nm.ssq[:, idx], "normed": nm.final_hidden(idx)}
             return {"x": nm.final_hidden(idx), "ssq": None, "normed": nm.final_hidden(idx)}
@@ -608,6 +650,26 @@ class NativeRunner:
         project and sample with the fused lm_head kernel (no logits in memory, noise keyed by the running count of
         prefilled prompts); other targets project with PyTorch (reference: smcsd/core/worker.py:668-707)."""
         n = hidden["n"]
+        if hasattr(nm, "tp_sample") and n <= nm.logits.shape[0]:
+            # vocabulary-parallel target: this rank's logits shard of the last prompt tokens, then the fused sampler
+            # that exchanges per-chunk partials by peer stores (every rank draws the same x0)
+            dev = self.device
+            if getattr(self, "_x0_epoch", None) is None:
+                self._x0_epoch = torch.zeros(1, dtype=torch.int64, device=dev)
+                self._x0_counter_tp = torch.zeros(1, dtype=torch.int64, device=dev)
+                self._x0_done_tp = 0
+            self._x0_epoch.add_(1)
+            self._x0_counter_tp.fill_(self._x0_done_tp)
+            self._x0_done_tp += n
+            X = hidden["x"].contiguous()
+            K.gemm_skinny(nm.m.lm_head, X, nm.logits, M=n, splits=1, epi=K.EPI_STORE_F32, ldo=nm.logits.stride(0),
+                          status=self.status)
+            tok = torch.zeros(n, dtype=torch.int32, device=dev)
+            lp = torch.zeros(n, dtype=torch.float32, device=dev)
+            nm.tp_sample(rows=n, temperature=self.T_target, alpha=self.alpha, tokens_in=None, seed=self.seed ^ 0x5EED,
+                         cycle_counter=self._x0_counter_tp, call_id=4096, tok_out=tok, logp_out=lp, logz_out=None,
+                         epoch=self._x0_epoch)
+            return tok
         if type(nm) is NativeLlama and self.fused_sampling and self.fused_lm_head and n <= 256:
             dev = self.device
             if getattr(self, "_x0_counter", None) is None:
@@ -899,7 +961,7 @@ def create(sched, comm=None):
     if not torch.cuda.is_available():
         raise RuntimeError("the native backend needs a CUDA device")
     K.lib()     # fail loudly if the kernel library is missing
-    ns = NativeState(sched.max_groups * sched.args.n_particles, sched.args.gamma, sched.device)
+    ns = NativeState(sched.max_groups * sched.args.n_particles, sched.args.gamma, sched.device, sched.args.n_particles)
     ns.fused_write_back = bool(sched.args.fused_write_back)
     runner = NativeRunner(sched, ns, comm)
     return ns, runner

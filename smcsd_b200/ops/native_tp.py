@@ -90,6 +90,8 @@ class NativeLlamaTP:
         f32, bf16 = torch.float32, torch.bfloat16
         self.h = torch.zeros(self.ctx.rpr_max, self.d, dtype=f32, device=dev)       # this rank's token rows
         self.attn = torch.empty(max_tokens, self.nq * self.D, dtype=bf16, device=dev)
+        self.q = torch.empty(max_tokens, self.nq * self.D, dtype=bf16, device=dev)    # rotated queries (prompt passes)
+        self.epoch_host = 0                  # forwards issued so far (the device epoch counts the same)
         self.act = torch.empty(max_tokens, self.ffn, dtype=bf16, device=dev)
         self.qkv = torch.empty(max_tokens, self.nqkv, dtype=f32, device=dev)
         self.ctx_hint = 0                    # context-length bound that sizes the attention key splits, see set_context
@@ -104,15 +106,17 @@ class NativeLlamaTP:
             self._splits_cache[key] = K.gemm_cluster_splits(N, Kd, M)
         return self._splits_cache[key]
 
-    def forward(self, ids, positions, cache_locs, rows, prefix_lens, bs: int, E: int):
-        for _ in self.stages(ids, positions, cache_locs, rows, prefix_lens, bs, E):
+    def forward(self, ids, positions, cache_locs, rows, prefix_lens, bs: int, E: int, two_pass: bool = False):
+        for _ in self.stages(ids, positions, cache_locs, rows, prefix_lens, bs, E, two_pass):
             pass
         return self.xn_a
 
-    def stages(self, ids, positions, cache_locs, rows, prefix_lens, bs: int, E: int):
+    def stages(self, ids, positions, cache_locs, rows, prefix_lens, bs: int, E: int, two_pass: bool = False):
         """The forward as a generator that yields after every kernel launch.  On real ranks it is
         simply exhausted; a single-GPU emulation of several ranks advances all ranks' generators in
-        lockstep so that no kernel ever waits on a launch that comes later in the stream."""
+        lockstep so that no kernel ever waits on a launch that comes later in the stream.
+        ``two_pass`` (prompt passes): rows of one launch may be consecutive 16-token blocks of the same sequence, so
+        every K/V row of this rank's heads is written before attention reads all keys through the block table."""
         m, c, pdl, ctx = self.m, self.c, self.pdl, self.ctx
         T = bs * E
         assert T <= self.T
@@ -122,6 +126,7 @@ class NativeLlamaTP:
         my_rows = max(0, min(rpr, T - self.rank * rpr))
         self._last_L = L
         ctx.epoch.add_(1)
+        self.epoch_host += 1
         o = ctx.off
         st = self.status
         scale = self.D ** -0.5
@@ -134,9 +139,14 @@ class NativeLlamaTP:
             K.gemm_skinny_tp(Lw.wqkv, self.xn_a, self.qkv, M=T, splits=self._splits(self.nqkv, self.d, T),
                              epi=K.EPI_STORE_F32, link=lk, ldo=self.qkv.stride(0), status=st, pdl=pdl)
             yield
+            q_in = None
+            if two_pass:
+                K.rope_kv_write(self.qkv, 1, 0, positions, cache_locs, m.rope, self.q, self.kv.k[li], self.kv.v[li],
+                                M=T, Hq=self.nq, Hkv=self.nkv, D=self.D, status=st, pdl=pdl)
+                q_in = self.q
             K.attention_fused(self.qkv, positions, cache_locs, m.rope, self.kv.k[li], self.kv.v[li], self.bt, rows,
                               prefix_lens, self.attn, self.part_acc, self.part_ml, bs=bs, E=E, Hq=self.nq,
-                              Hkv=self.nkv, D=self.D, KS=self._ks(bs, E), scale=scale, status=st, pdl=pdl)
+                              Hkv=self.nkv, D=self.D, KS=self._ks(bs, E), scale=scale, status=st, pdl=pdl, q_in=q_in)
             yield
             lk = ctx.link(rs="rs_o", rows_per_rank=rpr, arrive_slot=1)
             K.gemm_skinny_tp(Lw.wo, self.attn, None, M=T, splits=self._splits(self.d, self.nq * self.D, T),
@@ -186,16 +196,28 @@ class NativeLlamaTP:
                          link=lk, ldx=self.d * row_step, ldo=self.logits.stride(0), status=self.status, pdl=self.pdl)
         return self.logits
 
+    def wait_final_rows(self) -> None:
+        """Stream-ordered wait until every rank's rows of the last forward have landed in ``xn_a`` (for callers that
+        read the gathered activations with ordinary kernels instead of a GEMM that waits by itself)."""
+        L = self._last_L
+        want = ((self.epoch_host - 1) * (L + 1) + L + 1) * self.tp
+        if getattr(self, "_wait_outcome", None) is None:
+            self._wait_outcome = torch.zeros(1, dtype=torch.int32, device=self.h.device)
+        K.tp_wait_counter(self.ctx.local_ptr("flag_ag_a"), want, self._wait_outcome, self.status)
+
     def tp_sample(self, *, rows, temperature, alpha, tokens_in, seed, cycle_counter, call_id, tok_out, logp_out,
-                  logz_out, phase: int = 0):
+                  logz_out, phase: int = 0, epoch=None):
         """Vocab-parallel fused sampling / scoring: partials are exchanged by peer stores, every rank
-        merges all shards and ends up with identical tokens and log-probabilities."""
+        merges all shards and ends up with identical tokens and log-probabilities.  The exchange counter is expected
+        to advance once per ``epoch`` tick: by default the forward counter (one sampling call per forward); callers
+        that sample less often pass their own counter and bump it once per call."""
         ctx, c = self.ctx, self.c
         K.tp_sample_or_score(ctx.peers, self.logits, rows=rows, Vshard=self.Vshard, v0=self.rank * self.Vshard,
                              Vtotal=c.vocab_size, temperature=temperature, alpha=alpha,
                              softcap=float(c.logit_softcap), tokens_in=tokens_in, seed=seed,
                              cycle_counter=cycle_counter, call_id=call_id, gather_off=ctx.off["gather"],
                              gather_local_ptr=ctx.local_ptr("gather"), flag_off=ctx.off["flag_sample"],
-                             flag_local_ptr=ctx.local_ptr("flag_sample"), uses=1, idx=0, epoch=ctx.epoch,
+                             flag_local_ptr=ctx.local_ptr("flag_sample"), uses=1, idx=0,
+                             epoch=ctx.epoch if epoch is None else epoch,
                              nchunks=self.nchunks, tok_out=tok_out, logp_out=logp_out, logz_out=logz_out,
                              arrive=ctx.arrive[5:], status=self.status, pdl=self.pdl, phase=phase)

@@ -295,10 +295,13 @@ class SMCScheduler:
             if pages is None:
                 raise RuntimeError("page reservation violated")
             self.bt.table[g.parent_row, :L] = pages
-            for pool in (self.state_t, self.state_d):       # recurrent state of a reused parent row starts at zero
-                if pool is not None:
-                    pool.clear_rows(torch.tensor([g.parent_row], device=self.device))
             items.append(PrefillItem(g.parent_row, g.req.input_ids))
+        if items and (self.state_t is not None or self.state_d is not None):
+            # recurrent state of reused parent rows starts at zero: one indexed clear per pool for the whole batch
+            prow = torch.tensor([it.row for it in items], dtype=torch.long).to(self.device, non_blocking=True)
+            for pool in (self.state_t, self.state_d):
+                if pool is not None:
+                    pool.clear_rows(prow)
         with profiling.span(f"step[PREFILL smc bs={len(items)} toks={sum(len(i.input_ids) for i in items)}]"):
             x0 = self.worker.prefill(items).tolist()          # one blocking read per prefill batch
         self.stats["prefills"] += len(groups)

@@ -291,8 +291,10 @@ def test_score_tokens_rpc_native_matches_pytorch():
     assert max(abs(x - y) for x, y in zip(a, b)) < 0.05, (a, b)
 
 
-def test_shared_prefix_attention_in_the_decode_cycle(monkeypatch):
-    """The shared-prefix passes forced on for short prompts (draft steps: 4 particles per group pass, verify: 2).
+@pytest.mark.parametrize("tc", [False, True])
+def test_shared_prefix_attention_in_the_decode_cycle(monkeypatch, tc):
+    """The shared-prefix passes forced on for short prompts (draft steps: 4 particles per group pass, verify: 2; with
+    ``tc`` the group pass runs on the tcgen05 kernel, whole groups at once).
     With draft == target every log-weight increment must stay ~0, which it only does if the single-token, two-token
     and verify attention paths all compute the same softmax; and the graph replays match the eager launches."""
     from smcsd_b200.config import EngineArgs
@@ -301,6 +303,7 @@ def test_shared_prefix_attention_in_the_decode_cycle(monkeypatch):
     from smcsd_b200.runtime.scheduler import SMCScheduler
     monkeypatch.setenv("SMC_CASCADE_MIN_PROMPT", "32")
     monkeypatch.setenv("SMC_CASCADE_VERIFY", "1")
+    monkeypatch.setenv("SMC_ATTN_TC", "2" if tc else "0")
     tgt, _ = _cfgs()
     model = build_model(tgt, torch.bfloat16, "cuda", seed=0)
     outs = {}
@@ -312,6 +315,7 @@ def test_shared_prefix_attention_in_the_decode_cycle(monkeypatch):
         sched.add_request(GenerateRequest("r", _prompts(1, L=70)[0], SamplingParams(max_new_tokens=30, ignore_eos=True)))
         o = sched.run_until_idle()
         assert sched.native_runner.target._cascade and sched.native_runner.draft._cascade     # the plans were on
+        assert all(pl["tc"] == tc for pl in sched.native_runner.target._cascade.values())
         po = [x for x in o if isinstance(x, ParticleOutput)][0]
         assert max(abs(w) for w in po.log_w_tilde) < 0.35, po.log_w_tilde
         assert sched.native_runner.check_status() == 0

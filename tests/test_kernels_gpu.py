@@ -389,9 +389,13 @@ def test_attention_fused(bs, E, Hq, Hkv, D, ctx, KS, rd, extras):
     (1, 8, 8, 1, 32, 8, 64, 1500, 300, 4, 2), (1, 8, 2, 9, 32, 8, 128, 2100, 200, 4, 1), (2, 4, 4, 2, 8, 2, 64, 700, 40, 2, 1),
     (1, 8, 8, 1, 32, 8, 64, 100, 1200, 1, 4), (1, 4, 2, 5, 8, 2, 128, 333, 0, 1, 1),
 ])
-def test_attention_shared_prefix_passes(groups, N, NP, E, Hq, Hkv, D, P, suffix, KSg, KSs):
+@pytest.mark.parametrize("tc", [False, "scattered", "runs"])
+def test_attention_shared_prefix_passes(groups, N, NP, E, Hq, Hkv, D, P, suffix, KSg, KSs, tc):
     """Shared-prefix attention: one pass over the prompt keys for NP particles at a time (state parked per token and
-    head), then the per-particle pass over the remaining keys folds it in.  Must equal plain causal attention."""
+    head), then the per-particle pass over the remaining keys folds it in.  Must equal plain causal attention.
+    ``tc``: the group pass runs on the tcgen05 kernel (one parked state per key split) instead of the mma.sync one,
+    with every prompt page scattered (row gather) or with the prompt in consecutive pages except for one shuffled
+    stretch (TMA tiles and gathered tiles in the same launch)."""
     K = _K()
     from smcsd_b200.models.layers import ExtendBatch, paged_attention_reference
     torch.manual_seed(13)
@@ -405,8 +409,16 @@ def test_attention_shared_prefix_passes(groups, N, NP, E, Hq, Hkv, D, P, suffix,
     bt = torch.zeros(bs + 2, P + suffix + E + 8, device=dev, dtype=torch.int32)
     off = 0
     shared = []
+    if tc == "runs":
+        # prompts take pages 1 .. groups * P in order; keys 128..191 of each are shuffled so that one tile is gathered
+        rest = torch.arange(groups * P, pages, device=dev)
+        perm = torch.cat([torch.arange(groups * P, device=dev), rest[torch.randperm(rest.numel(), device=dev)]])
+        perm = (perm + 1).to(torch.int32)
     for gi in range(groups):
-        shared.append(perm[off:off + P])
+        pg = perm[off:off + P].clone()
+        if tc == "runs" and P >= 192:
+            pg[128:192] = pg[128:192].flip(0)
+        shared.append(pg)
         off += P
     prefix = torch.zeros(bs, device=dev, dtype=torch.int32)
     for b in range(bs):
@@ -431,12 +443,22 @@ def test_attention_shared_prefix_passes(groups, N, NP, E, Hq, Hkv, D, P, suffix,
     n_super = bs // NP
     rows_g = rows[::NP].contiguous()
     shared_len = torch.full((bs,), P, device=dev, dtype=torch.int32)
-    K.attention_fused(qkv, pos, locs, table, kp, vp, bt, rows_g, shared_len[::NP].contiguous(), None, bs=n_super, E=NP * E,
-                      Hq=Hq, Hkv=Hkv, D=D, KS=KSg, scale=D ** -0.5, status=st, q_in=q.reshape(T, -1), part_out=state,
-                      causal=False)
     out = torch.zeros(T, Hq * D, device=dev, dtype=torch.bfloat16)
-    K.attention_fused(qkv, pos, locs, table, kp, vp, bt, rows, prefix, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D, KS=KSs,
-                      scale=D ** -0.5, status=st, q_in=q.reshape(T, -1), key_begin=shared_len, part_in=state)
+    if tc:
+        if D == 256:
+            pytest.skip("the tcgen05 pass is built for head sizes 64 and 128")
+        state = torch.full((KSg, T, Hq, D + 2), float("nan"), device=dev)
+        K.attention_prefix_tc(q.reshape(T, -1), kp, vp, bt, rows_g, shared_len[::NP].contiguous(), state, n_seq=n_super,
+                              E=NP * E, T=T, Hq=Hq, Hkv=Hkv, D=D, KS=KSg, scale=D ** -0.5, status=st)
+        K.attention_fused(qkv, pos, locs, table, kp, vp, bt, rows, prefix, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D, KS=KSs,
+                          scale=D ** -0.5, status=st, q_in=q.reshape(T, -1), key_begin=shared_len, part_in=state,
+                          part_in_n=KSg, part_in_stride=state.stride(0))
+    else:
+        K.attention_fused(qkv, pos, locs, table, kp, vp, bt, rows_g, shared_len[::NP].contiguous(), None, bs=n_super,
+                          E=NP * E, Hq=Hq, Hkv=Hkv, D=D, KS=KSg, scale=D ** -0.5, status=st, q_in=q.reshape(T, -1),
+                          part_out=state, causal=False)
+        K.attention_fused(qkv, pos, locs, table, kp, vp, bt, rows, prefix, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D, KS=KSs,
+                          scale=D ** -0.5, status=st, q_in=q.reshape(T, -1), key_begin=shared_len, part_in=state)
     torch.cuda.synchronize()
     assert int(st) == 0
     err = (out.float() - ref).abs().max().item()

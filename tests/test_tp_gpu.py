@@ -121,6 +121,89 @@ def test_tp_chain_emulated_ranks_match_single_rank(tp, bs, E):
         assert (nm._o[2] - lz).abs().max().item() < 2e-3
 
 
+@pytest.mark.parametrize("tp", [2, 4])
+def test_tp_prompt_pass_emulated_ranks_match_single_rank(tp):
+    """Prompt pass through the tensor-parallel chain (16-token blocks as batch rows, K/V written before attention):
+    every rank ends with the same normalised last-layer rows as the single-rank chain, and its K/V shard matches."""
+    from smcsd_b200.memory.pools import KVPool, KVSpec
+    from smcsd_b200.models.llama import LlamaModel
+    from smcsd_b200.ops import native as K
+    from smcsd_b200.ops.native_backend import NativeLlama
+    from smcsd_b200.ops.native_tp import NativeLlamaTP
+    from smcsd_b200.parallel.symm import FakeHeap
+    K.lib()
+    dev = torch.device("cuda")
+    cfg = _cfg()
+    B = 16
+    lens = [37, 16, 50]
+    n_blocks = [(L + B - 1) // B for L in lens]
+    bs = sum(n_blocks)
+    T = bs * B
+    n_pages = 512
+    bt = torch.zeros(16, 256, dtype=torch.int32, device=dev)
+    perm = (torch.randperm(n_pages, device=dev) + 1).to(torch.int32)
+    gen = torch.Generator().manual_seed(1)
+    ids = torch.zeros(T, dtype=torch.int32)
+    pos = torch.zeros(T, dtype=torch.int32)
+    locs = torch.zeros(T, dtype=torch.int32)
+    rows, pref, last = [], [], []
+    t = 0
+    for i, (L, nb) in enumerate(zip(lens, n_blocks)):
+        bt[i, :L] = perm[i * 64:i * 64 + L]
+        ids[t:t + L] = torch.randint(0, 8192, (L,), generator=gen, dtype=torch.int32)
+        pos[t:t + nb * B] = torch.arange(nb * B, dtype=torch.int32).clamp_(max=L - 1)
+        locs[t:t + L] = bt[i, :L].cpu()
+        rows += [i] * nb
+        pref += [j * B for j in range(nb)]
+        last.append(t + L - 1)
+        t += nb * B
+    ids, pos, locs = ids.to(dev), pos.to(dev), locs.to(dev)
+    rows = torch.tensor(rows, dtype=torch.int32, device=dev)
+    pref = torch.tensor(pref, dtype=torch.int32, device=dev)
+    last = torch.tensor(last, dtype=torch.long, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    full = LlamaModel(cfg, torch.bfloat16, dev).init_random(3)
+    kv_full = KVPool(KVSpec(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim), n_pages, dev)
+    ref = NativeLlama(full, kv_full, bt, T, 8, 8, status, False)
+    ref.set_context(max(lens), bs)
+    ref.forward(ids, pos, locs, rows, pref, bs, B, two_pass=True)
+    ref_rows = ref.final_hidden(last).float()
+    heap = FakeHeap(64 << 20, dev, tp)
+    ranks = []
+    for r in range(tp):
+        m = LlamaModel(cfg, torch.bfloat16, dev, tp_rank=r, tp_size=tp).init_random(3)
+        kv = KVPool(KVSpec(cfg.n_layers, m.n_kv_heads, cfg.head_dim), n_pages, dev)
+        h = FakeHeap.__new__(FakeHeap)
+        h.__dict__.update(heap.__dict__)
+        h._cursor = 0
+        nm = NativeLlamaTP(m, kv, bt, T, 8, 8, status, False, h,
+                           heap_view=lambda off, shape, dt, r=r: heap.view(r, off, shape, dt))
+        nm.set_context(max(lens), bs)
+        ranks.append(nm)
+    gens = [nm.stages(ids, pos, locs, rows, pref, bs, B, True) for nm in ranks]
+    while True:
+        done = 0
+        for g in gens:
+            try:
+                next(g)
+            except StopIteration:
+                done += 1
+        if done == tp:
+            break
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    scale = ref_rows.abs().max().item()
+    valid = locs.long()[ids.new_zeros(T, dtype=torch.bool).index_fill_(0, torch.cat([torch.arange(s0, s0 + L, device=dev) for s0, L in zip([0, 48, 64], lens)]), True)]
+    for r, nm in enumerate(ranks):
+        got = nm.xn_a[last].float()
+        assert (got - ref_rows).abs().max().item() < 0.05 * scale
+        w = nm.nkv * cfg.head_dim
+        for li in range(cfg.n_layers):
+            a = nm.kv.k[li][valid].float()
+            b = kv_full.k[li][valid][:, r * w:(r + 1) * w].float()
+            assert (a - b).abs().max().item() < 0.06 * max(1.0, b.abs().max().item())
+
+
 def test_bounded_peer_wait_times_out_and_reports():
     """A counter that no peer ever bumps: the wait gives up after about a second, sets the status
     bit and returns, and the context stays usable."""
