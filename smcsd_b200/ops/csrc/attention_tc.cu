@@ -76,18 +76,6 @@ __device__ __forceinline__ bool tc_wait(TcShared& S, int* status, uint64_t* bar,
   }
 }
 
-// MN-major operand tile stored as panels of [rows = K index][64 MN elements = 128 bytes] with the 128-byte swizzle:
-// 8-row groups 1024 bytes apart (stride byte offset), panels `lbo` bytes apart (leading byte offset).
-__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t saddr, uint32_t lbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -209,7 +209,19 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t saddr) {
   d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
   return d;
 }
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, shape M x N x 16.
+// MN-major operand tile stored as panels of [rows = K index][64 MN elements = 128 bytes] with the 128-byte swizzle:
+// 8-row groups 1024 bytes apart (stride byte offset), panels `lbo` bytes apart (leading byte offset).
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t saddr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, shape M x N x 16 (bit 16 set by the caller
+// marks the B operand as MN-major).
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }

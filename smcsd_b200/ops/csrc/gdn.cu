@@ -38,6 +38,53 @@ __global__ void gdn_conv_kernel(const float* __restrict__ proj, int ldp, float* 
   for (int i = 0; i < W - 1; ++i) win[i] = hist[i];
 }
 
+// Prompt-pass form of the conv: the output at token t only needs inputs t-W+1 .. t, so tokens are processed in
+// parallel, CONV_TILE per thread.  grid.x covers the channels, grid.y the row's token tiles, grid.z the rows.  The thread
+// of a row's first tile is the only one that touches the row's window in the state pool: it reads the old window and
+// writes the new one (the row's last W-1 inputs).
+constexpr int CONV_TILE = 16;
+__global__ void gdn_conv_prefill_kernel(const float* __restrict__ proj, int ldp, float* __restrict__ conv_state,
+                                        const int* __restrict__ state_rows, const __nv_bfloat16* __restrict__ conv_w,
+                                        float* __restrict__ conv_out, int conv_dim, int W,
+                                        const int* __restrict__ tok_off, const int* __restrict__ tok_len, int pdl) {
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
+  const int ch = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.z;
+  const int len = tok_len[b], e0 = blockIdx.y * CONV_TILE;
+  if (ch >= conv_dim || e0 >= len) return;
+  const size_t t0 = (size_t)tok_off[b];
+  float* win = conv_state + ((size_t)state_rows[b] * conv_dim + ch) * (W - 1);
+  float w[8], hist[8];
+  for (int i = 0; i < W; ++i) w[i] = __bfloat162float(conv_w[ch * W + i]);
+  // inputs e0-W+1 .. e0-1: from the row itself, or from the old window for tokens before the row's first
+  for (int i = 0; i < W - 1; ++i) {
+    const int e = e0 - (W - 1) + i;
+    hist[i] = e >= 0 ? proj[(t0 + e) * ldp + ch] : win[W - 1 + e];
+  }
+  if (e0 == 0) {
+    // new window = inputs len-W+1 .. len-1 (old window entries where the row is shorter than the window)
+    float nw[8];
+    for (int i = 0; i < W - 1; ++i) {
+      const int e = len - (W - 1) + i;
+      nw[i] = e >= 0 ? proj[(t0 + e) * ldp + ch] : win[W - 1 + e];
+    }
+    for (int i = 0; i < W - 1; ++i) win[i] = nw[i];
+  }
+  // all of the tile's inputs first (independent loads in flight together), then the window arithmetic
+  float xin[CONV_TILE];
+#pragma unroll
+  for (int u = 0; u < CONV_TILE; ++u) xin[u] = e0 + u < len ? proj[(t0 + e0 + u) * ldp + ch] : 0.f;
+#pragma unroll
+  for (int u = 0; u < CONV_TILE; ++u) {
+    if (e0 + u >= len) break;
+    const float x = xin[u];
+    float acc = w[W - 1] * x;
+    for (int i = 0; i < W - 1; ++i) acc += w[i] * hist[i];
+    for (int i = 0; i + 1 < W - 1; ++i) hist[i] = hist[i + 1];
+    hist[W - 2] = x;
+    conv_out[(t0 + e0 + u) * conv_dim + ch] = acc / (1.f + __expf(-acc));
+  }
+}
+
 template <int DK>
 __global__ void gdn_recurrent_kernel(const float* __restrict__ conv_out, const float* __restrict__ proj, int ldp,
                                      float* __restrict__ temporal, const int* __restrict__ state_rows,
@@ -132,6 +179,38 @@ __global__ void gdn_recurrent_kernel(const float* __restrict__ conv_out, const f
 
 }  // namespace smc
 
+// Conv + SiLU pass alone (rows as in smc_gdn_varlen); the chunk-parallel delta-rule kernel consumes conv_out.
+// max_len: upper bound of tok_len known on the host (0 = unknown): rows longer than two token tiles use the
+// token-parallel conv kernel.
+SMC_API int smc_gdn_conv(const float* proj, int ldp, float* conv_state, const int* state_rows, const void* conv_w,
+                         float* conv_out, int bs, int E, const int* tok_off, const int* tok_len, int conv_dim, int W,
+                         int max_len, int pdl, cudaStream_t st) {
+  using namespace smc;
+  if ((tok_off == nullptr) != (tok_len == nullptr)) return -103;
+  if (bs <= 0) return 0;
+  if (W < 2 || W > 8) return -100;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  if (tok_len != nullptr && max_len > 2 * CONV_TILE && bs <= 65535) {
+    // long rows: token-parallel form
+    cfg.gridDim = dim3((conv_dim + 255) / 256, (max_len + CONV_TILE - 1) / CONV_TILE, bs);
+    cfg.blockDim = dim3(256);
+    CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_conv_prefill_kernel, proj, ldp, conv_state, state_rows,
+                                      (const __nv_bfloat16*)conv_w, conv_out, conv_dim, W, tok_off, tok_len, pdl));
+    return 0;
+  }
+  cfg.gridDim = dim3((bs * conv_dim + 255) / 256);
+  cfg.blockDim = dim3(256);
+  CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_conv_kernel, proj, ldp, conv_state, state_rows,
+                                    (const __nv_bfloat16*)conv_w, conv_out, bs, E, conv_dim, W, tok_off, tok_len, pdl));
+  return 0;
+}
+
 // Rows of variable length (prompt passes): row b covers tokens [tok_off[b], tok_off[b] + tok_len[b]) of the
 // token-major buffers.  With tok_off == tok_len == null every row has E tokens laid out back to back.
 SMC_API int smc_gdn_varlen(const float* proj, int ldp, float* conv_state, float* temporal, const int* state_rows,
@@ -143,6 +222,11 @@ SMC_API int smc_gdn_varlen(const float* proj, int ldp, float* conv_state, float*
   if (bs <= 0) return 0;
   if (W < 2 || W > 8 || Hv % Hk || dv > 256 || dk > 256) return -100;
   const int conv_dim = 2 * Hk * dk + Hv * dv;
+  {
+    const int rc = smc_gdn_conv(proj, ldp, conv_state, state_rows, conv_w, conv_out, bs, E, tok_off, tok_len, conv_dim,
+                                W, 0, pdl, st);
+    if (rc) return rc;
+  }
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -150,10 +234,6 @@ SMC_API int smc_gdn_varlen(const float* proj, int ldp, float* conv_state, float*
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  cfg.gridDim = dim3((bs * conv_dim + 255) / 256);
-  cfg.blockDim = dim3(256);
-  CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_conv_kernel, proj, ldp, conv_state, state_rows,
-                                    (const __nv_bfloat16*)conv_w, conv_out, bs, E, conv_dim, W, tok_off, tok_len, pdl));
   int threads = dv > dk ? dv : dk;
   threads = (threads + 31) / 32 * 32;
   if (threads > 128) return -101;

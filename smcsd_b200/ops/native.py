@@ -462,23 +462,49 @@ def tp_wait_counter(flag_ptr: int, want: int, outcome: torch.Tensor, status: tor
 
 
 # ----------------------------------------------------------------------------- gated delta net
+GDN_CHUNK_MIN_TOKENS = 64      # rows at least this long (on average) take the chunk-parallel tensor-core kernel
+
+
 def gdn_step(proj: torch.Tensor, conv_state: torch.Tensor, temporal: torch.Tensor, state_rows: torch.Tensor,
              conv_w: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, gnorm_w: torch.Tensor,
              conv_out: torch.Tensor, out: torch.Tensor, *, bs: int, E: int, Hk: int, Hv: int, dk: int, dv: int, W: int,
              eps: float, pdl: bool = False, tok_off: Optional[torch.Tensor] = None,
-             tok_len: Optional[torch.Tensor] = None) -> None:
+             tok_len: Optional[torch.Tensor] = None, chunked: bool = False, status: Optional[torch.Tensor] = None,
+             max_len: int = 0, trace: Optional[torch.Tensor] = None) -> None:
     """Conv + gated delta rule + gated RMSNorm for E new tokens per row; advances the state of one layer in place.
     conv_state [rows, conv_dim, W-1] fp32 and temporal [rows, Hv, dk, dv] fp32 are that layer's slices.
-    ``tok_off`` / ``tok_len`` (int32 per row) give rows of different lengths at arbitrary token offsets."""
+    ``tok_off`` / ``tok_len`` (int32 per row) give rows of different lengths at arbitrary token offsets.
+    ``chunked`` (prompt passes, dk = dv = 128): the delta rule runs chunk-parallel on tcgen05 (64 tokens per step)
+    instead of token by token; ``status`` receives its error bits; ``max_len`` (host-side bound of ``tok_len``) lets
+    the conv pass run token-parallel as well; ``trace`` (int64 [10]) accumulates the cycles the first CTA of the
+    chunk-parallel kernel spends per phase."""
     L = lib()
     if not getattr(L, "_gdn_declared", False):
         vp, i, f = C.c_void_p, C.c_int, C.c_float
         L.smc_gdn_varlen.argtypes = [vp, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp, vp, i, i, i, i, i, f, i, vp]
         L.smc_gdn_varlen.restype = C.c_int
+        L.smc_gdn_conv.argtypes = [vp, i, vp, vp, vp, vp, i, i, vp, vp, i, i, i, i, vp]
+        L.smc_gdn_conv.restype = C.c_int
+        L.smc_gdn_chunked.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, vp, i, i, vp, vp, i, i, i, i, f, vp, vp, i, vp]
+        L.smc_gdn_chunked.restype = C.c_int
         L._gdn_declared = True
+    if chunked and gdn_chunked_supported(dk, dv):
+        if status is None:
+            raise ValueError("the chunk-parallel kernel needs a status word")
+        conv_dim = 2 * Hk * dk + Hv * dv
+        _check(L.smc_gdn_conv(_p(proj), proj.stride(0), _p(conv_state), _p(state_rows), _p(conv_w), _p(conv_out), bs, E,
+                              _p(tok_off), _p(tok_len), conv_dim, W, int(max_len), int(pdl), _stream()), "smc_gdn_conv")
+        _check(L.smc_gdn_chunked(_p(conv_out), _p(proj), proj.stride(0), _p(temporal), _p(state_rows), _p(dt_bias),
+                                 _p(A_log), _p(gnorm_w), _p(out), bs, E, _p(tok_off), _p(tok_len), Hk, Hv, dk, dv, eps,
+                                 _p(status), _p(trace), int(pdl), _stream()), "smc_gdn_chunked")
+        return
     _check(L.smc_gdn_varlen(_p(proj), proj.stride(0), _p(conv_state), _p(temporal), _p(state_rows), _p(conv_w),
                             _p(dt_bias), _p(A_log), _p(gnorm_w), _p(conv_out), _p(out), bs, E, _p(tok_off),
                             _p(tok_len), Hk, Hv, dk, dv, W, eps, int(pdl), _stream()), "smc_gdn_varlen")
+
+
+def gdn_chunked_supported(dk: int, dv: int) -> bool:
+    return dk == 128 and dv == 128
 
 
 _KERNELS_PER_CALL["smc_gdn_step"] = 2

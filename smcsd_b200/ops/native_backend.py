@@ -599,7 +599,7 @@ class NativeRunner:
             return {"seqs": {"rows": pin(torch.tensor([it.row for it in items], dtype=torch.int32)),
                              "off": pin(torch.tensor(offs, dtype=torch.int32)),
                              "len": pin(torch.tensor([max(L - short, 0) for L in lens], dtype=torch.int32)),
-                             "n": len(items)}}
+                             "n": len(items), "max": max(lens)}}
         cb = max(1, min(nm.T for nm in (tgt, drf)) // B)     # blocks per pass
         last = torch.tensor(last_rows, dtype=torch.long, device=dev)
 

@@ -3,11 +3,12 @@
 Attention layers reuse the fused attention step (per-head q/k RMSNorm, partial rotary, sigmoid
 output gate all inside that kernel); Gated-DeltaNet layers run in-projection GEMM -> conv + SiLU ->
 recurrent delta-rule step with gated RMSNorm -> out-projection GEMM accumulating into the residual
-stream.  The recurrent state lives in the state pool and follows particles through resampling by
+stream; prompt passes replace the token-by-token delta rule by the chunk-parallel tcgen05 kernel.  The recurrent state lives in the state pool and follows particles through resampling by
 the same (dst, src) job list as the KV block table.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict
 
 import torch
@@ -46,6 +47,9 @@ class NativeHybrid:
         if not self.fuse_swiglu:
             self.gu = torch.empty(max_tokens, 2 * self.ffn, dtype=f32, device=dev)
         self._splits_cache: Dict = {}
+        # prompt passes of at least 64 tokens per row run the delta rule chunk-parallel on tcgen05 (SMC_GDN_CHUNKED=0:
+        # token by token, as the decode steps do)
+        self.gdn_chunked = os.environ.get("SMC_GDN_CHUNKED", "1") != "0"
 
     def _gemm(self, W, X, out, M, epi, ldo=None):
         N, Kd = W.shape
@@ -102,7 +106,9 @@ class NativeHybrid:
                     K.gdn_step(self.qkv, self.state.conv[si], self.state.temporal[si], seqs["rows"], L.conv_w,
                                L.dt_bias, L.A_log, L.gnorm_w, self.conv_out, mix, bs=seqs["n"], E=0,
                                Hk=c.gdn_n_k_heads, Hv=c.gdn_n_v_heads, dk=c.gdn_head_k_dim, dv=c.gdn_head_v_dim,
-                               W=c.gdn_conv_width, eps=c.rms_eps, pdl=pdl, tok_off=seqs["off"], tok_len=seqs["len"])
+                               W=c.gdn_conv_width, eps=c.rms_eps, pdl=pdl, tok_off=seqs["off"], tok_len=seqs["len"],
+                               chunked=self.gdn_chunked and T >= K.GDN_CHUNK_MIN_TOKENS * seqs["n"], status=self.status,
+                               max_len=seqs.get("max", 0))
                 else:
                     K.gdn_step(self.qkv, self.state.conv[si], self.state.temporal[si], rows, L.conv_w, L.dt_bias,
                                L.A_log, L.gnorm_w, self.conv_out, mix, bs=bs, E=E, Hk=c.gdn_n_k_heads,

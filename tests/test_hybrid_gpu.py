@@ -5,12 +5,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _hybrid_cfg():
+def _hybrid_cfg(gdn_dim: int = 64):
     from smcsd_b200.models.config import ModelConfig
     lt = ["linear_attention", "linear_attention", "linear_attention", "full_attention"] * 2
     return ModelConfig(arch="hybrid_gdn", vocab_size=8192, hidden_size=512, n_layers=8, n_heads=4, n_kv_heads=2,
                        head_dim=128, ffn_size=1024, rope_theta=10000.0, max_position=2048, layer_types=lt,
-                       gdn_n_k_heads=2, gdn_n_v_heads=4, gdn_head_k_dim=64, gdn_head_v_dim=64, gdn_conv_width=4,
+                       gdn_n_k_heads=2, gdn_n_v_heads=4, gdn_head_k_dim=gdn_dim, gdn_head_v_dim=gdn_dim, gdn_conv_width=4,
                        partial_rotary=0.25, attn_output_gate=True, qk_norm=True, norm_plus_one=True, rms_eps=1e-6,
                        name="hybrid-test")
 
@@ -102,22 +102,25 @@ def test_hybrid_state_follows_resampling_native():
     assert sched.native_runner.check_status() == 0
 
 
-def test_native_hybrid_prefill_matches_torch_prefill():
+@pytest.mark.parametrize("gdn_dim,lens", [(64, [37, 16, 5, 70]), (128, [137, 16, 5, 270])])
+def test_native_hybrid_prefill_matches_torch_prefill(gdn_dim, lens):
     """Prompt pass of a hybrid target and a hybrid draft through the kernel chains (attention layers over 16-token
     blocks, Gated-DeltaNet layers walking each prompt once) vs the plain PyTorch forward: same cache contents and
-    the same recurrent state, the draft's one token short under the deferred schedule."""
+    the same recurrent state, the draft's one token short under the deferred schedule.  With 128 x 128 heads and
+    long prompts the Gated-DeltaNet layers take the chunk-parallel tcgen05 kernel."""
     from smcsd_b200.config import EngineArgs
     from smcsd_b200.models import build_model
     from smcsd_b200.runtime.scheduler import SMCScheduler
     from smcsd_b200.runtime.worker import PrefillItem
-    cfg = _hybrid_cfg()
+    cfg = _hybrid_cfg(gdn_dim)
     model = build_model(cfg, torch.bfloat16, "cuda", seed=0)
     args = EngineArgs(model_path=cfg, draft_model_path=cfg, n_particles=4, gamma=3, max_running_requests=4,
                       context_length=512, device="cuda", max_total_tokens=8192, backend="native",
                       cycle_graph=False).finalize()
     s = SMCScheduler(args, target=model, draft=model)
     r = s.native_runner
-    lens = [37, 16, 5, 70]
+    if gdn_dim == 128:
+        assert r.target.gdn_chunked
     g = torch.Generator().manual_seed(4)
     items = []
     for L in lens:
@@ -154,3 +157,77 @@ def test_native_hybrid_prefill_matches_torch_prefill():
         assert err < 0.05 * max(1.0, x.abs().max().item()), (name, err)
     # the two pools must differ: the draft's state stops one token before the target's
     assert (s.state_t.temporal[:, rows] - s.state_d.temporal[:, rows]).abs().max().item() > 0
+
+
+@pytest.mark.parametrize("lens", [[150, 64, 1, 300], [512, 37]])
+def test_gdn_chunked_prefill_kernel_matches_recurrence(lens):
+    """Chunk-parallel delta rule on tcgen05 (64 tokens per step, dk = dv = 128) against the token-by-token recurrence in
+    fp32 PyTorch and against the token-serial kernel: outputs after the gated RMSNorm and the final recurrent state,
+    from a non-zero initial state, rows of different lengths (partial last chunks, a single-token row)."""
+    import torch.nn.functional as F
+    from smcsd_b200.models.hybrid_gdn import gdn_recurrent_step
+    from smcsd_b200.ops import native as K
+    torch.manual_seed(5)
+    dev = "cuda"
+    Hk, Hv, dk, dv, W, eps = 2, 4, 128, 128, 4, 1e-6
+    key_dim, value_dim = Hk * dk, Hv * dv
+    conv_dim = 2 * key_dim + value_dim
+    ldp = conv_dim + value_dim + 2 * Hv
+    ldp += (-ldp) % 8
+    T, bs = sum(lens), len(lens)
+    proj = torch.randn(T, ldp, device=dev)
+    proj[:, conv_dim + value_dim:] *= 2.0                        # spread the gates
+    conv_w = (torch.randn(conv_dim, W, device=dev) * 0.3).bfloat16()
+    dt_bias = torch.ones(Hv, device=dev)
+    A_log = torch.log(torch.empty(Hv, device=dev).uniform_(0.5, 8.0))
+    gnorm_w = (1.0 + 0.1 * torch.randn(dv, device=dev)).bfloat16()
+    rows = torch.tensor([3, 0, 2, 5][:bs], dtype=torch.int32, device=dev)
+    conv0 = torch.randn(8, conv_dim, W - 1, device=dev) * 0.5
+    temp0 = torch.randn(8, Hv, dk, dv, device=dev) * 0.2
+    off = torch.tensor([sum(lens[:i]) for i in range(bs)], dtype=torch.int32, device=dev)
+    ln = torch.tensor(lens, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    # fp32 reference
+    ref_out = torch.zeros(T, value_dim, device=dev)
+    ref_temp = temp0.clone()
+    rep = Hv // Hk
+    for b, n in enumerate(lens):
+        t0, r = int(off[b]), int(rows[b])
+        seq = torch.cat([conv0[r], proj[t0:t0 + n, :conv_dim].t()], dim=1)
+        conv = F.silu(F.conv1d(seq.unsqueeze(0), conv_w.float().unsqueeze(1), groups=conv_dim).squeeze(0)).t()
+        q = conv[:, :key_dim].reshape(n, Hk, dk)
+        k = conv[:, key_dim:2 * key_dim].reshape(n, Hk, dk)
+        v = conv[:, 2 * key_dim:].reshape(n, Hv, dv)
+        q = (q * torch.rsqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5).repeat_interleave(rep, dim=1)
+        k = (k * torch.rsqrt((k * k).sum(-1, keepdim=True) + 1e-6)).repeat_interleave(rep, dim=1)
+        z = proj[t0:t0 + n, conv_dim:conv_dim + value_dim].view(n, Hv, dv)
+        beta = torch.sigmoid(proj[t0:t0 + n, conv_dim + value_dim:conv_dim + value_dim + Hv])
+        g = -A_log.exp() * F.softplus(proj[t0:t0 + n, conv_dim + value_dim + Hv:conv_dim + value_dim + 2 * Hv] + dt_bias)
+        S = ref_temp[r].clone()
+        for t in range(n):
+            S, o = gdn_recurrent_step(S, q[t], k[t], v[t], g[t], beta[t])
+            y = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps)
+            ref_out[t0 + t] = (y.bfloat16().float() * gnorm_w.float() * F.silu(z[t])).reshape(-1)
+        ref_temp[r] = S
+
+    got = {}
+    for chunked in (False, True):
+        conv_s, temp_s = conv0.clone(), temp0.clone()
+        conv_out = torch.zeros(T, conv_dim, device=dev)
+        out = torch.zeros(T, value_dim, device=dev, dtype=torch.bfloat16)
+        K.gdn_step(proj, conv_s, temp_s, rows, conv_w, dt_bias, A_log, gnorm_w, conv_out, out, bs=bs, E=0, Hk=Hk, Hv=Hv,
+                   dk=dk, dv=dv, W=W, eps=eps, tok_off=off, tok_len=ln, chunked=chunked, status=status,
+                   max_len=max(lens) if chunked else 0)
+        torch.cuda.synchronize()
+        assert int(status) == 0
+        got[chunked] = (out.float(), temp_s)
+    o_scale, s_scale = ref_out.abs().max().item(), ref_temp.abs().max().item()
+    for chunked in (False, True):
+        o, s = got[chunked]
+        tol = 2e-2 if chunked else 1e-2                           # bf16 operands in the chunked form, fp32 otherwise
+        assert (o - ref_out).abs().max().item() < tol * o_scale, (chunked, (o - ref_out).abs().max().item(), o_scale)
+        assert (s - ref_temp).abs().max().item() < tol * s_scale, (chunked, (s - ref_temp).abs().max().item(), s_scale)
+    used = [int(r) for r in rows]
+    untouched = [r for r in range(8) if r not in used]
+    assert torch.equal(got[True][1][untouched], temp0[untouched])
