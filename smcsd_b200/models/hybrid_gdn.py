@@ -107,26 +107,30 @@ class HybridGDNModel:
 
     def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", tp_rank: int = 0, tp_size: int = 1,
                  max_positions: Optional[int] = None):
-        if tp_size != 1:
-            raise NotImplementedError("hybrid models run replicated (particle- or data-parallel), not tensor-parallel")
         self.cfg, self.dtype, self.device = cfg, dtype, torch.device(device)
-        self.tp_rank, self.tp_size = 0, 1
-        self.n_heads, self.n_kv_heads, self.ffn = cfg.n_heads, cfg.n_kv_heads, cfg.ffn_size
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+        w = tp_size
+        if cfg.n_heads % w or cfg.n_kv_heads % w or cfg.ffn_size % w or cfg.gdn_n_k_heads % w or cfg.gdn_n_v_heads % w:
+            raise ValueError("tensor-parallel size must divide the attention, KV, Gated-DeltaNet head counts and the FFN size")
+        # per-rank shares: attention heads, KV heads, Gated-DeltaNet key / value heads, FFN channels, vocabulary rows
+        self.n_heads, self.n_kv_heads, self.ffn = cfg.n_heads // w, cfg.n_kv_heads // w, cfg.ffn_size // w
+        self.gdn_k_heads, self.gdn_v_heads = cfg.gdn_n_k_heads // w, cfg.gdn_n_v_heads // w
+        self.vocab_shard = (cfg.vocab_size + w - 1) // w
         self.gu_block = 64 if self.ffn % 64 == 0 else self.ffn
         self.layers: List[HybridLayerWeights] = []
         self.embed = self.lm_head = self.final_norm = None
         mp = min(max_positions or cfg.max_position, cfg.max_position)
         self.rope = rope_table(cfg.rotary_dim, cfg.rope_theta, cfg.rope_scaling, mp, self.device)
-        self.tp_group = None
+        self.tp_group = None                              # torch.distributed group of the tensor-parallel ranks
         self.kv_index = {li: i for i, li in enumerate(cfg.attn_layers)}
         self.state_index = {li: i for i, li in enumerate(cfg.gdn_layers)}
-        self.key_dim = cfg.gdn_n_k_heads * cfg.gdn_head_k_dim
-        self.value_dim = cfg.gdn_n_v_heads * cfg.gdn_head_v_dim
+        self.key_dim = self.gdn_k_heads * cfg.gdn_head_k_dim
+        self.value_dim = self.gdn_v_heads * cfg.gdn_head_v_dim
         self.conv_dim = 2 * self.key_dim + self.value_dim
 
     def state_spec(self) -> StateSpec:
         c = self.cfg
-        return StateSpec(len(c.gdn_layers), self.conv_dim, c.gdn_conv_width, c.gdn_n_v_heads, c.gdn_head_k_dim,
+        return StateSpec(len(c.gdn_layers), self.conv_dim, c.gdn_conv_width, self.gdn_v_heads, c.gdn_head_k_dim,
                          c.gdn_head_v_dim, conv_dtype=torch.float32, state_dtype=torch.float32)
 
     def all_tensors(self):
@@ -147,29 +151,66 @@ class HybridGDNModel:
         return n
 
     # ---- construction ---------------------------------------------------------------
+    def _rows(self, w: torch.Tensor, n_units: int) -> torch.Tensor:
+        """This rank's share of a tensor whose leading dimension is ``n_units`` equal blocks (heads, channels)."""
+        if self.tp_size == 1:
+            return w
+        per = w.shape[0] // n_units * (n_units // self.tp_size)
+        return w[self.tp_rank * per:(self.tp_rank + 1) * per]
+
+    def _cols(self, w: torch.Tensor, n_units: int) -> torch.Tensor:
+        if self.tp_size == 1:
+            return w
+        per = w.shape[1] // n_units * (n_units // self.tp_size)
+        return w[:, self.tp_rank * per:(self.tp_rank + 1) * per]
+
+    def _shard_vocab(self, head: torch.Tensor) -> torch.Tensor:
+        if self.tp_size == 1:
+            return head
+        lo = self.tp_rank * self.vocab_shard
+        hi = min(lo + self.vocab_shard, head.shape[0])
+        out = torch.zeros(self.vocab_shard, head.shape[1], dtype=head.dtype, device=head.device)
+        if hi > lo:
+            out[:hi - lo] = head[lo:hi]
+        return out
+
     def _pack_attn(self, ln1, ln2, wg, wu, wd, q_proj, k_proj, v_proj, o_proj, q_norm, k_norm) -> HybridLayerWeights:
+        """Arguments are the full (unsharded) tensors; the rank keeps its heads / FFN channels."""
         c = self.cfg
-        H, D = c.n_heads, c.head_dim
+        H, Hkv, D = c.n_heads, c.n_kv_heads, c.head_dim
+        k_proj, v_proj, o_proj = self._rows(k_proj, Hkv), self._rows(v_proj, Hkv), self._cols(o_proj, H)
         if c.attn_output_gate:
-            qp = q_proj.view(H, 2, D, -1)         # HF stores [query | gate] per head
-            q_rows, gate_rows = qp[:, 0].reshape(H * D, -1), qp[:, 1].reshape(H * D, -1)
+            qp = self._rows(q_proj, H).view(self.n_heads, 2, D, -1)         # HF stores [query | gate] per head
+            q_rows, gate_rows = qp[:, 0].reshape(self.n_heads * D, -1), qp[:, 1].reshape(self.n_heads * D, -1)
             wqkv = torch.cat([q_rows, gate_rows, k_proj, v_proj], dim=0).contiguous()
         else:
-            wqkv = torch.cat([q_proj, k_proj, v_proj], dim=0).contiguous()
+            wqkv = torch.cat([self._rows(q_proj, H), k_proj, v_proj], dim=0).contiguous()
+        wg, wu, wd = self._rows(wg, self.tp_size), self._rows(wu, self.tp_size), self._cols(wd, self.tp_size)
         return HybridLayerWeights("full_attention", ln1.contiguous(), ln2.contiguous(),
                                   interleave_gate_up(wg.contiguous(), wu.contiguous(), self.gu_block), wd.contiguous(),
                                   wqkv=wqkv, q_norm=q_norm.contiguous(), k_norm=k_norm.contiguous(),
                                   wo=o_proj.contiguous())
 
     def _pack_gdn(self, ln1, ln2, wg, wu, wd, w_qkv, w_z, w_b, w_a, conv_w, dt_bias, A_log, gnorm_w, w_out):
-        win = torch.cat([w_qkv, w_z, w_b, w_a], dim=0)
+        """Arguments are the full tensors.  A rank keeps its key heads' q and k channels and its value heads' v, z,
+        b, a channels (of the in-projection and of the depthwise conv alike) and the matching out-projection columns."""
+        c = self.cfg
+        Hk, Hv = c.gdn_n_k_heads, c.gdn_n_v_heads
+        kd, vd = Hk * c.gdn_head_k_dim, Hv * c.gdn_head_v_dim
+
+        def mixed(t):           # [q | k | v] channel blocks of the conv input
+            return torch.cat([self._rows(t[:kd], Hk), self._rows(t[kd:2 * kd], Hk), self._rows(t[2 * kd:], Hv)], dim=0)
+        win = torch.cat([mixed(w_qkv), self._rows(w_z, Hv), self._rows(w_b, Hv), self._rows(w_a, Hv)], dim=0)
         pad = (-win.shape[0]) % 8
         if pad:                                    # keep the row count friendly to 16-byte tiles
             win = torch.cat([win, torch.zeros(pad, win.shape[1], dtype=win.dtype, device=win.device)], dim=0)
+        wg, wu, wd = self._rows(wg, self.tp_size), self._rows(wu, self.tp_size), self._cols(wd, self.tp_size)
         return HybridLayerWeights("linear_attention", ln1.contiguous(), ln2.contiguous(),
                                   interleave_gate_up(wg.contiguous(), wu.contiguous(), self.gu_block), wd.contiguous(),
-                                  win=win.contiguous(), conv_w=conv_w.contiguous(), dt_bias=dt_bias.float().contiguous(),
-                                  A_log=A_log.float().contiguous(), gnorm_w=gnorm_w.contiguous(), wout=w_out.contiguous())
+                                  win=win.contiguous(), conv_w=mixed(conv_w).contiguous(),
+                                  dt_bias=self._rows(dt_bias.float(), Hv).contiguous(),
+                                  A_log=self._rows(A_log.float(), Hv).contiguous(), gnorm_w=gnorm_w.contiguous(),
+                                  wout=self._cols(w_out, Hv).contiguous())
 
     def init_random(self, seed: int = 0, std: float = 0.02) -> "HybridGDNModel":
         c = self.cfg
@@ -181,6 +222,8 @@ class HybridGDNModel:
             return (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * scale).to(dt)
 
         d, f = c.hidden_size, c.ffn_size
+        kd_full, vd_full = c.gdn_n_k_heads * c.gdn_head_k_dim, c.gdn_n_v_heads * c.gdn_head_v_dim
+        conv_full = 2 * kd_full + vd_full
         self.embed = rnd(c.vocab_size, d)
         self.final_norm = torch.zeros(d, dtype=dt, device=dev)
         for li in range(c.n_layers):
@@ -195,10 +238,11 @@ class HybridGDNModel:
                 Hv = c.gdn_n_v_heads
                 A = torch.empty(Hv, device=dev).uniform_(0.5, 8.0, generator=g)
                 self.layers.append(self._pack_gdn(
-                    ln1, ln2, wg, wu, wd, rnd(self.conv_dim, d), rnd(self.value_dim, d), rnd(Hv, d), rnd(Hv, d),
-                    rnd(self.conv_dim, c.gdn_conv_width, scale=0.3), torch.ones(Hv, device=dev), torch.log(A),
-                    torch.ones(c.gdn_head_v_dim, dtype=dt, device=dev), rnd(d, self.value_dim)))
-        self.lm_head = self.embed if c.tie_embeddings else rnd(c.vocab_size, d)
+                    ln1, ln2, wg, wu, wd, rnd(conv_full, d), rnd(vd_full, d), rnd(Hv, d), rnd(Hv, d),
+                    rnd(conv_full, c.gdn_conv_width, scale=0.3), torch.ones(Hv, device=dev), torch.log(A),
+                    torch.ones(c.gdn_head_v_dim, dtype=dt, device=dev), rnd(d, vd_full)))
+        head = self.embed if c.tie_embeddings else rnd(c.vocab_size, d)
+        self.lm_head = head if self.tp_size == 1 else self._shard_vocab(head)
         return self
 
     def load_hf(self, path: str) -> "HybridGDNModel":
@@ -228,10 +272,10 @@ class HybridGDNModel:
                     get(a + "A_log", torch.float32), get(a + "norm.weight"), get(a + "out_proj.weight")))
         for cand in ("lm_head.weight", "language_model.lm_head.weight"):
             if cand in ck and not c.tie_embeddings:
-                self.lm_head = get(cand)
+                self.lm_head = self._shard_vocab(get(cand))
                 break
         else:
-            self.lm_head = self.embed
+            self.lm_head = self.embed if self.tp_size == 1 else self._shard_vocab(self.embed)
         ck.close()
         return self
 
@@ -239,7 +283,7 @@ class HybridGDNModel:
     def _gdn_layer(self, L: HybridLayerWeights, x: torch.Tensor, batch: ExtendBatch, state, si: int) -> torch.Tensor:
         """x [T, d] normalised input; returns the mixer output [T, d] and advances the recurrent state."""
         c = self.cfg
-        Hk, Hv, dk, dv, W = c.gdn_n_k_heads, c.gdn_n_v_heads, c.gdn_head_k_dim, c.gdn_head_v_dim, c.gdn_conv_width
+        Hk, Hv, dk, dv, W = self.gdn_k_heads, self.gdn_v_heads, c.gdn_head_k_dim, c.gdn_head_v_dim, c.gdn_conv_width
         proj = (x @ L.win.t()).float()
         mixed = proj[:, :self.conv_dim]
         z = proj[:, self.conv_dim:self.conv_dim + self.value_dim].view(-1, Hv, dv)
@@ -286,7 +330,7 @@ class HybridGDNModel:
 
     def _attn_layer(self, L: HybridLayerWeights, x, batch: ExtendBatch, kv, block_table, ki: int) -> torch.Tensor:
         c = self.cfg
-        T, H, Hkv, D = x.shape[0], c.n_heads, c.n_kv_heads, c.head_dim
+        T, H, Hkv, D = x.shape[0], self.n_heads, self.n_kv_heads, c.head_dim
         qkv = x @ L.wqkv.t()
         nq = H * D
         off = 2 * nq if c.attn_output_gate else nq
@@ -312,16 +356,29 @@ class HybridGDNModel:
         for li, L in enumerate(self.layers):
             x = rmsnorm(h, L.ln1, c.rms_eps, plus_one=c.norm_plus_one)
             if L.kind == "full_attention":
-                h = h + self._attn_layer(L, x, batch, kv, block_table, self.kv_index[li])
+                h = h + self._all_reduce(self._attn_layer(L, x, batch, kv, block_table, self.kv_index[li]))
             else:
-                h = h + self._gdn_layer(L, x, batch, state, self.state_index[li])
+                h = h + self._all_reduce(self._gdn_layer(L, x, batch, state, self.state_index[li]))
             x = rmsnorm(h, L.ln2, c.rms_eps, plus_one=c.norm_plus_one)
             gate, up = split_gate_up(x @ L.wgu.t(), self.gu_block)
-            h = h + swiglu(gate, up) @ L.wdown.t()
+            h = h + self._all_reduce(swiglu(gate, up) @ L.wdown.t())
         return rmsnorm(h, self.final_norm, c.rms_eps, plus_one=c.norm_plus_one)
+
+    def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum of the ranks' partial products (row-parallel projections: attention / Gated-DeltaNet out, MLP down)."""
+        if self.tp_size > 1 and self.tp_group is not None:
+            import torch.distributed as dist
+            x = x.contiguous()
+            dist.all_reduce(x, group=self.tp_group)
+        return x
 
     def logits_torch(self, hidden: torch.Tensor) -> torch.Tensor:
         lg = (hidden @ self.lm_head.t()).float()
+        if self.tp_size > 1 and self.tp_group is not None:
+            import torch.distributed as dist
+            parts = [torch.empty_like(lg) for _ in range(self.tp_size)]
+            dist.all_gather(parts, lg, group=self.tp_group)
+            lg = torch.cat(parts, dim=-1)[..., :self.cfg.vocab_size]
         if self.cfg.logit_softcap > 0:
             cap = self.cfg.logit_softcap
             lg = torch.tanh(lg / cap) * cap

@@ -88,6 +88,12 @@ class SMCScheduler:
         seed = a.random_seed
         self.target = target if target is not None else build_model(
             a.model_path, self.dtype, self.device, tp_rank, tp_size, seed=seed)
+        if tp_size > 1 and backend == "native" and self.target.cfg.arch != "llama":
+            # the kernel chain of the hybrid model has no collective stages: tensor-parallel hybrids run through the
+            # PyTorch forward (heads, FFN channels and vocabulary sharded; partial sums all-reduced)
+            if a.backend == "native":
+                raise ValueError("tensor-parallel hybrid models run with backend='torch' (or 'auto')")
+            backend = self.backend = "torch"
         if tp_size > 1 and not a.replicate_draft and backend == "native":
             raise ValueError("replicate_draft=False (a tensor-parallel draft) is only available with backend='torch': "
                              "the kernel path keeps a full draft replica on every rank")

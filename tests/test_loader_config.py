@@ -90,6 +90,47 @@ def test_tensor_parallel_shards_reassemble():
     assert torch.equal(torch.cat([p.lm_head for p in parts])[:cfg.vocab_size], full.lm_head)
 
 
+def test_hybrid_tensor_parallel_shards_sum_to_the_full_layers():
+    """Emulated ranks: the two shards of a hybrid model, run layer by layer on the same input with their own KV and
+    recurrent-state pools, must add up to the unsharded layer outputs (attention and Gated-DeltaNet mixers, MLP), and
+    their vocabulary shards must concatenate to the full logits."""
+    from smcsd_b200.memory.pools import KVPool, KVSpec, StatePool
+    from smcsd_b200.models.hybrid_gdn import HybridGDNModel
+    from smcsd_b200.models.layers import ExtendBatch, rmsnorm, swiglu
+    from smcsd_b200.models.llama import split_gate_up
+    cfg = preset("tiny-hybrid")
+    models = [HybridGDNModel(cfg, torch.float32, "cpu").init_random(2)] + \
+             [HybridGDNModel(cfg, torch.float32, "cpu", tp_rank=r, tp_size=2).init_random(2) for r in range(2)]
+    T = 11
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(T, cfg.hidden_size, generator=g)
+    batch = ExtendBatch(torch.zeros(T, dtype=torch.long), torch.arange(T), torch.arange(1, T + 1, dtype=torch.int32),
+                        torch.zeros(1, dtype=torch.int32), torch.zeros(1, dtype=torch.int32), extend_len=T,
+                        prefix_lens_host=[0])
+    bt = torch.zeros(2, 32, dtype=torch.int32)
+    bt[0, :T] = torch.arange(1, T + 1)
+    outs = []
+    for m in models:
+        kv = KVPool(KVSpec(len(cfg.attn_layers), m.n_kv_heads, cfg.head_dim, torch.float32), 64, "cpu")
+        st = StatePool(m.state_spec(), 2, "cpu")
+        res = {}
+        for li in (0, 3):                                   # one Gated-DeltaNet layer, one attention layer
+            L = m.layers[li]
+            xn = rmsnorm(x, L.ln1, cfg.rms_eps, plus_one=True)
+            if L.kind == "full_attention":
+                res[("mix", li)] = m._attn_layer(L, xn, batch, kv, bt, m.kv_index[li])
+            else:
+                res[("mix", li)] = m._gdn_layer(L, xn, batch, st, m.state_index[li])
+            gate, up = split_gate_up(xn @ L.wgu.t(), m.gu_block)
+            res[("mlp", li)] = swiglu(gate, up) @ L.wdown.t()
+        res["logits"] = (x @ m.lm_head.t())
+        outs.append(res)
+    full, a, b = outs
+    for key in [("mix", 0), ("mix", 3), ("mlp", 0), ("mlp", 3)]:
+        assert torch.allclose(a[key] + b[key], full[key], atol=2e-5, rtol=1e-4), key
+    assert torch.allclose(torch.cat([a["logits"], b["logits"]], dim=-1)[:, :cfg.vocab_size], full["logits"], atol=1e-5)
+
+
 def test_gate_up_interleave_is_invertible_and_llama3_rope_scaling():
     g, u = torch.randn(128, 8), torch.randn(128, 8)
     w = interleave_gate_up(g, u, 64)

@@ -42,6 +42,20 @@ def test_tensor_parallel_two_ranks_match_single_rank():
         assert agree >= 0.8      # summation order differs between sharded and unsharded fp32 matmuls
 
 
+def test_tensor_parallel_hybrid_two_ranks_match_single_rank():
+    """Hybrid Gated-DeltaNet target on two gloo ranks: attention heads, KV heads, Gated-DeltaNet key / value heads (with
+    their conv channels and recurrent state), FFN channels and vocabulary rows are split over the ranks; the sharded
+    run must reproduce the unsharded tokens (fp32, same seeds)."""
+    sp = {"max_new_tokens": 9, "ignore_eos": True}
+    ref = SMCEngine("preset:tiny-hybrid", "preset:tiny-draft", **_kw(in_process=True)).generate(input_ids=_prompts(2), sampling_params=sp)
+    with SMCEngine("preset:tiny-hybrid", "preset:tiny-draft", **_kw(tp_size=2)) as eng:
+        out = eng.generate(input_ids=_prompts(2), sampling_params=sp)
+    for r, o in zip(ref, out):
+        assert o["completion_tokens"] == 9
+        agree = sum(int(x == y) for x, y in zip(r["output_ids"], o["output_ids"])) / 9
+        assert agree >= 0.8      # summation order differs between sharded and unsharded fp32 matmuls
+
+
 def test_data_parallel_replicas_round_robin():
     with SMCEngine("preset:tiny-target", "preset:tiny-draft", **_kw(dp_size=2)) as eng:
         out = eng.generate(input_ids=_prompts(4), sampling_params={"max_new_tokens": 6, "ignore_eos": True})
