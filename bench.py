@@ -97,6 +97,8 @@ def main() -> int:
     ap.add_argument("--no-config2", action="store_true")
     ap.add_argument("--no-fused", action="store_true", help="skip the multi-GPU fused-collective measurements")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-fp8", action="store_true",
+                    help="skip the extra W8A8 (e4m3) measurement reported under the 'fp8' key (one GPU only)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -192,6 +194,38 @@ def main() -> int:
         config2["shape"] = "log-normal prompt lengths (median 200, sigma 1, clipped 4..2048), 512 new tokens"
     status |= sched.native_runner.check_status() if sched.native_runner else 0
 
+    # ---- the same K cycles with quantization='fp8' (labelled, next to the bf16 headline; one GPU only) -------------
+    fp8 = None
+    if world == 1 and not args.no_fp8 and args.impl == "native":
+        try:
+            eng.shutdown()
+            del eng, sched
+            gc.collect()
+            torch.cuda.empty_cache()
+            eng = SMCEngine(f"preset:{args.target}", f"preset:{args.draft}", n_particles=args.n_particles,
+                            gamma=args.gamma, draft_temperature=0.7, target_temperature=0.7, resample_threshold=0.5,
+                            max_running_requests=1, base_gpu_id=local,
+                            context_length=max(4096, args.prompt_len) + new_tokens + 4 * G, random_seed=rank,
+                            backend="native", in_process=True, cycle_graph=not args.no_graph, mem_fraction_static=0.6,
+                            quantization="fp8")
+            sched = eng._sched
+            sched.add_request(GenerateRequest("bench8", prompt, SamplingParams(max_new_tokens=new_tokens, ignore_eos=True)))
+            sched.step()
+            for _ in range(warm):
+                sched.step()
+            ms8 = [timed_cycles() / steps for _ in range(3)]
+            st8 = sched.native_runner.check_status()
+            sched.abort("bench8")
+            sched.step()
+            fp8 = {"dtype": "fp8 e4m3 weights + per-token e4m3 activations in every projection (W8A8, fp32 accumulate); "
+                            "attention, norms, residual stream and lm_head as in the bf16 run",
+                   "ms_per_step": ms8[0], "value": G / (ms8[0] / 1e3),
+                   "unit": "tokens/s", "all_ms_per_step": ms8, "device_status": int(st8),
+                   "note": "not the headline: reduced-precision variant of the same K device-timed cycles (first region, as the "
+                           "headline; the target's projections are quantised, the draft stays bf16)"}
+        except Exception as e:       # the headline line must still be printed
+            fp8 = {"error": f"{type(e).__name__}: {e}"[:300]}
+
     # ---- fused collective paths (two or more GPUs) ----------------------------------------------------
     fused = None
     if world > 1 and not args.no_fused and args.impl == "native":
@@ -238,7 +272,7 @@ def main() -> int:
                        "vs_baseline = end-to-end tokens/s (e2e.value) over the published 677 tok/s per GPU (wall clock, "
                        "same 256-in / 1024-out shape); vs_baseline_device_timed divides the device-timed decode rate "
                        "by the same figure"},
-            "clocks": clocks, "repeats": repeats, "e2e": e2e, "config2": config2, "fused": fused,
+            "clocks": clocks, "repeats": repeats, "e2e": e2e, "config2": config2, "fused": fused, "fp8": fp8,
             "gpu_launches": int(launches), "device_status": int(status),
         }
         print(json.dumps(line))

@@ -104,8 +104,11 @@ class EngineArgs:
             raise ValueError("power_alpha must be > 0")
         if self.resample_method not in ("systematic", "multinomial"):
             raise ValueError(f"unknown resample_method {self.resample_method!r}")
-        if self.quantization not in (None, "", "none"):
-            raise ValueError(f"quantization={self.quantization!r} is not supported: weights are served in bf16")
+        if self.quantization in ("", "none"):
+            self.quantization = None
+        if self.quantization not in (None, "fp8"):
+            raise ValueError(f"quantization={self.quantization!r} is not supported: weights are served in bf16 or, with "
+                             "quantization='fp8', as e4m3 with per-row scales (dense models, kernel backend)")
         if self.kv_cache_dtype not in ("auto", "bf16", "bfloat16"):
             raise ValueError(f"kv_cache_dtype={self.kv_cache_dtype!r} is not supported: the KV cache is bf16")
         self.target_temperature = max(float(self.target_temperature), 1e-5)

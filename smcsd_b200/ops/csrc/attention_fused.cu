@@ -57,8 +57,16 @@ struct FusedAttnParams {
 
 constexpr int RANGE = 2048;     // page ids staged per pass
 
-template <int D>
+// PFX = false compiles the shared-prefix options out (no key_begin, no parked states, causal): the plain decode and
+// verify steps keep the lean kernel.
+template <int D, bool PFX>
 __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p) {
+  const int* const pfx_key_begin = PFX ? p.key_begin : nullptr;
+  float* const pfx_part_out = PFX ? p.part_out : nullptr;
+  const float* const pfx_part_in = PFX ? p.part_in : nullptr;
+  const int pfx_part_in_n = PFX ? p.part_in_n : 0;
+  const long long pfx_part_in_stride = PFX ? p.part_in_stride : 0;
+  const int pfx_causal = PFX ? p.causal : 1;
   constexpr int LD = D + 8;
   constexpr bool Q_REGS = D <= 128;
   extern __shared__ __align__(16) uint8_t smem_fa[];
@@ -87,8 +95,8 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   const int g = lane >> 2, t = lane & 3;
 
   // ---- key range of this CTA and the first K/V fetch (runs under the new-token work below) -----------
-  const int n_keys = (pool_only && p.causal) ? prefix + p.E : prefix;     // keys served from the paged cache
-  const int kbeg = p.key_begin != nullptr ? max(0, min(p.key_begin[b], n_keys)) : 0;
+  const int n_keys = (pool_only && pfx_causal) ? prefix + p.E : prefix;     // keys served from the paged cache
+  const int kbeg = pfx_key_begin != nullptr ? max(0, min(pfx_key_begin[b], n_keys)) : 0;
   int per = (n_keys - kbeg + p.KS - 1) / p.KS;
   per = (per + TK - 1) / TK * TK;
   const int kb = kbeg + ks * per, ke = min(n_keys, kb + per);
@@ -307,8 +315,8 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       const __nv_bfloat16* Kt = my_tiles + (size_t)(j % stg) * 2 * TILE;
       const int key0 = r0 + tile * TK;
       process_tile<D, TK / 8, Q_REGS>(Kt, Kt + TILE, qa, Qs_mt, p.scale, st, nvalid,
-                                      p.causal ? prefix + e_row0 - key0 : 0x3fffffff,
-                                      p.causal ? prefix + e_row1 - key0 : 0x3fffffff);
+                                      pfx_causal ? prefix + e_row0 - key0 : 0x3fffffff,
+                                      pfx_causal ? prefix + e_row1 - key0 : 0x3fffffff);
     }
   }
   cp_async_wait<0>();
@@ -412,28 +420,28 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       float a_self = 1.f;
       float a_in[8];
       const float* sin_row = nullptr;
-      if (p.part_in != nullptr) {
+      if (pfx_part_in != nullptr) {
         // fold in the states a group pass left for this (token, head): flash-decoding merge of partial softmaxes
-        sin_row = p.part_in + ((size_t)tkn * p.Hq + head) * (D + 2);
+        sin_row = pfx_part_in + ((size_t)tkn * p.Hq + head) * (D + 2);
         float M = m;
 #pragma unroll
         for (int q = 0; q < 8; ++q)
-          if (q < p.part_in_n) M = fmaxf(M, sin_row[(size_t)q * p.part_in_stride + D]);
+          if (q < pfx_part_in_n) M = fmaxf(M, sin_row[(size_t)q * pfx_part_in_stride + D]);
         a_self = M == -INFINITY ? 1.f : __expf(m - M);
         l *= a_self;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
           a_in[q] = 0.f;
-          if (q < p.part_in_n) {
-            const float m_in = sin_row[(size_t)q * p.part_in_stride + D], l_in = sin_row[(size_t)q * p.part_in_stride + D + 1];
+          if (q < pfx_part_in_n) {
+            const float m_in = sin_row[(size_t)q * pfx_part_in_stride + D], l_in = sin_row[(size_t)q * pfx_part_in_stride + D + 1];
             a_in[q] = (M == -INFINITY || m_in == -INFINITY) ? 0.f : __expf(m_in - M);
             l += l_in * a_in[q];
           }
         }
         m = M;
       }
-      if (p.part_out != nullptr) {
-        float* so = p.part_out + ((size_t)tkn * p.Hq + head) * (D + 2);
+      if (pfx_part_out != nullptr) {
+        float* so = pfx_part_out + ((size_t)tkn * p.Hq + head) * (D + 2);
 #pragma unroll
         for (int nt = 0; nt < D / 8; ++nt)
           *reinterpret_cast<float2*>(so + nt * 8 + 2 * t) = make_float2(st.o[nt][2 * hrow], st.o[nt][2 * hrow + 1]);
@@ -449,8 +457,8 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
         if (sin_row != nullptr) {
 #pragma unroll
           for (int q = 0; q < 8; ++q)
-            if (q < p.part_in_n) {
-              const float2 x = *reinterpret_cast<const float2*>(sin_row + (size_t)q * p.part_in_stride + nt * 8 + 2 * t);
+            if (q < pfx_part_in_n) {
+              const float2 x = *reinterpret_cast<const float2*>(sin_row + (size_t)q * pfx_part_in_stride + nt * 8 + 2 * t);
               v0 += x.x * a_in[q];
               v1 += x.y * a_in[q];
             }
@@ -592,9 +600,10 @@ SMC_API int smc_attention_fused_ex(const float* qkv, const void* q_in, int ld_qk
   p.part_in_n = part_in_n; p.part_in_stride = part_in_stride;
   const size_t smem = fused_smem_bytes(D, n_mt, n_kw, stg);
   void (*kern)(const FusedAttnParams) = nullptr;
-  if (D == 64) kern = attn_fused_kernel<64>;
-  else if (D == 128) kern = attn_fused_kernel<128>;
-  else if (D == 256) kern = attn_fused_kernel<256>;
+  const bool pfx = key_begin != nullptr || part_out != nullptr || part_in != nullptr || !causal;
+  if (D == 64) kern = pfx ? attn_fused_kernel<64, true> : attn_fused_kernel<64, false>;
+  else if (D == 128) kern = pfx ? attn_fused_kernel<128, true> : attn_fused_kernel<128, false>;
+  else if (D == 256) kern = pfx ? attn_fused_kernel<256, true> : attn_fused_kernel<256, false>;
   else return -72;
   CUDA_CHECK_RET(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchAttribute attr[2];

@@ -4,6 +4,8 @@
 //   add_rmsnorm        residual += sum_s partials ; normalised bf16 activations
 //   rope_kv_write      sum_s qkv partials -> rotated q (bf16) ; rotated k and v into the paged cache
 //   swiglu_partials    sum_s gate/up partials -> silu(gate) * up (bf16)
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace smc {
@@ -29,7 +31,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, int splits, long long split_stride,
                    const int* __restrict__ ids, const __nv_bfloat16* __restrict__ embed,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ xn, int ldx, int d, float eps,
-                   int plus_one, __nv_bfloat16* __restrict__ hb, float* __restrict__ ssq, int pdl) {
+                   int plus_one, __nv_bfloat16* __restrict__ hb, float* __restrict__ ssq, uint8_t* __restrict__ q8,
+                   int ldq, float* __restrict__ qscale, int pdl) {
   __shared__ float red[32];
   if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const int m = blockIdx.x;
@@ -61,6 +64,33 @@ add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, in
   const float tot = block_sum<0>(ss, red);
   const float inv = rsqrtf(tot / (float)d + eps);
   if (ssq != nullptr && threadIdx.x == 0) ssq[m] = tot;     // for GEMMs that apply the norm in their epilogue
+  // optional e4m3 copy of the normalised row (W8A8 consumers): per-row scale = max|xn| / 448 over the bf16-rounded values
+  float q_inv = 0.f;
+  if (q8 != nullptr) {
+    float amax = 0.f;
+    const float add = plus_one ? 1.f : 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        const uint2 wr = *reinterpret_cast<const uint2*>(w + c * 4);
+        const __nv_bfloat162 w0 = *reinterpret_cast<const __nv_bfloat162*>(&wr.x);
+        const __nv_bfloat162 w1 = *reinterpret_cast<const __nv_bfloat162*>(&wr.y);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x * inv * (__low2float(w0) + add)), fabsf(v[i].y * inv * (__high2float(w0) + add))),
+                                 fmaxf(fabsf(v[i].z * inv * (__low2float(w1) + add)), fabsf(v[i].w * inv * (__high2float(w1) + add)))));
+      }
+    }
+    amax = warp_max(amax);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    float t = (threadIdx.x & 31) < (NORM_THREADS >> 5) ? red[threadIdx.x & 31] : 0.f;
+    t = warp_max(t);                     // every warp reduces the eight partial maxima itself
+    __syncthreads();
+    // scale taken over the bf16-rounded maximum, as a separate quantisation pass over xn would see it
+    const float sc = fmaxf(__bfloat162float(__float2bfloat16(t)), 1e-12f) * (1.f / 448.f);
+    q_inv = 1.f / sc;
+    if (threadIdx.x == 0) qscale[m] = sc;
+  }
 #pragma unroll
   for (int i = 0; i < NORM_MAXV; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
@@ -86,6 +116,13 @@ add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, in
         o.x = *reinterpret_cast<uint32_t*>(&o0);
         o.y = *reinterpret_cast<uint32_t*>(&o1);
         *reinterpret_cast<uint2*>(xn + (size_t)m * ldx + c * 4) = o;
+        if (q8 != nullptr) {
+          const __nv_fp8x2_storage_t a = __nv_cvt_float2_to_fp8x2(
+              make_float2(__low2float(o0) * q_inv, __high2float(o0) * q_inv), __NV_SATFINITE, __NV_E4M3);
+          const __nv_fp8x2_storage_t b2 = __nv_cvt_float2_to_fp8x2(
+              make_float2(__low2float(o1) * q_inv, __high2float(o1) * q_inv), __NV_SATFINITE, __NV_E4M3);
+          *reinterpret_cast<uint32_t*>(q8 + (size_t)m * ldq + c * 4) = (uint32_t)a | ((uint32_t)b2 << 16);
+        }
       }
     }
   }
@@ -248,6 +285,62 @@ static int launch_pdl(K kern, dim3 grid, dim3 block, cudaStream_t st, int pdl, A
 
 }  // namespace smc
 
+namespace smc {
+// Per-row dynamic quantisation of bf16 activations to e4m3: scale[m] = max|x| / 448, q = x / scale (saturating).
+// One block per row; the row is read twice (second time from L1 / L2).
+__global__ void __launch_bounds__(256) quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
+                                                              uint8_t* __restrict__ q, int ldq,
+                                                              float* __restrict__ scale, int K, int pdl) {
+  __shared__ float red[32];
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
+  const int m = blockIdx.x;
+  const __nv_bfloat16* xr = x + (size_t)m * ldx;
+  float amax = 0.f;
+  for (int c = threadIdx.x * 8; c < K; c += blockDim.x * 8) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fmaxf(fabsf(__low2float(h2[i])), fabsf(__high2float(h2[i]))));
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+  if (threadIdx.x < 32) {
+    t = warp_max(t);
+    if (threadIdx.x == 0) red[0] = t;
+  }
+  __syncthreads();
+  const float sc = fmaxf(red[0], 1e-12f) * (1.f / 448.f), inv = 1.f / sc;
+  if (threadIdx.x == 0) scale[m] = sc;
+  uint8_t* qr = q + (size_t)m * ldq;
+  for (int c = threadIdx.x * 8; c < K; c += blockDim.x * 8) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    uint32_t o[2];
+#pragma unroll
+    for (int i = 0; i < 4; i += 2) {
+      const __nv_fp8x2_storage_t a = __nv_cvt_float2_to_fp8x2(
+          make_float2(__low2float(h2[i]) * inv, __high2float(h2[i]) * inv), __NV_SATFINITE, __NV_E4M3);
+      const __nv_fp8x2_storage_t b = __nv_cvt_float2_to_fp8x2(
+          make_float2(__low2float(h2[i + 1]) * inv, __high2float(h2[i + 1]) * inv), __NV_SATFINITE, __NV_E4M3);
+      o[i >> 1] = (uint32_t)a | ((uint32_t)b << 16);
+    }
+    *reinterpret_cast<uint2*>(qr + c) = make_uint2(o[0], o[1]);
+  }
+}
+}  // namespace smc
+
+// x [M, ldx] bf16 -> q [M, ldq] e4m3 bytes + scale [M] fp32 (x ~ q * scale).  K, ldx and ldq multiples of 8.
+SMC_API int smc_quant_rows_e4m3(const void* x, int ldx, void* q, int ldq, float* scale, int M, int K, int pdl,
+                                cudaStream_t st) {
+  using namespace smc;
+  if (M <= 0) return 0;
+  if ((K & 7) || (ldx & 7) || (ldq & 7)) return -33;
+  return launch_pdl(quant_rows_e4m3_kernel, dim3(M), dim3(256), st, pdl, (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq,
+                    scale, K, pdl);
+}
+
 // h [M, d] fp32 in/out.  With ids != null the row is first loaded from the embedding table
 // (h's previous content is ignored); partials may be null (splits = 0).
 SMC_API int smc_add_rmsnorm(float* h, const float* partials, int splits, long long split_stride, const int* ids,
@@ -258,7 +351,20 @@ SMC_API int smc_add_rmsnorm(float* h, const float* partials, int splits, long lo
   if ((d & 3) || d > NORM_THREADS * 4 * NORM_MAXV) return -30;
   return launch_pdl(add_rmsnorm_kernel, dim3(M), dim3(NORM_THREADS), st, pdl, h, partials, splits, split_stride, ids,
                     (const __nv_bfloat16*)embed, (const __nv_bfloat16*)w, (__nv_bfloat16*)xn, ldx, d, eps, plus_one,
-                    (__nv_bfloat16*)hb, ssq, pdl);
+                    (__nv_bfloat16*)hb, ssq, (uint8_t*)nullptr, 0, (float*)nullptr, pdl);
+}
+
+// Same, also emitting the e4m3 copy of the normalised rows (q8 [M, ldq] bytes, qscale [M]) for W8A8 consumers; xn is
+// required (the scale is taken over its bf16 values).
+SMC_API int smc_add_rmsnorm_q8(float* h, const int* ids, const void* embed, const void* w, void* xn, int ldx, int M, int d,
+                               float eps, int plus_one, void* q8, int ldq, float* qscale, int pdl, cudaStream_t st) {
+  using namespace smc;
+  if (M <= 0) return 0;
+  if ((d & 3) || d > NORM_THREADS * 4 * NORM_MAXV || xn == nullptr || q8 == nullptr || qscale == nullptr || (ldq & 3))
+    return -30;
+  return launch_pdl(add_rmsnorm_kernel, dim3(M), dim3(NORM_THREADS), st, pdl, h, (const float*)nullptr, 0, 0ll, ids,
+                    (const __nv_bfloat16*)embed, (const __nv_bfloat16*)w, (__nv_bfloat16*)xn, ldx, d, eps, plus_one,
+                    (__nv_bfloat16*)nullptr, (float*)nullptr, (uint8_t*)q8, ldq, qscale, pdl);
 }
 
 SMC_API int smc_rope_kv_write(const float* partials, int splits, long long split_stride, const int* positions,

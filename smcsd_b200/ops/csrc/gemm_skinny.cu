@@ -17,6 +17,10 @@
 // partials in global memory (oracle / fallback), bf16 store, and a fused SwiGLU for gate/up
 // matrices whose rows are interleaved in blocks of 64 channels.
 //
+// FP8 (W8A8): with `fp8` set both operands are e4m3 bytes (128 per 128-byte tile row), the MMAs are issued as
+// tcgen05.mma.kind::f8f6f4 (K = 32 per instruction, fp32 accumulation) and the epilogues scale every value by the
+// weight row's scale and the token's activation scale.  Tiles, ring and descriptors are the same bytes as for bf16.
+//
 // Every mbarrier wait is bounded; on a timeout the CTA raises a status bit, drains its
 // outstanding copies, frees its tensor memory and returns.
 #include <string.h>
@@ -74,6 +78,10 @@ struct GemmParams {
   int hb_ld;
   // lm_head with fused sampling / scoring (EPI_LMHEAD): out = RowPartial [M, slabs]
   SampleArgs samp;
+  // FP8 operands: e4m3 bytes, value = byte * scale; w_scale per weight row, x_scale per token row (null: 1)
+  int fp8;
+  const float* w_scale;
+  const float* x_scale;
 };
 
 template <int BN, int EPI, bool LEAN>
@@ -90,7 +98,7 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <int BN, int EPI, bool LEAN>
+template <int BN, int EPI, bool LEAN, bool FP8>
 __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW,
                                                          const __grid_constant__ CUtensorMap tmX,
                                                          const GemmParams p) {
@@ -147,12 +155,13 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
     if (elect_one()) {
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
+      constexpr int bk = FP8 ? 2 * C::BK : C::BK;    // elements per 128-byte tile row
       // Weights do not depend on the previous kernel: start streaming them before the
       // programmatic-dependency wait, then fetch the activations.
       const int pre = nkb < nst ? nkb : nst;
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&full[i], C::STAGE_BYTES);
-        tma_load_2d(smem + i * C::STAGE_BYTES, &tmW, &full[i], (kb_begin + i) * C::BK, n_tile * C::BM, pol_w);
+        tma_load_2d(smem + i * C::STAGE_BYTES, &tmW, &full[i], (kb_begin + i) * bk, n_tile * C::BM, pol_w);
       }
       if (p.pdl) pdl_wait_prior_grid();
       if (p.tp.ag_flag != nullptr) {
@@ -166,7 +175,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
         fence_proxy_async_all();
       }
       for (int i = 0; i < pre; ++i)
-        tma_load_2d(smem + i * C::STAGE_BYTES + C::A_BYTES, &tmX, &full[i], (kb_begin + i) * C::BK, m_tile * BN,
+        tma_load_2d(smem + i * C::STAGE_BYTES + C::A_BYTES, &tmX, &full[i], (kb_begin + i) * bk, m_tile * BN,
                     pol_x);
       *sh_issued = pre;
       // stage index and phase advance by counting (the ring depth is a launch parameter: no division per k-block)
@@ -179,8 +188,8 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
           break;
         }
         mbar_expect_tx(&full[s], C::STAGE_BYTES);
-        tma_load_2d(smem + s * C::STAGE_BYTES, &tmW, &full[s], (kb_begin + i) * C::BK, n_tile * C::BM, pol_w);
-        tma_load_2d(smem + s * C::STAGE_BYTES + C::A_BYTES, &tmX, &full[s], (kb_begin + i) * C::BK, m_tile * BN,
+        tma_load_2d(smem + s * C::STAGE_BYTES, &tmW, &full[s], (kb_begin + i) * bk, n_tile * C::BM, pol_w);
+        tma_load_2d(smem + s * C::STAGE_BYTES + C::A_BYTES, &tmX, &full[s], (kb_begin + i) * bk, m_tile * BN,
                     pol_x);
         *sh_issued = i + 1;
       }
@@ -189,6 +198,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
   } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(C::BM, BN);
+      constexpr uint32_t idesc8 = umma_idesc_e4m3(C::BM, BN);
       int s = 0;
       uint32_t ph = 0u;
       for (int i = 0; i < nkb; ++i, ++s) {
@@ -202,8 +212,10 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
         const uint64_t adesc = umma_desc_k_sw128(a_addr);
         const uint64_t bdesc = umma_desc_k_sw128(a_addr + C::A_BYTES);
 #pragma unroll
-        for (int k = 0; k < C::BK / 16; ++k)   // advance 32 bytes (16 bf16) inside the swizzle atom
-          umma_bf16_ss(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) ? 1u : 0u);
+        for (int k = 0; k < C::BK / 16; ++k) {   // advance 32 bytes (16 bf16 or 32 e4m3) inside the swizzle atom
+          if constexpr (FP8) umma_f8_ss(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc8, (i | k) ? 1u : 0u);
+          else umma_bf16_ss(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) ? 1u : 0u);
+        }
         umma_commit(&empty[s]);
         *sh_consumed = i + 1;
       }
@@ -222,6 +234,12 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
         if (m < p.M)
           for (int q = 0; q < p.ssq_parts; ++q) ss += p.ssq_in[(size_t)q * p.ssq_ld + (size_t)m * p.ssq_mstride];
         s_rstd[c] = rsqrtf(ss * p.norm_inv_d + p.norm_eps);
+      }
+    } else if (FP8 && p.x_scale != nullptr) {
+      if (p.pdl) pdl_wait_prior_grid();
+      for (int c = tid2; c < BN; c += 64) {
+        const int m = m_tile * BN + c;
+        s_rstd[c] = m < p.M ? p.x_scale[(size_t)m * p.ssq_mstride] : 1.f;
       }
     } else {
       for (int c = tid2; c < BN; c += 64) s_rstd[c] = 1.f;
@@ -248,6 +266,8 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
     const int n = n_tile * C::BM + row_in_tile;
     const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
     const int m_base = m_tile * BN;
+    float wsc = 1.f;                                   // FP8: scale of this weight row
+    if constexpr (FP8) wsc = n < p.N ? p.w_scale[n] : 1.f;
     if constexpr (EPI == EPI_SWIGLU_BF16) {
       // rows 0..63 of the slab are gate channels, rows 64..127 the matching up channels
       float* sbuf = reinterpret_cast<float*>(smem);      // the ring is idle: every MMA has completed
@@ -259,7 +279,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
         tmem_ld_wait();
         if (warp >= 2) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) sbuf[(row_in_tile - 64) * LD + c0 + j] = __uint_as_float(r[j]);
+          for (int j = 0; j < 16; ++j) sbuf[(row_in_tile - 64) * LD + c0 + j] = __uint_as_float(r[j]) * wsc;
         }
         __syncthreads();
         if (warp < 2) {
@@ -269,7 +289,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
           for (int j = 0; j < 16; ++j) {
             const int m = m_base + c0 + j;
             if (m < p.M && ch * 2 < p.N) {
-              const float g = __uint_as_float(r[j]) * s_rstd[c0 + j];
+              const float g = __uint_as_float(r[j]) * wsc * s_rstd[c0 + j];
               const float u = sbuf[row_in_tile * LD + c0 + j] * s_rstd[c0 + j];
               out[(size_t)m * p.ldo + ch] = __float2bfloat16(g / (1.0f + __expf(-g)) * u);
             }
@@ -286,7 +306,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
         tmem_ld_32x32b_x16(taddr + c0, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) sbuf[(c0 + j) * C::BM + row_in_tile] = __uint_as_float(r[j]);
+        for (int j = 0; j < 16; ++j) sbuf[(c0 + j) * C::BM + row_in_tile] = __uint_as_float(r[j]) * wsc;
       }
     } else if constexpr (EPI == EPI_LMHEAD) {
       // Sampling / scoring straight out of tensor memory: the slab's 128 vocabulary rows are reduced per token to
@@ -303,7 +323,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
         tmem_ld_wait();
         float* trp = tr + parity * (16 * 129);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) trp[j * 129 + row_in_tile] = __uint_as_float(r[j]) * s_rstd[c0 + j];
+        for (int j = 0; j < 16; ++j) trp[j * 129 + row_in_tile] = __uint_as_float(r[j]) * wsc * s_rstd[c0 + j];
         __syncthreads();
         lm_reduce_chunk(p.samp, trp, n_tile * C::BM, c0, m_base, (int)threadIdx.x, s_rp);
         parity ^= 1;
@@ -326,10 +346,10 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
             if (m < p.M) {
               if constexpr (EPI == EPI_PARTIAL_F32) {
                 reinterpret_cast<float*>(p.out)[((size_t)split * p.M + m) * p.N + n] =
-                    __uint_as_float(r[j]) * s_rstd[c0 + j];
+                    __uint_as_float(r[j]) * wsc * s_rstd[c0 + j];
               } else {
                 reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] =
-                    __float2bfloat16(__uint_as_float(r[j]) * s_rstd[c0 + j]);
+                    __float2bfloat16(__uint_as_float(r[j]) * wsc * s_rstd[c0 + j]);
               }
             }
           }
@@ -480,11 +500,11 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
 }
 
 // ---------------------------------------------------------------- host side
-template <int BN, int EPI, bool LEAN = false>
+template <int BN, int EPI, bool LEAN = false, bool FP8 = false>
 static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, dim3 grid, cudaStream_t st) {
   using C = GemmCfg<BN, EPI, LEAN>;
   static bool configured = false;
-  auto kern = gemm_skinny_kernel<BN, EPI, LEAN>;
+  auto kern = gemm_skinny_kernel<BN, EPI, LEAN, FP8>;
   if (!configured) {
     CUDA_CHECK_RET(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured = true;
@@ -512,6 +532,21 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmPara
   cfg.numAttrs = na;
   CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p));
   return 0;
+}
+
+// e4m3 operands: the epilogues the quantised layer chain uses
+template <int EPI>
+static int dispatch_bn_fp8(int bn, const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3 g,
+                           cudaStream_t st) {
+  switch (bn) {
+    case 16: return launch<16, EPI, false, true>(a, b, p, g, st);
+    case 32: return launch<32, EPI, false, true>(a, b, p, g, st);
+    case 64: return launch<64, EPI, false, true>(a, b, p, g, st);
+    case 80: return launch<80, EPI, false, true>(a, b, p, g, st);
+    case 128: return p.stages == 3 ? launch<128, EPI, true, true>(a, b, p, g, st) : launch<128, EPI, false, true>(a, b, p, g, st);
+    case 256: return launch<256, EPI, false, true>(a, b, p, g, st);
+  }
+  return -10;
 }
 
 template <int EPI>
@@ -607,27 +642,28 @@ struct NormLink {            // host-side description of the folded RMSNorm (all
 // Encoded tensor maps are cached per (base, shape, pitch, box): an encode costs a driver call, and eager chains
 // (prompt passes, batches beyond the graph caps) issue two per GEMM with the same few operands over and over.
 struct TmapKey {
-  const void* base; long long rows, cols, ld; int box;
+  const void* base; long long rows, cols, ld; int box, es;
   bool operator==(const TmapKey& o) const {
-    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box == o.box;
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box == o.box && es == o.es;
   }
 };
 struct TmapKeyHash {
   size_t operator()(const TmapKey& k) const {
     size_t h = std::hash<const void*>()(k.base);
-    h = h * 1000003u ^ std::hash<long long>()(k.rows * 131 + k.box);
+    h = h * 1000003u ^ std::hash<long long>()(k.rows * 131 + k.box * 2 + k.es);
     h = h * 1000003u ^ std::hash<long long>()(k.cols * 8191 + k.ld);
     return h;
   }
 };
-static int cached_tmap(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box) {
+static int cached_tmap(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld, int box,
+                       int es = 2) {
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
   static std::mutex mu;
-  const TmapKey key{base, rows, cols, ld, box};
+  const TmapKey key{base, rows, cols, ld, box, es};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) { *tm = it->second; return 0; }
-  const int rc = smc::make_tmap(tm, base, rows, cols, ld, box);
+  const int rc = es == 1 ? smc::make_tmap_u8(tm, base, rows, cols, ld, box) : smc::make_tmap(tm, base, rows, cols, ld, box);
   if (rc == 0) {
     if (cache.size() > 65536) cache.clear();
     cache.emplace(key, *tm);
@@ -635,12 +671,16 @@ static int cached_tmap(CUtensorMap* tm, const void* base, long long rows, long l
   return rc;
 }
 
+struct Fp8Link { const float* w_scale; const float* x_scale; };      // e4m3 operands with their dequantisation scales
+
 static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo, int splits,
                       int epi, int* status, int pdl, const smc::TpLink* tp, const NormLink* nl, cudaStream_t stream,
-                      const smc::SampleArgs* samp = nullptr) {
+                      const smc::SampleArgs* samp = nullptr, const Fp8Link* f8 = nullptr) {
   using namespace smc;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((K % 8) != 0 || (ldx % 8) != 0) return -20;       // row pitch must be a multiple of 16 bytes
+  const int es = f8 != nullptr ? 1 : 2;                 // element size in bytes
+  if ((K * es) % 16 != 0 || (ldx * es) % 16 != 0) return -20;       // row pitch must be a multiple of 16 bytes
+  if (f8 != nullptr && nl != nullptr) return -28;
   if (epi == EPI_SWIGLU_BF16 && splits > 1) epi = EPI_SWIGLU_SPLIT;      // split-K reduced in the cluster, then SwiGLU
   const bool clustered = epi == EPI_STORE_F32 || epi == EPI_RESID_F32 || epi == EPI_RS_F32 || epi == EPI_SWIGLU_SPLIT;
   if (!clustered && epi != EPI_PARTIAL_F32 && splits != 1) return -21;
@@ -651,7 +691,8 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
   const int bn = bn_for(M, N, clustered);
   GemmParams p;
   p.N = N; p.K = K; p.M = M;
-  p.kblocks = (K + 63) / 64;
+  p.kblocks = f8 != nullptr ? (K + 127) / 128 : (K + 63) / 64;
+  p.fp8 = f8 != nullptr; p.w_scale = f8 ? f8->w_scale : nullptr; p.x_scale = f8 ? f8->x_scale : nullptr;
   p.splits = splits < 1 ? 1 : (splits > p.kblocks ? p.kblocks : splits);
   p.out = out; p.ldo = ldo; p.status = status; p.pdl = pdl;
   if (tp != nullptr) p.tp = *tp; else memset(&p.tp, 0, sizeof(p.tp));
@@ -668,9 +709,9 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
     if (p.ssq_out != nullptr && epi != EPI_RESID_F32) return -25;
   }
   CUtensorMap tmW, tmX;
-  int rc = cached_tmap(&tmW, W, N, K, K, 128);
+  int rc = cached_tmap(&tmW, W, N, K, K, 128, es);
   if (rc) return rc;
-  rc = cached_tmap(&tmX, X, M, K, ldx, bn);
+  rc = cached_tmap(&tmX, X, M, K, ldx, bn, es);
   if (rc) return rc;
   p.m_tiles = (M + bn - 1) / bn;
   {
@@ -680,6 +721,16 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
     if (bn == 128 && (clustered || tiles > 148)) p.stages = 3;
   }
   dim3 grid(((N + 127) / 128) * p.m_tiles, p.splits, 1);
+  if (p.fp8) {
+    switch (epi) {
+      case EPI_BF16: return dispatch_bn_fp8<EPI_BF16>(bn, tmW, tmX, p, grid, stream);
+      case EPI_SWIGLU_BF16: return dispatch_bn_fp8<EPI_SWIGLU_BF16>(bn, tmW, tmX, p, grid, stream);
+      case EPI_STORE_F32: return dispatch_bn_fp8<EPI_STORE_F32>(bn, tmW, tmX, p, grid, stream);
+      case EPI_RESID_F32: return dispatch_bn_fp8<EPI_RESID_F32>(bn, tmW, tmX, p, grid, stream);
+      case EPI_SWIGLU_SPLIT: return dispatch_bn_fp8<EPI_SWIGLU_SPLIT>(bn, tmW, tmX, p, grid, stream);
+    }
+    return -30;
+  }
   switch (epi) {
     case EPI_PARTIAL_F32: return dispatch_bn<EPI_PARTIAL_F32>(bn, tmW, tmX, p, grid, stream);
     case EPI_BF16: return dispatch_bn<EPI_BF16>(bn, tmW, tmX, p, grid, stream);
@@ -696,6 +747,16 @@ static int gemm_entry(const void* W, const void* X, void* out, int N, int K, int
 SMC_API int smc_gemm_skinny(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo,
                             int splits, int epi, int* status, int pdl, cudaStream_t stream) {
   return gemm_entry(W, X, out, N, K, M, ldx, ldo, splits, epi, status, pdl, nullptr, nullptr, stream);
+}
+
+// FP8 variant (W8A8): W [N, K] and X [M, ldx] hold e4m3 bytes; w_scale [N] and x_scale [M] (fp32) are the per-row
+// dequantisation scales applied in the epilogue (x_scale may be null).  K and ldx must be multiples of 16.
+SMC_API int smc_gemm_skinny_fp8(const void* W, const void* X, void* out, int N, int K, int M, int ldx, int ldo,
+                                int splits, int epi, const float* w_scale, const float* x_scale, int* status, int pdl,
+                                cudaStream_t stream) {
+  if (w_scale == nullptr) return -29;
+  Fp8Link f8 = {w_scale, x_scale};
+  return gemm_entry(W, X, out, N, K, M, ldx, ldo, splits, epi, status, pdl, nullptr, nullptr, stream, nullptr, &f8);
 }
 
 // Tensor-parallel variant: `tp` describes the all-gather wait of the activation operand and / or the

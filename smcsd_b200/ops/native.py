@@ -127,6 +127,48 @@ def gemm_skinny(W: torch.Tensor, X: torch.Tensor, out: torch.Tensor, *, M: int, 
                                  _stream()), "smc_gemm_skinny")
 
 
+def gemm_skinny_fp8(W8: torch.Tensor, w_scale: torch.Tensor, X8: torch.Tensor, x_scale: Optional[torch.Tensor],
+                    out: torch.Tensor, *, M: int, splits: int = 1, epi: int = EPI_PARTIAL_F32,
+                    ldx: Optional[int] = None, ldo: Optional[int] = None, status: torch.Tensor, pdl: bool = False) -> None:
+    """W8A8 GEMM on tcgen05 (kind::f8f6f4): out = (X8[:M] * x_scale[:, None]) @ (W8 * w_scale[:, None]).T with e4m3
+    operands (uint8 / float8_e4m3fn storage), fp32 accumulation, scales applied in the epilogue."""
+    N, K = W8.shape
+    ldx = ldx if ldx is not None else X8.stride(0)
+    ldo = ldo if ldo is not None else (out.stride(0) if out.dim() == 2 else N)
+    L = lib()
+    if not getattr(L, "_fp8_declared", False):
+        vp, i = C.c_void_p, C.c_int
+        L.smc_gemm_skinny_fp8.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, vp, vp, vp, i, vp]
+        L.smc_gemm_skinny_fp8.restype = C.c_int
+        L.smc_quant_rows_e4m3.argtypes = [vp, i, vp, i, vp, i, i, i, vp]
+        L.smc_quant_rows_e4m3.restype = C.c_int
+        L._fp8_declared = True
+    _check(L.smc_gemm_skinny_fp8(_p(W8), _p(X8), _p(out), N, K, M, ldx, ldo, splits, epi, _p(w_scale), _p(x_scale),
+                                 _p(status), int(pdl), _stream()), "smc_gemm_skinny_fp8")
+
+
+def quant_rows_e4m3(x: torch.Tensor, q: torch.Tensor, scale: torch.Tensor, *, M: int, K: int, pdl: bool = False) -> None:
+    """Per-row dynamic quantisation of bf16 rows to e4m3 bytes: ``scale[m] = max|x[m]| / 448``, ``q = x / scale``."""
+    L = lib()
+    if not getattr(L, "_fp8_declared", False):
+        vp, i = C.c_void_p, C.c_int
+        L.smc_gemm_skinny_fp8.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, vp, vp, vp, i, vp]
+        L.smc_gemm_skinny_fp8.restype = C.c_int
+        L.smc_quant_rows_e4m3.argtypes = [vp, i, vp, i, vp, i, i, i, vp]
+        L.smc_quant_rows_e4m3.restype = C.c_int
+        L._fp8_declared = True
+    _check(L.smc_quant_rows_e4m3(_p(x), x.stride(0), _p(q), q.stride(0), _p(scale), M, K, int(pdl), _stream()),
+           "smc_quant_rows_e4m3")
+
+
+def quantize_weight_e4m3(w: torch.Tensor):
+    """Per-output-row e4m3 quantisation of a weight matrix [N, K] (host-side helper, PyTorch): returns (bytes, scale)."""
+    wf = w.float()
+    scale = wf.abs().amax(dim=1).clamp_(min=1e-12) / 448.0
+    q = (wf / scale[:, None]).to(torch.float8_e4m3fn)
+    return q.view(torch.uint8).contiguous(), scale.contiguous()
+
+
 def gemm_skinny_norm(W: torch.Tensor, X: torch.Tensor, out: torch.Tensor, *, M: int, splits: int, epi: int, ldo: int,
                      status: torch.Tensor, ssq_in: Optional[torch.Tensor] = None, ssq_parts: int = 0, norm_d: int = 0,
                      norm_eps: float = 0.0, ssq_out: Optional[torch.Tensor] = None, hb_out: Optional[torch.Tensor] = None,
@@ -156,6 +198,21 @@ def add_rmsnorm(h: torch.Tensor, w: Optional[torch.Tensor], xn: Optional[torch.T
     ldx = ldx if ldx is not None else (xn.stride(0) if xn is not None else d)
     _check(lib().smc_add_rmsnorm(_p(h), _p(partials), splits, split_stride, _p(ids), _p(embed), _p(w), _p(xn), ldx, M,
                                  d, eps, int(plus_one), _p(hb), _p(ssq), int(pdl), _stream()), "smc_add_rmsnorm")
+
+
+def add_rmsnorm_q8(h: torch.Tensor, w: torch.Tensor, xn: torch.Tensor, q8: torch.Tensor, qscale: torch.Tensor, *, M: int,
+                   d: int, eps: float, ids: Optional[torch.Tensor] = None, embed: Optional[torch.Tensor] = None,
+                   plus_one: bool = False, pdl: bool = False) -> None:
+    """RMSNorm of the residual rows (or of embedding rows) that also emits the e4m3 copy of the normalised rows with
+    per-row scales, for the W8A8 GEMMs."""
+    L = lib()
+    if not getattr(L, "_q8norm_declared", False):
+        vp, i, f = C.c_void_p, C.c_int, C.c_float
+        L.smc_add_rmsnorm_q8.argtypes = [vp, vp, vp, vp, vp, i, i, i, f, i, vp, i, vp, i, vp]
+        L.smc_add_rmsnorm_q8.restype = C.c_int
+        L._q8norm_declared = True
+    _check(L.smc_add_rmsnorm_q8(_p(h), _p(ids), _p(embed), _p(w), _p(xn), xn.stride(0), M, d, eps, int(plus_one),
+                                _p(q8), q8.stride(0), _p(qscale), int(pdl), _stream()), "smc_add_rmsnorm_q8")
 
 
 def rope_kv_write(partials: torch.Tensor, splits: int, split_stride: int, positions: torch.Tensor,

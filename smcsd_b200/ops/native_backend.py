@@ -76,7 +76,18 @@ class NativeLlama:
         self.attn_tc = _env_int("SMC_ATTN_TC", ATTN_TC_DEFAULT)
         # RMSNorm folded into the GEMMs: consumers read the raw bf16 residual stream ``hb`` and scale by 1/rms in
         # their epilogue; residual GEMMs emit ``hb`` and per-slab sums of squares.  Five launches per layer.
-        self.fold = self.fuse_swiglu and model.tp_size == 1 and _env_flag("SMC_FOLD_NORM", True)
+        self.quant = getattr(model, "quantization", None)
+        self.fold = self.fuse_swiglu and model.tp_size == 1 and _env_flag("SMC_FOLD_NORM", True) and self.quant is None
+        if self.quant == "fp8":
+            # W8A8: e4m3 weights with per-row scales (quantised once per model), per-token activation scales
+            if not self.fuse_swiglu or model.tp_size != 1:
+                raise ValueError("quantization='fp8' needs the fused SwiGLU layout and tp_size=1")
+            if getattr(model, "_w8", None) is None:
+                model._w8 = [{n: K.quantize_weight_e4m3(getattr(L, n)) for n in ("wqkv", "wo", "wgu", "wdown")}
+                             for L in model.layers]
+            wide = max(self.d, self.nq * self.D, self.ffn)
+            self.x8 = torch.zeros(max_tokens, (wide + 15) // 16 * 16, dtype=torch.uint8, device=dev)
+            self.xs = torch.zeros(max_tokens, dtype=f32, device=dev)
         if self.fold:
             model.fold_norms()
             self.hb = torch.empty(max_tokens, self.d, dtype=bf16, device=dev)
@@ -245,6 +256,8 @@ class NativeLlama:
         assert T <= self.T
         if self.fold:
             return self._forward_folded(ids, positions, cache_locs, rows, prefix_lens, bs, E, two_pass)
+        if self.quant == "fp8":
+            return self._forward_fp8(ids, positions, cache_locs, rows, prefix_lens, bs, E, two_pass)
         L0 = m.layers[0]
         K.add_rmsnorm(self.h, L0.ln1, self.xn, M=T, d=self.d, eps=c.rms_eps, ids=ids, embed=m.embed, pdl=pdl)
         n_layers = len(m.layers)
@@ -264,6 +277,38 @@ class NativeLlama:
             self._gemm(L.wdown, self.act, self.h, T, K.EPI_RESID_F32)
             w_next = m.layers[li + 1].ln1 if li + 1 < n_layers else m.final_norm
             K.add_rmsnorm(self.h, w_next, self.xn, M=T, d=self.d, eps=c.rms_eps, pdl=pdl)
+        return self.xn
+
+    def _forward_fp8(self, ids, positions, cache_locs, rows, prefix_lens, bs: int, E: int, two_pass: bool):
+        """W8A8 layer chain: every projection reads e4m3 weights (half the bytes of bf16) and per-token quantised
+        activations through tcgen05.mma.kind::f8f6f4; norms, attention, residual stream and lm_head stay as in the bf16
+        chain.  Nine launches per layer: two norms that also emit the e4m3 rows, two quantisation passes (attention
+        output, SwiGLU output), four GEMMs, attention."""
+        m, c, pdl = self.m, self.c, self.pdl
+        T = bs * E
+        st, ldx = self.status, self.x8.stride(0)
+        K.add_rmsnorm_q8(self.h, m.layers[0].ln1, self.xn, self.x8, self.xs, M=T, d=self.d, eps=c.rms_eps, ids=ids,
+                         embed=m.embed, pdl=pdl)
+        n_layers = len(m.layers)
+        scale = self.D ** -0.5
+        nqd = self.nq * self.D
+
+        def gemm(w, x, kdim, out, epi, splits, ldo):
+            if x is not None:                       # x None: the norm kernel already left the e4m3 rows in x8
+                K.quant_rows_e4m3(x, self.x8, self.xs, M=T, K=kdim, pdl=pdl)
+            K.gemm_skinny_fp8(w[0], w[1], self.x8, self.xs, out, M=T, splits=splits, epi=epi, ldx=ldx, ldo=ldo,
+                              status=st, pdl=pdl)
+        for li, L in enumerate(m.layers):
+            w8 = m._w8[li]
+            gemm(w8["wqkv"], None, self.d, self.qkv, K.EPI_STORE_F32, self._splits(self.nqkv, self.d // 2, T),
+                 self.qkv.stride(0))
+            self._attention(li, positions, cache_locs, rows, prefix_lens, bs, E, two_pass, scale)
+            gemm(w8["wo"], self.attn, nqd, self.h, K.EPI_RESID_F32, self._splits(self.d, nqd // 2, T), self.d)
+            K.add_rmsnorm_q8(self.h, L.ln2, self.xn, self.x8, self.xs, M=T, d=self.d, eps=c.rms_eps, pdl=pdl)
+            gemm(w8["wgu"], None, self.d, self.act, K.EPI_SWIGLU_BF16, self._gu_splits(T), self.act.stride(0))
+            gemm(w8["wdown"], self.act, self.ffn, self.h, K.EPI_RESID_F32, self._splits(self.d, self.ffn // 2, T), self.d)
+            w_next = m.layers[li + 1].ln1 if li + 1 < n_layers else m.final_norm
+            K.add_rmsnorm_q8(self.h, w_next, self.xn, self.x8, self.xs, M=T, d=self.d, eps=c.rms_eps, pdl=pdl)
         return self.xn
 
     def _gu_splits(self, M: int) -> int:

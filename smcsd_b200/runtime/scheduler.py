@@ -110,6 +110,16 @@ class SMCScheduler:
                 self.draft.tp_group = comm.device_group
         if self.target.cfg.vocab_size != self.draft.cfg.vocab_size:
             raise ValueError("target and draft must share a vocabulary")
+        if a.quantization == "fp8":
+            # W8A8 on the tensor cores (e4m3 weights with per-row scales, activations quantised per token on the fly);
+            # the models keep their bf16 weights for the embedding, the lm_head and the PyTorch reference paths
+            if backend != "native" or tp_size > 1 or any(m.cfg.arch != "llama" for m in (self.target, self.draft)):
+                raise ValueError("quantization='fp8' needs the kernel backend, dense models and tp_size=1")
+            # the draft is bound by launch latency, not by weight bytes, and keeps its five-launch bf16 layers unless
+            # SMC_FP8_DRAFT=1 (the importance weights absorb whatever the proposal computes)
+            self.target.quantization = "fp8"
+            if os.environ.get("SMC_FP8_DRAFT", "0") == "1":
+                self.draft.quantization = "fp8"
         self.context_len = int(a.context_length or min(self.target.cfg.max_position, 16384))
         # ---- memory -----------------------------------------------------------
         N, G = self.n_local, a.gamma + 1

@@ -321,3 +321,63 @@ def test_shared_prefix_attention_in_the_decode_cycle(monkeypatch, tc):
         assert sched.native_runner.check_status() == 0
         outs[graph] = po.particle_output_ids
     assert outs[False] == outs[True]
+
+
+def test_fp8_quantised_engine(monkeypatch):
+    """quantization='fp8': the kernel chain serves e4m3 weights with per-row scales and per-token quantised activations.
+    (1) One forward against the PyTorch model whose projection weights were replaced by the dequantised e4m3 values:
+    only the activation quantisation separates the two.  (2) A decode run: graph replays equal the eager launches and
+    the importance weights stay small when draft == target (both quantised the same way)."""
+    from smcsd_b200.config import EngineArgs
+    from smcsd_b200.io_types import GenerateRequest, ParticleOutput, SamplingParams
+    from smcsd_b200.models import build_model
+    from smcsd_b200.models.layers import ExtendBatch
+    from smcsd_b200.ops import native as K
+    from smcsd_b200.runtime.scheduler import SMCScheduler
+    tgt, _ = _cfgs()
+    model = build_model(tgt, torch.bfloat16, "cuda", seed=0)
+    outs = {}
+    for graph in (False, True):
+        args = EngineArgs(model_path=tgt, draft_model_path=tgt, n_particles=4, gamma=4, draft_temperature=0.7,
+                          target_temperature=0.7, max_running_requests=2, context_length=512, device="cuda",
+                          max_total_tokens=8192, backend="native", resample_threshold=0.0, cycle_graph=graph,
+                          quantization="fp8").finalize()
+        sched = SMCScheduler(args, target=model, draft=model)
+        nm = sched.native_runner.target
+        assert nm.quant == "fp8" and not nm.fold
+        if not graph:
+            # (1) logits of a 4 x 5 token forward
+            dev = "cuda"
+            bs, E = 4, 5
+            g = torch.Generator(device=dev).manual_seed(1)
+            rows = torch.arange(bs, dtype=torch.int32, device=dev)
+            for b in range(bs):
+                sched.bt.table[b, :E + 3] = sched.alloc.alloc(E + 3)
+            ids = torch.randint(0, 8192, (bs * E,), generator=g, device=dev, dtype=torch.int32)
+            pos = torch.arange(E, device=dev).repeat(bs).to(torch.int32)
+            locs = sched.bt.table[:bs, :E].reshape(-1).contiguous()
+            pref = torch.zeros(bs, dtype=torch.int32, device=dev)
+            nm.forward(ids, pos, locs, rows, pref, bs, E)
+            got = nm.lm_head(bs * E)[: bs * E].clone()
+            torch.cuda.synchronize()
+            saved = [(L.wqkv, L.wo, L.wgu, L.wdown) for L in model.layers]
+            for L, w8 in zip(model.layers, model._w8):
+                for name in ("wqkv", "wo", "wgu", "wdown"):
+                    q, s = w8[name]
+                    setattr(L, name, (q.view(torch.float8_e4m3fn).float() * s[:, None]).bfloat16())
+            ext = ExtendBatch(ids.long(), pos.long(), locs, rows, pref, extend_len=E, prefix_lens_host=[0] * bs)
+            ref = model.logits_torch(model.forward_torch(ext, sched.kv_t, sched.bt.table))
+            for L, ws in zip(model.layers, saved):
+                L.wqkv, L.wo, L.wgu, L.wdown = ws
+            scale = ref.abs().max().item()
+            assert (got - ref).abs().max().item() < 0.08 * scale
+            for b in range(bs):
+                sched.alloc.free(sched.bt.table[b, :E + 3].clone())
+                sched.bt.table[b].zero_()
+        sched.add_request(GenerateRequest("r", _prompts(1, L=40)[0], SamplingParams(max_new_tokens=30, ignore_eos=True)))
+        o = sched.run_until_idle()
+        po = [x for x in o if isinstance(x, ParticleOutput)][0]
+        assert max(abs(w) for w in po.log_w_tilde) < 0.35, po.log_w_tilde
+        assert sched.native_runner.check_status() == 0
+        outs[graph] = po.particle_output_ids
+    assert outs[False] == outs[True]

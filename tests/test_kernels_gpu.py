@@ -465,6 +465,85 @@ def test_attention_shared_prefix_passes(groups, N, NP, E, Hq, Hkv, D, P, suffix,
     assert err < 3e-2 * max(1.0, ref.abs().max().item()), err
 
 
+# ------------------------------------------------------------------------------- FP8 (W8A8) GEMM
+def test_quant_rows_e4m3_matches_torch():
+    K = _K()
+    torch.manual_seed(31)
+    M, Kd = 37, 4096
+    x = (torch.randn(M, Kd, device="cuda") * torch.rand(M, 1, device="cuda") * 3).bfloat16()
+    q = torch.zeros(M, Kd, device="cuda", dtype=torch.uint8)
+    sc = torch.zeros(M, device="cuda")
+    K.quant_rows_e4m3(x, q, sc, M=M, K=Kd)
+    torch.cuda.synchronize()
+    ref_sc = x.float().abs().amax(dim=1) / 448.0
+    assert torch.allclose(sc, ref_sc, rtol=1e-6)
+    deq = q.view(torch.float8_e4m3fn).float() * sc[:, None]
+    # e4m3 keeps 3 mantissa bits: round-to-nearest error <= 2^-4 of the value (plus the subnormal step near zero)
+    err = (deq - x.float()).abs()
+    assert (err <= x.float().abs() * 2 ** -4 + sc[:, None] * 2 ** -9 * 1.001).all()
+    ref_q = (x.float() / ref_sc[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
+    assert (q != ref_q).float().mean().item() < 1e-3          # x * (1 / scale) against x / scale: rare one-step ties
+
+
+@pytest.mark.parametrize("N,Kd,M,splits", [
+    (3072, 2048, 8, 8), (6144, 4096, 72, 4), (4096, 14336, 72, 4), (2048, 8192, 8, 8), (1024, 512, 40, 2),
+    (4096, 4096, 200, 1), (300, 1024, 9, 1),
+])
+def test_gemm_fp8_matches_dequantised_reference(N, Kd, M, splits):
+    """W8A8 on tcgen05 kind::f8f6f4: e4m3 products are exact in fp32, so against an fp32 matmul of the dequantised
+    operands only the accumulation order differs.  Plain store, residual accumulate and bf16 store epilogues."""
+    K = _K()
+    torch.manual_seed(32)
+    W = torch.randn(N, Kd, device="cuda") * 0.05
+    X = torch.randn(M, Kd, device="cuda").bfloat16()
+    W8, ws = K.quantize_weight_e4m3(W)
+    X8 = torch.zeros(M, Kd, device="cuda", dtype=torch.uint8)
+    xs = torch.zeros(M, device="cuda")
+    K.quant_rows_e4m3(X, X8, xs, M=M, K=Kd)
+    ref = (X8.view(torch.float8_e4m3fn).float() * xs[:, None]) @ (W8.view(torch.float8_e4m3fn).float() * ws[:, None]).t()
+    st = _status()
+    out = torch.full((M, N), float("nan"), device="cuda")
+    K.gemm_skinny_fp8(W8, ws, X8, xs, out, M=M, splits=splits, epi=K.EPI_STORE_F32, ldo=N, status=st)
+    h0 = torch.randn(M, N, device="cuda")
+    h = h0.clone()
+    K.gemm_skinny_fp8(W8, ws, X8, xs, h, M=M, splits=splits, epi=K.EPI_RESID_F32, ldo=N, status=st, pdl=True)
+    ob = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    K.gemm_skinny_fp8(W8, ws, X8, xs, ob, M=M, splits=1, epi=K.EPI_BF16, ldo=N, status=st)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    tol = 1e-3 * max(1.0, ref.abs().max().item())
+    assert (out - ref).abs().max().item() < tol
+    assert (h - h0 - ref).abs().max().item() < tol
+    assert (ob.float() - ref).abs().max().item() < 6e-3 * max(1.0, ref.abs().max().item())
+    # and the quantised product stays close to the bf16 one (e4m3 noise averages out over K)
+    full = X.float() @ W.t()
+    assert (out - full).abs().max().item() < 0.08 * full.abs().max().item()
+
+
+@pytest.mark.parametrize("ffn,d,M,splits", [(8192, 2048, 8, 1), (14336, 4096, 72, 1), (1024, 256, 40, 2)])
+def test_gemm_fp8_swiglu_epilogue(ffn, d, M, splits):
+    K = _K()
+    from smcsd_b200.models.llama import interleave_gate_up
+    torch.manual_seed(33)
+    Wg, Wu = torch.randn(ffn, d, device="cuda") * 0.05, torch.randn(ffn, d, device="cuda") * 0.05
+    Wgu = interleave_gate_up(Wg.bfloat16(), Wu.bfloat16(), 64)
+    W8, ws = K.quantize_weight_e4m3(Wgu)
+    X = torch.randn(M, d, device="cuda").bfloat16()
+    X8 = torch.zeros(M, d, device="cuda", dtype=torch.uint8)
+    xs = torch.zeros(M, device="cuda")
+    K.quant_rows_e4m3(X, X8, xs, M=M, K=d)
+    from smcsd_b200.models.llama import split_gate_up
+    full = (X8.view(torch.float8_e4m3fn).float() * xs[:, None]) @ (W8.view(torch.float8_e4m3fn).float() * ws[:, None]).t()
+    g, u = split_gate_up(full, 64)
+    ref = torch.nn.functional.silu(g) * u
+    act = torch.zeros(M, ffn, device="cuda", dtype=torch.bfloat16)
+    st = _status()
+    K.gemm_skinny_fp8(W8, ws, X8, xs, act, M=M, splits=splits, epi=K.EPI_SWIGLU_BF16, ldo=ffn, status=st)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    assert (act.float() - ref).abs().max().item() < 6e-3 * max(1.0, ref.abs().max().item())
+
+
 # ------------------------------------------------------------------------------- RMSNorm folded into the GEMMs
 @pytest.mark.parametrize("d,ffn,M", [(2048, 8192, 8), (4096, 14336, 72), (512, 1536, 20)])
 def test_gemm_with_folded_rmsnorm(d, ffn, M):
@@ -547,3 +626,24 @@ def test_lm_head_sampling_epilogue_matches_sampler_on_stored_logits(V, d, M, ste
     sc = tokens_in >= 0
     got_ref = ref[torch.arange(M, device="cuda")[sc], tokens_in[sc].long()]
     assert (lp_b[sc] - got_ref).abs().max().item() < 5e-3
+
+
+def test_add_rmsnorm_with_e4m3_output_matches_separate_quantisation():
+    """The norm kernel's fused e4m3 output equals a separate quantisation pass over its bf16 output."""
+    K = _K()
+    torch.manual_seed(41)
+    M, d = 19, 4096
+    h = torch.randn(M, d, device="cuda")
+    w = (1.0 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+    xn = torch.zeros(M, d, device="cuda", dtype=torch.bfloat16)
+    q8 = torch.zeros(M, d, device="cuda", dtype=torch.uint8)
+    qs = torch.zeros(M, device="cuda")
+    K.add_rmsnorm_q8(h.clone(), w, xn, q8, qs, M=M, d=d, eps=1e-5)
+    ref_q = torch.zeros_like(q8)
+    ref_s = torch.zeros_like(qs)
+    K.quant_rows_e4m3(xn, ref_q, ref_s, M=M, K=d)
+    torch.cuda.synchronize()
+    ref_xn = (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()).bfloat16()
+    assert (xn.float() - ref_xn.float()).abs().max().item() < 2e-2
+    assert torch.allclose(qs, ref_s, rtol=1e-6)
+    assert torch.equal(q8, ref_q)
