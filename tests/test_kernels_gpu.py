@@ -70,6 +70,31 @@ def test_gemm_cluster_splitk(N, Kd, M, splits):
     assert torch.equal(out, out2), "the cluster reduction must be bit-deterministic"
 
 
+@pytest.mark.parametrize("N,Kd,M", [(4096, 4096, 1152), (6144, 4096, 513), (1024, 512, 400)])
+def test_gemm_large_batches(N, Kd, M):
+    """Prompt-pass sized batches (several token tiles per weight slab): bf16 store, fp32 store and residual
+    accumulate, against fp32 PyTorch."""
+    K = _K()
+    torch.manual_seed(17)
+    W = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    X = torch.randn(M, Kd, device="cuda").bfloat16()
+    ref = X.float() @ W.float().t()
+    st = _status()
+    ob = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    K.gemm_skinny(W, X, ob, M=M, splits=1, epi=K.EPI_BF16, status=st)
+    of = torch.full((M, N), float("nan"), device="cuda")
+    K.gemm_skinny(W, X, of, M=M, splits=1, epi=K.EPI_STORE_F32, ldo=N, status=st)
+    h0 = torch.randn(M, N, device="cuda")
+    h = h0.clone()
+    K.gemm_skinny(W, X, h, M=M, splits=1, epi=K.EPI_RESID_F32, ldo=N, status=st, pdl=True)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    tol = 1e-3 * max(1.0, ref.abs().max().item())
+    assert (of - ref).abs().max().item() < tol
+    assert (h - h0 - ref).abs().max().item() < tol
+    assert (ob.float() - ref).abs().max().item() < 6e-3 * max(1.0, ref.abs().max().item())
+
+
 def test_gemm_bf16_and_strided_rows():
     K = _K()
     torch.manual_seed(1)
@@ -86,7 +111,7 @@ def test_gemm_bf16_and_strided_rows():
     assert (out.float() - ref).abs().max().item() < 6e-3 * ref.abs().max().item()      # one bf16 rounding of the output
 
 
-@pytest.mark.parametrize("ffn,d,M", [(8192, 2048, 8), (14336, 4096, 72), (1024, 256, 40)])
+@pytest.mark.parametrize("ffn,d,M", [(8192, 2048, 8), (14336, 4096, 72), (1024, 256, 40), (14336, 4096, 700)])
 def test_gemm_swiglu_epilogue(ffn, d, M):
     K = _K()
     from smcsd_b200.models.llama import interleave_gate_up
