@@ -381,3 +381,27 @@ def test_fp8_quantised_engine(monkeypatch):
         assert sched.native_runner.check_status() == 0
         outs[graph] = po.particle_output_ids
     assert outs[False] == outs[True]
+
+
+def test_capture_warm_up_restores_token_histories_and_group_flags():
+    """The warm-up cycle that precedes a graph capture runs on live state and is then rolled back; the roll-back list
+    must cover everything a cycle (including a resampling step) writes: token histories and group flags too."""
+    eng = _engine(backend="native")
+    sched = eng._sched
+    r, st = sched.native_runner, sched.state
+    listed = r._mutable(st)
+    for name in ("all_token_ids", "seq_lens", "log_weights", "counters"):
+        assert any(t is getattr(st, name) for t in listed), name
+    assert any(t is st.bt.table for t in listed)
+    if getattr(st, "group_active", None) is not None:
+        assert any(t is st.group_active for t in listed)
+    # a run that captures a new graph key while a request is in flight (batch shrinks from two groups to one) yields
+    # the same tokens as the same run without graphs
+    outs = {}
+    for graph in (False, True):
+        e = _engine(backend="native", cycle_graph=graph, max_running_requests=2, random_seed=3)
+        o = e.generate(input_ids=[p for p in _prompts(2, L=30, seed=9)],
+                       sampling_params=[{"max_new_tokens": 12, "ignore_eos": True}, {"max_new_tokens": 40, "ignore_eos": True}])
+        outs[graph] = [x["smc_particle_output_ids"] for x in o]
+        assert e._sched.native_runner.check_status() == 0
+    assert outs[False] == outs[True]
