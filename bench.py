@@ -97,6 +97,10 @@ def main() -> int:
     ap.add_argument("--no-config2", action="store_true")
     ap.add_argument("--no-fused", action="store_true", help="skip the multi-GPU fused-collective measurements")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--quantization", default=None, choices=[None, "fp8"],
+                    help="run the MAIN measurement with W8A8 projections (the line's dtype says so; not the headline)")
+    ap.add_argument("--kv-cache-dtype", default="auto", choices=["auto", "fp8_e4m3"],
+                    help="run the MAIN measurement with the e4m3 KV cache (the line's dtype says so; not the headline)")
     ap.add_argument("--no-fp8", action="store_true",
                     help="skip the extra W8A8 (e4m3) measurement reported under the 'fp8' key (one GPU only)")
     args = ap.parse_args()
@@ -134,7 +138,8 @@ def main() -> int:
                     base_gpu_id=local, context_length=max(4096, args.prompt_len) + max(new_tokens, args.e2e_new_tokens) + 4 * G,
                     random_seed=rank,
                     backend="native" if args.impl == "native" else "torch", in_process=True,
-                    cycle_graph=not args.no_graph, mem_fraction_static=0.6)
+                    cycle_graph=not args.no_graph, mem_fraction_static=0.6, quantization=args.quantization,
+                    kv_cache_dtype=args.kv_cache_dtype)
     sched = eng._sched
     vocab = sched.target.cfg.vocab_size
     lens = [args.prompt_len] if args.prompt_len else lognormal_lengths(1, seed=1000 + rank)
@@ -196,7 +201,7 @@ def main() -> int:
 
     # ---- the same K cycles with quantization='fp8' (labelled, next to the bf16 headline; one GPU only) -------------
     fp8 = None
-    if world == 1 and not args.no_fp8 and args.impl == "native":
+    if world == 1 and not args.no_fp8 and args.impl == "native" and not args.quantization and args.kv_cache_dtype == "auto":
         try:
             eng.shutdown()
             del eng, sched
@@ -263,7 +268,9 @@ def main() -> int:
             "ms_per_step": ms_max / steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": e2e_ratio if e2e_ratio is not None else value / (PUBLISHED_TOKS * world),
             "vs_baseline_device_timed": value / (PUBLISHED_TOKS * world),
-            "dtype": "bf16", "data": "synthetic", "impl": args.impl,
+            "dtype": "bf16" + (" + e4m3 W8A8 projections of the target" if args.quantization else "") +
+                     (" + e4m3 KV cache" if args.kv_cache_dtype != "auto" else ""),
+            "data": "synthetic", "impl": args.impl,
             "config": {"model": f"{args.target}+{args.draft}", "global_batch": world, "seq_len": lens[0],
                        "parallelism": f"dp{world}", "n_particles": args.n_particles, "gamma": args.gamma,
                        "tokens_per_step_per_request": G, "cycle_graph": not args.no_graph,

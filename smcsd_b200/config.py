@@ -109,8 +109,11 @@ class EngineArgs:
         if self.quantization not in (None, "fp8"):
             raise ValueError(f"quantization={self.quantization!r} is not supported: weights are served in bf16 or, with "
                              "quantization='fp8', as e4m3 with per-row scales (dense models, kernel backend)")
-        if self.kv_cache_dtype not in ("auto", "bf16", "bfloat16"):
-            raise ValueError(f"kv_cache_dtype={self.kv_cache_dtype!r} is not supported: the KV cache is bf16")
+        if self.kv_cache_dtype in ("fp8", "fp8_e4m3"):
+            self.kv_cache_dtype = "fp8_e4m3"
+        if self.kv_cache_dtype not in ("auto", "bf16", "bfloat16", "fp8_e4m3"):
+            raise ValueError(f"kv_cache_dtype={self.kv_cache_dtype!r} is not supported: the KV cache holds bf16 rows or, "
+                             "with kv_cache_dtype='fp8_e4m3', e4m3 rows with one scale per token and kv head")
         self.target_temperature = max(float(self.target_temperature), 1e-5)
         self.defer_bonus = env_flag("SMC_DEFER_BONUS", self.defer_bonus, True)
         self.cycle_graph = env_flag("SMC_CYCLE_GRAPH", self.cycle_graph, True)

@@ -129,23 +129,62 @@ class KVSpec:
     n_kv_heads: int
     head_dim: int
     dtype: torch.dtype = torch.bfloat16
+    fp8: bool = False    # e4m3 cache: a page row holds Hkv * D value bytes + one fp32 scale per kv head (padded to 16)
+
+    @property
+    def row_width(self) -> int:
+        """Elements of one page row of the K (or V) tensor."""
+        if self.fp8:
+            return (self.n_kv_heads * self.head_dim + self.n_kv_heads * 4 + 15) // 16 * 16
+        return self.n_kv_heads * self.head_dim
+
+    @property
+    def store_dtype(self) -> torch.dtype:
+        return torch.uint8 if self.fp8 else self.dtype
 
     @property
     def cell_bytes(self) -> int:
-        return 2 * self.n_layers * self.n_kv_heads * self.head_dim * torch.empty((), dtype=self.dtype).element_size()
+        return 2 * self.n_layers * self.row_width * torch.empty((), dtype=self.store_dtype).element_size()
+
+
+def kv_rows_to_float(rows: torch.Tensor, n_kv_heads: int, head_dim: int) -> torch.Tensor:
+    """Page rows of a K or V pool -> fp32 [L, Hkv, D]; e4m3 rows (uint8) are dequantised with their per-head scales."""
+    L = rows.shape[0]
+    if rows.dtype != torch.uint8:
+        return rows.view(L, n_kv_heads, head_dim).float()
+    nv = n_kv_heads * head_dim
+    vals = rows[:, :nv].contiguous().view(torch.float8_e4m3fn).float().view(L, n_kv_heads, head_dim)
+    scales = rows[:, nv:nv + 4 * n_kv_heads].contiguous().view(torch.float32).view(L, n_kv_heads, 1)
+    return vals * scales
+
+
+def kv_rows_from_float(x: torch.Tensor, row_width: int) -> torch.Tensor:
+    """fp32 / bf16 [T, Hkv, D] -> e4m3 page rows [T, row_width] (uint8) with per-(token, head) scales max|x| / 448."""
+    T, H, D = x.shape
+    xf = x.float()
+    scale = xf.abs().amax(dim=-1).clamp_(min=1e-12) / 448.0                      # [T, H]
+    q = (xf / scale.unsqueeze(-1)).to(torch.float8_e4m3fn).view(torch.uint8).reshape(T, H * D)
+    out = torch.zeros(T, row_width, dtype=torch.uint8, device=x.device)
+    out[:, :H * D] = q
+    out[:, H * D:H * D + 4 * H] = scale.contiguous().view(torch.uint8).reshape(T, 4 * H)
+    return out
 
 
 class KVPool:
-    """K and V as ``[layer, page, kv_head * head_dim]``; one row per token page."""
+    """K and V as ``[layer, page, row]``; one row per token page (bf16 values, or the e4m3 layout of ``KVSpec``)."""
 
     def __init__(self, spec: KVSpec, n_pages: int, device):
         self.spec = spec
         self.n_pages = n_pages
-        row = spec.n_kv_heads * spec.head_dim
-        self.k = torch.zeros(spec.n_layers, n_pages + 1, row, dtype=spec.dtype, device=device)
-        self.v = torch.zeros(spec.n_layers, n_pages + 1, row, dtype=spec.dtype, device=device)
+        self.k = torch.zeros(spec.n_layers, n_pages + 1, spec.row_width, dtype=spec.store_dtype, device=device)
+        self.v = torch.zeros(spec.n_layers, n_pages + 1, spec.row_width, dtype=spec.store_dtype, device=device)
 
     def write(self, layer: int, locs: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
+        if self.spec.fp8:
+            H, D = self.spec.n_kv_heads, self.spec.head_dim
+            self.k[layer].index_copy_(0, locs.long(), kv_rows_from_float(k.reshape(k.shape[0], H, D), self.spec.row_width))
+            self.v[layer].index_copy_(0, locs.long(), kv_rows_from_float(v.reshape(v.shape[0], H, D), self.spec.row_width))
+            return
         self.k[layer].index_copy_(0, locs.long(), k.reshape(k.shape[0], -1).to(self.k.dtype))
         self.v[layer].index_copy_(0, locs.long(), v.reshape(v.shape[0], -1).to(self.v.dtype))
 

@@ -86,6 +86,11 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, table: torch.Tensor) ->
     return out.to(x.dtype)
 
 
+def kv_rows_to_float(rows: torch.Tensor, n_kv_heads: int, head_dim: int) -> torch.Tensor:
+    from ..memory.pools import kv_rows_to_float as f       # e4m3 page rows carry their scales (memory/pools.py)
+    return f(rows, n_kv_heads, head_dim)
+
+
 def paged_attention_reference(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                               block_table: torch.Tensor, batch: ExtendBatch, n_kv_heads: int,
                               scale: Optional[float] = None) -> torch.Tensor:
@@ -103,8 +108,8 @@ def paged_attention_reference(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
             continue
         L = p + e
         pages = block_table[batch.rows[b].long(), :L].long()
-        k = k_pool[pages].view(L, n_kv_heads, D).float()
-        v = v_pool[pages].view(L, n_kv_heads, D).float()
+        k = kv_rows_to_float(k_pool[pages], n_kv_heads, D)
+        v = kv_rows_to_float(v_pool[pages], n_kv_heads, D)
         qb = q[t0:t0 + e].float().view(e, n_kv_heads, G, D)
         s = torch.einsum("ehgd,lhd->hgel", qb, k) * scale
         causal = torch.arange(L, device=q.device).unsqueeze(0) <= (p + torch.arange(e, device=q.device)).unsqueeze(1)

@@ -12,6 +12,8 @@
 // buffered), scores and P*V run on tensor cores (mma.sync m16n8k16, bf16 in / fp32 out) with
 // flash-style running max / sum in registers.  The new tokens form a last, causally masked tile
 // served from shared memory.
+#include <cuda_fp8.h>
+
 #include "attn_core.cuh"
 #include "common.cuh"
 
@@ -53,13 +55,19 @@ struct FusedAttnParams {
   int part_in_n;             // number of states to fold in (>= 1 when part_in is given)
   long long part_in_stride;  // floats between consecutive states
   int causal;                // 0: every key of the range is visible to every query row
+  // FP8 KV cache: a page row holds Hkv * D e4m3 bytes, then one fp32 scale per kv head, padded to 16 bytes
+  // (kv_row_bytes); value = byte * scale.  k_pool / v_pool then point at bytes.
+  int kv_row_bytes;
 };
 
 constexpr int RANGE = 2048;     // page ids staged per pass
 
 // PFX = false compiles the shared-prefix options out (no key_begin, no parked states, causal): the plain decode and
 // verify steps keep the lean kernel.
-template <int D, bool PFX>
+// KV8 = true reads and writes the e4m3 cache layout: tiles arrive as bytes in the upper half of their bf16 rows and are
+// expanded in place (scaled) before the tensor-core loop; new K/V rows are quantised per (token, kv head) on their way
+// to the pages.
+template <int D, bool PFX, bool KV8>
 __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p) {
   const int* const pfx_key_begin = PFX ? p.key_begin : nullptr;
   float* const pfx_part_out = PFX ? p.part_out : nullptr;
@@ -117,12 +125,58 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
     __nv_bfloat16* Kt = my_tiles + (size_t)stage * 2 * TILE;
     __nv_bfloat16* Vt = Kt + TILE;
     const int k0 = tile * TK;
-    for (int c = gt; c < TK * CPR; c += gsize) {
-      const int key = c / CPR, col = c % CPR;
-      const int page = (r0 + k0 + key < r1) ? pg[k0 + key] : 0;
-      const size_t off = (size_t)page * kv_row + (size_t)kvh * D + col * 8;
-      cp_async16(Kt + key * LD + col * 8, p.k_pool + off);
-      cp_async16(Vt + key * LD + col * 8, p.v_pool + off);
+    if constexpr (KV8) {
+      // e4m3 rows: D bytes land in bytes [D, 2D) of the key's bf16 row, the scale in the row's padding at byte 2D
+      constexpr int CPR8 = D / 16;
+      const uint8_t* kp = reinterpret_cast<const uint8_t*>(p.k_pool);
+      const uint8_t* vp = reinterpret_cast<const uint8_t*>(p.v_pool);
+      for (int c = gt; c < TK * (CPR8 + 1); c += gsize) {
+        const int key = c / (CPR8 + 1), col = c % (CPR8 + 1);
+        const int page = (r0 + k0 + key < r1) ? pg[k0 + key] : 0;
+        const size_t rowoff = (size_t)page * p.kv_row_bytes;
+        uint8_t* kd = reinterpret_cast<uint8_t*>(Kt + key * LD);
+        uint8_t* vd = reinterpret_cast<uint8_t*>(Vt + key * LD);
+        if (col < CPR8) {
+          cp_async16(kd + D + col * 16, kp + rowoff + (size_t)kvh * D + col * 16);
+          cp_async16(vd + D + col * 16, vp + rowoff + (size_t)kvh * D + col * 16);
+        } else {
+          cp_async4(kd + 2 * D, kp + rowoff + (size_t)p.Hkv * D + kvh * 4);
+          cp_async4(vd + 2 * D, vp + rowoff + (size_t)p.Hkv * D + kvh * 4);
+        }
+      }
+    } else {
+      for (int c = gt; c < TK * CPR; c += gsize) {
+        const int key = c / CPR, col = c % CPR;
+        const int page = (r0 + k0 + key < r1) ? pg[k0 + key] : 0;
+        const size_t off = (size_t)page * kv_row + (size_t)kvh * D + col * 8;
+        cp_async16(Kt + key * LD + col * 8, p.k_pool + off);
+        cp_async16(Vt + key * LD + col * 8, p.v_pool + off);
+      }
+    }
+  };
+  // e4m3 tile -> bf16 in place: one thread per key row walks its 16-byte chunks in order (chunk c is read before the
+  // 32 bytes it expands to are written; those never reach a chunk that is still unread)
+  auto expand = [&](__nv_bfloat16* Kt) {
+    for (int rr = gt; rr < 2 * TK; rr += gsize) {                // rows of the K tile, then of the V tile
+      uint8_t* row = reinterpret_cast<uint8_t*>(Kt + (size_t)rr * LD);
+      const float sc = *reinterpret_cast<const float*>(row + 2 * D);
+#pragma unroll
+      for (int c = 0; c < D / 16; ++c) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(row + D + c * 16);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] & 0xffffu), __NV_E4M3);
+          const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] >> 16), __NV_E4M3);
+          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+          const float2 b2 = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+          o[2 * i] = pack_bf16(a.x * sc, a.y * sc);
+          o[2 * i + 1] = pack_bf16(b2.x * sc, b2.y * sc);
+        }
+        *reinterpret_cast<uint4*>(row + c * 32) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(row + c * 32 + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+      }
     }
   };
   // Ring of `stg` tiles per key-way: the prologue requests the first stg-1 tiles of a range, then every
@@ -262,6 +316,31 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
     __syncthreads();
   }
   // new K/V rows go to their pages (one CTA per (sequence, kv head) writes them)
+  if constexpr (KV8) {
+    if (ks == p.KS - 1 && !pool_only && blockIdx.z == 0) {
+      // one warp per new K / V row: scale = max|x| / 448, e4m3 bytes and the scale go to the row's page
+      uint8_t* kp = reinterpret_cast<uint8_t*>(p.k_pool);
+      uint8_t* vp = reinterpret_cast<uint8_t*>(p.v_pool);
+      for (int j = warp; j < 2 * p.E; j += nwarps) {
+        const bool is_v = j >= p.E;
+        const int e = is_v ? j - p.E : j;
+        const __nv_bfloat16* src = (is_v ? Vn : Kn) + (size_t)e * LD;
+        int loc = p.cache_locs[b * p.E + e];
+        if (loc < 0 || loc > p.n_pages) { if (lane == 0) atomicOr(p.status, SMC_ERR_BOUNDS); loc = 0; }
+        float amax = 0.f;
+        for (int i = lane; i < D; i += 32) amax = fmaxf(amax, fabsf(__bfloat162float(src[i])));
+        amax = warp_max(amax);
+        const float sc = fmaxf(amax, 1e-12f) * (1.f / 448.f), inv = 1.f / sc;
+        uint8_t* dst = (is_v ? vp : kp) + (size_t)loc * p.kv_row_bytes;
+        for (int i = lane * 2; i < D; i += 64) {
+          const __nv_fp8x2_storage_t q = __nv_cvt_float2_to_fp8x2(
+              make_float2(__bfloat162float(src[i]) * inv, __bfloat162float(src[i + 1]) * inv), __NV_SATFINITE, __NV_E4M3);
+          *reinterpret_cast<uint16_t*>(dst + (size_t)kvh * D + i) = (uint16_t)q;
+        }
+        if (lane == 0) *reinterpret_cast<float*>(dst + (size_t)p.Hkv * D + kvh * 4) = sc;
+      }
+    }
+  } else
   if (ks == p.KS - 1 && !pool_only && blockIdx.z == 0) {
     constexpr int CPR = D / 8;
     for (int c = threadIdx.x; c < p.E * CPR * 2; c += blockDim.x) {
@@ -312,6 +391,10 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       if (kw + jn * n_kw < ntiles) issue(r0, r1, kw + jn * n_kw, jn % stg);
       cp_async_commit();
       const int nvalid = min(TK, r1 - r0 - tile * TK);
+      if constexpr (KV8) {
+        expand(my_tiles + (size_t)(j % stg) * 2 * TILE);
+        group_barrier(1 + kw, gsize);
+      }
       const __nv_bfloat16* Kt = my_tiles + (size_t)(j % stg) * 2 * TILE;
       const int key0 = r0 + tile * TK;
       process_tile<D, TK / 8, Q_REGS>(Kt, Kt + TILE, qa, Qs_mt, p.scale, st, nvalid,
@@ -540,7 +623,7 @@ SMC_API int smc_attention_fused_ex(const float* qkv, const void* q_in, int ld_qk
                                    const int* rows, const int* prefix_lens, void* out, int bs, int E, int Hq, int Hkv,
                                    int D, int KS, float scale, int* status, int pdl, const int* key_begin,
                                    float* part_out, const float* part_in, int part_in_n, long long part_in_stride,
-                                   int causal, cudaStream_t st);
+                                   int causal, int kv_fp8, cudaStream_t st);
 
 SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, int q_off, int gate_off, int k_off, int v_off,
                                 const int* positions, const int* cache_locs, const float* rope, int rd, int max_pos,
@@ -553,7 +636,7 @@ SMC_API int smc_attention_fused(const float* qkv, const void* q_in, int ld_qkv, 
   return smc_attention_fused_ex(qkv, q_in, ld_qkv, q_off, gate_off, k_off, v_off, positions, cache_locs, rope, rd, max_pos,
                                 qn_w, kn_w, norm_eps, norm_plus_one, k_pool, v_pool, n_pages, block_table, bt_stride, rows,
                                 prefix_lens, out, bs, E, Hq, Hkv, D, KS, scale, status, pdl, nullptr, nullptr, nullptr, 0, 0,
-                                1, st);
+                                1, 0, st);
 }
 
 // Same, with the shared-prefix options: key_begin [bs] (first key served), part_out / part_in [T, Hq, D + 2] fp32
@@ -568,7 +651,7 @@ SMC_API int smc_attention_fused_ex(const float* qkv, const void* q_in, int ld_qk
                                    const int* rows, const int* prefix_lens, void* out, int bs, int E, int Hq, int Hkv,
                                    int D, int KS, float scale, int* status, int pdl, const int* key_begin,
                                    float* part_out, const float* part_in, int part_in_n, long long part_in_stride,
-                                   int causal, cudaStream_t st) {
+                                   int causal, int kv_fp8, cudaStream_t st) {
   using namespace smc;
   if (part_in != nullptr && (part_in_n < 1 || part_in_n > 8)) return -75;
   if (bs <= 0) return 0;
@@ -598,12 +681,17 @@ SMC_API int smc_attention_fused_ex(const float* qkv, const void* q_in, int ld_qk
   p.pdl = pdl;
   p.key_begin = key_begin; p.part_out = part_out; p.part_in = part_in; p.causal = causal ? 1 : 0;
   p.part_in_n = part_in_n; p.part_in_stride = part_in_stride;
+  p.kv_row_bytes = kv_fp8 ? (Hkv * D + Hkv * 4 + 15) / 16 * 16 : 0;
   const size_t smem = fused_smem_bytes(D, n_mt, n_kw, stg);
   void (*kern)(const FusedAttnParams) = nullptr;
   const bool pfx = key_begin != nullptr || part_out != nullptr || part_in != nullptr || !causal;
-  if (D == 64) kern = pfx ? attn_fused_kernel<64, true> : attn_fused_kernel<64, false>;
-  else if (D == 128) kern = pfx ? attn_fused_kernel<128, true> : attn_fused_kernel<128, false>;
-  else if (D == 256) kern = pfx ? attn_fused_kernel<256, true> : attn_fused_kernel<256, false>;
+  if (kv_fp8) {                                  // the e4m3 cache is served by the full-option build
+    if (D == 64) kern = attn_fused_kernel<64, true, true>;
+    else if (D == 128) kern = attn_fused_kernel<128, true, true>;
+    else if (D == 256) kern = attn_fused_kernel<256, true, true>;
+  } else if (D == 64) kern = pfx ? attn_fused_kernel<64, true, false> : attn_fused_kernel<64, false, false>;
+  else if (D == 128) kern = pfx ? attn_fused_kernel<128, true, false> : attn_fused_kernel<128, false, false>;
+  else if (D == 256) kern = pfx ? attn_fused_kernel<256, true, false> : attn_fused_kernel<256, false, false>;
   else return -72;
   CUDA_CHECK_RET(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchAttribute attr[2];

@@ -331,6 +331,46 @@ __global__ void __launch_bounds__(256) quant_rows_e4m3_kernel(const __nv_bfloat1
 }
 }  // namespace smc
 
+namespace smc {
+// Rotated K / V rows (bf16, [M, Hkv * D]) -> the e4m3 cache: one warp per (token, kv head, K | V) row; the row's scale
+// max|x| / 448 goes behind the value bytes of its page row.
+__global__ void __launch_bounds__(256) kv_store_e4m3_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                                            int M, const int* __restrict__ cache_locs,
+                                                            uint8_t* __restrict__ k_pool, uint8_t* __restrict__ v_pool,
+                                                            int n_pages, int Hkv, int D, int row_bytes, int* status,
+                                                            int pdl) {
+  if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= M * Hkv * 2) return;
+  const int is_v = warp & 1, kvh = (warp >> 1) % Hkv, m = (warp >> 1) / Hkv;
+  int loc = cache_locs[m];
+  if (loc < 0 || loc > n_pages) { if (lane == 0) atomicOr(status, SMC_ERR_BOUNDS); loc = 0; }
+  const __nv_bfloat16* src = (is_v ? v : k) + (size_t)m * Hkv * D + (size_t)kvh * D;
+  float amax = 0.f;
+  for (int i = lane; i < D; i += 32) amax = fmaxf(amax, fabsf(__bfloat162float(src[i])));
+  amax = warp_max(amax);
+  const float sc = fmaxf(amax, 1e-12f) * (1.f / 448.f), inv = 1.f / sc;
+  uint8_t* dst = (is_v ? v_pool : k_pool) + (size_t)loc * row_bytes;
+  for (int i = lane * 2; i < D; i += 64) {
+    const __nv_fp8x2_storage_t q = __nv_cvt_float2_to_fp8x2(
+        make_float2(__bfloat162float(src[i]) * inv, __bfloat162float(src[i + 1]) * inv), __NV_SATFINITE, __NV_E4M3);
+    *reinterpret_cast<uint16_t*>(dst + (size_t)kvh * D + i) = (uint16_t)q;
+  }
+  if (lane == 0) *reinterpret_cast<float*>(dst + (size_t)Hkv * D + kvh * 4) = sc;
+}
+}  // namespace smc
+
+SMC_API int smc_kv_store_e4m3(const void* k, const void* v, int M, const int* cache_locs, void* k_pool, void* v_pool,
+                              int n_pages, int Hkv, int D, int row_bytes, int* status, int pdl, cudaStream_t st) {
+  using namespace smc;
+  if (M <= 0) return 0;
+  if ((D & 1) || row_bytes < Hkv * D + Hkv * 4) return -34;
+  const long long warps = (long long)M * Hkv * 2;
+  return launch_pdl(kv_store_e4m3_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), st, pdl,
+                    (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, M, cache_locs, (uint8_t*)k_pool, (uint8_t*)v_pool,
+                    n_pages, Hkv, D, row_bytes, status, pdl);
+}
+
 // x [M, ldx] bf16 -> q [M, ldq] e4m3 bytes + scale [M] fp32 (x ~ q * scale).  K, ldx and ldq multiples of 8.
 SMC_API int smc_quant_rows_e4m3(const void* x, int ldx, void* q, int ldq, float* scale, int M, int K, int pdl,
                                 cudaStream_t st) {

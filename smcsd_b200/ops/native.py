@@ -53,8 +53,10 @@ def _declare(L) -> None:
     L.smc_rope_kv_write.argtypes = [vp, i, ll, vp, vp, vp, i, i, vp, vp, vp, i, i, i, i, i, vp, i, vp]
     L.smc_swiglu_partials.argtypes = [vp, i, ll, vp, i, i, i, i, i, vp]
     L.smc_attention_fused_ex.argtypes = [vp, vp, i, i, i, i, i, vp, vp, vp, i, i, vp, vp, f, i, vp, vp, i, vp, i, vp, vp,
-                                         vp, i, i, i, i, i, i, f, vp, i, vp, vp, vp, i, ll, i, vp]
+                                         vp, i, i, i, i, i, i, f, vp, i, vp, vp, vp, i, ll, i, i, vp]
     L.smc_attention_fused_ex.restype = C.c_int
+    L.smc_kv_store_e4m3.argtypes = [vp, vp, i, vp, vp, vp, i, i, i, i, vp, i, vp]
+    L.smc_kv_store_e4m3.restype = C.c_int
     L.smc_sample_scratch_bytes.argtypes = [i, i]
     L.smc_sample_or_score.argtypes = [vp, i, ll, ll, i, i, f, f, f, vp, ull, vp, i, vp, i, vp, vp, vp, i, vp]
     L.smc_slot_arrays_size.argtypes = []
@@ -215,10 +217,37 @@ def add_rmsnorm_q8(h: torch.Tensor, w: torch.Tensor, xn: torch.Tensor, q8: torch
                                 _p(q8), q8.stride(0), _p(qscale), int(pdl), _stream()), "smc_add_rmsnorm_q8")
 
 
+def kv_row_bytes_e4m3(Hkv: int, D: int) -> int:
+    """Bytes of one page row of the e4m3 KV cache: Hkv * D value bytes, one fp32 scale per kv head, padded to 16."""
+    return (Hkv * D + Hkv * 4 + 15) // 16 * 16
+
+
+_KV8_TMP = {}
+
+
 def rope_kv_write(partials: torch.Tensor, splits: int, split_stride: int, positions: torch.Tensor,
                   cache_locs: torch.Tensor, rope: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Tensor,
                   v_pool: torch.Tensor, *, M: int, Hq: int, Hkv: int, D: int, status: torch.Tensor,
                   pdl: bool = False) -> None:
+    """Rotary + bf16 rounding of the new tokens; q rows to ``q_out``, K/V rows to their cache pages.  With an e4m3
+    cache (uint8 pools) the rotated K/V rows pass through a bf16 staging buffer and a quantising store kernel."""
+    if k_pool.dtype == torch.uint8:
+        key = (k_pool.device, Hkv * D)
+        tmp = _KV8_TMP.get(key)
+        if tmp is None or tmp[0].shape[0] < M + 1:
+            n = max(M + 1, 4096)
+            tmp = (torch.zeros(n, Hkv * D, dtype=torch.bfloat16, device=k_pool.device),
+                   torch.zeros(n, Hkv * D, dtype=torch.bfloat16, device=k_pool.device),
+                   torch.arange(n, dtype=torch.int32, device=k_pool.device))
+            _KV8_TMP[key] = tmp
+        tk, tv, iota = tmp
+        _check(lib().smc_rope_kv_write(_p(partials), splits, split_stride, _p(positions), _p(iota), _p(rope),
+                                       rope.shape[1], rope.shape[0], _p(q_out), _p(tk), _p(tv), tk.shape[0] - 1, M, Hq,
+                                       Hkv, D, _p(status), int(pdl), _stream()), "smc_rope_kv_write")
+        _check(lib().smc_kv_store_e4m3(_p(tk), _p(tv), M, _p(cache_locs), _p(k_pool), _p(v_pool), k_pool.shape[0] - 1,
+                                       Hkv, D, kv_row_bytes_e4m3(Hkv, D), _p(status), int(pdl), _stream()),
+               "smc_kv_store_e4m3")
+        return
     _check(lib().smc_rope_kv_write(_p(partials), splits, split_stride, _p(positions), _p(cache_locs), _p(rope),
                                    rope.shape[1], rope.shape[0], _p(q_out), _p(k_pool), _p(v_pool),
                                    k_pool.shape[0] - 1, M, Hq, Hkv, D, _p(status), int(pdl), _stream()),
@@ -266,6 +295,8 @@ def attention_fused(qkv: torch.Tensor, positions: torch.Tensor, cache_locs: torc
                     part_in: Optional[torch.Tensor] = None, causal: bool = True, part_in_n: int = 1,
                     part_in_stride: int = 0) -> None:
     """Norm/rope/KV-write of the new tokens + paged causal attention + split merge, one launch per layer.
+    K/V pools of dtype uint8 hold the e4m3 cache layout (``kv_row_bytes_e4m3``): tiles are dequantised after they
+    land, new rows are quantised on their way to the pages.
     Shared-prefix passes: ``causal=False`` with ``q_in`` and ``part_out`` serves the rows of several sequences from
     one stream of their common keys and parks the unnormalised state; ``key_begin`` / ``part_in`` make the
     per-sequence launch start after those keys and fold the state in.  (``part_acc`` / ``part_ml`` are ignored.)"""
@@ -277,7 +308,8 @@ def attention_fused(qkv: torch.Tensor, positions: torch.Tensor, cache_locs: torc
                                         _p(block_table), block_table.stride(0), _p(rows), _p(prefix_lens), _p(out),
                                         bs, E, Hq, Hkv, D, KS, scale, _p(status), int(pdl), _p(key_begin),
                                         _p(part_out), _p(part_in), part_in_n if part_in is not None else 0,
-                                        part_in_stride, int(causal), _stream()), "smc_attention_fused")
+                                        part_in_stride, int(causal), int(k_pool.dtype == torch.uint8), _stream()),
+           "smc_attention_fused")
 
 
 def attention_tc_splits(n_seq: int, Hkv: int, keys: int, rows: int = 128) -> int:

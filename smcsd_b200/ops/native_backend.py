@@ -189,7 +189,7 @@ class NativeLlama:
         verify_env = os.environ.get("SMC_CASCADE_VERIFY", "")
         for E in Es:
             tc = self.D in (64, 128) and n_particles in self.cascade_bufs["rows_g"] and \
-                (self.attn_tc >= 2 or (self.attn_tc == 1 and E > 2))
+                (self.attn_tc >= 2 or (self.attn_tc == 1 and E > 2)) and self.kv.k.dtype != torch.uint8
             if E > 2:
                 on = tc and min_prompt >= max(thr, self.CASCADE_MIN_PROMPT_VERIFY) if verify_env == "" else verify_env == "1"
                 if not on:
@@ -530,7 +530,7 @@ class NativeRunner:
         if _env_flag("SMC_PERSISTENT", False):
             from .native_forward import PersistentLlama, supported
             for name, nm in (("pf_target", self.target), ("pf_draft", self.draft)):
-                if isinstance(nm, NativeLlama) and nm.fold and supported(nm.m, 1):
+                if isinstance(nm, NativeLlama) and nm.fold and supported(nm.m, 1) and nm.kv.k.dtype != torch.uint8:
                     setattr(self, name, PersistentLlama(nm.m, nm.kv, nm.bt, 128, self.status))
 
     def _wrap(self, model, kv, bt, max_tokens, max_logit_rows, splits, pdl, state=None):

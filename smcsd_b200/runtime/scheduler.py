@@ -126,8 +126,12 @@ class SMCScheduler:
         self.max_groups = a.max_running_requests
         n_slots = self.max_groups * N
         n_parent_rows = max(self.max_groups, 4)
-        kv_t = KVSpec(len(self.target.cfg.attn_layers), self.target.n_kv_heads, self.target.cfg.head_dim, self.dtype)
-        kv_d = KVSpec(len(self.draft.cfg.attn_layers), self.draft.n_kv_heads, self.draft.cfg.head_dim, self.dtype)
+        kv8 = a.kv_cache_dtype == "fp8_e4m3"
+        if kv8 and (tp_size > 1 or pp_size > 1 or any(m.cfg.arch != "llama" for m in (self.target, self.draft))):
+            # the e4m3 cache is read by the fused attention step of the dense chain (and by the PyTorch oracle)
+            raise ValueError("kv_cache_dtype='fp8_e4m3' needs dense models, tp_size=1 and no particle parallelism")
+        kv_t = KVSpec(len(self.target.cfg.attn_layers), self.target.n_kv_heads, self.target.cfg.head_dim, self.dtype, kv8)
+        kv_d = KVSpec(len(self.draft.cfg.attn_layers), self.draft.n_kv_heads, self.draft.cfg.head_dim, self.dtype, kv8)
         n_rows = n_slots + n_parent_rows
         spec_t, spec_d = self.target.state_spec(), self.draft.state_spec()
         state_bytes = sum(s.row_bytes * n_rows for s in (spec_t, spec_d) if s)

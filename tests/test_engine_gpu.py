@@ -405,3 +405,31 @@ def test_capture_warm_up_restores_token_histories_and_group_flags():
         outs[graph] = [x["smc_particle_output_ids"] for x in o]
         assert e._sched.native_runner.check_status() == 0
     assert outs[False] == outs[True]
+
+
+def test_e4m3_kv_cache_engine():
+    """kv_cache_dtype='fp8_e4m3': both KV pools hold e4m3 rows with per-(token, head) scales.  Prompt pass (rope kernel +
+    quantising store), draft steps and verify passes all read and write that layout; graph replays equal the eager
+    launches, and with draft == target the importance weights stay small (both see the same quantised history)."""
+    from smcsd_b200.config import EngineArgs
+    from smcsd_b200.io_types import GenerateRequest, ParticleOutput, SamplingParams
+    from smcsd_b200.models import build_model
+    from smcsd_b200.runtime.scheduler import SMCScheduler
+    tgt, _ = _cfgs()
+    model = build_model(tgt, torch.bfloat16, "cuda", seed=0)
+    outs = {}
+    for graph in (False, True):
+        args = EngineArgs(model_path=tgt, draft_model_path=tgt, n_particles=4, gamma=4, draft_temperature=0.7,
+                          target_temperature=0.7, max_running_requests=2, context_length=512, device="cuda",
+                          max_total_tokens=8192, backend="native", resample_threshold=0.5, cycle_graph=graph,
+                          kv_cache_dtype="fp8_e4m3").finalize()
+        sched = SMCScheduler(args, target=model, draft=model)
+        assert sched.kv_t.k.dtype == torch.uint8 and sched.kv_t.spec.cell_bytes < 0.6 * 2 * 3 * 2 * 128 * 2
+        sched.add_request(GenerateRequest("r", _prompts(1, L=70)[0], SamplingParams(max_new_tokens=40, ignore_eos=True)))
+        o = sched.run_until_idle()
+        po = [x for x in o if isinstance(x, ParticleOutput)][0]
+        assert max(abs(w) for w in po.log_w_tilde) < 0.5, po.log_w_tilde
+        assert sched.native_runner.check_status() == 0
+        sched.check_idle_invariants()
+        outs[graph] = po.particle_output_ids
+    assert outs[False] == outs[True]

@@ -410,6 +410,80 @@ def test_attention_fused(bs, E, Hq, Hkv, D, ctx, KS, rd, extras):
     assert err < 3e-2 * max(1.0, ref.abs().max().item()), err
 
 
+@pytest.mark.parametrize("bs,E,Hq,Hkv,D,ctx,KS,two_pass", [
+    (8, 9, 32, 8, 128, 1500, 1, False), (8, 1, 32, 8, 64, 700, 1, False), (5, 2, 32, 8, 64, 300, 2, False),
+    (4, 9, 32, 8, 128, 2500, 4, False), (3, 9, 8, 2, 128, 200, 1, True), (2, 5, 4, 2, 64, 0, 1, False),
+    (4, 9, 16, 2, 256, 260, 1, False), (6, 16, 32, 8, 128, 180, 1, True),
+])
+def test_attention_fused_e4m3_kv_cache(bs, E, Hq, Hkv, D, ctx, KS, two_pass):
+    """The e4m3 KV cache (value bytes + one scale per token and kv head in every page row): cached tiles are expanded
+    to bf16 after they land, new rows are quantised on their way to the pages (inside the attention step, or by the
+    store kernel behind the rope kernel for prompt passes).  Oracle: PyTorch attention over the dequantised pages."""
+    K = _K()
+    from smcsd_b200.memory.pools import kv_rows_from_float, kv_rows_to_float
+    from smcsd_b200.models.layers import ExtendBatch, apply_rope, paged_attention_reference, rope_table
+    torch.manual_seed(19)
+    dev = "cuda"
+    T = bs * E
+    pages = bs * (ctx + E) + 64
+    rw = K.kv_row_bytes_e4m3(Hkv, D)
+    kp = kv_rows_from_float(torch.randn(pages + 1, Hkv, D, device=dev), rw)
+    vp = kv_rows_from_float(torch.randn(pages + 1, Hkv, D, device=dev), rw)
+    kp[0].zero_(); vp[0].zero_()
+    max_ctx = ctx + E + 8
+    bt = torch.zeros(bs + 2, max_ctx, device=dev, dtype=torch.int32)
+    perm = (torch.randperm(pages, device=dev) + 1).to(torch.int32)
+    prefix = torch.tensor([max(0, ctx - 17 * i) for i in range(bs)], device=dev, dtype=torch.int32)
+    rows = torch.arange(bs, device=dev, dtype=torch.int32) + 1
+    locs = torch.zeros(T, device=dev, dtype=torch.int32)
+    pos = torch.zeros(T, device=dev, dtype=torch.int32)
+    off = 0
+    for b in range(bs):
+        P = int(prefix[b])
+        L = P + E
+        bt[b + 1, :L] = perm[off:off + L]
+        locs[b * E:(b + 1) * E] = perm[off + P:off + L]
+        pos[b * E:(b + 1) * E] = torch.arange(P, L, device=dev)
+        off += L
+    nq, nk = Hq * D, Hkv * D
+    qkv = torch.randn(T, nq + 2 * nk, device=dev)
+    table = rope_table(D, 10000.0, None, max_ctx + 8, dev)
+    qr = apply_rope(qkv[:, :nq].view(T, Hq, D), pos, table).bfloat16()
+    kr = apply_rope(qkv[:, nq:nq + nk].view(T, Hkv, D), pos, table).bfloat16()
+    vr = qkv[:, nq + nk:].view(T, Hkv, D).bfloat16()
+    kp_ref, vp_ref = kp.clone(), vp.clone()
+    kp_ref[locs.long()] = kv_rows_from_float(kr, rw)
+    vp_ref[locs.long()] = kv_rows_from_float(vr, rw)
+    batch = ExtendBatch(None, None, None, rows, prefix, extend_len=E)
+    ref = paged_attention_reference(qr, kp_ref, vp_ref, bt, batch, Hkv).float().reshape(T, -1)
+    out = torch.zeros(T, nq, device=dev, dtype=torch.bfloat16)
+    st = _status()
+    if two_pass:
+        q_rot = torch.zeros(T, nq, device=dev, dtype=torch.bfloat16)
+        K.rope_kv_write(qkv, 1, 0, pos, locs, table, q_rot, kp, vp, M=T, Hq=Hq, Hkv=Hkv, D=D, status=st)
+        K.attention_fused(qkv, pos, locs, table, kp, vp, bt, rows, prefix, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D, KS=KS,
+                          scale=D ** -0.5, status=st, q_in=q_rot)
+    else:
+        K.attention_fused(qkv, pos, locs, table, kp, vp, bt, rows, prefix, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D, KS=KS,
+                          scale=D ** -0.5, status=st)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    # the rows written by the kernels dequantise to (nearly) the same values as the PyTorch quantiser's
+    got_k = kv_rows_to_float(kp[locs.long()], Hkv, D)
+    want_k = kv_rows_to_float(kp_ref[locs.long()], Hkv, D)
+    assert (got_k - want_k).abs().max().item() < 0.07 * want_k.abs().max().item()
+    got_v = kv_rows_to_float(vp[locs.long()], Hkv, D)
+    want_v = kv_rows_to_float(vp_ref[locs.long()], Hkv, D)
+    assert (got_v - want_v).abs().max().item() < 0.07 * want_v.abs().max().item()
+    untouched = torch.ones(pages + 1, dtype=torch.bool, device=dev)
+    untouched[locs.long()] = False
+    assert torch.equal(kp[untouched], kp_ref[untouched]) and torch.equal(vp[untouched], vp_ref[untouched])
+    err = (out.float() - ref).abs().max().item()
+    # in the single-launch form the step attends its own new tokens in bf16 (before quantisation); the oracle reads
+    # them back from the e4m3 pages
+    assert err < 6e-2 * max(1.0, ref.abs().max().item()), err
+
+
 @pytest.mark.parametrize("groups,N,NP,E,Hq,Hkv,D,P,suffix,KSg,KSs", [
     (1, 8, 8, 1, 32, 8, 64, 1500, 300, 4, 2), (1, 8, 2, 9, 32, 8, 128, 2100, 200, 4, 1), (2, 4, 4, 2, 8, 2, 64, 700, 40, 2, 1),
     (1, 8, 8, 1, 32, 8, 64, 100, 1200, 1, 4), (1, 4, 2, 5, 8, 2, 128, 333, 0, 1, 1),
