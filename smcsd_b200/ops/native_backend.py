@@ -474,6 +474,7 @@ class NativeRunner:
         self.ns = nstate
         self.comm = comm
         self.heap = None
+        self.sched_models = (sched.target, sched.draft)
         self.device = sched.device
         self.gamma, self.G = a.gamma, a.gamma + 1
         self.max_bs = sched.max_groups * a.n_particles
@@ -545,9 +546,14 @@ class NativeRunner:
             if self.comm is None:
                 raise RuntimeError("a tensor-parallel model needs a process group (launch one rank per GPU)")
             if self.heap is None:
-                pf = self.PREFILL_MAX_TOKENS_TP            # a second, prompt-sized chain shares the heap
-                need = 4 * (max_tokens + pf) * model.cfg.hidden_size * 8 + \
-                    (max_tokens + pf) * 32 * 32 * model.tp_size + (8 << 20)
+                # one heap for every tensor-parallel chain of this rank: decode and prompt-sized chains of the target
+                # and, with replicate_draft=False, of the draft
+                pf = self.PREFILL_MAX_TOKENS_TP
+                cap = self.max_bs * self.G
+                need = 8 << 20
+                for mdl in self.sched_models:
+                    if mdl.tp_size > 1 and mdl.cfg.arch == "llama":
+                        need += 4 * (cap + pf) * mdl.cfg.hidden_size * 8 + (cap + pf) * 32 * 32 * mdl.tp_size + (1 << 20)
                 self.heap = SymmHeap(need, self.device, self.comm.device_group, self.comm.group_rank,
                                      self.comm.group_size)
             model.tp_group = self.comm.device_group      # the PyTorch prefill path all-reduces through NCCL

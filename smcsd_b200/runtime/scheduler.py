@@ -94,9 +94,8 @@ class SMCScheduler:
             if a.backend == "native":
                 raise ValueError("tensor-parallel hybrid models run with backend='torch' (or 'auto')")
             backend = self.backend = "torch"
-        if tp_size > 1 and not a.replicate_draft and backend == "native":
-            raise ValueError("replicate_draft=False (a tensor-parallel draft) is only available with backend='torch': "
-                             "the kernel path keeps a full draft replica on every rank")
+        # replicate_draft=False shards the draft over the tensor-parallel ranks like the target (fused all-gather /
+        # reduce-scatter chain and vocab-parallel sampling on the kernel path, NCCL all-reduce on the PyTorch path)
         d_tp = (0, 1) if a.replicate_draft else (tp_rank, tp_size)
         if draft is None and tp_size == 1 and a.draft_model_path == a.model_path:
             draft = self.target           # the target as its own proposal (vanilla arm): one set of weights, two KV pools
