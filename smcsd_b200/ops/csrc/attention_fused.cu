@@ -12,6 +12,8 @@
 // buffered), scores and P*V run on tensor cores (mma.sync m16n8k16, bf16 in / fp32 out) with
 // flash-style running max / sum in registers.  The new tokens form a last, causally masked tile
 // served from shared memory.
+#include <stdlib.h>
+
 #include <cuda_fp8.h>
 
 #include "attn_core.cuh"
@@ -561,6 +563,14 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   if (p.KS > 1) cluster_sync();
 }
 
+// Shared memory one CTA of a single-wave grid may take (SMC_ATTN_SMEM_KB overrides): large rings keep more K/V bytes
+// in flight, small CTAs can share an SM with the CTAs of the neighbouring GEMM launches.
+static int attn_smem_cap() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("SMC_ATTN_SMEM_KB"); v = (e != nullptr ? atoi(e) : 200) * 1024; }
+  return v;
+}
+
 static size_t fused_smem_bytes(int D, int n_mt, int n_kw, int stg) {
   const size_t LD = D + 8;
   size_t b = ((size_t)n_mt * 16 + 32) * LD * 2 + RANGE * 4;
@@ -583,7 +593,7 @@ static int pick_head_groups(int E, int G, long long ctas) {
 static int pick_key_ways(int D, int n_mt, long long ctas) {
   int n_kw = 8 / n_mt;
   if (n_kw < 1) n_kw = 1;
-  while (n_kw > 1 && fused_smem_bytes(D, n_mt, n_kw, 2) > 200 * 1024) --n_kw;
+  while (n_kw > 1 && fused_smem_bytes(D, n_mt, n_kw, 2) > (size_t)attn_smem_cap()) --n_kw;
   if (ctas > 2 * 148 && n_kw > 4) n_kw = 4;     // measured at 1024 CTAs: 4 key-ways 45 us, 8: 67 us, 2: 57 us
   return n_kw;
 }
@@ -666,7 +676,7 @@ SMC_API int smc_attention_fused_ex(const float* qkv, const void* q_in, int ld_qk
   int n_kw = pick_key_ways(D, n_mt, (long long)bs * Hkv * KS * gsub);
   // Ring depth: a grid that fits the GPU in one wave with one CTA per SM spends the whole shared memory on tiles
   // in flight; larger grids stay under half of it so two CTAs share an SM.
-  const size_t budget = (size_t)bs * Hkv * KS * gsub <= 148 ? 200 * 1024 : 100 * 1024;
+  const size_t budget = (size_t)bs * Hkv * KS * gsub <= 148 ? (size_t)attn_smem_cap() : 100 * 1024;
   int stg = 2;
   while (stg < 6 && fused_smem_bytes(D, n_mt, n_kw, stg + 1) <= budget) ++stg;
   FusedAttnParams p;

@@ -12,10 +12,13 @@
 namespace smc {
 
 // proj: fp32 [T, ldp] = mixed (conv_dim) | z (value_dim) | b (Hv) | a (Hv).
+// WT: the conv width as a compile-time constant (window arrays stay in registers); 0 takes it from the argument.
+template <int WT>
 __global__ void gdn_conv_kernel(const float* __restrict__ proj, int ldp, float* __restrict__ conv_state,
                                 const int* __restrict__ state_rows, const __nv_bfloat16* __restrict__ conv_w,
-                                float* __restrict__ conv_out, int bs, int E, int conv_dim, int W,
+                                float* __restrict__ conv_out, int bs, int E, int conv_dim, int W_rt,
                                 const int* __restrict__ tok_off, const int* __restrict__ tok_len, int pdl) {
+  const int W = WT ? WT : W_rt;
   if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= bs * conv_dim) return;
@@ -43,10 +46,13 @@ __global__ void gdn_conv_kernel(const float* __restrict__ proj, int ldp, float* 
 // of a row's first tile is the only one that touches the row's window in the state pool: it reads the old window and
 // writes the new one (the row's last W-1 inputs).
 constexpr int CONV_TILE = 16;
+// WT: the conv width as a compile-time constant (window arrays stay in registers); 0 takes it from the argument.
+template <int WT>
 __global__ void gdn_conv_prefill_kernel(const float* __restrict__ proj, int ldp, float* __restrict__ conv_state,
                                         const int* __restrict__ state_rows, const __nv_bfloat16* __restrict__ conv_w,
-                                        float* __restrict__ conv_out, int conv_dim, int W,
+                                        float* __restrict__ conv_out, int conv_dim, int W_rt,
                                         const int* __restrict__ tok_off, const int* __restrict__ tok_len, int pdl) {
+  const int W = WT ? WT : W_rt;
   if (pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   const int ch = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.z;
   const int len = tok_len[b], e0 = blockIdx.y * CONV_TILE;
@@ -75,13 +81,12 @@ __global__ void gdn_conv_prefill_kernel(const float* __restrict__ proj, int ldp,
   for (int u = 0; u < CONV_TILE; ++u) xin[u] = e0 + u < len ? proj[(t0 + e0 + u) * ldp + ch] : 0.f;
 #pragma unroll
   for (int u = 0; u < CONV_TILE; ++u) {
-    if (e0 + u >= len) break;
     const float x = xin[u];
     float acc = w[W - 1] * x;
     for (int i = 0; i < W - 1; ++i) acc += w[i] * hist[i];
     for (int i = 0; i + 1 < W - 1; ++i) hist[i] = hist[i + 1];
     hist[W - 2] = x;
-    conv_out[(t0 + e0 + u) * conv_dim + ch] = acc / (1.f + __expf(-acc));
+    if (e0 + u < len) conv_out[(t0 + e0 + u) * conv_dim + ch] = acc / (1.f + __expf(-acc));
   }
 }
 
@@ -200,14 +205,22 @@ SMC_API int smc_gdn_conv(const float* proj, int ldp, float* conv_state, const in
     // long rows: token-parallel form
     cfg.gridDim = dim3((conv_dim + 255) / 256, (max_len + CONV_TILE - 1) / CONV_TILE, bs);
     cfg.blockDim = dim3(256);
-    CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_conv_prefill_kernel, proj, ldp, conv_state, state_rows,
-                                      (const __nv_bfloat16*)conv_w, conv_out, conv_dim, W, tok_off, tok_len, pdl));
+    if (W == 4)
+      CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_conv_prefill_kernel<4>, proj, ldp, conv_state, state_rows,
+                                        (const __nv_bfloat16*)conv_w, conv_out, conv_dim, W, tok_off, tok_len, pdl));
+    else
+      CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_conv_prefill_kernel<0>, proj, ldp, conv_state, state_rows,
+                                        (const __nv_bfloat16*)conv_w, conv_out, conv_dim, W, tok_off, tok_len, pdl));
     return 0;
   }
   cfg.gridDim = dim3((bs * conv_dim + 255) / 256);
   cfg.blockDim = dim3(256);
-  CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_conv_kernel, proj, ldp, conv_state, state_rows,
-                                    (const __nv_bfloat16*)conv_w, conv_out, bs, E, conv_dim, W, tok_off, tok_len, pdl));
+  if (W == 4)
+    CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_conv_kernel<4>, proj, ldp, conv_state, state_rows,
+                                      (const __nv_bfloat16*)conv_w, conv_out, bs, E, conv_dim, W, tok_off, tok_len, pdl));
+  else
+    CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, gdn_conv_kernel<0>, proj, ldp, conv_state, state_rows,
+                                      (const __nv_bfloat16*)conv_w, conv_out, bs, E, conv_dim, W, tok_off, tok_len, pdl));
   return 0;
 }
 

@@ -197,6 +197,15 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_kernel(const GdnChunkParams 
     if (tid >= 32 && tid < GC) S.gc[tid] += S.gc[31];
     __syncthreads();
     const float gl = S.gc[GC - 1];
+    {
+      // the output phase reads this chunk's gate rows z (512 bytes per token and head): start them towards L2 now
+      const int jz = tid >> 1;
+      if (jz < n) {
+        const float* zr = p.proj + (tc0 + jz) * p.ldp + p.conv_dim + vh * GD + (tid & 1) * 64;
+        prefetch_l2(zr);
+        prefetch_l2(zr + 32);
+      }
+    }
     if (ch + 1 < n_chunks) {
       // pull the next chunk's q / k / v rows and gate values towards L2 while this chunk computes
       const int jn = tid >> 1, hfn = tid & 1;
@@ -309,31 +318,80 @@ __global__ void __launch_bounds__(128, 1) gdn_chunk_kernel(const GdnChunkParams 
     tc_fence_before();
     __syncthreads();
     lap(2);
-    if (tid < 64) {
-      // ---- Tm = (I + L)^-1: thread j solves (I + L) x = e_j; four partial sums shorten the dependent chain ----------
+    {
+      // ---- Tm = (I + L)^-1, in 32 x 32 blocks: [[A, 0], [C, B]]^-1 = [[A^-1, 0], [-B^-1 C A^-1, B^-1]] --------------
+      // (1) threads 0..63 solve the two diagonal blocks by forward substitution, one column per thread (fp32, exact);
+      // (2) all threads form M = C A^-1, (3) X21 = -B^-1 M; (4) Tm is written as bf16 rows.  Xf (fp32 [64][64]) lives
+      // in the k_cum tile, which is not live yet; M is parked in its unused upper-right quadrant.
       const float* Lf = reinterpret_cast<const float*>(sm + G_VNT);
-      const int j = tid;
-      float x[GC];
+      float* Xf = reinterpret_cast<float*>(sm + G_KC);
+      constexpr int HB = GC / 2;
+      if (tid < GC) {
+        const int blk = tid >> 5, j = tid & 31, o = blk * HB;      // column j of diagonal block blk
+        float x[HB];
 #pragma unroll
-      for (int i = 0; i < GC; ++i) {
-        float a0 = (i == j) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        const float* Li = Lf + i * GC;
+        for (int i = 0; i < HB; ++i) {
+          float a0 = (i == j) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+          const float* Li = Lf + (o + i) * GC + o;
 #pragma unroll
-        for (int k = 0; k + 3 < i; k += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(Li + k);
-          a0 = fmaf(-l4.x, x[k], a0);
-          a1 = fmaf(-l4.y, x[k + 1], a1);
-          a2 = fmaf(-l4.z, x[k + 2], a2);
-          a3 = fmaf(-l4.w, x[k + 3], a3);
+          for (int k = 0; k + 3 < i; k += 4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(Li + k);
+            a0 = fmaf(-l4.x, x[k], a0);
+            a1 = fmaf(-l4.y, x[k + 1], a1);
+            a2 = fmaf(-l4.z, x[k + 2], a2);
+            a3 = fmaf(-l4.w, x[k + 3], a3);
+          }
+#pragma unroll
+          for (int k = i & ~3; k < i; ++k) a0 = fmaf(-Li[k], x[k], a0);
+          x[i] = (a0 + a1) + (a2 + a3);
         }
 #pragma unroll
-        for (int k = i & ~3; k < i; ++k) a0 = fmaf(-Li[k], x[k], a0);
-        x[i] = (a0 + a1) + (a2 + a3);
+        for (int i = 0; i < HB; ++i) Xf[(o + i) * GC + o + j] = x[i];
       }
-      __syncwarp();
+      __syncthreads();
+      const int r = tid >> 2, c0 = (tid & 3) * 8;                  // every thread: row r, 8 columns of a 32 x 32 product
+      {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const float* Cr = Lf + (HB + r) * GC;                      // row r of C = L[32.., 0..32)
+#pragma unroll 8
+        for (int k = 0; k < HB; ++k) {
+          const float c = Cr[k];
+          const float4 a0 = *reinterpret_cast<const float4*>(Xf + k * GC + c0);
+          const float4 a1 = *reinterpret_cast<const float4*>(Xf + k * GC + c0 + 4);
+          acc[0] = fmaf(c, a0.x, acc[0]); acc[1] = fmaf(c, a0.y, acc[1]); acc[2] = fmaf(c, a0.z, acc[2]);
+          acc[3] = fmaf(c, a0.w, acc[3]); acc[4] = fmaf(c, a1.x, acc[4]); acc[5] = fmaf(c, a1.y, acc[5]);
+          acc[6] = fmaf(c, a1.z, acc[6]); acc[7] = fmaf(c, a1.w, acc[7]);
+        }
 #pragma unroll
-      for (int i = 0; i < GC; ++i)
-        *reinterpret_cast<__nv_bfloat16*>(sm + G_TM + sw_off(64, i, j)) = __float2bfloat16(x[i]);
+        for (int u = 0; u < 8; ++u) Xf[r * GC + HB + c0 + u] = acc[u];          // M[r][c0 + u], parked upper right
+      }
+      __syncthreads();
+      {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const float* Br = Xf + (HB + r) * GC + HB;                 // row r of B^-1 (lower triangular)
+#pragma unroll 8
+        for (int k = 0; k < HB; ++k) {
+          const float bv = Br[k];
+          const float4 m0 = *reinterpret_cast<const float4*>(Xf + k * GC + HB + c0);
+          const float4 m1 = *reinterpret_cast<const float4*>(Xf + k * GC + HB + c0 + 4);
+          acc[0] = fmaf(bv, m0.x, acc[0]); acc[1] = fmaf(bv, m0.y, acc[1]); acc[2] = fmaf(bv, m0.z, acc[2]);
+          acc[3] = fmaf(bv, m0.w, acc[3]); acc[4] = fmaf(bv, m1.x, acc[4]); acc[5] = fmaf(bv, m1.y, acc[5]);
+          acc[6] = fmaf(bv, m1.z, acc[6]); acc[7] = fmaf(bv, m1.w, acc[7]);
+        }
+        __syncthreads();                                           // every read of M is done before it is overwritten
+#pragma unroll
+        for (int u = 0; u < 8; ++u) Xf[(HB + r) * GC + c0 + u] = -acc[u];       // X21
+      }
+      __syncthreads();
+      {
+        // Tm rows as bf16: thread (row i, half h) stores 32 columns; the upper-right quadrant is zero
+        const int i = tid >> 1, h = tid & 1;
+        float f[32];
+#pragma unroll
+        for (int u = 0; u < 32; ++u) f[u] = (i < HB && h == 1) ? 0.f : Xf[i * GC + h * 32 + u];
+#pragma unroll
+        for (int u = 0; u < 32; u += 8) store8(sm + G_TM, 64, i, h * 32 + u, f + u, 1.f);
+      }
     }
     fence_proxy_async();
     __syncthreads();
