@@ -11,8 +11,8 @@
 // The exponent reference m_ref of a row only moves when the row's maximum has grown by more than 2^8 (P stays within
 // bf16 / fp32 range); only then is the row's O rescaled in tensor memory (tcgen05.ld / st), which after the first few
 // tiles is rare.  O is read back once, at the end.
-// K/V rows live one page per token.  A tile whose 64 pages are consecutive (what the allocator hands a prompt on a
-// fresh or lightly fragmented pool) is fetched with one TMA box per 64-column panel; a scattered tile is gathered by the
+// K/V rows live one page per token.  A tile whose 64 pages are consecutive, in ascending or descending order (what the
+// allocator hands a prompt on a fresh or lightly fragmented pool), is fetched with one TMA box per 64-column panel; a scattered tile is gathered by the
 // four loader warps with 16-byte cp.async copies into the same swizzled layout (a warp owns 16 keys and passes page
 // ids by shuffle).  Page ids are fetched four tiles ahead.  The pass has no causal limit
 // (every prompt key precedes every new token) and no new-token handling; it parks the unnormalised state
@@ -210,10 +210,14 @@ __global__ void __launch_bounds__((5 + TcCfg<D>::LOADERS) * 32, 1) attn_prefix_t
         const int pa = pg[u][0], pb = pg[u][1];
         pg[u][0] = page_of(j + PD, 0);
         pg[u][1] = page_of(j + PD, 1);
+        // 64 consecutive pages, ascending or descending (pages popped from a free stack come out either way; the pass
+        // has no causal limit, so the order of the keys inside a tile does not matter)
         const int base = __shfl_sync(0xffffffffu, pa, 0);
         const bool full_tile = kb + (j + 1) * TC_BK <= ke;
-        const bool run = p.use_tma && full_tile && base >= 1 &&
-                         __all_sync(0xffffffffu, pa == base + lane && pb == base + 32 + lane);
+        const bool asc = __all_sync(0xffffffffu, pa == base + lane && pb == base + 32 + lane);
+        const bool desc = __all_sync(0xffffffffu, pa == base - lane && pb == base - 32 - lane) && base >= TC_BK;
+        const bool run = p.use_tma && full_tile && base >= 1 && (asc || desc);
+        const int first_page = asc ? base : base - (TC_BK - 1);
         uint8_t* k_ptr = kv_s + (size_t)st * 2 * KV_BYTES;
         if (run) {
           // 64 consecutive pages: one TMA box per 64-column panel of K and of V; every warp owes the barrier one arrival
@@ -222,8 +226,8 @@ __global__ void __launch_bounds__((5 + TcCfg<D>::LOADERS) * 32, 1) attn_prefix_t
               mbar_expect_tx(&S.kv_full[st], 2 * KV_BYTES);
 #pragma unroll
               for (int pan = 0; pan < NPAN; ++pan) {
-                tma_load_2d(k_ptr + pan * PANEL_KV, &tmK, &S.kv_full[st], kvh * D + pan * 64, base, pol);
-                tma_load_2d(k_ptr + KV_BYTES + pan * PANEL_KV, &tmV, &S.kv_full[st], kvh * D + pan * 64, base, pol);
+                tma_load_2d(k_ptr + pan * PANEL_KV, &tmK, &S.kv_full[st], kvh * D + pan * 64, first_page, pol);
+                tma_load_2d(k_ptr + KV_BYTES + pan * PANEL_KV, &tmV, &S.kv_full[st], kvh * D + pan * 64, first_page, pol);
               }
             } else {
               mbar_arrive(&S.kv_full[st]);

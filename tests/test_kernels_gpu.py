@@ -493,8 +493,8 @@ def test_attention_shared_prefix_passes(groups, N, NP, E, Hq, Hkv, D, P, suffix,
     """Shared-prefix attention: one pass over the prompt keys for NP particles at a time (state parked per token and
     head), then the per-particle pass over the remaining keys folds it in.  Must equal plain causal attention.
     ``tc``: the group pass runs on the tcgen05 kernel (one parked state per key split) instead of the mma.sync one,
-    with every prompt page scattered (row gather) or with the prompt in consecutive pages except for one shuffled
-    stretch (TMA tiles and gathered tiles in the same launch)."""
+    with every prompt page scattered (row gather) or with the prompt in consecutive pages except for one reversed and
+    one shuffled stretch (ascending and descending TMA tiles and gathered tiles in the same launch)."""
     K = _K()
     from smcsd_b200.models.layers import ExtendBatch, paged_attention_reference
     torch.manual_seed(13)
@@ -516,7 +516,9 @@ def test_attention_shared_prefix_passes(groups, N, NP, E, Hq, Hkv, D, P, suffix,
     for gi in range(groups):
         pg = perm[off:off + P].clone()
         if tc == "runs" and P >= 192:
-            pg[128:192] = pg[128:192].flip(0)
+            pg[128:192] = pg[128:192].flip(0)                      # a descending run: still one TMA box
+        if tc == "runs" and P >= 320:
+            pg[256:320] = pg[256:320][torch.randperm(64, device=dev)]   # a scattered tile: gathered row by row
         shared.append(pg)
         off += P
     prefix = torch.zeros(bs, device=dev, dtype=torch.int32)
