@@ -102,6 +102,9 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   const int prefix = p.prefix_lens[b];
   const size_t kv_row = (size_t)p.Hkv * D;
   const bool pool_only = p.q_in != nullptr;
+  // A group pass without rotated queries (q_in == null, causal == 0) rotates its tokens' queries itself, but writes no
+  // K/V rows and skips the new-token tile: the per-sequence pass that follows does both.
+  const bool group_self = PFX && !pool_only && !pfx_causal;
   const int g = lane >> 2, t = lane & 3;
 
   // ---- key range of this CTA and the first K/V fetch (runs under the new-token work below) -----------
@@ -319,7 +322,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   }
   // new K/V rows go to their pages (one CTA per (sequence, kv head) writes them)
   if constexpr (KV8) {
-    if (ks == p.KS - 1 && !pool_only && blockIdx.z == 0) {
+    if (ks == p.KS - 1 && !pool_only && !group_self && blockIdx.z == 0) {
       // one warp per new K / V row: scale = max|x| / 448, e4m3 bytes and the scale go to the row's page
       uint8_t* kp = reinterpret_cast<uint8_t*>(p.k_pool);
       uint8_t* vp = reinterpret_cast<uint8_t*>(p.v_pool);
@@ -343,7 +346,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
       }
     }
   } else
-  if (ks == p.KS - 1 && !pool_only && blockIdx.z == 0) {
+  if (ks == p.KS - 1 && !pool_only && !group_self && blockIdx.z == 0) {
     constexpr int CPR = D / 8;
     for (int c = threadIdx.x; c < p.E * CPR * 2; c += blockDim.x) {
       const bool is_v = c >= p.E * CPR;
@@ -406,7 +409,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const FusedAttnParams p
   }
   cp_async_wait<0>();
   // ---- phase 3: the new tokens, causally masked (key-way 0 of the last split) ----------------------
-  if (ks == p.KS - 1 && kw == 0 && !pool_only) {
+  if (ks == p.KS - 1 && kw == 0 && !pool_only && !group_self) {
     process_tile<D, 2, Q_REGS>(Kn, Vn, qa, Qs_mt, p.scale, st, p.E, e_row0, e_row1);
   }
   st.l0 += __shfl_xor_sync(0xffffffffu, st.l0, 1);
@@ -667,7 +670,7 @@ SMC_API int smc_attention_fused_ex(const float* qkv, const void* q_in, int ld_qk
   if (bs <= 0) return 0;
   if (Hq % Hkv || E < 1 || (rd & 1) || rd > D) return -70;
   if (E > 16 && (q_in == nullptr || E * (Hq / Hkv) > 128)) return -70;
-  if (!causal && q_in == nullptr) return -74;
+  if (!causal && q_in == nullptr && (E > 16 || part_out == nullptr)) return -74;   // self-rotating group pass: <= 16 tokens
   if (!(KS == 1 || KS == 2 || KS == 4 || KS == 8)) return -73;
   const int gsub = part_out != nullptr ? 1 : pick_head_groups(E, Hq / Hkv, (long long)bs * Hkv);
   const int G = Hq / Hkv / gsub, R = E * G;

@@ -139,6 +139,16 @@ class NativeLlama:
                               status=self.status, pdl=pdl, q_in=q_in)
             return
         NP, cb = plan["NP"], self.cascade_bufs
+        if not plan["tc"] and NP * E <= 16 and k.dtype != torch.uint8:
+            # two launches: the group pass rotates its (at most 16) tokens' queries itself and writes nothing; the
+            # per-particle pass is the ordinary step (rope, KV write, new-token tile) started behind the shared keys
+            K.attention_fused(self.qkv, positions, cache_locs, m.rope, k, v, self.bt, cb["rows_g"][NP], cb["shared_g"][NP],
+                              None, bs=bs // NP, E=NP * E, Hq=self.nq, Hkv=self.nkv, D=self.D, KS=plan["KSg"],
+                              scale=scale, status=self.status, pdl=pdl, part_out=self.att_state, causal=False)
+            K.attention_fused(self.qkv, positions, cache_locs, m.rope, k, v, self.bt, rows, prefix_lens, self.attn, bs=bs,
+                              E=E, Hq=self.nq, Hkv=self.nkv, D=self.D, KS=plan["KSs"], scale=scale, status=self.status,
+                              pdl=pdl, key_begin=cb["shared"], part_in=self.att_state)
+            return
         K.rope_kv_write(self.qkv, 1, 0, positions, cache_locs, m.rope, self.q, k, v, M=T, Hq=self.nq, Hkv=self.nkv,
                         D=self.D, status=self.status, pdl=pdl)
         if plan["tc"]:

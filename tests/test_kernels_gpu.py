@@ -484,6 +484,66 @@ def test_attention_fused_e4m3_kv_cache(bs, E, Hq, Hkv, D, ctx, KS, two_pass):
     assert err < 6e-2 * max(1.0, ref.abs().max().item()), err
 
 
+@pytest.mark.parametrize("N,E,Hq,Hkv,D,P,suffix,KSg,KSs", [(8, 1, 32, 8, 64, 1500, 300, 4, 2), (8, 2, 32, 8, 64, 900, 70, 2, 1),
+                                                         (4, 2, 8, 2, 128, 333, 5, 1, 1)])
+def test_attention_shared_prefix_two_launches(N, E, Hq, Hkv, D, P, suffix, KSg, KSs):
+    """Draft-step form of the shared-prefix passes: the group pass takes the fp32 projections, rotates the (at most 16)
+    tokens' queries itself and writes nothing; the per-particle pass is the ordinary step (rope, KV write, new-token
+    tile) started behind the shared keys.  Must equal the single launch and the PyTorch oracle."""
+    K = _K()
+    from smcsd_b200.models.layers import ExtendBatch, apply_rope, paged_attention_reference, rope_table
+    torch.manual_seed(23)
+    dev = "cuda"
+    bs, T = N, N * E
+    pages = P + bs * (suffix + E) + 64
+    kp = torch.randn(pages + 1, Hkv * D, device=dev).bfloat16()
+    vp = torch.randn(pages + 1, Hkv * D, device=dev).bfloat16()
+    perm = (torch.randperm(pages, device=dev) + 1).to(torch.int32)
+    bt = torch.zeros(bs + 2, P + suffix + E + 8, device=dev, dtype=torch.int32)
+    prefix = torch.zeros(bs, device=dev, dtype=torch.int32)
+    locs = torch.zeros(T, device=dev, dtype=torch.int32)
+    pos = torch.zeros(T, device=dev, dtype=torch.int32)
+    off = P
+    for b in range(bs):
+        own = max(suffix - (b % 3), 0)
+        bt[b + 1, :P] = perm[:P]
+        bt[b + 1, P:P + own + E] = perm[off:off + own + E]
+        locs[b * E:(b + 1) * E] = perm[off + own:off + own + E]
+        pos[b * E:(b + 1) * E] = torch.arange(P + own, P + own + E, device=dev)
+        off += own + E
+        prefix[b] = P + own
+    rows = torch.arange(bs, device=dev, dtype=torch.int32) + 1
+    nq, nk = Hq * D, Hkv * D
+    qkv = torch.randn(T, nq + 2 * nk, device=dev)
+    table = rope_table(D, 10000.0, None, P + suffix + E + 16, dev)
+    qr = apply_rope(qkv[:, :nq].view(T, Hq, D), pos, table).bfloat16()
+    kr = apply_rope(qkv[:, nq:nq + nk].view(T, Hkv, D), pos, table).bfloat16()
+    kp_ref, vp_ref = kp.clone(), vp.clone()
+    kp_ref[locs.long()] = kr.reshape(T, -1)
+    vp_ref[locs.long()] = qkv[:, nq + nk:].bfloat16()
+    ref = paged_attention_reference(qr, kp_ref, vp_ref, bt, ExtendBatch(None, None, None, rows, prefix, extend_len=E),
+                                    Hkv).float().reshape(T, -1)
+    st = _status()
+    state = torch.zeros(T, Hq, D + 2, device=dev)
+    shared = torch.full((bs,), P, device=dev, dtype=torch.int32)
+    out2 = torch.zeros(T, nq, device=dev, dtype=torch.bfloat16)
+    kp2, vp2 = kp.clone(), vp.clone()
+    K.attention_fused(qkv, pos, locs, table, kp2, vp2, bt, rows[::N].contiguous(), shared[::N].contiguous(), None, bs=1,
+                      E=N * E, Hq=Hq, Hkv=Hkv, D=D, KS=KSg, scale=D ** -0.5, status=st, part_out=state, causal=False)
+    assert torch.equal(kp2, kp) and torch.equal(vp2, vp)              # the group pass writes no K/V rows
+    K.attention_fused(qkv, pos, locs, table, kp2, vp2, bt, rows, prefix, out2, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D, KS=KSs,
+                      scale=D ** -0.5, status=st, key_begin=shared, part_in=state)
+    out1 = torch.zeros_like(out2)
+    K.attention_fused(qkv, pos, locs, table, kp, vp, bt, rows, prefix, out1, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D, KS=1,
+                      scale=D ** -0.5, status=st)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    assert torch.equal(kp2, kp) and torch.equal(vp2, vp)              # both forms wrote the same new rows
+    tol = 3e-2 * max(1.0, ref.abs().max().item())
+    assert (out1.float() - ref).abs().max().item() < tol
+    assert (out2.float() - ref).abs().max().item() < tol
+
+
 @pytest.mark.parametrize("groups,N,NP,E,Hq,Hkv,D,P,suffix,KSg,KSs", [
     (1, 8, 8, 1, 32, 8, 64, 1500, 300, 4, 2), (1, 8, 2, 9, 32, 8, 128, 2100, 200, 4, 1), (2, 4, 4, 2, 8, 2, 64, 700, 40, 2, 1),
     (1, 8, 8, 1, 32, 8, 64, 100, 1200, 1, 4), (1, 4, 2, 5, 8, 2, 128, 333, 0, 1, 1),
