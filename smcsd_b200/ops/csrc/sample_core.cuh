@@ -12,6 +12,7 @@ struct RowPartial {
   int best_idx;
   int pad;
 };
+static_assert(sizeof(RowPartial) == 32, "partials are exchanged as two 16-byte words");
 
 __device__ __forceinline__ void lse_merge(float& m, float& s, float m2, float s2) {
   const float M = fmaxf(m, m2);
@@ -107,13 +108,14 @@ __device__ __forceinline__ void sample_merge_row(const SampleArgs& a, const RowP
                                                  int lane, int* tok_out, float* logp_out, float* logz_out) {
   RowPartial r = row_partial_neutral();
   float given_logit = -INFINITY;
+  // two 16-byte loads per partial, four partials in flight per lane (the loop is bound by load latency)
+#pragma unroll 4
   for (int c = lane; c < n; c += 32) {
-    const RowPartial* src = parts + (size_t)c * stride;
+    const float4* src = reinterpret_cast<const float4*>(parts + (size_t)c * stride);
+    const float4 lo = __ldcg(src), hi = __ldcg(src + 1);
     RowPartial b;
-    b.max_s = __ldcg(&src->max_s); b.sum_s = __ldcg(&src->sum_s);
-    b.max_b = __ldcg(&src->max_b); b.sum_b = __ldcg(&src->sum_b);
-    b.best = __ldcg(&src->best); b.best_scaled = __ldcg(&src->best_scaled);
-    b.best_idx = __ldcg(&src->best_idx); b.pad = __ldcg(&src->pad);
+    b.max_s = lo.x; b.sum_s = lo.y; b.max_b = lo.z; b.sum_b = lo.w;
+    b.best = hi.x; b.best_scaled = hi.y; b.best_idx = __float_as_int(hi.z); b.pad = __float_as_int(hi.w);
     lse_merge(r.max_s, r.sum_s, b.max_s, b.sum_s);
     lse_merge(r.max_b, r.sum_b, b.max_b, b.sum_b);
     if (b.best > r.best || (b.best == r.best && b.best_idx < r.best_idx)) {
