@@ -92,12 +92,13 @@ def main(argv=None) -> None:
         state_tc = torch.zeros(kst, T, Hq, D + 2, device=dev)
 
         def cascade_tc():
+            # two launches: the group pass rotates the queries itself, the per-particle pass is the ordinary step
             for k, v in pools:
-                K.rope_kv_write(qkv, 1, 0, pos, locs, rope, q, k, v, M=T, Hq=Hq, Hkv=Hkv, D=D, status=status, pdl=True)
-                K.attention_prefix_tc(q, k, v, bt, rows_t, shared_t, state_tc, n_seq=bs // N, E=N * E, T=T, Hq=Hq,
-                                      Hkv=Hkv, D=D, KS=kst, scale=D ** -0.5, status=status)
+                K.attention_prefix_tc(None, k, v, bt, rows_t, shared_t, state_tc, n_seq=bs // N, E=N * E, T=T, Hq=Hq,
+                                      Hkv=Hkv, D=D, KS=kst, scale=D ** -0.5, status=status, qkv=qkv, q_off=0,
+                                      positions=pos, rope=rope, pdl=True)
                 K.attention_fused(qkv, pos, locs, rope, k, v, bt, rows, prefix, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D,
-                                  KS=kss, scale=D ** -0.5, status=status, pdl=False, q_in=q, key_begin=shared,
+                                  KS=kss, scale=D ** -0.5, status=status, pdl=True, key_begin=shared,
                                   part_in=state_tc, part_in_n=kst, part_in_stride=state_tc.stride(0))
 
         def group_mma():
@@ -110,6 +111,20 @@ def main(argv=None) -> None:
             for k, v in pools:
                 K.attention_prefix_tc(q, k, v, bt, rows_t, shared_t, state_tc, n_seq=bs // N, E=N * E, T=T, Hq=Hq,
                                       Hkv=Hkv, D=D, KS=kst, scale=D ** -0.5, status=status)
+
+        def suffix_only():
+            for k, v in pools:
+                K.attention_fused(qkv, pos, locs, rope, k, v, bt, rows, prefix, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D,
+                                  KS=kss, scale=D ** -0.5, status=status, pdl=False, q_in=q, key_begin=shared, part_in=state)
+
+        def suffix_self():
+            for k, v in pools:
+                K.attention_fused(qkv, pos, locs, rope, k, v, bt, rows, prefix, out, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D,
+                                  KS=kss, scale=D ** -0.5, status=status, pdl=False, key_begin=shared, part_in=state)
+
+        def rope_only():
+            for k, v in pools:
+                K.rope_kv_write(qkv, 1, 0, pos, locs, rope, q, k, v, M=T, Hq=Hq, Hkv=Hkv, D=D, status=status, pdl=False)
 
         def timed(fn):
             fn()
@@ -135,6 +150,7 @@ def main(argv=None) -> None:
         t3 = timed(cascade_tc)
         err_tc = float((out.float() - o1).abs().max())
         t4, t5 = timed(group_mma), timed(group_tc)
+        t6, t7, t8 = timed(suffix_only), timed(suffix_self), timed(rope_only)
         trace = torch.zeros(4096, 12, dtype=torch.int64, device=dev)
         k0, v0 = pools[0]
         K.attention_prefix_tc(q, k0, v0, bt, rows_t, shared_t, state_tc, n_seq=bs // N, E=N * E, T=T, Hq=Hq, Hkv=Hkv, D=D,
@@ -148,7 +164,7 @@ def main(argv=None) -> None:
         rows_out.append({"shape": ns.shape, "pages": "consecutive" if ns.contiguous else "scattered", "prompt": P, "suffix": S, "particles": N, "E": E, "single_us": t1,
                          "shared_prefix_us": t2, "speedup": t1 / t2, "shared_prefix_tcgen05_us": t3, "speedup_tcgen05": t1 / t3,
                          "splits_group_tcgen05": kst, "group_pass_us": t4,
-                         "group_pass_tcgen05_us": t5,
+                         "group_pass_tcgen05_us": t5, "suffix_pass_us": t6, "suffix_pass_own_rope_us": t7, "rope_kv_write_us": t8,
                          "tcgen05_wait_shares": dict(zip(["scores_ready", "score_load", "p_buffer", "exp_store", "mma_kv",
                                                           "mma_score_buffer", "mma_p", "load_stage_free", "load_issue", "load_landing",
                                                           "softmax_total_cycles"], [round(x, 3) for x in wait_share])), "max_abs_diff_tcgen05": err_tc, "splits_single": ks1, "splits_group": ksg,

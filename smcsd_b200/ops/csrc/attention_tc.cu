@@ -39,7 +39,12 @@ template <> struct TcCfg<128> { static constexpr int BK = 64, STAGES = 5, LOADER
 template <> struct TcCfg<64> { static constexpr int BK = 64, STAGES = 8, LOADERS = 4; };
 
 struct TcAttnParams {
-  const __nv_bfloat16* q;        // rotated queries [T, Hq * D]
+  const __nv_bfloat16* q;        // rotated queries [T, Hq * D]; null: rotate the fp32 projections below in the kernel
+  const float* qkv;              // [T, ld_qkv] fp32 projections, query heads at q_off
+  const int* positions;          // [T]
+  const float* rope;             // [max_pos, rd] cos | sin (rotary pairs i, i + rd / 2; dims beyond rd pass through)
+  int ld_qkv, q_off, rd;
+  int pdl;                       // launched with programmatic stream serialisation: wait for the previous grid here
   const __nv_bfloat16* k_pool;   // [pages + 1, Hkv * D]
   const __nv_bfloat16* v_pool;
   const int* block_table;
@@ -74,6 +79,11 @@ __device__ __forceinline__ bool tc_wait(TcShared& S, int* status, uint64_t* bar,
       return false;
     }
   }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -140,13 +150,39 @@ __global__ void __launch_bounds__((5 + TcCfg<D>::LOADERS) * 32, 1) attn_prefix_t
     tmem_alloc(&S.tmem_slot, 512);
     tmem_relinquish();
   }
+  // everything above overlaps the previous kernel; the query projections are its output
+  if (p.pdl) { pdl_launch_dependents(); pdl_wait_prior_grid(); }
   // ---- Q tile: rows r = e * G + gq of this (super-)sequence, zero padded to 128, swizzled K-major panels ----------
   for (int idx = threadIdx.x; idx < 128 * CPR; idx += TC_THREADS) {
     const int r = idx / CPR, c = idx % CPR;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (row0 + r < R) {
-      const int e = (row0 + r) / G, gq = (row0 + r) % G;
-      v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(seq * p.E + e) * p.Hq + hbase + gq) * D + c * 8);
+      const int e = (row0 + r) / G, gq = (row0 + r) % G, tkn = seq * p.E + e;
+      if (p.q != nullptr) {
+        v = *reinterpret_cast<const uint4*>(p.q + ((size_t)tkn * p.Hq + hbase + gq) * D + c * 8);
+      } else {
+        // rotate this 8-element chunk of the fp32 query row: element i pairs with i + half inside the rotary span
+        const float* src = p.qkv + (size_t)tkn * p.ld_qkv + p.q_off + (size_t)(hbase + gq) * D;
+        const int half = p.rd >> 1, i0 = c * 8;
+        float x[8];
+        *reinterpret_cast<float4*>(x) = *reinterpret_cast<const float4*>(src + i0);
+        *reinterpret_cast<float4*>(x + 4) = *reinterpret_cast<const float4*>(src + i0 + 4);
+        if (i0 < p.rd) {
+          const bool lo = i0 < half;
+          const int j0 = lo ? i0 : i0 - half;                 // index into the cos / sin halves
+          const float* cs = p.rope + (size_t)p.positions[tkn] * p.rd;
+          float y[8], cv[8], sv[8];
+          *reinterpret_cast<float4*>(y) = *reinterpret_cast<const float4*>(src + (lo ? i0 + half : j0));
+          *reinterpret_cast<float4*>(y + 4) = *reinterpret_cast<const float4*>(src + (lo ? i0 + half : j0) + 4);
+          *reinterpret_cast<float4*>(cv) = *reinterpret_cast<const float4*>(cs + j0);
+          *reinterpret_cast<float4*>(cv + 4) = *reinterpret_cast<const float4*>(cs + j0 + 4);
+          *reinterpret_cast<float4*>(sv) = *reinterpret_cast<const float4*>(cs + half + j0);
+          *reinterpret_cast<float4*>(sv + 4) = *reinterpret_cast<const float4*>(cs + half + j0 + 4);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) x[u] = lo ? x[u] * cv[u] - y[u] * sv[u] : x[u] * cv[u] + y[u] * sv[u];
+        }
+        v = make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+      }
     }
     const int pan = c >> 3, cc = c & 7;
     *reinterpret_cast<uint4*>(q_s + pan * PANEL_Q + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
@@ -495,14 +531,22 @@ SMC_API int smc_attention_tc_splits(int n_seq, int Hkv, int keys, int rows) {
 // q: rotated bf16 queries [T, Hq * D]; every (super-)sequence s has E consecutive tokens, block-table row rows[s] and
 // attends keys [0, key_count[s]) without a causal limit; the E * Hq / Hkv query rows of a KV head take tiles of 128.  part_out [KS, T, Hq, D + 2] fp32 receives
 // the unnormalised state of every key split (D values, running max in natural-log units, running sum).
+// q may be null: then qkv (fp32 [T, ld_qkv], query heads at q_off), positions [T] and the rope table [max_pos, rd] are
+// given and the kernel rotates the queries itself (rd and rd / 2 multiples of 8, rd <= D).
 SMC_API int smc_attention_prefix_tc(const void* q, const void* k_pool, const void* v_pool, int n_pages,
                                     const int* block_table, int bt_stride, const int* rows, const int* key_count,
                                     float* part_out, int n_seq, int E, int T, int Hq, int Hkv, int D, int KS, float scale,
-                                    int* status, long long* trace, int use_tma, cudaStream_t st) {
+                                    int* status, long long* trace, int use_tma, const float* qkv, int ld_qkv, int q_off,
+                                    const int* positions, const float* rope, int rd, int pdl, cudaStream_t st) {
   using namespace smc;
   if (n_seq <= 0) return 0;
+  if (q == nullptr && (qkv == nullptr || positions == nullptr || rope == nullptr || (rd & 15) || rd > D ||
+                       (ld_qkv & 3) || (q_off & 3)))
+    return -82;
   if (Hq % Hkv || E < 1 || KS < 1 || KS > 8) return -80;
   TcAttnParams p;
+  p.pdl = pdl;
+  p.qkv = qkv; p.positions = positions; p.rope = rope; p.ld_qkv = ld_qkv; p.q_off = q_off; p.rd = rd;
   p.q = (const __nv_bfloat16*)q; p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
   p.block_table = block_table; p.rows = rows; p.key_count = key_count; p.part_out = part_out;
   p.bt_stride = bt_stride; p.n_pages = n_pages; p.E = E; p.Hq = Hq; p.Hkv = Hkv; p.KS = KS; p.T = T;
@@ -521,6 +565,16 @@ SMC_API int smc_attention_prefix_tc(const void* q, const void* k_pool, const voi
   else if (D == 64) { kern = attn_prefix_tc_kernel<64>; smem = tc_smem_bytes<64>(); threads = (5 + TcCfg<64>::LOADERS) * 32; }
   else return -81;
   CUDA_CHECK_RET(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3((unsigned)(n_seq * Hkv * ((E * (Hq / Hkv) + 127) / 128)), (unsigned)KS), threads, smem, st>>>(p, tmK, tmV);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(n_seq * Hkv * ((E * (Hq / Hkv) + 127) / 128)), (unsigned)KS);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  CUDA_CHECK_RET(cudaLaunchKernelEx(&cfg, kern, p, tmK, tmV));
   return (int)cudaGetLastError();
 }

@@ -319,25 +319,31 @@ def attention_tc_splits(n_seq: int, Hkv: int, keys: int, rows: int = 128) -> int
     return L.smc_attention_tc_splits(n_seq, Hkv, keys, rows)
 
 
-def attention_prefix_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+def attention_prefix_tc(q: Optional[torch.Tensor], k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                         rows: torch.Tensor, key_count: torch.Tensor, part_out: torch.Tensor, *, n_seq: int, E: int,
                         T: int, Hq: int, Hkv: int, D: int, KS: int, scale: float, status: torch.Tensor,
-                        trace: Optional[torch.Tensor] = None, use_tma: bool = True) -> None:
+                        trace: Optional[torch.Tensor] = None, use_tma: bool = True, qkv: Optional[torch.Tensor] = None,
+                        q_off: int = 0, positions: Optional[torch.Tensor] = None,
+                        rope: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
     """Shared-prefix attention pass on tcgen05: the E tokens (all query heads) of every (super-)sequence against keys
     [0, key_count) of its block-table row, no causal limit; parks the unnormalised state of every key split in
     ``part_out`` [KS, T, Hq, D + 2].  ``trace`` (int64 [CTAs, 12], optional) receives the cycles every CTA spent in
     its waits: softmax {scores ready, score load, P buffer free, exp + store, total}, MMA {K/V, score buffer, P}, first
     loader warp {stage free, copy issue, landing, total}.  Tiles of 64 consecutive pages are fetched by TMA unless
-    ``use_tma`` is off; scattered tiles are gathered row by row."""
+    ``use_tma`` is off; scattered tiles are gathered row by row.  With ``q`` None the kernel rotates the fp32 query
+    projections ``qkv`` (heads at ``q_off``) itself, given ``positions`` and the ``rope`` table."""
     L = lib()
     if not getattr(L, "_atc_declared", False):
         vp, i, f = C.c_void_p, C.c_int, C.c_float
-        L.smc_attention_prefix_tc.argtypes = [vp, vp, vp, i, vp, i, vp, vp, vp, i, i, i, i, i, i, i, f, vp, vp, i, vp]
+        L.smc_attention_prefix_tc.argtypes = [vp, vp, vp, i, vp, i, vp, vp, vp, i, i, i, i, i, i, i, f, vp, vp, i, vp, i, i, vp, vp, i,
+                                              i, vp]
         L.smc_attention_prefix_tc.restype = C.c_int
         L._atc_declared = True
     _check(L.smc_attention_prefix_tc(_p(q), _p(k_pool), _p(v_pool), k_pool.shape[0] - 1, _p(block_table),
                                      block_table.stride(0), _p(rows), _p(key_count), _p(part_out), n_seq, E, T, Hq, Hkv,
-                                     D, KS, scale, _p(status), _p(trace), int(use_tma), _stream()), "smc_attention_prefix_tc")
+                                     D, KS, scale, _p(status), _p(trace), int(use_tma), _p(qkv),
+                                     qkv.stride(0) if qkv is not None else 0, q_off, _p(positions), _p(rope),
+                                     rope.shape[1] if rope is not None else 0, int(pdl), _stream()), "smc_attention_prefix_tc")
 
 
 def attn_kv_splits(ctx: int, bs: int, Hkv: int, E: int = 1, G: int = 4, D: int = 128) -> int:

@@ -149,21 +149,23 @@ class NativeLlama:
                               E=E, Hq=self.nq, Hkv=self.nkv, D=self.D, KS=plan["KSs"], scale=scale, status=self.status,
                               pdl=pdl, key_begin=cb["shared"], part_in=self.att_state)
             return
-        K.rope_kv_write(self.qkv, 1, 0, positions, cache_locs, m.rope, self.q, k, v, M=T, Hq=self.nq, Hkv=self.nkv,
-                        D=self.D, status=self.status, pdl=pdl)
         if plan["tc"]:
-            # group pass on the tcgen05 kernel: one parked state per key split, folded in by the per-particle pass
+            # two launches: the tcgen05 group pass rotates the queries itself and parks one state per key split; the
+            # per-particle pass is the ordinary step (rope, KV write, new-token tile) started behind the shared keys
             if self.att_state_tc is None:
                 self.att_state_tc = torch.zeros(8, self.T, self.nq, self.D + 2, dtype=torch.float32, device=self.h.device)
-            K.attention_prefix_tc(self.q, k, v, self.bt, cb["rows_g"][NP], cb["shared_g"][NP], self.att_state_tc,
+            K.attention_prefix_tc(None, k, v, self.bt, cb["rows_g"][NP], cb["shared_g"][NP], self.att_state_tc,
                                   n_seq=bs // NP, E=NP * E, T=self.T, Hq=self.nq, Hkv=self.nkv, D=self.D,
-                                  KS=plan["KSg"], scale=scale, status=self.status)
+                                  KS=plan["KSg"], scale=scale, status=self.status, qkv=self.qkv, q_off=0,
+                                  positions=positions, rope=m.rope, pdl=pdl)
             K.attention_fused(self.qkv, positions, cache_locs, m.rope, k, v, self.bt, rows, prefix_lens, self.attn,
                               bs=bs, E=E, Hq=self.nq, Hkv=self.nkv, D=self.D, KS=plan["KSs"], scale=scale,
-                              status=self.status, pdl=False, q_in=self.q, key_begin=cb["shared"],
+                              status=self.status, pdl=pdl, key_begin=cb["shared"],
                               part_in=self.att_state_tc, part_in_n=plan["KSg"],
                               part_in_stride=self.att_state_tc.stride(0))
             return
+        K.rope_kv_write(self.qkv, 1, 0, positions, cache_locs, m.rope, self.q, k, v, M=T, Hq=self.nq, Hkv=self.nkv,
+                        D=self.D, status=self.status, pdl=pdl)
         K.attention_fused(self.qkv, positions, cache_locs, m.rope, k, v, self.bt, cb["rows_g"][NP], cb["shared_g"][NP],
                           None, bs=bs // NP, E=NP * E, Hq=self.nq, Hkv=self.nkv, D=self.D, KS=plan["KSg"], scale=scale,
                           status=self.status, pdl=pdl, q_in=self.q, part_out=self.att_state, causal=False)
@@ -177,14 +179,14 @@ class NativeLlama:
         self.ctx_hint = int(ctx)
         return tuple(self._ks(bs, E) for E in Es)
 
-    # Shortest shared prompt for which the extra two launches per layer pay off.  Measured on B200 (8 particles,
-    # 256 own tokens each): single-token steps with the mma.sync group pass 0.87x at 4k, 1.1x at 8k, 1.5x at 16k, 2.0x
-    # at 32k prompt tokens.  The verify shape (9 tokens x 4 heads per particle) loses at every length with the mma.sync
-    # group pass (bound by its issue rate) and wins with the tcgen05 one: pages scattered 1.0x at 8k, 1.14x at 12k,
-    # 1.2x at 16k, 1.4x at 32k; prompt in consecutive pages 1.2x at 8k, 1.5x at 12k, 1.9x at 32k.
+    # Shortest shared prompt for which the extra launch per layer pays off.  Measured on B200 (8 particles, 256 own
+    # tokens each): single-token steps with the mma.sync group pass 0.87x at 4k, 1.1x at 8k, 1.5x at 16k, 2.0x at 32k
+    # prompt tokens.  The verify shape (9 tokens x 4 heads per particle) loses at every length with the mma.sync group
+    # pass (bound by its issue rate) and wins with the tcgen05 one: pages scattered 0.83x at 4k, 1.1x at 8k, 1.25x at
+    # 16k, 1.5x at 32k; prompt in consecutive pages 0.88x at 4k, 1.3x at 8k, 1.7x at 16k, 2.1x at 32k.
     # SMC_CASCADE_VERIFY=1 / 0 forces the verify-shape passes on / off.
     CASCADE_MIN_PROMPT = 8192
-    CASCADE_MIN_PROMPT_VERIFY = 12288
+    CASCADE_MIN_PROMPT_VERIFY = 8192
 
     def set_prefix(self, min_prompt: int, max_prompt: int, bs: int, n_particles: int, Es=(1, 2)) -> tuple:
         """Plan the shared-prefix passes for forwards of ``Es`` new tokens per sequence: ``min_prompt`` / ``max_prompt``

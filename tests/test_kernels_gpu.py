@@ -536,12 +536,24 @@ def test_attention_shared_prefix_two_launches(N, E, Hq, Hkv, D, P, suffix, KSg, 
     out1 = torch.zeros_like(out2)
     K.attention_fused(qkv, pos, locs, table, kp, vp, bt, rows, prefix, out1, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D, KS=1,
                       scale=D ** -0.5, status=st)
+    # the tcgen05 group pass in the same role: rotates the fp32 queries itself, one parked state per key split
+    kst = K.attention_tc_splits(1, Hkv, P, N * E * (Hq // Hkv))
+    state_tc = torch.full((kst, T, Hq, D + 2), float("nan"), device=dev)
+    out3 = torch.zeros_like(out2)
+    kp3, vp3 = kp2.clone(), vp2.clone()
+    K.attention_prefix_tc(None, kp3, vp3, bt, rows[::N].contiguous(), shared[::N].contiguous(), state_tc, n_seq=1,
+                          E=N * E, T=T, Hq=Hq, Hkv=Hkv, D=D, KS=kst, scale=D ** -0.5, status=st, qkv=qkv, q_off=0,
+                          positions=pos, rope=table)
+    K.attention_fused(qkv, pos, locs, table, kp3, vp3, bt, rows, prefix, out3, bs=bs, E=E, Hq=Hq, Hkv=Hkv, D=D, KS=KSs,
+                      scale=D ** -0.5, status=st, key_begin=shared, part_in=state_tc, part_in_n=kst,
+                      part_in_stride=state_tc.stride(0))
     torch.cuda.synchronize()
     assert int(st) == 0
     assert torch.equal(kp2, kp) and torch.equal(vp2, vp)              # both forms wrote the same new rows
     tol = 3e-2 * max(1.0, ref.abs().max().item())
     assert (out1.float() - ref).abs().max().item() < tol
     assert (out2.float() - ref).abs().max().item() < tol
+    assert (out3.float() - ref).abs().max().item() < tol
 
 
 @pytest.mark.parametrize("groups,N,NP,E,Hq,Hkv,D,P,suffix,KSg,KSs", [
