@@ -6,7 +6,9 @@
 
 Datasets: ``random`` (uniform token ids, fixed or ranged lengths), ``lognormal`` (median 200, sigma 1,
 clipped to 4..2048), ``generated-shared-prefix`` (groups of prompts sharing a long prefix), ``file`` (one JSON
-list of token ids, or one text prompt with a tokenizer, per line).  Warm-up: 16 short requests.  Prints
+list of token ids, or one text prompt with a tokenizer, per line), ``sharegpt`` (a ShareGPT conversation dump given
+with ``--dataset-path``: the first human turn is the prompt and the length of the first reply the output budget of
+that request, as in the reference harness; without a tokenizer, words are hashed into the vocabulary).  Warm-up: 16 short requests.  Prints
 request / input / output / total throughput with the ``Output token throughput (tok/s):`` line that sweep
 scripts parse, and appends a JSON line to ``--result-file``.  Timing is wall clock around the whole
 ``generate`` call (tokenization and prefill included), like the reference harness
@@ -25,6 +27,33 @@ import torch
 
 from ..config import EngineArgs
 from ..utils.prompts import lognormal_lengths, random_prompts
+
+
+def load_sharegpt(path: str, n: int, vocab: int, tokenizer=None, max_in: int = 2048, max_out: int = 2048):
+    """(prompts as token ids, per-request output lengths) from a ShareGPT JSON dump: a list of records with a
+    ``conversations`` list of ``{"from": "human" | "gpt", "value": text}`` turns.  Conversations that do not start with
+    a human turn followed by a reply, or whose prompt is shorter than 4 tokens, are skipped."""
+    import zlib
+    with open(path) as f:
+        data = json.load(f)
+
+    def encode(text: str) -> List[int]:
+        if tokenizer is not None:
+            return list(tokenizer.encode(text))
+        return [zlib.crc32(w.encode()) % vocab for w in text.split()]      # stable stand-in for preset (random) models
+    prompts, outs = [], []
+    for rec in data:
+        conv = rec.get("conversations") or rec.get("conversation") or []
+        if len(conv) < 2 or conv[0].get("from") not in ("human", "user") or not conv[1].get("value"):
+            continue
+        ids, reply = encode(conv[0].get("value", "")), encode(conv[1]["value"])
+        if len(ids) < 4 or len(reply) < 4:
+            continue
+        prompts.append(ids[:max_in])
+        outs.append(min(len(reply), max_out))
+        if len(prompts) == n:
+            break
+    return prompts, outs
 
 
 def build_prompts(ns, vocab: int) -> List[List[int]]:
@@ -63,7 +92,7 @@ def main(argv=None) -> None:
                    choices=["smc_engine", "engine"],
                    help="smc_engine: SMC speculative decoding; engine: plain sampling from the target (vanilla arm)")
     p.add_argument("--dataset-name", default="random",
-                   choices=["random", "lognormal", "generated-shared-prefix", "file"])
+                   choices=["random", "lognormal", "generated-shared-prefix", "file", "sharegpt"])
     p.add_argument("--dataset-path", default=None)
     p.add_argument("--num-prompts", type=int, default=8)
     p.add_argument("--random-input-len", type=int, default=256)
@@ -81,8 +110,14 @@ def main(argv=None) -> None:
     eng = build_engine_from_args(ns) if ns.backend_name == "smc_engine" else \
         build_baseline_engine_from_args(ns, ns.temperature)
     vocab = eng._sched.target.cfg.vocab_size if eng._sched is not None else 32000
-    prompts = build_prompts(ns, vocab)
-    sp = {"max_new_tokens": ns.random_output_len, "ignore_eos": True, "temperature": ns.temperature}
+    if ns.dataset_name == "sharegpt":
+        if not ns.dataset_path:
+            raise SystemExit("--dataset-name sharegpt needs --dataset-path (a ShareGPT JSON dump)")
+        prompts, out_lens = load_sharegpt(ns.dataset_path, ns.num_prompts, vocab, getattr(eng, "tokenizer", None))
+        sp = [{"max_new_tokens": n, "ignore_eos": True, "temperature": ns.temperature} for n in out_lens]
+    else:
+        prompts = build_prompts(ns, vocab)
+        sp = {"max_new_tokens": ns.random_output_len, "ignore_eos": True, "temperature": ns.temperature}
     key = "prompt" if prompts and isinstance(prompts[0], str) else "input_ids"
     if not ns.skip_warmup:
         warm = random_prompts([min(256, ns.random_input_len)] * min(16, max(1, ns.max_running_requests)), vocab, 99)

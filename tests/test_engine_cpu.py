@@ -129,3 +129,29 @@ def test_e4m3_kv_cache_on_the_pytorch_path():
     eng._sched.check_idle_invariants()
     agree = sum(int(a == b) for r, o in zip(ref, out) for a, b in zip(r["output_ids"], o["output_ids"])) / 24
     assert agree >= 0.5
+
+
+def test_offline_throughput_sharegpt_dataset(tmp_path, capsys):
+    """The offline throughput harness on a ShareGPT-style dump: first human turn = prompt, first reply length = that
+    request's output budget; records without a reply are skipped; the sweep-parsable throughput line is printed."""
+    import json
+    from smcsd_b200.bench import offline_throughput as ot
+    data = [
+        {"conversations": [{"from": "human", "value": "tell me about the weather in the north of the country today"},
+                           {"from": "gpt", "value": "it is going to rain a little in the morning and clear up later"}]},
+        {"conversations": [{"from": "gpt", "value": "no human turn first"}]},
+        {"conversations": [{"from": "human", "value": "how do i sort a list of numbers in python please"},
+                           {"from": "gpt", "value": "call sorted on the list or use the sort method of the list"}]},
+    ]
+    path = tmp_path / "sharegpt.json"
+    path.write_text(json.dumps(data))
+    prompts, outs = ot.load_sharegpt(str(path), 8, 4096)
+    assert len(prompts) == 2 and outs == [14, 13] and all(0 <= t < 4096 for p in prompts for t in p)
+    res = tmp_path / "res.jsonl"
+    ot.main(["--model", "preset:tiny-target", "--draft-model", "preset:tiny-draft", "-N", "4", "-g", "3",
+             "--dataset-name", "sharegpt", "--dataset-path", str(path), "--num-prompts", "2", "--device", "cpu",
+             "--dtype", "float32", "--max-running-requests", "2", "--skip-warmup", "--result-file", str(res)])
+    out = capsys.readouterr().out
+    assert "Output token throughput (tok/s):" in out
+    rec = json.loads(res.read_text().strip())
+    assert rec["dataset"] == "sharegpt" and rec["num_prompts"] == 2
