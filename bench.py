@@ -78,6 +78,41 @@ def _e2e(eng, sched, lens, new_tokens, vocab, rank, world, dist, torch, seed):
             "timing": "wall clock around generate() calls, cuda-synchronized, max over ranks"}
 
 
+def _run_fused_children(rank: int, steps: int, warm: int, dry_run: bool = False, limit_s: int = 420):
+    """Start ``smcsd_b200.bench.fused_section`` for this rank (same RANK / WORLD_SIZE / LOCAL_RANK, next-door port, its
+    own store), wait at most ``limit_s`` seconds, stop it by pid on overrun; rank 0 returns the record it wrote."""
+    import subprocess
+    import tempfile
+    env = dict(os.environ)
+    env["MASTER_PORT"] = str(int(env.get("MASTER_PORT", "29500")) + 17)
+    env.setdefault("MASTER_ADDR", "127.0.0.1")
+    for k in [k for k in env if k.startswith("TORCHELASTIC_")]:
+        env.pop(k)                                   # the child hosts its own rendezvous store
+    out = os.path.join(tempfile.gettempdir(), f"smc_fused_{env['MASTER_PORT']}_{os.getppid()}.json")
+    if rank == 0 and os.path.exists(out):
+        os.remove(out)
+    cmd = [sys.executable, "-m", "smcsd_b200.bench.fused_section", "--steps", str(steps), "--warmup", str(warm),
+           "--out", out] + (["--dry-run"] if dry_run else [])
+    proc = subprocess.Popen(cmd, env=env, cwd=os.path.dirname(os.path.abspath(__file__)),
+                            stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    timed_out = False
+    try:
+        proc.wait(timeout=limit_s)
+    except subprocess.TimeoutExpired:
+        timed_out = True
+        proc.kill()
+        proc.wait()
+    if rank != 0:
+        return None
+    if os.path.exists(out):
+        with open(out) as f:
+            rec = json.load(f)
+        os.remove(out)
+        return rec
+    return {"status": -2, "error": "the fused-collective job " + ("ran past its time limit" if timed_out else
+                                                                 f"ended with code {proc.returncode} without a record")}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -232,32 +267,16 @@ def main() -> int:
             fp8 = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     # ---- fused collective paths (two or more GPUs) ----------------------------------------------------
+    # Run as child processes with a process group of their own and a time limit: a failure there cannot take this
+    # job's line down or leave its ranks waiting for one another.
     fused = None
     if world > 1 and not args.no_fused and args.impl == "native":
         eng.shutdown()
         del eng, sched
         gc.collect()
         torch.cuda.empty_cache()
-        fused = {"status": 0}
-        try:
-            from smcsd_b200.bench import pp_cycle, tp_layers
-            ns = tp_layers._parser().parse_args(["--model", "llama-3.1-70b", "--layers", "8", "--bs", "8", "--E", "9"])
-            r = tp_layers.run(ns, init_pg=False)
-            fused.update({"tp_layer_us": r["fused_us_per_layer"], "tp_layer_nccl_us": r["cublas_nccl_us_per_layer"],
-                          "tp_floor_us": r["floor_us_per_layer"], "tp_tokens": r["tokens"], "tp_size": r["tp"],
-                          "tp_model": "llama-3.1-70b layers (8 full-width layers per rank shard)",
-                          "tp_fraction_of_floor": r["fused_fraction_of_floor"]})
-            fused["status"] |= int(r["device_status"])
-            gc.collect()
-            torch.cuda.empty_cache()
-            r = pp_cycle.run(steps=steps, warmup=warm)
-            fused.update({"pp_cycle_ms": r["pp_cycle_ms"], "pp_nvlink_bytes_per_cycle": r["pp_nvlink_bytes_per_cycle"],
-                          "pp_n_particles": r["n_particles"], "pp_remote_copies_last_cycle": r["remote_copies_last_cycle"],
-                          "pp_tokens_per_s": r["tokens_per_s"]})
-            fused["status"] |= int(r["status"])
-        except Exception as e:       # the headline line must still be printed
-            fused["status"] = -1
-            fused["error"] = f"{type(e).__name__}: {e}"[:300]
+        fused = _run_fused_children(rank, steps, warm)
+        dist.barrier()
     clocks = sampler.stop() if sampler else None
 
     if rank == 0:
