@@ -107,6 +107,10 @@ __global__ void pp_collect_kernel(const PpWorld* __restrict__ w, PpLocal loc, co
     if (!ok) atomicOr(status, SMC_ERR_PEER_TIMEOUT);
   }
   __syncwarp();
+  // A shard that never arrived leaves stale weights in the gather buffer; a plan made from them would differ from
+  // the peers' plans and could name an ancestor whose rank has not populated it.  Such a rank resamples nothing this
+  // cycle (no local jobs, no peer reads); the status word tells the host.
+  if (!ok) return;
   const int N = W.n_ranks * W.n_local;
   const int row = active_rows[gi];
   const int pr = lane / W.n_local, pi = lane % W.n_local;       // global particle `lane` lives on rank pr
@@ -202,31 +206,43 @@ pp_release_kernel(PpLocal loc, int bt_stride, const long long* __restrict__ coun
 __global__ void __launch_bounds__(128)
 pp_adopt_kernel(const PpWorld* __restrict__ w, PpLocal loc, const long long* __restrict__ counters,
                 const int* __restrict__ rjob_dst, const int* __restrict__ rjob_rank, const int* __restrict__ rjob_idx,
-                int* __restrict__ rjob_src_slot) {
+                int* __restrict__ rjob_src_slot, int* status) {
   const PpWorld& W = *w;
   const int job = blockIdx.x;
   if (job >= (int)counters[3]) return;
-  __shared__ int s_base, s_src;
+  __shared__ int s_base, s_src, s_len;
   const int dst = rjob_dst[job];
   const PpRank& peer = W.r[rjob_rank[job]];
   const int P = loc.prompt_lens[dst];
   if (threadIdx.x == 0) {
-    const int src = peer.group_to_slots[rjob_idx[job]];
-    s_src = src;
-    rjob_src_slot[job] = src;
-    const int n_new = peer.seq_lens[src] - P;
-    const int old = atomicSub(loc.free_count, n_new);
-    if (old < n_new) {                       // pool ran dry: fall back to the scratch page and report
-      atomicAdd(loc.free_count, n_new);
-      atomicOr(loc.alloc_error, SMC_ERR_ALLOC_EXHAUSTED);
+    // everything read from the peer is checked before it becomes an index: a slot or a length outside its range
+    // (a peer that has not set the group up) ends the job here, with the destination left as it is
+    int src = peer.group_to_slots[rjob_idx[job]];
+    int Lp = -1;
+    if (src >= 0 && src < W.max_groups * W.n_local) Lp = peer.seq_lens[src];
+    if (Lp < P || Lp > W.bt_stride) {
+      atomicOr(status, SMC_ERR_BOUNDS);
+      src = -1;
       s_base = -1;
     } else {
-      s_base = old - n_new;
+      const int n_new = Lp - P;
+      const int old = atomicSub(loc.free_count, n_new);
+      if (old < n_new) {                     // pool ran dry: fall back to the scratch page and report
+        atomicAdd(loc.free_count, n_new);
+        atomicOr(loc.alloc_error, SMC_ERR_ALLOC_EXHAUSTED);
+        s_base = -1;
+      } else {
+        s_base = old - n_new;
+      }
     }
+    s_src = src;
+    s_len = Lp;
+    rjob_src_slot[job] = src;
   }
   __syncthreads();
   const int src = s_src, base = s_base;
-  const int Ls = peer.seq_lens[src];
+  if (src < 0) return;
+  const int Ls = s_len;
   int* bt = loc.block_table + (size_t)dst * W.bt_stride;
   for (int j = P + threadIdx.x; j < Ls; j += blockDim.x) {
     int page = 0;
@@ -263,6 +279,7 @@ pp_copy_kernel(const PpWorld* __restrict__ w, PpLocal loc, const long long* __re
   while (ti < W.n_tensors && lay >= W.r[W.rank].t[ti].n_layers) { lay -= W.r[W.rank].t[ti].n_layers; ++ti; }
   if (ti >= W.n_tensors) return;
   const int dst = rjob_dst[job], src = rjob_src_slot[job], pr = rjob_rank[job];
+  if (src < 0) return;                         // adopt refused this job
   const PpTensor& ts = W.r[pr].t[ti];
   const PpTensor& td = W.r[W.rank].t[ti];
   const long long rb = td.row_bytes;
@@ -284,7 +301,7 @@ pp_copy_kernel(const PpWorld* __restrict__ w, PpLocal loc, const long long* __re
   const int sub = threadIdx.x / lanes_per_row, l = threadIdx.x % lanes_per_row;
   for (int j = P + blockIdx.z * rows_per_block + sub; j < Ls; j += gridDim.z * rows_per_block) {
     const int ps = bt_src[j], pd = bt_dst[j];
-    if (pd <= 0) continue;
+    if (pd <= 0 || ps < 0 || ps > loc.n_pages) continue;
     const uint4* s = sbase + (size_t)ps * vec;
     uint4* d = dbase + (size_t)pd * vec;
     for (long long i = l; i < vec; i += lanes_per_row) d[i] = s[i];
@@ -335,12 +352,13 @@ SMC_API int smc_pp_collect(const PpWorld* w_dev, const PpLocal* loc, const doubl
 
 SMC_API int smc_pp_fetch(const PpWorld* w_dev, const PpLocal* loc, int bt_stride, const long long* counters,
                          const int* rjob_dst, const int* rjob_rank, const int* rjob_idx, int* rjob_src_slot,
-                         int max_jobs, int total_layers, int phase, cudaStream_t st) {
+                         int max_jobs, int total_layers, int phase, int* status, cudaStream_t st) {
   if (max_jobs <= 0) return 0;
   if (phase == 0 || phase == 1)
     pp_release_kernel<<<max_jobs, 128, 0, st>>>(*loc, bt_stride, counters, rjob_dst);
   if (phase == 0 || phase == 2) {
-    pp_adopt_kernel<<<max_jobs, 128, 0, st>>>(w_dev, *loc, counters, rjob_dst, rjob_rank, rjob_idx, rjob_src_slot);
+    pp_adopt_kernel<<<max_jobs, 128, 0, st>>>(w_dev, *loc, counters, rjob_dst, rjob_rank, rjob_idx, rjob_src_slot,
+                                              status);
     if (total_layers > 0)
       pp_copy_kernel<<<dim3(max_jobs, total_layers, 8), 256, 0, st>>>(w_dev, *loc, counters, rjob_dst, rjob_rank,
                                                                      rjob_src_slot);

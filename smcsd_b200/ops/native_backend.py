@@ -976,6 +976,8 @@ class NativeRunner:
             # warm up once eagerly on a side stream (also JIT-free: everything is precompiled), then capture
             gr = torch.cuda.CUDAGraph()
             saved = self._save_state(st)
+            if st.pp is not None:
+                st.pp.align()              # every rank enters the eager cycle's weight exchange together
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
@@ -989,6 +991,8 @@ class NativeRunner:
             self.launches_per_cycle = K.launch_count - n0
             self._restore_state(st, saved)
             self.graphs[key] = gr
+            if st.pp is not None:
+                st.pp.align()              # capture time differs per rank; replay starts together
         gr.replay()
 
     # capture runs the cycle for real; put the mutable state back afterwards

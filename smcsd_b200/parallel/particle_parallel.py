@@ -116,7 +116,7 @@ class ParticleParallel:
         vp, i, ll, d, ull = C.c_void_p, C.c_int, C.c_longlong, C.c_double, C.c_ulonglong
         L.smc_pp_share_weights.argtypes = [vp, vp, vp, vp, i, vp, ll, ll, vp]
         L.smc_pp_collect.argtypes = [vp, vp, vp, vp, vp, i, vp, d, ull, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
-        L.smc_pp_fetch.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, i, i, i, vp]
+        L.smc_pp_fetch.argtypes = [vp, vp, i, vp, vp, vp, vp, vp, i, i, i, vp, vp]
         L.smc_pp_barrier.argtypes = [vp, ll, vp, vp, vp, i, vp]
         L.smc_resample_apply.argtypes = [vp, vp, vp, vp, i, vp]
         for n in ("smc_pp_share_weights", "smc_pp_collect", "smc_pp_fetch", "smc_pp_barrier", "smc_resample_apply",
@@ -218,7 +218,7 @@ class ParticleParallel:
         self._chk(L.smc_pp_fetch(self.world_dev.data_ptr(), C.byref(self.loc), st.bt.table.stride(0),
                                  st.counters.data_ptr(), self.rjob_dst.data_ptr(), self.rjob_rank.data_ptr(),
                                  self.rjob_idx.data_ptr(), self.rjob_src.data_ptr(), max_jobs, self.total_layers,
-                                 fetch_phase, self._s()), "pp_fetch")
+                                 fetch_phase, self.status.data_ptr(), self._s()), "pp_fetch")
 
     def barrier(self, phase: int = 0) -> None:
         base = self.comm_local.data_ptr()
@@ -245,6 +245,15 @@ class PpHost:
         out = [None] * self.world
         dist.all_gather_object(out, obj, group=self.group)
         return out
+
+    def align(self) -> None:
+        """Host rendezvous of the ranks after the device has drained.  The in-kernel waits on peers are bounded (about a
+        second); host work whose length differs per rank (first-launch module loading, a prefill, a graph capture)
+        is followed by this call so that no rank enters a cycle's exchange far ahead of the others."""
+        import torch.distributed as dist
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        dist.barrier(group=self.group)
 
 
 class PpTorch(PpHost):

@@ -328,6 +328,8 @@ class SMCScheduler:
             g.x0 = int(tok)
             g.t_first_token = time.time()
             self._materialize(g)
+        if self.state.pp is not None:
+            self.state.pp.align()           # prefill time differs per rank; the next cycle's weight exchange is bounded
 
     def _materialize(self, g: SequenceGroup) -> None:
         req, sp = g.req, g.req.sampling_params
@@ -417,6 +419,9 @@ class SMCScheduler:
         snap.wait()
         if snap.alloc_error:
             raise RuntimeError("device page allocator ran dry inside a decode cycle")
+        if snap.peer_status:
+            raise RuntimeError(f"particle-parallel resampling reported device status {snap.peer_status} "
+                               "(2: a rank's weights did not arrive in time, 8: a peer's slot failed its range check)")
         self.last_free_pages = snap.free_pages
         self.min_free_pages = min(self.min_free_pages, snap.free_pages)
         if self.native_runner is not None:

@@ -52,7 +52,7 @@ class HostSnapshot:
     def __init__(self, n_slots: int, device: torch.device):
         pin = device.type == "cuda"
         self.finished = torch.zeros(n_slots, dtype=torch.bool, pin_memory=pin)
-        self.scalars = torch.zeros(4, dtype=torch.int32, pin_memory=pin)   # free_count, alloc_error, n_resampled, step
+        self.scalars = torch.zeros(4, dtype=torch.int32, pin_memory=pin)   # free_count, alloc_error, peer status, -
         self.resampled = torch.zeros(1, dtype=torch.int64, pin_memory=pin)   # cumulative count of resampled groups
         self.group_active = None            # [max_groups] running particles per group over all ranks (particle-parallel)
         self.event = torch.cuda.Event() if pin else None
@@ -68,6 +68,11 @@ class HostSnapshot:
     @property
     def alloc_error(self) -> bool:
         return bool(self.scalars[1])
+
+    @property
+    def peer_status(self) -> int:
+        """Status word of the cross-rank resampling kernels (0: every wait on a peer was answered)."""
+        return int(self.scalars[2])
 
 
 class SlotState:
@@ -337,6 +342,9 @@ class SlotState:
             if snap.group_active is None:
                 snap.group_active = torch.zeros(self.max_groups, dtype=torch.int32, pin_memory=self._pin)
             snap.group_active.copy_(self.group_active, non_blocking=True)
+            status = getattr(getattr(self.pp, "driver", None), "status", None)
+            if status is not None:
+                snap.scalars[2:3].copy_(status[0:1], non_blocking=True)
         if snap.event is not None:
             snap.event.record()
         return snap
