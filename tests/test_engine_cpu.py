@@ -155,3 +155,20 @@ def test_offline_throughput_sharegpt_dataset(tmp_path, capsys):
     assert "Output token throughput (tok/s):" in out
     rec = json.loads(res.read_text().strip())
     assert rec["dataset"] == "sharegpt" and rec["num_prompts"] == 2
+
+
+def test_peer_status_in_the_cycle_snapshot_raises():
+    """A non-zero status word of the cross-rank resampling kernels reaches the host with the cycle snapshot and stops
+    the scheduler instead of letting the ranks' particle sets drift apart."""
+    import pytest
+    eng = _engine()
+    sched = eng._sched
+    from smcsd_b200.io_types import GenerateRequest, SamplingParams
+    sched.add_request(GenerateRequest("r0", _prompts(1)[0], SamplingParams(max_new_tokens=32, ignore_eos=True)))
+    sched.step()                         # prefill
+    sched._run_decode()
+    snap, rids = sched.pending.popleft()
+    assert snap.peer_status == 0
+    snap.scalars[2] = 2                  # what a timed-out wait on a peer's weights leaves behind
+    with pytest.raises(RuntimeError, match="particle-parallel"):
+        sched._process_snapshot(snap, rids)
