@@ -83,14 +83,16 @@ def test_rank_death_mid_run_is_detected():
         eng.generate(input_ids=_prompts(1), sampling_params={"max_new_tokens": 200, "ignore_eos": True})
 
 
-def test_particle_parallel_two_ranks_cpu():
-    """Particles of every group sharded over two gloo ranks: global resampling with cross-rank ancestor
-    transfer, identical drain decisions on both ranks, gathered finalize."""
+@pytest.mark.parametrize("ranks,particles", [(2, 4), (4, 8)])
+def test_particle_parallel_ranks_cpu(ranks, particles):
+    """Particles of every group sharded over gloo ranks (two particles per rank): global resampling with cross-rank
+    ancestor transfer, identical drain decisions on every rank, gathered finalize."""
     sp = {"max_new_tokens": 14, "ignore_eos": True}
-    with SMCEngine("preset:tiny-target", "preset:tiny-draft", **_kw(pp_size=2, resample_threshold=0.9)) as eng:
+    with SMCEngine("preset:tiny-target", "preset:tiny-draft",
+                   **_kw(pp_size=ranks, n_particles=particles, resample_threshold=0.9)) as eng:
         out = eng.generate(input_ids=_prompts(3), sampling_params=sp)
         info = eng.collective_rpc("server_info")[0].value
     for o in out:
         assert o["completion_tokens"] == 14
-        assert len(o["smc_particle_output_ids"]) == 4 and len(o["smc_log_w_tilde"]) == 4
+        assert len(o["smc_particle_output_ids"]) == particles and len(o["smc_log_w_tilde"]) == particles
     assert info["stats"]["resampled_groups"] > 0
