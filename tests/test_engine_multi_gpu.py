@@ -41,6 +41,18 @@ def test_particle_parallel_engine_two_gpus():
     assert info["backend"] == "native"
 
 
+def test_particle_parallel_engine_four_gpus():
+    """Eight particles over four ranks (two each): most ancestors of a resampling step live on another GPU."""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    with _engine(pp_size=4, n_particles=8, resample_threshold=0.9) as eng:
+        outs = eng.generate(input_ids=_prompts(3), sampling_params={"max_new_tokens": 33, "ignore_eos": True})
+        info = eng.collective_rpc("server_info")[0].value
+    assert [o["completion_tokens"] for o in outs] == [33] * 3
+    assert all(len(o["smc_particle_output_ids"]) == 8 for o in outs)
+    assert info["backend"] == "native"
+
+
 def test_tensor_parallel_engine_two_gpus_matches_single_gpu():
     sp = {"max_new_tokens": 21, "ignore_eos": True}
     ref = _engine(in_process=True).generate(input_ids=_prompts(2), sampling_params=sp)
