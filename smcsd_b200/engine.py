@@ -111,7 +111,10 @@ class SMCEngine:
     def generate(self, prompt: Union[str, List[str], None] = None,
                  sampling_params: Union[dict, List[dict], None] = None,
                  input_ids: Union[List[int], List[List[int]], None] = None,
-                 return_particles: bool = True):
+                 return_particles: bool = True, timeout: Optional[float] = None):
+        """``timeout`` (seconds, scheduler processes only): requests without a final answer by then are aborted on
+        every replica and returned as ``{"aborted": True}`` instead of blocking the caller forever (a request or
+        an answer lost between the processes)."""
         if (prompt is None) == (input_ids is None):
             raise ValueError("pass exactly one of prompt / input_ids")
         single = False
@@ -155,9 +158,12 @@ class SMCEngine:
                 self._tx[(self._rr + i) % len(self._tx)].send_pyobj(r)
             self._rr = (self._rr + n) % len(self._tx)
             pending = set(rids)
+            deadline = None if timeout is None else time.time() + float(timeout)
             while pending:
                 if self._rx.poll(200) == 0:
                     self._check_children()
+                    if deadline is not None and time.time() > deadline:
+                        self._give_up(pending, results, float(timeout))
                     continue
                 self._absorb(self._rx.recv_pyobj(), results, particles, pending)
         outs = []
@@ -196,6 +202,17 @@ class SMCEngine:
                 d["time_stats"] = o.time_stats
             results[o.rid] = d
             pending.discard(o.rid)
+
+    def _give_up(self, pending, results, waited: float) -> None:
+        """No final answer arrived in time: abort the requests wherever they are and report them as aborted."""
+        for rid in list(pending):
+            for tx in self._tx:
+                tx.send_pyobj(AbortReq(rid))
+            ids = self._partials.pop(rid, [])
+            msg = f"no answer from the scheduler within {waited:g} s"
+            results[rid] = dict(output_ids=ids, completion_tokens=len(ids), aborted=True, error=msg,
+                                finish_reason={"type": "abort", "message": msg})
+            pending.discard(rid)
 
     def _check_children(self) -> None:
         dead = [p for p in self._procs if not p.is_alive()]

@@ -110,6 +110,7 @@ def run_scheduler_process(args: EngineArgs, rank: int, world: int, ports: PortAr
         pipe_writer.send({"status": "ready", "rank": rank, "kv_pages": sched.alloc.size,
                           "context_len": sched.context_len, "backend": sched.backend})
         iters = 0
+        n_requests_seen = 0
         while True:
             msgs = []
             if leader:
@@ -124,6 +125,15 @@ def run_scheduler_process(args: EngineArgs, rank: int, world: int, ports: PortAr
                         break
                 while rpc.poll(0):
                     msgs.append(pickle.loads(rpc.recv()))
+            if leader and fault.get("drop_request") is not None:
+                kept = []
+                for m in msgs:                       # injected loss of one request message on its way in
+                    if isinstance(m, GenerateRequest):
+                        n_requests_seen += 1
+                        if n_requests_seen - 1 == fault["drop_request"]:
+                            continue
+                    kept.append(m)
+                msgs = kept
             if comm is not None and comm.group_size > 1:
                 msgs = comm.broadcast_objects(msgs)
             stop = False

@@ -96,3 +96,16 @@ def test_particle_parallel_ranks_cpu(ranks, particles):
         assert o["completion_tokens"] == 14
         assert len(o["smc_particle_output_ids"]) == particles and len(o["smc_log_w_tilde"]) == particles
     assert info["stats"]["resampled_groups"] > 0
+
+
+def test_lost_request_message_is_reported_not_waited_for():
+    """One request message is dropped on its way to the scheduler (injected on the host): with a time limit the caller
+    gets that request back as aborted, the others complete, and the engine keeps serving."""
+    sp = {"max_new_tokens": 8, "ignore_eos": True}
+    with SMCEngine("preset:tiny-target", "preset:tiny-draft", **_kw(in_process=False),
+                   _fault={"drop_request": 0}) as eng:
+        out = eng.generate(input_ids=_prompts(2), sampling_params=sp, timeout=6.0)
+        assert out[0].get("aborted") and "no answer" in out[0]["error"] and out[0]["completion_tokens"] == 0
+        assert not out[1].get("aborted") and out[1]["completion_tokens"] == 8
+        again = eng.generate(input_ids=_prompts(1, seed=3), sampling_params=sp, timeout=60.0)
+        assert again[0]["completion_tokens"] == 8 and not again[0].get("aborted")
