@@ -1,8 +1,10 @@
 """HTTP serving: ``python -m smcsd_b200.http_server --model ... --draft-model ... -N 8 -g 8``.
 
-Routes: ``/generate`` (native), ``/v1/completions`` and ``/v1/models`` (OpenAI style), ``/health``,
-``/health_generate``, ``/server_info`` (alias ``/get_server_info``), ``/get_model_info``,
-``/flush_cache``; ``"stream": true`` on the two generation routes answers as server-sent events.  Concurrent HTTP requests are multiplexed onto the SMC scheduler by a pump thread
+Routes: ``/generate`` (native; an optional ``rid`` names the request), ``/abort_request`` (by ``rid`` or
+``abort_all``), ``/v1/completions``, ``/v1/chat/completions`` (the tokenizer's chat template) and ``/v1/models``
+(OpenAI style), ``/health``, ``/health_generate``, ``/server_info`` (alias ``/get_server_info``),
+``/get_model_info``, ``/flush_cache``, ``/start_profile`` / ``/stop_profile``; ``"stream": true`` on the generation
+routes answers as server-sent events.  Concurrent HTTP requests are multiplexed onto the SMC scheduler by a pump thread
 that owns the engine: it feeds new requests into the scheduler between decode cycles and resolves
 each request's future when its group finalizes, so many clients share the batched decode loop.
 Same CLI flags and routes as the reference server (smcsd/http_server.py:140-212; the routes it
@@ -22,7 +24,7 @@ import uuid
 from typing import Any, Dict, List, Optional
 
 from .config import EngineArgs
-from .io_types import GenerateRequest, ParticleOutput, RequestOutput, SamplingParams
+from .io_types import AbortReq, GenerateRequest, ParticleOutput, RequestOutput, SamplingParams
 
 log = logging.getLogger("smcsd_b200.http")
 
@@ -50,12 +52,28 @@ class EngineBridge:
         self._stop.set()
         self.thread.join(timeout=10)
 
-    async def submit(self, input_ids: List[int], sp: SamplingParams) -> dict:
-        rid = uuid.uuid4().hex
+    async def submit(self, input_ids: List[int], sp: SamplingParams, rid: Optional[str] = None) -> dict:
+        rid = rid or uuid.uuid4().hex
+        if rid in self.futures:
+            raise ValueError(f"request id {rid!r} is already in flight")
         fut = self.loop.create_future()
         self.futures[rid] = fut
         req = GenerateRequest(rid, list(input_ids), sp, eos_token_ids=self.engine._eos_ids(), arrival_time=time.time())
         self.inbox.put(req)
+        return await fut
+
+    def abort(self, rid: Optional[str] = None) -> List[str]:
+        """Abort one request in flight (or all of them): the scheduler drops the group and answers it as aborted."""
+        rids = [rid] if rid is not None else list(self.futures)
+        rids = [r for r in rids if r in self.futures]
+        for r in rids:
+            self.inbox.put(AbortReq(r))
+        return rids
+
+    async def control(self, fn) -> Any:
+        """Run ``fn()`` on the pump thread (the only thread that may touch the engine) and return its result."""
+        fut = self.loop.create_future()
+        self.inbox.put((fn, fut))
         return await fut
 
     def _resolve(self, rid: str, result: dict) -> None:
@@ -79,6 +97,17 @@ class EngineBridge:
             self.n_served += 1
             self.loop.call_soon_threadsafe(self._resolve, o.rid, res)
 
+    def _run_control(self, fn, fut) -> None:
+        try:
+            res, err = fn(), None
+        except Exception as e:        # the caller gets the failure, the pump keeps serving
+            res, err = None, e
+
+        def done():
+            if not fut.done():
+                fut.set_exception(err) if err is not None else fut.set_result(res)
+        self.loop.call_soon_threadsafe(done)
+
     def _pump(self) -> None:
         eng = self.engine
         sched = eng._sched
@@ -89,7 +118,12 @@ class EngineBridge:
                     try:
                         while True:
                             req = self.inbox.get(timeout=0.02) if block else self.inbox.get_nowait()
-                            sched.add_request(req)
+                            if isinstance(req, AbortReq):
+                                sched.abort(req.rid)
+                            elif isinstance(req, tuple):
+                                self._run_control(*req)
+                            else:
+                                sched.add_request(req)
                             block = False
                     except queue.Empty:
                         pass
@@ -101,8 +135,14 @@ class EngineBridge:
                     try:
                         while True:
                             req = self.inbox.get_nowait()
-                            eng._tx[eng._rr].send_pyobj(req)
-                            eng._rr = (eng._rr + 1) % len(eng._tx)
+                            if isinstance(req, AbortReq):
+                                for tx in eng._tx:          # the replica that holds it answers; the others ignore it
+                                    tx.send_pyobj(req)
+                            elif isinstance(req, tuple):
+                                self._run_control(*req)
+                            else:
+                                eng._tx[eng._rr].send_pyobj(req)
+                                eng._rr = (eng._rr + 1) % len(eng._tx)
                     except queue.Empty:
                         pass
                     if eng._rx.poll(20):
@@ -158,16 +198,17 @@ def build_app(engine, model_name: str = "smc"):
     def _decode(ids: List[int]) -> str:
         return engine.tokenizer.decode(ids, skip_special_tokens=True) if engine.tokenizer is not None else ""
 
-    async def _one(ids: List[int], params: Optional[dict]) -> dict:
+    async def _one(ids: List[int], params: Optional[dict], rid: Optional[str] = None) -> dict:
         try:
             sp = SamplingParams.from_dict(params).normalize()
+            rid = rid or uuid.uuid4().hex
+            r = await bridge.submit(ids, sp, rid)
         except (TypeError, ValueError) as e:
             raise HTTPException(400, str(e))
-        r = await bridge.submit(ids, sp)
         if r["aborted"]:
             raise HTTPException(400, r["error"] or "request aborted")
         return {"text": _decode(r["output_ids"]), "output_ids": r["output_ids"],
-                "meta_info": {"id": uuid.uuid4().hex, "prompt_tokens": len(ids),
+                "meta_info": {"id": rid, "prompt_tokens": len(ids),
                               "completion_tokens": r["completion_tokens"], "finish_reason": r["finish_reason"],
                               "smc_log_Z_hat": r["smc_log_Z_hat"], "time_stats": r.get("time_stats")}}
 
@@ -181,17 +222,31 @@ def build_app(engine, model_name: str = "smc"):
         many = isinstance(src, list) and len(src) > 0 and isinstance(src[0], (list, str))
         items = src if many else [src]
         plist = params if isinstance(params, list) else [params] * len(items)
+        rid = body.get("rid")                                # caller-chosen id(s), usable with /abort_request
+        rids = rid if isinstance(rid, list) else [rid] * len(items) if (rid is None or not many) else None
+        if rids is None or len(rids) != len(items):
+            raise HTTPException(400, "rid must be one id per input")
         async def run():
-            outs = await asyncio.gather(*[_one(_encode(x), p) for x, p in zip(items, plist)])
+            outs = await asyncio.gather(*[_one(_encode(x), p, r) for x, p, r in zip(items, plist, rids)])
             return outs if many else outs[0]
         if body.get("stream"):
             encoded = [_encode(x) for x in items]          # malformed input fails before the stream opens
 
             async def run_stream():
-                outs = await asyncio.gather(*[_one(e, p) for e, p in zip(encoded, plist)])
+                outs = await asyncio.gather(*[_one(e, p, r) for e, p, r in zip(encoded, plist, rids)])
                 return outs if many else outs[0]
             return _sse(run_stream)
         return await run()
+
+    @app.post("/abort_request")
+    async def abort_request(body: Dict[str, Any]):
+        """``{"rid": id}`` aborts that request, ``{"abort_all": true}`` every request in flight; the aborted calls
+        answer with status 400 and the abort reason."""
+        if body.get("abort_all"):
+            return {"aborted": bridge.abort(None)}
+        if not body.get("rid"):
+            raise HTTPException(400, "send rid or abort_all")
+        return {"aborted": bridge.abort(str(body["rid"]))}
 
     @app.post("/v1/completions")
     async def completions(body: Dict[str, Any]):
@@ -220,6 +275,52 @@ def build_app(engine, model_name: str = "smc"):
         if body.get("stream"):
             return _sse(run)
         return await run()
+
+    def _chat_prompt(messages) -> List[int]:
+        tok = engine.tokenizer
+        if tok is None:
+            raise HTTPException(400, "this server has no tokenizer; chat completions need one")
+        if not isinstance(messages, list) or not messages or not all(isinstance(m, dict) for m in messages):
+            raise HTTPException(400, "messages must be a non-empty list of {role, content} objects")
+        if getattr(tok, "chat_template", None) and hasattr(tok, "apply_chat_template"):
+            ids = tok.apply_chat_template(messages, tokenize=True, add_generation_prompt=True)
+            return list(ids["input_ids"] if isinstance(ids, dict) else ids)
+        text = "".join(f"{m.get('role', 'user')}: {m.get('content', '')}\n" for m in messages) + "assistant:"
+        return list(tok.encode(text))
+
+    @app.post("/v1/chat/completions")
+    async def chat_completions(body: Dict[str, Any]):
+        ids = _chat_prompt(body.get("messages"))
+        params = {"max_new_tokens": int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
+                  "temperature": body.get("temperature", 1.0), "ignore_eos": bool(body.get("ignore_eos", False))}
+        if body.get("stop"):
+            params["stop"] = body["stop"]
+        if body.get("stop_token_ids"):
+            params["stop_token_ids"] = body["stop_token_ids"]
+
+        async def run():
+            o = await _one(ids, params)
+            fr = "length" if o["meta_info"]["finish_reason"]["type"] == "length" else "stop"
+            pt, ct = o["meta_info"]["prompt_tokens"], o["meta_info"]["completion_tokens"]
+            return {"id": "chatcmpl-" + uuid.uuid4().hex, "object": "chat.completion", "created": int(time.time()),
+                    "model": body.get("model", model_name),
+                    "choices": [{"index": 0, "message": {"role": "assistant", "content": o["text"]},
+                                 "finish_reason": fr}],
+                    "usage": {"prompt_tokens": pt, "completion_tokens": ct, "total_tokens": pt + ct}}
+        if body.get("stream"):
+            return _sse(run)
+        return await run()
+
+    @app.post("/start_profile")
+    async def start_profile(body: Optional[Dict[str, Any]] = None):
+        b = body or {}
+        kw = {k: b[k] for k in ("output_dir", "num_steps", "activities", "with_stack", "record_shapes",
+                                "profile_by_stage", "profile_stages") if k in b}
+        return {"result": await bridge.control(lambda: engine.start_profile(**kw))}
+
+    @app.post("/stop_profile")
+    async def stop_profile():
+        return {"result": await bridge.control(engine.stop_profile)}
 
     @app.get("/v1/models")
     async def models():

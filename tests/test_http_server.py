@@ -8,6 +8,13 @@ import requests
 import torch
 
 
+_ENGINE = []
+
+
+def server_app_engine():
+    return _ENGINE[-1]
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -23,6 +30,7 @@ def server():
     eng = SMCEngine("preset:tiny-target", "preset:tiny-draft", n_particles=4, gamma=4, dtype="float32", device="cpu",
                     max_running_requests=4, draft_temperature=0.7, target_temperature=0.7)
     app = build_app(eng, "tiny")
+    _ENGINE.append(eng)
     port = _free_port()
     cfg = uvicorn.Config(app, host="127.0.0.1", port=port, log_level="warning")
     srv = uvicorn.Server(cfg)
@@ -94,3 +102,57 @@ def test_streaming_routes_answer_as_server_sent_events(server):
         assert n == 6
     m = requests.get(server + "/server_info", timeout=10).json()["metrics"]
     assert 0.0 <= m["kv_occupancy"] <= 1.0 and m["decode_cycles"] >= 1
+
+
+class _StubTokenizer:
+    """Byte-level stand-in: enough of the tokenizer surface for the text routes."""
+    chat_template = None
+
+    def encode(self, text):
+        return [ord(c) % 4096 for c in text]
+
+    def decode(self, ids, skip_special_tokens=True):
+        return "".join(chr(97 + int(t) % 26) for t in ids)
+
+
+def test_abort_request_by_rid(server):
+    out = {}
+
+    def call():
+        out["r"] = requests.post(server + "/generate", json={
+            "input_ids": [9, 8, 7, 6, 5], "rid": "long-1",
+            "sampling_params": {"max_new_tokens": 900, "ignore_eos": True}}, timeout=300)
+    t = threading.Thread(target=call)
+    t.start()
+    time.sleep(0.5)
+    a = requests.post(server + "/abort_request", json={"rid": "long-1"}, timeout=10)
+    assert a.status_code == 200 and a.json()["aborted"] == ["long-1"]
+    t.join(timeout=60)
+    assert not t.is_alive() and out["r"].status_code == 400
+    # an id that is not in flight aborts nothing; the server keeps serving
+    assert requests.post(server + "/abort_request", json={"rid": "nobody"}, timeout=10).json()["aborted"] == []
+    assert requests.post(server + "/abort_request", json={}, timeout=10).status_code == 400
+    ok = requests.post(server + "/generate", json={"input_ids": [1, 2, 3], "rid": "short-1",
+                                                   "sampling_params": {"max_new_tokens": 5, "ignore_eos": True}}, timeout=120)
+    assert ok.status_code == 200 and ok.json()["meta_info"]["id"] == "short-1"
+
+
+def test_chat_completions_and_profile_routes(server, tmp_path):
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}]
+    assert requests.post(server + "/v1/chat/completions", json={"messages": msgs}, timeout=10).status_code == 400
+    server_app_engine().tokenizer = _StubTokenizer()
+    try:
+        r = requests.post(server + "/v1/chat/completions", json={"messages": msgs, "max_tokens": 6, "ignore_eos": True},
+                          timeout=120)
+        j = r.json()
+        assert r.status_code == 200 and j["object"] == "chat.completion"
+        assert j["choices"][0]["message"]["role"] == "assistant" and len(j["choices"][0]["message"]["content"]) == 6
+        assert j["usage"]["completion_tokens"] == 6 and j["usage"]["prompt_tokens"] > 10
+        assert requests.post(server + "/v1/chat/completions", json={"messages": "hi"}, timeout=10).status_code == 400
+    finally:
+        server_app_engine().tokenizer = None
+    s = requests.post(server + "/start_profile", json={"output_dir": str(tmp_path), "activities": ["CPU"]}, timeout=30)
+    assert s.status_code == 200 and s.json()["result"][0]["ok"]
+    requests.post(server + "/generate", json={"input_ids": [4, 5, 6], "sampling_params": {"max_new_tokens": 6, "ignore_eos": True}}, timeout=120)
+    e = requests.post(server + "/stop_profile", timeout=60)
+    assert e.status_code == 200 and e.json()["result"][0]["ok"]
