@@ -75,6 +75,8 @@ class EngineArgs:
     # ---- serving ------------------------------------------------------------
     max_running_requests: int = 8       # user-facing concurrent groups
     max_queued_requests: Optional[int] = None
+    enable_priority_scheduling: bool = False          # requests may carry a priority; the waiting queue is ordered by it
+    schedule_low_priority_values_first: bool = False  # smaller numbers are served first (default: larger first)
     mem_fraction_static: float = 0.6
     max_total_tokens: Optional[int] = None
     kv_cache_dtype: str = "auto"
@@ -168,6 +170,8 @@ class EngineArgs:
         p.add_argument("--mem-fraction-static", type=float, default=0.4)
         p.add_argument("--max-running-requests", type=int, default=8)
         p.add_argument("--max-queued-requests", type=int, default=None)
+        p.add_argument("--enable-priority-scheduling", action="store_true")
+        p.add_argument("--schedule-low-priority-values-first", action="store_true")
         p.add_argument("--max-total-tokens", type=int, default=None)
         p.add_argument("--context-length", type=int, default=None)
         p.add_argument("--cuda-graph-max-bs", type=int, default=None)

@@ -72,6 +72,9 @@ class SMCEngine:
             self._rx = self._zmq.socket(zmq.PULL)
             self._rx.bind(f"tcp://127.0.0.1:{self.ports.result_port}")
             self._rpc = self._zmq.socket(zmq.ROUTER)
+            # a ROUTER silently drops a message for a peer whose connection handshake has not finished (a call right
+            # after start-up); with this option the send fails instead and is retried
+            self._rpc.setsockopt(zmq.ROUTER_MANDATORY, 1)
             self._rpc.bind(f"tcp://127.0.0.1:{self.ports.rpc_port}")
             self._crashed = False
             try:
@@ -146,6 +149,9 @@ class SMCEngine:
                 self._sched.add_request(r)
             pending = set(rids)
             while pending:
+                if self._sched.paused:
+                    raise RuntimeError("generation is paused (continue_generation() resumes it); an in-process "
+                                       "scheduler cannot serve generate() meanwhile")
                 for o in self._sched.step():
                     self._absorb(o, results, particles, pending)
                 if not self._sched.has_work() and pending:
@@ -227,10 +233,19 @@ class SMCEngine:
                 return [self._sched.handle_profile(msg)]
             return [self._sched.handle_rpc(msg)]
         leaders = [f"sched-{r * self.args.tp_size * self.args.pp_size}".encode() for r in range(self.args.dp_size)]
-        for ident in leaders:
-            self._rpc.send_multipart([ident, pickle.dumps(msg)])
-        out = []
+        import zmq
         deadline = time.time() + timeout
+        for ident in leaders:
+            while True:
+                try:
+                    self._rpc.send_multipart([ident, pickle.dumps(msg)])
+                    break
+                except zmq.ZMQError as e:
+                    if e.errno != zmq.EHOSTUNREACH or time.time() > deadline:
+                        raise
+                    self._check_children()
+                    time.sleep(0.01)             # the scheduler's control socket is still connecting
+        out = []
         while len(out) < len(leaders):
             if self._rpc.poll(200) == 0:
                 self._check_children()
@@ -252,6 +267,14 @@ class SMCEngine:
 
     def stop_profile(self):
         return self._rpc_roundtrip(ProfileReq("stop"))
+
+    def pause_generation(self):
+        """Every scheduler finishes the cycle in flight and then neither admits nor advances groups until
+        ``continue_generation``; requests sent meanwhile wait in the queue."""
+        return self.collective_rpc("pause_generation")
+
+    def continue_generation(self):
+        return self.collective_rpc("continue_generation")
 
     def collective_rpc(self, method: str, **kwargs):
         return self._rpc_roundtrip(RpcReq(method, kwargs, req_id=int(time.time_ns() & 0x7FFFFFFF)))

@@ -3,7 +3,8 @@
 Routes: ``/generate`` (native; an optional ``rid`` names the request), ``/abort_request`` (by ``rid`` or
 ``abort_all``), ``/v1/completions``, ``/v1/chat/completions`` (the tokenizer's chat template) and ``/v1/models``
 (OpenAI style), ``/health``, ``/health_generate``, ``/server_info`` (alias ``/get_server_info``),
-``/get_model_info``, ``/flush_cache``, ``/start_profile`` / ``/stop_profile``; ``"stream": true`` on the generation
+``/get_model_info``, ``/flush_cache``, ``/pause_generation`` / ``/continue_generation``, ``/start_profile`` /
+``/stop_profile``; ``"stream": true`` on the generation
 routes answers as server-sent events.  Concurrent HTTP requests are multiplexed onto the SMC scheduler by a pump thread
 that owns the engine: it feeds new requests into the scheduler between decode cycles and resolves
 each request's future when its group finalizes, so many clients share the batched decode loop.
@@ -52,13 +53,15 @@ class EngineBridge:
         self._stop.set()
         self.thread.join(timeout=10)
 
-    async def submit(self, input_ids: List[int], sp: SamplingParams, rid: Optional[str] = None) -> dict:
+    async def submit(self, input_ids: List[int], sp: SamplingParams, rid: Optional[str] = None,
+                     priority: Optional[int] = None) -> dict:
         rid = rid or uuid.uuid4().hex
         if rid in self.futures:
             raise ValueError(f"request id {rid!r} is already in flight")
         fut = self.loop.create_future()
         self.futures[rid] = fut
-        req = GenerateRequest(rid, list(input_ids), sp, eos_token_ids=self.engine._eos_ids(), arrival_time=time.time())
+        req = GenerateRequest(rid, list(input_ids), sp, eos_token_ids=self.engine._eos_ids(), arrival_time=time.time(),
+                              priority=priority)
         self.inbox.put(req)
         return await fut
 
@@ -198,11 +201,12 @@ def build_app(engine, model_name: str = "smc"):
     def _decode(ids: List[int]) -> str:
         return engine.tokenizer.decode(ids, skip_special_tokens=True) if engine.tokenizer is not None else ""
 
-    async def _one(ids: List[int], params: Optional[dict], rid: Optional[str] = None) -> dict:
+    async def _one(ids: List[int], params: Optional[dict], rid: Optional[str] = None,
+                   priority: Optional[int] = None) -> dict:
         try:
             sp = SamplingParams.from_dict(params).normalize()
             rid = rid or uuid.uuid4().hex
-            r = await bridge.submit(ids, sp, rid)
+            r = await bridge.submit(ids, sp, rid, None if priority is None else int(priority))
         except (TypeError, ValueError) as e:
             raise HTTPException(400, str(e))
         if r["aborted"]:
@@ -226,14 +230,15 @@ def build_app(engine, model_name: str = "smc"):
         rids = rid if isinstance(rid, list) else [rid] * len(items) if (rid is None or not many) else None
         if rids is None or len(rids) != len(items):
             raise HTTPException(400, "rid must be one id per input")
+        prio = body.get("priority")                          # honoured with --enable-priority-scheduling only
         async def run():
-            outs = await asyncio.gather(*[_one(_encode(x), p, r) for x, p, r in zip(items, plist, rids)])
+            outs = await asyncio.gather(*[_one(_encode(x), p, r, prio) for x, p, r in zip(items, plist, rids)])
             return outs if many else outs[0]
         if body.get("stream"):
             encoded = [_encode(x) for x in items]          # malformed input fails before the stream opens
 
             async def run_stream():
-                outs = await asyncio.gather(*[_one(e, p, r) for e, p, r in zip(encoded, plist, rids)])
+                outs = await asyncio.gather(*[_one(e, p, r, prio) for e, p, r in zip(encoded, plist, rids)])
                 return outs if many else outs[0]
             return _sse(run_stream)
         return await run()
@@ -310,6 +315,18 @@ def build_app(engine, model_name: str = "smc"):
         if body.get("stream"):
             return _sse(run)
         return await run()
+
+    @app.post("/pause_generation")
+    async def pause_generation():
+        """The cycle in flight completes, then nothing is admitted or advanced until ``/continue_generation``;
+        requests sent meanwhile wait in the queue (their HTTP calls stay open)."""
+        await bridge.control(engine.pause_generation)
+        return {"paused": True}
+
+    @app.post("/continue_generation")
+    async def continue_generation():
+        await bridge.control(engine.continue_generation)
+        return {"paused": False}
 
     @app.post("/start_profile")
     async def start_profile(body: Optional[Dict[str, Any]] = None):

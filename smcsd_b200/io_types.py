@@ -54,6 +54,7 @@ class GenerateRequest:
     image_data: Any = None
     grammar: Any = None
     arrival_time: float = 0.0
+    priority: Optional[int] = None     # only with priority scheduling switched on (otherwise the request is refused)
 
 
 @dataclass

@@ -155,6 +155,8 @@ def run_scheduler_process(args: EngineArgs, rank: int, world: int, ports: PortAr
             if stop:
                 break
             outs = sched.step() if (sched.has_work() or msgs) else []
+            if sched.paused and not msgs:
+                time.sleep(0.005)                   # paused with work queued: wait for the next message, do not spin
             if leader:
                 for o in outs:
                     tx.send_pyobj(o)

@@ -177,6 +177,7 @@ class SMCScheduler:
         self.last_free_pages = self.min_free_pages = self.alloc.size
         self._log_alloc_retries = os.environ.get("SMC_LOG_ALLOC_RETRIES") == "1" and self.device.type == "cuda"
         self._alloc_retries_seen = 0
+        self.paused = False
         self.pending: Deque = deque()       # snapshots awaiting host post-processing
         self.outbox: List = []
         self.final_gen = torch.Generator().manual_seed(seed * 31 + 5)
@@ -246,12 +247,31 @@ class SMCScheduler:
         if err is None and self.args.max_queued_requests is not None and \
                 len(self.waiting) >= self.args.max_queued_requests:
             err = "the request queue is full"
+        prio = getattr(req, "priority", None)
+        if err is None and prio is not None and not self.args.enable_priority_scheduling:
+            # same rule as the reference's scheduler base (smcsd/core/scheduler.py:576-577)
+            err = "using priority is disabled for this server; send the request without a priority"
         if err is not None:
             self.stats["aborted"] += 1
             self.outbox.append(RequestOutput(req.rid, [], True, {"type": "abort", "message": err},
                                              len(req.input_ids), 0, aborted=True, error=err))
             return
-        self.waiting.append(SequenceGroup(req, self.args.n_particles, t_arrive=time.time()))
+        g = SequenceGroup(req, self.args.n_particles, t_arrive=time.time())
+        if not self.args.enable_priority_scheduling:
+            self.waiting.append(g)
+            return
+        # ordered insert: more urgent groups first, arrival order among equals; a request without a priority is the
+        # least urgent.  Admission always takes the head, so a large urgent request is not overtaken by smaller ones.
+        low_first = self.args.schedule_low_priority_values_first
+        key = (lambda p: p if p is not None else float("inf")) if low_first else \
+              (lambda p: -p if p is not None else float("inf"))
+        k = key(prio)
+        at = len(self.waiting)
+        for i, other in enumerate(self.waiting):
+            if key(getattr(other.req, "priority", None)) > k:
+                at = i
+                break
+        self.waiting.insert(at, g)
 
     def abort(self, rid: str) -> None:
         for g in list(self.waiting):
@@ -270,6 +290,17 @@ class SMCScheduler:
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.running or self.pending)
+
+    def pause_generation(self) -> bool:
+        """Stop admitting and advancing groups after the cycle in flight (the snapshot queue is drained first, so a
+        paused scheduler holds no unprocessed device results).  Requests that arrive meanwhile wait in the queue."""
+        self._flush_pending()
+        self.paused = True
+        return True
+
+    def continue_generation(self) -> bool:
+        self.paused = False
+        return True
 
     # ------------------------------------------------------------------ admission
     def _pages_needed(self, g: SequenceGroup) -> int:
@@ -477,6 +508,10 @@ class SMCScheduler:
         which is harmless because finished particles are absorbing)."""
         if self.profiler is not None:
             self._profile_tick()
+        if self.paused:
+            # generation is paused: requests keep arriving (and can be aborted), nothing is admitted or advanced
+            out, self.outbox = self.outbox, []
+            return out
         admitted = self._admit()
         if self.profiler is not None and (admitted or self.running):
             self.profiler.enter_stage("prefill" if admitted else "decode")
@@ -500,6 +535,8 @@ class SMCScheduler:
     def run_until_idle(self) -> List:
         outs: List = []
         while self.has_work():
+            if self.paused:
+                raise RuntimeError("generation is paused; continue_generation() first")
             outs.extend(self.step())
         outs.extend(self.step())
         return outs
@@ -551,7 +588,8 @@ class SMCScheduler:
     def server_info(self) -> dict:
         return dict(args=self.args.to_dict(), backend=self.backend, device=str(self.device),
                     kv_pages=self.alloc.size, context_len=self.context_len, stats=dict(self.stats),
-                    n_running=len(self.running), n_waiting=len(self.waiting), metrics=self.metrics(),
+                    n_running=len(self.running), n_waiting=len(self.waiting), paused=self.paused,
+                    metrics=self.metrics(),
                     target=self.target.cfg.name, draft=self.draft.cfg.name)
 
     def flush_cache(self) -> bool:

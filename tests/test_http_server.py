@@ -156,3 +156,23 @@ def test_chat_completions_and_profile_routes(server, tmp_path):
     requests.post(server + "/generate", json={"input_ids": [4, 5, 6], "sampling_params": {"max_new_tokens": 6, "ignore_eos": True}}, timeout=120)
     e = requests.post(server + "/stop_profile", timeout=60)
     assert e.status_code == 200 and e.json()["result"][0]["ok"]
+
+
+def test_pause_continue_and_priority_over_http(server):
+    assert requests.post(server + "/pause_generation", timeout=30).json() == {"paused": True}
+    out = {}
+
+    def call():
+        out["r"] = requests.post(server + "/generate", json={
+            "input_ids": [2, 3, 4], "sampling_params": {"max_new_tokens": 5, "ignore_eos": True}}, timeout=120)
+    t = threading.Thread(target=call)
+    t.start()
+    time.sleep(1.0)
+    assert t.is_alive()                       # queued, not served, while paused
+    assert requests.post(server + "/continue_generation", timeout=30).json() == {"paused": False}
+    t.join(timeout=60)
+    assert not t.is_alive() and out["r"].status_code == 200 and out["r"].json()["meta_info"]["completion_tokens"] == 5
+    # this server runs without priority scheduling: a request that carries a priority is refused with a message
+    bad = requests.post(server + "/generate", json={"input_ids": [2, 3, 4], "priority": 2,
+                                                    "sampling_params": {"max_new_tokens": 5}}, timeout=60)
+    assert bad.status_code == 400 and "priority" in bad.json()["detail"]

@@ -109,3 +109,16 @@ def test_lost_request_message_is_reported_not_waited_for():
         assert not out[1].get("aborted") and out[1]["completion_tokens"] == 8
         again = eng.generate(input_ids=_prompts(1, seed=3), sampling_params=sp, timeout=60.0)
         assert again[0]["completion_tokens"] == 8 and not again[0].get("aborted")
+
+
+def test_pause_and_continue_reach_the_scheduler_process():
+    sp = {"max_new_tokens": 6, "ignore_eos": True}
+    with SMCEngine("preset:tiny-target", "preset:tiny-draft", **_kw(in_process=False)) as eng:
+        eng.pause_generation()
+        assert eng.get_server_info()["paused"] is True
+        out = eng.generate(input_ids=_prompts(1), sampling_params=sp, timeout=2.0)     # nothing is served while paused
+        assert out[0].get("aborted")
+        eng.continue_generation()
+        assert eng.get_server_info()["paused"] is False
+        out = eng.generate(input_ids=_prompts(1), sampling_params=sp, timeout=60.0)
+        assert out[0]["completion_tokens"] == 6 and not out[0].get("aborted")

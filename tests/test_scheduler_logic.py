@@ -178,3 +178,41 @@ def test_request_at_the_context_limit_survives_the_extra_overlap_cycle():
     done = [o for o in outs if isinstance(o, RequestOutput)]
     assert len(done) == 2 and not any(o.aborted for o in done)
     s.check_idle_invariants()
+
+
+def test_priority_is_refused_unless_switched_on_and_orders_the_queue():
+    s = _sched()
+    r = _req("p", max_new_tokens=8, ignore_eos=True)
+    r.priority = 3
+    s.add_request(r)
+    assert any(isinstance(o, RequestOutput) and o.aborted and "priority" in o.error for o in s.outbox)
+    for low_first, want in ((False, ["hi", "mid", "mid2", "lo", "none"]), (True, ["lo", "mid", "mid2", "hi", "none"])):
+        s = _sched(enable_priority_scheduling=True, schedule_low_priority_values_first=low_first,
+                   max_running_requests=1)
+        for rid, prio in (("mid", 5), ("none", None), ("lo", 1), ("hi", 9), ("mid2", 5)):
+            r = _req(rid, max_new_tokens=6, ignore_eos=True)
+            r.priority = prio
+            s.add_request(r)
+        assert [g.rid for g in s.waiting] == want
+        done = [o.rid for o in s.run_until_idle() if isinstance(o, RequestOutput) and o.finished]
+        assert done == want                   # one group at a time: served in queue order
+        s.check_idle_invariants()
+
+
+def test_pause_holds_the_queue_and_continue_resumes():
+    s = _sched()
+    s.add_request(_req("a", max_new_tokens=12, ignore_eos=True))
+    s.step()                                  # prefill
+    s.step()
+    cycles = s.stats["cycles"]
+    assert s.pause_generation() and not s.pending
+    s.add_request(_req("b", max_new_tokens=6, ignore_eos=True))
+    for _ in range(5):
+        assert all(not (isinstance(o, RequestOutput) and o.finished) for o in s.step())
+    assert s.stats["cycles"] == cycles and len(s.waiting) == 1 and s.has_work()
+    s.abort("b")                              # still possible while paused
+    assert any(isinstance(o, RequestOutput) and o.rid == "b" and o.aborted for o in s.step())
+    s.continue_generation()
+    outs = s.run_until_idle()
+    assert any(isinstance(o, RequestOutput) and o.rid == "a" and o.completion_tokens == 12 for o in outs)
+    s.check_idle_invariants()
