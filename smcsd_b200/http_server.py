@@ -24,6 +24,11 @@ import time
 import uuid
 from typing import Any, Dict, List, Optional
 
+try:                                     # route signatures name this type; annotations are resolved at module level
+    from fastapi import Request
+except ImportError:                      # the offline engine works without the HTTP stack
+    Request = Any
+
 from .config import EngineArgs
 from .io_types import AbortReq, GenerateRequest, ParticleOutput, RequestOutput, SamplingParams
 
@@ -202,11 +207,18 @@ def build_app(engine, model_name: str = "smc"):
         return engine.tokenizer.decode(ids, skip_special_tokens=True) if engine.tokenizer is not None else ""
 
     async def _one(ids: List[int], params: Optional[dict], rid: Optional[str] = None,
-                   priority: Optional[int] = None) -> dict:
+                   priority: Optional[int] = None, http: Optional[Request] = None) -> dict:
         try:
             sp = SamplingParams.from_dict(params).normalize()
             rid = rid or uuid.uuid4().hex
-            r = await bridge.submit(ids, sp, rid, None if priority is None else int(priority))
+            task = asyncio.ensure_future(bridge.submit(ids, sp, rid, None if priority is None else int(priority)))
+            while http is not None and not task.done():
+                # a client that hung up frees its slots and pages now, not when its generation would have ended
+                await asyncio.wait([task], timeout=0.25)
+                if not task.done() and await http.is_disconnected():
+                    bridge.abort(rid)
+                    http = None                       # aborted once; the scheduler's answer ends the wait
+            r = await task
         except (TypeError, ValueError) as e:
             raise HTTPException(400, str(e))
         if r["aborted"]:
@@ -217,7 +229,7 @@ def build_app(engine, model_name: str = "smc"):
                               "smc_log_Z_hat": r["smc_log_Z_hat"], "time_stats": r.get("time_stats")}}
 
     @app.post("/generate")
-    async def generate(body: Dict[str, Any]):
+    async def generate(body: Dict[str, Any], request: Request):
         text, ids = body.get("text"), body.get("input_ids")
         if (text is None) == (ids is None):
             raise HTTPException(400, "send exactly one of text / input_ids")
@@ -232,13 +244,13 @@ def build_app(engine, model_name: str = "smc"):
             raise HTTPException(400, "rid must be one id per input")
         prio = body.get("priority")                          # honoured with --enable-priority-scheduling only
         async def run():
-            outs = await asyncio.gather(*[_one(_encode(x), p, r, prio) for x, p, r in zip(items, plist, rids)])
+            outs = await asyncio.gather(*[_one(_encode(x), p, r, prio, request) for x, p, r in zip(items, plist, rids)])
             return outs if many else outs[0]
         if body.get("stream"):
             encoded = [_encode(x) for x in items]          # malformed input fails before the stream opens
 
             async def run_stream():
-                outs = await asyncio.gather(*[_one(e, p, r, prio) for e, p, r in zip(encoded, plist, rids)])
+                outs = await asyncio.gather(*[_one(e, p, r, prio, request) for e, p, r in zip(encoded, plist, rids)])
                 return outs if many else outs[0]
             return _sse(run_stream)
         return await run()
@@ -254,7 +266,7 @@ def build_app(engine, model_name: str = "smc"):
         return {"aborted": bridge.abort(str(body["rid"]))}
 
     @app.post("/v1/completions")
-    async def completions(body: Dict[str, Any]):
+    async def completions(body: Dict[str, Any], request: Request):
         prompt = body.get("prompt")
         if prompt is None:
             raise HTTPException(400, "prompt is required")
@@ -268,7 +280,7 @@ def build_app(engine, model_name: str = "smc"):
         encoded = [_encode(p) for p in prompts]
 
         async def run():
-            outs = await asyncio.gather(*[_one(e, params) for e in encoded])
+            outs = await asyncio.gather(*[_one(e, params, http=request) for e in encoded])
             choices = [{"index": i, "text": o["text"], "token_ids": o["output_ids"],
                         "finish_reason": "length" if o["meta_info"]["finish_reason"]["type"] == "length" else "stop"}
                        for i, o in enumerate(outs)]
@@ -294,7 +306,7 @@ def build_app(engine, model_name: str = "smc"):
         return list(tok.encode(text))
 
     @app.post("/v1/chat/completions")
-    async def chat_completions(body: Dict[str, Any]):
+    async def chat_completions(body: Dict[str, Any], request: Request):
         ids = _chat_prompt(body.get("messages"))
         params = {"max_new_tokens": int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
                   "temperature": body.get("temperature", 1.0), "ignore_eos": bool(body.get("ignore_eos", False))}
@@ -304,7 +316,7 @@ def build_app(engine, model_name: str = "smc"):
             params["stop_token_ids"] = body["stop_token_ids"]
 
         async def run():
-            o = await _one(ids, params)
+            o = await _one(ids, params, http=request)
             fr = "length" if o["meta_info"]["finish_reason"]["type"] == "length" else "stop"
             pt, ct = o["meta_info"]["prompt_tokens"], o["meta_info"]["completion_tokens"]
             return {"id": "chatcmpl-" + uuid.uuid4().hex, "object": "chat.completion", "created": int(time.time()),

@@ -176,3 +176,16 @@ def test_pause_continue_and_priority_over_http(server):
     bad = requests.post(server + "/generate", json={"input_ids": [2, 3, 4], "priority": 2,
                                                     "sampling_params": {"max_new_tokens": 5}}, timeout=60)
     assert bad.status_code == 400 and "priority" in bad.json()["detail"]
+
+
+def test_client_that_hangs_up_frees_its_group(server):
+    with pytest.raises(requests.exceptions.ReadTimeout):
+        requests.post(server + "/generate", json={"input_ids": [7, 7, 7, 7], "sampling_params": {
+            "max_new_tokens": 900, "ignore_eos": True}}, timeout=0.6)
+    for _ in range(40):                       # the disconnect is noticed within a poll interval, then the group goes
+        info = requests.get(server + "/server_info", timeout=10).json()
+        if info["n_running"] == 0 and info["n_waiting"] == 0:
+            break
+        time.sleep(0.1)
+    assert info["n_running"] == 0 and info["n_waiting"] == 0
+    assert info["stats"]["aborted"] >= 1
