@@ -3,7 +3,7 @@
 Routes: ``/generate`` (native; an optional ``rid`` names the request), ``/abort_request`` (by ``rid`` or
 ``abort_all``), ``/v1/completions``, ``/v1/chat/completions`` (the tokenizer's chat template) and ``/v1/models``
 (OpenAI style), ``/health``, ``/health_generate``, ``/server_info`` (alias ``/get_server_info``),
-``/get_model_info``, ``/flush_cache``, ``/pause_generation`` / ``/continue_generation``, ``/start_profile`` /
+``/metrics`` (Prometheus text), ``/get_model_info``, ``/flush_cache``, ``/pause_generation`` / ``/continue_generation``, ``/start_profile`` /
 ``/stop_profile``; ``"stream": true`` on the generation
 routes answers as server-sent events.  Concurrent HTTP requests are multiplexed onto the SMC scheduler by a pump thread
 that owns the engine: it feeds new requests into the scheduler between decode cycles and resolves
@@ -365,10 +365,10 @@ def build_app(engine, model_name: str = "smc"):
         await _one(vocab_ok, {"max_new_tokens": 2, "ignore_eos": True})
         return JSONResponse({"status": "ok"})
 
-    def _info() -> dict:
-        info = dict(engine.scheduler_info[0]) if engine.scheduler_info else {}
-        if engine._sched is not None:
-            info = engine._sched.server_info()
+    async def _info() -> dict:
+        # read on the pump thread, the only one that may touch the scheduler or the control socket; with scheduler
+        # processes this is a live round trip to the first replica, not the record taken at start-up
+        info = dict(await bridge.control(engine.get_server_info))
         info["n_served"] = bridge.n_served
         info["smc"] = {"n_particles": engine.args.n_particles, "gamma": engine.args.gamma,
                        "draft_temperature": engine.args.draft_temperature,
@@ -378,11 +378,35 @@ def build_app(engine, model_name: str = "smc"):
 
     @app.get("/server_info")
     async def server_info():
-        return _info()
+        return await _info()
 
     @app.get("/get_server_info")
     async def get_server_info():
-        return _info()
+        return await _info()
+
+    @app.get("/metrics")
+    async def metrics():
+        """Prometheus text exposition of the serving gauges and counters."""
+        from fastapi.responses import PlainTextResponse
+        info = await _info()
+        m, st = info.get("metrics", {}), info.get("stats", {})
+        rows = [("num_running_reqs", "gauge", "request groups being decoded", info.get("n_running", 0)),
+                ("num_queue_reqs", "gauge", "request groups waiting for admission", info.get("n_waiting", 0)),
+                ("kv_occupancy", "gauge", "fraction of KV pages in use after the last cycle", m.get("kv_occupancy", 0.0)),
+                ("kv_occupancy_peak", "gauge", "highest KV page occupancy seen", m.get("kv_occupancy_peak", 0.0)),
+                ("kv_pages_reserved", "gauge", "KV pages reserved for running groups", m.get("kv_pages_reserved", 0)),
+                ("resample_rate", "gauge", "resampling steps per group and decode cycle", m.get("resample_rate", 0.0)),
+                ("decode_cycles_total", "counter", "decode cycles run", m.get("decode_cycles", 0)),
+                ("decode_tokens_total", "counter", "tokens advanced over all particles", m.get("decode_tokens", 0)),
+                ("prefills_total", "counter", "prompts prefilled", st.get("prefills", 0)),
+                ("requests_finished_total", "counter", "requests finished", st.get("finished", 0)),
+                ("requests_aborted_total", "counter", "requests aborted", st.get("aborted", 0)),
+                ("requests_served_total", "counter", "HTTP generations answered", info.get("n_served", 0))]
+        cyc = m.get("cycle_ms") or {}
+        if isinstance(cyc, dict) and cyc.get("ms_mean") is not None:
+            rows.append(("decode_cycle_ms", "gauge", "device-timed milliseconds per decode cycle (mean)", cyc["ms_mean"]))
+        text = "".join(f"# HELP smcsd:{n} {h}\n# TYPE smcsd:{n} {t}\nsmcsd:{n} {float(v):g}\n" for n, t, h, v in rows)
+        return PlainTextResponse(text, media_type="text/plain; version=0.0.4")
 
     @app.get("/get_model_info")
     async def model_info():

@@ -189,3 +189,12 @@ def test_client_that_hangs_up_frees_its_group(server):
         time.sleep(0.1)
     assert info["n_running"] == 0 and info["n_waiting"] == 0
     assert info["stats"]["aborted"] >= 1
+
+
+def test_metrics_route_is_prometheus_text(server):
+    r = requests.get(server + "/metrics", timeout=10)
+    assert r.status_code == 200 and r.headers["content-type"].startswith("text/plain")
+    vals = {ln.split()[0]: float(ln.split()[1]) for ln in r.text.splitlines() if ln and not ln.startswith("#")}
+    assert vals["smcsd:decode_cycles_total"] >= 1 and vals["smcsd:requests_finished_total"] >= 1
+    assert 0.0 <= vals["smcsd:kv_occupancy"] <= 1.0 and vals["smcsd:num_running_reqs"] == 0
+    assert "# TYPE smcsd:decode_tokens_total counter" in r.text
