@@ -166,6 +166,7 @@ class SMCScheduler:
             raise ValueError("the fused resampling kernels implement 'systematic' only")
         if self.native_runner is not None:
             self.native_runner.st = self.state
+            self.state.device_status = self.native_runner.status      # travels with every cycle snapshot
         self.worker = SMCWorker(a, self.target, self.draft, self.kv_t, self.kv_d, self.bt, self.alloc,
                                 self.state_t, self.state_d, native_runner=self.native_runner, noise_rank=pp_rank)
         if pp_size > 1:
@@ -441,7 +442,9 @@ class SMCScheduler:
         self.stats["group_cycles"] = self.stats.get("group_cycles", 0) + len(self.running)
         self.stats["decode_tokens"] += st.bs * (self.args.gamma + 1)
         snap = st.snapshot_to_host()
-        self.io_bytes["d2h"] += snap.finished.numel() + 8
+        # finished flags, free-page count, allocator flag, resample counter, (status word), (per-group running counts)
+        self.io_bytes["d2h"] += snap.finished.numel() + 16 + (4 if st.device_status is not None else 0) + \
+            (4 * st.max_groups if st.pp is not None else 0)
         for g in self.running.values():
             g.launched += 1
         self.pending.append((snap, list(self.running.keys())))
@@ -450,9 +453,10 @@ class SMCScheduler:
         snap.wait()
         if snap.alloc_error:
             raise RuntimeError("device page allocator ran dry inside a decode cycle")
-        if snap.peer_status:
-            raise RuntimeError(f"particle-parallel resampling reported device status {snap.peer_status} "
-                               "(2: a rank's weights did not arrive in time, 8: a peer's slot failed its range check)")
+        if snap.device_status:
+            raise RuntimeError(f"the kernels reported device status {snap.device_status} in a decode cycle (bit 1: a wait "
+                               "on an mbarrier ran out, 2: a wait on another rank ran out, 4: the page allocator ran "
+                               "dry, 8: an index failed its range check)")
         self.last_free_pages = snap.free_pages
         self.min_free_pages = min(self.min_free_pages, snap.free_pages)
         if self.native_runner is not None:

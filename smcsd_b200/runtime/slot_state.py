@@ -52,7 +52,7 @@ class HostSnapshot:
     def __init__(self, n_slots: int, device: torch.device):
         pin = device.type == "cuda"
         self.finished = torch.zeros(n_slots, dtype=torch.bool, pin_memory=pin)
-        self.scalars = torch.zeros(4, dtype=torch.int32, pin_memory=pin)   # free_count, alloc_error, peer status, -
+        self.scalars = torch.zeros(4, dtype=torch.int32, pin_memory=pin)   # free_count, alloc_error, device status, -
         self.resampled = torch.zeros(1, dtype=torch.int64, pin_memory=pin)   # cumulative count of resampled groups
         self.group_active = None            # [max_groups] running particles per group over all ranks (particle-parallel)
         self.event = torch.cuda.Event() if pin else None
@@ -70,8 +70,8 @@ class HostSnapshot:
         return bool(self.scalars[1])
 
     @property
-    def peer_status(self) -> int:
-        """Status word of the cross-rank resampling kernels (0: every wait on a peer was answered)."""
+    def device_status(self) -> int:
+        """Status word of the kernels as of this cycle (0: no wait ran out, no index failed its check)."""
         return int(self.scalars[2])
 
 
@@ -116,6 +116,7 @@ class SlotState:
         self.group_log_Z = torch.zeros(max_groups, dtype=torch.float64, device=dev)
         self.group_active = torch.zeros(max_groups, **i32)    # particle-parallel: running particles per group, all ranks
         self.pp = None                                        # particle-parallel driver (None: all particles are local)
+        self.device_status = None                             # status word of the kernel chains (kernel backend only)
         # device-side counters: [0] cycle step (Philox counter), [1] resample jobs this cycle,
         # [2] groups resampled in total
         self.counters = torch.zeros(4, dtype=torch.int64, device=dev)
@@ -338,13 +339,12 @@ class SlotState:
         snap.scalars[0:1].copy_(self.alloc.free_count, non_blocking=True)
         snap.scalars[1:2].copy_(self.alloc.error_flag, non_blocking=True)
         snap.resampled.copy_(self.counters[2:3], non_blocking=True)     # groups resampled so far (device counter)
+        if self.device_status is not None:
+            snap.scalars[2:3].copy_(self.device_status[0:1], non_blocking=True)
         if self.pp is not None:
             if snap.group_active is None:
                 snap.group_active = torch.zeros(self.max_groups, dtype=torch.int32, pin_memory=self._pin)
             snap.group_active.copy_(self.group_active, non_blocking=True)
-            status = getattr(getattr(self.pp, "driver", None), "status", None)
-            if status is not None:
-                snap.scalars[2:3].copy_(status[0:1], non_blocking=True)
         if snap.event is not None:
             snap.event.record()
         return snap

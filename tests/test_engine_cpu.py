@@ -157,9 +157,9 @@ def test_offline_throughput_sharegpt_dataset(tmp_path, capsys):
     assert rec["dataset"] == "sharegpt" and rec["num_prompts"] == 2
 
 
-def test_peer_status_in_the_cycle_snapshot_raises():
-    """A non-zero status word of the cross-rank resampling kernels reaches the host with the cycle snapshot and stops
-    the scheduler instead of letting the ranks' particle sets drift apart."""
+def test_device_status_in_the_cycle_snapshot_raises():
+    """A non-zero status word of the kernels (a wait on another rank that ran out, a failed range check) reaches the
+    host with the cycle snapshot and stops the scheduler instead of letting it serve from a damaged state."""
     import pytest
     eng = _engine()
     sched = eng._sched
@@ -168,7 +168,7 @@ def test_peer_status_in_the_cycle_snapshot_raises():
     sched.step()                         # prefill
     sched._run_decode()
     snap, rids = sched.pending.popleft()
-    assert snap.peer_status == 0
+    assert snap.device_status == 0
     snap.scalars[2] = 2                  # what a timed-out wait on a peer's weights leaves behind
-    with pytest.raises(RuntimeError, match="particle-parallel"):
+    with pytest.raises(RuntimeError, match="device status 2"):
         sched._process_snapshot(snap, rids)
