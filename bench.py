@@ -178,6 +178,15 @@ def main() -> int:
     sched = eng._sched
     vocab = sched.target.cfg.vocab_size
     lens = [args.prompt_len] if args.prompt_len else lognormal_lengths(1, seed=1000 + rank)
+    # bytes a decode cycle cannot avoid reading (weights once per pass, cached keys and values) over the measured copy
+    # bandwidth; the context is taken at the middle of the timed region
+    try:
+        from smcsd_b200.utils.roofline import decode_cycle_floor
+        floor = decode_cycle_floor(sched.target.cfg, sched.draft.cfg, args.gamma,
+                                   defer_bonus=bool(sched.args.defer_bonus), rows=args.n_particles,
+                                   context=lens[0] + (warm + steps // 2) * G, shared_prompt=lens[0])
+    except Exception:                 # an explanatory key must never cost the measurement
+        floor = None
     prompt = random_prompts(lens, vocab, seed=rank)[0]
 
     # ---- device-timed region: K decode cycles of one live request ------------------------------
@@ -301,6 +310,12 @@ def main() -> int:
             "clocks": clocks, "repeats": repeats, "e2e": e2e, "config2": config2, "fused": fused, "fp8": fp8,
             "gpu_launches": int(launches), "device_status": int(status),
         }
+        if floor is not None and not args.quantization and args.kv_cache_dtype == "auto":
+            line["roofline"] = {"floor_ms": floor["floor_ms"], "fraction_of_floor": floor["floor_ms"] / (ms_max / steps),
+                                "weight_gb_per_cycle": floor["weight_bytes"] / 1e9, "kv_gb_per_cycle": floor["kv_bytes"] / 1e9,
+                                "hbm_gbs": floor["hbm_gbs"], "peaks": floor["peaks"],
+                                "note": "floor = bytes one cycle must read from HBM / copy bandwidth (of " +
+                                        floor["peaks"] + "); fraction = floor / device-timed ms per cycle"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
