@@ -121,7 +121,7 @@ def test_abort_request_by_rid(server):
     def call():
         out["r"] = requests.post(server + "/generate", json={
             "input_ids": [9, 8, 7, 6, 5], "rid": "long-1",
-            "sampling_params": {"max_new_tokens": 900, "ignore_eos": True}}, timeout=300)
+            "sampling_params": {"max_new_tokens": 1900, "ignore_eos": True}}, timeout=300)
     t = threading.Thread(target=call)
     t.start()
     time.sleep(0.5)
@@ -181,7 +181,7 @@ def test_pause_continue_and_priority_over_http(server):
 def test_client_that_hangs_up_frees_its_group(server):
     with pytest.raises(requests.exceptions.ReadTimeout):
         requests.post(server + "/generate", json={"input_ids": [7, 7, 7, 7], "sampling_params": {
-            "max_new_tokens": 900, "ignore_eos": True}}, timeout=0.6)
+            "max_new_tokens": 1900, "ignore_eos": True}}, timeout=0.6)
     for _ in range(40):                       # the disconnect is noticed within a poll interval, then the group goes
         info = requests.get(server + "/server_info", timeout=10).json()
         if info["n_running"] == 0 and info["n_waiting"] == 0:
