@@ -124,9 +124,13 @@ def test_abort_request_by_rid(server):
             "sampling_params": {"max_new_tokens": 1900, "ignore_eos": True}}, timeout=300)
     t = threading.Thread(target=call)
     t.start()
-    time.sleep(0.5)
-    a = requests.post(server + "/abort_request", json={"rid": "long-1"}, timeout=10)
-    assert a.status_code == 200 and a.json()["aborted"] == ["long-1"]
+    for _ in range(100):                      # until the request is in flight (a loaded machine may take a while)
+        a = requests.post(server + "/abort_request", json={"rid": "long-1"}, timeout=10)
+        assert a.status_code == 200
+        if a.json()["aborted"] == ["long-1"]:
+            break
+        time.sleep(0.1)
+    assert a.json()["aborted"] == ["long-1"]
     t.join(timeout=60)
     assert not t.is_alive() and out["r"].status_code == 400
     # an id that is not in flight aborts nothing; the server keeps serving
