@@ -278,6 +278,7 @@ class SMCScheduler:
         for g in list(self.waiting):
             if g.rid == rid:
                 self.waiting.remove(g)
+                self.stats["aborted"] += 1
                 self.outbox.append(RequestOutput(rid, [], True, {"type": "abort"}, aborted=True))
                 return
         g = self.running.get(rid)
@@ -287,6 +288,7 @@ class SMCScheduler:
             if self.running.get(rid) is not g:
                 return
             self._release_group(g)
+            self.stats["aborted"] += 1
             self.outbox.append(RequestOutput(rid, [], True, {"type": "abort"}, aborted=True))
 
     def has_work(self) -> bool:

@@ -196,6 +196,7 @@ def test_client_that_hangs_up_frees_its_group(server):
 
 
 def test_metrics_route_is_prometheus_text(server):
+    requests.post(server + "/generate", json={"input_ids": [5, 6, 7], "sampling_params": {"max_new_tokens": 6, "ignore_eos": True}}, timeout=120)
     r = requests.get(server + "/metrics", timeout=10)
     assert r.status_code == 200 and r.headers["content-type"].startswith("text/plain")
     vals = {ln.split()[0]: float(ln.split()[1]) for ln in r.text.splitlines() if ln and not ln.startswith("#")}
