@@ -184,17 +184,17 @@ def build_app(engine, model_name: str = "smc"):
             yield "data: [DONE]\n\n"
         return StreamingResponse(gen(), media_type="text/event-stream")
 
-    app = FastAPI(title="smcsd_b200")
+    from contextlib import asynccontextmanager
     bridge = EngineBridge(engine)
-    app.state.bridge = bridge
 
-    @app.on_event("startup")
-    async def _startup():
-        bridge.start(asyncio.get_running_loop())
-
-    @app.on_event("shutdown")
-    async def _shutdown():
+    @asynccontextmanager
+    async def lifespan(_app):
+        bridge.start(asyncio.get_running_loop())      # the pump thread lives as long as the server
+        yield
         bridge.stop()
+
+    app = FastAPI(title="smcsd_b200", lifespan=lifespan)
+    app.state.bridge = bridge
 
     def _encode(text_or_ids) -> List[int]:
         if isinstance(text_or_ids, str):
