@@ -49,6 +49,7 @@ class EngineBridge:
         self.thread = threading.Thread(target=self._pump, name="smc-engine-pump", daemon=True)
         self.n_served = 0
         self.last_step_time = time.time()
+        self.failed: Optional[str] = None       # first failure of the engine loop; the server reports unhealthy from then on
 
     def start(self, loop: asyncio.AbstractEventLoop) -> None:
         self.loop = loop
@@ -160,6 +161,8 @@ class EngineBridge:
                         eng._check_children()
             except Exception as e:  # surface the failure to every waiting client
                 log.exception("engine pump failed")
+                if self.failed is None:
+                    self.failed = repr(e)
                 for rid in list(self.futures):
                     self.loop.call_soon_threadsafe(
                         self._resolve, rid, dict(output_ids=[], completion_tokens=0, prompt_tokens=0,
@@ -357,6 +360,10 @@ def build_app(engine, model_name: str = "smc"):
 
     @app.get("/health")
     async def health():
+        # a scheduler that raised (device status, a dead scheduler process) does not recover by itself: report it,
+        # so that whatever supervises the server restarts it
+        if bridge.failed is not None:
+            return JSONResponse({"status": "error", "message": bridge.failed}, status_code=503)
         return JSONResponse({"status": "ok"})
 
     @app.get("/health_generate")

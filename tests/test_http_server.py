@@ -203,3 +203,28 @@ def test_metrics_route_is_prometheus_text(server):
     assert vals["smcsd:decode_cycles_total"] >= 1 and vals["smcsd:requests_finished_total"] >= 1
     assert 0.0 <= vals["smcsd:kv_occupancy"] <= 1.0 and vals["smcsd:num_running_reqs"] == 0
     assert "# TYPE smcsd:decode_tokens_total counter" in r.text
+
+
+def test_health_reports_a_failed_engine_loop():
+    """A scheduler step that raises (here injected on the host) answers the waiting client with the error and turns
+    /health to 503 from then on."""
+    from fastapi.testclient import TestClient
+
+    from smcsd_b200 import SMCEngine
+    from smcsd_b200.http_server import build_app
+    eng = SMCEngine("preset:tiny-target", "preset:tiny-draft", n_particles=2, gamma=2, dtype="float32", device="cpu",
+                    max_running_requests=2)
+    real_step, calls = eng._sched.step, {"n": 0}
+
+    def step():
+        calls["n"] += 1
+        if calls["n"] == 3:
+            raise RuntimeError("the kernels reported device status 2 in a decode cycle")
+        return real_step()
+    eng._sched.step = step
+    with TestClient(build_app(eng, "tiny")) as c:
+        assert c.get("/health").status_code == 200
+        r = c.post("/generate", json={"input_ids": [1, 2, 3], "sampling_params": {"max_new_tokens": 40, "ignore_eos": True}})
+        assert r.status_code == 400 and "device status" in r.json()["detail"]
+        h = c.get("/health")
+        assert h.status_code == 503 and "device status" in h.json()["message"]
