@@ -216,3 +216,25 @@ def test_pause_holds_the_queue_and_continue_resumes():
     outs = s.run_until_idle()
     assert any(isinstance(o, RequestOutput) and o.rid == "a" and o.completion_tokens == 12 for o in outs)
     s.check_idle_invariants()
+
+
+def test_materialize_failure_rolls_back_and_aborts_only_that_group():
+    """The fan-out of one admitted group fails (injected on the host): that request comes back aborted with the
+    message, its prompt pages and parent row are returned, and the other requests are served as usual."""
+    s = _sched(max_running_requests=2)
+    real = s.state.allocate_group
+
+    def flaky(rid, **kw):
+        if rid == "bad":
+            raise RuntimeError("injected fan-out failure")
+        return real(rid, **kw)
+    s.state.allocate_group = flaky
+    for rid in ("ok1", "bad", "ok2"):
+        s.add_request(_req(rid, max_new_tokens=9, ignore_eos=True))
+    outs = [o for o in s.run_until_idle() if isinstance(o, RequestOutput) and o.finished]
+    by = {o.rid: o for o in outs}
+    assert by["bad"].aborted and "injected" in by["bad"].error
+    assert by["ok1"].completion_tokens == 9 and by["ok2"].completion_tokens == 9 and not by["ok1"].aborted
+    s.check_idle_invariants()
+    s.alloc.check_conservation()
+    assert s.alloc.available() == s.alloc.size
