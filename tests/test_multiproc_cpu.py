@@ -122,3 +122,14 @@ def test_pause_and_continue_reach_the_scheduler_process():
         assert eng.get_server_info()["paused"] is False
         out = eng.generate(input_ids=_prompts(1), sampling_params=sp, timeout=60.0)
         assert out[0]["completion_tokens"] == 6 and not out[0].get("aborted")
+
+
+def test_a_group_rank_that_exits_mid_run_is_detected():
+    """Two ranks share every request (particle-parallel).  The second rank exits between steps (host-injected); the
+    first would wait for it in its next collective, but the engine sees the dead process, stops the others and raises
+    instead of hanging."""
+    eng = SMCEngine("preset:tiny-target", "preset:tiny-draft", **_kw(pp_size=2, resample_threshold=0.9),
+                    _fault={"die_after": 4, "die_rank": 1})
+    with pytest.raises(RuntimeError, match="scheduler process died"):
+        eng.generate(input_ids=_prompts(2), sampling_params={"max_new_tokens": 400, "ignore_eos": True})
+    assert all(not p.is_alive() for p in eng._procs)
