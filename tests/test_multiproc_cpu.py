@@ -133,3 +133,19 @@ def test_a_group_rank_that_exits_mid_run_is_detected():
     with pytest.raises(RuntimeError, match="scheduler process died"):
         eng.generate(input_ids=_prompts(2), sampling_params={"max_new_tokens": 400, "ignore_eos": True})
     assert all(not p.is_alive() for p in eng._procs)
+
+
+def test_bench_child_process_section_plumbing(tmp_path):
+    """``bench.py --gpus N`` measures its fused-collective paths in child processes with a process group of their own
+    and reads back the record rank 0 wrote; the plumbing-only mode runs the same path on two CPU ranks."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "children.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29637", os.path.join(root, "tests", "mp_bench_children_check.py"), str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, PYTHONPATH=root))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert json.loads(out.read_text()) == {"status": 0, "dry_run_world": 2}
