@@ -20,10 +20,13 @@ def _sched(overlap: bool, **kw):
     return SMCScheduler(EngineArgs(**base).finalize())
 
 
-@pytest.mark.parametrize("seed,overlap", [(0, True), (1, False), (2, True), (3, True)])
-def test_random_operation_sequences_leave_nothing_behind(seed, overlap):
+@pytest.mark.parametrize("seed,overlap,models", [(0, True, "dense"), (1, False, "dense"), (2, True, "dense"),
+                                                 (3, True, "hybrid"), (4, False, "hybrid")])
+def test_random_operation_sequences_leave_nothing_behind(seed, overlap, models):
     rnd = random.Random(seed)
-    s = _sched(overlap)
+    # hybrid: recurrent-state rows are forked, copied by resampling and released next to the KV pages
+    kw = dict(model_path="preset:tiny-hybrid", draft_model_path="preset:tiny-hybrid") if models == "hybrid" else {}
+    s = _sched(overlap, **kw)
     g = torch.Generator().manual_seed(seed)
     sent, ended = {}, {}
 
