@@ -312,28 +312,37 @@ class PpTorch(PpHost):
         st.group_active.copy_(alive.to(st.device))
         gathered = [torch.zeros_like(w_local) for _ in range(self.world)]
         dist.all_gather(gathered, w_local, group=self.group)
-        n_res = 0
+        # every rank derives the same plans; ancestors are never destinations, so everything another rank needs from
+        # this one can be exported before any job is applied and exchanged in one collective per cycle
+        plans = []
+        exports = {}
         for i, row in enumerate(rows):
             go, jobs, inc = plan_global([g[i] for g in gathered], st.threshold, st.seed, st.step, row)
             if not go:
                 continue
-            n_res += 1
+            plans.append((row, jobs, inc))
             slots = st.row_slots[row]
             for dr, di, sr, si in jobs:
-                if dr == sr:
-                    if dr == self.rank:
-                        st._copy_particle(slots[di], slots[si])
+                if dr != sr and sr == self.rank and (row, si) not in exports:
+                    exports[(row, si)] = self._export(st, slots[si])
+        if not plans:
+            return 0
+        remote = self.all_gather_objects(exports)
+        for row, jobs, inc in plans:
+            slots = st.row_slots[row]
+            for dr, di, sr, si in jobs:
+                if dr != self.rank:
                     continue
-                box = [self._export(st, slots[si]) if self.rank == sr else None]
-                dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, sr), group=self.group)
-                if self.rank == dr:
-                    self._import(st, slots[di], box[0])
+                if sr == self.rank:
+                    st._copy_particle(slots[di], slots[si])
+                else:
+                    self._import(st, slots[di], remote[sr][(row, si)])
             idx = torch.tensor(slots, dtype=torch.long, device=st.device)
             st.interval_weights[idx] = 0.0
             st.log_weights[idx] = 0.0
             st.group_log_Z[row] += inc
-        st.n_resamples += n_res
-        return n_res
+        st.n_resamples += len(plans)
+        return len(plans)
 
 
 class PpNative(PpHost):

@@ -74,3 +74,31 @@ def test_output_law_and_normalising_constant(threshold):
     assert abs(float(zhat.mean()) - 1.0) < max(4 * se, 0.03), (float(zhat.mean()), se)
     if threshold == 1.0:
         assert eng._sched.stats["resampled_groups"] >= n           # every group was resampled after its first cycle
+
+
+def test_particle_parallel_groups_keep_the_same_statistics():
+    """The 32 particles of every request sharded over two gloo ranks, resampling after every cycle: weights are
+    exchanged, every rank derives the same global plan and ancestors cross ranks.  The returned sequences must still
+    follow the target law and exp(log_Z_hat) must still average to one."""
+    tgt, drf = _cfgs()
+    prompt = [1, 5, 2, 7, 3]
+    p_t, p_d = _marginals(prompt)
+    n, counts, z = 0, torch.zeros(V), []
+    with SMCEngine(tgt, drf, n_particles=32, gamma=2, draft_temperature=T, target_temperature=T,
+                   resample_threshold=1.0, max_running_requests=16, pp_size=2, **_kw()) as eng:
+        for _ in range(5):
+            outs = eng.generate(input_ids=[prompt] * 96, sampling_params={"max_new_tokens": 7, "ignore_eos": True})
+            for o in outs:
+                assert len(o["smc_particle_output_ids"]) == 32
+                counts[o["output_ids"][1]] += 1
+                z.append(o["smc_log_Z_hat"])
+                n += 1
+        info = eng.get_server_info()
+    assert info["stats"]["resampled_groups"] >= n
+    emp = counts / n
+    tv_target = 0.5 * float((emp - p_t).abs().sum())
+    tv_draft = 0.5 * float((emp - p_d).abs().sum())
+    assert tv_target < 0.16 and tv_target < tv_draft - 0.04, (tv_target, tv_draft)
+    zhat = torch.tensor(z, dtype=torch.float64).exp()
+    se = float(zhat.std()) / n ** 0.5
+    assert abs(float(zhat.mean()) - 1.0) < max(4 * se, 0.04), (float(zhat.mean()), se)
