@@ -149,3 +149,16 @@ def test_bench_child_process_section_plumbing(tmp_path):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, PYTHONPATH=root))
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert json.loads(out.read_text()) == {"status": 0, "dry_run_world": 2}
+
+
+def test_particle_parallel_hybrid_models_cpu():
+    """Gated-DeltaNet models with the particles sharded over two ranks: a cross-rank ancestor brings its recurrent
+    state (conv window and temporal state of every linear-attention layer) along with its KV rows."""
+    sp = {"max_new_tokens": 14, "ignore_eos": True}
+    kw = _kw(pp_size=2, resample_threshold=0.9, draft_temperature=1.0, target_temperature=0.5)
+    with SMCEngine("preset:tiny-hybrid", "preset:tiny-hybrid", **kw) as eng:
+        out = eng.generate(input_ids=_prompts(3), sampling_params=sp)
+        info = eng.collective_rpc("server_info")[0].value
+    assert [o["completion_tokens"] for o in out] == [14] * 3
+    assert all(len(o["smc_particle_output_ids"]) == 4 for o in out)
+    assert info["stats"]["resampled_groups"] > 0
