@@ -23,13 +23,9 @@ EPIS = {"store": K.EPI_STORE_F32, "resid": K.EPI_RESID_F32, "swiglu": K.EPI_SWIG
 
 
 def peaks():
-    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-    p = os.path.join(here, "MEASURED_PEAKS.json")
-    if os.path.exists(p):
-        with open(p) as f:
-            j = json.load(f)
-        return j.get("hbm_gbs", 6650.0), j.get("bf16_tflops", 1590.0), "measured"
-    return 6650.0, 1590.0, "fallback"
+    """(HBM copy GB/s, bf16 TFLOP/s, "measured" | "fallback"): the machine's measured-peaks record, else the fallback."""
+    from ..utils.roofline import measured_peaks
+    return measured_peaks()
 
 
 def time_graph(fn, inner: int, reps: int = 20) -> float:
