@@ -60,14 +60,14 @@ class EngineBridge:
         self.thread.join(timeout=10)
 
     async def submit(self, input_ids: List[int], sp: SamplingParams, rid: Optional[str] = None,
-                     priority: Optional[int] = None) -> dict:
+                     priority: Optional[int] = None, extra: Optional[Dict[str, Any]] = None) -> dict:
         rid = rid or uuid.uuid4().hex
         if rid in self.futures:
             raise ValueError(f"request id {rid!r} is already in flight")
         fut = self.loop.create_future()
         self.futures[rid] = fut
         req = GenerateRequest(rid, list(input_ids), sp, eos_token_ids=self.engine._eos_ids(), arrival_time=time.time(),
-                              priority=priority)
+                              priority=priority, **(extra or {}))
         self.inbox.put(req)
         return await fut
 
@@ -209,12 +209,33 @@ def build_app(engine, model_name: str = "smc"):
     def _decode(ids: List[int]) -> str:
         return engine.tokenizer.decode(ids, skip_special_tokens=True) if engine.tokenizer is not None else ""
 
+    def _unsupported(body: Dict[str, Any]) -> Dict[str, Any]:
+        """Request features this engine refuses (the scheduler answers each with its message, like the reference's
+        request validation, smcsd/common/utils.py:150-167): they are passed on, not dropped silently."""
+        x: Dict[str, Any] = {}
+        if body.get("return_logprob") or body.get("logprobs") or body.get("top_logprobs"):
+            x["return_logprob"] = True
+        if body.get("return_hidden_states"):
+            x["return_hidden_states"] = True
+        if body.get("return_routed_experts"):
+            x["return_routed_experts"] = True
+        if body.get("input_embeds") is not None:
+            x["input_embeds"] = True
+        if body.get("image_data") is not None:
+            x["image_data"] = True
+        sp = body.get("sampling_params") if isinstance(body.get("sampling_params"), dict) else {}
+        if any(body.get(k) or sp.get(k) for k in ("json_schema", "regex", "ebnf", "structural_tag")) \
+                or body.get("response_format"):
+            x["grammar"] = True
+        return x
+
     async def _one(ids: List[int], params: Optional[dict], rid: Optional[str] = None,
-                   priority: Optional[int] = None, http: Optional[Request] = None) -> dict:
+                   priority: Optional[int] = None, http: Optional[Request] = None,
+                   extra: Optional[Dict[str, Any]] = None) -> dict:
         try:
             sp = SamplingParams.from_dict(params).normalize()
             rid = rid or uuid.uuid4().hex
-            task = asyncio.ensure_future(bridge.submit(ids, sp, rid, None if priority is None else int(priority)))
+            task = asyncio.ensure_future(bridge.submit(ids, sp, rid, None if priority is None else int(priority), extra))
             while http is not None and not task.done():
                 # a client that hung up frees its slots and pages now, not when its generation would have ended
                 await asyncio.wait([task], timeout=0.25)
@@ -246,14 +267,15 @@ def build_app(engine, model_name: str = "smc"):
         if rids is None or len(rids) != len(items):
             raise HTTPException(400, "rid must be one id per input")
         prio = body.get("priority")                          # honoured with --enable-priority-scheduling only
+        extra = _unsupported(body)
         async def run():
-            outs = await asyncio.gather(*[_one(_encode(x), p, r, prio, request) for x, p, r in zip(items, plist, rids)])
+            outs = await asyncio.gather(*[_one(_encode(x), p, r, prio, request, extra) for x, p, r in zip(items, plist, rids)])
             return outs if many else outs[0]
         if body.get("stream"):
             encoded = [_encode(x) for x in items]          # malformed input fails before the stream opens
 
             async def run_stream():
-                outs = await asyncio.gather(*[_one(e, p, r, prio, request) for e, p, r in zip(encoded, plist, rids)])
+                outs = await asyncio.gather(*[_one(e, p, r, prio, request, extra) for e, p, r in zip(encoded, plist, rids)])
                 return outs if many else outs[0]
             return _sse(run_stream)
         return await run()
@@ -280,10 +302,14 @@ def build_app(engine, model_name: str = "smc"):
             params["stop"] = body["stop"]
         if body.get("stop_token_ids"):
             params["stop_token_ids"] = body["stop_token_ids"]
+        if int(body.get("n") or 1) != 1 or int(body.get("best_of") or 1) != 1:
+            raise HTTPException(400, "n and best_of other than 1 are not supported: the particles of a request are not "
+                                     "independent samples")
         encoded = [_encode(p) for p in prompts]
+        extra = _unsupported(body)
 
         async def run():
-            outs = await asyncio.gather(*[_one(e, params, http=request) for e in encoded])
+            outs = await asyncio.gather(*[_one(e, params, http=request, extra=extra) for e in encoded])
             choices = [{"index": i, "text": o["text"], "token_ids": o["output_ids"],
                         "finish_reason": "length" if o["meta_info"]["finish_reason"]["type"] == "length" else "stop"}
                        for i, o in enumerate(outs)]
@@ -318,8 +344,13 @@ def build_app(engine, model_name: str = "smc"):
         if body.get("stop_token_ids"):
             params["stop_token_ids"] = body["stop_token_ids"]
 
+        if int(body.get("n") or 1) != 1:
+            raise HTTPException(400, "n other than 1 is not supported: the particles of a request are not independent "
+                                     "samples")
+        extra = _unsupported(body)
+
         async def run():
-            o = await _one(ids, params, http=request)
+            o = await _one(ids, params, http=request, extra=extra)
             fr = "length" if o["meta_info"]["finish_reason"]["type"] == "length" else "stop"
             pt, ct = o["meta_info"]["prompt_tokens"], o["meta_info"]["completion_tokens"]
             return {"id": "chatcmpl-" + uuid.uuid4().hex, "object": "chat.completion", "created": int(time.time()),

@@ -228,3 +228,16 @@ def test_health_reports_a_failed_engine_loop():
         assert r.status_code == 400 and "device status" in r.json()["detail"]
         h = c.get("/health")
         assert h.status_code == 503 and "device status" in h.json()["message"]
+
+
+def test_unsupported_request_features_are_refused_with_a_message(server):
+    base = {"input_ids": [1, 2, 3], "sampling_params": {"max_new_tokens": 4}}
+    for extra, word in (({"return_logprob": True}, "return_logprob"), ({"return_hidden_states": True}, "hidden_states"),
+                        ({"image_data": "x"}, "multimodal"), ({"input_embeds": [[0.1]]}, "input_embeds"),
+                        ({"sampling_params": {"max_new_tokens": 4, "json_schema": "{}"}}, "grammar")):
+        r = requests.post(server + "/generate", json={**base, **extra}, timeout=60)
+        assert r.status_code == 400 and word in r.json()["detail"], (extra, r.text)
+    r = requests.post(server + "/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 4, "logprobs": 2}, timeout=60)
+    assert r.status_code == 400 and "return_logprob" in r.json()["detail"]
+    r = requests.post(server + "/v1/completions", json={"prompt": [5, 6, 7], "max_tokens": 4, "n": 3}, timeout=60)
+    assert r.status_code == 400 and "not supported" in r.json()["detail"]
