@@ -250,10 +250,19 @@ class PpHost:
         """Host rendezvous of the ranks after the device has drained.  The in-kernel waits on peers are bounded (about a
         second); host work whose length differs per rank (first-launch module loading, a prefill, a graph capture)
         is followed by this call so that no rank enters a cycle's exchange far ahead of the others."""
+        import datetime
+        import os
+
         import torch.distributed as dist
         if torch.cuda.is_available():
             torch.cuda.synchronize()
-        dist.barrier(group=self.group)
+        # a rank that never arrives (it died, or it took another path through the scheduler) ends this wait with an
+        # error that names it, instead of blocking the others for the process group's half-hour default
+        limit = datetime.timedelta(seconds=float(os.environ.get("SMC_PP_ALIGN_TIMEOUT_S", "300")))
+        if dist.get_backend(self.group) == "gloo":
+            dist.monitored_barrier(group=self.group, timeout=limit)
+        else:
+            dist.barrier(group=self.group)
 
 
 class PpTorch(PpHost):

@@ -154,6 +154,8 @@ def run_scheduler_process(args: EngineArgs, rank: int, world: int, ports: PortAr
                     stop = True
             if stop:
                 break
+            if fault.get("stall_rank") == rank and sched.waiting:
+                time.sleep(3600)                    # injected: this rank never reaches the step its peers wait in
             outs = sched.step() if (sched.has_work() or msgs) else []
             if sched.paused and not msgs:
                 time.sleep(0.005)                   # paused with work queued: wait for the next message, do not spin

@@ -162,3 +162,17 @@ def test_particle_parallel_hybrid_models_cpu():
     assert [o["completion_tokens"] for o in out] == [14] * 3
     assert all(len(o["smc_particle_output_ids"]) == 4 for o in out)
     assert info["stats"]["resampled_groups"] > 0
+
+
+def test_a_group_rank_that_stalls_ends_the_others_wait(monkeypatch):
+    """One of two particle-parallel ranks never reaches the step (host-injected stall).  Its peer's host rendezvous
+    after the prefill is time-limited: it fails naming the missing rank, the engine sees the crash and raises, well
+    before any default collective timeout."""
+    import time
+    monkeypatch.setenv("SMC_PP_ALIGN_TIMEOUT_S", "4")
+    eng = SMCEngine("preset:tiny-target", "preset:tiny-draft", **_kw(pp_size=2), _fault={"stall_rank": 1})
+    t0 = time.time()
+    with pytest.raises(RuntimeError, match="scheduler process died"):
+        eng.generate(input_ids=_prompts(1), sampling_params={"max_new_tokens": 20, "ignore_eos": True})
+    assert time.time() - t0 < 60
+    assert all(not p.is_alive() for p in eng._procs)
