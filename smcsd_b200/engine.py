@@ -18,7 +18,7 @@ import pickle
 import signal
 import time
 import uuid
-from typing import Any, Dict, List, Optional, Sequence, Union
+from typing import Any, Dict, List, Optional, Union
 
 from .config import EngineArgs
 from .io_types import (AbortReq, GenerateRequest, ParticleOutput, ProfileReq, RequestOutput, RpcReq, SamplingParams,

@@ -14,7 +14,7 @@ smcsd/model_executor/smc_model_runner.py:109-239.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence
+from typing import List, Optional
 
 import torch
 

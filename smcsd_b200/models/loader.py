@@ -11,7 +11,7 @@ import mmap
 import os
 import struct
 import warnings
-from typing import Dict, Iterable, Iterator, List, Optional, Tuple
+from typing import Dict, Iterable, List, Optional, Tuple
 
 import torch
 

@@ -11,7 +11,7 @@ smcsd/model_executor/smc_draft_phase_graph_runner.py:824-1197, smcsd/core/schedu
 from __future__ import annotations
 
 import os
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional
 
 import torch
 

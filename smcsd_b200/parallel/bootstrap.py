@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import datetime
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, List, Optional
 
 import torch

@@ -16,7 +16,7 @@ keeps all particles of a group on one GPU and resamples by pointer copies only
 from __future__ import annotations
 
 import ctypes as C
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Callable, List, Sequence, Tuple
 
 import torch
 

@@ -71,8 +71,6 @@ def run_scheduler_process(args: EngineArgs, rank: int, world: int, ports: PortAr
                           parent_pid: int, fault: Optional[dict] = None) -> None:
     """Entry point of one scheduler process.  ``fault`` injects host-side failures for the
     tests (raise during init, never report ready, die after k iterations)."""
-    import torch
-    import torch.distributed as dist
     import zmq
 
     from ..io_types import AbortReq, GenerateRequest, ProfileReq, RpcReq, ShutdownReq

@@ -14,19 +14,19 @@ import logging
 import os
 import time
 from collections import deque
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Deque, Dict, List, Optional
 
 import torch
 
 from ..config import EngineArgs
-from ..io_types import (AbortReq, GenerateRequest, ParticleOutput, ProfileReq, RequestOutput, RpcReq, RpcResp,
+from ..io_types import (GenerateRequest, ParticleOutput, ProfileReq, RequestOutput, RpcReq, RpcResp,
                         validate_request)
 from ..memory.pools import BlockTable, KVPool, KVSpec, PageAllocator, StatePool, cobudget_pages
 from ..models import build_model
 from ..utils import debug as smc_debug
 from ..utils import profiling
-from .slot_state import CycleInputs, HostSnapshot, SlotState
+from .slot_state import HostSnapshot, SlotState
 from .worker import PrefillItem, SMCWorker
 
 log = logging.getLogger("smcsd_b200.scheduler")
