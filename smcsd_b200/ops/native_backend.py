@@ -980,8 +980,19 @@ class NativeRunner:
                 st.pp.align()              # every rank enters the eager cycle's weight exchange together
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(s):
-                self._full_cycle(st)
+            # The eager cycle only has to launch every kernel once before the capture; its effects are rolled back by
+            # putting the metadata back.  That is exact for ancestor copies on one GPU (they copy page ids), but a
+            # cross-GPU adoption refills the destination's released pages with the ancestor's KV rows.  So with
+            # particle-parallel groups the eager cycle runs with resampling off on every rank (the exchange, plan and
+            # fetch kernels still launch and find nothing to do).
+            threshold = st.threshold
+            if st.pp is not None:
+                st.threshold = 0.0
+            try:
+                with torch.cuda.stream(s):
+                    self._full_cycle(st)
+            finally:
+                st.threshold = threshold
             torch.cuda.current_stream().wait_stream(s)
             torch.cuda.synchronize()
             self._restore_state(st, saved)
@@ -1008,20 +1019,12 @@ class NativeRunner:
         return ts
 
     def _save_state(self, st):
-        saved = [t.clone() for t in self._mutable(st)]
-        # A cross-GPU adoption in the eager cycle moves KV rows: it releases the destination's post-prompt pages, pops
-        # them again and fills them with the ancestor's rows.  Putting the block table back is then not enough, the
-        # rows themselves have to come back too (ancestor copies on one GPU only copy page ids).
-        kv = save_kv_suffix(st, [self.target.kv, self.draft.kv]) if st.pp is not None else None
-        return saved, kv
+        return [t.clone() for t in self._mutable(st)]
 
     def _restore_state(self, st, saved) -> None:
-        saved, kv = saved
         step = st.counters[0:1].clone()
         for t, s in zip(self._mutable(st), saved):
             t.copy_(s)
-        if kv is not None:
-            restore_kv_suffix(kv, [self.target.kv, self.draft.kv])
         if st.pp is not None:
             # cross-rank counters advanced during the warm-up cycle; keep the cycle number in step with them
             st.counters[0:1].copy_(step)
@@ -1029,30 +1032,6 @@ class NativeRunner:
     def check_status(self) -> int:
         self._status_host.copy_(self.status)
         return int(self._status_host[0])
-
-
-def save_kv_suffix(st, pools):
-    """Copies of the KV rows behind every active slot's post-prompt pages, for all layers of ``pools``.
-    Returns ``(page ids, [(k rows, v rows) per pool])``; page ids are unique, so the restore is a plain scatter."""
-    slots = st.active_slots.long()
-    if slots.numel() == 0:
-        return None
-    lo = st.prompt_lens[slots].tolist()
-    hi = st.seq_lens[slots].tolist()
-    rows = [st.bt.table[s, p:l] for s, p, l in zip(slots.tolist(), lo, hi) if l > p]
-    if not rows:
-        return None
-    pages = torch.unique(torch.cat(rows)).long()
-    return pages, [(pool.k[:, pages], pool.v[:, pages]) for pool in pools]      # indexing by a tensor copies
-
-
-def restore_kv_suffix(saved, pools) -> None:
-    if saved is None:
-        return
-    pages, rows = saved
-    for pool, (k, v) in zip(pools, rows):
-        pool.k[:, pages] = k
-        pool.v[:, pages] = v
 
 
 def create(sched, comm=None):
