@@ -976,8 +976,7 @@ class NativeRunner:
             # warm up once eagerly on a side stream (also JIT-free: everything is precompiled), then capture
             gr = torch.cuda.CUDAGraph()
             saved = self._save_state(st)
-            if st.pp is not None:
-                st.pp.align()              # every rank enters the eager cycle's weight exchange together
+            self._align_ranks(st)          # every rank enters the eager cycle's cross-rank waits together
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
             # The eager cycle only has to launch every kernel once before the capture; its effects are rolled back by
@@ -1002,9 +1001,18 @@ class NativeRunner:
             self.launches_per_cycle = K.launch_count - n0
             self._restore_state(st, saved)
             self.graphs[key] = gr
-            if st.pp is not None:
-                st.pp.align()              # capture time differs per rank; replay starts together
+            self._align_ranks(st)          # capture time differs per rank; replay starts together
         gr.replay()
+
+    def _align_ranks(self, st) -> None:
+        """Host rendezvous of the ranks that share requests (particle- or tensor-parallel) around a graph capture: the
+        in-kernel waits on peers are bounded at about a second, and eager launching and capturing take the ranks
+        different amounts of host time."""
+        if st.pp is not None:
+            st.pp.align()
+        elif self.comm is not None and getattr(self.comm, "group_size", 1) > 1:
+            torch.cuda.synchronize()
+            self.comm.barrier()
 
     # capture runs the cycle for real; put the mutable state back afterwards
     def _mutable(self, st) -> List[torch.Tensor]:
